@@ -1,0 +1,231 @@
+/*
+ * CPU oracle for the LUT-layer hot path.  TEST INFRASTRUCTURE ONLY.
+ *
+ * This file is a plain-C restatement of the arithmetic the reference performs on its
+ * CPU path (the reference executes its kernel source as nested host loops, batch outermost,
+ * see spiky_cuda/misc/misc.h:119-129).  It is used as the checker in tests/, in the smoke
+ * test and as the timed CPU baseline of the benchmark; nothing in the product path may
+ * call it.  Loop nests follow the reference's host loop order so that fp32 results agree
+ * with the reference CPU build to the last bit where the reference itself is
+ * deterministic; the golden fixtures under tests/golden/ (produced by the real reference)
+ * pin that.
+ *
+ * Conventions shared by every function:
+ *   anchors  int32 [Nt][Nc][2]; a pair with either end == -1 (0xFFFFFFFF) is skipped
+ *   W        fp32 [Nt][T][O] flat, element (t*T + row)*O + o   (fully connected layers)
+ *   int_mode 0: fp32 accumulators; 1: int32 fixed-point accumulators (scale 0xFFFFF * rescaler,
+ *            spiky_cuda/misc/misc.h:92-103), converted to fp32 at the end of each call
+ *            (spiky_cuda/lut/lut_runtime_kernels_logic.proto:200-213)
+ *
+ * Compile with:  gcc -O2 -ffp-contract=off -fno-fast-math  (no FMA contraction, IEEE semantics)
+ */
+#include <math.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+
+#define ORC_DENOM 1048575.0                 /* DENOMINATOR32, misc.h:101 */
+#define ORC_DENOM_RECIP 9.536752259018191e-07 /* DENOMINATOR32_RECIPROC, misc.h:102 */
+#define ORC_EPS 0.00000000000000001         /* EPS, misc.h:90 */
+#define ORC_NO_ANCHOR (-1)
+
+/*
+ * Thread count of the batch-parallel loops.  1 reproduces the reference, whose CPU path is
+ * single-threaded by construction (misc.h:119-129).  Larger values only split loops whose
+ * iterations touch disjoint cells (samples for outputs / input gradients, detectors for weight
+ * gradients), so every result stays bit-identical; they exist for the "all host cores" baseline.
+ */
+static int orc_threads = 1;
+void orc_set_threads(int n) { orc_threads = n > 0 ? n : 1; }
+#define ORC_PARALLEL_FOR _Pragma("omp parallel for schedule(static) num_threads(orc_threads)")
+
+/* ROUNDED_COMPARISON_GREATER(delta, 0, eps), misc.h:16 */
+static inline int orc_greater(float delta, float cmp_eps) {
+    if (cmp_eps == 0.0f) return delta > 0.0f;
+    if (fabs((double)delta) < (double)cmp_eps) return 0;
+    return delta > 0.0f;
+}
+
+/* surrogate derivative up(m) = +-0.5 / (1+|m|)^2, zero counts as negative
+ * (lut_runtime_kernels_logic.proto:1339-1345) */
+static inline double orc_up(float m) {
+    double du = (double)m;
+    if (du > 0) {
+        du = 1.0 / (1.0 + fabs(du));
+        du *= 0.5 * du;
+    } else {
+        du = 1.0 / (1.0 + fabs(du));
+        du *= -0.5 * du;
+    }
+    return du;
+}
+
+/* convert_integers_to_floats_logic, proto:200-213 */
+void orc_int_to_float(float *buf, int64_t n, double rescaler) {
+    for (int64_t i = 0; i < n; i++) {
+        double y = (double)(*(int32_t *)(buf + i)) * ORC_DENOM_RECIP;
+        buf[i] = (float)(y / rescaler);
+    }
+}
+
+/*
+ * check_detectors_logic / check_detectors_eval_logic / check_detectors_seq*_logic
+ * (proto:1050-1158, 1589-1707).  rows = B for non-sequence layers, B*S for sequence layers.
+ * min_delta / min_k may be NULL (eval variant).
+ */
+void orc_check_detectors(const float *x, int64_t rows, int I, const int32_t *anchors, int Nt, int Nc,
+                         float cmp_eps, int32_t *idx, float *min_delta, int32_t *min_k) {
+    ORC_PARALLEL_FOR
+    for (int64_t r = 0; r < rows; r++) {
+        const float *xr = x + r * (int64_t)I;
+        for (int t = 0; t < Nt; t++) {
+            const int32_t *ap = anchors + (int64_t)t * Nc * 2;
+            int32_t li = 0;
+            float md = 0.0f;
+            int32_t mk = -1;
+            for (int k = 0; k < Nc; k++) {
+                int32_t a1 = ap[2 * k], a2 = ap[2 * k + 1];
+                if (a1 == ORC_NO_ANCHOR || a2 == ORC_NO_ANCHOR) continue;
+                float delta = xr[a1] - xr[a2];
+                if (orc_greater(delta, cmp_eps)) li |= (1 << k);
+                if (mk == -1 || fabsf(delta) < fabsf(md)) {
+                    md = delta;
+                    mk = k;
+                }
+            }
+            idx[r * Nt + t] = li;
+            if (min_delta) min_delta[r * Nt + t] = md;
+            if (min_k) min_k[r * Nt + t] = mk;
+        }
+    }
+}
+
+/*
+ * check_positional_embeddings[_eval]_logic (proto:1709-1805): sign bits of pe[d][t][:],
+ * first minimal |value| and its dimension.  pe is [(S-1)][Nt][Npe].
+ */
+void orc_check_positional(const float *pe, int S, int Nt, int Npe, float cmp_eps, int32_t *pidx,
+                          float *pmin, int32_t *pmin_k) {
+    int64_t n = (int64_t)(S - 1) * Nt;
+    for (int64_t i = 0; i < n; i++) {
+        const float *p = pe + i * Npe;
+        int32_t li = 0, mk = -1;
+        float md = 0.0f;
+        for (int d = 0; d < Npe; d++) {
+            float v = p[d];
+            if (orc_greater(v, cmp_eps)) li |= (1 << d);
+            if (mk == -1 || fabsf(v) < fabsf(md)) {
+                md = v;
+                mk = d;
+            }
+        }
+        pidx[i] = li;
+        if (pmin) pmin[i] = md;
+        if (pmin_k) pmin_k[i] = mk;
+    }
+}
+
+/*
+ * fill_outputs_non_seq_fc_logic (proto:1214-1299) + the int->float pass of
+ * LUTRuntimeContext::forward_step (lut_runtime.cu:200-210).
+ * y is accumulated into (caller zero-fills).  Gb = backward_group_size: detectors are summed in
+ * double inside blocks of Gb, each block sum is rounded (fp32) or truncated (int32 fixed point)
+ * and then added to y.
+ */
+void orc_nonseq_fc_forward(const float *W, const int32_t *idx, float *y, int64_t B, int O, int Nt, int T,
+                           int Gb, int int_mode, double rescaler) {
+    int n_blocks = (Nt + Gb - 1) / Gb;
+    ORC_PARALLEL_FOR
+    for (int64_t b = 0; b < B; b++) {
+        const int32_t *li = idx + b * Nt;
+        float *yb = y + b * O;
+        for (int blk = 0; blk < n_blocks; blk++) {
+            int t0 = blk * Gb, t1 = t0 + Gb < Nt ? t0 + Gb : Nt;
+            for (int o = 0; o < O; o++) {
+                double s = 0.0;
+                for (int t = t0; t < t1; t++) s += (double)W[((int64_t)t * T + li[t]) * O + o];
+                if (int_mode)
+                    *(int32_t *)(yb + o) += (int32_t)(s * ORC_DENOM * rescaler);
+                else
+                    yb[o] += (float)s;
+            }
+        }
+    }
+    if (int_mode) orc_int_to_float(y, B * O, rescaler);
+}
+
+/*
+ * propagate_through_detectors_non_seq_fc_logic (proto:1421-1499) followed by
+ * gather_w_gradients_non_seq_fc_logic (proto:1547-1585, helper :716-819) and the int->float passes
+ * of LUTRuntimeContext::backward_backprop (lut_runtime.cu:365-396).
+ *   G        forward_group_size: outputs are processed in blocks of G; every block issues its own
+ *            (rounded / truncated) contribution to dX
+ *   lr_meta  SynapseMeta.learning_rate
+ *   ext_lr   < 0: write lr_meta*dY into dW (caller zero-fills);  >= 0: "Internal" policy, dW must be
+ *            NULL and W is updated in place by -ext_lr*lr_meta*dY (lut_runtime.cu:236-238, 343-361)
+ * dX is accumulated into (caller zero-fills).
+ */
+void orc_nonseq_fc_backward(float *W, const float *dY, const int32_t *anchors, const int32_t *idx,
+                            const float *min_delta, const int32_t *min_k, float *dX, float *dW, int64_t B,
+                            int I, int O, int Nt, int Nc, int T, int G, double lr_meta, double ext_lr,
+                            int int_mode, double rescaler) {
+    int n_ob = (O + G - 1) / G;
+    ORC_PARALLEL_FOR
+    for (int64_t b = 0; b < B; b++) {
+        const float *dy = dY + b * O;
+        float *dx = dX + b * (int64_t)I;
+        for (int t = 0; t < Nt; t++) {
+            int32_t li = idx[b * Nt + t];
+            int32_t k = min_k[b * Nt + t];
+            int64_t row = ((int64_t)t * T + li) * O;
+            int64_t alt = ((int64_t)t * T + (li ^ (1 << k))) * O;
+            for (int ob = 0; ob < n_ob; ob++) {
+                int o0 = ob * G, o1 = o0 + G < O ? o0 + G : O;
+                double du = orc_up(min_delta[b * Nt + t]);
+                double ms = 0.0, as = 0.0;
+                for (int o = o0; o < o1; o++) {
+                    double g = (double)dy[o];
+                    ms += (double)W[row + o] * g;
+                    as += (double)W[alt + o] * g;
+                }
+                du *= ms - as;
+                if (fabs(du) > ORC_EPS) {
+                    int32_t a1 = anchors[((int64_t)t * Nc + k) * 2], a2 = anchors[((int64_t)t * Nc + k) * 2 + 1];
+                    if (int_mode) {
+                        int32_t d = (int32_t)(du * ORC_DENOM * rescaler);
+                        *(int32_t *)(dx + a1) += d;
+                        *(int32_t *)(dx + a2) -= d;
+                    } else {
+                        dx[a1] += du;
+                        dx[a2] -= du;
+                    }
+                }
+            }
+        }
+    }
+    double lr = lr_meta;
+    if (ext_lr >= 0) lr *= -ext_lr;
+    float *target = ext_lr >= 0 ? W : dW;
+    /* every cell belongs to one detector and receives its contributions in batch order, exactly as
+     * in the reference's batch-outermost loop; detectors are therefore independent */
+    ORC_PARALLEL_FOR
+    for (int t = 0; t < Nt; t++) {
+        for (int64_t b = 0; b < B; b++) {
+            const float *dy = dY + b * O;
+            int64_t row = ((int64_t)t * T + idx[b * Nt + t]) * O;
+            for (int o = 0; o < O; o++) {
+                double g = (double)dy[o];
+                if (fabs(g) > ORC_EPS) {
+                    if (int_mode)
+                        *(int32_t *)(target + row + o) += (int32_t)(g * lr * ORC_DENOM * rescaler);
+                    else
+                        target[row + o] += (float)(g * lr);
+                }
+            }
+        }
+    }
+    if (int_mode) {
+        orc_int_to_float(dX, B * (int64_t)I, rescaler);
+        if (dW) orc_int_to_float(dW, (int64_t)Nt * T * O, rescaler);
+    }
+}

@@ -1,0 +1,130 @@
+"""numpy front-end of the CPU oracle (``lut_oracle.c``).  TEST INFRASTRUCTURE ONLY.
+
+Only the tests, the smoke test and the benchmark's CPU-baseline leg may import this module;
+the product package never does.  Every function takes and returns numpy arrays and mirrors one
+runtime call of the reference's ``LUTDataManagerF`` / ``LUTDataManagerI``
+(spiky_cuda/lut/lut.cu:629-1180).
+"""
+import ctypes
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_SO = os.path.join(_HERE, "_build", "liblut_oracle.so")
+_lib = None
+
+_f = ctypes.c_float
+_d = ctypes.c_double
+_i = ctypes.c_int
+_l = ctypes.c_int64
+_p = ctypes.c_void_p
+
+
+def build(force=False):
+    """Compile the C oracle with the host gcc (a few seconds)."""
+    src = os.path.join(_HERE, "lut_oracle.c")
+    if force or not os.path.exists(_SO) or os.path.getmtime(_SO) < os.path.getmtime(src):
+        cc = "/usr/bin/gcc" if os.path.exists("/usr/bin/gcc") else "gcc"
+        subprocess.check_call(["make", "-C", _HERE, "-B", f"CC={cc}"], stdout=subprocess.DEVNULL)
+    return _SO
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        build()
+        _lib = ctypes.CDLL(_SO)
+    return _lib
+
+
+def _ptr(a):
+    if a is None:
+        return None
+    assert a.flags["C_CONTIGUOUS"], "oracle arrays must be contiguous"
+    return a.ctypes.data_as(_p)
+
+
+def _f32(a):
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+def _i32(a):
+    return np.ascontiguousarray(a, dtype=np.int32)
+
+
+def set_threads(n):
+    """Number of OpenMP threads used by the batch-parallel baseline loops (1 = reference-like)."""
+    lib().orc_set_threads(_i(int(n)))
+
+
+def check_detectors(x, anchors, n_detectors, n_anchors, cmp_eps=0.0, train=True):
+    """x [rows, I] -> idx int32 [rows, Nt] (+ min_delta f32, min_k int32 when train)."""
+    x = _f32(x)
+    rows, n_in = x.shape
+    anchors = _i32(anchors).reshape(-1)
+    idx = np.zeros((rows, n_detectors), np.int32)
+    md = np.zeros((rows, n_detectors), np.float32) if train else None
+    mk = np.zeros((rows, n_detectors), np.int32) if train else None
+    lib().orc_check_detectors(_ptr(x), _l(rows), _i(n_in), _ptr(anchors), _i(n_detectors), _i(n_anchors),
+                              _f(cmp_eps), _ptr(idx), _ptr(md), _ptr(mk))
+    return (idx, md, mk) if train else idx
+
+
+def check_positional(pe, seq_len, n_detectors, pos_dim, cmp_eps=0.0, train=True):
+    pe = _f32(pe).reshape(-1)
+    n = (seq_len - 1) * n_detectors
+    pidx = np.zeros(n, np.int32)
+    pm = np.zeros(n, np.float32) if train else None
+    pk = np.zeros(n, np.int32) if train else None
+    lib().orc_check_positional(_ptr(pe), _i(seq_len), _i(n_detectors), _i(pos_dim), _f(cmp_eps), _ptr(pidx),
+                               _ptr(pm), _ptr(pk))
+    return (pidx, pm, pk) if train else pidx
+
+
+def nonseq_fc_forward(W, x, anchors, n_detectors, n_anchors, n_outputs, cmp_eps=0.0, train=True,
+                      backward_group_size=32, int_mode=False, int_rescaler=0.001):
+    """One ``forward_step`` of a fully connected non-sequence layer.
+
+    Returns (y [B,O], idx [B,Nt], min_delta, min_k); the last two are None when train is False.
+    """
+    x = _f32(x)
+    B = x.shape[0]
+    T = 1 << n_anchors
+    W = _f32(W).reshape(-1)
+    assert W.size == n_detectors * T * n_outputs
+    res = check_detectors(x, anchors, n_detectors, n_anchors, cmp_eps, train)
+    idx, md, mk = res if train else (res, None, None)
+    y = np.zeros((B, n_outputs), np.float32)
+    lib().orc_nonseq_fc_forward(_ptr(W), _ptr(idx), _ptr(y), _l(B), _i(n_outputs), _i(n_detectors), _i(T),
+                                _i(backward_group_size), _i(int(int_mode)), _d(int_rescaler))
+    return y, idx, md, mk
+
+
+def nonseq_fc_backward(W, dY, anchors, idx, min_delta, min_k, n_inputs, n_anchors, lr_meta=1.0,
+                       external_lr=-1.0, forward_group_size=32, int_mode=False, int_rescaler=0.001):
+    """One ``backward_backprop`` of a fully connected non-sequence layer.
+
+    Returns (dX [B,I], dW [Nt*T*O] or None).  With external_lr >= 0 the weights array ``W`` is
+    updated in place (it must then be a writable contiguous float32 array) and dW is None.
+    """
+    dY = _f32(dY)
+    B, O = dY.shape
+    Nt = idx.shape[1]
+    T = 1 << n_anchors
+    if external_lr >= 0:
+        assert W.dtype == np.float32 and W.flags["C_CONTIGUOUS"] and W.flags["WRITEABLE"]
+        Wf = W.reshape(-1)
+        dW = None
+    else:
+        Wf = _f32(W).reshape(-1)
+        dW = np.zeros(Wf.size, np.float32)
+    dX = np.zeros((B, n_inputs), np.float32)
+    anchors = _i32(anchors).reshape(-1)
+    lib().orc_nonseq_fc_backward(_ptr(Wf), _ptr(dY), _ptr(anchors), _ptr(_i32(idx)), _ptr(_f32(min_delta)),
+                                 _ptr(_i32(min_k)), _ptr(dX), _ptr(dW), _l(B), _i(n_inputs), _i(O), _i(Nt),
+                                 _i(n_anchors), _i(T), _i(forward_group_size),
+                                 _d(float(np.float32(lr_meta))), _d(float(np.float32(external_lr))),
+                                 _i(int(int_mode)), _d(int_rescaler))
+    return dX, dW

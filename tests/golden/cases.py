@@ -1,0 +1,53 @@
+"""Golden-case definitions: scalar configurations and the seeded input builders.
+
+Imported both by make_golden.py (which runs the reference on these inputs) and by the tests
+(which rebuild the same inputs and compare against the recorded reference outputs).  This module
+must not import the reference.
+"""
+import synth
+
+
+def nonseq_fc_inputs(cfg):
+    """Inputs of a fully connected non-sequence case, rebuilt from cfg seeds (used by tests too)."""
+    s = cfg["seed"]
+    B, I, Nt, Nc, O = cfg["B"], cfg["I"], cfg["Nt"], cfg["Nc"], cfg["O"]
+    T = 1 << Nc
+    if cfg.get("sparse_input"):
+        x = synth.sparse_images(s + 11, (B, I))
+    elif cfg.get("normal_input"):
+        x = synth.normal(s + 11, (B, I))
+    else:
+        x = synth.uniform(s + 11, (B, I))
+    anchors = synth.anchor_pairs(s + 12, Nt, Nc, I)
+    if cfg.get("unused_pair"):
+        anchors[0, Nc - 1, :] = -1  # a disabled pair (0xFFFFFFFF), spiky_cuda/lut/lut_runtime_kernels_logic.proto:1077
+    W = synth.normal(s + 13, (Nt * T * O,), 0.0, cfg.get("w_std", 0.02))
+    dY = synth.normal(s + 14, (B, O))
+    if cfg.get("zero_dy"):
+        dY[:, ::3] = 0.0
+    return x, anchors, W, dY
+
+
+
+NONSEQ_FC_CASES = {
+    # tiny ragged shapes: O not a multiple of 4, Nt not a multiple of the block sizes
+    "fc_tiny_f32": dict(seed=100, B=5, I=20, Nt=7, Nc=3, O=5, G=2, Gb=3),
+    "fc_tiny_i32": dict(seed=101, B=5, I=20, Nt=7, Nc=3, O=5, G=2, Gb=3, int_mode=True, int_rescaler=10.0),
+    "fc_tiny_b1": dict(seed=102, B=1, I=9, Nt=1, Nc=1, O=1),
+    "fc_unused_pair": dict(seed=103, B=6, I=16, Nt=4, Nc=4, O=6, unused_pair=True),
+    "fc_cmp_eps": dict(seed=104, B=8, I=24, Nt=6, Nc=5, O=8, cmp_eps=0.05, normal_input=True),
+    "fc_internal": dict(seed=105, B=9, I=30, Nt=5, Nc=4, O=7, policy="internal", ext_lr=0.25, lr_meta=0.5),
+    "fc_lr_meta_zero_dy": dict(seed=106, B=7, I=18, Nt=6, Nc=3, O=9, lr_meta=0.125, zero_dy=True, G=4),
+    # exact ties are the common case with sparse inputs: first minimal |delta| wins, up(0) < 0
+    "fc_sparse_input_f32": dict(seed=107, B=12, I=64, Nt=16, Nc=6, O=12, sparse_input=True),
+    "fc_sparse_input_i32": dict(seed=108, B=12, I=64, Nt=16, Nc=6, O=12, sparse_input=True, int_mode=True,
+                                int_rescaler=0.5),
+    # a slice of the single-layer benchmark configuration (784 inputs, 64 tables x 6 pairs, 32 outputs)
+    "fc_c1_slice_f32": dict(seed=109, B=16, I=784, Nt=64, Nc=6, O=32),
+    "fc_c1_slice_i32": dict(seed=110, B=16, I=784, Nt=64, Nc=6, O=32, int_mode=True),
+    # wider outputs than one forward group, more detectors than one backward group
+    "fc_wide_f32": dict(seed=111, B=4, I=40, Nt=35, Nc=3, O=35, G=32, Gb=32),
+    "fc_wide_i32": dict(seed=112, B=4, I=40, Nt=35, Nc=3, O=35, G=32, Gb=32, int_mode=True, int_rescaler=3.0),
+}
+
+

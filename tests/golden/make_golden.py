@@ -1,0 +1,93 @@
+"""Records golden vectors from the REAL reference (its CPU build) for the LUT hot path.
+
+Run in a container that has the reference checkout:
+
+    tests/golden/build_reference_cpu.sh                      # once, builds into /tmp/spiky_ref
+    PYTHONPATH=/tmp/spiky_ref/spiky_cuda:/tmp/spiky_ref/src \
+        python tests/golden/make_golden.py [case-name-prefix ...]
+
+Each case is written to tests/golden/<name>.npz: the scalar configuration, the seeds of the
+hashed synthetic inputs (see synth.py; small inputs are stored verbatim as well) and every tensor
+the reference produced.  The tests rebuild the inputs from the seeds and compare the oracle and
+the CUDA path with the stored reference outputs.
+"""
+import json
+import os
+import sys
+
+import numpy as np
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+import synth  # noqa: E402,F401
+from cases import NONSEQ_FC_CASES, nonseq_fc_inputs  # noqa: E402
+
+from spiky.lut.LUTLayer import (  # noqa: E402  (the reference)
+    LUTLayer, SynapseMeta, GradientPolicy, GradientType, LUTSharedContext,
+)
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def save(name, cfg, **arrays):
+    path = os.path.join(HERE, name + ".npz")
+    np.savez_compressed(path, cfg=np.frombuffer(json.dumps(cfg).encode(), dtype=np.uint8), **arrays)
+    print(f"{name}: {os.path.getsize(path) / 1024:.1f} KiB")
+
+
+def t2n(t):
+    return None if t is None else t.detach().cpu().numpy().copy()
+
+
+# ----------------------------------------------------------------------------- non-seq FC
+def run_nonseq_fc(name, cfg):
+    x, anchors, W, dY = nonseq_fc_inputs(cfg)
+    B, I, Nt, Nc, O = cfg["B"], cfg["I"], cfg["Nt"], cfg["Nc"], cfg["O"]
+    int_mode = cfg.get("int_mode", False)
+    policy = {"dense": GradientType.Dense, "internal": GradientType.Internal}[cfg.get("policy", "dense")]
+    ctx = LUTSharedContext(_cmp_eps=cfg.get("cmp_eps", 0.0))
+    ctx.to_device(torch.device("cpu"))
+    layer = LUTLayer(
+        n_inputs=I, n_anchors_per_detector=Nc, n_detectors=Nt, n_outputs=O,
+        synapse_meta=SynapseMeta(learning_rate=cfg.get("lr_meta", 1.0), min_weight=-1.0, max_weight=1.0),
+        weights_gradient_policy=GradientPolicy(policy),
+        shared_context=ctx,
+        summation_dtype=torch.int32 if int_mode else torch.float32,
+        _explicit_anchors=torch.from_numpy(anchors.reshape(-1).copy()),
+        _int_rescaler=cfg.get("int_rescaler", 0.001),
+        _forward_group_size=cfg.get("G", 32), _backward_group_size=cfg.get("Gb", 32),
+        random_seed=1,
+    )
+    with torch.no_grad():
+        layer._weights.copy_(torch.from_numpy(W))
+    xt = torch.from_numpy(x).view(B, 1, I)
+    out = {}
+    layer.eval()
+    out["y_eval"] = t2n(layer.forward_step(xt)).reshape(B, O)
+    layer.train()
+    y, idx, md, mk = layer.forward_step(xt)
+    out.update(y=t2n(y).reshape(B, O), idx=t2n(idx).reshape(B, Nt), min_delta=t2n(md).reshape(B, Nt),
+               min_k=t2n(mk).reshape(B, Nt))
+    if policy == GradientType.Internal:
+        layer.set_external_learning_rate_hook(lambda w: cfg["ext_lr"])
+    dx, dw = layer.backward_step(xt, torch.from_numpy(dY).view(B, 1, O), idx, md, mk)
+    out["dX"] = t2n(dx).reshape(B, I)
+    if policy == GradientType.Internal:
+        out["W_after"] = t2n(layer._weights)
+    else:
+        out["dW"] = t2n(dw)
+    extra = {}
+    if x.size <= 4096:
+        extra = dict(in_x=x, in_anchors=anchors, in_W=W, in_dY=dY)
+    save(name, dict(cfg, kind="nonseq_fc"), **out, **extra)
+
+
+def main():
+    prefixes = sys.argv[1:]
+    for name, cfg in NONSEQ_FC_CASES.items():
+        if not prefixes or any(name.startswith(p) for p in prefixes):
+            run_nonseq_fc(name, cfg)
+
+
+if __name__ == "__main__":
+    main()
