@@ -1,0 +1,96 @@
+/*
+ * spiky_b200 - C ABI of the B200-native LUT-layer runtime.
+ *
+ * Every entry point takes raw device pointers, sizes and a CUDA stream handle and returns an int
+ * status: 0 = ok, < 0 = argument error (LUTB_ERR_*), > 0 = a cudaError_t raised by a launch.
+ * Nothing throws, aborts or allocates unless stated.  lutb_last_error() returns a thread-local,
+ * human readable description of the last non-zero status.
+ *
+ * The functions replace the runtime methods of the reference's pybind11 classes
+ * LUTDataManagerF / LUTDataManagerI (registered in spiky_cuda/spiky_py.cpp:6-24, defined in
+ * spiky_cuda/lut/lut.cu); each declaration cites the method it stands in for.  Tensor layouts are
+ * the reference's: all arrays flat, contiguous, fp32 / int32, outputs accumulated into
+ * caller-zeroed buffers.  Unlike the reference, kernels are enqueued on ONE caller-supplied stream
+ * and the call returns without synchronising.
+ */
+#ifndef SPIKY_B200_H
+#define SPIKY_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define LUTB_OK 0
+#define LUTB_ERR_NULL (-1)      /* a required pointer is NULL */
+#define LUTB_ERR_SHAPE (-2)     /* a size is zero, negative or out of the supported range */
+#define LUTB_ERR_MODE (-3)      /* inconsistent flags (e.g. dW given together with an internal learning rate) */
+#define LUTB_ERR_WORKSPACE (-4) /* workspace missing or too small */
+#define LUTB_ERR_ALIGN (-5)     /* a pointer is not aligned as documented */
+
+/* weight-gradient kernel selection for the backward entry points */
+#define LUTB_DW_AUTO 0      /* pick by the expected number of hits per table row */
+#define LUTB_DW_ATOMIC 1    /* row-coalesced global reductions (red.global.add) */
+#define LUTB_DW_SMEM 2      /* shared-memory privatised table slices, flushed once per block */
+#define LUTB_DW_SORTED 3    /* counting sort of the batch by row + segmented reduce; deterministic order; needs workspace */
+
+/*
+ * Geometry and numeric mode of one LUT layer; mirrors the constructor arguments of
+ * LUTDataManagerF/I (spiky_cuda/lut/lut.cu:17-31) plus the per-call scalars.
+ */
+typedef struct lutb_layer_cfg {
+    int32_t n_inputs;        /* I  */
+    int32_t n_outputs;       /* O  */
+    int32_t n_detectors;     /* Nt */
+    int32_t n_anchors;       /* Nc, 1..30; a table has 2^Nc rows (non-sequence and product layers) */
+    int32_t seq_len;         /* S, 1 for non-sequence layers */
+    int32_t pos_dim;         /* Npe, 0 when unused */
+    int32_t forward_group;   /* forward_group_size: outputs per block in the backward pass */
+    int32_t backward_group;  /* backward_group_size: detectors per block in the forward pass */
+    int32_t int_mode;        /* 0: fp32 accumulators (LUTDataManagerF); 1: int32 fixed point (LUTDataManagerI) */
+    int32_t sliced_product;  /* product layers only: interleaved [x_i, x_j, pe] anchor numbering */
+    float cmp_eps;           /* dead band of the anchor comparison, 0 = plain '>' */
+    float reserved0;
+    double int_rescaler;     /* fixed-point scale multiplier (int_mode == 1) */
+    double lr_meta;          /* SynapseMeta.learning_rate applied to weight gradients */
+} lutb_layer_cfg;
+
+/* Library / build identification. */
+int lutb_version(void);
+const char *lutb_last_error(void);
+
+/*
+ * Non-sequence, fully connected forward.  Replaces LUTDataManager::forward_step
+ * (spiky_cuda/lut/lut.cu:629-716 -> LUTRuntimeContext::forward_step, lut_runtime.cu:76-211).
+ *   weights    fp32 [Nt * 2^Nc * O]        anchors  int32 [Nt * Nc * 2] (-1 = unused pair)
+ *   x          fp32 [batch * I]            y        fp32 [batch * O], accumulated into
+ *   idx        int32 [batch * Nt] out      min_delta fp32 / min_k int32 [batch * Nt] out, both NULL = eval
+ */
+int lutb_nonseq_fc_forward(const lutb_layer_cfg *cfg, int64_t batch, const float *weights, const float *x,
+                           const int32_t *anchors, float *y, int32_t *idx, float *min_delta, int32_t *min_k,
+                           void *stream);
+
+/*
+ * Bytes of scratch memory lutb_nonseq_fc_backward needs for the given variant (0 for all but
+ * LUTB_DW_SORTED).  The caller allocates it; 256-byte alignment is required.
+ */
+size_t lutb_nonseq_fc_backward_workspace(const lutb_layer_cfg *cfg, int64_t batch, int dw_variant);
+
+/*
+ * Non-sequence, fully connected backward.  Replaces LUTDataManager::backward_backprop
+ * (spiky_cuda/lut/lut.cu:1030-1088 -> LUTRuntimeContext::backward_backprop, lut_runtime.cu:213-397).
+ *   dX  fp32 [batch * I] accumulated into.
+ *   external_lr < 0: dW fp32 [Nt * 2^Nc * O] receives lr_meta * dY rows (accumulated into).
+ *   external_lr >= 0: dW must be NULL and weights are updated in place by -external_lr * lr_meta * dY.
+ */
+int lutb_nonseq_fc_backward(const lutb_layer_cfg *cfg, int64_t batch, float *weights, const float *dY,
+                            const int32_t *anchors, const int32_t *idx, const float *min_delta,
+                            const int32_t *min_k, float *dX, float *dW, double external_lr, int dw_variant,
+                            void *workspace, size_t workspace_bytes, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SPIKY_B200_H */

@@ -1,0 +1,86 @@
+"""ctypes binding of libspiky_b200.so, the C-ABI CUDA library (include/spiky_b200.h).
+
+The library is the only compute path: there is no CPU or PyTorch fallback.  Loading fails loudly
+when the library has not been built (``python -m spiky_b200.build``).
+"""
+import ctypes
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "lib", "libspiky_b200.so")
+
+# dW kernel variants (include/spiky_b200.h)
+DW_AUTO, DW_ATOMIC, DW_SMEM, DW_SORTED = 0, 1, 2, 3
+
+
+class LayerCfg(ctypes.Structure):
+    """Mirror of ``lutb_layer_cfg``."""
+
+    _fields_ = [
+        ("n_inputs", ctypes.c_int32),
+        ("n_outputs", ctypes.c_int32),
+        ("n_detectors", ctypes.c_int32),
+        ("n_anchors", ctypes.c_int32),
+        ("seq_len", ctypes.c_int32),
+        ("pos_dim", ctypes.c_int32),
+        ("forward_group", ctypes.c_int32),
+        ("backward_group", ctypes.c_int32),
+        ("int_mode", ctypes.c_int32),
+        ("sliced_product", ctypes.c_int32),
+        ("cmp_eps", ctypes.c_float),
+        ("reserved0", ctypes.c_float),
+        ("int_rescaler", ctypes.c_double),
+        ("lr_meta", ctypes.c_double),
+    ]
+
+
+_vp = ctypes.c_void_p
+_i64 = ctypes.c_int64
+_int = ctypes.c_int
+_dbl = ctypes.c_double
+_size = ctypes.c_size_t
+_cfgp = ctypes.POINTER(LayerCfg)
+
+# name -> (restype, argtypes); every symbol include/spiky_b200.h declares is listed here
+SIGNATURES = {
+    "lutb_version": (_int, []),
+    "lutb_last_error": (ctypes.c_char_p, []),
+    "lutb_nonseq_fc_forward": (_int, [_cfgp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "lutb_nonseq_fc_backward_workspace": (_size, [_cfgp, _i64, _int]),
+    "lutb_nonseq_fc_backward": (_int, [_cfgp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _dbl, _int, _vp, _size, _vp]),
+}
+
+_lib = None
+
+
+def lib():
+    """The loaded library; raises RuntimeError when it is missing (no fallback exists)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build the CUDA library with `python -m spiky_b200.build` "
+                "(spiky_b200 has no CPU or PyTorch fallback)"
+            )
+        handle = ctypes.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(handle, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = handle
+    return _lib
+
+
+class LutbError(RuntimeError):
+    pass
+
+
+def check(status):
+    """Translate a C-ABI status into the exception type the reference raises for the same mistake:
+    argument errors -> ValueError (py::value_error in spiky_cuda/lut/lut.cu), CUDA errors -> RuntimeError."""
+    if status == 0:
+        return
+    msg = lib().lutb_last_error().decode(errors="replace")
+    if status < 0:
+        raise ValueError(msg)
+    raise LutbError(f"CUDA error {status}: {msg}")

@@ -1,0 +1,340 @@
+"""Host-side mirror of the reference's native data managers ``LUTDataManagerF`` / ``LUTDataManagerI``
+(pybind11 classes of spiky_cuda/lut/lut.cu:12-1656), backed by the C-ABI CUDA library.
+
+Method names, argument order and error behaviour follow the reference so that layer code written
+against it runs unchanged: argument mistakes raise ``ValueError`` (the reference's
+``py::value_error``), tensor dtype / layout / device mistakes raise ``RuntimeError``
+(``checkTensor``, spiky_cuda/misc/misc.cpp:217-277).  Differences, all deliberate:
+
+* kernels are enqueued on torch's CURRENT CUDA stream and the call returns without synchronising;
+  ``r_stream_handles`` is accepted and ignored (the reference spreads work over three caller
+  streams and the caller synchronises them);
+* there is no CPU execution path: ``to_device(-1)`` is accepted during set-up, runtime calls on a
+  CPU-resident manager raise ``RuntimeError``;
+* fully connected layers need no native structure at all; sparse connectivity is attached as a
+  compact per-detector index (``set_sparse_index``) instead of the reference's byte arena.
+"""
+import ctypes
+
+import torch
+
+from . import _native
+from ._native import LayerCfg
+
+_EPS = 0.00000000000000001
+_DENOM32 = 0xFFFFF
+_MAX_GROUP = 1024  # forward_group_size upper bound of the reference's launch configuration
+
+
+def _check_tensor(t, name, real, device_index, int_bytes=4):
+    if not isinstance(t, torch.Tensor):
+        raise RuntimeError(f"{name} must be a tensor")
+    if not t.is_contiguous():
+        raise RuntimeError(f"tensor {name} must be contiguous")
+    if t.dim() != 1:
+        raise RuntimeError(f"tensor {name} must be flat and has stride = 1")
+    want = torch.float32 if real else (torch.int32 if int_bytes == 4 else torch.int64)
+    if t.dtype != want:
+        raise RuntimeError(f"tensor {name} must have dtype {str(want).replace('torch.', '')}")
+    if device_index == -1:
+        if t.device.type != "cpu":
+            raise RuntimeError(f"tensor {name} must be on CPU")
+    else:
+        if t.device.type != "cuda":
+            raise RuntimeError(f"tensor {name} must be on CUDA")
+        if t.device.index != device_index:
+            raise RuntimeError(f"tensor {name} must be on CUDA device {device_index}")
+
+
+def _ptr(t):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+class _LUTDataManager:
+    _INT_MODE = False
+
+    def __init__(self, n_inputs, n_outputs, n_detectors, n_anchors_per_detector, sequence_length, positional_dim,
+                 initial_synapse_capacity, forward_group_size, backward_group_size, int_rescaler=1.0):
+        for value, name in ((n_inputs, "n_inputs"), (n_outputs, "n_outputs"), (n_detectors, "n_detectors"),
+                            (n_anchors_per_detector, "n_anchors_per_detector"), (sequence_length, "sequence_length"),
+                            (forward_group_size, "forward_group_size"), (backward_group_size, "backward_group_size")):
+            if int(value) <= 0:
+                raise ValueError(f"{name} == 0")
+        if forward_group_size > _MAX_GROUP:
+            raise ValueError("forward_group_size > LUT_RUNTIME_KERNELS_TPB")
+        self._n_inputs = int(n_inputs)
+        self._n_outputs = int(n_outputs)
+        self._n_detectors = int(n_detectors)
+        self._n_anchors = int(n_anchors_per_detector)
+        self._seq_len = int(sequence_length)
+        self._pos_dim = int(positional_dim)
+        self._fwd_group = int(forward_group_size)
+        self._bwd_group = int(backward_group_size)
+        self._int_rescaler = float(int_rescaler)
+        bits = self._n_anchors + ((self._n_anchors + self._pos_dim) if self._seq_len > 1 else 0)
+        if bits > 30:
+            raise ValueError("lookup table too large: more than 2^30 rows per detector")
+        self._rows_per_detector = 1 << bits
+        self._n_lookup_neurons = self._n_detectors * self._rows_per_detector
+        self._metas = []
+        self._fully_connected = None
+        self._device = -1
+        self._forward_seen = False
+        self._sparse = None
+        self._timers = {}
+
+    # ------------------------------------------------------------------ description
+    def get_smallest_distinguishable_fraction(self):
+        return (1.0 / _DENOM32) / self._int_rescaler if self._INT_MODE else 0.0
+
+    def get_epsilon(self):
+        return _EPS
+
+    def get_summations_data_type(self):
+        return "int32" if self._INT_MODE else "float32"
+
+    def get_number_of_inputs(self):
+        return self._n_inputs
+
+    def get_number_of_outputs(self):
+        return self._n_outputs
+
+    def get_number_of_detectors(self):
+        return self._n_detectors
+
+    def get_number_of_lookup_neurons(self):
+        return self._n_lookup_neurons
+
+    def get_number_of_anchors_per_detector(self):
+        return self._n_anchors
+
+    def get_number_of_synapses(self):
+        if self._fully_connected:
+            return self._n_lookup_neurons * self._n_outputs
+        return 0 if self._sparse is None else int(self._sparse.n_synapses)
+
+    def get_weights_dimension(self):
+        if self._fully_connected:
+            return self._n_lookup_neurons * self._n_outputs
+        if self._sparse is None:
+            raise ValueError("sparse connectivity has not been attached yet")
+        return int(self._sparse.n_weights)
+
+    def get_max_forward_groups_per_neuron(self):
+        if self._fully_connected:
+            return (self._n_outputs + self._fwd_group - 1) // self._fwd_group
+        if self._sparse is None:
+            return 0
+        return int(self._sparse.max_groups_per_neuron)
+
+    def __repr__(self):
+        return (f"LUTDataManager(backend: spiky_b200; summation type: {self.get_summations_data_type()}; "
+                f"smallest distinguishable fraction: {self.get_smallest_distinguishable_fraction()}; "
+                f"n_synapses: {self.get_number_of_synapses() if self._fully_connected is not None else 0}; "
+                f"n_detectors: {self._n_detectors}; n_lookup_neurons: {self._n_lookup_neurons})")
+
+    def get_memory_stats(self):
+        n = 0 if self._sparse is None else self._sparse.nbytes()
+        return f"sparse index: {n // 1024} KB\n"
+
+    def get_profiling_stats(self):
+        # Timings are opt-in CUDA-event measurements collected by the layer (no forced synchronisation
+        # inside runtime calls, unlike the reference's always-on profiler, spiky_cuda/misc/misc.h:14,170-214).
+        lines = []
+        for name, (total_ms, count) in sorted(self._timers.items()):
+            lines.append(f"{name}: {total_ms:.4f} ms / {count} = {total_ms / max(count, 1):.4f} ms")
+        return "\n".join(lines)
+
+    def reset_profiler(self):
+        self._timers = {}
+
+    def _record_time(self, name, ms):
+        total, count = self._timers.get(name, (0.0, 0))
+        self._timers[name] = (total + ms, count + 1)
+
+    # ------------------------------------------------------------------ set-up
+    def register_synapse_meta(self, learning_rate, min_synaptic_weight, max_synaptic_weight, initial_noise_level,
+                              initial_weight):
+        if self._fully_connected is not None:
+            raise ValueError("can't register new synapse metas after neurons were initialized")
+        if learning_rate < 0.0:
+            raise ValueError("learning_rate < 0")
+        if learning_rate > 1.0:
+            raise ValueError("learning_rate > 1")
+        if self._INT_MODE and learning_rate > 0.0 and learning_rate * self._int_rescaler < 1.0 / _DENOM32:
+            raise ValueError(f"too small value for 'learning_rate' {learning_rate} "
+                             f"(less than smallest distinguishable fraction {1.0 / _DENOM32})")
+        if min_synaptic_weight > max_synaptic_weight:
+            raise ValueError("min_synaptic_weight > max_synaptic_weight")
+        if initial_weight < min_synaptic_weight:
+            raise ValueError("initial_weight < min_synaptic_weight")
+        if initial_weight > max_synaptic_weight:
+            raise ValueError("initial_weight > max_synaptic_weight")
+        meta = (float(learning_rate), float(min_synaptic_weight), float(max_synaptic_weight),
+                float(initial_noise_level), float(initial_weight))
+        if meta in self._metas:
+            return self._metas.index(meta)
+        self._metas.append(meta)
+        return len(self._metas) - 1
+
+    def initialize_neurons(self, is_fully_connected):
+        if not self._metas:
+            raise ValueError("no synapse metas were registered")
+        if is_fully_connected and len(self._metas) > 1:
+            raise ValueError("fully connected mode is not compatible with multiple synapse metas")
+        self._fully_connected = bool(is_fully_connected)
+
+    def set_sparse_index(self, index):
+        """Attach the compact connectivity of a sparse (projection / convolution) layer."""
+        if self._fully_connected is not False:
+            raise ValueError("sparse connectivity can only be attached in sparse mode")
+        self._sparse = index
+
+    def to_device(self, device):
+        """device: CUDA ordinal, or -1 for host (set-up only)."""
+        self._device = int(device)
+        if self._sparse is not None:
+            self._sparse.to_device(self._device)
+
+    # ------------------------------------------------------------------ runtime helpers
+    def _lr_meta(self):
+        # the reference stores the rate as fp32 (BaseSynapseMeta.lr) and widens it to double
+        return float(torch.tensor(self._metas[0][0], dtype=torch.float32).item())
+
+    def _cfg(self, cmp_eps=0.0, sliced=False, seq_len=None):
+        return LayerCfg(
+            n_inputs=self._n_inputs, n_outputs=self._n_outputs, n_detectors=self._n_detectors,
+            n_anchors=self._n_anchors, seq_len=self._seq_len if seq_len is None else seq_len, pos_dim=self._pos_dim,
+            forward_group=self._fwd_group, backward_group=self._bwd_group, int_mode=int(self._INT_MODE),
+            sliced_product=int(bool(sliced)), cmp_eps=float(cmp_eps), reserved0=0.0,
+            int_rescaler=self._int_rescaler, lr_meta=self._lr_meta(),
+        )
+
+    def _require_cuda(self):
+        if self._device < 0:
+            raise RuntimeError("spiky_b200 has no CPU execution path: move the layer to a CUDA device first")
+
+    def _stream(self):
+        return ctypes.c_void_p(torch.cuda.current_stream(self._device).cuda_stream)
+
+    # ------------------------------------------------------------------ non-sequence runtime
+    def forward_step(self, r_weights, batch_size, r_input, r_detector_anchors, w_output, w_lookup_indices,
+                     cmp_eps=0.0, r_stream_handles=None, w_min_anchor_deltas=None, w_min_anchor_delta_indices=None):
+        self._require_cuda()
+        dev = self._device
+        _check_tensor(r_weights, "r_weights", True, dev)
+        _check_tensor(r_input, "r_input", True, dev)
+        _check_tensor(r_detector_anchors, "r_detector_anchors", False, dev)
+        _check_tensor(w_output, "w_output", True, dev)
+        _check_tensor(w_lookup_indices, "w_lookup_indices", False, dev)
+        if w_min_anchor_deltas is not None:
+            _check_tensor(w_min_anchor_deltas, "w_min_anchor_deltas", True, dev)
+        if w_min_anchor_delta_indices is not None:
+            _check_tensor(w_min_anchor_delta_indices, "w_min_anchor_delta_indices", False, dev)
+        if batch_size == 0:
+            raise ValueError("batch_size == 0")
+        if self._seq_len != 1:
+            raise ValueError("forward_step should only be called when sequence_length == 1")
+        B = int(batch_size)
+        self._expect(r_input, B * self._n_inputs, "r_input")
+        self._expect(w_output, B * self._n_outputs, "w_output")
+        self._expect(w_lookup_indices, B * self._n_detectors, "w_lookup_indices")
+        self._expect(r_detector_anchors, self._n_detectors * self._n_anchors * 2, "r_detector_anchors")
+        self._expect(r_weights, self.get_weights_dimension(), "r_weights")
+        cfg = self._cfg(cmp_eps)
+        L = _native.lib()
+        with torch.cuda.device(dev):
+            if self._fully_connected:
+                rc = L.lutb_nonseq_fc_forward(ctypes.byref(cfg), B, _ptr(r_weights), _ptr(r_input),
+                                              _ptr(r_detector_anchors), _ptr(w_output), _ptr(w_lookup_indices),
+                                              _ptr(w_min_anchor_deltas), _ptr(w_min_anchor_delta_indices),
+                                              self._stream())
+            else:
+                rc = self._sparse_forward(L, cfg, B, r_weights, r_input, r_detector_anchors, w_output,
+                                          w_lookup_indices, w_min_anchor_deltas, w_min_anchor_delta_indices)
+        _native.check(rc)
+        self._forward_seen = True
+
+    def backward_backprop(self, r_weights, batch_size, r_output_gradients, r_detector_anchors, r_lookup_indices,
+                          r_min_anchor_deltas, r_min_anchor_delta_indices, w_input_gradients, external_lr,
+                          w_weights_gradients=None, r_stream_handles=None, dw_variant=_native.DW_AUTO,
+                          workspace=None):
+        if batch_size == 0:
+            raise ValueError("batch_size == 0")
+        if not self._forward_seen:
+            raise ValueError("no active context")
+        self._require_cuda()
+        dev = self._device
+        _check_tensor(r_weights, "r_weights", True, dev)
+        _check_tensor(w_input_gradients, "w_input_gradients", True, dev)
+        _check_tensor(r_output_gradients, "r_output_gradients", True, dev)
+        _check_tensor(r_detector_anchors, "r_detector_anchors", False, dev)
+        _check_tensor(r_lookup_indices, "r_lookup_indices", False, dev)
+        _check_tensor(r_min_anchor_deltas, "r_min_anchor_deltas", True, dev)
+        _check_tensor(r_min_anchor_delta_indices, "r_min_anchor_delta_indices", False, dev)
+        if w_weights_gradients is not None:
+            _check_tensor(w_weights_gradients, "w_weights_gradients", True, dev)
+        if self._seq_len != 1:
+            raise ValueError("backward_backprop should only be called when sequence_length == 1")
+        if external_lr >= 0.0 and w_weights_gradients is not None:
+            raise ValueError("in internal weight gradients mode w_weights_gradients should be nullptr")
+        B = int(batch_size)
+        self._expect(r_output_gradients, B * self._n_outputs, "r_output_gradients")
+        self._expect(w_input_gradients, B * self._n_inputs, "w_input_gradients")
+        self._expect(r_lookup_indices, B * self._n_detectors, "r_lookup_indices")
+        if w_weights_gradients is not None and w_weights_gradients.numel() < self.get_weights_dimension():
+            raise ValueError("w_weights_gradients is smaller than the weights")
+        cfg = self._cfg()
+        L = _native.lib()
+        with torch.cuda.device(dev):
+            if self._fully_connected:
+                ws_bytes = L.lutb_nonseq_fc_backward_workspace(ctypes.byref(cfg), B, dw_variant)
+                if ws_bytes and (workspace is None or workspace.numel() * workspace.element_size() < ws_bytes):
+                    workspace = torch.empty(ws_bytes, dtype=torch.uint8, device=r_weights.device)
+                rc = L.lutb_nonseq_fc_backward(ctypes.byref(cfg), B, _ptr(r_weights), _ptr(r_output_gradients),
+                                               _ptr(r_detector_anchors), _ptr(r_lookup_indices),
+                                               _ptr(r_min_anchor_deltas), _ptr(r_min_anchor_delta_indices),
+                                               _ptr(w_input_gradients), _ptr(w_weights_gradients),
+                                               float(external_lr), int(dw_variant), _ptr(workspace),
+                                               0 if workspace is None else workspace.numel() * workspace.element_size(),
+                                               self._stream())
+            else:
+                rc = self._sparse_backward(L, cfg, B, r_weights, r_output_gradients, r_detector_anchors,
+                                           r_lookup_indices, r_min_anchor_deltas, r_min_anchor_delta_indices,
+                                           w_input_gradients, external_lr, w_weights_gradients)
+        _native.check(rc)
+
+    @staticmethod
+    def _expect(t, numel, name):
+        if t.numel() != numel:
+            raise ValueError(f"{name} has {t.numel()} elements, expected {numel}")
+
+    def _sparse_forward(self, *args):
+        raise ValueError("sparse connectivity is not attached")
+
+    def _sparse_backward(self, *args):
+        raise ValueError("sparse connectivity is not attached")
+
+
+class LUTDataManagerF(_LUTDataManager):
+    """fp32 accumulators (reference: LUTDataManagerF, spiky_cuda/lut/lut.cu:1477-1480)."""
+
+    _INT_MODE = False
+
+    def __init__(self, n_inputs, n_outputs, n_detectors, n_anchors_per_detector, sequence_length, positional_dim,
+                 initial_synapse_capacity, forward_group_size, backward_group_size):
+        super().__init__(n_inputs, n_outputs, n_detectors, n_anchors_per_detector, sequence_length, positional_dim,
+                         initial_synapse_capacity, forward_group_size, backward_group_size, 1.0)
+
+
+class LUTDataManagerI(_LUTDataManager):
+    """int32 fixed-point accumulators, order-independent sums (reference: LUTDataManagerI, lut.cu:1481-1483)."""
+
+    _INT_MODE = True
+
+    def __init__(self, n_inputs, n_outputs, n_detectors, n_anchors_per_detector, sequence_length, positional_dim,
+                 initial_synapse_capacity, forward_group_size, backward_group_size, int_rescaler):
+        if not int_rescaler > 0:
+            raise ValueError("int_rescaler must be positive")
+        super().__init__(n_inputs, n_outputs, n_detectors, n_anchors_per_detector, sequence_length, positional_dim,
+                         initial_synapse_capacity, forward_group_size, backward_group_size, int_rescaler)
