@@ -1,0 +1,353 @@
+"""Benchmark of the LUT-layer hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl ours|reference]
+
+One "step" is one pass of the hot path over one batch of seeded synthetic input.  Rank 0 prints ONE
+JSON line.  `value` is whole-job throughput with inputs resident in HBM; `e2e` is the same metric
+through the public layer API with pinned-host inputs copied in and the result copied out inside the
+timed region.  `roofline` describes the dominant kernel (algorithmic bytes / CUDA-event time against
+the measured HBM peak), `cpu_baseline` the CPU oracle (a port of the reference's CPU path) timed on
+a bounded sample on this host.  With --impl reference the CPU implementation itself is the arm.
+"""
+import argparse
+import json
+import os
+import statistics
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests", "golden"))
+
+L2_BYTES = 126 * 1024 * 1024
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+# ------------------------------------------------------------------------------------ clocks
+class ClockSampler:
+    """Samples SM clocks and throttle reasons through NVML from a thread while the timed region runs."""
+
+    REASONS = {  # nvmlClocksEventReason* bit masks
+        0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap",
+    }
+
+    def __init__(self, gpu_index, period_s=0.01):
+        import threading
+        self.gpu_index = gpu_index
+        self.period_s = period_s
+        self.samples = []
+        self.reasons = set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        self._error = None
+
+    def _run(self):
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            # NVML enumerates physical devices: honour CUDA_VISIBLE_DEVICES when it is a plain index list
+            index = self.gpu_index
+            vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+            if vis:
+                ids = [v.strip() for v in vis.split(",")]
+                if index < len(ids) and ids[index].isdigit():
+                    index = int(ids[index])
+            h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM))
+            while not self._stop.is_set():
+                self.samples.append(float(pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM)))
+                mask = pynvml.nvmlDeviceGetCurrentClocksEventReasons(h)
+                for bit, name in self.REASONS.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+                time.sleep(self.period_s)
+        except Exception as e:  # NVML missing or restricted: report it instead of failing the run
+            self._error = repr(e)
+
+    def start(self):
+        import threading
+        self._thread = threading.Thread(target=self._run, daemon=True)
+        self._thread.start()
+
+    def stop(self):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join(timeout=5)
+        out = {"sm_mhz": statistics.median(self.samples) if self.samples else None, "sm_max_mhz": self.max_mhz,
+               "samples": len(self.samples), "reasons": sorted(self.reasons)}
+        if self._error:
+            out["error"] = self._error
+        return out
+
+
+# ------------------------------------------------------------------------------------ workloads
+class LutLayerWorkload:
+    """Single fully connected LUT layer, forward + backward (train mode), fp32.
+
+    Layer of the single-layer configuration: 784 inputs, 64 tables x 6 anchor pairs (64 rows), 32
+    outputs; x uniform [0,1), tables N(0, 0.02), upstream gradient N(0,1).  The batch is raised above
+    the configuration's 256 so that one step's inputs exceed L2 (the HBM roofline is meaningless on a
+    12 MB step that is launch-latency bound).
+    """
+
+    metric = "LUT fwd+bwd samples/sec"
+    unit = "samples/s"
+    dtype = "f32"
+
+    def __init__(self, batch=65536, n_inputs=784, n_detectors=64, n_anchors=6, n_outputs=32):
+        self.B, self.I, self.Nt, self.Nc, self.O = batch, n_inputs, n_detectors, n_anchors, n_outputs
+        self.name = f"single LUT layer fwd+bwd fp32 (I={n_inputs}, Nt={n_detectors}, Nc={n_anchors}, O={n_outputs}), batch {batch}"
+        self.units_per_step = batch
+
+    def host_inputs(self, seed, batch):
+        import synth
+        x = synth.uniform(seed + 1, (batch, self.I))
+        dY = synth.normal(seed + 2, (batch, self.O))
+        return x, dY
+
+    def structure(self):
+        import synth
+        anchors = synth.anchor_pairs(12, self.Nt, self.Nc, self.I)
+        W = synth.normal(13, (self.Nt * (1 << self.Nc) * self.O,), 0.0, 0.02)
+        return anchors, W
+
+    def setup(self, device, rank):
+        import torch
+        from spiky_b200.lut_layer import LUTLayer, SynapseMeta
+
+        anchors, W = self.structure()
+        self.layer = LUTLayer(self.I, self.Nc, self.Nt, self.O, synapse_meta=SynapseMeta(min_weight=-1.0, max_weight=1.0),
+                              _explicit_anchors=torch.from_numpy(anchors.reshape(-1)), device=device)
+        with torch.no_grad():
+            self.layer._weights.copy_(torch.from_numpy(W))
+        self.layer.train()
+        x, dY = self.host_inputs(1000 + rank, self.B)
+        self.hx = torch.from_numpy(x).view(self.B, 1, self.I).pin_memory()
+        self.hdy = torch.from_numpy(dY).view(self.B, 1, self.O).pin_memory()
+        self.dx = self.hx.to(device)
+        self.ddy = self.hdy.to(device)
+        self.device = device
+        self.h2d_bytes = self.hx.numel() * 4 + self.hdy.numel() * 4
+        self.d2h_bytes = 4
+        self.input_bytes = self.h2d_bytes
+        self.l2_note = "inputs>L2" if self.input_bytes > L2_BYTES else "flushed"
+
+    def _run(self, x, dy):
+        x = x.detach().requires_grad_(True)
+        self.layer._weights.grad = None
+        y = self.layer(x)
+        y.backward(dy)
+        return y
+
+    def step_device(self):
+        return self._run(self.dx, self.ddy)
+
+    def step_e2e(self):
+        x = self.hx.to(self.device, non_blocking=True)
+        dy = self.hdy.to(self.device, non_blocking=True)
+        y = self._run(x, dy)
+        return float(y.sum().item())  # device -> host read of the step's result
+
+    # dominant kernel: the table-gradient scatter (2 x 4 x Nt x O bytes of row read-modify-write per sample)
+    dominant_kernel = "fc_weight_grad"
+
+    def algorithmic_bytes(self):
+        """Per sample, by kernel family (every gathered / scattered row at full size, RMW counted twice)."""
+        I, Nt, O = self.I, self.Nt, self.O
+        return {
+            "check_detectors": 4 * I + 12 * Nt,
+            "fc_gather_forward": 4 * Nt + 4 * Nt * O + 4 * O,
+            "fc_input_grad": 4 * O + 12 * Nt + 2 * 4 * Nt * O + 16 * Nt,
+            "fc_weight_grad": 4 * O + 4 * Nt + 2 * 4 * Nt * O,
+        }
+
+    def cpu_step(self, batch, threads):
+        """One forward+backward of `batch` samples on the CPU oracle; returns seconds."""
+        from oracle import lut_oracle as orc
+        anchors, W = self.structure()
+        x, dY = self.host_inputs(77, batch)
+        orc.set_threads(threads)
+        t0 = time.perf_counter()
+        y, idx, md, mk = orc.nonseq_fc_forward(W, x, anchors, self.Nt, self.Nc, self.O)
+        orc.nonseq_fc_backward(W, dY, anchors, idx, md, mk, self.I, self.Nc)
+        return time.perf_counter() - t0
+
+
+WORKLOADS = {
+    "lut_layer": lambda: LutLayerWorkload(),
+    "lut_layer_b256": lambda: LutLayerWorkload(batch=256),
+}
+DEFAULT_WORKLOAD = "lut_layer"
+
+
+def cpu_baseline(wl, budget_s=12.0):
+    """Times the CPU oracle on a bounded sample of the workload (rank 0, N=1 only)."""
+    threads = os.cpu_count() or 1
+    batch = min(wl.units_per_step, 256)
+    dt = wl.cpu_step(batch, threads)  # warm-up and calibration
+    per_unit = max(dt / batch, 1e-9)
+    batch = int(max(batch, min(wl.units_per_step, budget_s / 3 / per_unit)))
+    times = [wl.cpu_step(batch, threads) for _ in range(3)]
+    best = min(times)
+    return {"value": batch / best, "unit": wl.unit, "cores": threads, "kind": "port",
+            "sample": f"{batch} samples of the same workload, best of 3, OpenMP over samples/detectors "
+                      f"({threads} threads; the reference's own CPU path is single-threaded)"}
+
+
+# ------------------------------------------------------------------------------------ arms
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    wl = WORKLOADS[args.workload]()
+    threads = os.cpu_count() or 1
+    batch = min(wl.units_per_step, 256)
+    per_unit = max(wl.cpu_step(batch, threads) / batch, 1e-9)
+    # each step is a bounded sample so that warmup + steps stay within ~2 minutes in total
+    total = max(1, args.steps + args.warmup)
+    batch = int(max(64, min(wl.units_per_step, 100.0 / total / per_unit)))
+    for _ in range(args.warmup):
+        wl.cpu_step(batch, threads)
+    times = [wl.cpu_step(batch, threads) for _ in range(args.steps)]
+    ms = 1e3 * sum(times) / len(times)
+    value = batch / (ms / 1e3)
+    sample = f"{batch} samples per step of the same workload, CPU oracle (port of the reference CPU path), {threads} threads"
+    print(json.dumps({
+        "impl": "reference", "metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic",
+        "config": {"workload": wl.name, "sample": sample},
+        "cpu_baseline": {"value": value, "unit": wl.unit, "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": wl.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    from spiky_b200 import _native
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device (no CPU fallback exists)"
+    torch.cuda.set_device(local_rank)
+    device = torch.device(f"cuda:{local_rank}")
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+
+    wl = WORKLOADS[args.workload]()
+    wl.setup(device, rank)
+    flush = None
+    if wl.l2_note == "flushed":
+        flush = torch.empty(2 * L2_BYTES, dtype=torch.uint8, device=device)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed_region(step_fn, steps, profile):
+        """Returns (ms per step measured with CUDA events on the current stream, launches)."""
+        _native.profiler_reset()
+        _native.profiler_enable(profile)
+        starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+        stops = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+        barrier()
+        for i in range(steps):
+            if flush is not None:
+                flush.zero_()
+            starts[i].record()
+            step_fn()
+            stops[i].record()
+        barrier()
+        ms = sum(a.elapsed_time(b) for a, b in zip(starts, stops)) / steps
+        prof = _native.profiler_read()
+        _native.profiler_enable(False)
+        return ms, prof
+
+    if args.profile_only:
+        # bare loop for profilers: warm-up + steps of the device-resident step, nothing else
+        for _ in range(args.warmup + args.steps):
+            wl.step_device()
+        torch.cuda.synchronize()
+        return
+    for _ in range(max(args.warmup, 3)):
+        wl.step_device()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    ms_dev, prof = timed_region(wl.step_device, args.steps, profile=True)
+    clocks = sampler.stop() if rank == 0 else None
+    for _ in range(2):
+        wl.step_e2e()
+    ms_e2e, _ = timed_region(wl.step_e2e, args.steps, profile=False)
+
+    t = torch.tensor([ms_dev, ms_e2e], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_dev, ms_e2e = t.tolist()
+    if rank == 0:
+        peak, peak_kind = measured_peaks()
+        units = wl.units_per_step * world
+        value = units / (ms_dev / 1e3)
+        launches = sum(v["launches"] for v in prof.values())
+        dom = wl.dominant_kernel
+        alg = wl.algorithmic_bytes()
+        per_kernel = {}
+        for k, v in prof.items():
+            if v["timed"]:
+                per_kernel[k] = {"ms_per_launch": v["ms"] / v["timed"], "launches": v["launches"],
+                                 "alg_gbs": (alg.get(k, 0) * wl.units_per_step * (args.steps / v["timed"]) / 1e9) / (v["ms"] / v["timed"] / 1e3) if v["ms"] > 0 else None}
+        d = prof[dom]
+        dom_ms = d["ms"] / max(d["timed"], 1)
+        launches_per_step = d["timed"] / args.steps
+        achieved = alg[dom] * wl.units_per_step / launches_per_step / 1e9 / (dom_ms / 1e3)
+        line = {
+            "metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_dev, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic",
+            "config": {"workload": wl.name, "l2": wl.l2_note, "per_gpu_units": wl.units_per_step},
+            "roofline": {"bound": "hbm", "kernel": dom, "achieved": achieved, "peak": peak, "unit": "GB/s",
+                         "frac": achieved / peak, "peak_kind": peak_kind, "traffic": None,
+                         "ms_per_launch": dom_ms},
+            "kernels": per_kernel,
+            "e2e": {"value": units / (ms_e2e / 1e3), "unit": wl.unit, "h2d_bytes_per_step": wl.h2d_bytes,
+                    "d2h_bytes_per_step": wl.d2h_bytes, "ms_per_step": ms_e2e},
+            "gpu_launches": int(launches),
+            "clocks": clocks,
+        }
+        if world == 1:
+            line["cpu_baseline"] = cpu_baseline(wl)
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
+    ap.add_argument("--profile-only", action="store_true",
+                    help="run only warm-up + steps of the device-resident step and exit (for ncu captures)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -62,6 +62,20 @@ int lutb_version(void);
 const char *lutb_last_error(void);
 
 /*
+ * Opt-in kernel profiler.  Stands in for LUTDataManager::get_profiling_stats / reset_profiler
+ * (spiky_cuda/lut/lut.cu:1274-1288; SimpleProfiler, spiky_cuda/misc/misc.h:365-405), which in the
+ * reference is always on and synchronises the stream after every launch.  Here launches are only
+ * counted by default; after lutb_profiler_enable(1) each launch is additionally bracketed by CUDA
+ * events on its stream, resolved lazily by lutb_profiler_read (which waits for the recorded events).
+ * Kernel ids run from 0 to lutb_profiler_kernel_count() - 1.
+ */
+int lutb_profiler_enable(int on);
+int lutb_profiler_reset(void);
+int lutb_profiler_kernel_count(void);
+const char *lutb_profiler_kernel_name(int kernel_id);
+int lutb_profiler_read(int kernel_id, double *total_ms, int64_t *timed_launches, int64_t *launches);
+
+/*
  * Non-sequence, fully connected forward.  Replaces LUTDataManager::forward_step
  * (spiky_cuda/lut/lut.cu:629-716 -> LUTRuntimeContext::forward_step, lut_runtime.cu:76-211).
  *   weights    fp32 [Nt * 2^Nc * O]        anchors  int32 [Nt * Nc * 2] (-1 = unused pair)

@@ -45,6 +45,11 @@ _cfgp = ctypes.POINTER(LayerCfg)
 SIGNATURES = {
     "lutb_version": (_int, []),
     "lutb_last_error": (ctypes.c_char_p, []),
+    "lutb_profiler_enable": (_int, [_int]),
+    "lutb_profiler_reset": (_int, []),
+    "lutb_profiler_kernel_count": (_int, []),
+    "lutb_profiler_kernel_name": (ctypes.c_char_p, [_int]),
+    "lutb_profiler_read": (_int, [_int, ctypes.POINTER(_dbl), ctypes.POINTER(_i64), ctypes.POINTER(_i64)]),
     "lutb_nonseq_fc_forward": (_int, [_cfgp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "lutb_nonseq_fc_backward_workspace": (_size, [_cfgp, _i64, _int]),
     "lutb_nonseq_fc_backward": (_int, [_cfgp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _dbl, _int, _vp, _size, _vp]),
@@ -84,3 +89,22 @@ def check(status):
     if status < 0:
         raise ValueError(msg)
     raise LutbError(f"CUDA error {status}: {msg}")
+
+
+def profiler_enable(on=True):
+    check(lib().lutb_profiler_enable(int(bool(on))))
+
+
+def profiler_reset():
+    check(lib().lutb_profiler_reset())
+
+
+def profiler_read():
+    """{kernel family: {"ms": resolved device time, "timed": launches timed, "launches": launches counted}}."""
+    L = lib()
+    out = {}
+    for k in range(L.lutb_profiler_kernel_count()):
+        ms, timed, launches = _dbl(0.0), _i64(0), _i64(0)
+        check(L.lutb_profiler_read(k, ctypes.byref(ms), ctypes.byref(timed), ctypes.byref(launches)))
+        out[L.lutb_profiler_kernel_name(k).decode()] = {"ms": ms.value, "timed": timed.value, "launches": launches.value}
+    return out

@@ -2,6 +2,10 @@
 #include <stdarg.h>
 #include <string.h>
 
+#include <atomic>
+#include <mutex>
+#include <vector>
+
 #include "lutb_common.cuh"
 
 namespace lutb {
@@ -59,12 +63,101 @@ int launch_fixed_to_float(float *buf, int64_t n, double rescaler, cudaStream_t s
     int64_t blocks = (n + 255) / 256;
     int64_t cap = (int64_t)device_info().sm_count * 16;
     if (blocks > cap) blocks = cap;
+    KernelScope scope(K_FIXED_TO_FLOAT, stream);
     fixed_to_float_kernel<<<(unsigned)blocks, 256, 0, stream>>>(buf, n, rescaler);
     LUTB_LAUNCH_CHECK();
     return LUTB_OK;
 }
 
+// ------------------------------------------------------------------------------ profiler
+static const char *const kKernelNames[K_COUNT] = {
+    "check_detectors", "fc_gather_forward", "fc_input_grad", "fc_weight_grad", "fixed_to_float",
+};
+
+struct EventPair {
+    cudaEvent_t start, stop;
+    int id;
+};
+static std::mutex g_prof_mutex;
+static std::atomic<int> g_prof_enabled{0};
+static std::atomic<long long> g_launches[K_COUNT];
+static std::vector<EventPair> g_pairs;      // recorded since the last reset
+static std::vector<EventPair> g_free;       // recycled events
+static double g_total_ms[K_COUNT];           // resolved time
+static long long g_timed[K_COUNT];           // launches with resolved time
+constexpr size_t kMaxPendingPairs = 1 << 16;
+
+KernelScope::KernelScope(KernelId id, cudaStream_t stream) : stream_(stream), stop_(nullptr) {
+    g_launches[id].fetch_add(1, std::memory_order_relaxed);
+    if (!g_prof_enabled.load(std::memory_order_relaxed)) return;
+    std::lock_guard<std::mutex> lock(g_prof_mutex);
+    if (g_pairs.size() >= kMaxPendingPairs) return;
+    EventPair p;
+    if (!g_free.empty()) {
+        p = g_free.back();
+        g_free.pop_back();
+    } else {
+        if (cudaEventCreate(&p.start) != cudaSuccess) return;
+        if (cudaEventCreate(&p.stop) != cudaSuccess) { cudaEventDestroy(p.start); return; }
+    }
+    p.id = id;
+    cudaEventRecord(p.start, stream);
+    g_pairs.push_back(p);
+    stop_ = p.stop;
+}
+
+KernelScope::~KernelScope() {
+    if (stop_) cudaEventRecord(stop_, stream_);
+}
+
+static void resolve_pending_locked() {
+    for (EventPair &p : g_pairs) {
+        float ms = 0.f;
+        if (cudaEventSynchronize(p.stop) == cudaSuccess && cudaEventElapsedTime(&ms, p.start, p.stop) == cudaSuccess) {
+            g_total_ms[p.id] += ms;
+            g_timed[p.id] += 1;
+        }
+        g_free.push_back(p);
+    }
+    g_pairs.clear();
+}
+
 }  // namespace lutb
+
+extern "C" int lutb_profiler_enable(int on) {
+    lutb::g_prof_enabled.store(on ? 1 : 0);
+    return LUTB_OK;
+}
+
+extern "C" int lutb_profiler_reset(void) {
+    std::lock_guard<std::mutex> lock(lutb::g_prof_mutex);
+    lutb::resolve_pending_locked();
+    for (int i = 0; i < lutb::K_COUNT; i++) {
+        lutb::g_total_ms[i] = 0.0;
+        lutb::g_timed[i] = 0;
+        lutb::g_launches[i].store(0);
+    }
+    return LUTB_OK;
+}
+
+extern "C" int lutb_profiler_kernel_count(void) { return lutb::K_COUNT; }
+
+extern "C" const char *lutb_profiler_kernel_name(int kernel_id) {
+    return (kernel_id >= 0 && kernel_id < lutb::K_COUNT) ? lutb::kKernelNames[kernel_id] : "";
+}
+
+extern "C" int lutb_profiler_read(int kernel_id, double *total_ms, int64_t *timed_launches, int64_t *launches) {
+    if (kernel_id < 0 || kernel_id >= lutb::K_COUNT) {
+        lutb::set_error("unknown kernel id %d", kernel_id);
+        return LUTB_ERR_SHAPE;
+    }
+    std::lock_guard<std::mutex> lock(lutb::g_prof_mutex);
+    lutb::resolve_pending_locked();
+    if (total_ms) *total_ms = lutb::g_total_ms[kernel_id];
+    if (timed_launches) *timed_launches = lutb::g_timed[kernel_id];
+    if (launches) *launches = lutb::g_launches[kernel_id].load();
+    return LUTB_OK;
+}
 
 extern "C" int lutb_version(void) { return 100; }
 extern "C" const char *lutb_last_error(void) { return lutb::g_error; }

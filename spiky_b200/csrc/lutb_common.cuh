@@ -54,6 +54,31 @@ DeviceInfo device_info();
 
 int validate_cfg(const lutb_layer_cfg *cfg);
 
+// Kernel families, as reported by the opt-in profiler (lutb_profiler_*) and the launch counter.
+enum KernelId {
+    K_CHECK_DETECTORS = 0,
+    K_FC_GATHER_FORWARD,
+    K_FC_INPUT_GRAD,
+    K_FC_WEIGHT_GRAD,
+    K_FIXED_TO_FLOAT,
+    K_COUNT
+};
+
+// RAII marker around one kernel launch: always bumps the launch counter; when the profiler is enabled
+// it also brackets the launch with CUDA events on the launching stream (no synchronisation here, the
+// events are resolved when the profiler is read).
+class KernelScope {
+public:
+    KernelScope(KernelId id, cudaStream_t stream);
+    ~KernelScope();
+    KernelScope(const KernelScope &) = delete;
+    KernelScope &operator=(const KernelScope &) = delete;
+
+private:
+    cudaStream_t stream_;
+    cudaEvent_t stop_;
+};
+
 // Dead-band comparison "delta > 0" (reference: ROUNDED_COMPARISON_GREATER, misc.h:16).
 __device__ __forceinline__ bool greater_than_zero(float delta, float cmp_eps) {
     if (cmp_eps == 0.0f) return delta > 0.0f;

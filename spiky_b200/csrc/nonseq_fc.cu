@@ -146,6 +146,7 @@ static int launch_check_detectors_r(const float *x, int64_t rows, int n_inputs, 
     const bool train = min_delta != nullptr;
     auto kern = train ? check_detectors_kernel<R, true> : check_detectors_kernel<R, false>;
     if (smem > 48 * 1024) LUTB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    KernelScope scope(K_CHECK_DETECTORS, stream);
     kern<<<(unsigned)blocks, tpg * groups, smem, stream>>>(x, rows, n_inputs, reinterpret_cast<const int2 *>(anchors),
                                                           n_detectors, n_anchors, cmp_eps, tpg, idx, min_delta, min_k);
     LUTB_LAUNCH_CHECK();
@@ -167,6 +168,7 @@ int launch_check_detectors(const float *x, int64_t rows, int n_inputs, const int
         const bool train = min_delta != nullptr;
         const int64_t total = rows * n_detectors;
         int64_t blocks = min((total + 255) / 256, (int64_t)sm * 32);
+        KernelScope scope(K_CHECK_DETECTORS, stream);
         if (train)
             check_detectors_global_kernel<true><<<(unsigned)blocks, 256, 0, stream>>>(
                 x, rows, n_inputs, reinterpret_cast<const int2 *>(anchors), n_detectors, n_anchors, cmp_eps, idx,
@@ -369,6 +371,7 @@ int launch_fc_gather_forward(const float *W, const int32_t *idx, float *y, int64
     dim3 grid((unsigned)blocks, (unsigned)n_chunks);
     for (int64_t t0 = 0; t0 < n_detectors; t0 += per_range) {
         const int t1 = (int)min((int64_t)n_detectors, t0 + per_range);
+        KernelScope scope(K_FC_GATHER_FORWARD, stream);
         if (vec4) {
             if (int_mode)
                 fc_gather_forward_kernel<4, true><<<grid, warps * 32, 0, stream>>>(W, idx, y, batch, n_outputs, n_detectors, table_rows, (int)t0, t1, det_block, lanes, chunk, fixed_scale);
@@ -584,6 +587,8 @@ int launch_fc_backward(const lutb_layer_cfg *cfg, int64_t batch, float *W, const
     const int sm = device_info().sm_count;
 
     // input gradient
+    {
+    KernelScope scope(K_FC_INPUT_GRAD, stream);
     if (int_mode) {
         const int64_t total = batch * Nt;
         const int64_t gblocks = min((total + 127) / 128, (int64_t)sm * 64);
@@ -599,6 +604,7 @@ int launch_fc_backward(const lutb_layer_cfg *cfg, int64_t batch, float *W, const
             W, dY, reinterpret_cast<const int2 *>(anchors), idx, min_delta, min_k, dX, batch, cfg->n_inputs, O, Nt,
             cfg->n_anchors, T, lanes);
     }
+    }
     LUTB_LAUNCH_CHECK();
 
     // table gradient (or in-place update)
@@ -606,6 +612,7 @@ int launch_fc_backward(const lutb_layer_cfg *cfg, int64_t batch, float *W, const
     const int n_chunks = (O + chunk - 1) / chunk;
     LUTB_REQUIRE(n_chunks <= 65535, LUTB_ERR_SHAPE, "too many output chunks");
     dim3 grid((unsigned)blocks, (unsigned)n_chunks);
+    KernelScope scope(K_FC_WEIGHT_GRAD, stream);
     if (vec4) {
         if (int_mode)
             fc_weight_grad_atomic_kernel<4, true><<<grid, warps * 32, 0, stream>>>(dY, idx, target, batch, O, Nt, T, lanes, chunk, lr, cfg->int_rescaler);
