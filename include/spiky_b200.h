@@ -104,6 +104,46 @@ int lutb_nonseq_fc_backward(const lutb_layer_cfg *cfg, int64_t batch, float *wei
                             const int32_t *min_k, float *dX, float *dW, double external_lr, int dw_variant,
                             void *workspace, size_t workspace_bytes, void *stream);
 
+/*
+ * Sparse lookup -> output connectivity (projection / convolution layers), all arrays in device memory.
+ * Stands in for the reference's forward-synapse-group arena (ForwardSynapseGroup runs per lookup neuron,
+ * spiky_cuda/connections_manager/connections_manager.h:39-66, indexed through NoDelaysIndexedSynapsesInfo,
+ * :124-131).  The lookup neurons (table rows) of one detector share one target list; the flat weight
+ * array keeps the reference's slot layout: synapse p of a row at row_base + p + 2 * (p / group_size),
+ * rows det_stride apart.
+ */
+typedef struct lutb_sparse_index {
+    const int64_t *det_wbase;   /* [Nt] weight slot of (row 0, synapse 0) */
+    const int32_t *det_stride;  /* [Nt] slots between consecutive rows */
+    const int32_t *det_count;   /* [Nt] synapses per row */
+    const int32_t *det_sstart;  /* [Nt] exclusive prefix sum of det_count */
+    const int32_t *syn_det;     /* [n_syn_per_sample] detector of each (detector, synapse) pair, detector order */
+    const int32_t *syn_target;  /* [n_syn_per_sample] output index of each pair */
+    int64_t n_syn_per_sample;   /* sum of det_count */
+    int64_t n_weights;          /* length of the flat weight array */
+    int32_t group_size;         /* forward_group_size G */
+    int32_t max_count;          /* max of det_count */
+} lutb_sparse_index;
+
+/*
+ * Non-sequence, sparse forward.  Replaces LUTDataManager::forward_step for layers built with lookup
+ * connections (lut.cu:629-716 -> fill_outputs_non_seq_sparse_logic, lut_runtime_kernels_logic.proto:1160-1212).
+ * Arguments as lutb_nonseq_fc_forward; weights is fp32 [sp->n_weights].
+ */
+int lutb_nonseq_sparse_forward(const lutb_layer_cfg *cfg, const lutb_sparse_index *sp, int64_t batch,
+                               const float *weights, const float *x, const int32_t *anchors, float *y,
+                               int32_t *idx, float *min_delta, int32_t *min_k, void *stream);
+
+/*
+ * Non-sequence, sparse backward.  Replaces LUTDataManager::backward_backprop for sparse layers
+ * (lut.cu:1030-1088 -> propagate_through_detectors_non_seq_sparse_logic, proto:1303-1419, and
+ * gather_w_gradients_non_seq_sparse_logic, proto:1501-1545).  Arguments as lutb_nonseq_fc_backward.
+ */
+int lutb_nonseq_sparse_backward(const lutb_layer_cfg *cfg, const lutb_sparse_index *sp, int64_t batch,
+                                float *weights, const float *dY, const int32_t *anchors, const int32_t *idx,
+                                const float *min_delta, const int32_t *min_k, float *dX, float *dW,
+                                double external_lr, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

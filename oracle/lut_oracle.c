@@ -229,3 +229,113 @@ void orc_nonseq_fc_backward(float *W, const float *dY, const int32_t *anchors, c
         if (dW) orc_int_to_float(dW, (int64_t)Nt * T * O, rescaler);
     }
 }
+
+/* ------------------------------------------------------------------------------------------
+ * Sparse (projection / convolution) lookup -> output connectivity.
+ *
+ * The reference stores, per lookup neuron, a run of "forward synapse groups": an 8-byte header
+ * followed by up to G 4-byte target ids (spiky_cuda/connections_manager/connections_manager.h:39-66).
+ * The weight of a synapse lives in a separate fp32 array at the index of its target id inside the
+ * arena, counted in 4-byte words from the first synapse (lut_runtime_kernels_logic.proto:227), so
+ * every group header leaves two unused weight slots.  In all reference layer types the lookup
+ * neurons of one detector share one target list, and neurons are laid out in id order; the oracle
+ * therefore takes the connectivity per detector:
+ *   det_wbase[t]   weight index of synapse 0 of row 0
+ *   det_stride[t]  weight-index distance between consecutive rows (= P + 2*ceil(P/G))
+ *   det_count[t]   P, synapses per row
+ *   det_toff[t]    offset of the detector's target list (output indices, synapse order) in `targets`
+ * Synapse p of a row sits at row_base + p + 2*(p/G); group `ob` holds synapses [ob*G, ob*G+G).
+ * ------------------------------------------------------------------------------------------ */
+static inline int64_t orc_syn_slot(int64_t row_base, int p, int G) { return row_base + p + 2 * (p / G); }
+
+/* fill_outputs_non_seq_sparse_logic + fire_single_synapse_group (proto:1160-1212, 215-313) */
+void orc_nonseq_sparse_forward(const float *W, const int32_t *idx, float *y, int64_t B, int O, int Nt,
+                               const int64_t *det_wbase, const int32_t *det_stride, const int32_t *det_count,
+                               const int32_t *det_toff, const int32_t *targets, int G, int int_mode,
+                               double rescaler) {
+    ORC_PARALLEL_FOR
+    for (int64_t b = 0; b < B; b++) {
+        float *yb = y + b * O;
+        for (int t = 0; t < Nt; t++) {
+            int64_t row = det_wbase[t] + (int64_t)idx[b * Nt + t] * det_stride[t];
+            const int32_t *tg = targets + det_toff[t];
+            for (int p = 0; p < det_count[t]; p++) {
+                double w = (double)W[orc_syn_slot(row, p, G)];
+                if (int_mode)
+                    *(int32_t *)(yb + tg[p]) += (int32_t)(w * ORC_DENOM * rescaler);
+                else
+                    yb[tg[p]] += (float)w;
+            }
+        }
+    }
+    if (int_mode) orc_int_to_float(y, B * O, rescaler);
+}
+
+/* propagate_through_detectors_non_seq_sparse_logic (proto:1303-1419, helper :315-395) and
+ * gather_w_gradients_non_seq_sparse_logic (proto:1501-1545, helper :584-714).
+ * n_weights is the length of W / dW. */
+void orc_nonseq_sparse_backward(float *W, const float *dY, const int32_t *anchors, const int32_t *idx,
+                                const float *min_delta, const int32_t *min_k, float *dX, float *dW, int64_t B,
+                                int I, int O, int Nt, int Nc, const int64_t *det_wbase,
+                                const int32_t *det_stride, const int32_t *det_count, const int32_t *det_toff,
+                                const int32_t *targets, int G, int64_t n_weights, double lr_meta, double ext_lr,
+                                int int_mode, double rescaler) {
+    ORC_PARALLEL_FOR
+    for (int64_t b = 0; b < B; b++) {
+        const float *dy = dY + b * O;
+        float *dx = dX + b * (int64_t)I;
+        for (int t = 0; t < Nt; t++) {
+            int32_t li = idx[b * Nt + t];
+            int32_t k = min_k[b * Nt + t];
+            int P = det_count[t];
+            int64_t row = det_wbase[t] + (int64_t)li * det_stride[t];
+            int64_t alt = det_wbase[t] + (int64_t)(li ^ (1 << k)) * det_stride[t];
+            const int32_t *tg = targets + det_toff[t];
+            int n_groups = (P + G - 1) / G;
+            for (int ob = 0; ob < n_groups; ob++) {
+                int p0 = ob * G, p1 = p0 + G < P ? p0 + G : P;
+                double du = orc_up(min_delta[b * Nt + t]);
+                double ms = 0.0, as = 0.0;
+                for (int p = p0; p < p1; p++) ms += (double)W[orc_syn_slot(row, p, G)] * (double)dy[tg[p]];
+                for (int p = p0; p < p1; p++) as += (double)W[orc_syn_slot(alt, p, G)] * (double)dy[tg[p]];
+                du *= ms - as;
+                if (fabs(du) > ORC_EPS) {
+                    int32_t a1 = anchors[((int64_t)t * Nc + k) * 2], a2 = anchors[((int64_t)t * Nc + k) * 2 + 1];
+                    if (int_mode) {
+                        int32_t d = (int32_t)(du * ORC_DENOM * rescaler);
+                        *(int32_t *)(dx + a1) += d;
+                        *(int32_t *)(dx + a2) -= d;
+                    } else {
+                        dx[a1] += du;
+                        dx[a2] -= du;
+                    }
+                }
+            }
+        }
+    }
+    double lr = lr_meta;
+    if (ext_lr >= 0) lr *= -ext_lr;
+    float *target = ext_lr >= 0 ? W : dW;
+    ORC_PARALLEL_FOR
+    for (int t = 0; t < Nt; t++) {
+        const int32_t *tg = targets + det_toff[t];
+        for (int64_t b = 0; b < B; b++) {
+            const float *dy = dY + b * O;
+            int64_t row = det_wbase[t] + (int64_t)idx[b * Nt + t] * det_stride[t];
+            for (int p = 0; p < det_count[t]; p++) {
+                double g = (double)dy[tg[p]];
+                if (fabs(g) > ORC_EPS) {
+                    int64_t slot = orc_syn_slot(row, p, G);
+                    if (int_mode)
+                        *(int32_t *)(target + slot) += (int32_t)(g * lr * ORC_DENOM * rescaler);
+                    else
+                        target[slot] += (float)(g * lr);
+                }
+            }
+        }
+    }
+    if (int_mode) {
+        orc_int_to_float(dX, B * (int64_t)I, rescaler);
+        if (dW) orc_int_to_float(dW, n_weights, rescaler);
+    }
+}

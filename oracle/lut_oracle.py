@@ -128,3 +128,50 @@ def nonseq_fc_backward(W, dY, anchors, idx, min_delta, min_k, n_inputs, n_anchor
                                  _d(float(np.float32(lr_meta))), _d(float(np.float32(external_lr))),
                                  _i(int(int_mode)), _d(int_rescaler))
     return dX, dW
+
+
+def _i64(a):
+    return np.ascontiguousarray(a, dtype=np.int64)
+
+
+def nonseq_sparse_forward(W, x, anchors, sp, n_anchors, n_outputs, cmp_eps=0.0, train=True, int_mode=False,
+                          int_rescaler=0.001):
+    """One ``forward_step`` of a sparse non-sequence layer.  ``sp`` holds the per-detector connectivity:
+    dict(det_wbase, det_stride, det_count, det_sstart, syn_target, group_size)."""
+    x = _f32(x)
+    B = x.shape[0]
+    Nt = len(sp["det_count"])
+    W = _f32(W).reshape(-1)
+    res = check_detectors(x, anchors, Nt, n_anchors, cmp_eps, train)
+    idx, md, mk = res if train else (res, None, None)
+    y = np.zeros((B, n_outputs), np.float32)
+    lib().orc_nonseq_sparse_forward(_ptr(W), _ptr(idx), _ptr(y), _l(B), _i(n_outputs), _i(Nt),
+                                    _ptr(_i64(sp["det_wbase"])), _ptr(_i32(sp["det_stride"])),
+                                    _ptr(_i32(sp["det_count"])), _ptr(_i32(sp["det_sstart"])),
+                                    _ptr(_i32(sp["syn_target"])), _i(int(sp["group_size"])), _i(int(int_mode)),
+                                    _d(int_rescaler))
+    return y, idx, md, mk
+
+
+def nonseq_sparse_backward(W, dY, anchors, idx, min_delta, min_k, sp, n_inputs, n_anchors, lr_meta=1.0,
+                           external_lr=-1.0, int_mode=False, int_rescaler=0.001):
+    """One ``backward_backprop`` of a sparse non-sequence layer; returns (dX, dW or None)."""
+    dY = _f32(dY)
+    B, O = dY.shape
+    Nt = idx.shape[1]
+    if external_lr >= 0:
+        assert W.dtype == np.float32 and W.flags["C_CONTIGUOUS"] and W.flags["WRITEABLE"]
+        Wf, dW = W.reshape(-1), None
+    else:
+        Wf = _f32(W).reshape(-1)
+        dW = np.zeros(Wf.size, np.float32)
+    dX = np.zeros((B, n_inputs), np.float32)
+    anchors = _i32(anchors).reshape(-1)
+    lib().orc_nonseq_sparse_backward(_ptr(Wf), _ptr(dY), _ptr(anchors), _ptr(_i32(idx)), _ptr(_f32(min_delta)),
+                                     _ptr(_i32(min_k)), _ptr(dX), _ptr(dW), _l(B), _i(n_inputs), _i(O), _i(Nt),
+                                     _i(n_anchors), _ptr(_i64(sp["det_wbase"])), _ptr(_i32(sp["det_stride"])),
+                                     _ptr(_i32(sp["det_count"])), _ptr(_i32(sp["det_sstart"])),
+                                     _ptr(_i32(sp["syn_target"])), _i(int(sp["group_size"])), _l(Wf.size),
+                                     _d(float(np.float32(lr_meta))), _d(float(np.float32(external_lr))),
+                                     _i(int(int_mode)), _d(int_rescaler))
+    return dX, dW

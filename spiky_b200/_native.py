@@ -34,12 +34,30 @@ class LayerCfg(ctypes.Structure):
     ]
 
 
+class SparseIndexC(ctypes.Structure):
+    """Mirror of ``lutb_sparse_index`` (device pointers)."""
+
+    _fields_ = [
+        ("det_wbase", ctypes.c_void_p),
+        ("det_stride", ctypes.c_void_p),
+        ("det_count", ctypes.c_void_p),
+        ("det_sstart", ctypes.c_void_p),
+        ("syn_det", ctypes.c_void_p),
+        ("syn_target", ctypes.c_void_p),
+        ("n_syn_per_sample", ctypes.c_int64),
+        ("n_weights", ctypes.c_int64),
+        ("group_size", ctypes.c_int32),
+        ("max_count", ctypes.c_int32),
+    ]
+
+
 _vp = ctypes.c_void_p
 _i64 = ctypes.c_int64
 _int = ctypes.c_int
 _dbl = ctypes.c_double
 _size = ctypes.c_size_t
 _cfgp = ctypes.POINTER(LayerCfg)
+_spp = ctypes.POINTER(SparseIndexC)
 
 # name -> (restype, argtypes); every symbol include/spiky_b200.h declares is listed here
 SIGNATURES = {
@@ -53,6 +71,8 @@ SIGNATURES = {
     "lutb_nonseq_fc_forward": (_int, [_cfgp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "lutb_nonseq_fc_backward_workspace": (_size, [_cfgp, _i64, _int]),
     "lutb_nonseq_fc_backward": (_int, [_cfgp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _dbl, _int, _vp, _size, _vp]),
+    "lutb_nonseq_sparse_forward": (_int, [_cfgp, _spp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "lutb_nonseq_sparse_backward": (_int, [_cfgp, _spp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _dbl, _vp]),
 }
 
 _lib = None

@@ -61,6 +61,9 @@ enum KernelId {
     K_FC_INPUT_GRAD,
     K_FC_WEIGHT_GRAD,
     K_FIXED_TO_FLOAT,
+    K_SPARSE_FORWARD,
+    K_SPARSE_INPUT_GRAD,
+    K_SPARSE_WEIGHT_GRAD,
     K_COUNT
 };
 

@@ -309,11 +309,27 @@ class _LUTDataManager:
         if t.numel() != numel:
             raise ValueError(f"{name} has {t.numel()} elements, expected {numel}")
 
-    def _sparse_forward(self, *args):
-        raise ValueError("sparse connectivity is not attached")
+    def _sparse_forward(self, L, cfg, B, r_weights, r_input, r_detector_anchors, w_output, w_lookup_indices,
+                        w_min_anchor_deltas, w_min_anchor_delta_indices):
+        if self._sparse is None:
+            raise ValueError("sparse connectivity is not attached")
+        sp = self._sparse.c_struct()
+        return L.lutb_nonseq_sparse_forward(ctypes.byref(cfg), ctypes.byref(sp), B, _ptr(r_weights), _ptr(r_input),
+                                            _ptr(r_detector_anchors), _ptr(w_output), _ptr(w_lookup_indices),
+                                            _ptr(w_min_anchor_deltas), _ptr(w_min_anchor_delta_indices),
+                                            self._stream())
 
-    def _sparse_backward(self, *args):
-        raise ValueError("sparse connectivity is not attached")
+    def _sparse_backward(self, L, cfg, B, r_weights, r_output_gradients, r_detector_anchors, r_lookup_indices,
+                         r_min_anchor_deltas, r_min_anchor_delta_indices, w_input_gradients, external_lr,
+                         w_weights_gradients):
+        if self._sparse is None:
+            raise ValueError("sparse connectivity is not attached")
+        sp = self._sparse.c_struct()
+        return L.lutb_nonseq_sparse_backward(ctypes.byref(cfg), ctypes.byref(sp), B, _ptr(r_weights),
+                                             _ptr(r_output_gradients), _ptr(r_detector_anchors),
+                                             _ptr(r_lookup_indices), _ptr(r_min_anchor_deltas),
+                                             _ptr(r_min_anchor_delta_indices), _ptr(w_input_gradients),
+                                             _ptr(w_weights_gradients), float(external_lr), self._stream())
 
 
 class LUTDataManagerF(_LUTDataManager):

@@ -23,6 +23,7 @@ import torch.nn as nn
 
 from .lut_data_manager import LUTDataManagerF, LUTDataManagerI
 from . import structure as _structure
+from .structure import PointSamplingPolicy, PointSamplingType  # noqa: F401  (part of the public surface)
 
 
 class GradientType(Enum):
@@ -631,3 +632,91 @@ class LUTLayer(Conv2DLUTLayer):
     def __repr__(self):
         return (f"LUTLayer({self.n_inputs()} inputs, {self.n_detectors()} detectors, {self.n_outputs()} outputs, "
                 f"{self.n_anchors_per_detector()} anchors per detector)")
+
+
+class ProjectionLUTLayer(LUTLayerBasic):
+    """Groups of detectors on rectangles of a 2-D input; every table row of a group projects onto a small
+    rectangle of the 2-D output around the group's (rescaled) centre
+    (reference: ProjectionLUTLayer, LUTLayer.py:1511-1648)."""
+
+    def __init__(self, input_shape, output_shape, n_anchors_per_detector, n_detector_groups, n_detectors_in_group,
+                 receptive_shape, projection_shape, synapse_meta=SynapseMeta(), projection_prob=1.0,
+                 detectors_sampling_policy: PointSamplingPolicy = PointSamplingPolicy(PointSamplingType.RandomUniform),
+                 input_sparsity_mask=None, output_sparsity_mask=None, weights_gradient_policy: GradientPolicy = None,
+                 shared_context: LUTSharedContext = None, summation_dtype=torch.float32, _int_rescaler=0.001,
+                 _forward_group_size=32, _backward_group_size=32, _max_groups_in_growth_buffer=2 ** 20,
+                 random_seed=None, device=None):
+        assert n_detector_groups >= 1 and n_detectors_in_group >= 1
+        assert 0.0 < projection_prob <= 1.0
+        self._n_detector_groups = n_detector_groups
+        self._n_detectors_in_group = n_detectors_in_group
+        self._input_shape = tuple(input_shape)
+        self._output_shape = tuple(output_shape)
+        h, w = input_shape
+        oh, ow = output_shape
+        super().__init__(
+            n_inputs=h * w, n_outputs=oh * ow, n_detectors=n_detector_groups * n_detectors_in_group,
+            n_anchors_per_detector=n_anchors_per_detector, is_fully_connected=False, sequence_length=1,
+            synapse_metas=[synapse_meta], weights_gradient_policy=weights_gradient_policy,
+            shared_context=shared_context, summation_dtype=summation_dtype, _int_rescaler=_int_rescaler,
+            _forward_group_size=_forward_group_size, _backward_group_size=_backward_group_size,
+            random_seed=random_seed)
+
+        centers = _structure.sample_centers(detectors_sampling_policy, n_detector_groups, h, w, random_seed)
+        self._group_centers = centers
+        # detector inputs: grid points within (r-1)/2 of the centre
+        pools, counts = _structure.rectangle_members(centers, (receptive_shape[0] - 1) / 2 + 1e-4,
+                                                     (receptive_shape[1] - 1) / 2 + 1e-4, h, w, input_sparsity_mask)
+        pools = pools.repeat_interleave(n_detectors_in_group, dim=0)
+        counts = counts.repeat_interleave(n_detectors_in_group)
+        self._set_anchors(_structure.sample_anchor_pairs(pools, counts, n_anchors_per_detector, random_seed))
+        # lookup -> output: output cells within r/2 of the centre rescaled to output coordinates
+        scaled = centers.clone()
+        scaled[:, 0] *= ow / w
+        scaled[:, 1] *= oh / h
+        targets, tcounts = _structure.rectangle_members(scaled, projection_shape[0] / 2 + 1e-4,
+                                                        projection_shape[1] / 2 + 1e-4, oh, ow, output_sparsity_mask)
+        if projection_prob < 1.0:
+            gen = torch.Generator(device="cpu")
+            if random_seed is not None:
+                gen.manual_seed(int(random_seed) + 1)
+            keep = (torch.rand(targets.shape, generator=gen) < projection_prob) & (targets >= 0)
+            order = torch.argsort((~keep).to(torch.int8), dim=1, stable=True)
+            targets = torch.where(torch.gather(keep, 1, order), torch.gather(targets, 1, order),
+                                  torch.full_like(targets, -1))
+            tcounts = keep.sum(dim=1)
+        targets = targets.repeat_interleave(n_detectors_in_group, dim=0)
+        tcounts = tcounts.repeat_interleave(n_detectors_in_group)
+        index = _structure.SparseIndex.from_detector_targets(
+            targets, tcounts, rows_per_detector=1 << n_anchors_per_detector, group_size=_forward_group_size,
+            n_outputs=oh * ow)
+        self._lut_dm.set_sparse_index(index)
+        self._weights = nn.Parameter(index.initial_weights(synapse_meta, random_seed))
+        if device is not None:
+            self.to(device=device)
+
+    def load_structure(self, anchors, source_ids, weight_slots, target_ids, n_weights):
+        """Adopt the structure of a reference-built layer: its anchor pairs and its synapse export (per
+        synapse: lookup neuron id, slot in the flat weight array, output index).  Weights of that layer
+        can then be copied into ``_weights`` verbatim."""
+        self._set_anchors(torch.as_tensor(anchors))
+        index = _structure.SparseIndex.from_export(
+            source_ids, weight_slots, target_ids, self._n_detectors, 1 << self._n_anchors_per_detector,
+            self._forward_group_size, self._n_outputs, n_weights)
+        self._lut_dm.set_sparse_index(index)
+        self._weights = nn.Parameter(torch.zeros(n_weights, dtype=torch.float32, device=self.device))
+        self._lut_dm.to_device(self.device.index if self.device.type == "cuda" else -1)
+        return self
+
+    def input_shape(self):
+        return self._input_shape
+
+    def output_shape(self):
+        return self._output_shape
+
+    def detectors_shape(self):
+        return (self._n_detector_groups, self._n_detectors_in_group)
+
+    def __repr__(self):
+        return (f"ProjectionLUTLayer(input_shape={self.input_shape()}, output_shape={self.output_shape()}, "
+                f"n_detectors={self._n_detectors}, n_anchors_per_detector={self.n_anchors_per_detector()})")

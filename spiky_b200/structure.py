@@ -14,7 +14,62 @@ the LUT layers is simple and is restated here directly:
   drawn independently per pair (prepare_detectors_compact_logic,
   spiky_cuda/lut/lut_compile_time_kernels_logic.proto:70-125)
 """
+from dataclasses import dataclass
+from enum import Enum
+
 import torch
+
+
+class PointSamplingType(Enum):
+    """How the centres of detector groups are placed (reference: synapse_growth.py:498-502)."""
+    RandomUniform = 0
+    RandomNormal = 1
+    Grid = 2
+
+
+@dataclass(frozen=True)
+class PointSamplingPolicy:
+    """Same fields as the reference's policy object (synapse_growth.py:505-528)."""
+    type: PointSamplingType
+    mu: float = None
+    sigma: float = None
+    pad_h: float = 0.0
+    pad_w: float = 0.0
+    grid_h: int = None
+    grid_w: int = None
+    stride_h: int = None
+    stride_w: int = None
+
+    def __post_init__(self):
+        if self.sigma is not None:
+            assert self.sigma > 0.0
+        assert self.pad_h >= 0.0 and self.pad_w >= 0.0
+
+
+def sample_centers(policy, n_points, h, w, seed=None):
+    """float32 [n_points, 2] (x, y) centres inside the (h, w) grid according to `policy`
+    (reference: sample_random_points / sample_grid_points, synapse_growth.py:452-495)."""
+    if policy.type == PointSamplingType.Grid:
+        assert policy.grid_h is not None and policy.grid_w is not None
+        assert policy.grid_h * policy.grid_w == n_points
+        xs = policy.pad_w + policy.stride_w * torch.arange(policy.grid_w, dtype=torch.float32)
+        ys = policy.pad_h + policy.stride_h * torch.arange(policy.grid_h, dtype=torch.float32)
+        yy, xx = torch.meshgrid(ys, xs, indexing="ij")
+        return torch.stack([xx.reshape(-1), yy.reshape(-1)], dim=1)
+    gen = torch.Generator(device="cpu")
+    if seed is not None:
+        gen.manual_seed(int(seed))
+    if policy.type == PointSamplingType.RandomNormal:
+        mu = policy.mu if policy.mu is not None else (w / 2.0, h / 2.0)
+        sigma = policy.sigma if policy.sigma is not None else (w / 6.0, h / 6.0)
+        mu = mu if isinstance(mu, (tuple, list)) else (mu, mu)
+        sigma = sigma if isinstance(sigma, (tuple, list)) else (sigma, sigma)
+        x = torch.randn(n_points, generator=gen) * sigma[0] + mu[0]
+        y = torch.randn(n_points, generator=gen) * sigma[1] + mu[1]
+    else:
+        x = torch.rand(n_points, generator=gen) * float(w)
+        y = torch.rand(n_points, generator=gen) * float(h)
+    return torch.stack([x.clamp(policy.pad_w, w - policy.pad_w), y.clamp(policy.pad_h, h - policy.pad_h)], dim=1)
 
 
 class SlidingWindows:
@@ -123,3 +178,147 @@ def rectangle_members(centers, half_h, half_w, grid_h, grid_w, mask=None):
     members = torch.sort(key, dim=1).values[:, :pmax]
     members = torch.where(members >= grid_h * grid_w, torch.full_like(members, -1), members)
     return members, counts
+
+
+class SparseIndex:
+    """Compact lookup -> output connectivity of a sparse LUT layer.
+
+    All lookup neurons (table rows) of one detector share one target list.  The flat weight array
+    keeps the reference's layout so that weights trained with the reference load verbatim: neurons in
+    id order, synapse p of a row at ``row_base + p + 2 * (p // G)`` (every group of G synapses is
+    preceded by a two-slot hole where the reference's arena has its group header,
+    spiky_cuda/connections_manager/connections_manager.h:39-66), rows ``stride`` slots apart.
+
+    Per detector t:   det_wbase[t]  weight index of (row 0, synapse 0)
+                      det_stride[t] slots between consecutive rows
+                      det_count[t]  synapses per row (P)
+                      det_sstart[t] prefix sum of det_count: position of the detector in the flat lists
+    Per (detector, synapse), flattened in detector order:
+                      syn_det[s], syn_target[s] (output index)
+    """
+
+    def __init__(self, det_wbase, det_stride, det_count, syn_target, group_size, n_weights, n_outputs,
+                 rows_per_detector):
+        self.det_wbase = det_wbase.to(torch.int64).contiguous()
+        self.det_stride = det_stride.to(torch.int32).contiguous()
+        self.det_count = det_count.to(torch.int32).contiguous()
+        self.syn_target = syn_target.to(torch.int32).contiguous()
+        counts64 = self.det_count.to(torch.int64)
+        self.det_sstart = (torch.cumsum(counts64, 0) - counts64).to(torch.int32).contiguous()
+        self.syn_det = torch.repeat_interleave(torch.arange(counts64.numel(), dtype=torch.int32), counts64).contiguous()
+        self.group_size = int(group_size)
+        self.n_weights = int(n_weights)
+        self.n_outputs = int(n_outputs)
+        self.rows_per_detector = int(rows_per_detector)
+        self.n_syn_per_sample = int(counts64.sum().item())
+        self.n_synapses = self.n_syn_per_sample * self.rows_per_detector
+        self.max_count = int(counts64.max().item()) if counts64.numel() else 0
+        self.max_groups_per_neuron = (self.max_count + self.group_size - 1) // self.group_size
+        assert self.syn_target.numel() == self.n_syn_per_sample
+        if self.syn_target.numel():
+            assert int(self.syn_target.min()) >= 0 and int(self.syn_target.max()) < n_outputs
+
+    _TENSORS = ("det_wbase", "det_stride", "det_count", "det_sstart", "syn_det", "syn_target")
+
+    @staticmethod
+    def row_stride(count, group_size):
+        return count + 2 * ((count + group_size - 1) // group_size)
+
+    @classmethod
+    def from_detector_targets(cls, targets, counts, rows_per_detector, group_size, n_outputs):
+        """targets int64 [Nt, Pmax] padded with -1 (synapse order), counts [Nt]."""
+        counts = counts.to(torch.int64)
+        stride = cls.row_stride(counts, group_size)
+        per_det = stride * rows_per_detector
+        wbase = torch.cumsum(per_det, 0) - per_det      # the first header hole lies before index 0
+        n_weights = int(per_det.sum().item()) - 2
+        mask = torch.arange(targets.shape[1]).view(1, -1) < counts.view(-1, 1)
+        return cls(wbase, stride, counts, targets[mask], group_size, n_weights, n_outputs, rows_per_detector)
+
+    @classmethod
+    def from_export(cls, source_ids, weight_indices, target_ids, n_detectors, rows_per_detector, group_size,
+                    n_outputs, n_weights):
+        """Rebuild the index from a reference layer's synapse export: per synapse its lookup neuron, its
+        slot in the flat weight array and its output index.  Checks the regularity the kernels rely on."""
+        src = torch.as_tensor(source_ids, dtype=torch.int64)
+        slot = torch.as_tensor(weight_indices, dtype=torch.int64)
+        tgt = torch.as_tensor(target_ids, dtype=torch.int64)
+        order = torch.argsort(src * (int(slot.max().item()) + 1) + slot)
+        src, slot, tgt = src[order], slot[order], tgt[order]
+        n_neurons = n_detectors * rows_per_detector
+        counts_n = torch.bincount(src, minlength=n_neurons)
+        counts_n = counts_n.view(n_detectors, rows_per_detector)
+        if not bool((counts_n == counts_n[:, :1]).all()):
+            raise ValueError("lookup neurons of one detector have different synapse counts; unsupported connectivity")
+        counts = counts_n[:, 0]
+        starts = torch.cumsum(counts_n.reshape(-1), 0) - counts_n.reshape(-1)
+        first_slot = torch.full((n_neurons,), -1, dtype=torch.int64)
+        has = counts_n.reshape(-1) > 0
+        first_slot[has] = slot[starts[has]]
+        first_slot = first_slot.view(n_detectors, rows_per_detector)
+        stride = cls.row_stride(counts, group_size)
+        wbase = first_slot[:, 0]
+        expect = wbase.view(-1, 1) + torch.arange(rows_per_detector).view(1, -1) * stride.view(-1, 1)
+        if not bool(((first_slot == expect) | (counts.view(-1, 1) == 0)).all()):
+            raise ValueError("weight slots of a detector's rows are not evenly spaced; unsupported layout")
+        p = torch.arange(src.numel()) - starts[src]
+        if not bool((slot == first_slot.reshape(-1)[src] + p + 2 * (p // group_size)).all()):
+            raise ValueError("synapse slots do not follow the grouped layout")
+        # the target list of row 0 stands for the detector; every other row must repeat it
+        tmax = int(counts.max().item())
+        tl = torch.full((n_neurons, max(tmax, 1)), -1, dtype=torch.int64)
+        tl[src, p] = tgt
+        tl = tl.view(n_detectors, rows_per_detector, -1)
+        if not bool((tl == tl[:, :1]).all()):
+            raise ValueError("lookup neurons of one detector have different target lists; unsupported connectivity")
+        det_targets = tl[:, 0]
+        mask = torch.arange(det_targets.shape[1]).view(1, -1) < counts.view(-1, 1)
+        return cls(wbase, stride, counts, det_targets[mask], group_size, n_weights, n_outputs, rows_per_detector)
+
+    def initial_weights(self, synapse_meta, seed=None):
+        """fp32 [n_weights]: noise * U[0,1) + initial weight, clipped to the meta's range; holes are zero."""
+        gen = None
+        if seed is not None:
+            gen = torch.Generator(device="cpu")
+            gen.manual_seed(int(seed))
+        w = torch.rand(self.n_weights, generator=gen, dtype=torch.float32)
+        w.mul_(synapse_meta.initial_noise_level).add_(synapse_meta.initial_weight)
+        w.clip_(synapse_meta.min_weight, synapse_meta.max_weight)
+        w[~self.slot_mask()] = 0.0
+        return w
+
+    def slot_mask(self):
+        """bool [n_weights]: True where a slot holds a synapse weight (False in header holes)."""
+        dev = self.det_wbase.device
+        mask = torch.zeros(self.n_weights, dtype=torch.bool, device=dev)
+        counts = self.det_count.to(torch.int64)
+        p = torch.arange(self.n_syn_per_sample, device=dev) - self.det_sstart.to(torch.int64)[self.syn_det.to(torch.int64)]
+        base = self.det_wbase[self.syn_det.to(torch.int64)] + p + 2 * (p // self.group_size)
+        stride = self.det_stride.to(torch.int64)[self.syn_det.to(torch.int64)]
+        for row in range(self.rows_per_detector):
+            mask[base + row * stride] = True
+        del counts
+        return mask
+
+    def to_device(self, device_index):
+        dev = torch.device("cpu") if device_index < 0 else torch.device("cuda", device_index)
+        for name in self._TENSORS:
+            setattr(self, name, getattr(self, name).to(dev))
+        return self
+
+    def c_struct(self):
+        """ctypes view for the C ABI (valid while this object and its tensors are alive)."""
+        from ._native import SparseIndexC
+
+        return SparseIndexC(
+            det_wbase=self.det_wbase.data_ptr(), det_stride=self.det_stride.data_ptr(),
+            det_count=self.det_count.data_ptr(), det_sstart=self.det_sstart.data_ptr(),
+            syn_det=self.syn_det.data_ptr(), syn_target=self.syn_target.data_ptr(),
+            n_syn_per_sample=self.n_syn_per_sample, n_weights=self.n_weights, group_size=self.group_size,
+            max_count=self.max_count)
+
+    def nbytes(self):
+        return sum(getattr(self, n).numel() * getattr(self, n).element_size() for n in self._TENSORS)
+
+    def numpy(self):
+        return {n: getattr(self, n).cpu().numpy() for n in self._TENSORS}

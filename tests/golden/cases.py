@@ -51,3 +51,37 @@ NONSEQ_FC_CASES = {
 }
 
 
+
+
+def projection_inputs(cfg, n_weights):
+    """Batch, table weights and upstream gradient of a sparse projection-layer case."""
+    s = cfg["seed"]
+    B = cfg["B"]
+    I = cfg["in_shape"][0] * cfg["in_shape"][1]
+    O = cfg["out_shape"][0] * cfg["out_shape"][1]
+    x = synth.sparse_images(s + 21, (B, I)) if cfg.get("sparse_input") else synth.uniform(s + 21, (B, I))
+    W = synth.normal(s + 23, (n_weights,), 0.0, 0.05)
+    dY = synth.normal(s + 24, (B, O))
+    if cfg.get("zero_dy"):
+        dY[:, ::4] = 0.0
+    return x, W, dY
+
+
+PROJECTION_CASES = {
+    "proj_grid_f32": dict(seed=200, B=6, in_shape=(12, 12), out_shape=(10, 10), Nc=3, groups=9, per_group=4,
+                          receptive=(5, 5), projection=(4, 4), grid=(3, 3, 3, 3, 2, 2)),
+    "proj_grid_i32": dict(seed=201, B=6, in_shape=(12, 12), out_shape=(10, 10), Nc=3, groups=9, per_group=4,
+                          receptive=(5, 5), projection=(4, 4), grid=(3, 3, 3, 3, 2, 2), int_mode=True,
+                          int_rescaler=2.0),
+    "proj_random_f32": dict(seed=202, B=5, in_shape=(16, 16), out_shape=(12, 12), Nc=4, groups=7, per_group=3,
+                            receptive=(5, 5), projection=(4, 4), sparse_input=True, zero_dy=True),
+    "proj_random_i32": dict(seed=203, B=5, in_shape=(16, 16), out_shape=(12, 12), Nc=4, groups=7, per_group=3,
+                            receptive=(5, 5), projection=(4, 4), sparse_input=True, int_mode=True, int_rescaler=1.0),
+    # several synapse groups per lookup neuron (group size 8 < synapses per row)
+    "proj_multigroup_f32": dict(seed=204, B=4, in_shape=(14, 14), out_shape=(14, 14), Nc=3, groups=5, per_group=2,
+                                receptive=(7, 7), projection=(4, 4), G=8),
+    "proj_multigroup_i32": dict(seed=205, B=4, in_shape=(14, 14), out_shape=(14, 14), Nc=3, groups=5, per_group=2,
+                                receptive=(7, 7), projection=(4, 4), G=8, int_mode=True, int_rescaler=0.25),
+    "proj_internal": dict(seed=206, B=7, in_shape=(12, 12), out_shape=(8, 8), Nc=3, groups=6, per_group=3,
+                          receptive=(5, 5), projection=(3, 3), policy="internal", ext_lr=0.5, lr_meta=0.25),
+}

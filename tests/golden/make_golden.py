@@ -20,11 +20,12 @@ import torch
 
 sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 import synth  # noqa: E402,F401
-from cases import NONSEQ_FC_CASES, nonseq_fc_inputs  # noqa: E402
+from cases import NONSEQ_FC_CASES, PROJECTION_CASES, nonseq_fc_inputs, projection_inputs  # noqa: E402
 
 from spiky.lut.LUTLayer import (  # noqa: E402  (the reference)
-    LUTLayer, SynapseMeta, GradientPolicy, GradientType, LUTSharedContext,
+    LUTLayer, ProjectionLUTLayer, SynapseMeta, GradientPolicy, GradientType, LUTSharedContext,
 )
+from spiky.util.synapse_growth import PointSamplingPolicy, PointSamplingType  # noqa: E402
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 
@@ -82,11 +83,80 @@ def run_nonseq_fc(name, cfg):
     save(name, dict(cfg, kind="nonseq_fc"), **out, **extra)
 
 
+# ----------------------------------------------------------------------------- sparse projection
+def export_structure(layer):
+    """Per synapse of a reference-built sparse layer: lookup neuron, slot in the flat weight array and
+    output index.  The slot is read back by exporting with the weights set to 0, 1, 2, ..."""
+    n = layer.n_synapses()
+    saved = layer._weights.detach().clone()
+    with torch.no_grad():
+        layer._weights.copy_(torch.arange(layer._weights.numel(), dtype=torch.float32))
+    src = torch.zeros(n, dtype=torch.int32)
+    tgt = torch.zeros(n, dtype=torch.int32)
+    slot = torch.zeros(n, dtype=torch.float32)
+    layer._export_synapses(layer.get_lookup_neuron_ids(), src, slot, tgt)
+    with torch.no_grad():
+        layer._weights.copy_(saved)
+    assert layer._weights.numel() < (1 << 24), "slots must be exactly representable in fp32"
+    return src.numpy().astype(np.int64), slot.numpy().astype(np.int64), tgt.numpy().astype(np.int64) - layer.n_lookup_neurons()
+
+
+def run_projection(name, cfg):
+    int_mode = cfg.get("int_mode", False)
+    policy = {"dense": GradientType.Dense, "internal": GradientType.Internal}[cfg.get("policy", "dense")]
+    if "grid" in cfg:
+        gh, gw, sh, sw, ph, pw = cfg["grid"]
+        sampling = PointSamplingPolicy(PointSamplingType.Grid, grid_h=gh, grid_w=gw, stride_h=sh, stride_w=sw,
+                                       pad_h=ph, pad_w=pw)
+    else:
+        sampling = PointSamplingPolicy(PointSamplingType.RandomUniform)
+    layer = ProjectionLUTLayer(
+        input_shape=cfg["in_shape"], output_shape=cfg["out_shape"], n_anchors_per_detector=cfg["Nc"],
+        n_detector_groups=cfg["groups"], n_detectors_in_group=cfg["per_group"], receptive_shape=cfg["receptive"],
+        projection_shape=cfg["projection"],
+        synapse_meta=SynapseMeta(learning_rate=cfg.get("lr_meta", 1.0), min_weight=-1.0, max_weight=1.0),
+        detectors_sampling_policy=sampling, weights_gradient_policy=GradientPolicy(policy),
+        summation_dtype=torch.int32 if int_mode else torch.float32, _int_rescaler=cfg.get("int_rescaler", 0.001),
+        _forward_group_size=cfg.get("G", 32), random_seed=cfg["seed"],
+    )
+    src, slot, tgt = export_structure(layer)
+    n_weights = layer._weights.numel()
+    x, W, dY = projection_inputs(cfg, n_weights)
+    with torch.no_grad():
+        layer._weights.copy_(torch.from_numpy(W))
+    B = cfg["B"]
+    I = cfg["in_shape"][0] * cfg["in_shape"][1]
+    O = cfg["out_shape"][0] * cfg["out_shape"][1]
+    Nt = layer.n_detectors()
+    xt = torch.from_numpy(x).view((B, 1) + tuple(cfg["in_shape"]))
+    out = {}
+    layer.eval()
+    out["y_eval"] = t2n(layer.forward_step(xt)).reshape(B, O)
+    layer.train()
+    y, idx, md, mk = layer.forward_step(xt)
+    out.update(y=t2n(y).reshape(B, O), idx=t2n(idx).reshape(B, Nt), min_delta=t2n(md).reshape(B, Nt),
+               min_k=t2n(mk).reshape(B, Nt))
+    if policy == GradientType.Internal:
+        layer.set_external_learning_rate_hook(lambda w: cfg["ext_lr"])
+    dx, dw = layer.backward_step(xt, torch.from_numpy(dY).view((B, 1) + tuple(cfg["out_shape"])), idx, md, mk)
+    out["dX"] = t2n(dx).reshape(B, I)
+    if policy == GradientType.Internal:
+        out["W_after"] = t2n(layer._weights)
+    else:
+        out["dW"] = t2n(dw)
+    save(name, dict(cfg, kind="projection", Nt=Nt, n_weights=n_weights, n_lookup_neurons=layer.n_lookup_neurons()),
+         anchors=t2n(layer._detector_anchors), syn_source=src.astype(np.int32), syn_slot=slot.astype(np.int32),
+         syn_target=tgt.astype(np.int32), **out)
+
+
 def main():
     prefixes = sys.argv[1:]
     for name, cfg in NONSEQ_FC_CASES.items():
         if not prefixes or any(name.startswith(p) for p in prefixes):
             run_nonseq_fc(name, cfg)
+    for name, cfg in PROJECTION_CASES.items():
+        if not prefixes or any(name.startswith(p) for p in prefixes):
+            run_projection(name, cfg)
 
 
 if __name__ == "__main__":

@@ -51,3 +51,56 @@ def test_oracle_threads_do_not_change_results():
     finally:
         orc.set_threads(1)
     assert np.array_equal(y, ref["y"]) and np.array_equal(dX, ref["dX"]) and np.array_equal(dW, ref["dW"])
+
+
+def sparse_index_from_golden(cfg, ref):
+    from spiky_b200.structure import SparseIndex
+
+    rows = cfg["n_lookup_neurons"] // cfg["Nt"]
+    O = cfg["out_shape"][0] * cfg["out_shape"][1]
+    return SparseIndex.from_export(ref["syn_source"], ref["syn_slot"], ref["syn_target"], cfg["Nt"], rows,
+                                   cfg.get("G", 32), O, cfg["n_weights"])
+
+
+@pytest.mark.parametrize("name", golden_util.names("proj_"))
+def test_sparse_oracle_matches_reference(name):
+    from cases import projection_inputs
+
+    cfg, ref = golden_util.load(name)
+    index = sparse_index_from_golden(cfg, ref)
+    sp = dict(index.numpy(), group_size=index.group_size)
+    x, W, dY = projection_inputs(cfg, cfg["n_weights"])
+    I = cfg["in_shape"][0] * cfg["in_shape"][1]
+    O = cfg["out_shape"][0] * cfg["out_shape"][1]
+    kw = dict(int_mode=cfg.get("int_mode", False), int_rescaler=cfg.get("int_rescaler", 0.001))
+    anchors = ref["anchors"]
+    y_eval, _, _, _ = orc.nonseq_sparse_forward(W, x, anchors, sp, cfg["Nc"], O, train=False, **kw)
+    y, idx, md, mk = orc.nonseq_sparse_forward(W, x, anchors, sp, cfg["Nc"], O, train=True, **kw)
+    assert np.array_equal(idx, ref["idx"]) and np.array_equal(mk, ref["min_k"])
+    assert np.array_equal(md.view(np.int32), ref["min_delta"].view(np.int32))
+    assert np.array_equal(y, ref["y"]) and np.array_equal(y_eval, ref["y_eval"])
+    internal = cfg.get("policy") == "internal"
+    Wb = W.copy()
+    dX, dW = orc.nonseq_sparse_backward(Wb, dY, anchors, idx, md, mk, sp, I, cfg["Nc"],
+                                        lr_meta=cfg.get("lr_meta", 1.0),
+                                        external_lr=cfg["ext_lr"] if internal else -1.0, **kw)
+    assert np.array_equal(dX, ref["dX"])
+    if internal:
+        assert np.array_equal(Wb, ref["W_after"])
+    else:
+        assert np.array_equal(dW, ref["dW"])
+
+
+def test_own_sparse_construction_is_self_consistent():
+    """Connectivity built without the reference: layout invariants of the flat weight array."""
+    import torch
+    from spiky_b200.structure import SparseIndex
+
+    targets = torch.tensor([[3, 4, 9, -1], [0, 1, -1, -1], [5, 6, 7, 8]])
+    counts = torch.tensor([3, 2, 4])
+    sp = SparseIndex.from_detector_targets(targets, counts, rows_per_detector=4, group_size=2, n_outputs=10)
+    # strides: P + 2*ceil(P/G) = 3+4, 2+2, 4+4
+    assert sp.det_stride.tolist() == [7, 4, 8] and sp.det_wbase.tolist() == [0, 28, 44]
+    assert sp.n_weights == 28 + 16 + 32 - 2 and sp.n_synapses == (3 + 2 + 4) * 4
+    assert sp.syn_target.tolist() == [3, 4, 9, 0, 1, 5, 6, 7, 8] and sp.max_groups_per_neuron == 2
+    assert int(sp.slot_mask().sum()) == sp.n_synapses
