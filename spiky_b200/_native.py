@@ -44,6 +44,8 @@ class SparseIndexC(ctypes.Structure):
         ("det_sstart", ctypes.c_void_p),
         ("syn_det", ctypes.c_void_p),
         ("syn_target", ctypes.c_void_p),
+        ("chunk_info", ctypes.c_void_p),
+        ("n_chunks", ctypes.c_int64),
         ("n_syn_per_sample", ctypes.c_int64),
         ("n_weights", ctypes.c_int64),
         ("group_size", ctypes.c_int32),

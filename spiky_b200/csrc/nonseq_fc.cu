@@ -65,7 +65,11 @@ __global__ void __launch_bounds__(256) check_detectors_kernel(const float *__res
     __syncthreads();
     if (nrows <= 0) return;
 
-    for (int t = lt; t < n_detectors; t += threads_per_group) {
+    // blockIdx.y selects a slice of the detectors so that small batches still fill the machine
+    const int det_per_slice = (n_detectors + gridDim.y - 1) / gridDim.y;
+    const int det_begin = blockIdx.y * det_per_slice;
+    const int det_end = min(n_detectors, det_begin + det_per_slice);
+    for (int t = det_begin + lt; t < det_end; t += threads_per_group) {
         int32_t li[R];
         float md[R];
         int32_t mk[R];
@@ -138,7 +142,7 @@ __global__ void check_detectors_global_kernel(const float *__restrict__ x, int64
 template <int R>
 static int launch_check_detectors_r(const float *x, int64_t rows, int n_inputs, const int32_t *anchors,
                                     int n_detectors, int n_anchors, float cmp_eps, int32_t *idx, float *min_delta,
-                                    int32_t *min_k, int tpg, int groups, cudaStream_t stream) {
+                                    int32_t *min_k, int tpg, int groups, int det_slices, cudaStream_t stream) {
     const size_t smem = (size_t)groups * R * n_inputs * sizeof(float);
     const int64_t rows_per_block = (int64_t)groups * R;
     const int64_t blocks = (rows + rows_per_block - 1) / rows_per_block;
@@ -147,7 +151,7 @@ static int launch_check_detectors_r(const float *x, int64_t rows, int n_inputs, 
     auto kern = train ? check_detectors_kernel<R, true> : check_detectors_kernel<R, false>;
     if (smem > 48 * 1024) LUTB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     KernelScope scope(K_CHECK_DETECTORS, stream);
-    kern<<<(unsigned)blocks, tpg * groups, smem, stream>>>(x, rows, n_inputs, reinterpret_cast<const int2 *>(anchors),
+    kern<<<dim3((unsigned)blocks, (unsigned)det_slices), tpg * groups, smem, stream>>>(x, rows, n_inputs, reinterpret_cast<const int2 *>(anchors),
                                                           n_detectors, n_anchors, cmp_eps, tpg, idx, min_delta, min_k);
     LUTB_LAUNCH_CHECK();
     return LUTB_OK;
@@ -159,11 +163,11 @@ int launch_check_detectors(const float *x, int64_t rows, int n_inputs, const int
     const int sm = device_info().sm_count;
     // threads per row group: one per detector, rounded to warps, at most 256
     int tpg = ((min(n_detectors, 256) + 31) / 32) * 32;
-    // rows per group: as many as keep at least ~2 blocks per SM busy and fit in shared memory
+    // rows per group: up to 8 (each anchor pair is fetched once per 8 rows), fewer when rows are long
     const size_t row_bytes = (size_t)n_inputs * sizeof(float);
     const size_t budget = 100 * 1024;  // two resident blocks per SM
     int R = 8;
-    while (R > 1 && ((size_t)R * row_bytes > budget || rows < (int64_t)R * 2 * sm)) R >>= 1;
+    while (R > 1 && ((size_t)R * row_bytes > budget || rows < R)) R >>= 1;
     if ((size_t)R * row_bytes > (size_t)kMaxSmemPerBlock - 1024) {
         const bool train = min_delta != nullptr;
         const int64_t total = rows * n_detectors;
@@ -182,11 +186,15 @@ int launch_check_detectors(const float *x, int64_t rows, int n_inputs, const int
     }
     int groups = 256 / tpg;
     while (groups > 1 && ((size_t)groups * R * row_bytes > budget || rows < (int64_t)groups * R * 2 * sm)) groups >>= 1;
+    // small batches: split the detectors over blockIdx.y until there are ~2 blocks per SM
+    const int64_t row_tiles = (rows + (int64_t)groups * R - 1) / ((int64_t)groups * R);
+    const int max_slices = (n_detectors + tpg - 1) / tpg;
+    const int det_slices = (int)max((int64_t)1, min((int64_t)max_slices, ((int64_t)2 * sm + row_tiles - 1) / row_tiles));
     switch (R) {
-        case 8: return launch_check_detectors_r<8>(x, rows, n_inputs, anchors, n_detectors, n_anchors, cmp_eps, idx, min_delta, min_k, tpg, groups, stream);
-        case 4: return launch_check_detectors_r<4>(x, rows, n_inputs, anchors, n_detectors, n_anchors, cmp_eps, idx, min_delta, min_k, tpg, groups, stream);
-        case 2: return launch_check_detectors_r<2>(x, rows, n_inputs, anchors, n_detectors, n_anchors, cmp_eps, idx, min_delta, min_k, tpg, groups, stream);
-        default: return launch_check_detectors_r<1>(x, rows, n_inputs, anchors, n_detectors, n_anchors, cmp_eps, idx, min_delta, min_k, tpg, groups, stream);
+        case 8: return launch_check_detectors_r<8>(x, rows, n_inputs, anchors, n_detectors, n_anchors, cmp_eps, idx, min_delta, min_k, tpg, groups, det_slices, stream);
+        case 4: return launch_check_detectors_r<4>(x, rows, n_inputs, anchors, n_detectors, n_anchors, cmp_eps, idx, min_delta, min_k, tpg, groups, det_slices, stream);
+        case 2: return launch_check_detectors_r<2>(x, rows, n_inputs, anchors, n_detectors, n_anchors, cmp_eps, idx, min_delta, min_k, tpg, groups, det_slices, stream);
+        default: return launch_check_detectors_r<1>(x, rows, n_inputs, anchors, n_detectors, n_anchors, cmp_eps, idx, min_delta, min_k, tpg, groups, det_slices, stream);
     }
 }
 

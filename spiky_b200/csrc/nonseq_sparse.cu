@@ -12,9 +12,9 @@ struct SparseView {
     const int32_t *det_stride;
     const int32_t *det_count;
     const int32_t *det_sstart;
-    const int32_t *syn_det;
     const int32_t *syn_target;
-    int64_t n_syn;
+    const int4 *chunks;   // (first detector, detector count <= 32, target list offset, synapses per row)
+    int64_t n_chunks;
     int32_t group;
     int32_t group_shift;  // log2(group) when group is a power of two, else -1
 };
@@ -24,115 +24,198 @@ __device__ __forceinline__ int hole_offset(int p, const SparseView &sp) {
     return 2 * (sp.group_shift >= 0 ? (p >> sp.group_shift) : (p / sp.group));
 }
 
+// All three training kernels give one warp to a (sample, chunk) pair.  A chunk is a run of up to 32
+// consecutive detectors that share one target list (the detectors of one group).  Lane L first loads
+// the table index of detector L of the chunk (one coalesced read) and turns it into the offset of the
+// selected row relative to the chunk's first table; the offsets are then broadcast with shuffles while
+// the lanes cover the synapses of a row, so that every row read or update is one contiguous segment.
+// When rows are short the warp splits into NG = 32 / LG lane groups that take detectors round-robin.
+struct ChunkLane {
+    int det0, ndet, toff, P;
+    int64_t wbase0;
+    int32_t row_off;   // offset of this lane's detector's selected row from wbase0 (0 when lane >= ndet)
+};
+
+__device__ __forceinline__ ChunkLane load_chunk(const SparseView &sp, const int32_t *__restrict__ idx_b, int64_t c,
+                                                int lane, int32_t *li_out) {
+    const int4 ci = __ldg(sp.chunks + c);
+    ChunkLane ch;
+    ch.det0 = ci.x; ch.ndet = ci.y; ch.toff = ci.z; ch.P = ci.w;
+    ch.wbase0 = __ldg(sp.det_wbase + ch.det0);
+    ch.row_off = 0;
+    int32_t li = 0;
+    if (lane < ch.ndet) {
+        const int t = ch.det0 + lane;
+        li = __ldg(idx_b + t);
+        ch.row_off = (int32_t)(__ldg(sp.det_wbase + t) - ch.wbase0) + li * __ldg(sp.det_stride + t);
+    }
+    if (li_out) *li_out = li;
+    return ch;
+}
+
 // --------------------------------------------------------------------------------------------
-// Forward: y[b, target(t, p)] += W[slot(t, idx[b, t], p)] over all (detector, synapse) pairs
+// Forward: y[b, target(p)] += sum over the chunk's detectors of W[row(t, idx[b, t]) + p]
 // (reference: fill_outputs_non_seq_sparse_logic + fire_single_synapse_group, proto:1160-1212, 215-313).
-// A block owns one sample and a slice of the flattened pair list; the sample's index row and the
-// output accumulators live in shared memory; consecutive threads read consecutive weights of a row.
+// The chunk's detectors are summed in registers, so the shared output cells see one reduction per
+// (sample, chunk, target) instead of one per synapse.
 // --------------------------------------------------------------------------------------------
 template <bool INT_MODE>
 __global__ void __launch_bounds__(256) sparse_forward_kernel(SparseView sp, const float *__restrict__ W,
                                                             const int32_t *__restrict__ idx, float *__restrict__ y,
-                                                            int n_outputs, int n_detectors, int slices,
+                                                            int64_t batch, int n_outputs, int n_detectors,
                                                             double fixed_scale) {
-    extern __shared__ __align__(16) unsigned char smem_raw[];
-    float *ys = reinterpret_cast<float *>(smem_raw);
-    int32_t *yi = reinterpret_cast<int32_t *>(smem_raw);
-    int32_t *idx_s = reinterpret_cast<int32_t *>(smem_raw) + n_outputs;
-    const int64_t b = blockIdx.x;
-    const int slice = blockIdx.y;
-    const int64_t per = (sp.n_syn + slices - 1) / slices;
-    const int64_t s0 = slice * per, s1 = min(sp.n_syn, s0 + per);
-    for (int o = threadIdx.x; o < n_outputs; o += blockDim.x) yi[o] = 0;
-    const int32_t *idx_b = idx + b * n_detectors;
-    for (int t = threadIdx.x; t < n_detectors; t += blockDim.x) idx_s[t] = __ldg(idx_b + t);
-    __syncthreads();
-    for (int64_t s = s0 + threadIdx.x; s < s1; s += blockDim.x) {
-        const int t = __ldg(sp.syn_det + s);
-        const int target = __ldg(sp.syn_target + s);
-        const int p = (int)(s - __ldg(sp.det_sstart + t));
-        const int64_t slot = __ldg(sp.det_wbase + t) + (int64_t)idx_s[t] * __ldg(sp.det_stride + t) + p + hole_offset(p, sp);
-        const float w = __ldg(W + slot);
-        if (INT_MODE) atomicAdd(yi + target, to_fixed((double)w, fixed_scale));
-        else atomicAdd(ys + target, w);
-    }
-    __syncthreads();
-    if (INT_MODE) {
-        int32_t *yb = reinterpret_cast<int32_t *>(y) + b * n_outputs;
-        for (int o = threadIdx.x; o < n_outputs; o += blockDim.x) {
-            const int32_t v = yi[o];
-            if (v != 0) {
-                if (slices == 1) yb[o] += v;
-                else atomicAdd(yb + o, v);
+    const int lane = threadIdx.x & 31;
+    const int64_t work = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (work >= batch * sp.n_chunks) return;
+    const int64_t b = work / sp.n_chunks;
+    const int64_t c = work - b * sp.n_chunks;
+    const ChunkLane ch = load_chunk(sp, idx + b * n_detectors, c, lane, nullptr);
+    int LG = 32;
+    while (LG > 4 && (LG >> 1) >= ch.P) LG >>= 1;
+    const int NG = 32 / LG;
+    const int g = lane / LG, j = lane - g * LG;
+    const float *Wb = W + ch.wbase0;
+    const int32_t *tg = sp.syn_target + ch.toff;
+    for (int p0 = 0; p0 < ch.P; p0 += LG) {
+        const int p = p0 + j;
+        const bool valid = p < ch.P;
+        const int q = p + hole_offset(p, sp);
+        float acc = 0.f;
+        int32_t iacc = 0;
+#pragma unroll 4
+        for (int d0 = 0; d0 < ch.ndet; d0 += NG) {
+            const int d = d0 + g;
+            const int32_t off = __shfl_sync(0xffffffffu, ch.row_off, d & 31);
+            if (valid && d < ch.ndet) {
+                const float w = __ldg(Wb + (int64_t)off + q);
+                if (INT_MODE) iacc += to_fixed((double)w, fixed_scale);
+                else acc += w;
             }
         }
-    } else {
-        float *yb = y + b * n_outputs;
-        for (int o = threadIdx.x; o < n_outputs; o += blockDim.x) {
-            const float v = ys[o];
-            if (slices == 1) yb[o] += v;
-            else if (v != 0.f) atomicAdd(yb + o, v);
+        for (int m = LG; m < 32; m <<= 1) {
+            if (INT_MODE) iacc += __shfl_xor_sync(0xffffffffu, iacc, m);
+            else acc += __shfl_xor_sync(0xffffffffu, acc, m);
+        }
+        if (valid && g == 0) {
+            const int target = __ldg(tg + p);
+            if (INT_MODE) atomicAdd(reinterpret_cast<int32_t *>(y) + b * n_outputs + target, iacc);
+            else atomicAdd(y + b * n_outputs + target, acc);
         }
     }
 }
 
 // --------------------------------------------------------------------------------------------
-// Input gradient (reference: propagate_through_detectors_non_seq_sparse_logic, proto:1303-1419).
-// fp32 mode: a lane group of LG lanes owns one (sample, detector); lanes cover the synapses, the
-// dot product dY[target] * (W[row] - W[alt]) is accumulated in double and reduced with shuffles.
+// Input gradient (reference: propagate_through_detectors_non_seq_sparse_logic, proto:1303-1419):
+// per (sample, detector) g = sum_p dY[target(p)] * (W[row + p] - W[alt + p]), du = up(min_delta) * g.
+// A lane group of LG lanes covers the synapses; every lane keeps one partial per detector it sees
+// (LG of them), and a butterfly of LG - 1 shuffles transposes and reduces them so that each lane
+// ends with the full sum of exactly one detector and performs that detector's two updates itself.
+// Rows have at most 32 synapses here (longer rows use the generic kernel below); partial products are
+// fp32 (<= 32 terms), the scaling by up() is done in double.
 // --------------------------------------------------------------------------------------------
+template <int LG>
 __global__ void __launch_bounds__(256) sparse_input_grad_kernel(SparseView sp, const float *__restrict__ W,
                                                                const float *__restrict__ dY,
                                                                const int2 *__restrict__ anchors,
                                                                const int32_t *__restrict__ idx,
                                                                const float *__restrict__ min_delta,
                                                                const int32_t *__restrict__ min_k,
-                                                               float *__restrict__ dX, int n_inputs, int n_outputs,
-                                                               int n_detectors, int n_anchors, int lanes_per_det,
-                                                               int slices) {
-    extern __shared__ __align__(16) unsigned char smem_raw[];
-    float *dys = reinterpret_cast<float *>(smem_raw);
-    const int64_t b = blockIdx.x;
-    const float *dy = dY + b * n_outputs;
-    for (int o = threadIdx.x; o < n_outputs; o += blockDim.x) dys[o] = __ldg(dy + o);
-    __syncthreads();
-    const int LG = lanes_per_det;
-    const int groups_per_block = blockDim.x / LG;
-    const int g = threadIdx.x / LG;
-    const int j = threadIdx.x - g * LG;
-    const unsigned lane = threadIdx.x & 31;
-    const unsigned group_mask = (LG == 32) ? 0xffffffffu : (((1u << LG) - 1u) << (lane & ~(unsigned)(LG - 1)));
-    const int per = (n_detectors + slices - 1) / slices;
-    const int t_begin = blockIdx.y * per, t_end = min(n_detectors, t_begin + per);
-    float *dx = dX + b * n_inputs;
-    const int64_t base = b * n_detectors;
-    for (int t0 = t_begin; t0 < t_end; t0 += groups_per_block) {
-        const int t = t0 + g;
-        const bool valid = t < t_end;
-        double acc = 0.0;
-        int32_t k = 0;
-        if (valid) {
-            const int32_t li = __ldg(idx + base + t);
-            k = __ldg(min_k + base + t);
-            const int P = __ldg(sp.det_count + t);
-            const int64_t wbase = __ldg(sp.det_wbase + t);
-            const int stride = __ldg(sp.det_stride + t);
-            const int32_t *tg = sp.syn_target + __ldg(sp.det_sstart + t);
-            const float *row = W + wbase + (int64_t)li * stride;
-            const float *alt = W + wbase + (int64_t)(li ^ (1 << k)) * stride;
-            for (int p = j; p < P; p += LG) {
-                const int q = p + hole_offset(p, sp);
-                acc += (double)dys[__ldg(tg + p)] * ((double)__ldg(row + q) - (double)__ldg(alt + q));
-            }
+                                                               float *__restrict__ dX, int64_t batch, int n_inputs,
+                                                               int n_outputs, int n_detectors, int n_anchors) {
+    constexpr int NG = 32 / LG;
+    const int lane = threadIdx.x & 31;
+    const int64_t work = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (work >= batch * sp.n_chunks) return;
+    const int64_t b = work / sp.n_chunks;
+    const int64_t c = work - b * sp.n_chunks;
+    int32_t li;
+    const ChunkLane ch = load_chunk(sp, idx + b * n_detectors, c, lane, &li);
+    // this lane's detector: alternative row (minimum-margin bit flipped), margin, flipped pair
+    int32_t alt_off = 0, my_k = 0;
+    float my_m = 0.f;
+    if (lane < ch.ndet) {
+        const int t = ch.det0 + lane;
+        my_k = __ldg(min_k + b * n_detectors + t);
+        my_m = __ldg(min_delta + b * n_detectors + t);
+        alt_off = ch.row_off + ((li ^ (1 << my_k)) - li) * __ldg(sp.det_stride + t);
+    }
+    const int g = lane / LG, j = lane - g * LG;
+    const bool valid = j < ch.P;
+    const int q = j + hole_offset(j, sp);
+    const float *Wb = W + ch.wbase0 + q;
+    const float gp = valid ? __ldg(dY + b * n_outputs + __ldg(sp.syn_target + ch.toff + j)) : 0.f;
+    float v[LG];
+#pragma unroll
+    for (int i = 0; i < LG; i++) {
+        const int d = i * NG + g;
+        const int32_t ro = __shfl_sync(0xffffffffu, ch.row_off, d);
+        const int32_t ao = __shfl_sync(0xffffffffu, alt_off, d);
+        // detectors beyond the chunk have ro == ao == 0: the difference below is exactly zero
+        v[i] = valid ? gp * (__ldg(Wb + ro) - __ldg(Wb + ao)) : 0.f;
+    }
+    // transpose-reduce: after the stage with offset o, a lane keeps the half of the values whose
+    // index bit matches its own lane bit, summed with the partner lane's copy
+#pragma unroll
+    for (int o = LG / 2; o >= 1; o >>= 1) {
+        const bool upper = (j & o) != 0;
+#pragma unroll
+        for (int i = 0; i < o; i++) {
+            const float send = upper ? v[i] : v[i + o];
+            const float keep = upper ? v[i + o] : v[i];
+            v[i] = keep + __shfl_xor_sync(0xffffffffu, send, o);
         }
-        for (int off = 1; off < LG; off <<= 1) acc += __shfl_xor_sync(group_mask, acc, off);
-        if (valid && j == 0) {
-            const double du = surrogate_up(__ldg(min_delta + base + t)) * acc;
-            if (fabs(du) > kEps) {
-                const int2 a = __ldg(anchors + (size_t)t * n_anchors + k);
-                atomicAdd(dx + a.x, (float)du);
-                atomicAdd(dx + a.y, -(float)du);
-            }
+    }
+    // lane (g, j) now holds detector d = j * NG + g of the chunk
+    const int d = j * NG + g;
+    const int32_t k = __shfl_sync(0xffffffffu, my_k, d);
+    const float m = __shfl_sync(0xffffffffu, my_m, d);
+    if (d < ch.ndet) {
+        const double du = surrogate_up(m) * (double)v[0];
+        if (fabs(du) > kEps) {
+            const int2 a = __ldg(anchors + (size_t)(ch.det0 + d) * n_anchors + k);
+            float *dx = dX + b * n_inputs;
+            atomicAdd(dx + a.x, (float)du);
+            atomicAdd(dx + a.y, -(float)du);
+        }
+    }
+}
+
+// Generic fp32 input gradient for rows longer than 32 synapses: one warp per (sample, detector).
+__global__ void __launch_bounds__(256) sparse_input_grad_long_kernel(SparseView sp, const float *__restrict__ W,
+                                                                    const float *__restrict__ dY,
+                                                                    const int2 *__restrict__ anchors,
+                                                                    const int32_t *__restrict__ idx,
+                                                                    const float *__restrict__ min_delta,
+                                                                    const int32_t *__restrict__ min_k,
+                                                                    float *__restrict__ dX, int64_t batch,
+                                                                    int n_inputs, int n_outputs, int n_detectors,
+                                                                    int n_anchors) {
+    const int lane = threadIdx.x & 31;
+    const int64_t work = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (work >= batch * n_detectors) return;
+    const int64_t b = work / n_detectors;
+    const int t = (int)(work - b * n_detectors);
+    const int32_t li = __ldg(idx + work);
+    const int32_t k = __ldg(min_k + work);
+    const int P = __ldg(sp.det_count + t);
+    const int64_t wbase = __ldg(sp.det_wbase + t);
+    const int stride = __ldg(sp.det_stride + t);
+    const int32_t *tg = sp.syn_target + __ldg(sp.det_sstart + t);
+    const float *row = W + wbase + (int64_t)li * stride;
+    const float *alt = W + wbase + (int64_t)(li ^ (1 << k)) * stride;
+    const float *dy = dY + b * n_outputs;
+    double acc = 0.0;
+    for (int p = lane; p < P; p += 32) {
+        const int q = p + hole_offset(p, sp);
+        acc += (double)__ldg(dy + __ldg(tg + p)) * ((double)__ldg(row + q) - (double)__ldg(alt + q));
+    }
+    for (int off = 16; off >= 1; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+    if (lane == 0) {
+        const double du = surrogate_up(__ldg(min_delta + work)) * acc;
+        if (fabs(du) > kEps) {
+            const int2 a = __ldg(anchors + (size_t)t * n_anchors + k);
+            atomicAdd(dX + b * n_inputs + a.x, (float)du);
+            atomicAdd(dX + b * n_inputs + a.y, -(float)du);
         }
     }
 }
@@ -176,35 +259,50 @@ __global__ void sparse_input_grad_fixed_kernel(SparseView sp, const float *__res
 }
 
 // --------------------------------------------------------------------------------------------
-// Table gradient: target[slot(t, idx[b, t], p)] += lr * dY[b, target(t, p)] for |dY| > EPS
+// Table gradient: target[row(t, idx[b, t]) + p] += lr * dY[b, target(p)] for |dY| > EPS
 // (reference: gather_w_gradients_non_seq_sparse_logic, proto:1501-1545, helper :584-714).
-// Same flattened pair list as the forward; consecutive threads update consecutive slots of a row.
+// The value a lane adds is the same for all detectors of the chunk; every detector's row receives one
+// contiguous run of reductions.
 // --------------------------------------------------------------------------------------------
 template <bool INT_MODE>
 __global__ void __launch_bounds__(256) sparse_weight_grad_kernel(SparseView sp, const float *__restrict__ dY,
                                                                 const int32_t *__restrict__ idx,
-                                                                float *__restrict__ target_arr, int n_outputs,
-                                                                int n_detectors, int slices, double lr,
+                                                                float *__restrict__ target_arr, int64_t batch,
+                                                                int n_outputs, int n_detectors, double lr,
                                                                 double fixed_scale) {
-    extern __shared__ __align__(16) unsigned char smem_raw[];
-    float *dys = reinterpret_cast<float *>(smem_raw);
-    int32_t *idx_s = reinterpret_cast<int32_t *>(smem_raw) + n_outputs;
-    const int64_t b = blockIdx.x;
-    const int64_t per = (sp.n_syn + slices - 1) / slices;
-    const int64_t s0 = blockIdx.y * per, s1 = min(sp.n_syn, s0 + per);
-    const float *dy = dY + b * n_outputs;
-    for (int o = threadIdx.x; o < n_outputs; o += blockDim.x) dys[o] = __ldg(dy + o);
-    const int32_t *idx_b = idx + b * n_detectors;
-    for (int t = threadIdx.x; t < n_detectors; t += blockDim.x) idx_s[t] = __ldg(idx_b + t);
-    __syncthreads();
-    for (int64_t s = s0 + threadIdx.x; s < s1; s += blockDim.x) {
-        const int t = __ldg(sp.syn_det + s);
-        const double g = (double)dys[__ldg(sp.syn_target + s)];
-        if (fabs(g) > kEps) {
-            const int p = (int)(s - __ldg(sp.det_sstart + t));
-            const int64_t slot = __ldg(sp.det_wbase + t) + (int64_t)idx_s[t] * __ldg(sp.det_stride + t) + p + hole_offset(p, sp);
-            if (INT_MODE) atomicAdd(reinterpret_cast<int32_t *>(target_arr) + slot, to_fixed(g * lr, fixed_scale));
-            else atomicAdd(target_arr + slot, (float)(g * lr));
+    const int lane = threadIdx.x & 31;
+    const int64_t work = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (work >= batch * sp.n_chunks) return;
+    const int64_t b = work / sp.n_chunks;
+    const int64_t c = work - b * sp.n_chunks;
+    const ChunkLane ch = load_chunk(sp, idx + b * n_detectors, c, lane, nullptr);
+    int LG = 32;
+    while (LG > 4 && (LG >> 1) >= ch.P) LG >>= 1;
+    const int NG = 32 / LG;
+    const int g = lane / LG, j = lane - g * LG;
+    float *Tb = target_arr + ch.wbase0;
+    const int32_t *tg = sp.syn_target + ch.toff;
+    for (int p0 = 0; p0 < ch.P; p0 += LG) {
+        const int p = p0 + j;
+        const int q = p + hole_offset(p, sp);
+        float val = 0.f;
+        int32_t ival = 0;
+        bool active = false;
+        if (p < ch.P) {
+            const double gd = (double)__ldg(dY + b * n_outputs + __ldg(tg + p));
+            if (fabs(gd) > kEps) {
+                active = true;
+                if (INT_MODE) ival = to_fixed(gd * lr, fixed_scale);
+                else val = (float)(gd * lr);
+            }
+        }
+        for (int d0 = 0; d0 < ch.ndet; d0 += NG) {
+            const int d = d0 + g;
+            const int32_t off = __shfl_sync(0xffffffffu, ch.row_off, d & 31);
+            if (active && d < ch.ndet) {
+                if (INT_MODE) atomicAdd(reinterpret_cast<int32_t *>(Tb) + (int64_t)off + q, ival);
+                else atomicAdd(Tb + (int64_t)off + q, val);
+            }
         }
     }
 }
@@ -212,8 +310,8 @@ __global__ void __launch_bounds__(256) sparse_weight_grad_kernel(SparseView sp, 
 static SparseView make_view(const lutb_sparse_index *sp) {
     SparseView v;
     v.det_wbase = sp->det_wbase; v.det_stride = sp->det_stride; v.det_count = sp->det_count;
-    v.det_sstart = sp->det_sstart; v.syn_det = sp->syn_det; v.syn_target = sp->syn_target;
-    v.n_syn = sp->n_syn_per_sample; v.group = sp->group_size;
+    v.det_sstart = sp->det_sstart; v.syn_target = sp->syn_target;
+    v.chunks = reinterpret_cast<const int4 *>(sp->chunk_info); v.n_chunks = sp->n_chunks; v.group = sp->group_size;
     v.group_shift = -1;
     for (int s = 0; s < 31; s++) if ((1 << s) == sp->group_size) v.group_shift = s;
     return v;
@@ -221,18 +319,22 @@ static SparseView make_view(const lutb_sparse_index *sp) {
 
 static int validate_sparse(const lutb_sparse_index *sp) {
     LUTB_REQUIRE(sp != nullptr, LUTB_ERR_NULL, "sparse index is NULL");
-    LUTB_REQUIRE(sp->det_wbase && sp->det_stride && sp->det_count && sp->det_sstart && sp->syn_det && sp->syn_target,
+    LUTB_REQUIRE(sp->det_wbase && sp->det_stride && sp->det_count && sp->det_sstart && sp->syn_det && sp->syn_target &&
+                     sp->chunk_info,
                  LUTB_ERR_NULL, "a sparse index array is NULL");
-    LUTB_REQUIRE(sp->group_size > 0 && sp->n_syn_per_sample > 0 && sp->n_weights > 0 && sp->max_count > 0,
+    LUTB_REQUIRE(sp->group_size > 0 && sp->n_syn_per_sample > 0 && sp->n_weights > 0 && sp->max_count > 0 &&
+                     sp->n_chunks > 0,
                  LUTB_ERR_SHAPE, "empty sparse index");
+    LUTB_REQUIRE((reinterpret_cast<uintptr_t>(sp->chunk_info) & 15) == 0, LUTB_ERR_ALIGN,
+                 "chunk_info must be 16-byte aligned");
     return LUTB_OK;
 }
 
-static int pick_slices(int64_t batch, int sm, int64_t work_items, int min_items) {
-    // enough blocks for ~4 per SM, but never slices with fewer than `min_items` work items
-    int64_t want = ((int64_t)sm * 4 + batch - 1) / batch;
-    int64_t cap = max((int64_t)1, work_items / min_items);
-    return (int)max((int64_t)1, min(min(want, cap), (int64_t)64));
+static int chunk_grid(int64_t items, unsigned *blocks) {
+    const int64_t n = (items + 7) / 8;  // 8 warps per block
+    LUTB_REQUIRE(n <= 0x7FFFFFFF, LUTB_ERR_SHAPE, "batch too large for one launch");
+    *blocks = (unsigned)n;
+    return LUTB_OK;
 }
 
 }  // namespace lutb
@@ -255,21 +357,16 @@ extern "C" int lutb_nonseq_sparse_forward(const lutb_layer_cfg *cfg, const lutb_
     rc = launch_check_detectors(x, batch, cfg->n_inputs, anchors, cfg->n_detectors, cfg->n_anchors, cfg->cmp_eps, idx,
                                 min_delta, min_k, st);
     if (rc) return rc;
-    const size_t smem = (size_t)(cfg->n_outputs + cfg->n_detectors) * 4;
-    LUTB_REQUIRE(smem <= (size_t)kMaxSmemPerBlock - 1024, LUTB_ERR_SHAPE,
-                 "n_outputs + n_detectors too large for the sparse forward kernel");
-    const int slices = pick_slices(batch, device_info().sm_count, sp->n_syn_per_sample, 4096);
     SparseView v = make_view(sp);
-    dim3 grid((unsigned)batch, (unsigned)slices);
+    unsigned blocks;
+    rc = chunk_grid(batch * sp->n_chunks, &blocks);
+    if (rc) return rc;
     {
         KernelScope scope(K_SPARSE_FORWARD, st);
-        if (cfg->int_mode) {
-            if (smem > 48 * 1024) LUTB_CUDA(cudaFuncSetAttribute(sparse_forward_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            sparse_forward_kernel<true><<<grid, 256, smem, st>>>(v, weights, idx, y, cfg->n_outputs, cfg->n_detectors, slices, cfg->int_rescaler);
-        } else {
-            if (smem > 48 * 1024) LUTB_CUDA(cudaFuncSetAttribute(sparse_forward_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            sparse_forward_kernel<false><<<grid, 256, smem, st>>>(v, weights, idx, y, cfg->n_outputs, cfg->n_detectors, slices, cfg->int_rescaler);
-        }
+        if (cfg->int_mode)
+            sparse_forward_kernel<true><<<blocks, 256, 0, st>>>(v, weights, idx, y, batch, cfg->n_outputs, cfg->n_detectors, cfg->int_rescaler);
+        else
+            sparse_forward_kernel<false><<<blocks, 256, 0, st>>>(v, weights, idx, y, batch, cfg->n_outputs, cfg->n_detectors, cfg->int_rescaler);
     }
     LUTB_LAUNCH_CHECK();
     if (cfg->int_mode) return launch_fixed_to_float(y, batch * (int64_t)cfg->n_outputs, cfg->int_rescaler, st);
@@ -303,17 +400,23 @@ extern "C" int lutb_nonseq_sparse_backward(const lutb_layer_cfg *cfg, const lutb
             sparse_input_grad_fixed_kernel<<<(unsigned)blocks, 128, 0, st>>>(
                 v, weights, dY, reinterpret_cast<const int2 *>(anchors), idx, min_delta, min_k, dX, batch,
                 cfg->n_inputs, O, Nt, cfg->n_anchors, cfg->int_rescaler);
+        } else if (sp->max_count > 32) {
+            unsigned blocks;
+            rc = chunk_grid(batch * Nt, &blocks);
+            if (rc) return rc;
+            sparse_input_grad_long_kernel<<<blocks, 256, 0, st>>>(v, weights, dY, reinterpret_cast<const int2 *>(anchors), idx,
+                                                                 min_delta, min_k, dX, batch, cfg->n_inputs, O, Nt, cfg->n_anchors);
         } else {
-            int lanes = 1;
-            while (lanes < 32 && lanes < sp->max_count) lanes <<= 1;
-            const size_t smem = (size_t)O * 4;
-            LUTB_REQUIRE(smem <= (size_t)kMaxSmemPerBlock - 1024, LUTB_ERR_SHAPE, "n_outputs too large for the sparse backward kernel");
-            if (smem > 48 * 1024) LUTB_CUDA(cudaFuncSetAttribute(sparse_input_grad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            const int slices = pick_slices(batch, sm, Nt, 256);
-            dim3 grid((unsigned)batch, (unsigned)slices);
-            sparse_input_grad_kernel<<<grid, 256, smem, st>>>(v, weights, dY, reinterpret_cast<const int2 *>(anchors), idx,
-                                                             min_delta, min_k, dX, cfg->n_inputs, O, Nt, cfg->n_anchors,
-                                                             lanes, slices);
+            unsigned blocks;
+            rc = chunk_grid(batch * sp->n_chunks, &blocks);
+            if (rc) return rc;
+            const int2 *an = reinterpret_cast<const int2 *>(anchors);
+            if (sp->max_count > 16)
+                sparse_input_grad_kernel<32><<<blocks, 256, 0, st>>>(v, weights, dY, an, idx, min_delta, min_k, dX, batch, cfg->n_inputs, O, Nt, cfg->n_anchors);
+            else if (sp->max_count > 8)
+                sparse_input_grad_kernel<16><<<blocks, 256, 0, st>>>(v, weights, dY, an, idx, min_delta, min_k, dX, batch, cfg->n_inputs, O, Nt, cfg->n_anchors);
+            else
+                sparse_input_grad_kernel<8><<<blocks, 256, 0, st>>>(v, weights, dY, an, idx, min_delta, min_k, dX, batch, cfg->n_inputs, O, Nt, cfg->n_anchors);
         }
     }
     LUTB_LAUNCH_CHECK();
@@ -321,19 +424,14 @@ extern "C" int lutb_nonseq_sparse_backward(const lutb_layer_cfg *cfg, const lutb
     if (external_lr >= 0.0) lr *= -(double)(float)external_lr;
     float *target = external_lr >= 0.0 ? weights : dW;
     {
-        const size_t smem = (size_t)(O + Nt) * 4;
-        LUTB_REQUIRE(smem <= (size_t)kMaxSmemPerBlock - 1024, LUTB_ERR_SHAPE,
-                     "n_outputs + n_detectors too large for the sparse table-gradient kernel");
-        const int slices = pick_slices(batch, sm, sp->n_syn_per_sample, 4096);
-        dim3 grid((unsigned)batch, (unsigned)slices);
+        unsigned blocks;
+        rc = chunk_grid(batch * sp->n_chunks, &blocks);
+        if (rc) return rc;
         KernelScope scope(K_SPARSE_WEIGHT_GRAD, st);
-        if (cfg->int_mode) {
-            if (smem > 48 * 1024) LUTB_CUDA(cudaFuncSetAttribute(sparse_weight_grad_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            sparse_weight_grad_kernel<true><<<grid, 256, smem, st>>>(v, dY, idx, target, O, Nt, slices, lr, cfg->int_rescaler);
-        } else {
-            if (smem > 48 * 1024) LUTB_CUDA(cudaFuncSetAttribute(sparse_weight_grad_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            sparse_weight_grad_kernel<false><<<grid, 256, smem, st>>>(v, dY, idx, target, O, Nt, slices, lr, cfg->int_rescaler);
-        }
+        if (cfg->int_mode)
+            sparse_weight_grad_kernel<true><<<blocks, 256, 0, st>>>(v, dY, idx, target, batch, O, Nt, lr, cfg->int_rescaler);
+        else
+            sparse_weight_grad_kernel<false><<<blocks, 256, 0, st>>>(v, dY, idx, target, batch, O, Nt, lr, cfg->int_rescaler);
     }
     LUTB_LAUNCH_CHECK();
     if (cfg->int_mode) {

@@ -217,8 +217,46 @@ class SparseIndex:
         assert self.syn_target.numel() == self.n_syn_per_sample
         if self.syn_target.numel():
             assert int(self.syn_target.min()) >= 0 and int(self.syn_target.max()) < n_outputs
+        self.chunk_info = self._build_chunks()
+        self.n_chunks = self.chunk_info.shape[0]
 
-    _TENSORS = ("det_wbase", "det_stride", "det_count", "det_sstart", "syn_det", "syn_target")
+    CHUNK = 32  # detectors per chunk = lanes of a warp
+
+    def _build_chunks(self):
+        """int32 [n_chunks, 4] = (first detector, detector count <= 32, offset of the shared target list in
+        syn_target, synapses per row).  A chunk is a run of consecutive detectors with identical target
+        lists (the detectors of one group); the kernels give one warp to each (sample, chunk)."""
+        counts = self.det_count.to(torch.int64).cpu()
+        starts = self.det_sstart.to(torch.int64).cpu()
+        tgt = self.syn_target.cpu()
+        n = counts.numel()
+        same = torch.zeros(n, dtype=torch.bool)  # same[t]: detector t repeats the target list of t-1
+        if n > 1:
+            pmax = int(counts.max().item())
+            lists = torch.full((n, max(pmax, 1)), -1, dtype=torch.int32)
+            det = torch.repeat_interleave(torch.arange(n), counts)
+            pos = torch.arange(tgt.numel()) - starts[det]
+            lists[det, pos] = tgt
+            same[1:] = (lists[1:] == lists[:-1]).all(dim=1) & (counts[1:] > 0)
+        chunks = []
+        t = 0
+        same_l = same.tolist()
+        counts_l = counts.tolist()
+        starts_l = starts.tolist()
+        wbase_l = self.det_wbase.cpu().tolist()
+        stride_l = self.det_stride.cpu().tolist()
+        while t < n:
+            end = t + 1
+            while end < n and end - t < self.CHUNK and same_l[end]:
+                end += 1
+            if counts_l[t] > 0:
+                span = wbase_l[end - 1] + stride_l[end - 1] * self.rows_per_detector - wbase_l[t]
+                assert span < (1 << 31), "tables of one detector chunk span more than 2^31 weight slots"
+                chunks.append((t, end - t, starts_l[t], counts_l[t]))
+            t = end
+        return torch.tensor(chunks, dtype=torch.int32).reshape(-1, 4).contiguous()
+
+    _TENSORS = ("det_wbase", "det_stride", "det_count", "det_sstart", "syn_det", "syn_target", "chunk_info")
 
     @staticmethod
     def row_stride(count, group_size):
@@ -314,7 +352,7 @@ class SparseIndex:
             det_wbase=self.det_wbase.data_ptr(), det_stride=self.det_stride.data_ptr(),
             det_count=self.det_count.data_ptr(), det_sstart=self.det_sstart.data_ptr(),
             syn_det=self.syn_det.data_ptr(), syn_target=self.syn_target.data_ptr(),
-            n_syn_per_sample=self.n_syn_per_sample, n_weights=self.n_weights, group_size=self.group_size,
+            chunk_info=self.chunk_info.data_ptr(), n_chunks=self.n_chunks, n_syn_per_sample=self.n_syn_per_sample, n_weights=self.n_weights, group_size=self.group_size,
             max_count=self.max_count)
 
     def nbytes(self):
