@@ -292,7 +292,7 @@ class SparseConvNetWorkload:
     def algorithmic_bytes(self):
         """Per sample and kernel family, summed over the layers that launch it."""
         out = {k: 0 for k in ("check_detectors", "sparse_forward", "sparse_input_grad", "sparse_weight_grad",
-                              "fc_gather_forward", "fc_input_grad", "fc_weight_grad")}
+                              "sparse_backward_fused", "fc_gather_forward", "fc_input_grad", "fc_weight_grad")}
         for (h, o, g, per) in self.LAYERS:
             I, O, Nt = h * h, o * o, g * g * per
             sp = self._syn_per_sample.get((h, o), None)
@@ -300,6 +300,8 @@ class SparseConvNetWorkload:
             out["sparse_forward"] += 4 * Nt + 4 * sp[0] + 4 * sp[1] + 4 * O
             out["sparse_input_grad"] += 4 * O + 12 * Nt + 2 * 4 * sp[0] + 16 * Nt
             out["sparse_weight_grad"] += 4 * O + 4 * Nt + 2 * 4 * sp[0]
+            # fused input + table gradient: dY, idx / margins, rows S and S-bar, dX updates, dW row RMW
+            out["sparse_backward_fused"] += 4 * O + 12 * Nt + 2 * 4 * sp[0] + 16 * Nt + 2 * 4 * sp[0]
         I, O, Nt, Nc = self.READOUT
         out["check_detectors"] += 4 * I + 12 * Nt
         out["fc_gather_forward"] += 4 * Nt + 4 * Nt * O + 4 * O

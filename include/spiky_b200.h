@@ -119,9 +119,11 @@ typedef struct lutb_sparse_index {
     const int32_t *det_sstart;  /* [Nt] exclusive prefix sum of det_count */
     const int32_t *syn_det;     /* [n_syn_per_sample] detector of each (detector, synapse) pair, detector order */
     const int32_t *syn_target;  /* [n_syn_per_sample] output index of each pair */
-    const int32_t *chunk_info;  /* [n_chunks][4]: first detector, detector count (<= 32), offset of the shared
-                                   target list in syn_target, synapses per row.  A chunk is a run of consecutive
-                                   detectors with identical target lists; its tables must span < 2^31 slots */
+    const int32_t *chunk_info;  /* [n_chunks][8], 32-byte aligned: first detector, detector count (<= 32), offset of
+                                   the shared target list in syn_target, synapses per row, row stride, slots per
+                                   detector table (rows * stride), det_wbase of the first detector (low, high
+                                   word).  A chunk is a run of consecutive detectors with identical target lists
+                                   whose tables lie back to back and together span < 2^31 slots */
     int64_t n_chunks;
     int64_t n_syn_per_sample;   /* sum of det_count */
     int64_t n_weights;          /* length of the flat weight array */

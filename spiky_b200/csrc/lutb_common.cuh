@@ -64,6 +64,7 @@ enum KernelId {
     K_SPARSE_FORWARD,
     K_SPARSE_INPUT_GRAD,
     K_SPARSE_WEIGHT_GRAD,
+    K_SPARSE_BACKWARD_FUSED,
     K_COUNT
 };
 

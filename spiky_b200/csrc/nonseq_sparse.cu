@@ -13,7 +13,7 @@ struct SparseView {
     const int32_t *det_count;
     const int32_t *det_sstart;
     const int32_t *syn_target;
-    const int4 *chunks;   // (first detector, detector count <= 32, target list offset, synapses per row)
+    const int4 *chunks;   // two int4 per chunk, see lutb_sparse_index::chunk_info
     int64_t n_chunks;
     int32_t group;
     int32_t group_shift;  // log2(group) when group is a power of two, else -1
@@ -24,33 +24,32 @@ __device__ __forceinline__ int hole_offset(int p, const SparseView &sp) {
     return 2 * (sp.group_shift >= 0 ? (p >> sp.group_shift) : (p / sp.group));
 }
 
-// All three training kernels give one warp to a (sample, chunk) pair.  A chunk is a run of up to 32
-// consecutive detectors that share one target list (the detectors of one group).  Lane L first loads
-// the table index of detector L of the chunk (one coalesced read) and turns it into the offset of the
-// selected row relative to the chunk's first table; the offsets are then broadcast with shuffles while
-// the lanes cover the synapses of a row, so that every row read or update is one contiguous segment.
-// When rows are short the warp splits into NG = 32 / LG lane groups that take detectors round-robin.
-struct ChunkLane {
-    int det0, ndet, toff, P;
+// The training kernels give one warp to a (chunk, run of kSampleRun samples) pair.  A chunk is a run of
+// up to 32 consecutive detectors that share one target list (the detectors of one group) and whose
+// tables lie back to back.  Work is ordered chunk-major: warps that run at the same time work on the
+// same few chunks for different samples, so a chunk's tables (a few hundred KB) are fetched from HBM
+// once and then served by L2 for the rest of the batch.
+// Per sample, lane L loads the table index of detector L of the chunk (one coalesced read, issued one
+// sample ahead so that it overlaps the row reads of the current sample) and turns it into the offset
+// of the selected row from the chunk's first table; offsets are broadcast with shuffles while the lanes
+// cover the synapses of a row, so every row access is one contiguous segment and all row reads of a
+// sample are in flight together.  Rows of up to LG synapses use LG-lane groups (NG = 32 / LG groups
+// take detectors round-robin).
+constexpr int kSampleRun = 8;
+
+struct ChunkStatic {
+    int det0, ndet, toff, P, stride, table;
     int64_t wbase0;
-    int32_t row_off;   // offset of this lane's detector's selected row from wbase0 (0 when lane >= ndet)
 };
 
-__device__ __forceinline__ ChunkLane load_chunk(const SparseView &sp, const int32_t *__restrict__ idx_b, int64_t c,
-                                                int lane, int32_t *li_out) {
-    const int4 ci = __ldg(sp.chunks + c);
-    ChunkLane ch;
-    ch.det0 = ci.x; ch.ndet = ci.y; ch.toff = ci.z; ch.P = ci.w;
-    ch.wbase0 = __ldg(sp.det_wbase + ch.det0);
-    ch.row_off = 0;
-    int32_t li = 0;
-    if (lane < ch.ndet) {
-        const int t = ch.det0 + lane;
-        li = __ldg(idx_b + t);
-        ch.row_off = (int32_t)(__ldg(sp.det_wbase + t) - ch.wbase0) + li * __ldg(sp.det_stride + t);
-    }
-    if (li_out) *li_out = li;
-    return ch;
+__device__ __forceinline__ ChunkStatic load_chunk(const SparseView &sp, int64_t c) {
+    const int4 a = __ldg(sp.chunks + 2 * c);
+    const int4 w = __ldg(sp.chunks + 2 * c + 1);
+    ChunkStatic cs;
+    cs.det0 = a.x; cs.ndet = a.y; cs.toff = a.z; cs.P = a.w;
+    cs.stride = w.x; cs.table = w.y;
+    cs.wbase0 = (int64_t)(((uint64_t)(uint32_t)w.w << 32) | (uint32_t)w.z);
+    return cs;
 }
 
 // --------------------------------------------------------------------------------------------
@@ -59,159 +58,260 @@ __device__ __forceinline__ ChunkLane load_chunk(const SparseView &sp, const int3
 // The chunk's detectors are summed in registers, so the shared output cells see one reduction per
 // (sample, chunk, target) instead of one per synapse.
 // --------------------------------------------------------------------------------------------
-template <bool INT_MODE>
-__global__ void __launch_bounds__(256) sparse_forward_kernel(SparseView sp, const float *__restrict__ W,
-                                                            const int32_t *__restrict__ idx, float *__restrict__ y,
-                                                            int64_t batch, int n_outputs, int n_detectors,
-                                                            double fixed_scale) {
-    const int lane = threadIdx.x & 31;
-    const int64_t work = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (work >= batch * sp.n_chunks) return;
-    const int64_t b = work / sp.n_chunks;
-    const int64_t c = work - b * sp.n_chunks;
-    const ChunkLane ch = load_chunk(sp, idx + b * n_detectors, c, lane, nullptr);
-    int LG = 32;
-    while (LG > 4 && (LG >> 1) >= ch.P) LG >>= 1;
-    const int NG = 32 / LG;
+template <int LG, bool INT_MODE>
+__device__ __forceinline__ void chunk_forward(const SparseView &sp, const ChunkStatic &cs, const float *__restrict__ W,
+                                              const int32_t *__restrict__ idx, float *__restrict__ y, int64_t b0,
+                                              int64_t b1, int n_outputs, int n_detectors, int lane,
+                                              double fixed_scale) {
+    constexpr int NG = 32 / LG;
     const int g = lane / LG, j = lane - g * LG;
-    const float *Wb = W + ch.wbase0;
-    const int32_t *tg = sp.syn_target + ch.toff;
-    for (int p0 = 0; p0 < ch.P; p0 += LG) {
-        const int p = p0 + j;
-        const bool valid = p < ch.P;
-        const int q = p + hole_offset(p, sp);
+    const bool valid = j < cs.P;
+    const bool has_det = lane < cs.ndet;
+    const float *Wb = W + cs.wbase0 + j + hole_offset(j, sp);
+    const int target = (valid && g == 0) ? __ldg(sp.syn_target + cs.toff + j) : 0;
+    const int32_t *idx_l = idx + cs.det0 + lane;
+    int32_t li_next = has_det ? __ldg(idx_l + b0 * n_detectors) : 0;
+    for (int64_t b = b0; b < b1; b++) {
+        const int32_t row_off = has_det ? lane * cs.table + li_next * cs.stride : 0;
+        if (b + 1 < b1 && has_det) li_next = __ldg(idx_l + (b + 1) * n_detectors);
+        float w[LG];
+#pragma unroll
+        for (int i = 0; i < LG; i++) {
+            const int d = i * NG + g;
+            const int32_t off = __shfl_sync(0xffffffffu, row_off, d);
+            w[i] = (valid && d < cs.ndet) ? __ldg(Wb + off) : 0.f;
+        }
         float acc = 0.f;
         int32_t iacc = 0;
-#pragma unroll 4
-        for (int d0 = 0; d0 < ch.ndet; d0 += NG) {
-            const int d = d0 + g;
-            const int32_t off = __shfl_sync(0xffffffffu, ch.row_off, d & 31);
-            if (valid && d < ch.ndet) {
-                const float w = __ldg(Wb + (int64_t)off + q);
-                if (INT_MODE) iacc += to_fixed((double)w, fixed_scale);
-                else acc += w;
-            }
+#pragma unroll
+        for (int i = 0; i < LG; i++) {
+            // beyond the chunk w is exactly 0 and truncates to 0
+            if (INT_MODE) iacc += to_fixed((double)w[i], fixed_scale);
+            else acc += w[i];
         }
+#pragma unroll
         for (int m = LG; m < 32; m <<= 1) {
             if (INT_MODE) iacc += __shfl_xor_sync(0xffffffffu, iacc, m);
             else acc += __shfl_xor_sync(0xffffffffu, acc, m);
         }
         if (valid && g == 0) {
-            const int target = __ldg(tg + p);
             if (INT_MODE) atomicAdd(reinterpret_cast<int32_t *>(y) + b * n_outputs + target, iacc);
             else atomicAdd(y + b * n_outputs + target, acc);
         }
     }
 }
 
-// --------------------------------------------------------------------------------------------
-// Input gradient (reference: propagate_through_detectors_non_seq_sparse_logic, proto:1303-1419):
-// per (sample, detector) g = sum_p dY[target(p)] * (W[row + p] - W[alt + p]), du = up(min_delta) * g.
-// A lane group of LG lanes covers the synapses; every lane keeps one partial per detector it sees
-// (LG of them), and a butterfly of LG - 1 shuffles transposes and reduces them so that each lane
-// ends with the full sum of exactly one detector and performs that detector's two updates itself.
-// Rows have at most 32 synapses here (longer rows use the generic kernel below); partial products are
-// fp32 (<= 32 terms), the scaling by up() is done in double.
-// --------------------------------------------------------------------------------------------
-template <int LG>
-__global__ void __launch_bounds__(256) sparse_input_grad_kernel(SparseView sp, const float *__restrict__ W,
-                                                               const float *__restrict__ dY,
-                                                               const int2 *__restrict__ anchors,
-                                                               const int32_t *__restrict__ idx,
-                                                               const float *__restrict__ min_delta,
-                                                               const int32_t *__restrict__ min_k,
-                                                               float *__restrict__ dX, int64_t batch, int n_inputs,
-                                                               int n_outputs, int n_detectors, int n_anchors) {
-    constexpr int NG = 32 / LG;
+template <bool INT_MODE>
+__global__ void __launch_bounds__(256) sparse_forward_kernel(SparseView sp, const float *__restrict__ W,
+                                                            const int32_t *__restrict__ idx, float *__restrict__ y,
+                                                            int64_t batch, int n_outputs, int n_detectors,
+                                                            double fixed_scale) {
     const int lane = threadIdx.x & 31;
+    const int64_t runs = (batch + kSampleRun - 1) / kSampleRun;
     const int64_t work = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (work >= batch * sp.n_chunks) return;
-    const int64_t b = work / sp.n_chunks;
-    const int64_t c = work - b * sp.n_chunks;
-    int32_t li;
-    const ChunkLane ch = load_chunk(sp, idx + b * n_detectors, c, lane, &li);
-    // this lane's detector: alternative row (minimum-margin bit flipped), margin, flipped pair
-    int32_t alt_off = 0, my_k = 0;
-    float my_m = 0.f;
-    if (lane < ch.ndet) {
-        const int t = ch.det0 + lane;
-        my_k = __ldg(min_k + b * n_detectors + t);
-        my_m = __ldg(min_delta + b * n_detectors + t);
-        alt_off = ch.row_off + ((li ^ (1 << my_k)) - li) * __ldg(sp.det_stride + t);
-    }
-    const int g = lane / LG, j = lane - g * LG;
-    const bool valid = j < ch.P;
-    const int q = j + hole_offset(j, sp);
-    const float *Wb = W + ch.wbase0 + q;
-    const float gp = valid ? __ldg(dY + b * n_outputs + __ldg(sp.syn_target + ch.toff + j)) : 0.f;
-    float v[LG];
-#pragma unroll
-    for (int i = 0; i < LG; i++) {
-        const int d = i * NG + g;
-        const int32_t ro = __shfl_sync(0xffffffffu, ch.row_off, d);
-        const int32_t ao = __shfl_sync(0xffffffffu, alt_off, d);
-        // detectors beyond the chunk have ro == ao == 0: the difference below is exactly zero
-        v[i] = valid ? gp * (__ldg(Wb + ro) - __ldg(Wb + ao)) : 0.f;
-    }
-    // transpose-reduce: after the stage with offset o, a lane keeps the half of the values whose
-    // index bit matches its own lane bit, summed with the partner lane's copy
-#pragma unroll
-    for (int o = LG / 2; o >= 1; o >>= 1) {
-        const bool upper = (j & o) != 0;
-#pragma unroll
-        for (int i = 0; i < o; i++) {
-            const float send = upper ? v[i] : v[i + o];
-            const float keep = upper ? v[i + o] : v[i];
-            v[i] = keep + __shfl_xor_sync(0xffffffffu, send, o);
-        }
-    }
-    // lane (g, j) now holds detector d = j * NG + g of the chunk
-    const int d = j * NG + g;
-    const int32_t k = __shfl_sync(0xffffffffu, my_k, d);
-    const float m = __shfl_sync(0xffffffffu, my_m, d);
-    if (d < ch.ndet) {
-        const double du = surrogate_up(m) * (double)v[0];
-        if (fabs(du) > kEps) {
-            const int2 a = __ldg(anchors + (size_t)(ch.det0 + d) * n_anchors + k);
-            float *dx = dX + b * n_inputs;
-            atomicAdd(dx + a.x, (float)du);
-            atomicAdd(dx + a.y, -(float)du);
+    if (work >= runs * sp.n_chunks) return;
+    const int64_t c = work / runs;
+    const int64_t b0 = (work - c * runs) * kSampleRun;
+    const int64_t b1 = min(batch, b0 + kSampleRun);
+    const ChunkStatic cs = load_chunk(sp, c);
+    if (cs.P <= 8) chunk_forward<8, INT_MODE>(sp, cs, W, idx, y, b0, b1, n_outputs, n_detectors, lane, fixed_scale);
+    else if (cs.P <= 16) chunk_forward<16, INT_MODE>(sp, cs, W, idx, y, b0, b1, n_outputs, n_detectors, lane, fixed_scale);
+    else if (cs.P <= 32) chunk_forward<32, INT_MODE>(sp, cs, W, idx, y, b0, b1, n_outputs, n_detectors, lane, fixed_scale);
+    else {
+        // rows longer than a warp: plain loop, one detector at a time
+        const float *Wb = W + cs.wbase0;
+        for (int64_t b = b0; b < b1; b++) {
+            const int32_t li = lane < cs.ndet ? __ldg(idx + b * n_detectors + cs.det0 + lane) : 0;
+            const int32_t row_off = lane * cs.table + li * cs.stride;
+            for (int p = lane; p < cs.P; p += 32) {
+                const int q = p + hole_offset(p, sp);
+                float acc = 0.f;
+                int32_t iacc = 0;
+                for (int d = 0; d < cs.ndet; d++) {
+                    const float w = __ldg(Wb + (int64_t)__shfl_sync(0xffffffffu, row_off, d) + q);
+                    if (INT_MODE) iacc += to_fixed((double)w, fixed_scale);
+                    else acc += w;
+                }
+                const int target = __ldg(sp.syn_target + cs.toff + p);
+                if (INT_MODE) atomicAdd(reinterpret_cast<int32_t *>(y) + b * n_outputs + target, iacc);
+                else atomicAdd(y + b * n_outputs + target, acc);
+            }
         }
     }
 }
 
-// Generic fp32 input gradient for rows longer than 32 synapses: one warp per (sample, detector).
-__global__ void __launch_bounds__(256) sparse_input_grad_long_kernel(SparseView sp, const float *__restrict__ W,
-                                                                    const float *__restrict__ dY,
-                                                                    const int2 *__restrict__ anchors,
-                                                                    const int32_t *__restrict__ idx,
-                                                                    const float *__restrict__ min_delta,
-                                                                    const int32_t *__restrict__ min_k,
-                                                                    float *__restrict__ dX, int64_t batch,
-                                                                    int n_inputs, int n_outputs, int n_detectors,
-                                                                    int n_anchors) {
+// --------------------------------------------------------------------------------------------
+// Backward over a chunk (rows of at most 32 synapses):
+//   input gradient (reference: propagate_through_detectors_non_seq_sparse_logic, proto:1303-1419):
+//     per detector g = sum_p dY[target(p)] * (W[row + p] - W[alt + p]), du = up(min_delta) * g,
+//     +du / -du on the two inputs of the minimum-margin anchor pair;
+//   table gradient (reference: gather_w_gradients_non_seq_sparse_logic, proto:1501-1545, helper :584-714):
+//     target[row + p] += lr * dY[target(p)] for |dY| > EPS.
+// Each lane keeps one partial product sum per detector it sees (LG of them); a butterfly of LG - 1
+// shuffles transposes and reduces them so that every lane ends with the full sum of exactly one
+// detector and performs that detector's two updates itself.  Partial sums are fp32 (<= 32 terms), the
+// scaling by up() is done in double.  With DO_DX and DO_DW both set the row just read for the input
+// gradient is updated while it is still in L2; the internal (in-place SGD) policy must not fuse,
+// because there the table gradient modifies the very weights other samples still have to read.
+// --------------------------------------------------------------------------------------------
+template <int LG, bool DO_DX, bool DO_DW, bool INT_DW>
+__device__ __forceinline__ void chunk_backward(const SparseView &sp, const ChunkStatic &cs, const float *__restrict__ W,
+                                               const float *__restrict__ dY, const int2 *__restrict__ anchors,
+                                               const int32_t *__restrict__ idx, const float *__restrict__ min_delta,
+                                               const int32_t *__restrict__ min_k, float *__restrict__ dX,
+                                               float *__restrict__ target_arr, int64_t b0, int64_t b1, int n_inputs,
+                                               int n_outputs, int n_detectors, int n_anchors, int lane, double lr,
+                                               double fixed_scale) {
+    constexpr int NG = 32 / LG;
+    const int g = lane / LG, j = lane - g * LG;
+    const bool valid = j < cs.P;
+    const bool has_det = lane < cs.ndet;
+    const int q = j + hole_offset(j, sp);
+    const int my_target = valid ? __ldg(sp.syn_target + cs.toff + j) : 0;
+    const float *Wb = W + cs.wbase0 + q;
+    float *Tb = DO_DW ? target_arr + cs.wbase0 + q : nullptr;
+    // lane (g, j) ends up owning detector j * NG + g of the chunk
+    const int own = j * NG + g;
+    const int64_t det_l = cs.det0 + lane;
+    // per-sample inputs are fetched one sample ahead
+    int32_t li_n = 0, k_n = 0;
+    float m_n = 0.f, gp_n = 0.f;
+    if (has_det) {
+        li_n = __ldg(idx + b0 * n_detectors + det_l);
+        if (DO_DX) { k_n = __ldg(min_k + b0 * n_detectors + det_l); m_n = __ldg(min_delta + b0 * n_detectors + det_l); }
+    }
+    if (valid) gp_n = __ldg(dY + b0 * n_outputs + my_target);
+    for (int64_t b = b0; b < b1; b++) {
+        const int32_t li = li_n, my_k = k_n;
+        const float my_m = m_n, gp = gp_n;
+        if (b + 1 < b1) {
+            if (has_det) {
+                li_n = __ldg(idx + (b + 1) * n_detectors + det_l);
+                if (DO_DX) { k_n = __ldg(min_k + (b + 1) * n_detectors + det_l); m_n = __ldg(min_delta + (b + 1) * n_detectors + det_l); }
+            }
+            if (valid) gp_n = __ldg(dY + (b + 1) * n_outputs + my_target);
+        }
+        const int32_t row_off = has_det ? lane * cs.table + li * cs.stride : 0;
+        // alternative row: minimum-margin bit flipped
+        const int32_t alt_off = (DO_DX && has_det) ? row_off + ((li ^ (1 << my_k)) - li) * cs.stride : 0;
+        float val = 0.f;
+        int32_t ival = 0;
+        bool active = false;
+        if (DO_DW && valid && fabs((double)gp) > kEps) {
+            active = true;
+            if (INT_DW) ival = to_fixed((double)gp * lr, fixed_scale);
+            else val = (float)((double)gp * lr);
+        }
+        float v[LG];
+#pragma unroll
+        for (int i = 0; i < LG; i++) {
+            const int d = i * NG + g;
+            const int32_t ro = __shfl_sync(0xffffffffu, row_off, d);
+            if (DO_DX) {
+                const int32_t ao = __shfl_sync(0xffffffffu, alt_off, d);
+                // detectors beyond the chunk have ro == ao == 0: the difference is exactly zero
+                v[i] = valid ? gp * (__ldg(Wb + ro) - __ldg(Wb + ao)) : 0.f;
+            }
+            if (DO_DW && active && d < cs.ndet) {
+                if (INT_DW) atomicAdd(reinterpret_cast<int32_t *>(Tb) + ro, ival);
+                else atomicAdd(Tb + ro, val);
+            }
+        }
+        if (!DO_DX) continue;
+        // transpose-reduce: after the stage with offset o a lane keeps the half of the values whose
+        // index bit matches its own lane bit, summed with the partner lane's copy
+#pragma unroll
+        for (int o = LG / 2; o >= 1; o >>= 1) {
+            const bool upper = (j & o) != 0;
+#pragma unroll
+            for (int i = 0; i < o; i++) {
+                const float send = upper ? v[i] : v[i + o];
+                const float keep = upper ? v[i + o] : v[i];
+                v[i] = keep + __shfl_xor_sync(0xffffffffu, send, o);
+            }
+        }
+        const int32_t k = __shfl_sync(0xffffffffu, my_k, own);
+        const float m = __shfl_sync(0xffffffffu, my_m, own);
+        if (own < cs.ndet) {
+            const double du = surrogate_up(m) * (double)v[0];
+            if (fabs(du) > kEps) {
+                const int2 a = __ldg(anchors + (size_t)(cs.det0 + own) * n_anchors + k);
+                float *dxb = dX + b * n_inputs;
+                atomicAdd(dxb + a.x, (float)du);
+                atomicAdd(dxb + a.y, -(float)du);
+            }
+        }
+    }
+}
+
+template <bool DO_DX, bool DO_DW, bool INT_DW>
+__global__ void __launch_bounds__(256) sparse_backward_kernel(SparseView sp, const float *__restrict__ W,
+                                                             const float *__restrict__ dY,
+                                                             const int2 *__restrict__ anchors,
+                                                             const int32_t *__restrict__ idx,
+                                                             const float *__restrict__ min_delta,
+                                                             const int32_t *__restrict__ min_k,
+                                                             float *__restrict__ dX, float *__restrict__ target_arr,
+                                                             int64_t batch, int n_inputs, int n_outputs,
+                                                             int n_detectors, int n_anchors, double lr,
+                                                             double fixed_scale) {
+    const int lane = threadIdx.x & 31;
+    const int64_t runs = (batch + kSampleRun - 1) / kSampleRun;
+    const int64_t work = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (work >= runs * sp.n_chunks) return;
+    const int64_t c = work / runs;
+    const int64_t b0 = (work - c * runs) * kSampleRun;
+    const int64_t b1 = min(batch, b0 + kSampleRun);
+    const ChunkStatic cs = load_chunk(sp, c);
+    if (cs.P <= 8)
+        chunk_backward<8, DO_DX, DO_DW, INT_DW>(sp, cs, W, dY, anchors, idx, min_delta, min_k, dX, target_arr, b0, b1, n_inputs, n_outputs, n_detectors, n_anchors, lane, lr, fixed_scale);
+    else if (cs.P <= 16)
+        chunk_backward<16, DO_DX, DO_DW, INT_DW>(sp, cs, W, dY, anchors, idx, min_delta, min_k, dX, target_arr, b0, b1, n_inputs, n_outputs, n_detectors, n_anchors, lane, lr, fixed_scale);
+    else
+        chunk_backward<32, DO_DX, DO_DW, INT_DW>(sp, cs, W, dY, anchors, idx, min_delta, min_k, dX, target_arr, b0, b1, n_inputs, n_outputs, n_detectors, n_anchors, lane, lr, fixed_scale);
+}
+
+// Generic fp32 backward for rows longer than 32 synapses: one warp per (sample, detector).
+template <bool DO_DX, bool DO_DW, bool INT_DW>
+__global__ void __launch_bounds__(256) sparse_backward_long_kernel(SparseView sp, const float *__restrict__ W,
+                                                                  const float *__restrict__ dY,
+                                                                  const int2 *__restrict__ anchors,
+                                                                  const int32_t *__restrict__ idx,
+                                                                  const float *__restrict__ min_delta,
+                                                                  const int32_t *__restrict__ min_k,
+                                                                  float *__restrict__ dX,
+                                                                  float *__restrict__ target_arr, int64_t batch,
+                                                                  int n_inputs, int n_outputs, int n_detectors,
+                                                                  int n_anchors, double lr, double fixed_scale) {
     const int lane = threadIdx.x & 31;
     const int64_t work = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (work >= batch * n_detectors) return;
-    const int64_t b = work / n_detectors;
-    const int t = (int)(work - b * n_detectors);
-    const int32_t li = __ldg(idx + work);
-    const int32_t k = __ldg(min_k + work);
+    const int t = (int)(work / batch);
+    const int64_t b = work - (int64_t)t * batch;
+    const int64_t bt = b * n_detectors + t;
+    const int32_t li = __ldg(idx + bt);
+    const int32_t k = DO_DX ? __ldg(min_k + bt) : 0;
     const int P = __ldg(sp.det_count + t);
     const int64_t wbase = __ldg(sp.det_wbase + t);
     const int stride = __ldg(sp.det_stride + t);
     const int32_t *tg = sp.syn_target + __ldg(sp.det_sstart + t);
-    const float *row = W + wbase + (int64_t)li * stride;
-    const float *alt = W + wbase + (int64_t)(li ^ (1 << k)) * stride;
+    const int64_t row = wbase + (int64_t)li * stride;
+    const int64_t alt = wbase + (int64_t)(li ^ (1 << k)) * stride;
     const float *dy = dY + b * n_outputs;
     double acc = 0.0;
     for (int p = lane; p < P; p += 32) {
         const int q = p + hole_offset(p, sp);
-        acc += (double)__ldg(dy + __ldg(tg + p)) * ((double)__ldg(row + q) - (double)__ldg(alt + q));
+        const double gd = (double)__ldg(dy + __ldg(tg + p));
+        if (DO_DX) acc += gd * ((double)__ldg(W + row + q) - (double)__ldg(W + alt + q));
+        if (DO_DW && fabs(gd) > kEps) {
+            if (INT_DW) atomicAdd(reinterpret_cast<int32_t *>(target_arr) + row + q, to_fixed(gd * lr, fixed_scale));
+            else atomicAdd(target_arr + row + q, (float)(gd * lr));
+        }
     }
+    if (!DO_DX) return;
     for (int off = 16; off >= 1; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
     if (lane == 0) {
-        const double du = surrogate_up(__ldg(min_delta + work)) * acc;
+        const double du = surrogate_up(__ldg(min_delta + bt)) * acc;
         if (fabs(du) > kEps) {
             const int2 a = __ldg(anchors + (size_t)t * n_anchors + k);
             atomicAdd(dX + b * n_inputs + a.x, (float)du);
@@ -258,55 +358,6 @@ __global__ void sparse_input_grad_fixed_kernel(SparseView sp, const float *__res
     }
 }
 
-// --------------------------------------------------------------------------------------------
-// Table gradient: target[row(t, idx[b, t]) + p] += lr * dY[b, target(p)] for |dY| > EPS
-// (reference: gather_w_gradients_non_seq_sparse_logic, proto:1501-1545, helper :584-714).
-// The value a lane adds is the same for all detectors of the chunk; every detector's row receives one
-// contiguous run of reductions.
-// --------------------------------------------------------------------------------------------
-template <bool INT_MODE>
-__global__ void __launch_bounds__(256) sparse_weight_grad_kernel(SparseView sp, const float *__restrict__ dY,
-                                                                const int32_t *__restrict__ idx,
-                                                                float *__restrict__ target_arr, int64_t batch,
-                                                                int n_outputs, int n_detectors, double lr,
-                                                                double fixed_scale) {
-    const int lane = threadIdx.x & 31;
-    const int64_t work = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (work >= batch * sp.n_chunks) return;
-    const int64_t b = work / sp.n_chunks;
-    const int64_t c = work - b * sp.n_chunks;
-    const ChunkLane ch = load_chunk(sp, idx + b * n_detectors, c, lane, nullptr);
-    int LG = 32;
-    while (LG > 4 && (LG >> 1) >= ch.P) LG >>= 1;
-    const int NG = 32 / LG;
-    const int g = lane / LG, j = lane - g * LG;
-    float *Tb = target_arr + ch.wbase0;
-    const int32_t *tg = sp.syn_target + ch.toff;
-    for (int p0 = 0; p0 < ch.P; p0 += LG) {
-        const int p = p0 + j;
-        const int q = p + hole_offset(p, sp);
-        float val = 0.f;
-        int32_t ival = 0;
-        bool active = false;
-        if (p < ch.P) {
-            const double gd = (double)__ldg(dY + b * n_outputs + __ldg(tg + p));
-            if (fabs(gd) > kEps) {
-                active = true;
-                if (INT_MODE) ival = to_fixed(gd * lr, fixed_scale);
-                else val = (float)(gd * lr);
-            }
-        }
-        for (int d0 = 0; d0 < ch.ndet; d0 += NG) {
-            const int d = d0 + g;
-            const int32_t off = __shfl_sync(0xffffffffu, ch.row_off, d & 31);
-            if (active && d < ch.ndet) {
-                if (INT_MODE) atomicAdd(reinterpret_cast<int32_t *>(Tb) + (int64_t)off + q, ival);
-                else atomicAdd(Tb + (int64_t)off + q, val);
-            }
-        }
-    }
-}
-
 static SparseView make_view(const lutb_sparse_index *sp) {
     SparseView v;
     v.det_wbase = sp->det_wbase; v.det_stride = sp->det_stride; v.det_count = sp->det_count;
@@ -325,8 +376,8 @@ static int validate_sparse(const lutb_sparse_index *sp) {
     LUTB_REQUIRE(sp->group_size > 0 && sp->n_syn_per_sample > 0 && sp->n_weights > 0 && sp->max_count > 0 &&
                      sp->n_chunks > 0,
                  LUTB_ERR_SHAPE, "empty sparse index");
-    LUTB_REQUIRE((reinterpret_cast<uintptr_t>(sp->chunk_info) & 15) == 0, LUTB_ERR_ALIGN,
-                 "chunk_info must be 16-byte aligned");
+    LUTB_REQUIRE((reinterpret_cast<uintptr_t>(sp->chunk_info) & 31) == 0, LUTB_ERR_ALIGN,
+                 "chunk_info must be 32-byte aligned");
     return LUTB_OK;
 }
 
@@ -359,7 +410,7 @@ extern "C" int lutb_nonseq_sparse_forward(const lutb_layer_cfg *cfg, const lutb_
     if (rc) return rc;
     SparseView v = make_view(sp);
     unsigned blocks;
-    rc = chunk_grid(batch * sp->n_chunks, &blocks);
+    rc = chunk_grid(((batch + kSampleRun - 1) / kSampleRun) * sp->n_chunks, &blocks);
     if (rc) return rc;
     {
         KernelScope scope(K_SPARSE_FORWARD, st);
@@ -392,47 +443,50 @@ extern "C" int lutb_nonseq_sparse_backward(const lutb_layer_cfg *cfg, const lutb
     const int sm = device_info().sm_count;
     SparseView v = make_view(sp);
     const int O = cfg->n_outputs, Nt = cfg->n_detectors;
-    {
-        KernelScope scope(K_SPARSE_INPUT_GRAD, st);
-        if (cfg->int_mode) {
-            const int64_t total = batch * Nt;
-            const int64_t blocks = min((total + 127) / 128, (int64_t)sm * 64);
-            sparse_input_grad_fixed_kernel<<<(unsigned)blocks, 128, 0, st>>>(
-                v, weights, dY, reinterpret_cast<const int2 *>(anchors), idx, min_delta, min_k, dX, batch,
-                cfg->n_inputs, O, Nt, cfg->n_anchors, cfg->int_rescaler);
-        } else if (sp->max_count > 32) {
-            unsigned blocks;
-            rc = chunk_grid(batch * Nt, &blocks);
-            if (rc) return rc;
-            sparse_input_grad_long_kernel<<<blocks, 256, 0, st>>>(v, weights, dY, reinterpret_cast<const int2 *>(anchors), idx,
-                                                                 min_delta, min_k, dX, batch, cfg->n_inputs, O, Nt, cfg->n_anchors);
-        } else {
-            unsigned blocks;
-            rc = chunk_grid(batch * sp->n_chunks, &blocks);
-            if (rc) return rc;
-            const int2 *an = reinterpret_cast<const int2 *>(anchors);
-            if (sp->max_count > 16)
-                sparse_input_grad_kernel<32><<<blocks, 256, 0, st>>>(v, weights, dY, an, idx, min_delta, min_k, dX, batch, cfg->n_inputs, O, Nt, cfg->n_anchors);
-            else if (sp->max_count > 8)
-                sparse_input_grad_kernel<16><<<blocks, 256, 0, st>>>(v, weights, dY, an, idx, min_delta, min_k, dX, batch, cfg->n_inputs, O, Nt, cfg->n_anchors);
-            else
-                sparse_input_grad_kernel<8><<<blocks, 256, 0, st>>>(v, weights, dY, an, idx, min_delta, min_k, dX, batch, cfg->n_inputs, O, Nt, cfg->n_anchors);
-        }
-    }
-    LUTB_LAUNCH_CHECK();
+    const int2 *an = reinterpret_cast<const int2 *>(anchors);
     double lr = cfg->lr_meta;
     if (external_lr >= 0.0) lr *= -(double)(float)external_lr;
     float *target = external_lr >= 0.0 ? weights : dW;
-    {
-        unsigned blocks;
-        rc = chunk_grid(batch * sp->n_chunks, &blocks);
-        if (rc) return rc;
-        KernelScope scope(K_SPARSE_WEIGHT_GRAD, st);
-        if (cfg->int_mode)
-            sparse_weight_grad_kernel<true><<<blocks, 256, 0, st>>>(v, dY, idx, target, batch, O, Nt, lr, cfg->int_rescaler);
-        else
-            sparse_weight_grad_kernel<false><<<blocks, 256, 0, st>>>(v, dY, idx, target, batch, O, Nt, lr, cfg->int_rescaler);
+    const bool long_rows = sp->max_count > 32;
+    unsigned blocks;
+    rc = chunk_grid(long_rows ? batch * (int64_t)Nt : ((batch + kSampleRun - 1) / kSampleRun) * sp->n_chunks, &blocks);
+    if (rc) return rc;
+#define LUTB_SPARSE_BWD(DX, DWF, INTF)                                                                              \
+    do {                                                                                                            \
+        if (long_rows)                                                                                              \
+            sparse_backward_long_kernel<DX, DWF, INTF><<<blocks, 256, 0, st>>>(v, weights, dY, an, idx, min_delta, min_k, dX, target, batch, cfg->n_inputs, O, Nt, cfg->n_anchors, lr, cfg->int_rescaler); \
+        else                                                                                                        \
+            sparse_backward_kernel<DX, DWF, INTF><<<blocks, 256, 0, st>>>(v, weights, dY, an, idx, min_delta, min_k, dX, target, batch, cfg->n_inputs, O, Nt, cfg->n_anchors, lr, cfg->int_rescaler); \
+    } while (0)
+    if (cfg->int_mode) {
+        {
+            KernelScope scope(K_SPARSE_INPUT_GRAD, st);
+            const int64_t total = batch * Nt;
+            const int64_t gblocks = min((total + 127) / 128, (int64_t)sm * 64);
+            sparse_input_grad_fixed_kernel<<<(unsigned)gblocks, 128, 0, st>>>(v, weights, dY, an, idx, min_delta, min_k, dX, batch,
+                                                                            cfg->n_inputs, O, Nt, cfg->n_anchors, cfg->int_rescaler);
+        }
+        LUTB_LAUNCH_CHECK();
+        {
+            KernelScope scope(K_SPARSE_WEIGHT_GRAD, st);
+            LUTB_SPARSE_BWD(false, true, true);
+        }
+    } else if (external_lr >= 0.0) {
+        // in-place SGD: every sample must read the weights before any of them is modified
+        {
+            KernelScope scope(K_SPARSE_INPUT_GRAD, st);
+            LUTB_SPARSE_BWD(true, false, false);
+        }
+        LUTB_LAUNCH_CHECK();
+        {
+            KernelScope scope(K_SPARSE_WEIGHT_GRAD, st);
+            LUTB_SPARSE_BWD(false, true, false);
+        }
+    } else {
+        KernelScope scope(K_SPARSE_BACKWARD_FUSED, st);
+        LUTB_SPARSE_BWD(true, true, false);
     }
+#undef LUTB_SPARSE_BWD
     LUTB_LAUNCH_CHECK();
     if (cfg->int_mode) {
         rc = launch_fixed_to_float(dX, batch * (int64_t)cfg->n_inputs, cfg->int_rescaler, st);

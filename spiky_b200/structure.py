@@ -223,21 +223,25 @@ class SparseIndex:
     CHUNK = 32  # detectors per chunk = lanes of a warp
 
     def _build_chunks(self):
-        """int32 [n_chunks, 4] = (first detector, detector count <= 32, offset of the shared target list in
-        syn_target, synapses per row).  A chunk is a run of consecutive detectors with identical target
-        lists (the detectors of one group); the kernels give one warp to each (sample, chunk)."""
+        """int32 [n_chunks, 8] = (first detector, detector count <= 32, offset of the shared target list in
+        syn_target, synapses per row, row stride, slots per detector table, wbase0 low word, wbase0 high word).
+        A chunk is a run of consecutive detectors with identical target lists (the detectors of one group)
+        whose tables lie back to back in the weight array; the kernels give one warp to each (sample, chunk)."""
         counts = self.det_count.to(torch.int64).cpu()
         starts = self.det_sstart.to(torch.int64).cpu()
         tgt = self.syn_target.cpu()
         n = counts.numel()
-        same = torch.zeros(n, dtype=torch.bool)  # same[t]: detector t repeats the target list of t-1
+        same = torch.zeros(n, dtype=torch.bool)  # same[t]: detector t continues the chunk of detector t-1
         if n > 1:
             pmax = int(counts.max().item())
             lists = torch.full((n, max(pmax, 1)), -1, dtype=torch.int32)
             det = torch.repeat_interleave(torch.arange(n), counts)
             pos = torch.arange(tgt.numel()) - starts[det]
             lists[det, pos] = tgt
-            same[1:] = (lists[1:] == lists[:-1]).all(dim=1) & (counts[1:] > 0)
+            wbase = self.det_wbase.cpu()
+            stride = self.det_stride.to(torch.int64).cpu()
+            contiguous = wbase[1:] == wbase[:-1] + stride[:-1] * self.rows_per_detector
+            same[1:] = (lists[1:] == lists[:-1]).all(dim=1) & (counts[1:] > 0) & contiguous
         chunks = []
         t = 0
         same_l = same.tolist()
@@ -250,11 +254,14 @@ class SparseIndex:
             while end < n and end - t < self.CHUNK and same_l[end]:
                 end += 1
             if counts_l[t] > 0:
-                span = wbase_l[end - 1] + stride_l[end - 1] * self.rows_per_detector - wbase_l[t]
-                assert span < (1 << 31), "tables of one detector chunk span more than 2^31 weight slots"
-                chunks.append((t, end - t, starts_l[t], counts_l[t]))
+                table = stride_l[t] * self.rows_per_detector
+                assert table * (end - t) < (1 << 31), "tables of one detector chunk span more than 2^31 weight slots"
+                chunks.append((t, end - t, starts_l[t], counts_l[t], stride_l[t], table,
+                               wbase_l[t] & 0xFFFFFFFF, wbase_l[t] >> 32))
             t = end
-        return torch.tensor(chunks, dtype=torch.int32).reshape(-1, 4).contiguous()
+        out = torch.tensor(chunks, dtype=torch.int64).reshape(-1, 8)
+        out = torch.where(out >= (1 << 31), out - (1 << 32), out)  # low words above 2^31 wrap into int32
+        return out.to(torch.int32).contiguous()
 
     _TENSORS = ("det_wbase", "det_stride", "det_count", "det_sstart", "syn_det", "syn_target", "chunk_info")
 
