@@ -339,3 +339,173 @@ void orc_nonseq_sparse_backward(float *W, const float *dY, const int32_t *anchor
         if (dW) orc_int_to_float(dW, n_weights, rescaler);
     }
 }
+
+/* ------------------------------------------------------------------------------------------
+ * Product-mode sequence layers: the table index is computed per causal pair (i < j) from the
+ * virtual vector [x1[b,i,:] | x2[b,j,:] | pe[j-i-1, t, :]] (sliced mode: interleaved, anchor id =
+ * 3 * slot + component) with the non-sequence rule, tables have 2^Nc rows.
+ * ------------------------------------------------------------------------------------------ */
+typedef struct {
+    int comp;   /* 0: x1 at position i, 1: x2 at position j, 2: positional embedding */
+    int index;  /* element inside that source */
+} orc_src;
+
+/* anchor id -> (source, element), proto:60-66 (sliced) and :82-88 (sequential layout) */
+static inline orc_src orc_product_src(int32_t id, int sliced, int E1, int E2) {
+    orc_src s;
+    if (sliced) {
+        s.index = id / 3;
+        s.comp = id % 3;
+    } else {
+        s.comp = id < E1 ? 0 : (id < E1 + E2 ? 1 : 2);
+        s.index = id - (s.comp == 0 ? 0 : (s.comp == 1 ? E1 : E1 + E2));
+    }
+    return s;
+}
+
+/* calculate_product_lookup_index_backprop, proto:102-198 (the forward-only variant :32-100 computes
+ * the same index: val1 > val2 and (val1 - val2) > 0 agree in IEEE arithmetic with denormals kept).
+ * Returns the index; *alt, the two flipped sources and the minimal delta are optional outputs. */
+static inline int32_t orc_product_index(const int32_t *ap, int Nc, int sliced, int E1, int E2, const float *v1,
+                                        const float *v2, const float *pe, float cmp_eps, int32_t *alt,
+                                        orc_src *first, orc_src *second, float *min_delta) {
+    const float *src[3] = {v1, v2, pe};
+    int32_t li = 0;
+    float md = 3.402823466e+38F;
+    int flip = -1;
+    orc_src f1 = {-1, -1}, f2 = {-1, -1};
+    for (int k = 0; k < Nc; k++) {
+        int32_t a1 = ap[2 * k], a2 = ap[2 * k + 1];
+        if (a1 == ORC_NO_ANCHOR || a2 == ORC_NO_ANCHOR) continue;
+        orc_src s1 = orc_product_src(a1, sliced, E1, E2), s2 = orc_product_src(a2, sliced, E1, E2);
+        float delta = src[s1.comp][s1.index] - src[s2.comp][s2.index];
+        if (orc_greater(delta, cmp_eps)) li |= (1 << k);
+        if (fabsf(delta) < fabsf(md)) {
+            md = delta;
+            flip = k;
+            f1 = s1;
+            f2 = s2;
+        }
+    }
+    if (alt) *alt = flip >= 0 ? (li ^ (1 << flip)) : li;
+    if (first) *first = f1;
+    if (second) *second = f2;
+    if (min_delta) *min_delta = md;
+    return li;
+}
+
+/* fill_outputs_product_cpu_logic, proto:2148-2264 (fully connected branch) */
+void orc_product_forward(const float *W, const float *x1, const float *x2, const float *pe, const int32_t *anchors,
+                         float *y, int64_t B, int S, int E1, int E2, int Npe, int O, int Nt, int Nc, int sliced,
+                         float cmp_eps, int int_mode, double rescaler) {
+    int T = 1 << Nc;
+    ORC_PARALLEL_FOR
+    for (int64_t b = 0; b < B; b++) {
+        for (int j = 0; j < S; j++) {
+            float *yo = y + (b * S + j) * O;
+            for (int t = 0; t < Nt; t++) {
+                const int32_t *ap = anchors + (int64_t)t * Nc * 2;
+                for (int i = 0; i < j; i++) {
+                    const float *p = Npe > 0 ? pe + ((int64_t)(j - i - 1) * Nt + t) * Npe : NULL;
+                    int32_t li = orc_product_index(ap, Nc, sliced, E1, E2, x1 + (b * S + i) * E1, x2 + (b * S + j) * E2, p,
+                                                   cmp_eps, NULL, NULL, NULL, NULL);
+                    const float *row = W + ((int64_t)t * T + li) * O;
+                    for (int o = 0; o < O; o++) {
+                        double w = (double)row[o];
+                        if (int_mode)
+                            *(int32_t *)(yo + o) += (int32_t)(w * ORC_DENOM * rescaler);
+                        else
+                            yo[o] += (float)w;
+                    }
+                }
+            }
+        }
+    }
+    if (int_mode) orc_int_to_float(y, B * S * O, rescaler);
+}
+
+static inline void orc_route(orc_src s, double du, float *dX1, float *dX2, float *dPE, int64_t b, int S, int i, int j,
+                             int E1, int E2, int Npe, int Nt, int t, int int_mode, double rescaler) {
+    float *cell;
+    if (s.comp == 0) cell = dX1 + (b * S + i) * E1 + s.index;
+    else if (s.comp == 1) cell = dX2 + (b * S + j) * E2 + s.index;
+    else if (s.comp == 2) cell = dPE + ((int64_t)(j - i - 1) * Nt + t) * Npe + s.index;
+    else return;
+    if (int_mode) *(int32_t *)cell += (int32_t)(du * ORC_DENOM * rescaler);
+    else *cell += (float)du;
+}
+
+/*
+ * propagate_backward_product_cpu_logic (proto:2396-2628, helper propagate_through_detector_product :869-1014)
+ * and, for the internal policy, gather_w_gradients_internal_product_cpu_logic (proto:2630-2744).
+ * dX1 / dX2 may alias (the layer passes the same buffer twice).  Not thread-parallel over samples when
+ * dPE is given (dPE is shared by the batch), to keep the reference's accumulation order.
+ */
+void orc_product_backward(float *W, const float *x1, const float *x2, const float *pe, const int32_t *anchors,
+                          const float *dY, float *dX1, float *dX2, float *dPE, float *dW, int64_t B, int S, int E1,
+                          int E2, int Npe, int O, int Nt, int Nc, int sliced, float cmp_eps, double lr_meta,
+                          double ext_lr, int int_mode, double rescaler) {
+    int T = 1 << Nc;
+    for (int64_t b = 0; b < B; b++) {
+        for (int j = 0; j < S; j++) {
+            const float *dy = dY + (b * S + j) * O;
+            for (int t = 0; t < Nt; t++) {
+                const int32_t *ap = anchors + (int64_t)t * Nc * 2;
+                for (int i = 0; i < j; i++) {
+                    const float *p = Npe > 0 ? pe + ((int64_t)(j - i - 1) * Nt + t) * Npe : NULL;
+                    int32_t alt_li;
+                    orc_src f1, f2;
+                    float md;
+                    int32_t li = orc_product_index(ap, Nc, sliced, E1, E2, x1 + (b * S + i) * E1, x2 + (b * S + j) * E2, p,
+                                                   cmp_eps, &alt_li, &f1, &f2, &md);
+                    const float *row = W + ((int64_t)t * T + li) * O;
+                    const float *alt = W + ((int64_t)t * T + alt_li) * O;
+                    double ms = 0.0, as = 0.0;
+                    for (int o = 0; o < O; o++) ms += (double)row[o] * (double)dy[o];
+                    for (int o = 0; o < O; o++) as += (double)alt[o] * (double)dy[o];
+                    double du = orc_up(md) * (ms - as);
+                    if (fabs(du) > ORC_EPS) {
+                        orc_route(f1, du, dX1, dX2, dPE, b, S, i, j, E1, E2, Npe, Nt, t, int_mode, rescaler);
+                        orc_route(f2, -du, dX1, dX2, dPE, b, S, i, j, E1, E2, Npe, Nt, t, int_mode, rescaler);
+                    }
+                    if (dW) {
+                        float *drow = dW + ((int64_t)t * T + li) * O;
+                        for (int o = 0; o < O; o++) {
+                            double g = (double)dy[o];
+                            if (fabs(g) > ORC_EPS) {
+                                if (int_mode) *(int32_t *)(drow + o) += (int32_t)(g * lr_meta * ORC_DENOM * rescaler);
+                                else drow[o] += (float)(g * lr_meta);
+                            }
+                        }
+                    }
+                }
+            }
+        }
+    }
+    if (ext_lr >= 0) {
+        double lr = lr_meta * -ext_lr;
+        for (int64_t b = 0; b < B; b++)
+            for (int j = 0; j < S; j++) {
+                const float *dy = dY + (b * S + j) * O;
+                for (int t = 0; t < Nt; t++) {
+                    const int32_t *ap = anchors + (int64_t)t * Nc * 2;
+                    for (int i = 0; i < j; i++) {
+                        const float *p = Npe > 0 ? pe + ((int64_t)(j - i - 1) * Nt + t) * Npe : NULL;
+                        int32_t li = orc_product_index(ap, Nc, sliced, E1, E2, x1 + (b * S + i) * E1, x2 + (b * S + j) * E2,
+                                                       p, cmp_eps, NULL, NULL, NULL, NULL);
+                        float *wrow = W + ((int64_t)t * T + li) * O;
+                        for (int o = 0; o < O; o++) {
+                            double g = (double)dy[o];
+                            if (fabs(g) > ORC_EPS) wrow[o] += (float)(g * lr);
+                        }
+                    }
+                }
+            }
+    }
+    if (int_mode) {
+        orc_int_to_float(dX1, B * S * (int64_t)E1, rescaler);
+        if (dX2 != dX1) orc_int_to_float(dX2, B * S * (int64_t)E2, rescaler);
+        if (dW) orc_int_to_float(dW, (int64_t)Nt * T * O, rescaler);
+        if (Npe > 0 && dPE) orc_int_to_float(dPE, (int64_t)(S - 1) * Nt * Npe, rescaler);
+    }
+}

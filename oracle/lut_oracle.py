@@ -175,3 +175,42 @@ def nonseq_sparse_backward(W, dY, anchors, idx, min_delta, min_k, sp, n_inputs, 
                                      _d(float(np.float32(lr_meta))), _d(float(np.float32(external_lr))),
                                      _i(int(int_mode)), _d(int_rescaler))
     return dX, dW
+
+
+def product_forward(W, x, pe, anchors, n_detectors, n_anchors, n_outputs, pos_dim, sliced=False, cmp_eps=0.0,
+                    int_mode=False, int_rescaler=0.001):
+    """One ``forward_step_product``: x [B,S,E] is used for both pair members (as the layer does),
+    pe [(S-1), Nt, Npe] (already repeated over detectors for unified embeddings) or None."""
+    x = _f32(x)
+    B, S, E = x.shape
+    W = _f32(W).reshape(-1)
+    y = np.zeros((B, S, n_outputs), np.float32)
+    pe_f = None if pe is None else _f32(pe).reshape(-1)
+    lib().orc_product_forward(_ptr(W), _ptr(x), _ptr(x), _ptr(pe_f), _ptr(_i32(anchors).reshape(-1)), _ptr(y),
+                              _l(B), _i(S), _i(E), _i(E), _i(pos_dim), _i(n_outputs), _i(n_detectors),
+                              _i(n_anchors), _i(int(sliced)), _f(cmp_eps), _i(int(int_mode)), _d(int_rescaler))
+    return y
+
+
+def product_backward(W, x, pe, anchors, dY, n_detectors, n_anchors, pos_dim, sliced=False, cmp_eps=0.0,
+                     lr_meta=1.0, external_lr=-1.0, int_mode=False, int_rescaler=0.001):
+    """One ``backward_backprop_product``; returns (dX [B,S,E], dW or None, dPE or None)."""
+    x = _f32(x)
+    dY = _f32(dY)
+    B, S, E = x.shape
+    O = dY.shape[-1]
+    if external_lr >= 0:
+        assert W.dtype == np.float32 and W.flags["C_CONTIGUOUS"] and W.flags["WRITEABLE"]
+        Wf, dW = W.reshape(-1), None
+    else:
+        Wf = _f32(W).reshape(-1)
+        dW = np.zeros(Wf.size, np.float32)
+    dX = np.zeros((B, S, E), np.float32)
+    pe_f = None if pe is None else _f32(pe).reshape(-1)
+    dPE = None if pe is None else np.zeros(pe_f.size, np.float32)
+    lib().orc_product_backward(_ptr(Wf), _ptr(x), _ptr(x), _ptr(pe_f), _ptr(_i32(anchors).reshape(-1)), _ptr(dY),
+                               _ptr(dX), _ptr(dX), _ptr(dPE), _ptr(dW), _l(B), _i(S), _i(E), _i(E), _i(pos_dim),
+                               _i(O), _i(n_detectors), _i(n_anchors), _i(int(sliced)), _f(cmp_eps),
+                               _d(float(np.float32(lr_meta))), _d(float(np.float32(external_lr))),
+                               _i(int(int_mode)), _d(int_rescaler))
+    return dX, dW, dPE

@@ -85,3 +85,36 @@ PROJECTION_CASES = {
     "proj_internal": dict(seed=206, B=7, in_shape=(12, 12), out_shape=(8, 8), Nc=3, groups=6, per_group=3,
                           receptive=(5, 5), projection=(3, 3), policy="internal", ext_lr=0.5, lr_meta=0.25),
 }
+
+
+def sequence_inputs(cfg, n_weights, n_pe):
+    """Inputs of a sequence-layer case (product or concatenation mode): x [B,S,E], anchors over the
+    layer's (virtual) input vector, tables, positional embeddings (flat, as the layer stores them), dY."""
+    s = cfg["seed"]
+    B, S, E, Nt, Nc, O = cfg["B"], cfg["S"], cfg["E"], cfg["Nt"], cfg["Nc"], cfg["O"]
+    x = synth.uniform(s + 31, (B, S, E), -1.0, 1.0)
+    if cfg.get("quantized_input"):  # coarse values make exact ties and dead-band hits common
+        x = (x * 4).round().astype("float32") / 4
+    n_virtual = cfg.get("n_virtual", E)
+    anchors = synth.anchor_pairs(s + 32, Nt, Nc, n_virtual)
+    W = synth.normal(s + 33, (n_weights,), 0.0, 0.05)
+    pe = synth.uniform(s + 34, (n_pe,), -1.0, 1.0) if n_pe else None
+    dY = synth.normal(s + 35, (B, S, O))
+    return x, anchors, W, pe, dY
+
+
+PRODUCT_CASES = {
+    "prod_plain_f32": dict(seed=300, B=3, S=6, E=7, Nt=4, Nc=3, Npe=2, O=5),
+    "prod_plain_i32": dict(seed=301, B=3, S=6, E=7, Nt=4, Nc=3, Npe=2, O=5, int_mode=True, int_rescaler=5.0),
+    "prod_sliced_f32": dict(seed=302, B=2, S=7, E=5, Nt=3, Nc=4, Npe=5, O=6, sliced=True, unified_pe=True,
+                            cmp_eps=1e-4, quantized_input=True),
+    "prod_sliced_i32": dict(seed=303, B=2, S=7, E=5, Nt=3, Nc=4, Npe=5, O=6, sliced=True, unified_pe=True,
+                            cmp_eps=1e-4, int_mode=True, int_rescaler=1.0),
+    "prod_nope_f32": dict(seed=304, B=2, S=5, E=6, Nt=3, Nc=3, Npe=0, O=4),
+    "prod_internal": dict(seed=305, B=2, S=6, E=6, Nt=3, Nc=3, Npe=3, O=7, policy="internal", ext_lr=0.5,
+                          lr_meta=0.5),
+    "prod_wide_f32": dict(seed=306, B=2, S=9, E=12, Nt=5, Nc=4, Npe=4, O=40, unified_pe=True),
+    "prod_wide_i32": dict(seed=307, B=2, S=9, E=12, Nt=5, Nc=4, Npe=4, O=40, int_mode=True, int_rescaler=0.5),
+}
+for _c in PRODUCT_CASES.values():
+    _c["n_virtual"] = 3 * _c["E"] if _c.get("sliced") else 2 * _c["E"] + _c["Npe"]

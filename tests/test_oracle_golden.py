@@ -104,3 +104,40 @@ def test_own_sparse_construction_is_self_consistent():
     assert sp.n_weights == 28 + 16 + 32 - 2 and sp.n_synapses == (3 + 2 + 4) * 4
     assert sp.syn_target.tolist() == [3, 4, 9, 0, 1, 5, 6, 7, 8] and sp.max_groups_per_neuron == 2
     assert int(sp.slot_mask().sum()) == sp.n_synapses
+
+
+def expand_pe(cfg, pe):
+    """Flat layer embeddings -> [(S-1), Nt, Npe] as the runtime sees them (unified ones repeated per detector)."""
+    if pe is None:
+        return None
+    S, Nt, Npe = cfg["S"], cfg["Nt"], cfg["Npe"]
+    if cfg.get("unified_pe"):
+        return np.repeat(pe.reshape(S - 1, 1, Npe), Nt, axis=1).copy()
+    return pe.reshape(S - 1, Nt, Npe)
+
+
+@pytest.mark.parametrize("name", golden_util.names("prod_"))
+def test_product_oracle_matches_reference(name):
+    from cases import sequence_inputs
+
+    cfg, ref = golden_util.load(name)
+    S, Nt, Nc, O, Npe = cfg["S"], cfg["Nt"], cfg["Nc"], cfg["O"], cfg["Npe"]
+    n_pe = (S - 1) * (1 if cfg.get("unified_pe") else Nt) * Npe
+    x, anchors, W, pe, dY = sequence_inputs(cfg, Nt * (1 << Nc) * O, n_pe)
+    assert np.array_equal(x, ref["in_x"]) and np.array_equal(anchors, ref["in_anchors"])
+    pe3 = expand_pe(cfg, pe)
+    kw = dict(sliced=cfg.get("sliced", False), cmp_eps=cfg.get("cmp_eps", 0.0), int_mode=cfg.get("int_mode", False),
+              int_rescaler=cfg.get("int_rescaler", 0.001))
+    y = orc.product_forward(W, x, pe3, anchors, Nt, Nc, O, Npe, **kw)
+    assert np.array_equal(y, ref["y"])
+    internal = cfg.get("policy") == "internal"
+    Wb = W.copy()
+    dX, dW, dPE = orc.product_backward(Wb, x, pe3, anchors, dY, Nt, Nc, Npe, lr_meta=cfg.get("lr_meta", 1.0),
+                                       external_lr=cfg["ext_lr"] if internal else -1.0, **kw)
+    assert np.array_equal(dX, ref["dX"])
+    if Npe > 0:
+        assert np.array_equal(dPE, ref["dPE"])
+    if internal:
+        assert np.array_equal(Wb, ref["W_after"])
+    else:
+        assert np.array_equal(dW, ref["dW"])
