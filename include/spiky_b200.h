@@ -150,6 +150,33 @@ int lutb_nonseq_sparse_backward(const lutb_layer_cfg *cfg, const lutb_sparse_ind
                                 const float *min_delta, const int32_t *min_k, float *dX, float *dW,
                                 double external_lr, void *stream);
 
+/*
+ * Product-mode sequence layer, forward.  Replaces LUTDataManager::forward_step_product
+ * (spiky_cuda/lut/lut.cu:847-943 -> LUTRuntimeContext::forward_step_product, lut_runtime.cu:852-1049).
+ * For every causal pair i < j and detector t the table index is computed from
+ * [x1[b,i,:] | x2[b,j,:] | pos_embeddings[j-i-1, t, :]] (cfg->sliced_product: interleaved numbering) and
+ * row (t, index) is added to y[b, j, :].  Tables have 2^Nc rows.
+ *   x1 fp32 [batch * seq_len * n_inputs_1], x2 likewise (the layer passes the same tensor twice)
+ *   pos_embeddings fp32 [(seq_len - 1) * Nt * cfg->pos_dim] or NULL when cfg->pos_dim == 0
+ *   anchors int32 [Nt * Nc * 2] over the virtual vector; y fp32 [batch * seq_len * O], accumulated into
+ * cfg->seq_len and cfg->n_inputs are ignored (the reference builds the manager with sequence_length 1 and
+ * n_inputs = 2 * E + pos_dim and passes the real sizes per call).  batch <= 65535, Nc <= 16.
+ */
+int lutb_product_forward(const lutb_layer_cfg *cfg, int64_t batch, int32_t seq_len, const float *weights,
+                         const float *x1, const float *x2, int32_t n_inputs_1, int32_t n_inputs_2,
+                         const float *pos_embeddings, const int32_t *anchors, float *y, void *stream);
+
+/*
+ * Product-mode sequence layer, backward.  Replaces LUTDataManager::backward_backprop_product
+ * (spiky_cuda/lut/lut.cu:945-1028 -> LUTRuntimeContext::backward_backprop_product, lut_runtime.cu:1051-1463).
+ * Indices are recomputed; dX1 / dX2 (may alias) and dPE are accumulated into; dW / external_lr as in
+ * lutb_nonseq_fc_backward.
+ */
+int lutb_product_backward(const lutb_layer_cfg *cfg, int64_t batch, int32_t seq_len, float *weights, const float *x1,
+                          const float *x2, int32_t n_inputs_1, int32_t n_inputs_2, const float *pos_embeddings,
+                          const int32_t *anchors, const float *dY, float *dX1, float *dX2, float *dPE, float *dW,
+                          double external_lr, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -73,6 +73,7 @@ int launch_fixed_to_float(float *buf, int64_t n, double rescaler, cudaStream_t s
 static const char *const kKernelNames[K_COUNT] = {
     "check_detectors", "fc_gather_forward", "fc_input_grad", "fc_weight_grad", "fixed_to_float",
     "sparse_forward", "sparse_input_grad", "sparse_weight_grad", "sparse_backward_fused",
+    "product_forward", "product_backward", "product_weight_update",
 };
 
 struct EventPair {

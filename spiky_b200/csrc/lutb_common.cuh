@@ -65,6 +65,9 @@ enum KernelId {
     K_SPARSE_INPUT_GRAD,
     K_SPARSE_WEIGHT_GRAD,
     K_SPARSE_BACKWARD_FUSED,
+    K_PRODUCT_FORWARD,
+    K_PRODUCT_BACKWARD,
+    K_PRODUCT_WEIGHT_UPDATE,
     K_COUNT
 };
 

@@ -304,6 +304,82 @@ class _LUTDataManager:
                                            w_input_gradients, external_lr, w_weights_gradients)
         _native.check(rc)
 
+    # ------------------------------------------------------------------ product-mode sequence runtime
+    def forward_step_product(self, r_weights, batch_size, sequence_length, r_input_1, r_input_2, r_detector_anchors,
+                             w_output, n_inputs_1, n_inputs_2, sliced_mode, cmp_eps=0.0, r_positional_embeddings=None,
+                             r_stream_handles=None):
+        self._require_cuda()
+        dev = self._device
+        _check_tensor(r_weights, "r_weights", True, dev)
+        _check_tensor(r_input_1, "r_input_1", True, dev)
+        _check_tensor(r_input_2, "r_input_2", True, dev)
+        _check_tensor(r_detector_anchors, "r_detector_anchors", False, dev)
+        _check_tensor(w_output, "w_output", True, dev)
+        if r_positional_embeddings is not None:
+            _check_tensor(r_positional_embeddings, "r_positional_embeddings", True, dev)
+        if batch_size == 0:
+            raise ValueError("batch_size == 0")
+        if self._seq_len != 1:
+            raise ValueError("forward_step_product: this is an experimental method, this->sequence_length should be "
+                             "equal to 1, real length of the sequence is passed as the method parameter")
+        if sequence_length == 0:
+            raise ValueError("sequence_length == 0")
+        if not self._fully_connected:
+            raise ValueError("product mode is only available for fully connected layers in this backend")
+        B, S = int(batch_size), int(sequence_length)
+        self._expect(r_input_1, B * S * n_inputs_1, "r_input_1")
+        self._expect(r_input_2, B * S * n_inputs_2, "r_input_2")
+        self._expect(w_output, B * S * self._n_outputs, "w_output")
+        self._expect(r_weights, self.get_weights_dimension(), "r_weights")
+        if self._pos_dim > 0:
+            if r_positional_embeddings is None:
+                raise ValueError("r_positional_embeddings is required when positional_dim > 0")
+            self._expect(r_positional_embeddings, (S - 1) * self._n_detectors * self._pos_dim, "r_positional_embeddings")
+        cfg = self._cfg(cmp_eps, sliced=sliced_mode)
+        with torch.cuda.device(dev):
+            rc = _native.lib().lutb_product_forward(
+                ctypes.byref(cfg), B, S, _ptr(r_weights), _ptr(r_input_1), _ptr(r_input_2), int(n_inputs_1),
+                int(n_inputs_2), _ptr(r_positional_embeddings), _ptr(r_detector_anchors), _ptr(w_output),
+                self._stream())
+        _native.check(rc)
+        self._forward_seen = True
+
+    def backward_backprop_product(self, r_weights, batch_size, sequence_length, r_input_1, r_input_2,
+                                  r_detector_anchors, r_output_gradients, w_input_gradients_1, w_input_gradients_2,
+                                  external_lr, n_inputs_1, n_inputs_2, sliced_mode, cmp_eps=0.0,
+                                  w_weights_gradients=None, r_positional_embeddings=None,
+                                  w_positional_embeddings_gradients=None, r_stream_handles=None):
+        if batch_size == 0:
+            raise ValueError("batch_size == 0")
+        if not self._forward_seen:
+            raise ValueError("no active context")
+        self._require_cuda()
+        dev = self._device
+        for t, name in ((r_weights, "r_weights"), (r_input_1, "r_input_1"), (r_input_2, "r_input_2"),
+                        (r_output_gradients, "r_output_gradients"), (w_input_gradients_1, "w_input_gradients_1"),
+                        (w_input_gradients_2, "w_input_gradients_2")):
+            _check_tensor(t, name, True, dev)
+        _check_tensor(r_detector_anchors, "r_detector_anchors", False, dev)
+        for t, name in ((w_weights_gradients, "w_weights_gradients"),
+                        (r_positional_embeddings, "r_positional_embeddings"),
+                        (w_positional_embeddings_gradients, "w_positional_embeddings_gradients")):
+            if t is not None:
+                _check_tensor(t, name, True, dev)
+        if external_lr >= 0.0 and w_weights_gradients is not None:
+            raise ValueError("in internal weight gradients mode w_weights_gradients should be nullptr")
+        B, S = int(batch_size), int(sequence_length)
+        self._expect(r_output_gradients, B * S * self._n_outputs, "r_output_gradients")
+        self._expect(w_input_gradients_1, B * S * n_inputs_1, "w_input_gradients_1")
+        self._expect(w_input_gradients_2, B * S * n_inputs_2, "w_input_gradients_2")
+        cfg = self._cfg(cmp_eps, sliced=sliced_mode)
+        with torch.cuda.device(dev):
+            rc = _native.lib().lutb_product_backward(
+                ctypes.byref(cfg), B, S, _ptr(r_weights), _ptr(r_input_1), _ptr(r_input_2), int(n_inputs_1),
+                int(n_inputs_2), _ptr(r_positional_embeddings), _ptr(r_detector_anchors), _ptr(r_output_gradients),
+                _ptr(w_input_gradients_1), _ptr(w_input_gradients_2), _ptr(w_positional_embeddings_gradients),
+                _ptr(w_weights_gradients), float(external_lr), self._stream())
+        _native.check(rc)
+
     @staticmethod
     def _expect(t, numel, name):
         if t.numel() != numel:

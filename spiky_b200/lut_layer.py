@@ -482,10 +482,44 @@ class LUTLayerBasic(nn.Module):
         raise NotImplementedError("concatenation-mode sequence layers are not available in this build")
 
     def forward_step_product(self, x, pos_embeddings, output=None):
-        raise NotImplementedError("product-mode sequence layers are not available in this build")
+        assert not self._concatenation_product
+        x = self._check_input(x, self._sequence_length)
+        B, S = x.shape[0], x.shape[1]
+        external = output is not None
+        if not external:
+            output = torch.zeros(B * S * self._n_outputs, dtype=torch.float32, device=self.device)
+        xf = x.view(-1)
+        pe = None if pos_embeddings is None else pos_embeddings.detach().contiguous().view(-1)
+        self._lut_dm.forward_step_product(self._weights.detach(), B, S, xf, xf, self._detector_anchors, output,
+                                          self._n_inputs, self._n_inputs, self._sliced_product_mode,
+                                          self._shared_context._cmp_eps, pe, None)
+        return None if external else output.view((B, S) + tuple(self.output_shape()))
 
-    def backward_step_product(self, *args, **kwargs):
-        raise NotImplementedError("product-mode sequence layers are not available in this build")
+    def backward_step_product(self, x, pos_embeddings, grad_output, x_grad=None):
+        assert not self._concatenation_product
+        x = self._check_input(x, self._sequence_length)
+        B, S = x.shape[0], x.shape[1]
+        assert grad_output.shape == (B, S) + tuple(self.output_shape())
+        external = x_grad is not None
+        if not external:
+            x_grad = torch.zeros(x.numel(), dtype=torch.float32, device=self.device)
+        w_grad = self._weight_grad_target()
+        pe = pe_grad = None
+        if self._positional_dim > 0:
+            pe = pos_embeddings.detach().contiguous().view(-1)
+            pe_grad = torch.zeros_like(pe)
+        xf, gf = x.view(-1), x_grad.view(-1)
+        self._lut_dm.backward_backprop_product(
+            self._weights.detach(), B, S, xf, xf, self._detector_anchors, grad_output.contiguous().view(-1), gf, gf,
+            self._external_lr(), self._n_inputs, self._n_inputs, self._sliced_product_mode,
+            self._shared_context._cmp_eps, w_grad, pe, pe_grad, None)
+        if not external:
+            w_grad = self._process_gradients(w_grad, B)
+        if pe_grad is not None and self._weights_gradient_policy.normalized:
+            pe_grad /= pe_grad.abs().max().clip(1e-16)
+        if external:
+            return w_grad, pe_grad
+        return x_grad.view(x.shape), w_grad, pe_grad
 
     def forward(self, x):
         if self._sequence_length == 1:

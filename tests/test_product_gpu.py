@@ -1,0 +1,122 @@
+"""CUDA path of product-mode sequence (attention) layers against the reference's golden vectors and the oracle."""
+import numpy as np
+import pytest
+import torch
+
+import golden_util
+from cases import sequence_inputs, PRODUCT_CASES
+from oracle import lut_oracle as orc
+from test_oracle_golden import expand_pe
+
+pytestmark = pytest.mark.gpu
+REL = 1e-5
+
+
+def build_layer(cfg, anchors, W, pe):
+    from spiky_b200.lut_layer import LUTLayer, SynapseMeta, GradientPolicy, GradientType, LUTSharedContext
+
+    internal = cfg.get("policy") == "internal"
+    ctx = LUTSharedContext(_cmp_eps=cfg.get("cmp_eps", 0.0)).to_device("cuda:0")
+    layer = LUTLayer(
+        cfg["E"], cfg["Nc"], cfg["Nt"], cfg["O"], sequence_length=cfg["S"],
+        synapse_meta=SynapseMeta(learning_rate=cfg.get("lr_meta", 1.0), min_weight=-1.0, max_weight=1.0),
+        concatenation_product=False, sliced_product_mode=cfg.get("sliced", False), positional_dim=cfg["Npe"],
+        unified_pe=cfg.get("unified_pe", False),
+        weights_gradient_policy=GradientPolicy(GradientType.Internal if internal else GradientType.Dense),
+        shared_context=ctx, summation_dtype=torch.int32 if cfg.get("int_mode") else torch.float32,
+        _explicit_anchors=torch.from_numpy(anchors.reshape(-1).copy()), _int_rescaler=cfg.get("int_rescaler", 0.001),
+        random_seed=1, device="cuda:0")
+    with torch.no_grad():
+        layer._weights.copy_(torch.from_numpy(W))
+        if pe is not None:
+            layer._positional_embeddings.copy_(torch.from_numpy(pe))
+    if internal:
+        layer.set_external_learning_rate_hook(lambda w: cfg["ext_lr"])
+    return layer
+
+
+def run_gpu(cfg, x, anchors, W, pe, dY):
+    layer = build_layer(cfg, anchors, W, pe)
+    layer.train()
+    xt = torch.from_numpy(x).cuda()
+    pos = layer._prepare_positional_embeddings()
+    pos = None if pos is None else pos.detach()
+    y = layer.forward_step_product(xt, pos)
+    dx, dw, dpe = layer.backward_step_product(xt, pos, torch.from_numpy(dY).cuda())
+    torch.cuda.synchronize()
+    out = dict(y=y.cpu().numpy(), dX=dx.cpu().numpy())
+    if dpe is not None:
+        out["dPE"] = dpe.cpu().numpy()
+    if cfg.get("policy") == "internal":
+        out["W_after"] = layer._weights.detach().cpu().numpy()
+    else:
+        out["dW"] = dw.cpu().numpy()
+    return out
+
+
+def compare(cfg, got, ref):
+    keys = ["y", "dX"] + (["dPE"] if cfg["Npe"] > 0 else []) + (["W_after"] if "W_after" in ref else ["dW"])
+    for k in keys:
+        if cfg.get("int_mode"):
+            assert np.array_equal(got[k], ref[k]), f"{k}: fixed-point results must be bit-exact"
+        else:
+            golden_util.assert_close(got[k], ref[k], REL, k)
+
+
+def inputs_for(cfg):
+    n_pe = (cfg["S"] - 1) * (1 if cfg.get("unified_pe") else cfg["Nt"]) * cfg["Npe"]
+    return sequence_inputs(cfg, cfg["Nt"] * (1 << cfg["Nc"]) * cfg["O"], n_pe)
+
+
+@pytest.mark.parametrize("name", golden_util.names("prod_"))
+def test_product_matches_reference_golden(name):
+    cfg, ref = golden_util.load(name)
+    x, anchors, W, pe, dY = inputs_for(cfg)
+    compare(cfg, run_gpu(cfg, x, anchors, W, pe, dY), ref)
+
+
+ORACLE_CASES = {
+    # one attention layer of the character-level transformer configuration at reduced batch:
+    # context 128, d_model 256, 64 detectors (16 x 4 heads), 8 pairs, 4 positional dims
+    "c3_attention": dict(seed=700, B=2, S=128, E=256, Nt=64, Nc=8, Npe=4, O=256),
+    "c3_attention_i32": dict(seed=701, B=1, S=48, E=64, Nt=16, Nc=8, Npe=4, O=64, int_mode=True, int_rescaler=0.01),
+    "ragged_outputs": dict(seed=702, B=3, S=33, E=20, Nt=7, Nc=5, Npe=3, O=10, unified_pe=True),
+    "long_rows": dict(seed=703, B=2, S=17, E=16, Nt=3, Nc=6, Npe=2, O=600),
+    "sliced": dict(seed=704, B=2, S=40, E=12, Nt=6, Nc=7, Npe=12, O=12, sliced=True, unified_pe=True, cmp_eps=1e-4,
+                   quantized_input=True),
+    "two_tokens": dict(seed=705, B=2, S=2, E=8, Nt=2, Nc=3, Npe=2, O=4),
+}
+for _c in ORACLE_CASES.values():
+    _c["n_virtual"] = 3 * _c["E"] if _c.get("sliced") else 2 * _c["E"] + _c["Npe"]
+
+
+@pytest.mark.parametrize("name", sorted(ORACLE_CASES))
+def test_product_matches_oracle(name):
+    cfg = ORACLE_CASES[name]
+    x, anchors, W, pe, dY = inputs_for(cfg)
+    pe3 = expand_pe(cfg, pe)
+    kw = dict(sliced=cfg.get("sliced", False), cmp_eps=cfg.get("cmp_eps", 0.0), int_mode=cfg.get("int_mode", False),
+              int_rescaler=cfg.get("int_rescaler", 0.001))
+    y = orc.product_forward(W, x, pe3, anchors, cfg["Nt"], cfg["Nc"], cfg["O"], cfg["Npe"], **kw)
+    dX, dW, dPE = orc.product_backward(W, x, pe3, anchors, dY, cfg["Nt"], cfg["Nc"], cfg["Npe"], **kw)
+    got = run_gpu(cfg, x, anchors, W, pe, dY)
+    ref = dict(y=y, dX=dX, dW=dW, dPE=dPE)
+    assert not got["y"][:, 0].any()  # the first position has no earlier token to pair with
+    compare(cfg, got, ref)
+
+
+def test_product_autograd_unified_pe():
+    """Gradients reach the (unified) positional embeddings through the layer's autograd function."""
+    cfg = dict(seed=710, B=2, S=12, E=10, Nt=4, Nc=4, Npe=3, O=8, unified_pe=True, n_virtual=23)
+    x, anchors, W, pe, dY = inputs_for(cfg)
+    layer = build_layer(cfg, anchors, W, pe)
+    layer.train()
+    xt = torch.from_numpy(x).cuda().requires_grad_(True)
+    y = layer(xt)
+    y.backward(torch.from_numpy(dY).cuda())
+    pe3 = expand_pe(cfg, pe)
+    dX, dW, dPE = orc.product_backward(W, x, pe3, anchors, dY, cfg["Nt"], cfg["Nc"], cfg["Npe"])
+    golden_util.assert_close(xt.grad.cpu().numpy(), dX, REL, "dX")
+    golden_util.assert_close(layer._weights.grad.cpu().numpy(), dW, REL, "dW")
+    want = dPE.reshape(cfg["S"] - 1, cfg["Nt"], cfg["Npe"]).sum(axis=1).reshape(-1)
+    golden_util.assert_close(layer._positional_embeddings.grad.cpu().numpy(), want, REL, "dPE (summed over detectors)")
