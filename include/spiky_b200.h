@@ -177,6 +177,30 @@ int lutb_product_backward(const lutb_layer_cfg *cfg, int64_t batch, int32_t seq_
                           const int32_t *anchors, const float *dY, float *dX1, float *dX2, float *dPE, float *dW,
                           double external_lr, void *stream);
 
+/*
+ * Concatenation-mode sequence layer, forward.  Replaces LUTDataManager::forward_step_concat
+ * (spiky_cuda/lut/lut.cu:718-845 -> LUTRuntimeContext::forward_step_concat, lut_runtime.cu:399-593).
+ * cfg->seq_len = S > 1, cfg->n_inputs = inputs per token.  Tables have 2^(2*Nc + pos_dim) rows; pair (i < j)
+ * selects row (idx[b,j,t] << (Nc + pos_dim)) | (idx[b,i,t] << pos_dim) | pos_idx[j-i-1, t].
+ *   x fp32 [batch * S * I]; pos_embeddings fp32 [(S-1) * Nt * pos_dim] or NULL; y fp32 [batch * S * O] accumulated
+ *   idx int32 [batch * S * Nt] out; min_delta / min_k [batch * S * Nt] out (both NULL = eval)
+ *   pos_idx int32 [(S-1) * Nt] out, pos_min_delta / pos_min_k likewise (training only); NULL when pos_dim == 0
+ */
+int lutb_concat_forward(const lutb_layer_cfg *cfg, int64_t batch, const float *weights, const float *x,
+                        const int32_t *anchors, const float *pos_embeddings, float *y, int32_t *idx, float *min_delta,
+                        int32_t *min_k, int32_t *pos_idx, float *pos_min_delta, int32_t *pos_min_k, void *stream);
+
+/*
+ * Concatenation-mode sequence layer, backward.  Replaces LUTDataManager::backward_backprop_concat
+ * (spiky_cuda/lut/lut.cu:1090-1180 -> LUTRuntimeContext::backward_backprop_concat, lut_runtime.cu:595-850).
+ * dX fp32 [batch * S * I] and dPE fp32 [(S-1) * Nt * pos_dim] are accumulated into; dW / external_lr as in
+ * lutb_nonseq_fc_backward.
+ */
+int lutb_concat_backward(const lutb_layer_cfg *cfg, int64_t batch, float *weights, const float *dY,
+                         const int32_t *anchors, const int32_t *idx, const float *min_delta, const int32_t *min_k,
+                         const int32_t *pos_idx, const float *pos_min_delta, const int32_t *pos_min_k, float *dX,
+                         float *dPE, float *dW, double external_lr, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

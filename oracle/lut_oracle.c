@@ -509,3 +509,134 @@ void orc_product_backward(float *W, const float *x1, const float *x2, const floa
         if (Npe > 0 && dPE) orc_int_to_float(dPE, (int64_t)(S - 1) * Nt * Npe, rescaler);
     }
 }
+
+/* ------------------------------------------------------------------------------------------
+ * Concatenation-mode sequence layers: every token gets its own index (orc_check_detectors over
+ * B*S rows), every (distance, detector) its positional index (orc_check_positional); a causal pair
+ * (i < j) selects row (Q_j << (Nc + Npe)) | (K_i << Npe) | PE_{j-i-1} of a table with 2^(2Nc+Npe) rows.
+ * ------------------------------------------------------------------------------------------ */
+static inline int64_t orc_concat_row(int32_t Q, int32_t K, int32_t PE, int Nc, int Npe) {
+    return (int64_t)(((uint32_t)Q << (Nc + Npe)) | ((uint32_t)K << Npe) | (uint32_t)PE);
+}
+
+/* fill_outputs_fully_connected_seq_logic, proto:1807-1904 */
+void orc_concat_forward(const float *W, const int32_t *idx, const int32_t *pidx, float *y, int64_t B, int S, int O,
+                        int Nt, int Nc, int Npe, int int_mode, double rescaler) {
+    int64_t T = (int64_t)1 << (2 * Nc + Npe);
+    ORC_PARALLEL_FOR
+    for (int64_t b = 0; b < B; b++) {
+        const int32_t *ib = idx + b * S * Nt;
+        for (int j = 1; j < S; j++)
+            for (int t = 0; t < Nt; t++) {
+                int32_t Q = ib[j * Nt + t];
+                for (int o = 0; o < O; o++) {
+                    double s = 0.0;
+                    for (int i = 0; i < j; i++) {
+                        int32_t PE = Npe > 0 ? pidx[(j - i - 1) * Nt + t] : 0;
+                        s += (double)W[((int64_t)t * T + orc_concat_row(Q, ib[i * Nt + t], PE, Nc, Npe)) * O + o];
+                    }
+                    float *cell = y + (b * S + j) * O + o;
+                    if (int_mode) *(int32_t *)cell += (int32_t)(s * ORC_DENOM * rescaler);
+                    else *cell += (float)s;
+                }
+            }
+    }
+    if (int_mode) orc_int_to_float(y, B * S * O, rescaler);
+}
+
+/*
+ * propagate_through_detectors_seq_fc_logic (proto:3629-3835) followed by gather_w_gradients_seq_fc_cpu_logic
+ * (proto:3944-4044); loop nest = the reference's host grid: (sample, output block) outermost, then 32x32
+ * pair tiles row-major, detectors, and inside a tile the query index outer / key index inner
+ * (lut_runtime.cu:639-799, 32 = TILE of lut_runtime.cuh:68).
+ */
+void orc_concat_backward(float *W, const float *dY, const int32_t *anchors, const int32_t *idx,
+                         const float *min_delta, const int32_t *min_k, const int32_t *pidx, const float *pmin,
+                         const int32_t *pmin_k, float *dX, float *dPE, float *dW, int64_t B, int S, int I, int O,
+                         int Nt, int Nc, int Npe, int G, double lr_meta, double ext_lr, int int_mode,
+                         double rescaler) {
+    int64_t T = (int64_t)1 << (2 * Nc + Npe);
+    int n_ob = (O + G - 1) / G;
+    int tiles = (S + 31) / 32;
+    double lr = lr_meta;
+    if (ext_lr >= 0) lr *= -ext_lr;
+    float *target = ext_lr >= 0 ? W : dW;
+    for (int pass = 0; pass < 2; pass++)  /* 0: input + positional gradients, 1: table gradients */
+        for (int64_t b = 0; b < B; b++)
+            for (int ob = 0; ob < n_ob; ob++) {
+                int o0 = ob * G, o1 = o0 + G < O ? o0 + G : O;
+                for (int ti = 0; ti < tiles; ti++)
+                    for (int tj = 0; tj < tiles; tj++) {
+                        if (ti > tj) continue;
+                        for (int t = 0; t < Nt; t++)
+                            for (int jl = 0; jl < 32; jl++)
+                                for (int il = 0; il < 32; il++) {
+                                    int i = ti * 32 + il, j = tj * 32 + jl;
+                                    if (i >= j || i >= S || j >= S) continue;
+                                    const float *dy = dY + (b * S + j) * O;
+                                    int64_t ko = (b * S + i) * Nt + t, qo = (b * S + j) * Nt + t;
+                                    int32_t K = idx[ko], Q = idx[qo];
+                                    int32_t PE = 0, pk = -1;
+                                    float pm = 0.0f;
+                                    int64_t po = (int64_t)(j - i - 1) * Nt + t;
+                                    if (Npe > 0) { PE = pidx[po]; pk = pmin_k[po]; pm = pmin[po]; }
+                                    int64_t row = (int64_t)t * T + orc_concat_row(Q, K, PE, Nc, Npe);
+                                    if (pass == 1) {
+                                        for (int o = o0; o < o1; o++) {
+                                            double g = (double)dy[o];
+                                            if (fabs(g) > ORC_EPS) {
+                                                if (int_mode) *(int32_t *)(target + row * O + o) += (int32_t)(g * lr * ORC_DENOM * rescaler);
+                                                else target[row * O + o] += (float)(g * lr);
+                                            }
+                                        }
+                                        continue;
+                                    }
+                                    float qm = min_delta[qo], km = min_delta[ko];
+                                    int64_t alt;
+                                    double du;
+                                    int flip, pos;
+                                    if (fabsf(qm) < fabsf(km)) {
+                                        alt = (int64_t)t * T + orc_concat_row(Q ^ (1 << min_k[qo]), K, PE, Nc, Npe);
+                                        du = orc_up(qm); flip = min_k[qo]; pos = j;
+                                    } else {
+                                        alt = (int64_t)t * T + orc_concat_row(Q, K ^ (1 << min_k[ko]), PE, Nc, Npe);
+                                        du = orc_up(km); flip = min_k[ko]; pos = i;
+                                    }
+                                    double ms = 0.0, as = 0.0;
+                                    for (int o = o0; o < o1; o++) {
+                                        double g = (double)dy[o];
+                                        ms += (double)W[row * O + o] * g;
+                                        as += (double)W[alt * O + o] * g;
+                                    }
+                                    du *= ms - as;
+                                    if (fabs(du) > ORC_EPS) {
+                                        int32_t a1 = anchors[((int64_t)t * Nc + flip) * 2], a2 = anchors[((int64_t)t * Nc + flip) * 2 + 1];
+                                        float *dx = dX + (b * S + pos) * (int64_t)I;
+                                        if (int_mode) {
+                                            int32_t d = (int32_t)(du * ORC_DENOM * rescaler);
+                                            *(int32_t *)(dx + a1) += d;
+                                            *(int32_t *)(dx + a2) -= d;
+                                        } else {
+                                            dx[a1] += du;
+                                            dx[a2] -= du;
+                                        }
+                                    }
+                                    if (Npe > 0 && fabsf(pm) < fabsf(qm) && fabsf(pm) < fabsf(km)) {
+                                        int64_t palt = (int64_t)t * T + orc_concat_row(Q, K, PE ^ (1 << pk), Nc, Npe);
+                                        double dp = orc_up(pm);
+                                        double ps = 0.0;
+                                        for (int o = o0; o < o1; o++) ps += (double)W[palt * O + o] * (double)dy[o];
+                                        dp *= ms - ps;
+                                        float *cell = dPE + po * Npe + pk;
+                                        if (int_mode) *(int32_t *)cell += (int32_t)(dp * ORC_DENOM * rescaler);
+                                        else *cell += dp;
+                                    }
+                                }
+                    }
+            }
+    if (int_mode) {
+        orc_int_to_float(dX, B * S * (int64_t)I, rescaler);
+        if (dW) orc_int_to_float(dW, (int64_t)Nt * T * O, rescaler);
+        if (Npe > 0) orc_int_to_float(dPE, (int64_t)(S - 1) * Nt * Npe, rescaler);
+    }
+}

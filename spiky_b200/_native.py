@@ -73,6 +73,8 @@ SIGNATURES = {
     "lutb_nonseq_fc_forward": (_int, [_cfgp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "lutb_nonseq_fc_backward_workspace": (_size, [_cfgp, _i64, _int]),
     "lutb_nonseq_fc_backward": (_int, [_cfgp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _dbl, _int, _vp, _size, _vp]),
+    "lutb_concat_forward": (_int, [_cfgp, _i64] + [_vp] * 12),
+    "lutb_concat_backward": (_int, [_cfgp, _i64] + [_vp] * 12 + [_dbl, _vp]),
     "lutb_product_forward": (_int, [_cfgp, _i64, ctypes.c_int32, _vp, _vp, _vp, ctypes.c_int32, ctypes.c_int32, _vp, _vp, _vp, _vp]),
     "lutb_product_backward": (_int, [_cfgp, _i64, ctypes.c_int32, _vp, _vp, _vp, ctypes.c_int32, ctypes.c_int32, _vp, _vp,
                                      _vp, _vp, _vp, _vp, _vp, _dbl, _vp]),

@@ -74,6 +74,7 @@ static const char *const kKernelNames[K_COUNT] = {
     "check_detectors", "fc_gather_forward", "fc_input_grad", "fc_weight_grad", "fixed_to_float",
     "sparse_forward", "sparse_input_grad", "sparse_weight_grad", "sparse_backward_fused",
     "product_forward", "product_backward", "product_weight_update",
+    "check_positional", "concat_forward", "concat_backward", "concat_weight_update",
 };
 
 struct EventPair {

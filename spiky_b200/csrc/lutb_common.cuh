@@ -68,6 +68,10 @@ enum KernelId {
     K_PRODUCT_FORWARD,
     K_PRODUCT_BACKWARD,
     K_PRODUCT_WEIGHT_UPDATE,
+    K_CHECK_POSITIONAL,
+    K_CONCAT_FORWARD,
+    K_CONCAT_BACKWARD,
+    K_CONCAT_WEIGHT_UPDATE,
     K_COUNT
 };
 

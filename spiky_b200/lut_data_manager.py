@@ -380,6 +380,92 @@ class _LUTDataManager:
                 _ptr(w_weights_gradients), float(external_lr), self._stream())
         _native.check(rc)
 
+    # ------------------------------------------------------------------ concatenation-mode sequence runtime
+    def forward_step_concat(self, r_weights, batch_size, r_input, r_detector_anchors, w_output, w_lookup_indices,
+                            cmp_eps=0.0, r_positional_embeddings=None, w_positional_lookup_indices=None,
+                            w_min_anchor_deltas=None, w_min_anchor_delta_indices=None,
+                            w_positional_min_deltas=None, w_positional_min_delta_indices=None,
+                            r_stream_handles=None):
+        self._require_cuda()
+        dev = self._device
+        _check_tensor(r_weights, "r_weights", True, dev)
+        _check_tensor(r_input, "r_input", True, dev)
+        _check_tensor(r_detector_anchors, "r_detector_anchors", False, dev)
+        _check_tensor(w_output, "w_output", True, dev)
+        _check_tensor(w_lookup_indices, "w_lookup_indices", False, dev)
+        for t, name, real in ((r_positional_embeddings, "r_positional_embeddings", True),
+                              (w_positional_lookup_indices, "w_positional_lookup_indices", False),
+                              (w_min_anchor_deltas, "w_min_anchor_deltas", True),
+                              (w_min_anchor_delta_indices, "w_min_anchor_delta_indices", False),
+                              (w_positional_min_deltas, "w_positional_min_deltas", True),
+                              (w_positional_min_delta_indices, "w_positional_min_delta_indices", False)):
+            if t is not None:
+                _check_tensor(t, name, real, dev)
+        if batch_size == 0:
+            raise ValueError("batch_size == 0")
+        if self._seq_len <= 1:
+            raise ValueError("forward_step_concat should only be called when sequence_length > 1")
+        if not self._fully_connected:
+            raise ValueError("sequence layers are only available with fully connected outputs in this backend")
+        B, S = int(batch_size), self._seq_len
+        self._expect(r_input, B * S * self._n_inputs, "r_input")
+        self._expect(w_output, B * S * self._n_outputs, "w_output")
+        self._expect(w_lookup_indices, B * S * self._n_detectors, "w_lookup_indices")
+        self._expect(r_weights, self.get_weights_dimension(), "r_weights")
+        if self._pos_dim > 0 and (r_positional_embeddings is None or w_positional_lookup_indices is None):
+            raise ValueError("positional embeddings and their index buffer are required when positional_dim > 0")
+        cfg = self._cfg(cmp_eps)
+        with torch.cuda.device(dev):
+            rc = _native.lib().lutb_concat_forward(
+                ctypes.byref(cfg), B, _ptr(r_weights), _ptr(r_input), _ptr(r_detector_anchors),
+                _ptr(r_positional_embeddings), _ptr(w_output), _ptr(w_lookup_indices), _ptr(w_min_anchor_deltas),
+                _ptr(w_min_anchor_delta_indices), _ptr(w_positional_lookup_indices), _ptr(w_positional_min_deltas),
+                _ptr(w_positional_min_delta_indices), self._stream())
+        _native.check(rc)
+        self._forward_seen = True
+
+    def backward_backprop_concat(self, r_weights, batch_size, r_output_gradients, r_detector_anchors,
+                                 r_lookup_indices, r_min_anchor_deltas, r_min_anchor_delta_indices,
+                                 w_input_gradients, external_lr, r_positional_lookup_indices=None,
+                                 r_positional_min_deltas=None, r_positional_min_delta_indices=None,
+                                 w_positional_embeddings_gradients=None, w_weights_gradients=None,
+                                 r_stream_handles=None):
+        if batch_size == 0:
+            raise ValueError("batch_size == 0")
+        if not self._forward_seen:
+            raise ValueError("no active context")
+        self._require_cuda()
+        dev = self._device
+        for t, name, real in ((r_weights, "r_weights", True), (r_output_gradients, "r_output_gradients", True),
+                              (r_detector_anchors, "r_detector_anchors", False),
+                              (r_lookup_indices, "r_lookup_indices", False),
+                              (r_min_anchor_deltas, "r_min_anchor_deltas", True),
+                              (r_min_anchor_delta_indices, "r_min_anchor_delta_indices", False),
+                              (w_input_gradients, "w_input_gradients", True)):
+            _check_tensor(t, name, real, dev)
+        for t, name, real in ((r_positional_lookup_indices, "r_positional_lookup_indices", False),
+                              (r_positional_min_deltas, "r_positional_min_deltas", True),
+                              (r_positional_min_delta_indices, "r_positional_min_delta_indices", False),
+                              (w_positional_embeddings_gradients, "w_positional_embeddings_gradients", True),
+                              (w_weights_gradients, "w_weights_gradients", True)):
+            if t is not None:
+                _check_tensor(t, name, real, dev)
+        if external_lr >= 0.0 and w_weights_gradients is not None:
+            raise ValueError("in internal weight gradients mode w_weights_gradients should be nullptr")
+        B, S = int(batch_size), self._seq_len
+        self._expect(r_output_gradients, B * S * self._n_outputs, "r_output_gradients")
+        self._expect(w_input_gradients, B * S * self._n_inputs, "w_input_gradients")
+        cfg = self._cfg()
+        with torch.cuda.device(dev):
+            rc = _native.lib().lutb_concat_backward(
+                ctypes.byref(cfg), B, _ptr(r_weights), _ptr(r_output_gradients), _ptr(r_detector_anchors),
+                _ptr(r_lookup_indices), _ptr(r_min_anchor_deltas), _ptr(r_min_anchor_delta_indices),
+                _ptr(r_positional_lookup_indices), _ptr(r_positional_min_deltas),
+                _ptr(r_positional_min_delta_indices), _ptr(w_input_gradients),
+                _ptr(w_positional_embeddings_gradients), _ptr(w_weights_gradients), float(external_lr),
+                self._stream())
+        _native.check(rc)
+
     @staticmethod
     def _expect(t, numel, name):
         if t.numel() != numel:

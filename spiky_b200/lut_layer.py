@@ -476,10 +476,71 @@ class LUTLayerBasic(nn.Module):
         return self._positional_embeddings
 
     def forward_step_concat(self, x, pos_embeddings, output=None):
-        raise NotImplementedError("concatenation-mode sequence layers are not available in this build")
+        assert self._concatenation_product
+        x = self._check_input(x, self._sequence_length)
+        B, S, Nt, dev = x.shape[0], x.shape[1], self._n_detectors, self.device
+        external = output is not None
+        if not external:
+            output = torch.zeros(B * S * self._n_outputs, dtype=torch.float32, device=dev)
+        train = self.training
+        idx = torch.empty(B * S * Nt, dtype=torch.int32, device=dev)
+        md = torch.empty(B * S * Nt, dtype=torch.float32, device=dev) if train else None
+        mk = torch.empty(B * S * Nt, dtype=torch.int32, device=dev) if train else None
+        pidx = pmd = pmk = pe = None
+        if self._positional_dim > 0:
+            pe = pos_embeddings.detach().contiguous().view(-1)
+            pidx = torch.empty((S - 1) * Nt, dtype=torch.int32, device=dev)
+            if train:
+                pmd = torch.empty((S - 1) * Nt, dtype=torch.float32, device=dev)
+                pmk = torch.empty((S - 1) * Nt, dtype=torch.int32, device=dev)
+        self._lut_dm.forward_step_concat(self._weights.detach(), B, x.view(-1), self._detector_anchors, output, idx,
+                                         self._shared_context._cmp_eps, pe, pidx, md, mk, pmd, pmk, None)
+        result = () if external else (output.view((B, S) + tuple(self.output_shape())),)
+        if not train:
+            return None if external else result[0]
+        tok = (B, S, Nt)
+        state = (idx.view(tok), md.view(tok), mk.view(tok))
+        if self._positional_dim > 0:
+            state += (pidx.view(S - 1, Nt), pmd.view(S - 1, Nt), pmk.view(S - 1, Nt))
+        else:
+            state += (None, None, None)
+        return result + state
 
-    def backward_step_concat(self, *args, **kwargs):
-        raise NotImplementedError("concatenation-mode sequence layers are not available in this build")
+    def backward_step_concat(self, x, grad_output, lookup_indices, min_anchor_deltas, min_anchor_delta_indices,
+                             positional_lookup_indices, positional_min_deltas, positional_min_delta_indices,
+                             x_grad=None):
+        assert self._concatenation_product
+        x = self._check_input(x, self._sequence_length)
+        B, S, Nt = x.shape[0], x.shape[1], self._n_detectors
+        assert lookup_indices.shape == (B, S, Nt)
+        assert grad_output.shape == (B, S) + tuple(self.output_shape())
+        if self._positional_dim > 0:
+            assert positional_lookup_indices.shape == (S - 1, Nt)
+        else:
+            assert positional_lookup_indices is None and positional_min_deltas is None
+        external = x_grad is not None
+        if not external:
+            x_grad = torch.zeros(x.numel(), dtype=torch.float32, device=self.device)
+        w_grad = self._weight_grad_target()
+        pe_grad = None
+        if self._positional_dim > 0:
+            pe_grad = torch.zeros((S - 1) * Nt * self._positional_dim, dtype=torch.float32, device=self.device)
+
+        def flat(t):
+            return None if t is None else t.reshape(-1)
+
+        self._lut_dm.backward_backprop_concat(
+            self._weights.detach(), B, grad_output.contiguous().view(-1), self._detector_anchors,
+            flat(lookup_indices), flat(min_anchor_deltas), flat(min_anchor_delta_indices), x_grad.view(-1),
+            self._external_lr(), flat(positional_lookup_indices), flat(positional_min_deltas),
+            flat(positional_min_delta_indices), pe_grad, w_grad, None)
+        if not external:
+            w_grad = self._process_gradients(w_grad, B)
+        if pe_grad is not None and self._weights_gradient_policy.normalized:
+            pe_grad /= pe_grad.abs().max().clip(1e-16)
+        if external:
+            return w_grad, pe_grad
+        return x_grad.view(x.shape), w_grad, pe_grad
 
     def forward_step_product(self, x, pos_embeddings, output=None):
         assert not self._concatenation_product

@@ -118,3 +118,16 @@ PRODUCT_CASES = {
 }
 for _c in PRODUCT_CASES.values():
     _c["n_virtual"] = 3 * _c["E"] if _c.get("sliced") else 2 * _c["E"] + _c["Npe"]
+
+
+CONCAT_CASES = {
+    "concat_f32": dict(seed=400, B=3, S=6, E=9, Nt=4, Nc=2, Npe=2, O=5, G=4),
+    "concat_i32": dict(seed=401, B=3, S=6, E=9, Nt=4, Nc=2, Npe=2, O=5, G=4, int_mode=True, int_rescaler=10.0),
+    "concat_unified_f32": dict(seed=402, B=2, S=7, E=8, Nt=3, Nc=3, Npe=3, O=6, unified_pe=True, quantized_input=True),
+    "concat_nope_f32": dict(seed=403, B=2, S=5, E=8, Nt=3, Nc=2, Npe=0, O=7),
+    "concat_internal": dict(seed=404, B=2, S=6, E=8, Nt=3, Nc=2, Npe=2, O=6, policy="internal", ext_lr=0.25,
+                            lr_meta=0.5),
+    # more than one 32x32 pair tile, outputs wider than one forward group
+    "concat_long_f32": dict(seed=405, B=1, S=40, E=10, Nt=2, Nc=2, Npe=1, O=35),
+    "concat_long_i32": dict(seed=406, B=1, S=40, E=10, Nt=2, Nc=2, Npe=1, O=35, int_mode=True, int_rescaler=0.5),
+}

@@ -20,7 +20,7 @@ import torch
 
 sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 import synth  # noqa: E402,F401
-from cases import (NONSEQ_FC_CASES, PROJECTION_CASES, PRODUCT_CASES, nonseq_fc_inputs, projection_inputs,  # noqa: E402
+from cases import (CONCAT_CASES, NONSEQ_FC_CASES, PROJECTION_CASES, PRODUCT_CASES, nonseq_fc_inputs, projection_inputs,  # noqa: E402
                    sequence_inputs)
 
 from spiky.lut.LUTLayer import (  # noqa: E402  (the reference)
@@ -193,11 +193,61 @@ def run_product(name, cfg):
     save(name, dict(cfg, kind="product"), in_x=x, in_anchors=anchors, **out)
 
 
+# ----------------------------------------------------------------------------- concatenation-mode sequence layers
+def run_concat(name, cfg):
+    B, S, E, Nt, Nc, O, Npe = cfg["B"], cfg["S"], cfg["E"], cfg["Nt"], cfg["Nc"], cfg["O"], cfg["Npe"]
+    int_mode = cfg.get("int_mode", False)
+    policy = {"dense": GradientType.Dense, "internal": GradientType.Internal}[cfg.get("policy", "dense")]
+    unified = cfg.get("unified_pe", False)
+    n_weights = Nt * (1 << (2 * Nc + Npe)) * O
+    n_pe = (S - 1) * (1 if unified else Nt) * Npe
+    x, anchors, W, pe, dY = sequence_inputs(cfg, n_weights, n_pe)
+    layer = LUTLayer(
+        n_inputs=E, n_anchors_per_detector=Nc, n_detectors=Nt, n_outputs=O, sequence_length=S,
+        synapse_meta=SynapseMeta(learning_rate=cfg.get("lr_meta", 1.0), min_weight=-1.0, max_weight=1.0),
+        concatenation_product=True, positional_dim=Npe, unified_pe=unified,
+        weights_gradient_policy=GradientPolicy(policy),
+        summation_dtype=torch.int32 if int_mode else torch.float32,
+        _explicit_anchors=torch.from_numpy(anchors.reshape(-1).copy()), _int_rescaler=cfg.get("int_rescaler", 0.001),
+        _forward_group_size=cfg.get("G", 32), random_seed=1,
+    )
+    with torch.no_grad():
+        layer._weights.copy_(torch.from_numpy(W))
+        if pe is not None:
+            layer._positional_embeddings.copy_(torch.from_numpy(pe))
+    xt = torch.from_numpy(x)
+    pos = layer._prepare_positional_embeddings() if Npe > 0 else None
+    if pos is not None:
+        pos = pos.detach()
+    layer.eval()
+    out = {"y_eval": t2n(layer.forward_step_concat(xt, pos)).reshape(B, S, O)}
+    layer.train()
+    y, idx, md, mk, pidx, pmd, pmk = layer.forward_step_concat(xt, pos)
+    out.update(y=t2n(y).reshape(B, S, O), idx=t2n(idx).reshape(B * S, Nt), min_delta=t2n(md).reshape(B * S, Nt),
+               min_k=t2n(mk).reshape(B * S, Nt))
+    if Npe > 0:
+        out.update(pidx=t2n(pidx).reshape(-1), pmin=t2n(pmd).reshape(-1), pmin_k=t2n(pmk).reshape(-1))
+    if policy == GradientType.Internal:
+        layer.set_external_learning_rate_hook(lambda w: cfg["ext_lr"])
+    dx, dw, dpe = layer.backward_step_concat(xt, torch.from_numpy(dY), idx, md, mk, pidx, pmd, pmk)
+    out["dX"] = t2n(dx).reshape(B, S, E)
+    if dpe is not None:
+        out["dPE"] = t2n(dpe)
+    if policy == GradientType.Internal:
+        out["W_after"] = t2n(layer._weights)
+    else:
+        out["dW"] = t2n(dw)
+    save(name, dict(cfg, kind="concat"), in_x=x, in_anchors=anchors, **out)
+
+
 def main():
     prefixes = sys.argv[1:]
     for name, cfg in NONSEQ_FC_CASES.items():
         if not prefixes or any(name.startswith(p) for p in prefixes):
             run_nonseq_fc(name, cfg)
+    for name, cfg in CONCAT_CASES.items():
+        if not prefixes or any(name.startswith(p) for p in prefixes):
+            run_concat(name, cfg)
     for name, cfg in PRODUCT_CASES.items():
         if not prefixes or any(name.startswith(p) for p in prefixes):
             run_product(name, cfg)

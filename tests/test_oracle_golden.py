@@ -141,3 +141,36 @@ def test_product_oracle_matches_reference(name):
         assert np.array_equal(Wb, ref["W_after"])
     else:
         assert np.array_equal(dW, ref["dW"])
+
+
+@pytest.mark.parametrize("name", golden_util.names("concat_"))
+def test_concat_oracle_matches_reference(name):
+    from cases import sequence_inputs
+
+    cfg, ref = golden_util.load(name)
+    S, Nt, Nc, O, Npe, E = cfg["S"], cfg["Nt"], cfg["Nc"], cfg["O"], cfg["Npe"], cfg["E"]
+    n_pe = (S - 1) * (1 if cfg.get("unified_pe") else Nt) * Npe
+    x, anchors, W, pe, dY = sequence_inputs(cfg, Nt * (1 << (2 * Nc + Npe)) * O, n_pe)
+    assert np.array_equal(x, ref["in_x"]) and np.array_equal(anchors, ref["in_anchors"])
+    pe3 = expand_pe(cfg, pe)
+    kw = dict(int_mode=cfg.get("int_mode", False), int_rescaler=cfg.get("int_rescaler", 0.001))
+    y_eval, _ = orc.concat_forward(W, x, pe3, anchors, Nt, Nc, O, Npe, train=False, **kw)
+    y, st = orc.concat_forward(W, x, pe3, anchors, Nt, Nc, O, Npe, train=True, **kw)
+    assert np.array_equal(st["idx"], ref["idx"]) and np.array_equal(st["min_k"], ref["min_k"])
+    assert np.array_equal(st["min_delta"].view(np.int32), ref["min_delta"].view(np.int32))
+    if Npe > 0:
+        assert np.array_equal(st["pidx"], ref["pidx"]) and np.array_equal(st["pmin_k"], ref["pmin_k"])
+        assert np.array_equal(st["pmin"].view(np.int32), ref["pmin"].view(np.int32))
+    assert np.array_equal(y, ref["y"]) and np.array_equal(y_eval, ref["y_eval"])
+    internal = cfg.get("policy") == "internal"
+    Wb = W.copy()
+    dX, dW, dPE = orc.concat_backward(Wb, dY, anchors, st, E, Nc, Npe, lr_meta=cfg.get("lr_meta", 1.0),
+                                      external_lr=cfg["ext_lr"] if internal else -1.0,
+                                      forward_group_size=cfg.get("G", 32), **kw)
+    assert np.array_equal(dX, ref["dX"])
+    if Npe > 0:
+        assert np.array_equal(dPE, ref["dPE"])
+    if internal:
+        assert np.array_equal(Wb, ref["W_after"])
+    else:
+        assert np.array_equal(dW, ref["dW"])
