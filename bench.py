@@ -146,7 +146,11 @@ class LutLayerWorkload:
         self.layer._weights.grad = None
         y = self.layer(x)
         y.backward(dy)
+        if self.allreduce is not None:
+            self.allreduce([self.layer._weights])
         return y
+
+    allreduce = None
 
     def step_device(self):
         return self._run(self.dx, self.ddy)
@@ -360,7 +364,138 @@ class SparseConvNetWorkload:
         return time.perf_counter() - t0
 
 
+class CharTransformerWorkload:
+    """Character-level LUTTransformer training step (forward + cross-entropy + backward).
+
+    vocab 65, context 128, batch 64, d_model 256, 4 layers, 4 heads, LUT attention (product mode, 2^8-row
+    tables, 16 detectors per head, 4 positional dims) and LUT FFN / unembedder (16 detectors x 8 pairs), fp32
+    tables N(0, 0.02).  Tokens are drawn from a Zipf(s=1.1) distribution over the 65 symbols (seeded synthetic
+    stand-in for the byte-level text the reference trains on).  The configuration does not fix the number
+    of detectors, the positional dimension or the attention mode; the values are the reference notebook's
+    defaults, and product mode is the only one whose table size (2^Nc rows) matches the configuration.
+    """
+
+    metric = "LUTTransformer tokens/sec"
+    unit = "tokens/s"
+    dtype = "f32"
+    dominant_kernel = None
+
+    def __init__(self, batch=64, context=128, vocab=65, d_model=256, layers=4, heads=4, n_detectors=16, nc=8, npe=4):
+        self.B, self.S, self.V, self.E, self.L, self.H = batch, context, vocab, d_model, layers, heads
+        self.Nd, self.Nc, self.Npe = n_detectors, nc, npe
+        self.units_per_step = batch * context
+        self.name = (f"LUTTransformer training step (vocab {vocab}, context {context}, batch {batch}, d_model {d_model}, "
+                     f"{layers} layers, {heads} heads, {n_detectors} detectors/head, Nc={nc}, product attention, Npe={npe})")
+
+    def build(self, device):
+        import torch
+        from spiky_b200.lut_transformer import LUTTransformer
+        from spiky_b200.lut_layer import SynapseMeta
+        model = LUTTransformer(self.V, self.E, self.S, self.Npe, self.L, self.H, self.Nd, self.Nc,
+                               concatenation_product=False, seed=11, device=device,
+                               synapse_meta=SynapseMeta(min_weight=-1.0, max_weight=1.0))
+        gen = torch.Generator().manual_seed(12)
+        with torch.no_grad():
+            for layer in model._lut_layers():
+                layer._weights.copy_(torch.empty(layer._weights.shape).normal_(0.0, 0.02, generator=gen))
+        return model
+
+    def host_tokens(self, seed, batch):
+        import torch
+        p = torch.arange(1, self.V + 1, dtype=torch.float64) ** -1.1
+        gen = torch.Generator().manual_seed(seed)
+        return torch.multinomial(p / p.sum(), batch * (self.S + 1), replacement=True, generator=gen).view(batch, self.S + 1)
+
+    def setup(self, device, rank):
+        self.model = self.build(device)
+        self.model.train()
+        self.params = [p for p in self.model.parameters() if p.requires_grad]
+        self.htok = self.host_tokens(1000 + rank, self.B).pin_memory()
+        self.dtok = self.htok.to(device)
+        self.device = device
+        self.h2d_bytes = self.htok.numel() * 8
+        self.d2h_bytes = 4
+        self.l2_note = "flushed"
+
+    allreduce = None
+
+    def _run(self, tok):
+        import torch.nn.functional as F
+        for p in self.params:
+            p.grad = None
+        logits = self.model(tok[:, :-1])
+        loss = F.cross_entropy(logits.reshape(-1, self.V), tok[:, 1:].reshape(-1))
+        loss.backward()
+        if self.allreduce is not None:
+            self.allreduce(self.params)
+        return loss
+
+    def step_device(self):
+        return self._run(self.dtok)
+
+    def step_e2e(self):
+        return float(self._run(self.htok.to(self.device, non_blocking=True)).item())
+
+    def algorithmic_bytes(self):
+        """Per token and kernel family, summed over the layers (attention: per token = (S-1)/2 pairs on average)."""
+        E, V, Nt, Na, O = self.E, self.V, self.Nd, self.Nd * self.H, self.E
+        pairs = (self.S - 1) / 2.0
+        fc = lambda o: dict(fwd=4 * Nt + 4 * Nt * o + 4 * o, dx=4 * o + 12 * Nt + 8 * Nt * o + 16 * Nt, dw=4 * o + 4 * Nt + 8 * Nt * o)
+        ffn, un = fc(E), fc(V)
+        return {
+            "check_detectors": (self.L + 1) * (4 * E + 12 * Nt),
+            "fc_gather_forward": self.L * ffn["fwd"] + un["fwd"],
+            "fc_input_grad": self.L * ffn["dx"] + un["dx"],
+            "fc_weight_grad": self.L * ffn["dw"] + un["dw"],
+            "product_forward": self.L * (pairs * Na * 4 * O + 4 * E + 4 * O),
+            "product_backward": self.L * (pairs * Na * 16 * O + 4 * O + 8 * E),
+        }
+
+    def cpu_step(self, batch, threads):
+        """Forward + backward of `batch` sequences with the oracle's layer functions (same model)."""
+        import numpy as np
+        from oracle import lut_oracle as orc
+        if getattr(self, "_cpu_model", None) is None:
+            self._cpu_model = self.build(None)
+        m = self._cpu_model
+        tok = self.host_tokens(77, batch).numpy()
+        orc.set_threads(threads)
+        S, E, V = self.S, self.E, self.V
+        t0 = time.perf_counter()
+        z = m.token_embedder.weight.detach().numpy()[tok[:, :-1]]
+        tape = []
+        for block in m.layers:
+            a, f = block["attention_lut"], block["ffn"]
+            Wa, Aa = a._weights.detach().numpy(), a._detector_anchors.numpy()
+            pe = a._prepare_positional_embeddings().detach().numpy().reshape(S - 1, a._n_detectors, -1)
+            tape.append(("att", z.copy(), Wa, Aa, pe, a))
+            z = z + orc.product_forward(Wa, z, pe, Aa, a._n_detectors, self.Nc, E, self.Npe)
+            Wf, Af = f._weights.detach().numpy(), f._detector_anchors.numpy()
+            y, idx, md, mk = orc.nonseq_fc_forward(Wf, z.reshape(-1, E), Af, self.Nd, self.Nc, E)
+            tape.append(("ffn", Wf, Af, idx, md, mk))
+            z = z + y.reshape(z.shape)
+        u = m.unembedder
+        Wu, Au = u._weights.detach().numpy(), u._detector_anchors.numpy()
+        logits, idx, md, mk = orc.nonseq_fc_forward(Wu, z.reshape(-1, E), Au, self.Nd, self.Nc, V)
+        p = np.exp(logits - logits.max(axis=1, keepdims=True))
+        p /= p.sum(axis=1, keepdims=True)
+        p[np.arange(p.shape[0]), tok[:, 1:].reshape(-1)] -= 1.0
+        dz, _ = orc.nonseq_fc_backward(Wu, (p / p.shape[0]).astype(np.float32), Au, idx, md, mk, E, self.Nc)
+        dz = dz.reshape(z.shape)
+        for rec in reversed(tape):
+            if rec[0] == "ffn":
+                _, Wf, Af, idx, md, mk = rec
+                dx, _ = orc.nonseq_fc_backward(Wf, dz.reshape(-1, E), Af, idx, md, mk, E, self.Nc)
+                dz = dz + dx.reshape(dz.shape)
+            else:
+                _, zin, Wa, Aa, pe, a = rec
+                dx, _, _ = orc.product_backward(Wa, zin, pe, Aa, dz, a._n_detectors, self.Nc, self.Npe)
+                dz = dz + dx
+        return time.perf_counter() - t0
+
+
 WORKLOADS = {
+    "char_transformer": lambda: CharTransformerWorkload(),
     "sparse_convnet": lambda: SparseConvNetWorkload(),
     "lut_layer": lambda: LutLayerWorkload(),
     "lut_layer_b256": lambda: LutLayerWorkload(batch=256),
@@ -371,15 +506,17 @@ DEFAULT_WORKLOAD = "sparse_convnet"
 def cpu_baseline(wl, budget_s=12.0):
     """Times the CPU oracle on a bounded sample of the workload (rank 0, N=1 only)."""
     threads = os.cpu_count() or 1
-    batch = min(wl.units_per_step, 256)
+    per_item = getattr(wl, "S", 1) if wl.unit == "tokens/s" else 1   # units per batch item
+    full = wl.units_per_step // per_item
+    batch = min(full, 256 if per_item == 1 else 1)
     dt = wl.cpu_step(batch, threads)  # warm-up and calibration
     per_unit = max(dt / batch, 1e-9)
-    batch = int(max(batch, min(wl.units_per_step, budget_s / 3 / per_unit)))
-    times = [wl.cpu_step(batch, threads) for _ in range(3)]
+    batch = int(max(batch, min(full, budget_s / 3 / per_unit)))
+    times = [wl.cpu_step(batch, threads) for _ in range(3 if per_item == 1 else 1)]
     best = min(times)
-    return {"value": batch / best, "unit": wl.unit, "cores": threads, "kind": "port",
-            "sample": f"{batch} samples of the same workload, best of 3, OpenMP over samples/detectors "
-                      f"({threads} threads; the reference's own CPU path is single-threaded)"}
+    return {"value": batch * per_item / best, "unit": wl.unit, "cores": threads, "kind": "port",
+            "sample": f"{batch} batch items ({batch * per_item} {wl.unit.split('/')[0]}) of the same workload, best of "
+                      f"{len(times)}, OpenMP ({threads} threads; the reference's own CPU path is single-threaded)"}
 
 
 # ------------------------------------------------------------------------------------ arms
@@ -389,17 +526,20 @@ def run_reference(args):
         return
     wl = WORKLOADS[args.workload]()
     threads = os.cpu_count() or 1
-    batch = min(wl.units_per_step, 256)
+    per_item = getattr(wl, "S", 1) if wl.unit == "tokens/s" else 1   # units per batch item
+    full = wl.units_per_step // per_item
+    batch = min(full, 256 if per_item == 1 else 1)
     per_unit = max(wl.cpu_step(batch, threads) / batch, 1e-9)
     # each step is a bounded sample so that warmup + steps stay within ~2 minutes in total
     total = max(1, args.steps + args.warmup)
-    batch = int(max(64, min(wl.units_per_step, 100.0 / total / per_unit)))
+    batch = int(max(1 if per_item > 1 else 64, min(full, 100.0 / total / per_unit)))
     for _ in range(args.warmup):
         wl.cpu_step(batch, threads)
     times = [wl.cpu_step(batch, threads) for _ in range(args.steps)]
     ms = 1e3 * sum(times) / len(times)
-    value = batch / (ms / 1e3)
-    sample = f"{batch} samples per step of the same workload, CPU oracle (port of the reference CPU path), {threads} threads"
+    value = batch * per_item / (ms / 1e3)
+    sample = (f"{batch} batch items ({batch * per_item} {wl.unit.split('/')[0]}) per step of the same workload, CPU oracle "
+              f"(port of the reference CPU path), {threads} threads")
     print(json.dumps({
         "impl": "reference", "metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
@@ -426,6 +566,9 @@ def run_ours(args):
 
     wl = WORKLOADS[args.workload]()
     wl.setup(device, rank)
+    if world > 1:
+        from spiky_b200.data_parallel import allreduce_gradients
+        wl.allreduce = lambda params: allreduce_gradients(params, average=True)
     flush = None
     if wl.l2_note == "flushed":
         flush = torch.empty(2 * L2_BYTES, dtype=torch.uint8, device=device)

@@ -1,0 +1,16 @@
+// Sorted (deterministic) table-gradient variant of the non-sequence fully connected layer.
+#pragma once
+#include "lutb_common.cuh"
+
+namespace lutb {
+
+// bytes of int32 scratch: per-(detector, row, 1024-sample block) counters + the sorted sample lists
+size_t fc_dw_sorted_workspace(int64_t batch, int n_detectors, int table_rows);
+
+// target[t, idx[b, t], :] += lr * dY[b, :] (|dY| > EPS), samples added in ascending order per cell.
+// `workspace` must hold fc_dw_sorted_workspace() bytes.
+int launch_fc_dw_sorted(const float *dY, const int32_t *idx, float *target, int64_t batch, int n_outputs,
+                        int n_detectors, int table_rows, double lr, void *workspace, cudaStream_t stream,
+                        bool clear_with_memset = true);
+
+}  // namespace lutb

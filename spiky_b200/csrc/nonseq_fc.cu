@@ -3,6 +3,7 @@
 // path is gather/scatter bound.
 #include "lutb_common.cuh"
 #include "nonseq_fc.cuh"
+#include "fc_dw_sorted.cuh"
 
 namespace lutb {
 
@@ -581,7 +582,7 @@ __global__ void __launch_bounds__(256) fc_weight_grad_atomic_kernel(const float 
 
 int launch_fc_backward(const lutb_layer_cfg *cfg, int64_t batch, float *W, const float *dY, const int32_t *anchors,
                        const int32_t *idx, const float *min_delta, const int32_t *min_k, float *dX, float *target,
-                       double lr, cudaStream_t stream) {
+                       double lr, cudaStream_t stream, bool skip_table_gradient = false) {
     const int O = cfg->n_outputs, Nt = cfg->n_detectors, T = 1 << cfg->n_anchors;
     const bool int_mode = cfg->int_mode != 0;
     const bool vec4 = (O % 4 == 0) && ((reinterpret_cast<uintptr_t>(W) & 15) == 0) &&
@@ -615,6 +616,7 @@ int launch_fc_backward(const lutb_layer_cfg *cfg, int64_t batch, float *W, const
     }
     LUTB_LAUNCH_CHECK();
 
+    if (skip_table_gradient) return LUTB_OK;
     // table gradient (or in-place update)
     const int chunk = min(O, lanes * kFwdJ * vec);
     const int n_chunks = (O + chunk - 1) / chunk;
@@ -663,18 +665,26 @@ extern "C" int lutb_nonseq_fc_forward(const lutb_layer_cfg *cfg, int64_t batch, 
 }
 
 extern "C" size_t lutb_nonseq_fc_backward_workspace(const lutb_layer_cfg *cfg, int64_t batch, int dw_variant) {
-    (void)cfg; (void)batch; (void)dw_variant;
-    return 0;
+    if (cfg == nullptr || batch <= 0 || dw_variant != LUTB_DW_SORTED || cfg->int_mode) return 0;
+    return fc_dw_sorted_workspace(batch, cfg->n_detectors, 1 << cfg->n_anchors);
 }
 
 extern "C" int lutb_nonseq_fc_backward(const lutb_layer_cfg *cfg, int64_t batch, float *weights, const float *dY,
                                        const int32_t *anchors, const int32_t *idx, const float *min_delta,
                                        const int32_t *min_k, float *dX, float *dW, double external_lr, int dw_variant,
                                        void *workspace, size_t workspace_bytes, void *stream) {
-    (void)dw_variant; (void)workspace; (void)workspace_bytes;
     int rc = validate_cfg(cfg);
     if (rc) return rc;
     LUTB_REQUIRE(cfg->seq_len == 1, LUTB_ERR_MODE, "backward_backprop should only be called when sequence_length == 1");
+    LUTB_REQUIRE(dw_variant >= LUTB_DW_AUTO && dw_variant <= LUTB_DW_SORTED, LUTB_ERR_MODE, "unknown dw_variant");
+    // fixed-point sums are order independent already: the sorted variant only applies to fp32 accumulators
+    const bool sorted = dw_variant == LUTB_DW_SORTED && !cfg->int_mode;
+    if (sorted) {
+        const size_t need = fc_dw_sorted_workspace(batch, cfg->n_detectors, 1 << cfg->n_anchors);
+        LUTB_REQUIRE(workspace != nullptr && workspace_bytes >= need, LUTB_ERR_WORKSPACE,
+                     "the sorted table-gradient variant needs %zu bytes of workspace", need);
+        LUTB_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, LUTB_ERR_ALIGN, "workspace must be 256-byte aligned");
+    }
     LUTB_REQUIRE(batch > 0, LUTB_ERR_SHAPE, "batch_size == 0");
     LUTB_REQUIRE(weights && dY && anchors && idx && min_delta && min_k && dX, LUTB_ERR_NULL,
                  "a required tensor pointer is NULL");
@@ -686,8 +696,13 @@ extern "C" int lutb_nonseq_fc_backward(const lutb_layer_cfg *cfg, int64_t batch,
     // the reference narrows external_lr to fp32 before use (lut.cu:1076)
     if (external_lr >= 0.0) lr *= -(double)(float)external_lr;
     float *target = external_lr >= 0.0 ? weights : dW;
-    rc = launch_fc_backward(cfg, batch, weights, dY, anchors, idx, min_delta, min_k, dX, target, lr, st);
+    rc = launch_fc_backward(cfg, batch, weights, dY, anchors, idx, min_delta, min_k, dX, target, lr, st, sorted);
     if (rc) return rc;
+    if (sorted) {
+        rc = launch_fc_dw_sorted(dY, idx, target, batch, cfg->n_outputs, cfg->n_detectors, 1 << cfg->n_anchors, lr,
+                                 workspace, st);
+        if (rc) return rc;
+    }
     if (cfg->int_mode) {
         rc = launch_fixed_to_float(dX, batch * (int64_t)cfg->n_inputs, cfg->int_rescaler, st);
         if (rc) return rc;

@@ -1,0 +1,74 @@
+"""Data-parallel glue for LUT models: one process per GPU, identical replicas, batch split per rank.
+
+The reference is single-process; this module adds the one exchange step data parallelism needs: table
+gradients (and positional-embedding gradients) are sums over the batch, so after every backward the ranks
+all-reduce them (NCCL over NVLink on GPUs; any torch.distributed backend works, gloo is used by the CPU
+tests).  Forward outputs and input gradients are per-sample and need no communication.
+
+Replicas must be built from the same seeds: anchors are structure, not parameters, and are never
+synchronised afterwards; ``broadcast_structure`` copies rank 0's anchors and parameters once at start-up.
+"""
+import torch
+import torch.distributed as dist
+
+
+def _buckets(tensors, bucket_bytes):
+    bucket, size = [], 0
+    for t in tensors:
+        nbytes = t.numel() * t.element_size()
+        if bucket and size + nbytes > bucket_bytes:
+            yield bucket
+            bucket, size = [], 0
+        bucket.append(t)
+        size += nbytes
+    if bucket:
+        yield bucket
+
+
+def allreduce_gradients(params, group=None, average=False, bucket_bytes=256 << 20):
+    """Sum (or average) the dense ``.grad`` of every parameter over the ranks, in place.
+
+    Large gradients (a table's dW is as large as the table) are reduced in place one by one; small ones are
+    packed into flat buckets first so that the collective's launch latency is paid once per bucket.
+    Sparse gradients are densified per parameter before the reduction.
+    """
+    if not dist.is_available() or not dist.is_initialized() or dist.get_world_size(group) == 1:
+        return
+    world = dist.get_world_size(group)
+    grads = []
+    for p in params:
+        if p.grad is None:
+            continue
+        if p.grad.is_sparse:
+            p.grad = p.grad.to_dense()
+        grads.append(p.grad)
+    small_limit = 4 << 20
+    large = [g for g in grads if g.numel() * g.element_size() >= small_limit]
+    small = [g for g in grads if g.numel() * g.element_size() < small_limit]
+    for g in large:
+        dist.all_reduce(g, op=dist.ReduceOp.SUM, group=group)
+        if average:
+            g.div_(world)
+    for bucket in _buckets(small, bucket_bytes):
+        flat = torch.cat([g.reshape(-1) for g in bucket])
+        dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=group)
+        if average:
+            flat.div_(world)
+        offset = 0
+        for g in bucket:
+            g.copy_(flat[offset:offset + g.numel()].view_as(g))
+            offset += g.numel()
+
+
+def broadcast_structure(module, src=0, group=None):
+    """Make every rank's replica identical to rank ``src``'s: parameters and buffers (anchors included)."""
+    if not dist.is_available() or not dist.is_initialized() or dist.get_world_size(group) == 1:
+        return
+    for t in list(module.parameters()) + list(module.buffers()):
+        dist.broadcast(t.data, src=src, group=group)
+
+
+def shard_batch(n, rank, world):
+    """[begin, end) of the contiguous slice of an ``n``-sample batch owned by ``rank``."""
+    per = (n + world - 1) // world
+    return min(n, rank * per), min(n, (rank + 1) * per)

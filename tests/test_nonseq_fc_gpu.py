@@ -156,3 +156,34 @@ def test_runtime_errors_mirror_reference():
     with pytest.raises(ValueError):
         dm.forward_step(w, 0, torch.zeros(8, device=dev), torch.zeros(16, dtype=torch.int32, device=dev),
                         torch.zeros(4, device=dev), torch.zeros(4, dtype=torch.int32, device=dev))
+
+
+@pytest.mark.parametrize("name", ["c1_full_f32", "ragged", "ffn_like"])
+def test_sorted_table_gradient_is_bit_exact_and_deterministic(name):
+    """LUTB_DW_SORTED adds every cell's contributions in ascending sample order with one fp32 rounding each,
+    the order of the reference's host loop: dW equals the oracle's bit for bit, run after run."""
+    cfg = ORACLE_CASES[name]
+    x, anchors, W, dY = nonseq_fc_inputs(cfg)
+    ref = oracle_reference(cfg, x, anchors, W, dY)
+    a = run_gpu(cfg, x, anchors, W, dY, dw_variant=3)
+    b = run_gpu(cfg, x, anchors, W, dY, dw_variant=3)
+    assert np.array_equal(a["dW"], ref["dW"])
+    assert np.array_equal(a["dW"], b["dW"])
+    golden_util.assert_close(a["dX"], ref["dX"], REL, "dX")
+
+
+def test_sorted_variant_rejects_missing_workspace():
+    import ctypes
+    from spiky_b200 import _native
+
+    dm = make_dm(dict(I=8, O=4, Nt=4, Nc=2))
+    cfg = dm._cfg()
+    L = _native.lib()
+    need = L.lutb_nonseq_fc_backward_workspace(ctypes.byref(cfg), 16, 3)
+    assert need > 0 and L.lutb_nonseq_fc_backward_workspace(ctypes.byref(cfg), 16, 1) == 0
+    dev = torch.device("cuda:0")
+    t = lambda n, dt=torch.float32: torch.zeros(n, dtype=dt, device=dev)
+    p = lambda z: ctypes.c_void_p(z.data_ptr())
+    rc = L.lutb_nonseq_fc_backward(ctypes.byref(cfg), 16, p(t(64)), p(t(64)), p(t(16, torch.int32)), p(t(64, torch.int32)),
+                                   p(t(64)), p(t(64, torch.int32)), p(t(128)), p(t(64)), -1.0, 3, None, 0, None)
+    assert rc == -4 and b"workspace" in L.lutb_last_error()
