@@ -105,6 +105,34 @@ int lutb_nonseq_fc_backward(const lutb_layer_cfg *cfg, int64_t batch, float *wei
                             void *workspace, size_t workspace_bytes, void *stream);
 
 /*
+ * Non-sequence, fully connected backward for callers that must not allocate device memory.
+ * No counterpart in the reference (its runtime allocates through torch at every call).
+ *
+ * Who needs it: code that runs where cudaMalloc is unavailable or forbidden - inside a host callback or a
+ * real-time loop that may not block on the allocator, in a process whose memory pool is owned and fully
+ * handed out by another component, or under a memory budget that was fixed at start-up.  Such a caller
+ * cannot provide the workspace that lutb_nonseq_fc_backward(..., LUTB_DW_SORTED, workspace, ...) wants.
+ *
+ * This entry point computes exactly what that call computes (deterministic table gradient: per cell the
+ * samples are added in ascending order; fp32 accumulators only, cfg->int_mode must be 0) but takes its
+ * scratch from an array of LUTB_STATIC_SCRATCH_BYTES bytes that is part of the library's device image.  It
+ * calls no cudaMalloc / cudaFree and no allocating library routine, and it records no profiler events.
+ *   - limit: lutb_nonseq_fc_backward_workspace(cfg, batch, LUTB_DW_SORTED) must not exceed
+ *     LUTB_STATIC_SCRATCH_BYTES; larger problems are refused with LUTB_ERR_WORKSPACE and a message;
+ *   - the first call on a device looks the array's device address up (cudaGetSymbolAddress with that device
+ *     current); make that first call before any stream capture begins;
+ *   - every call on a device shares the one array and overwrites what the previous call left there (the part
+ *     that must start at zero is cleared on the stream first): two calls that overlap on the GPU, e.g. on
+ *     different streams, race; serialise them;
+ *   - every GPU that loads the library carries the array for the life of the process.
+ * Arguments as lutb_nonseq_fc_backward without dw_variant / workspace.
+ */
+#define LUTB_STATIC_SCRATCH_BYTES (8u << 20)
+int lutb_nonseq_fc_backward_noalloc(const lutb_layer_cfg *cfg, int64_t batch, float *weights, const float *dY,
+                                    const int32_t *anchors, const int32_t *idx, const float *min_delta,
+                                    const int32_t *min_k, float *dX, float *dW, double external_lr, void *stream);
+
+/*
  * Sparse lookup -> output connectivity (projection / convolution layers), all arrays in device memory.
  * Stands in for the reference's forward-synapse-group arena (ForwardSynapseGroup runs per lookup neuron,
  * spiky_cuda/connections_manager/connections_manager.h:39-66, indexed through NoDelaysIndexedSynapsesInfo,

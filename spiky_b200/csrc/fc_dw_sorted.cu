@@ -8,6 +8,8 @@
 #include "lutb_common.cuh"
 #include "fc_dw_sorted.cuh"
 
+#include <mutex>
+
 namespace lutb {
 
 constexpr int kSortBlock = 1024;  // samples per (detector, block) histogram slice
@@ -128,6 +130,31 @@ int launch_fc_dw_sorted(const float *dY, const int32_t *idx, float *target, int6
     dw_sort_reduce_kernel<<<(unsigned)((segs + 7) / 8), 256, 0, stream>>>(dY, counts, perm, target, batch, n_outputs,
                                                                         n_detectors, table_rows, nblk, lr);
     LUTB_LAUNCH_CHECK();
+    return LUTB_OK;
+}
+
+// ------------------------------------------------------------------------------------------
+// Built-in scratch for callers that cannot allocate device memory.  The array lives in the library's
+// device image: every GPU that loads the library holds it until the process exits.
+// In host code `g_static_scratch` is only a handle for the runtime, not a device address; the address a
+// kernel may use is obtained per device with cudaGetSymbolAddress.
+// ------------------------------------------------------------------------------------------
+static __device__ __align__(256) unsigned char g_static_scratch[LUTB_STATIC_SCRATCH_BYTES];
+
+static std::mutex g_scratch_mutex;
+static void *g_scratch_ptr[64] = {nullptr};
+
+int static_scratch(void **ptr) {
+    int dev = 0;
+    LUTB_CUDA(cudaGetDevice(&dev));
+    LUTB_REQUIRE(dev >= 0 && dev < 64, LUTB_ERR_SHAPE, "device ordinal %d out of range", dev);
+    std::lock_guard<std::mutex> lock(g_scratch_mutex);
+    if (g_scratch_ptr[dev] == nullptr) {
+        void *p = nullptr;
+        LUTB_CUDA(cudaGetSymbolAddress(&p, g_static_scratch));  // resolved for the current device
+        g_scratch_ptr[dev] = p;
+    }
+    *ptr = g_scratch_ptr[dev];
     return LUTB_OK;
 }
 

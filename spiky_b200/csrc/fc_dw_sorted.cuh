@@ -13,4 +13,8 @@ int launch_fc_dw_sorted(const float *dY, const int32_t *idx, float *target, int6
                         int n_detectors, int table_rows, double lr, void *workspace, cudaStream_t stream,
                         bool clear_with_memset = true);
 
+// Device address (on the current device) of the library's built-in scratch array of
+// LUTB_STATIC_SCRATCH_BYTES bytes; resolved once per device on first use.
+int static_scratch(void **ptr);
+
 }  // namespace lutb

@@ -90,9 +90,13 @@ static double g_total_ms[K_COUNT];           // resolved time
 static long long g_timed[K_COUNT];           // launches with resolved time
 constexpr size_t kMaxPendingPairs = 1 << 16;
 
+static thread_local int g_no_events = 0;
+NoEventsGuard::NoEventsGuard() { ++g_no_events; }
+NoEventsGuard::~NoEventsGuard() { --g_no_events; }
+
 KernelScope::KernelScope(KernelId id, cudaStream_t stream) : stream_(stream), stop_(nullptr) {
     g_launches[id].fetch_add(1, std::memory_order_relaxed);
-    if (!g_prof_enabled.load(std::memory_order_relaxed)) return;
+    if (!g_prof_enabled.load(std::memory_order_relaxed) || g_no_events > 0) return;
     std::lock_guard<std::mutex> lock(g_prof_mutex);
     if (g_pairs.size() >= kMaxPendingPairs) return;
     EventPair p;

@@ -54,6 +54,14 @@ DeviceInfo device_info();
 
 int validate_cfg(const lutb_layer_cfg *cfg);
 
+// While an instance lives on a thread, KernelScope only counts launches on that thread and never creates
+// CUDA events (event creation allocates); used by entry points that promise not to allocate.
+class NoEventsGuard {
+public:
+    NoEventsGuard();
+    ~NoEventsGuard();
+};
+
 // Kernel families, as reported by the opt-in profiler (lutb_profiler_*) and the launch counter.
 enum KernelId {
     K_CHECK_DETECTORS = 0,

@@ -710,3 +710,24 @@ extern "C" int lutb_nonseq_fc_backward(const lutb_layer_cfg *cfg, int64_t batch,
     }
     return rc;
 }
+
+extern "C" int lutb_nonseq_fc_backward_noalloc(const lutb_layer_cfg *cfg, int64_t batch, float *weights,
+                                               const float *dY, const int32_t *anchors, const int32_t *idx,
+                                               const float *min_delta, const int32_t *min_k, float *dX, float *dW,
+                                               double external_lr, void *stream) {
+    NoEventsGuard no_events;  // event creation allocates
+    int rc = validate_cfg(cfg);
+    if (rc) return rc;
+    LUTB_REQUIRE(cfg->int_mode == 0, LUTB_ERR_MODE,
+                 "the no-allocation backward supports fp32 accumulators only (int_mode must be 0)");
+    LUTB_REQUIRE(batch > 0, LUTB_ERR_SHAPE, "batch_size == 0");
+    const size_t need = fc_dw_sorted_workspace(batch, cfg->n_detectors, 1 << cfg->n_anchors);
+    LUTB_REQUIRE(need <= (size_t)LUTB_STATIC_SCRATCH_BYTES, LUTB_ERR_WORKSPACE,
+                 "problem needs %zu bytes of scratch, the built-in array holds %u: reduce the batch or use "
+                 "lutb_nonseq_fc_backward with a caller workspace", need, (unsigned)LUTB_STATIC_SCRATCH_BYTES);
+    void *scratch = nullptr;
+    rc = static_scratch(&scratch);
+    if (rc) return rc;
+    return lutb_nonseq_fc_backward(cfg, batch, weights, dY, anchors, idx, min_delta, min_k, dX, dW, external_lr,
+                                   LUTB_DW_SORTED, scratch, (size_t)LUTB_STATIC_SCRATCH_BYTES, stream);
+}
