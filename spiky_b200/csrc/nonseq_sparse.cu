@@ -35,7 +35,7 @@ __device__ __forceinline__ int hole_offset(int p, const SparseView &sp) {
 // cover the synapses of a row, so every row access is one contiguous segment and all row reads of a
 // sample are in flight together.  Rows of up to LG synapses use LG-lane groups (NG = 32 / LG groups
 // take detectors round-robin).
-constexpr int kSampleRun = 8;
+constexpr int kSampleRun = 4;
 
 struct ChunkStatic {
     int det0, ndet, toff, P, stride, table;
@@ -102,7 +102,7 @@ __device__ __forceinline__ void chunk_forward(const SparseView &sp, const ChunkS
 }
 
 template <bool INT_MODE>
-__global__ void __launch_bounds__(256) sparse_forward_kernel(SparseView sp, const float *__restrict__ W,
+__global__ void __launch_bounds__(256, 4) sparse_forward_kernel(SparseView sp, const float *__restrict__ W,
                                                             const int32_t *__restrict__ idx, float *__restrict__ y,
                                                             int64_t batch, int n_outputs, int n_detectors,
                                                             double fixed_scale) {
@@ -245,7 +245,7 @@ __device__ __forceinline__ void chunk_backward(const SparseView &sp, const Chunk
 }
 
 template <bool DO_DX, bool DO_DW, bool INT_DW>
-__global__ void __launch_bounds__(256) sparse_backward_kernel(SparseView sp, const float *__restrict__ W,
+__global__ void __launch_bounds__(256, 4) sparse_backward_kernel(SparseView sp, const float *__restrict__ W,
                                                              const float *__restrict__ dY,
                                                              const int2 *__restrict__ anchors,
                                                              const int32_t *__restrict__ idx,
