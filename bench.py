@@ -152,6 +152,9 @@ class LutLayerWorkload:
 
     allreduce = None
 
+    def trainable_parameters(self):
+        return [self.layer._weights]
+
     def step_device(self):
         return self._run(self.dx, self.ddy)
 
@@ -282,6 +285,9 @@ class SparseConvNetWorkload:
         return loss
 
     allreduce = None
+
+    def trainable_parameters(self):
+        return self.grad_params
 
     def step_device(self):
         return self._run(self.dx, self.dl)
@@ -418,6 +424,9 @@ class CharTransformerWorkload:
         self.l2_note = "flushed"
 
     allreduce = None
+
+    def trainable_parameters(self):
+        return self.params
 
     def _run(self, tok):
         import torch.nn.functional as F
@@ -567,8 +576,11 @@ def run_ours(args):
     wl = WORKLOADS[args.workload]()
     wl.setup(device, rank)
     if world > 1:
-        from spiky_b200.data_parallel import allreduce_gradients
-        wl.allreduce = lambda params: allreduce_gradients(params, average=True)
+        # gradients are exchanged per parameter as soon as its backward has run, overlapping the rest of
+        # the backward pass; the workload only waits for the outstanding collectives before it updates
+        from spiky_b200.data_parallel import OverlappedGradientSync
+        sync = OverlappedGradientSync(wl.trainable_parameters(), average=True)
+        wl.allreduce = lambda params: sync.wait()
     flush = None
     if wl.l2_note == "flushed":
         flush = torch.empty(2 * L2_BYTES, dtype=torch.uint8, device=device)

@@ -72,3 +72,45 @@ def shard_batch(n, rank, world):
     """[begin, end) of the contiguous slice of an ``n``-sample batch owned by ``rank``."""
     per = (n + world - 1) // world
     return min(n, rank * per), min(n, (rank + 1) * per)
+
+
+class OverlappedGradientSync:
+    """All-reduces each parameter's gradient as soon as autograd has produced it, on the collective's own
+    stream, so that the exchange of the last layers' table gradients overlaps the backward pass of the earlier
+    layers (the tables of the last layer finish first).  Call ``wait()`` before the optimiser step.
+
+    Only dense gradients are handled; parameters whose layer uses the Internal policy have no gradient and are
+    skipped (their update happens inside the backward kernel and would need reduce-then-apply instead).
+    """
+
+    def __init__(self, params, group=None, average=True):
+        self.group = group
+        self.average = average
+        self.handles = []
+        self.enabled = dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1
+        self.world = dist.get_world_size(group) if self.enabled else 1
+        self._hooks = []
+        if self.enabled:
+            for p in params:
+                if p.requires_grad:
+                    self._hooks.append(p.register_post_accumulate_grad_hook(self._on_grad))
+
+    def _on_grad(self, p):
+        g = p.grad
+        if g is None:
+            return
+        if g.is_sparse:
+            p.grad = g = g.to_dense()
+        if self.average:
+            g.div_(self.world)
+        self.handles.append(dist.all_reduce(g, op=dist.ReduceOp.SUM, group=self.group, async_op=True))
+
+    def wait(self):
+        for h in self.handles:
+            h.wait()
+        self.handles = []
+
+    def remove(self):
+        for h in self._hooks:
+            h.remove()
+        self._hooks = []
