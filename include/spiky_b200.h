@@ -229,6 +229,21 @@ int lutb_concat_backward(const lutb_layer_cfg *cfg, int64_t batch, float *weight
                          const int32_t *pos_idx, const float *pos_min_delta, const int32_t *pos_min_k, float *dX,
                          float *dPE, float *dW, double external_lr, void *stream);
 
+/*
+ * Forward-only inference with int8 tables (non-sequence, fully connected).  No counterpart in the reference,
+ * which has no quantised tables: the result is DEFINED as the reference's int32 fixed-point forward
+ * (LUTDataManagerI::forward_step, spiky_cuda/lut/lut.cu:629-716 with INTEGERS_INSTEAD_OF_FLOATS) run on the
+ * de-quantised table f32(scales[t] * q_tables[t][row][o]).
+ *   q_tables int8 [Nt * 2^Nc * O] (O a multiple of 4), scales fp32 [Nt], x fp32 [batch * I]
+ *   acc int32 [batch * O]: fixed-point accumulators, ADDED to (zero them first); idx int32 [batch * Nt] out
+ * The accumulators of detector shards (each a multiple of cfg->backward_group detectors) add up exactly, on one
+ * GPU or across GPUs; lutb_fixed_to_float then converts in place: y = f32(double(acc) * 2^-20-ish / int_rescaler)
+ * (convert_integers_to_floats_logic, lut_runtime_kernels_logic.proto:200-213).
+ */
+int lutb_infer_int8_accumulate(const lutb_layer_cfg *cfg, int64_t batch, const int8_t *q_tables, const float *scales,
+                               const float *x, const int32_t *anchors, int32_t *acc, int32_t *idx, void *stream);
+int lutb_fixed_to_float(float *buffer, int64_t n, double int_rescaler, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

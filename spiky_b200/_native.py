@@ -79,6 +79,8 @@ SIGNATURES = {
     "lutb_product_backward": (_int, [_cfgp, _i64, ctypes.c_int32, _vp, _vp, _vp, ctypes.c_int32, ctypes.c_int32, _vp, _vp,
                                      _vp, _vp, _vp, _vp, _vp, _dbl, _vp]),
     "lutb_nonseq_fc_backward_noalloc": (_int, [_cfgp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _dbl, _vp]),
+    "lutb_infer_int8_accumulate": (_int, [_cfgp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "lutb_fixed_to_float": (_int, [_vp, _i64, _dbl, _vp]),
     "lutb_nonseq_sparse_forward": (_int, [_cfgp, _spp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "lutb_nonseq_sparse_backward": (_int, [_cfgp, _spp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _dbl, _vp]),
 }

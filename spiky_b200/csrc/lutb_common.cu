@@ -75,6 +75,7 @@ static const char *const kKernelNames[K_COUNT] = {
     "sparse_forward", "sparse_input_grad", "sparse_weight_grad", "sparse_backward_fused",
     "product_forward", "product_backward", "product_weight_update",
     "check_positional", "concat_forward", "concat_backward", "concat_weight_update",
+    "int8_gather",
 };
 
 struct EventPair {

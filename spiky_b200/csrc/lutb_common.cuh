@@ -80,6 +80,7 @@ enum KernelId {
     K_CONCAT_FORWARD,
     K_CONCAT_BACKWARD,
     K_CONCAT_WEIGHT_UPDATE,
+    K_INT8_GATHER,
     K_COUNT
 };
 
