@@ -298,6 +298,9 @@ class SparseConvNetWorkload:
         return float(self._run(x, labels).item())
 
     dominant_kernel = None  # picked by measured time
+    # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) per step of each kernel family, summed over its three
+    # launches, from the ncu capture summarised in profiles/sparse_convnet_step_b512.md
+    ncu_dram_bytes_per_step = {"sparse_backward_fused": 915.8e6, "sparse_forward": 351.2e6, "check_detectors": 7.7e6}
 
     def algorithmic_bytes(self):
         """Per sample and kernel family, summed over the layers that launch it."""
@@ -745,7 +748,9 @@ def run_ours(args):
             "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic",
             "config": {"workload": wl.name, "l2": wl.l2_note, "per_gpu_units": wl.units_per_step},
             "roofline": {"bound": "hbm", "kernel": dom, "achieved": achieved, "peak": peak, "unit": "GB/s",
-                         "frac": achieved / peak, "peak_kind": peak_kind, "traffic": None,
+                         "frac": achieved / peak, "peak_kind": peak_kind,
+                         "traffic": (getattr(wl, "ncu_dram_bytes_per_step", {}).get(dom, 0) / max(d["timed"] / args.steps, 1)) or None,
+                         "algorithmic_bytes_per_launch": alg[dom] * wl.units_per_step / max(d["timed"] / args.steps, 1),
                          "ms_per_launch": dom_ms, "launches_per_step": d["timed"] / args.steps},
             "kernels": per_kernel,
             "e2e": {"value": units / (ms_e2e / 1e3), "unit": wl.unit, "h2d_bytes_per_step": wl.h2d_bytes,

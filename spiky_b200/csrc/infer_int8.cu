@@ -15,19 +15,21 @@ namespace lutb {
 // load per lane), NG = 32 / LG groups take the detectors of a block round-robin; the per-group double sums
 // are exact (<= 32 fp32 terms of similar magnitude), so combining them across groups before the truncation
 // gives the same bits as the sequential sum.
+template <int LG>
 __global__ void __launch_bounds__(256) int8_gather_kernel(const int8_t *__restrict__ Q, const float *__restrict__ scales,
                                                          const int32_t *__restrict__ idx, int32_t *__restrict__ acc,
                                                          int64_t batch, int n_outputs, int n_detectors, int table_rows,
-                                                         int det_block, int lanes_per_row, double fixed_scale) {
+                                                         int det_block, double fixed_scale) {
+    constexpr int NG = 32 / LG;   // lane groups; group g takes detectors g, g + NG, ... of every 32
+    constexpr int IT = 32 / NG;   // = LG row loads per lane and 32 detectors, all issued before the first use
     const int lane = threadIdx.x & 31;
     const int64_t b = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (b >= batch) return;
-    const int LG = lanes_per_row, NG = 32 / LG;
     const int g = lane / LG, j = lane - g * LG;
-    const int c0 = blockIdx.y * (LG * 4);
-    const int col = c0 + j * 4;
+    const int col = blockIdx.y * (LG * 4) + j * 4;
     const bool active = col < n_outputs;   // n_outputs is a multiple of 4
     const int32_t *idx_b = idx + b * n_detectors;
+    const int8_t *Qc = Q + col;
     int32_t iacc[4] = {0, 0, 0, 0};
     for (int tb = 0; tb < n_detectors; tb += det_block) {
         const int tend = min(tb + det_block, n_detectors);
@@ -37,21 +39,25 @@ __global__ void __launch_bounds__(256) int8_gather_kernel(const int8_t *__restri
             int32_t my_idx = 0;
             float my_scale = 0.f;
             if (lane < nvalid) { my_idx = __ldg(idx_b + t0 + lane); my_scale = __ldg(scales + t0 + lane); }
-#pragma unroll 4
-            for (int sb = 0; sb < nvalid; sb += NG) {
-                const int d = sb + g;
-                const int32_t li = __shfl_sync(0xffffffffu, my_idx, d & 31);
-                const float sc = __shfl_sync(0xffffffffu, my_scale, d & 31);
-                if (active && d < nvalid) {
-                    const int32_t packed = __ldg(reinterpret_cast<const int32_t *>(
-                        Q + ((size_t)(t0 + d) * table_rows + li) * n_outputs + col));
-                    s[0] += (double)__fmul_rn(sc, (float)(int8_t)(packed & 0xff));
-                    s[1] += (double)__fmul_rn(sc, (float)(int8_t)((packed >> 8) & 0xff));
-                    s[2] += (double)__fmul_rn(sc, (float)(int8_t)((packed >> 16) & 0xff));
-                    s[3] += (double)__fmul_rn(sc, (float)(int8_t)((packed >> 24) & 0xff));
-                }
+            int32_t packed[IT];
+#pragma unroll
+            for (int i = 0; i < IT; i++) {
+                const int d = i * NG + g;
+                const int32_t li = __shfl_sync(0xffffffffu, my_idx, d);
+                packed[i] = (active && d < nvalid)
+                                ? __ldg(reinterpret_cast<const int32_t *>(Qc + ((size_t)(t0 + d) * table_rows + li) * n_outputs))
+                                : 0;
+            }
+#pragma unroll
+            for (int i = 0; i < IT; i++) {
+                const float sc = __shfl_sync(0xffffffffu, my_scale, i * NG + g);   // 0 beyond nvalid
+                s[0] += (double)__fmul_rn(sc, (float)(int8_t)(packed[i] & 0xff));
+                s[1] += (double)__fmul_rn(sc, (float)(int8_t)((packed[i] >> 8) & 0xff));
+                s[2] += (double)__fmul_rn(sc, (float)(int8_t)((packed[i] >> 16) & 0xff));
+                s[3] += (double)__fmul_rn(sc, (float)(int8_t)((packed[i] >> 24) & 0xff));
             }
         }
+#pragma unroll
         for (int m = LG; m < 32; m <<= 1) {
 #pragma unroll
             for (int e = 0; e < 4; e++) s[e] += __shfl_xor_sync(0xffffffffu, s[e], m);
@@ -92,9 +98,18 @@ extern "C" int lutb_infer_int8_accumulate(const lutb_layer_cfg *cfg, int64_t bat
     const int64_t blocks = (batch + 7) / 8;
     LUTB_REQUIRE(blocks <= 0x7FFFFFFF && n_chunks <= 65535, LUTB_ERR_SHAPE, "grid too large");
     KernelScope scope(K_INT8_GATHER, st);
-    int8_gather_kernel<<<dim3((unsigned)blocks, (unsigned)n_chunks), 256, 0, st>>>(
-        q_tables, scales, idx, acc, batch, cfg->n_outputs, cfg->n_detectors, 1 << cfg->n_anchors, cfg->backward_group,
-        lanes, cfg->int_rescaler);
+    const dim3 grid((unsigned)blocks, (unsigned)n_chunks);
+#define LUTB_INT8(LGV) int8_gather_kernel<LGV><<<grid, 256, 0, st>>>(q_tables, scales, idx, acc, batch, cfg->n_outputs, \
+        cfg->n_detectors, 1 << cfg->n_anchors, cfg->backward_group, cfg->int_rescaler)
+    switch (lanes) {
+        case 32: LUTB_INT8(32); break;
+        case 16: LUTB_INT8(16); break;
+        case 8: LUTB_INT8(8); break;
+        case 4: LUTB_INT8(4); break;
+        case 2: LUTB_INT8(2); break;
+        default: LUTB_INT8(1); break;
+    }
+#undef LUTB_INT8
     LUTB_LAUNCH_CHECK();
     return LUTB_OK;
 }

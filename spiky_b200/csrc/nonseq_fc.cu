@@ -352,6 +352,60 @@ __global__ void __launch_bounds__(256) fc_gather_forward_kernel(const float *__r
     }
 }
 
+// Fast path of the forward gather for fp32 accumulators and 16-byte aligned rows: one warp per (sample,
+// chunk of LG float4 columns); the row loads of up to 16 detectors per lane are all issued before the first
+// one is consumed, which is what hides the latency of the (random) row reads.
+template <int LG>
+__global__ void __launch_bounds__(256) fc_gather_forward_vec_kernel(const float *__restrict__ W,
+                                                                   const int32_t *__restrict__ idx,
+                                                                   float *__restrict__ y, int64_t batch, int n_outputs,
+                                                                   int n_detectors, int table_rows, int t0, int t1) {
+    constexpr int NG = 32 / LG;
+    constexpr int IT = 32 / NG;                  // row loads per lane and 32 detectors
+    constexpr int BATCH = IT > 16 ? 16 : IT;     // loads in flight per lane
+    const int lane = threadIdx.x & 31;
+    const int64_t b = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (b >= batch) return;
+    const int g = lane / LG, j = lane - g * LG;
+    const int col = (blockIdx.y * LG + j) * 4;
+    const bool active = col < n_outputs;
+    const int32_t *idx_b = idx + b * n_detectors;
+    const float *Wc = W + col;
+    double acc[4] = {0.0, 0.0, 0.0, 0.0};
+    for (int tb = t0; tb < t1; tb += 32) {
+        const int nvalid = min(32, t1 - tb);
+        const int32_t mine = (lane < nvalid) ? __ldg(idx_b + tb + lane) : 0;
+        float part[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int i0 = 0; i0 < IT; i0 += BATCH) {
+            float4 w[BATCH];
+#pragma unroll
+            for (int i = 0; i < BATCH; i++) {
+                const int d = (i0 + i) * NG + g;
+                const int32_t li = __shfl_sync(0xffffffffu, mine, d);
+                w[i] = (active && d < nvalid)
+                           ? __ldg(reinterpret_cast<const float4 *>(Wc + ((size_t)(tb + d) * table_rows + li) * n_outputs))
+                           : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int i = 0; i < BATCH; i++) { part[0] += w[i].x; part[1] += w[i].y; part[2] += w[i].z; part[3] += w[i].w; }
+        }
+#pragma unroll
+        for (int e = 0; e < 4; e++) acc[e] += (double)part[e];
+    }
+#pragma unroll
+    for (int m = LG; m < 32; m <<= 1) {
+#pragma unroll
+        for (int e = 0; e < 4; e++) acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], m);
+    }
+    if (active && g == 0) {
+        float4 *out = reinterpret_cast<float4 *>(y + b * n_outputs + col);
+        float4 cur = *out;
+        cur.x += (float)acc[0]; cur.y += (float)acc[1]; cur.z += (float)acc[2]; cur.w += (float)acc[3];
+        *out = cur;
+    }
+}
+
 static int pow2_ceil(int v) {
     int p = 1;
     while (p < v) p <<= 1;
@@ -381,7 +435,19 @@ int launch_fc_gather_forward(const float *W, const int32_t *idx, float *y, int64
     for (int64_t t0 = 0; t0 < n_detectors; t0 += per_range) {
         const int t1 = (int)min((int64_t)n_detectors, t0 + per_range);
         KernelScope scope(K_FC_GATHER_FORWARD, stream);
-        if (vec4) {
+        if (vec4 && !int_mode) {
+            const dim3 vgrid((unsigned)blocks, (unsigned)((vpr + lanes - 1) / lanes));
+#define LUTB_FWD(LGV) fc_gather_forward_vec_kernel<LGV><<<vgrid, warps * 32, 0, stream>>>(W, idx, y, batch, n_outputs, n_detectors, table_rows, (int)t0, t1)
+            switch (lanes) {
+                case 32: LUTB_FWD(32); break;
+                case 16: LUTB_FWD(16); break;
+                case 8: LUTB_FWD(8); break;
+                case 4: LUTB_FWD(4); break;
+                case 2: LUTB_FWD(2); break;
+                default: LUTB_FWD(1); break;
+            }
+#undef LUTB_FWD
+        } else if (vec4) {
             if (int_mode)
                 fc_gather_forward_kernel<4, true><<<grid, warps * 32, 0, stream>>>(W, idx, y, batch, n_outputs, n_detectors, table_rows, (int)t0, t1, det_block, lanes, chunk, fixed_scale);
             else
