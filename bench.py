@@ -461,6 +461,13 @@ class CharTransformerWorkload:
             "fc_weight_grad": self.L * ffn["dw"] + un["dw"],
             "product_forward": self.L * (pairs * Na * 4 * O + 4 * E + 4 * O),
             "product_backward": self.L * (pairs * Na * 16 * O + 4 * O + 8 * E),
+            # histogram variant of the backward pass: the same algorithmic bytes, split over its kernels
+            # (row pairs read for the input gradient; gradient rows read-modify-written; routing per token)
+            "product_hist": self.L * 4 * E,
+            "product_row_dots": self.L * pairs * Na * 8 * O,
+            "product_route": self.L * (4 * O + 8 * E),
+            "product_hist_weight_grad": self.L * pairs * Na * 8 * O,
+            "product_hist_forward": self.L * (pairs * Na * 4 * O + 4 * O),
         }
 
     def cpu_step(self, batch, threads):

@@ -192,7 +192,26 @@ int lutb_nonseq_sparse_backward(const lutb_layer_cfg *cfg, const lutb_sparse_ind
  */
 int lutb_product_forward(const lutb_layer_cfg *cfg, int64_t batch, int32_t seq_len, const float *weights,
                          const float *x1, const float *x2, int32_t n_inputs_1, int32_t n_inputs_2,
-                         const float *pos_embeddings, const int32_t *anchors, float *y, void *stream);
+                         const float *pos_embeddings, const int32_t *anchors, float *y, int variant, void *workspace,
+                         size_t workspace_bytes, void *stream);
+
+/*
+ * Kernel variants of the product-mode layer (no reference counterpart: the reference has one kernel per pass).
+ *   DIRECT  one table row per (pair, detector) is gathered (forward) or gathered twice and scatter-added
+ *           (backward) through L2; needs no workspace.
+ *   HIST    per (query, detector) the selected rows are counted into a histogram first and the pass becomes
+ *           a register-tiled fp32 contraction with the tables (see spiky_b200/csrc/product_hist.cuh); fp32
+ *           accumulators only, 4 <= Nc <= 12, O % 4 == 0, 16-byte aligned tensors, and a caller workspace of at
+ *           least lutb_product_workspace(cfg, 1, S, backward) bytes (the batch is processed in chunks of as
+ *           many sequences as fit); LUTB_ERR_WORKSPACE / LUTB_ERR_MODE when asked for and not possible.
+ *   AUTO    HIST when it is possible, a workspace is supplied and the sequence is long enough against the
+ *           table (forward: S >= 2^Nc; backward: 4 * S >= 2^Nc), else DIRECT.
+ * lutb_product_workspace returns the bytes that let `batch` sequences go through in one chunk.
+ */
+#define LUTB_PRODUCT_AUTO 0
+#define LUTB_PRODUCT_DIRECT 1
+#define LUTB_PRODUCT_HIST 2
+size_t lutb_product_workspace(const lutb_layer_cfg *cfg, int64_t batch, int32_t seq_len, int backward);
 
 /*
  * Product-mode sequence layer, backward.  Replaces LUTDataManager::backward_backprop_product
@@ -203,7 +222,7 @@ int lutb_product_forward(const lutb_layer_cfg *cfg, int64_t batch, int32_t seq_l
 int lutb_product_backward(const lutb_layer_cfg *cfg, int64_t batch, int32_t seq_len, float *weights, const float *x1,
                           const float *x2, int32_t n_inputs_1, int32_t n_inputs_2, const float *pos_embeddings,
                           const int32_t *anchors, const float *dY, float *dX1, float *dX2, float *dPE, float *dW,
-                          double external_lr, void *stream);
+                          double external_lr, int variant, void *workspace, size_t workspace_bytes, void *stream);
 
 /*
  * Concatenation-mode sequence layer, forward.  Replaces LUTDataManager::forward_step_concat

@@ -11,6 +11,8 @@ LIB_PATH = os.path.join(_HERE, "lib", "libspiky_b200.so")
 
 # dW kernel variants (include/spiky_b200.h)
 DW_AUTO, DW_ATOMIC, DW_SMEM, DW_SORTED = 0, 1, 2, 3
+# product-mode kernel variants (include/spiky_b200.h)
+PRODUCT_AUTO, PRODUCT_DIRECT, PRODUCT_HIST = 0, 1, 2
 
 
 class LayerCfg(ctypes.Structure):
@@ -75,9 +77,11 @@ SIGNATURES = {
     "lutb_nonseq_fc_backward": (_int, [_cfgp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _dbl, _int, _vp, _size, _vp]),
     "lutb_concat_forward": (_int, [_cfgp, _i64] + [_vp] * 12),
     "lutb_concat_backward": (_int, [_cfgp, _i64] + [_vp] * 12 + [_dbl, _vp]),
-    "lutb_product_forward": (_int, [_cfgp, _i64, ctypes.c_int32, _vp, _vp, _vp, ctypes.c_int32, ctypes.c_int32, _vp, _vp, _vp, _vp]),
+    "lutb_product_workspace": (_size, [_cfgp, _i64, ctypes.c_int32, _int]),
+    "lutb_product_forward": (_int, [_cfgp, _i64, ctypes.c_int32, _vp, _vp, _vp, ctypes.c_int32, ctypes.c_int32, _vp, _vp, _vp,
+                                    _int, _vp, _size, _vp]),
     "lutb_product_backward": (_int, [_cfgp, _i64, ctypes.c_int32, _vp, _vp, _vp, ctypes.c_int32, ctypes.c_int32, _vp, _vp,
-                                     _vp, _vp, _vp, _vp, _vp, _dbl, _vp]),
+                                     _vp, _vp, _vp, _vp, _vp, _dbl, _int, _vp, _size, _vp]),
     "lutb_nonseq_fc_backward_noalloc": (_int, [_cfgp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _dbl, _vp]),
     "lutb_infer_int8_accumulate": (_int, [_cfgp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "lutb_fixed_to_float": (_int, [_vp, _i64, _dbl, _vp]),

@@ -81,6 +81,11 @@ enum KernelId {
     K_CONCAT_BACKWARD,
     K_CONCAT_WEIGHT_UPDATE,
     K_INT8_GATHER,
+    K_PRODUCT_HIST,
+    K_PRODUCT_HIST_FORWARD,
+    K_PRODUCT_ROW_DOTS,
+    K_PRODUCT_ROUTE,
+    K_PRODUCT_HIST_WEIGHT_GRAD,
     K_COUNT
 };
 

@@ -7,95 +7,11 @@
 // Reference: calculate_product_lookup_index[_backprop] (lut_runtime_kernels_logic.proto:32-198),
 // fill_outputs_product_cpu_logic (:2148-2264), propagate_backward_product_cpu_logic (:2396-2628),
 // gather_w_gradients_internal_product_cpu_logic (:2630-2744).
-#include "lutb_common.cuh"
+#include "product_hist.cuh"
+#include "product_pairs.cuh"
 
 namespace lutb {
 
-constexpr int kMaxPairs = 16;  // anchor pairs per detector supported by the pair kernels (table of 2^16 rows)
-
-// Per-block staging shared by forward and backward.  A block owns one (sample, detector): it gathers
-// the 2*Nc input elements its anchors read from every token of the sample once, so the S*(S-1)/2 pair
-// evaluations run entirely out of shared memory.
-struct PairStage {
-    float *U;        // [S][ustride]  U[s][2k+e] = x[b, s, element(k, e)] for ends that read a token
-    float *PE;       // [S-1][pstride] positional embedding of (distance, this detector)
-    int ustride, pstride;
-    // per anchor end (shared memory): source (0: token i, 1: token j, 2: positional embedding, 3: unused
-    // pair) and element inside that source
-    int *comp;       // [2 * kMaxPairs]
-    int *elem;       // [2 * kMaxPairs]
-    float *scratch;  // 16-byte aligned start of the per-warp scratch area behind the staged data
-};
-
-__device__ __forceinline__ void decode_anchor(int32_t id, bool sliced, int e1, int e2, int &comp, int &elem) {
-    if (id == kNoAnchor) { comp = 3; elem = 0; return; }
-    if (sliced) { elem = id / 3; comp = id % 3; }
-    else if (id < e1) { comp = 0; elem = id; }
-    else if (id < e1 + e2) { comp = 1; elem = id - e1; }
-    else { comp = 2; elem = id - e1 - e2; }
-}
-
-// Evaluates the anchors of one pair (i, j).  Returns the table index; when TRACK also the first anchor of
-// minimal |delta| (strict '<' from FLT_MAX, reference proto:166-173) and that delta.
-template <bool TRACK>
-__device__ __forceinline__ int32_t eval_pair(const PairStage &st, int n_anchors, int i, int j, float cmp_eps,
-                                             int &kmin, float &dmin) {
-    const float *ui = st.U + i * st.ustride;
-    const float *uj = st.U + j * st.ustride;
-    const float *pe = st.PE + (j - i - 1) * st.pstride;
-    int32_t li = 0;
-    float md = 3.402823466e+38F;
-    int mk = -1;
-    for (int k = 0; k < n_anchors; k++) {
-        const int c1 = st.comp[2 * k], c2 = st.comp[2 * k + 1];
-        if (c1 == 3 || c2 == 3) continue;
-        const float v1 = c1 == 0 ? ui[2 * k] : (c1 == 1 ? uj[2 * k] : pe[st.elem[2 * k]]);
-        const float v2 = c2 == 0 ? ui[2 * k + 1] : (c2 == 1 ? uj[2 * k + 1] : pe[st.elem[2 * k + 1]]);
-        const float d = __fsub_rn(v1, v2);
-        if (greater_than_zero(d, cmp_eps)) li |= (1 << k);
-        if (TRACK && fabsf(d) < fabsf(md)) { md = d; mk = k; }
-    }
-    if (TRACK) { kmin = mk; dmin = md; }
-    return li;
-}
-
-__device__ __forceinline__ void stage_pairs(PairStage &st, float *smem, const float *__restrict__ x1b,
-                                            const float *__restrict__ x2b, const float *__restrict__ pe,
-                                            const int32_t *__restrict__ anchors_t, int S, int e1, int e2, int npe,
-                                            int n_anchors, int n_detectors, int t, bool sliced) {
-    st.ustride = (2 * n_anchors) | 1;  // odd strides keep the per-token reads conflict free
-    st.pstride = npe | 1;
-    st.comp = reinterpret_cast<int *>(smem);
-    st.elem = st.comp + 2 * kMaxPairs;
-    st.U = smem + 4 * kMaxPairs;
-    st.PE = st.U + S * st.ustride;
-    st.scratch = st.PE + (((S - 1) * st.pstride + 3) & ~3) + ((4 - ((S * st.ustride) & 3)) & 3);
-    if (threadIdx.x < 2 * kMaxPairs) {
-        int c = 3, e = 0;
-        if (threadIdx.x < 2 * n_anchors) decode_anchor(__ldg(anchors_t + threadIdx.x), sliced, e1, e2, c, e);
-        st.comp[threadIdx.x] = c;
-        st.elem[threadIdx.x] = e;
-    }
-    __syncthreads();
-    for (int w = threadIdx.x; w < S * 2 * n_anchors; w += blockDim.x) {
-        const int s = w / (2 * n_anchors), q = w - s * (2 * n_anchors);
-        float v = 0.f;
-        // an end reads the same element whether its token plays the "i" or the "j" part
-        if (st.comp[q] == 0) v = __ldg(x1b + (size_t)s * e1 + st.elem[q]);
-        else if (st.comp[q] == 1) v = __ldg(x2b + (size_t)s * e2 + st.elem[q]);
-        st.U[s * st.ustride + q] = v;
-    }
-    if (npe > 0) {
-        for (int w = threadIdx.x; w < (S - 1) * npe; w += blockDim.x) {
-            const int d = w / npe, c = w - d * npe;
-            st.PE[d * st.pstride + c] = __ldg(pe + ((size_t)d * n_detectors + t) * npe + c);
-        }
-    }
-    __syncthreads();
-}
-
-// Note on U: an end with source "token i" is read from row i of U, an end with source "token j" from
-// row j; both rows hold x at the end's element, taken from x1 for "i" ends and x2 for "j" ends.
 
 // --------------------------------------------------------------------------------------------
 // Forward.  Block = (detector, sample); each warp takes queries j round-robin: lanes first evaluate 32
@@ -363,11 +279,6 @@ __global__ void product_backward_fixed_kernel(const float *__restrict__ W, const
     }
 }
 
-static size_t pair_stage_floats(int S, int n_anchors, int npe) {
-    // anchor metadata + U + PE, plus slack for the 16-byte alignment of the scratch area behind them
-    return 4 * kMaxPairs + (size_t)S * ((2 * n_anchors) | 1) + (size_t)(S > 1 ? S - 1 : 0) * (npe | 1) + 8;
-}
-
 static int validate_product(const lutb_layer_cfg *cfg, int64_t batch, int S, int e1, int e2) {
     int rc = validate_cfg(cfg);
     if (rc) return rc;
@@ -379,18 +290,50 @@ static int validate_product(const lutb_layer_cfg *cfg, int64_t batch, int S, int
     return LUTB_OK;
 }
 
+// Resolves LUTB_PRODUCT_* into "use the histogram path".
+static int choose_variant(const ProductCall &c, int variant, bool backward, const void *weights, const void *io_rows,
+                          const void *dW, const void *workspace, size_t workspace_bytes, bool &hist) {
+    hist = false;
+    LUTB_REQUIRE(variant == LUTB_PRODUCT_AUTO || variant == LUTB_PRODUCT_DIRECT || variant == LUTB_PRODUCT_HIST,
+                 LUTB_ERR_MODE, "unknown product kernel variant %d", variant);
+    if (variant == LUTB_PRODUCT_DIRECT) return LUTB_OK;
+    const bool possible = product_hist_supported(c, weights, io_rows, dW);
+    if (variant == LUTB_PRODUCT_HIST) {
+        LUTB_REQUIRE(possible, LUTB_ERR_MODE,
+                     "the histogram variant needs fp32 accumulators, 4 <= Nc <= 12, O %% 4 == 0, S >= 2 and 16-byte aligned tensors");
+        hist = true;
+        return LUTB_OK;
+    }
+    const int64_t rows = (int64_t)1 << c.cfg->n_anchors;
+    const bool long_enough = backward ? 4 * (int64_t)c.S >= rows : (int64_t)c.S >= rows;
+    hist = possible && long_enough && workspace != nullptr &&
+           workspace_bytes >= product_hist_bytes_per_sequence(c.cfg, c.S, backward) + 256;
+    return LUTB_OK;
+}
+
 }  // namespace lutb
 
 using namespace lutb;
 
+extern "C" size_t lutb_product_workspace(const lutb_layer_cfg *cfg, int64_t batch, int32_t seq_len, int backward) {
+    if (!cfg || batch <= 0 || seq_len <= 0 || cfg->n_anchors < 1 || cfg->n_anchors > 16) return 0;
+    return (size_t)batch * product_hist_bytes_per_sequence(cfg, seq_len, backward != 0) + 256;
+}
+
 extern "C" int lutb_product_forward(const lutb_layer_cfg *cfg, int64_t batch, int32_t seq_len, const float *weights,
                                     const float *x1, const float *x2, int32_t n_inputs_1, int32_t n_inputs_2,
-                                    const float *pos_embeddings, const int32_t *anchors, float *y, void *stream) {
+                                    const float *pos_embeddings, const int32_t *anchors, float *y, int variant,
+                                    void *workspace, size_t workspace_bytes, void *stream) {
     int rc = validate_product(cfg, batch, seq_len, n_inputs_1, n_inputs_2);
     if (rc) return rc;
     LUTB_REQUIRE(weights && x1 && x2 && anchors && y, LUTB_ERR_NULL, "a required tensor pointer is NULL");
     LUTB_REQUIRE(cfg->pos_dim == 0 || pos_embeddings, LUTB_ERR_NULL, "positional embeddings are NULL");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const ProductCall call{cfg, batch, seq_len, n_inputs_1, n_inputs_2, x1, x2, pos_embeddings, anchors};
+    bool hist = false;
+    rc = choose_variant(call, variant, false, weights, y, nullptr, workspace, workspace_bytes, hist);
+    if (rc) return rc;
+    if (hist) return launch_product_hist_forward(call, weights, y, workspace, workspace_bytes, st);
     if (seq_len > 1) {
         const int warps = 8;
         const size_t smem = (pair_stage_floats(seq_len, cfg->n_anchors, cfg->pos_dim) + (size_t)warps * seq_len) * 4;
@@ -413,7 +356,8 @@ extern "C" int lutb_product_forward(const lutb_layer_cfg *cfg, int64_t batch, in
 extern "C" int lutb_product_backward(const lutb_layer_cfg *cfg, int64_t batch, int32_t seq_len, float *weights,
                                      const float *x1, const float *x2, int32_t n_inputs_1, int32_t n_inputs_2,
                                      const float *pos_embeddings, const int32_t *anchors, const float *dY, float *dX1,
-                                     float *dX2, float *dPE, float *dW, double external_lr, void *stream) {
+                                     float *dX2, float *dPE, float *dW, double external_lr, int variant, void *workspace,
+                                     size_t workspace_bytes, void *stream) {
     int rc = validate_product(cfg, batch, seq_len, n_inputs_1, n_inputs_2);
     if (rc) return rc;
     LUTB_REQUIRE(weights && x1 && x2 && anchors && dY && dX1 && dX2, LUTB_ERR_NULL, "a required tensor pointer is NULL");
@@ -425,6 +369,13 @@ extern "C" int lutb_product_backward(const lutb_layer_cfg *cfg, int64_t batch, i
     const int O = cfg->n_outputs, Nt = cfg->n_detectors, Nc = cfg->n_anchors, npe = cfg->pos_dim;
     double lr = cfg->lr_meta;
     if (external_lr >= 0.0) lr *= -(double)(float)external_lr;
+    const ProductCall call{cfg, batch, seq_len, n_inputs_1, n_inputs_2, x1, x2, pos_embeddings, anchors};
+    bool hist = false;
+    rc = choose_variant(call, variant, true, weights, dY, dW, workspace, workspace_bytes, hist);
+    if (rc) return rc;
+    if (hist)
+        return launch_product_hist_backward(call, weights, dY, dX1, dX2, dPE, external_lr >= 0.0 ? weights : dW, lr,
+                                            external_lr >= 0.0, workspace, workspace_bytes, st);
     if (seq_len > 1) {
         if (cfg->int_mode) {
             const int64_t total = batch * seq_len * (int64_t)Nt * seq_len;

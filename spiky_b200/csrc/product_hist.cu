@@ -1,0 +1,435 @@
+// Histogram formulation of the product-mode sequence layer (see product_hist.cuh).
+//
+// Reference semantics: fill_outputs_product_cpu_logic (lut_runtime_kernels_logic.proto:2148-2264),
+// propagate_backward_product_cpu_logic (:2396-2628), gather_w_gradients_internal_product_cpu_logic (:2630-2744).
+#include "product_hist.cuh"
+#include "product_pairs.cuh"
+
+namespace lutb {
+
+// --------------------------------------------------------------------------------------------
+// Row-selection histogram.  Block = (detector, sequence of the chunk); a warp owns a query j, counts the
+// rows its j keys select in a per-warp shared-memory histogram and writes it out as T uint16 counters.
+// H layout: [detector][row of the chunk = local sequence * S + j][T].
+// --------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) product_hist_kernel(const float *__restrict__ x1, const float *__restrict__ x2,
+                                                          const float *__restrict__ pe,
+                                                          const int32_t *__restrict__ anchors, uint16_t *__restrict__ H,
+                                                          int64_t b0, int64_t chunk_rows, int S, int e1, int e2, int npe,
+                                                          int n_detectors, int n_anchors, int sliced, float cmp_eps) {
+    extern __shared__ __align__(16) float smem[];
+    const int t = blockIdx.x;
+    const int64_t bl = blockIdx.y, b = b0 + bl;
+    PairStage st;
+    stage_pairs(st, smem, x1 + b * S * e1, x2 + b * S * e2, pe, anchors + (size_t)t * n_anchors * 2, S, e1, e2, npe,
+                n_anchors, n_detectors, t, sliced != 0);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+    const int T = 1 << n_anchors;
+    uint32_t *hist = reinterpret_cast<uint32_t *>(st.scratch) + warp * T;
+    for (int r = lane; r < T; r += 32) hist[r] = 0u;
+    __syncwarp();
+    for (int j = warp; j < S; j += nwarps) {
+        for (int i0 = 0; i0 < j; i0 += 32) {
+            const int i = i0 + lane;
+            int km; float dm;
+            if (i < j) atomicAdd(hist + eval_pair<false>(st, n_anchors, i, j, cmp_eps, km, dm), 1u);
+        }
+        __syncwarp();
+        uint16_t *out = H + ((size_t)t * chunk_rows + bl * S + j) * T;
+        for (int r = lane * 8; r < T; r += 256) {
+            const uint4 lo = *reinterpret_cast<const uint4 *>(hist + r);
+            const uint4 hi = *reinterpret_cast<const uint4 *>(hist + r + 4);
+            uint4 packed;
+            packed.x = lo.x | (lo.y << 16);
+            packed.y = lo.z | (lo.w << 16);
+            packed.z = hi.x | (hi.y << 16);
+            packed.w = hi.z | (hi.w << 16);
+            *reinterpret_cast<uint4 *>(out + r) = packed;
+            *reinterpret_cast<uint4 *>(hist + r) = make_uint4(0u, 0u, 0u, 0u);
+            *reinterpret_cast<uint4 *>(hist + r + 4) = make_uint4(0u, 0u, 0u, 0u);
+        }
+        __syncwarp();
+    }
+}
+
+// --------------------------------------------------------------------------------------------
+// Input-gradient routing.  Same block / warp layout; the warp stages Q_t[(b,j), :] (the dot product of
+// dY[b,j,:] with every row of table t) and each pair reads its two entries: g = Q[idx] - Q[idx ^ 2^kmin],
+// du = up(min_delta) * g, +du / -du to the sources of the flipped anchor's two ends.
+// Contributions to the query token's own elements are pre-reduced per warp in shared memory.
+// --------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) product_route_kernel(const float *__restrict__ x1, const float *__restrict__ x2,
+                                                           const float *__restrict__ pe,
+                                                           const int32_t *__restrict__ anchors,
+                                                           const float *__restrict__ Q, float *__restrict__ dX1,
+                                                           float *__restrict__ dX2, float *__restrict__ dPE, int64_t b0,
+                                                           int64_t chunk_rows, int S, int e1, int e2, int npe,
+                                                           int n_detectors, int n_anchors, int sliced, float cmp_eps) {
+    extern __shared__ __align__(16) float smem[];
+    const int t = blockIdx.x;
+    const int64_t bl = blockIdx.y, b = b0 + bl;
+    PairStage st;
+    stage_pairs(st, smem, x1 + b * S * e1, x2 + b * S * e2, pe, anchors + (size_t)t * n_anchors * 2, S, e1, e2, npe,
+                n_anchors, n_detectors, t, sliced != 0);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+    const int T = 1 << n_anchors;
+    float *q_s = st.scratch + warp * (T + 2 * kMaxPairs);
+    float *jacc = q_s + T;  // per anchor end: sum of the contributions that go to the query token j
+    for (int j = 1 + warp; j < S; j += nwarps) {
+        const float *qrow = Q + ((size_t)t * chunk_rows + bl * S + j) * T;
+        for (int r = lane * 4; r < T; r += 128)
+            *reinterpret_cast<float4 *>(q_s + r) = __ldcs(reinterpret_cast<const float4 *>(qrow + r));
+        jacc[lane] = 0.f;  // 2 * kMaxPairs == 32
+        __syncwarp();
+        for (int i0 = 0; i0 < j; i0 += 32) {
+            const int i = i0 + lane;
+            if (i >= j) continue;
+            int k; float d;
+            const int32_t li = eval_pair<true>(st, n_anchors, i, j, cmp_eps, k, d);
+            if (k < 0) continue;
+            const double du = surrogate_up(d) * (double)(q_s[li] - q_s[li ^ (1 << k)]);
+            if (!(fabs(du) > kEps)) continue;
+#pragma unroll
+            for (int e = 0; e < 2; e++) {
+                const int comp = st.comp[2 * k + e], elem = st.elem[2 * k + e];
+                const float val = e == 0 ? (float)du : (float)(-du);
+                if (comp == 0) atomicAdd(dX1 + ((size_t)b * S + i) * e1 + elem, val);
+                else if (comp == 1) atomicAdd(jacc + 2 * k + e, val);
+                else if (comp == 2) atomicAdd(dPE + ((size_t)(j - i - 1) * n_detectors + t) * npe + elem, val);
+            }
+        }
+        __syncwarp();
+        if (lane < 2 * n_anchors && st.comp[lane] == 1 && jacc[lane] != 0.f)
+            atomicAdd(dX2 + ((size_t)b * S + j) * e2 + st.elem[lane], jacc[lane]);
+        __syncwarp();
+    }
+}
+
+// --------------------------------------------------------------------------------------------
+// Register-tiled fp32 contraction  C[z] (+)= alpha * A[z] . B[z]  on 128 x 128 x 16 tiles: 256 threads, an
+// 8 x 8 accumulator block per thread, operands staged k-major in shared memory ([k][m] and [k][n]) so the
+// inner loop reads them with 16-byte loads, the next tile prefetched into registers while the current one is
+// consumed.  Operand sources come in two layouts: "k contiguous" (element (m, k) at m * ld + k) and "row of k"
+// (element (m, k) at k * ld + m); A may hold uint16 counters.
+// --------------------------------------------------------------------------------------------
+constexpr int GM = 128, GK = 16, GLD = GM + 4;
+
+enum OperandKind { KC_F32, KC_U16, RK_F32, RK_U16 };
+
+struct Frag { uint4 r[2]; };
+
+// Loads this thread's part of the tile rows [m0, m0+128) x k [k0, k0+16); out-of-range parts read as zero.
+template <int KIND>
+__device__ __forceinline__ void fetch_tile(Frag &f, const void *base, int64_t ld, int m0, int M, int k0, int K) {
+    const int tid = threadIdx.x;
+    f.r[0] = make_uint4(0u, 0u, 0u, 0u);
+    f.r[1] = make_uint4(0u, 0u, 0u, 0u);
+    if (KIND == KC_F32) {
+        const float *p = static_cast<const float *>(base);
+        const int k = k0 + (tid & 3) * 4;
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const int m = m0 + (tid >> 2) + h * 64;
+            if (m < M && k < K) f.r[h] = __ldg(reinterpret_cast<const uint4 *>(p + (int64_t)m * ld + k));
+        }
+    } else if (KIND == KC_U16) {
+        const uint16_t *p = static_cast<const uint16_t *>(base);
+        const int m = m0 + (tid >> 1), k = k0 + (tid & 1) * 8;
+        if (m < M && k < K) f.r[0] = __ldg(reinterpret_cast<const uint4 *>(p + (int64_t)m * ld + k));
+    } else if (KIND == RK_F32) {
+        const float *p = static_cast<const float *>(base);
+        const int m = m0 + (tid & 31) * 4;
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const int k = k0 + (tid >> 5) + h * 8;
+            if (m < M && k < K) f.r[h] = __ldg(reinterpret_cast<const uint4 *>(p + (int64_t)k * ld + m));
+        }
+    } else {
+        const uint16_t *p = static_cast<const uint16_t *>(base);
+        const int m = m0 + (tid & 15) * 8, k = k0 + (tid >> 4);
+        if (m < M && k < K) f.r[0] = __ldg(reinterpret_cast<const uint4 *>(p + (int64_t)k * ld + m));
+    }
+}
+
+__device__ __forceinline__ float lo16(uint32_t v) { return (float)(v & 0xffffu); }
+__device__ __forceinline__ float hi16(uint32_t v) { return (float)(v >> 16); }
+
+template <int KIND>
+__device__ __forceinline__ void stash_tile(const Frag &f, float (*tile)[GLD]) {
+    const int tid = threadIdx.x;
+    if (KIND == KC_F32) {
+        const int k = (tid & 3) * 4;
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const int m = (tid >> 2) + h * 64;
+            tile[k + 0][m] = __uint_as_float(f.r[h].x);
+            tile[k + 1][m] = __uint_as_float(f.r[h].y);
+            tile[k + 2][m] = __uint_as_float(f.r[h].z);
+            tile[k + 3][m] = __uint_as_float(f.r[h].w);
+        }
+    } else if (KIND == KC_U16) {
+        const int m = tid >> 1, k = (tid & 1) * 8;
+        tile[k + 0][m] = lo16(f.r[0].x); tile[k + 1][m] = hi16(f.r[0].x);
+        tile[k + 2][m] = lo16(f.r[0].y); tile[k + 3][m] = hi16(f.r[0].y);
+        tile[k + 4][m] = lo16(f.r[0].z); tile[k + 5][m] = hi16(f.r[0].z);
+        tile[k + 6][m] = lo16(f.r[0].w); tile[k + 7][m] = hi16(f.r[0].w);
+    } else if (KIND == RK_F32) {
+        const int m = (tid & 31) * 4;
+#pragma unroll
+        for (int h = 0; h < 2; h++) *reinterpret_cast<uint4 *>(&tile[(tid >> 5) + h * 8][m]) = f.r[h];
+    } else {
+        const int m = (tid & 15) * 8, k = tid >> 4;
+        *reinterpret_cast<float4 *>(&tile[k][m]) = make_float4(lo16(f.r[0].x), hi16(f.r[0].x), lo16(f.r[0].y), hi16(f.r[0].y));
+        *reinterpret_cast<float4 *>(&tile[k][m + 4]) = make_float4(lo16(f.r[0].z), hi16(f.r[0].z), lo16(f.r[0].w), hi16(f.r[0].w));
+    }
+}
+
+struct GemmArgs {
+    const void *A;
+    const float *B;
+    float *C;
+    int M, N, K;
+    int64_t lda, ldb, ldc;
+    int64_t za, zb, zc;  // per blockIdx.z strides, in elements
+    int kblock;          // A only: k = q * kblock + r is found at k-offset q * kblock_stride + r (k contiguous kinds)
+    int64_t kblock_stride;
+    float alpha;
+    int accumulate;      // 0: C = alpha * acc, 1: C += alpha * acc
+};
+
+template <int KIND_A, int KIND_B>
+__global__ void __launch_bounds__(256, 2) tile_contract_kernel(const GemmArgs g) {
+    __shared__ __align__(16) float As[2][GK][GLD];
+    __shared__ __align__(16) float Bs[2][GK][GLD];
+    const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+    const int m0 = blockIdx.y * GM, n0 = blockIdx.x * GM;
+    const int64_t z = blockIdx.z;
+    const size_t a_elem = (KIND_A == KC_U16 || KIND_A == RK_U16) ? 2 : 4;
+    const char *A = static_cast<const char *>(g.A) + (size_t)(z * g.za) * a_elem;
+    const float *B = g.B + z * g.zb;
+    float *C = g.C + z * g.zc;
+
+    float acc[8][8];
+#pragma unroll
+    for (int i = 0; i < 8; i++)
+#pragma unroll
+        for (int j = 0; j < 8; j++) acc[i][j] = 0.f;
+
+    const int nkt = (g.K + GK - 1) / GK;
+    Frag fa, fb;
+    auto fetch = [&](int kt) {
+        const int k0 = kt * GK;
+        if (KIND_A == KC_F32 || KIND_A == KC_U16) {
+            const int q = k0 / g.kblock, r = k0 - q * g.kblock;
+            fetch_tile<KIND_A>(fa, A + (size_t)(q * g.kblock_stride) * a_elem, g.lda, m0, g.M, r, g.kblock < g.K ? g.kblock : g.K);
+        } else {
+            fetch_tile<KIND_A>(fa, A, g.lda, m0, g.M, k0, g.K);
+        }
+        fetch_tile<KIND_B>(fb, B, g.ldb, n0, g.N, k0, g.K);
+    };
+    fetch(0);
+    stash_tile<KIND_A>(fa, As[0]);
+    stash_tile<KIND_B>(fb, Bs[0]);
+    __syncthreads();
+    for (int kt = 0; kt < nkt; kt++) {
+        const int buf = kt & 1;
+        if (kt + 1 < nkt) fetch(kt + 1);
+#pragma unroll
+        for (int k = 0; k < GK; k++) {
+            const float4 a0 = *reinterpret_cast<const float4 *>(&As[buf][k][ty * 4]);
+            const float4 a1 = *reinterpret_cast<const float4 *>(&As[buf][k][64 + ty * 4]);
+            const float4 b0 = *reinterpret_cast<const float4 *>(&Bs[buf][k][tx * 4]);
+            const float4 b1 = *reinterpret_cast<const float4 *>(&Bs[buf][k][64 + tx * 4]);
+            const float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+            const float b[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+            for (int i = 0; i < 8; i++)
+#pragma unroll
+                for (int j = 0; j < 8; j++) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        }
+        if (kt + 1 < nkt) {
+            stash_tile<KIND_A>(fa, As[buf ^ 1]);
+            stash_tile<KIND_B>(fb, Bs[buf ^ 1]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const int m = m0 + (i < 4 ? ty * 4 + i : 64 + ty * 4 + (i - 4));
+        if (m >= g.M) continue;
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const int n = n0 + h * 64 + tx * 4;
+            if (n >= g.N) continue;
+            float4 *dst = reinterpret_cast<float4 *>(C + (int64_t)m * g.ldc + n);
+            float4 v = make_float4(g.alpha * acc[i][h * 4 + 0], g.alpha * acc[i][h * 4 + 1], g.alpha * acc[i][h * 4 + 2],
+                                   g.alpha * acc[i][h * 4 + 3]);
+            if (g.accumulate) {
+                const float4 old = *dst;
+                v.x += old.x; v.y += old.y; v.z += old.z; v.w += old.w;
+            }
+            *dst = v;
+        }
+    }
+}
+
+template <int KIND_A, int KIND_B>
+static int launch_contract(KernelId id, const GemmArgs &g, int batches, cudaStream_t stream) {
+    dim3 grid((unsigned)((g.N + GM - 1) / GM), (unsigned)((g.M + GM - 1) / GM), (unsigned)batches);
+    LUTB_REQUIRE(grid.y <= 65535 && grid.z <= 65535, LUTB_ERR_SHAPE, "product histogram path: chunk too large");
+    KernelScope scope(id, stream);
+    tile_contract_kernel<KIND_A, KIND_B><<<grid, 256, 0, stream>>>(g);
+    LUTB_LAUNCH_CHECK();
+    return LUTB_OK;
+}
+
+static size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
+
+static size_t stage_bytes(const ProductCall &c, size_t per_warp_floats) {
+    return (pair_stage_floats(c.S, c.cfg->n_anchors, c.cfg->pos_dim) + 8 * per_warp_floats) * 4;
+}
+
+bool product_hist_supported(const ProductCall &c, const void *weights, const void *io_rows, const void *dW) {
+    const lutb_layer_cfg *cfg = c.cfg;
+    if (cfg->int_mode || c.S < 2 || c.S > 65535) return false;
+    if (cfg->n_anchors < 4 || cfg->n_anchors > 12 || cfg->n_outputs % 4 != 0) return false;
+    const uintptr_t bits = reinterpret_cast<uintptr_t>(weights) | reinterpret_cast<uintptr_t>(io_rows) |
+                           reinterpret_cast<uintptr_t>(dW);
+    if (bits & 15) return false;
+    const size_t T = (size_t)1 << cfg->n_anchors;
+    return stage_bytes(c, T + 2 * kMaxPairs) <= (size_t)kMaxSmemPerBlock - 1024;
+}
+
+size_t product_hist_bytes_per_sequence(const lutb_layer_cfg *cfg, int S, bool backward) {
+    const size_t cells = (size_t)cfg->n_detectors * S * ((size_t)1 << cfg->n_anchors);
+    return align256(cells * 2) + (backward ? align256(cells * 4) : 0) + 512;
+}
+
+struct HistPlan {
+    int64_t chunk;  // sequences per pass
+    uint16_t *H;
+    float *Q;
+};
+
+static int plan(const ProductCall &c, bool backward, void *workspace, size_t bytes, HistPlan &p) {
+    LUTB_REQUIRE(workspace != nullptr, LUTB_ERR_WORKSPACE, "product histogram path needs a workspace");
+    const uintptr_t base = (reinterpret_cast<uintptr_t>(workspace) + 255) & ~(uintptr_t)255;
+    const size_t slack = base - reinterpret_cast<uintptr_t>(workspace);
+    const size_t per_seq = product_hist_bytes_per_sequence(c.cfg, c.S, backward);
+    LUTB_REQUIRE(bytes >= slack + per_seq, LUTB_ERR_WORKSPACE,
+                 "product histogram path: workspace of %zu bytes is smaller than the %zu bytes one sequence needs", bytes,
+                 per_seq + 256);
+    p.chunk = (int64_t)((bytes - slack) / per_seq);
+    if (p.chunk > c.batch) p.chunk = c.batch;
+    // grid.y of the contraction covers chunk * S / 128 row tiles
+    const int64_t max_rows = (int64_t)65535 * GM;
+    if (p.chunk * c.S > max_rows) p.chunk = max_rows / c.S;
+    const size_t cells = (size_t)c.cfg->n_detectors * (size_t)p.chunk * c.S * ((size_t)1 << c.cfg->n_anchors);
+    p.H = reinterpret_cast<uint16_t *>(base);
+    p.Q = backward ? reinterpret_cast<float *>(base + align256(cells * 2)) : nullptr;
+    return LUTB_OK;
+}
+
+static int launch_hist(const ProductCall &c, const HistPlan &p, int64_t b0, int64_t n, cudaStream_t stream) {
+    const lutb_layer_cfg *cfg = c.cfg;
+    const size_t T = (size_t)1 << cfg->n_anchors;
+    const size_t smem = stage_bytes(c, T);
+    if (smem > 48 * 1024) LUTB_CUDA(cudaFuncSetAttribute(product_hist_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    dim3 grid((unsigned)cfg->n_detectors, (unsigned)n);
+    KernelScope scope(K_PRODUCT_HIST, stream);
+    product_hist_kernel<<<grid, 256, smem, stream>>>(c.x1, c.x2, c.pe, c.anchors, p.H, b0, n * c.S, c.S, c.e1, c.e2,
+                                                     cfg->pos_dim, cfg->n_detectors, cfg->n_anchors, cfg->sliced_product,
+                                                     cfg->cmp_eps);
+    LUTB_LAUNCH_CHECK();
+    return LUTB_OK;
+}
+
+int launch_product_hist_forward(const ProductCall &c, const float *weights, float *y, void *workspace,
+                                size_t workspace_bytes, cudaStream_t stream) {
+    HistPlan p;
+    int rc = plan(c, false, workspace, workspace_bytes, p);
+    if (rc) return rc;
+    const lutb_layer_cfg *cfg = c.cfg;
+    const int T = 1 << cfg->n_anchors, O = cfg->n_outputs, Nt = cfg->n_detectors;
+    for (int64_t b0 = 0; b0 < c.batch; b0 += p.chunk) {
+        const int64_t n = (c.batch - b0 < p.chunk) ? c.batch - b0 : p.chunk;
+        const int64_t rows = n * c.S;
+        rc = launch_hist(c, p, b0, n, stream);
+        if (rc) return rc;
+        GemmArgs g{};
+        g.A = p.H; g.B = weights; g.C = y + b0 * c.S * O;
+        g.M = (int)rows; g.N = O; g.K = Nt * T;
+        g.lda = T; g.ldb = O; g.ldc = O;
+        g.kblock = T; g.kblock_stride = rows * T;
+        g.alpha = 1.f; g.accumulate = 1;
+        rc = launch_contract<KC_U16, RK_F32>(K_PRODUCT_HIST_FORWARD, g, 1, stream);
+        if (rc) return rc;
+    }
+    return LUTB_OK;
+}
+
+int launch_product_hist_backward(const ProductCall &c, const float *weights, const float *dY, float *dX1, float *dX2,
+                                 float *dPE, float *target, double lr, bool in_place, void *workspace,
+                                 size_t workspace_bytes, cudaStream_t stream) {
+    HistPlan p;
+    int rc = plan(c, true, workspace, workspace_bytes, p);
+    if (rc) return rc;
+    const lutb_layer_cfg *cfg = c.cfg;
+    const int T = 1 << cfg->n_anchors, O = cfg->n_outputs, Nt = cfg->n_detectors;
+    const size_t route_smem = stage_bytes(c, (size_t)T + 2 * kMaxPairs);
+    if (route_smem > 48 * 1024) LUTB_CUDA(cudaFuncSetAttribute(product_route_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)route_smem));
+    // In-place SGD reads unmodified tables for every input gradient: with more than one chunk the table update
+    // runs as a second sweep over the chunks.
+    const bool second_sweep = in_place && p.chunk < c.batch;
+    auto table_gradient = [&](int64_t b0, int64_t rows) -> int {
+        GemmArgs g{};
+        g.A = p.H; g.B = dY + b0 * c.S * O; g.C = target;
+        g.M = T; g.N = O; g.K = (int)rows;
+        g.lda = T; g.ldb = O; g.ldc = O;
+        g.za = rows * T; g.zb = 0; g.zc = (int64_t)T * O;
+        g.kblock = g.K; g.kblock_stride = 0;
+        g.alpha = (float)lr; g.accumulate = 1;
+        return launch_contract<RK_U16, RK_F32>(K_PRODUCT_HIST_WEIGHT_GRAD, g, Nt, stream);
+    };
+    for (int64_t b0 = 0; b0 < c.batch; b0 += p.chunk) {
+        const int64_t n = (c.batch - b0 < p.chunk) ? c.batch - b0 : p.chunk;
+        const int64_t rows = n * c.S;
+        rc = launch_hist(c, p, b0, n, stream);
+        if (rc) return rc;
+        {
+            GemmArgs g{};
+            g.A = dY + b0 * c.S * O; g.B = weights; g.C = p.Q;
+            g.M = (int)rows; g.N = T; g.K = O;
+            g.lda = O; g.ldb = O; g.ldc = T;
+            g.za = 0; g.zb = (int64_t)T * O; g.zc = rows * T;
+            g.kblock = O; g.kblock_stride = 0;
+            g.alpha = 1.f; g.accumulate = 0;
+            rc = launch_contract<KC_F32, KC_F32>(K_PRODUCT_ROW_DOTS, g, Nt, stream);
+            if (rc) return rc;
+        }
+        {
+            dim3 grid((unsigned)Nt, (unsigned)n);
+            KernelScope scope(K_PRODUCT_ROUTE, stream);
+            product_route_kernel<<<grid, 256, route_smem, stream>>>(c.x1, c.x2, c.pe, c.anchors, p.Q, dX1, dX2, dPE, b0, rows,
+                                                                    c.S, c.e1, c.e2, cfg->pos_dim, Nt, cfg->n_anchors,
+                                                                    cfg->sliced_product, cfg->cmp_eps);
+            LUTB_LAUNCH_CHECK();
+        }
+        if (!second_sweep) {
+            rc = table_gradient(b0, rows);
+            if (rc) return rc;
+        }
+    }
+    if (second_sweep) {
+        for (int64_t b0 = 0; b0 < c.batch; b0 += p.chunk) {
+            const int64_t n = (c.batch - b0 < p.chunk) ? c.batch - b0 : p.chunk;
+            rc = launch_hist(c, p, b0, n, stream);
+            if (rc) return rc;
+            rc = table_gradient(b0, n * c.S);
+            if (rc) return rc;
+        }
+    }
+    return LUTB_OK;
+}
+
+}  // namespace lutb

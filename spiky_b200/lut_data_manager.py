@@ -307,7 +307,7 @@ class _LUTDataManager:
     # ------------------------------------------------------------------ product-mode sequence runtime
     def forward_step_product(self, r_weights, batch_size, sequence_length, r_input_1, r_input_2, r_detector_anchors,
                              w_output, n_inputs_1, n_inputs_2, sliced_mode, cmp_eps=0.0, r_positional_embeddings=None,
-                             r_stream_handles=None):
+                             r_stream_handles=None, variant=_native.PRODUCT_AUTO):
         self._require_cuda()
         dev = self._device
         _check_tensor(r_weights, "r_weights", True, dev)
@@ -337,10 +337,11 @@ class _LUTDataManager:
             self._expect(r_positional_embeddings, (S - 1) * self._n_detectors * self._pos_dim, "r_positional_embeddings")
         cfg = self._cfg(cmp_eps, sliced=sliced_mode)
         with torch.cuda.device(dev):
+            ws, ws_bytes = self._product_workspace(cfg, B, S, False, variant, r_weights.device)
             rc = _native.lib().lutb_product_forward(
                 ctypes.byref(cfg), B, S, _ptr(r_weights), _ptr(r_input_1), _ptr(r_input_2), int(n_inputs_1),
                 int(n_inputs_2), _ptr(r_positional_embeddings), _ptr(r_detector_anchors), _ptr(w_output),
-                self._stream())
+                int(variant), _ptr(ws), ws_bytes, self._stream())
         _native.check(rc)
         self._forward_seen = True
 
@@ -348,7 +349,8 @@ class _LUTDataManager:
                                   r_detector_anchors, r_output_gradients, w_input_gradients_1, w_input_gradients_2,
                                   external_lr, n_inputs_1, n_inputs_2, sliced_mode, cmp_eps=0.0,
                                   w_weights_gradients=None, r_positional_embeddings=None,
-                                  w_positional_embeddings_gradients=None, r_stream_handles=None):
+                                  w_positional_embeddings_gradients=None, r_stream_handles=None,
+                                  variant=_native.PRODUCT_AUTO):
         if batch_size == 0:
             raise ValueError("batch_size == 0")
         if not self._forward_seen:
@@ -373,12 +375,36 @@ class _LUTDataManager:
         self._expect(w_input_gradients_2, B * S * n_inputs_2, "w_input_gradients_2")
         cfg = self._cfg(cmp_eps, sliced=sliced_mode)
         with torch.cuda.device(dev):
+            ws, ws_bytes = self._product_workspace(cfg, B, S, True, variant, r_weights.device)
             rc = _native.lib().lutb_product_backward(
                 ctypes.byref(cfg), B, S, _ptr(r_weights), _ptr(r_input_1), _ptr(r_input_2), int(n_inputs_1),
                 int(n_inputs_2), _ptr(r_positional_embeddings), _ptr(r_detector_anchors), _ptr(r_output_gradients),
                 _ptr(w_input_gradients_1), _ptr(w_input_gradients_2), _ptr(w_positional_embeddings_gradients),
-                _ptr(w_weights_gradients), float(external_lr), self._stream())
+                _ptr(w_weights_gradients), float(external_lr), int(variant), _ptr(ws), ws_bytes, self._stream())
         _native.check(rc)
+
+    # scratch of the histogram variant of the product kernels: one buffer per device, shared by all layers
+    # (a call only uses it between its own launches on the current stream)
+    _product_scratch = {}
+    product_scratch_limit = 4 << 30
+
+    def _product_workspace(self, cfg, B, S, backward, variant, device):
+        """(tensor or None, bytes) handed to the product entry points; None lets AUTO fall back to DIRECT."""
+        if variant == _native.PRODUCT_DIRECT or self._INT_MODE or S < 2:
+            return None, 0
+        rows = 1 << self._n_anchors
+        if variant == _native.PRODUCT_AUTO and not ((4 * S >= rows) if backward else (S >= rows)):
+            return None, 0
+        L = _native.lib()
+        one = L.lutb_product_workspace(ctypes.byref(cfg), 1, S, int(backward))
+        want = min(L.lutb_product_workspace(ctypes.byref(cfg), B, S, int(backward)),
+                   max(one, _LUTDataManager.product_scratch_limit))
+        buf = _LUTDataManager._product_scratch.get(device)
+        if buf is None or buf.numel() < want:
+            _LUTDataManager._product_scratch[device] = None
+            buf = torch.empty(want, dtype=torch.uint8, device=device)
+            _LUTDataManager._product_scratch[device] = buf
+        return buf, buf.numel()
 
     # ------------------------------------------------------------------ concatenation-mode sequence runtime
     def forward_step_concat(self, r_weights, batch_size, r_input, r_detector_anchors, w_output, w_lookup_indices,

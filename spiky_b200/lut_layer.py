@@ -553,7 +553,8 @@ class LUTLayerBasic(nn.Module):
         pe = None if pos_embeddings is None else pos_embeddings.detach().contiguous().view(-1)
         self._lut_dm.forward_step_product(self._weights.detach(), B, S, xf, xf, self._detector_anchors, output,
                                           self._n_inputs, self._n_inputs, self._sliced_product_mode,
-                                          self._shared_context._cmp_eps, pe, None)
+                                          self._shared_context._cmp_eps, pe, None,
+                                          variant=getattr(self, "_product_variant", 0))
         return None if external else output.view((B, S) + tuple(self.output_shape()))
 
     def backward_step_product(self, x, pos_embeddings, grad_output, x_grad=None):
@@ -573,7 +574,7 @@ class LUTLayerBasic(nn.Module):
         self._lut_dm.backward_backprop_product(
             self._weights.detach(), B, S, xf, xf, self._detector_anchors, grad_output.contiguous().view(-1), gf, gf,
             self._external_lr(), self._n_inputs, self._n_inputs, self._sliced_product_mode,
-            self._shared_context._cmp_eps, w_grad, pe, pe_grad, None)
+            self._shared_context._cmp_eps, w_grad, pe, pe_grad, None, variant=getattr(self, "_product_variant", 0))
         if not external:
             w_grad = self._process_gradients(w_grad, B)
         if pe_grad is not None and self._weights_gradient_policy.normalized:

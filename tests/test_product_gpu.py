@@ -35,8 +35,9 @@ def build_layer(cfg, anchors, W, pe):
     return layer
 
 
-def run_gpu(cfg, x, anchors, W, pe, dY):
+def run_gpu(cfg, x, anchors, W, pe, dY, variant=0):
     layer = build_layer(cfg, anchors, W, pe)
+    layer._product_variant = variant  # 0 auto, 1 direct gathers, 2 histogram + tiled contraction
     layer.train()
     xt = torch.from_numpy(x).cuda()
     pos = layer._prepare_positional_embeddings()
@@ -90,19 +91,61 @@ for _c in ORACLE_CASES.values():
     _c["n_virtual"] = 3 * _c["E"] if _c.get("sliced") else 2 * _c["E"] + _c["Npe"]
 
 
-@pytest.mark.parametrize("name", sorted(ORACLE_CASES))
-def test_product_matches_oracle(name):
+def hist_capable(cfg):
+    return not cfg.get("int_mode") and 4 <= cfg["Nc"] <= 12 and cfg["O"] % 4 == 0 and cfg["S"] >= 2
+
+
+ORACLE_CASES["internal_sgd"] = dict(seed=706, B=3, S=24, E=16, Nt=5, Nc=5, Npe=3, O=12, policy="internal", ext_lr=0.25,
+                                    lr_meta=0.5, n_virtual=35)
+VARIANT_CASES = [(n, v) for n in sorted(ORACLE_CASES) for v in (1, 2) if v == 1 or hist_capable(ORACLE_CASES[n])]
+
+
+@pytest.mark.parametrize("name,variant", VARIANT_CASES)
+def test_product_matches_oracle(name, variant):
     cfg = ORACLE_CASES[name]
     x, anchors, W, pe, dY = inputs_for(cfg)
     pe3 = expand_pe(cfg, pe)
     kw = dict(sliced=cfg.get("sliced", False), cmp_eps=cfg.get("cmp_eps", 0.0), int_mode=cfg.get("int_mode", False),
               int_rescaler=cfg.get("int_rescaler", 0.001))
     y = orc.product_forward(W, x, pe3, anchors, cfg["Nt"], cfg["Nc"], cfg["O"], cfg["Npe"], **kw)
-    dX, dW, dPE = orc.product_backward(W, x, pe3, anchors, dY, cfg["Nt"], cfg["Nc"], cfg["Npe"], **kw)
-    got = run_gpu(cfg, x, anchors, W, pe, dY)
-    ref = dict(y=y, dX=dX, dW=dW, dPE=dPE)
+    if cfg.get("policy") == "internal":
+        W_after = W.copy()
+        dX, _, dPE = orc.product_backward(W_after, x, pe3, anchors, dY, cfg["Nt"], cfg["Nc"], cfg["Npe"],
+                                          lr_meta=cfg["lr_meta"], external_lr=cfg["ext_lr"], **kw)
+        ref = dict(y=y, dX=dX, dPE=dPE, W_after=W_after)
+    else:
+        dX, dW, dPE = orc.product_backward(W, x, pe3, anchors, dY, cfg["Nt"], cfg["Nc"], cfg["Npe"], **kw)
+        ref = dict(y=y, dX=dX, dW=dW, dPE=dPE)
+    got = run_gpu(cfg, x, anchors, W, pe, dY, variant)
     assert not got["y"][:, 0].any()  # the first position has no earlier token to pair with
     compare(cfg, got, ref)
+
+
+def test_product_histogram_chunks_match_single_pass():
+    """A workspace that holds one sequence at a time gives the same result as one pass over the batch
+    (in-place SGD then runs its table update as a second sweep)."""
+    from spiky_b200.lut_data_manager import _LUTDataManager
+    for name in ("c3_attention", "internal_sgd"):
+        cfg = ORACLE_CASES[name]
+        x, anchors, W, pe, dY = inputs_for(cfg)
+        full = run_gpu(cfg, x, anchors, W, pe, dY, 2)
+        saved = _LUTDataManager.product_scratch_limit
+        _LUTDataManager.product_scratch_limit = 0
+        _LUTDataManager._product_scratch.clear()
+        try:
+            chunked = run_gpu(cfg, x, anchors, W, pe, dY, 2)
+        finally:
+            _LUTDataManager.product_scratch_limit = saved
+            _LUTDataManager._product_scratch.clear()
+        for k in full:
+            golden_util.assert_close(chunked[k], full[k], REL, f"{name}.{k}")
+
+
+def test_product_histogram_rejects_unsupported():
+    cfg = dict(seed=711, B=1, S=4, E=6, Nt=2, Nc=3, Npe=2, O=4, n_virtual=14)
+    x, anchors, W, pe, dY = inputs_for(cfg)
+    with pytest.raises(ValueError, match="histogram variant"):
+        run_gpu(cfg, x, anchors, W, pe, dY, 2)
 
 
 def test_product_autograd_unified_pe():
