@@ -32,7 +32,7 @@ __global__ void __launch_bounds__(256) product_forward_kernel(const float *__res
     const int64_t b = blockIdx.y;
     PairStage st;
     stage_pairs(st, smem, x1 + b * S * e1, x2 + b * S * e2, pe, anchors + (size_t)t * n_anchors * 2, S, e1, e2, npe,
-                n_anchors, n_detectors, t, sliced != 0);
+                n_anchors, n_detectors, t, sliced != 0, cmp_eps);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
     int32_t *idx_list = reinterpret_cast<int32_t *>(st.scratch) + warp * S;
     const float *Wt = W + (size_t)t * ((size_t)1 << n_anchors) * n_outputs;
@@ -54,7 +54,7 @@ __global__ void __launch_bounds__(256) product_forward_kernel(const float *__res
                 for (int q = 0; q < kProdJ; q++)
 #pragma unroll
                     for (int e = 0; e < 4; e++) { acc[q][e] = 0.f; iacc[q][e] = 0; }
-#pragma unroll 4
+#pragma unroll 8
                 for (int i = 0; i < j; i++) {
                     const float *row = Wt + (size_t)idx_list[i] * n_outputs + c0;
 #pragma unroll
@@ -123,7 +123,7 @@ __global__ void __launch_bounds__(256) product_backward_kernel(const float *__re
     const int64_t b = blockIdx.y;
     PairStage st;
     stage_pairs(st, smem, x1 + b * S * e1, x2 + b * S * e2, pe, anchors + (size_t)t * n_anchors * 2, S, e1, e2, npe,
-                n_anchors, n_detectors, t, sliced != 0);
+                n_anchors, n_detectors, t, sliced != 0, cmp_eps);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
     // per-warp scratch: dY row of the current query (padded to a multiple of 4)
     const int o_pad = (n_outputs + 3) & ~3;

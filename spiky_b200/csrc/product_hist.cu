@@ -22,7 +22,7 @@ __global__ void __launch_bounds__(256) product_hist_kernel(const float *__restri
     const int64_t bl = blockIdx.y, b = b0 + bl;
     PairStage st;
     stage_pairs(st, smem, x1 + b * S * e1, x2 + b * S * e2, pe, anchors + (size_t)t * n_anchors * 2, S, e1, e2, npe,
-                n_anchors, n_detectors, t, sliced != 0);
+                n_anchors, n_detectors, t, sliced != 0, cmp_eps);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
     const int T = 1 << n_anchors;
     uint32_t *hist = reinterpret_cast<uint32_t *>(st.scratch) + warp * T;
@@ -56,8 +56,12 @@ __global__ void __launch_bounds__(256) product_hist_kernel(const float *__restri
 // Input-gradient routing.  Same block / warp layout; the warp stages Q_t[(b,j), :] (the dot product of
 // dY[b,j,:] with every row of table t) and each pair reads its two entries: g = Q[idx] - Q[idx ^ 2^kmin],
 // du = up(min_delta) * g, +du / -du to the sources of the flipped anchor's two ends.
-// Contributions to the query token's own elements are pre-reduced per warp in shared memory.
+// SMEM_ACC: the block first sums its contributions per (token, anchor end) and per (distance, element) in shared
+// memory and issues one global atomic per touched cell at the end (the global atomics of a block drop from one
+// or two per pair to at most S * 2 * Nc + (S-1) * Npe); without it only the query token's cells are pre-reduced
+// per warp.
 // --------------------------------------------------------------------------------------------
+template <bool SMEM_ACC>
 __global__ void __launch_bounds__(256) product_route_kernel(const float *__restrict__ x1, const float *__restrict__ x2,
                                                            const float *__restrict__ pe,
                                                            const int32_t *__restrict__ anchors,
@@ -70,16 +74,26 @@ __global__ void __launch_bounds__(256) product_route_kernel(const float *__restr
     const int64_t bl = blockIdx.y, b = b0 + bl;
     PairStage st;
     stage_pairs(st, smem, x1 + b * S * e1, x2 + b * S * e2, pe, anchors + (size_t)t * n_anchors * 2, S, e1, e2, npe,
-                n_anchors, n_detectors, t, sliced != 0);
+                n_anchors, n_detectors, t, sliced != 0, cmp_eps);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
     const int T = 1 << n_anchors;
-    float *q_s = st.scratch + warp * (T + 2 * kMaxPairs);
-    float *jacc = q_s + T;  // per anchor end: sum of the contributions that go to the query token j
+    const int ends = 2 * n_anchors;
+    const int per_warp = T + 32 * ends;
+    float *q_s = st.scratch + warp * per_warp;
+    // contributions to the query token j: a private column per lane ([end][lane], plain read-modify-write; every
+    // lane of a pair batch would otherwise hit the same few cells), summed over the lanes once per query
+    float *jacc = q_s + T;
+    float *tacc = st.scratch + nwarps * per_warp;  // [S][ends]
+    float *pacc = tacc + S * ends;                            // [S-1][npe]
+    if (SMEM_ACC) {
+        for (int w = threadIdx.x; w < S * ends + (S - 1) * npe; w += blockDim.x) tacc[w] = 0.f;
+        __syncthreads();
+    }
     for (int j = 1 + warp; j < S; j += nwarps) {
         const float *qrow = Q + ((size_t)t * chunk_rows + bl * S + j) * T;
         for (int r = lane * 4; r < T; r += 128)
             *reinterpret_cast<float4 *>(q_s + r) = __ldcs(reinterpret_cast<const float4 *>(qrow + r));
-        jacc[lane] = 0.f;  // 2 * kMaxPairs == 32
+        for (int q = 0; q < ends; q++) jacc[q * 32 + lane] = 0.f;
         __syncwarp();
         for (int i0 = 0; i0 < j; i0 += 32) {
             const int i = i0 + lane;
@@ -93,15 +107,44 @@ __global__ void __launch_bounds__(256) product_route_kernel(const float *__restr
             for (int e = 0; e < 2; e++) {
                 const int comp = st.comp[2 * k + e], elem = st.elem[2 * k + e];
                 const float val = e == 0 ? (float)du : (float)(-du);
-                if (comp == 0) atomicAdd(dX1 + ((size_t)b * S + i) * e1 + elem, val);
-                else if (comp == 1) atomicAdd(jacc + 2 * k + e, val);
-                else if (comp == 2) atomicAdd(dPE + ((size_t)(j - i - 1) * n_detectors + t) * npe + elem, val);
+                if (comp == 0) {
+                    if (SMEM_ACC) atomicAdd(tacc + i * ends + 2 * k + e, val);
+                    else atomicAdd(dX1 + ((size_t)b * S + i) * e1 + elem, val);
+                } else if (comp == 1) {
+                    jacc[(2 * k + e) * 32 + lane] += val;
+                } else if (comp == 2) {
+                    if (SMEM_ACC) atomicAdd(pacc + (j - i - 1) * npe + elem, val);
+                    else atomicAdd(dPE + ((size_t)(j - i - 1) * n_detectors + t) * npe + elem, val);
+                }
             }
         }
         __syncwarp();
-        if (lane < 2 * n_anchors && st.comp[lane] == 1 && jacc[lane] != 0.f)
-            atomicAdd(dX2 + ((size_t)b * S + j) * e2 + st.elem[lane], jacc[lane]);
+        if (lane < ends && st.comp[lane] == 1) {
+            float sum = 0.f;
+#pragma unroll 8
+            for (int m = 0; m < 32; m++) sum += jacc[lane * 32 + ((m + lane) & 31)];
+            if (sum != 0.f) {
+                if (SMEM_ACC) atomicAdd(tacc + j * ends + lane, sum);
+                else atomicAdd(dX2 + ((size_t)b * S + j) * e2 + st.elem[lane], sum);
+            }
+        }
         __syncwarp();
+    }
+    if (SMEM_ACC) {
+        __syncthreads();
+        for (int w = threadIdx.x; w < S * ends; w += blockDim.x) {
+            const float v = tacc[w];
+            if (v == 0.f) continue;
+            const int s = w / ends, q = w - s * ends;
+            if (st.comp[q] == 0) atomicAdd(dX1 + ((size_t)b * S + s) * e1 + st.elem[q], v);
+            else if (st.comp[q] == 1) atomicAdd(dX2 + ((size_t)b * S + s) * e2 + st.elem[q], v);
+        }
+        for (int w = threadIdx.x; w < (S - 1) * npe; w += blockDim.x) {
+            const float v = pacc[w];
+            if (v == 0.f) continue;
+            const int d = w / npe, c = w - d * npe;
+            atomicAdd(dPE + ((size_t)d * n_detectors + t) * npe + c, v);
+        }
     }
 }
 
@@ -195,6 +238,7 @@ struct GemmArgs {
     int64_t kblock_stride;
     float alpha;
     int accumulate;      // 0: C = alpha * acc, 1: C += alpha * acc
+    int ksplit;          // > 1: blockIdx.z also splits K; partial sums are added atomically (accumulate only)
 };
 
 template <int KIND_A, int KIND_B>
@@ -203,7 +247,8 @@ __global__ void __launch_bounds__(256, 2) tile_contract_kernel(const GemmArgs g)
     __shared__ __align__(16) float Bs[2][GK][GLD];
     const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
     const int m0 = blockIdx.y * GM, n0 = blockIdx.x * GM;
-    const int64_t z = blockIdx.z;
+    const int64_t z = blockIdx.z / g.ksplit;
+    const int split = blockIdx.z - (int)z * g.ksplit;
     const size_t a_elem = (KIND_A == KC_U16 || KIND_A == RK_U16) ? 2 : 4;
     const char *A = static_cast<const char *>(g.A) + (size_t)(z * g.za) * a_elem;
     const float *B = g.B + z * g.zb;
@@ -215,7 +260,8 @@ __global__ void __launch_bounds__(256, 2) tile_contract_kernel(const GemmArgs g)
 #pragma unroll
         for (int j = 0; j < 8; j++) acc[i][j] = 0.f;
 
-    const int nkt = (g.K + GK - 1) / GK;
+    const int all_tiles = (g.K + GK - 1) / GK, per_split = (all_tiles + g.ksplit - 1) / g.ksplit;
+    const int kt0 = split * per_split, nkt = min(all_tiles, kt0 + per_split);
     Frag fa, fb;
     auto fetch = [&](int kt) {
         const int k0 = kt * GK;
@@ -227,11 +273,12 @@ __global__ void __launch_bounds__(256, 2) tile_contract_kernel(const GemmArgs g)
         }
         fetch_tile<KIND_B>(fb, B, g.ldb, n0, g.N, k0, g.K);
     };
-    fetch(0);
-    stash_tile<KIND_A>(fa, As[0]);
-    stash_tile<KIND_B>(fb, Bs[0]);
+    if (kt0 >= nkt) return;
+    fetch(kt0);
+    stash_tile<KIND_A>(fa, As[kt0 & 1]);
+    stash_tile<KIND_B>(fb, Bs[kt0 & 1]);
     __syncthreads();
-    for (int kt = 0; kt < nkt; kt++) {
+    for (int kt = kt0; kt < nkt; kt++) {
         const int buf = kt & 1;
         if (kt + 1 < nkt) fetch(kt + 1);
 #pragma unroll
@@ -264,6 +311,11 @@ __global__ void __launch_bounds__(256, 2) tile_contract_kernel(const GemmArgs g)
             float4 *dst = reinterpret_cast<float4 *>(C + (int64_t)m * g.ldc + n);
             float4 v = make_float4(g.alpha * acc[i][h * 4 + 0], g.alpha * acc[i][h * 4 + 1], g.alpha * acc[i][h * 4 + 2],
                                    g.alpha * acc[i][h * 4 + 3]);
+            if (g.ksplit > 1) {
+                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w)
+                             : "memory");
+                continue;
+            }
             if (g.accumulate) {
                 const float4 old = *dst;
                 v.x += old.x; v.y += old.y; v.z += old.z; v.w += old.w;
@@ -274,8 +326,9 @@ __global__ void __launch_bounds__(256, 2) tile_contract_kernel(const GemmArgs g)
 }
 
 template <int KIND_A, int KIND_B>
-static int launch_contract(KernelId id, const GemmArgs &g, int batches, cudaStream_t stream) {
-    dim3 grid((unsigned)((g.N + GM - 1) / GM), (unsigned)((g.M + GM - 1) / GM), (unsigned)batches);
+static int launch_contract(KernelId id, GemmArgs g, int batches, cudaStream_t stream) {
+    if (g.ksplit < 1) g.ksplit = 1;
+    dim3 grid((unsigned)((g.N + GM - 1) / GM), (unsigned)((g.M + GM - 1) / GM), (unsigned)(batches * g.ksplit));
     LUTB_REQUIRE(grid.y <= 65535 && grid.z <= 65535, LUTB_ERR_SHAPE, "product histogram path: chunk too large");
     KernelScope scope(id, stream);
     tile_contract_kernel<KIND_A, KIND_B><<<grid, 256, 0, stream>>>(g);
@@ -297,7 +350,7 @@ bool product_hist_supported(const ProductCall &c, const void *weights, const voi
                            reinterpret_cast<uintptr_t>(dW);
     if (bits & 15) return false;
     const size_t T = (size_t)1 << cfg->n_anchors;
-    return stage_bytes(c, T + 2 * kMaxPairs) <= (size_t)kMaxSmemPerBlock - 1024;
+    return stage_bytes(c, T + 64 * cfg->n_anchors) <= (size_t)kMaxSmemPerBlock - 1024;
 }
 
 size_t product_hist_bytes_per_sequence(const lutb_layer_cfg *cfg, int S, bool backward) {
@@ -376,8 +429,15 @@ int launch_product_hist_backward(const ProductCall &c, const float *weights, con
     if (rc) return rc;
     const lutb_layer_cfg *cfg = c.cfg;
     const int T = 1 << cfg->n_anchors, O = cfg->n_outputs, Nt = cfg->n_detectors;
-    const size_t route_smem = stage_bytes(c, (size_t)T + 2 * kMaxPairs);
-    if (route_smem > 48 * 1024) LUTB_CUDA(cudaFuncSetAttribute(product_route_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)route_smem));
+    size_t route_smem = stage_bytes(c, (size_t)T + 64 * cfg->n_anchors);
+    const size_t acc_bytes = ((size_t)c.S * 2 * cfg->n_anchors + (size_t)(c.S - 1) * cfg->pos_dim) * 4;
+    // block-level accumulators only while two blocks still fit an SM
+    const bool smem_acc = route_smem + acc_bytes <= 100 * 1024;
+    if (smem_acc) route_smem += acc_bytes;
+    if (route_smem > 48 * 1024) {
+        if (smem_acc) LUTB_CUDA(cudaFuncSetAttribute(product_route_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)route_smem));
+        else LUTB_CUDA(cudaFuncSetAttribute(product_route_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)route_smem));
+    }
     // In-place SGD reads unmodified tables for every input gradient: with more than one chunk the table update
     // runs as a second sweep over the chunks.
     const bool second_sweep = in_place && p.chunk < c.batch;
@@ -389,6 +449,11 @@ int launch_product_hist_backward(const ProductCall &c, const float *weights, con
         g.za = rows * T; g.zb = 0; g.zc = (int64_t)T * O;
         g.kblock = g.K; g.kblock_stride = 0;
         g.alpha = (float)lr; g.accumulate = 1;
+        // few output tiles and a long reduction: split K so that every SM gets several blocks
+        const int64_t tiles = (int64_t)((T + GM - 1) / GM) * ((O + GM - 1) / GM) * Nt;
+        const int64_t want = (8 * (int64_t)device_info().sm_count + tiles - 1) / tiles;
+        const int64_t most = (rows / GK + 31) / 32;  // at least 32 k-tiles per block
+        g.ksplit = (int)(want < 1 ? 1 : (want > most ? (most < 1 ? 1 : most) : want));
         return launch_contract<RK_U16, RK_F32>(K_PRODUCT_HIST_WEIGHT_GRAD, g, Nt, stream);
     };
     for (int64_t b0 = 0; b0 < c.batch; b0 += p.chunk) {
@@ -410,9 +475,14 @@ int launch_product_hist_backward(const ProductCall &c, const float *weights, con
         {
             dim3 grid((unsigned)Nt, (unsigned)n);
             KernelScope scope(K_PRODUCT_ROUTE, stream);
-            product_route_kernel<<<grid, 256, route_smem, stream>>>(c.x1, c.x2, c.pe, c.anchors, p.Q, dX1, dX2, dPE, b0, rows,
-                                                                    c.S, c.e1, c.e2, cfg->pos_dim, Nt, cfg->n_anchors,
-                                                                    cfg->sliced_product, cfg->cmp_eps);
+            if (smem_acc)
+                product_route_kernel<true><<<grid, 256, route_smem, stream>>>(c.x1, c.x2, c.pe, c.anchors, p.Q, dX1, dX2, dPE, b0,
+                                                                              rows, c.S, c.e1, c.e2, cfg->pos_dim, Nt,
+                                                                              cfg->n_anchors, cfg->sliced_product, cfg->cmp_eps);
+            else
+                product_route_kernel<false><<<grid, 256, route_smem, stream>>>(c.x1, c.x2, c.pe, c.anchors, p.Q, dX1, dX2, dPE, b0,
+                                                                               rows, c.S, c.e1, c.e2, cfg->pos_dim, Nt,
+                                                                               cfg->n_anchors, cfg->sliced_product, cfg->cmp_eps);
             LUTB_LAUNCH_CHECK();
         }
         if (!second_sweep) {
