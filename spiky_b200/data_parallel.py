@@ -84,12 +84,18 @@ class OverlappedGradientSync:
     """
 
     def __init__(self, params, group=None, average=True):
-        self.group = group
         self.average = average
         self.handles = []
         self.enabled = dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1
         self.world = dist.get_world_size(group) if self.enabled else 1
         self._hooks = []
+        self._nccl = self.enabled and dist.get_backend(group) == "nccl"
+        if self._nccl and group is None:
+            # The backward kernels keep every SM busy; on a high-priority stream the collective's blocks are
+            # scheduled as soon as any block of the running kernel retires instead of after its last one.
+            opts = dist.ProcessGroupNCCL.Options(is_high_priority_stream=True)
+            group = dist.new_group(backend="nccl", pg_options=opts)
+        self.group = group
         if self.enabled:
             for p in params:
                 if p.requires_grad:
@@ -101,14 +107,26 @@ class OverlappedGradientSync:
             return
         if g.is_sparse:
             p.grad = g = g.to_dense()
+        op = dist.ReduceOp.SUM
         if self.average:
-            g.div_(self.world)
-        self.handles.append(dist.all_reduce(g, op=dist.ReduceOp.SUM, group=self.group, async_op=True))
+            if self._nccl:
+                op = dist.ReduceOp.AVG  # averaged inside the collective: no extra pass over the gradient
+            else:
+                g.div_(self.world)
+        self.handles.append((p, dist.all_reduce(g, op=op, group=self.group, async_op=True)))
 
     def wait(self):
-        for h in self.handles:
+        for _, h in self.handles:
             h.wait()
         self.handles = []
+
+    def wait_each(self):
+        """Yields the parameters in the order their gradients were produced, each once its exchange has finished:
+        an update applied per parameter overlaps the exchanges that are still in flight."""
+        handles, self.handles = self.handles, []
+        for p, h in handles:
+            h.wait()
+            yield p
 
     def remove(self):
         for h in self._hooks:
