@@ -195,6 +195,14 @@ class LutLayerWorkload:
 
     # dominant kernel: the table-gradient scatter (2 x 4 x Nt x O bytes of row read-modify-write per sample)
     dominant_kernel = "fc_weight_grad"
+    # DRAM bytes per step by kernel family at batch 65536, from the ncu capture summarised in profiles/fc_layer_b65536.md
+    # (other batch sizes: not captured)
+    ncu_dram_bytes_b65536 = {"fc_weight_grad": 25.7e6, "fc_input_grad": 352.3e6, "fc_gather_forward": 25.7e6,
+                             "check_detectors": 215.1e6}
+
+    @property
+    def ncu_dram_bytes_per_step(self):
+        return self.ncu_dram_bytes_b65536 if self.B == 65536 and self.cuda_graph is None else {}
 
     def algorithmic_bytes(self):
         """Per sample, by kernel family (every gathered / scattered row at full size, RMW counted twice)."""
@@ -334,7 +342,7 @@ class SparseConvNetWorkload:
     dominant_kernel = None  # picked by measured time
     # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) per step of each kernel family, summed over its three
     # launches, from the ncu capture summarised in profiles/sparse_convnet_step_b512.md
-    ncu_dram_bytes_per_step = {"sparse_backward_fused": 915.8e6, "sparse_forward": 351.2e6, "check_detectors": 7.7e6}
+    ncu_dram_bytes_per_step = {"sparse_backward_fused": 928.2e6, "sparse_forward": 354.6e6}
 
     def algorithmic_bytes(self):
         """Per sample and kernel family, summed over the layers that launch it."""
@@ -423,6 +431,13 @@ class CharTransformerWorkload:
     dtype = "f32"
     dominant_kernel = None
     zipf_s = 1.1
+    # DRAM bytes per step (4 layers) of the two contractions at batch 64: captured on one layer and 8 sequences
+    # (profiles/product_attention_layer.md) and scaled: the uint16 histograms / Q grow with the batch, the tables do not
+    ncu_dram_bytes_c3 = {"product_hist_weight_grad": 4 * (8 * 33.5e6 + 17.9e6), "product_row_dots": 4 * (8 * 10.1e6 + 17.9e6)}
+
+    @property
+    def ncu_dram_bytes_per_step(self):
+        return self.ncu_dram_bytes_c3 if (self.B, self.S, self.E, self.L) == (64, 128, 256, 4) else {}
 
     def __init__(self, batch=64, context=128, vocab=65, d_model=256, layers=4, heads=4, n_detectors=16, nc=8, npe=4):
         self.B, self.S, self.V, self.E, self.L, self.H = batch, context, vocab, d_model, layers, heads
@@ -602,6 +617,12 @@ class LutInferWorkload:
     unit = "samples/s"
     scaling = "strong"
     dominant_kernel = None
+    # DRAM bytes per step on one GPU at batch 16384 (profiles/lut_infer_b16384.md; fp32: 6 launches of 146 MB)
+    ncu_dram_bytes_b16384 = {"int8_gather": 923.1e6, "fc_gather_forward": 6 * 146.0e6, "check_detectors": 478.7e6}
+
+    @property
+    def ncu_dram_bytes_per_step(self):
+        return self.ncu_dram_bytes_b16384 if self.B == 16384 and self.world == 1 else {}
 
     def __init__(self, table_dtype="int8", batch=16384, n_inputs=4096, n_detectors=4096, n_anchors=8, n_outputs=64):
         self.kind = table_dtype
