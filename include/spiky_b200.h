@@ -258,9 +258,16 @@ int lutb_concat_backward(const lutb_layer_cfg *cfg, int64_t batch, float *weight
  * The accumulators of detector shards (each a multiple of cfg->backward_group detectors) add up exactly, on one
  * GPU or across GPUs; lutb_fixed_to_float then converts in place: y = f32(double(acc) * 2^-20-ish / int_rescaler)
  * (convert_integers_to_floats_logic, lut_runtime_kernels_logic.proto:200-213).
+ * dequant selects what a table entry is: LUTB_INT8_DEQUANT_F32 the fp32 number f32(scale * q) (the table the
+ * reference would be handed; slower: two conversions per entry), LUTB_INT8_DEQUANT_EXACT the exact real
+ * scale * q (evaluated in fp64, where the 24 x 8 bit product is exact).  The two differ by at most the fp32
+ * rounding of one entry (6e-8 relative) before the block truncation.
  */
+#define LUTB_INT8_DEQUANT_F32 0
+#define LUTB_INT8_DEQUANT_EXACT 1
 int lutb_infer_int8_accumulate(const lutb_layer_cfg *cfg, int64_t batch, const int8_t *q_tables, const float *scales,
-                               const float *x, const int32_t *anchors, int32_t *acc, int32_t *idx, void *stream);
+                               const float *x, const int32_t *anchors, int32_t *acc, int32_t *idx, int dequant,
+                               void *stream);
 int lutb_fixed_to_float(float *buffer, int64_t n, double int_rescaler, void *stream);
 
 #ifdef __cplusplus

@@ -155,6 +155,33 @@ void orc_nonseq_fc_forward(const float *W, const int32_t *idx, float *y, int64_t
 }
 
 /*
+ * int8-table inference (no reference counterpart): fill_outputs_non_seq_fc_logic in int32 fixed-point mode
+ * (proto:1214-1299) on the de-quantised table.  exact = 0: entries are the fp32 numbers f32(scale * q), i.e.
+ * orc_nonseq_fc_forward(int_mode = 1) on that fp32 table; exact = 1: entries are the exact reals scale * q
+ * (the 24 x 8 bit product is exact in double).  acc is accumulated into and left as int32.
+ */
+void orc_infer_int8(const int8_t *Q, const float *scales, const int32_t *idx, int32_t *acc, int64_t B, int O, int Nt,
+                    int T, int Gb, double rescaler, int exact) {
+    int n_blocks = (Nt + Gb - 1) / Gb;
+    ORC_PARALLEL_FOR
+    for (int64_t b = 0; b < B; b++) {
+        const int32_t *li = idx + b * Nt;
+        for (int blk = 0; blk < n_blocks; blk++) {
+            int t0 = blk * Gb, t1 = t0 + Gb < Nt ? t0 + Gb : Nt;
+            for (int o = 0; o < O; o++) {
+                double s = 0.0;
+                for (int t = t0; t < t1; t++) {
+                    int q = Q[((int64_t)t * T + li[t]) * O + o];
+                    if (exact) s += (double)scales[t] * (double)q;
+                    else { volatile float w = scales[t] * (float)q; s += (double)w; }
+                }
+                acc[b * O + o] += (int32_t)(s * ORC_DENOM * rescaler);
+            }
+        }
+    }
+}
+
+/*
  * propagate_through_detectors_non_seq_fc_logic (proto:1421-1499) followed by
  * gather_w_gradients_non_seq_fc_logic (proto:1547-1585, helper :716-819) and the int->float passes
  * of LUTRuntimeContext::backward_backprop (lut_runtime.cu:365-396).

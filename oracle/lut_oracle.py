@@ -102,6 +102,30 @@ def nonseq_fc_forward(W, x, anchors, n_detectors, n_anchors, n_outputs, cmp_eps=
     return y, idx, md, mk
 
 
+def int_to_float(acc, int_rescaler):
+    """int32 fixed-point accumulators -> fp32 (convert_integers_to_floats_logic); returns a new array."""
+    out = np.ascontiguousarray(acc, np.int32).copy().view(np.float32)
+    lib().orc_int_to_float(_ptr(out), _l(out.size), _d(int_rescaler))
+    return out
+
+
+def infer_int8(q, scales, x, anchors, n_detectors, n_anchors, n_outputs, cmp_eps=0.0, backward_group_size=32,
+               int_rescaler=0.001, exact=True):
+    """int8-table inference: (int32 accumulators [B,O], idx [B,Nt]).  exact=False de-quantises to the fp32 numbers
+    f32(scale * q) (identical to the fixed-point forward on that fp32 table), exact=True to the exact reals."""
+    x = _f32(x)
+    B = x.shape[0]
+    T = 1 << n_anchors
+    q = np.ascontiguousarray(q, np.int8).reshape(-1)
+    scales = _f32(scales).reshape(-1)
+    assert q.size == n_detectors * T * n_outputs and scales.size == n_detectors
+    idx = check_detectors(x, anchors, n_detectors, n_anchors, cmp_eps, False)
+    acc = np.zeros((B, n_outputs), np.int32)
+    lib().orc_infer_int8(_ptr(q), _ptr(scales), _ptr(idx), _ptr(acc), _l(B), _i(n_outputs), _i(n_detectors), _i(T),
+                         _i(backward_group_size), _d(int_rescaler), _i(int(exact)))
+    return acc, idx
+
+
 def nonseq_fc_backward(W, dY, anchors, idx, min_delta, min_k, n_inputs, n_anchors, lr_meta=1.0,
                        external_lr=-1.0, forward_group_size=32, int_mode=False, int_rescaler=0.001):
     """One ``backward_backprop`` of a fully connected non-sequence layer.

@@ -13,6 +13,8 @@ LIB_PATH = os.path.join(_HERE, "lib", "libspiky_b200.so")
 DW_AUTO, DW_ATOMIC, DW_SMEM, DW_SORTED = 0, 1, 2, 3
 # product-mode kernel variants (include/spiky_b200.h)
 PRODUCT_AUTO, PRODUCT_DIRECT, PRODUCT_HIST = 0, 1, 2
+# de-quantisation rules of the int8 inference path (include/spiky_b200.h)
+INT8_DEQUANT_F32, INT8_DEQUANT_EXACT = 0, 1
 
 
 class LayerCfg(ctypes.Structure):
@@ -83,7 +85,7 @@ SIGNATURES = {
     "lutb_product_backward": (_int, [_cfgp, _i64, ctypes.c_int32, _vp, _vp, _vp, ctypes.c_int32, ctypes.c_int32, _vp, _vp,
                                      _vp, _vp, _vp, _vp, _vp, _dbl, _int, _vp, _size, _vp]),
     "lutb_nonseq_fc_backward_noalloc": (_int, [_cfgp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _dbl, _vp]),
-    "lutb_infer_int8_accumulate": (_int, [_cfgp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "lutb_infer_int8_accumulate": (_int, [_cfgp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _int, _vp]),
     "lutb_fixed_to_float": (_int, [_vp, _i64, _dbl, _vp]),
     "lutb_nonseq_sparse_forward": (_int, [_cfgp, _spp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "lutb_nonseq_sparse_backward": (_int, [_cfgp, _spp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _dbl, _vp]),

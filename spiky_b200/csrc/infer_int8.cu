@@ -6,6 +6,13 @@
 // truncated toward zero and added to an int32 accumulator.  Integer accumulators make the result independent
 // of summation order, so detector shards computed on different GPUs combine bit-exactly with an integer
 // all-reduce before the final conversion to fp32 (convert_integers_to_floats_logic, proto:200-213).
+//
+// Two de-quantisation rules (cfg-independent argument `dequant`):
+//   LUTB_INT8_DEQUANT_F32    entry = f32(scale * q): exactly the fp32 table the reference would be given; costs two
+//                            conversions per entry (int8 -> fp32 -> fp64) on the conversion unit, which bound the kernel
+//   LUTB_INT8_DEQUANT_EXACT  entry = scale * q as an exact real (24 x 8 bit product, exact in fp64): q is turned into
+//                            a double with integer operations plus one subtraction and multiplied in fp64, so the
+//                            per-entry work runs on the fp64 pipe (one DADD + one DFMA)
 #include "lutb_common.cuh"
 #include "nonseq_fc.cuh"
 
@@ -15,11 +22,18 @@ namespace lutb {
 // load per lane), NG = 32 / LG groups take the detectors of a block round-robin; the per-group double sums
 // are exact (<= 32 fp32 terms of similar magnitude), so combining them across groups before the truncation
 // gives the same bits as the sequential sum.
-template <int LG>
+// q (sign-extended byte) as a double without the conversion unit: the low word of 2^52 + 2^31 + q is
+// 0x80000000 ^ q, and subtracting 2^52 + 2^31 leaves q exactly.  (Byte permutes and shift-and-mask of the biased
+// byte were measured slower than the shift pair that sign-extends.)
+__device__ __forceinline__ double int_to_double_exact(int32_t q) {
+    return __hiloint2double(0x43300000, (int)(0x80000000u ^ (uint32_t)q)) - 4503601774854144.0;
+}
+
+template <int LG, bool EXACT>
 __global__ void __launch_bounds__(256) int8_gather_kernel(const int8_t *__restrict__ Q, const float *__restrict__ scales,
                                                          const int32_t *__restrict__ idx, int32_t *__restrict__ acc,
                                                          int64_t batch, int n_outputs, int n_detectors, int table_rows,
-                                                         int det_block, double fixed_scale) {
+                                                         int det_block, double fixed_scale, int det_begin, int det_end) {
     constexpr int NG = 32 / LG;   // lane groups; group g takes detectors g, g + NG, ... of every 32
     constexpr int IT = 32 / NG;   // = LG row loads per lane and 32 detectors, all issued before the first use
     const int lane = threadIdx.x & 31;
@@ -31,8 +45,9 @@ __global__ void __launch_bounds__(256) int8_gather_kernel(const int8_t *__restri
     const int32_t *idx_b = idx + b * n_detectors;
     const int8_t *Qc = Q + col;
     int32_t iacc[4] = {0, 0, 0, 0};
-    for (int tb = 0; tb < n_detectors; tb += det_block) {
-        const int tend = min(tb + det_block, n_detectors);
+    // [det_begin, det_end) starts on a block boundary: one launch covers a range of detectors whose tables stay in L2
+    for (int tb = det_begin; tb < det_end; tb += det_block) {
+        const int tend = min(tb + det_block, det_end);
         double s[4] = {0.0, 0.0, 0.0, 0.0};
         for (int t0 = tb; t0 < tend; t0 += 32) {
             const int nvalid = min(32, tend - t0);
@@ -51,10 +66,18 @@ __global__ void __launch_bounds__(256) int8_gather_kernel(const int8_t *__restri
 #pragma unroll
             for (int i = 0; i < IT; i++) {
                 const float sc = __shfl_sync(0xffffffffu, my_scale, i * NG + g);   // 0 beyond nvalid
-                s[0] += (double)__fmul_rn(sc, (float)(int8_t)(packed[i] & 0xff));
-                s[1] += (double)__fmul_rn(sc, (float)(int8_t)((packed[i] >> 8) & 0xff));
-                s[2] += (double)__fmul_rn(sc, (float)(int8_t)((packed[i] >> 16) & 0xff));
-                s[3] += (double)__fmul_rn(sc, (float)(int8_t)((packed[i] >> 24) & 0xff));
+                if (EXACT) {
+                    const double sd = (double)sc;
+                    s[0] = fma(sd, int_to_double_exact((int32_t)(packed[i] << 24) >> 24), s[0]);
+                    s[1] = fma(sd, int_to_double_exact((int32_t)(packed[i] << 16) >> 24), s[1]);
+                    s[2] = fma(sd, int_to_double_exact((int32_t)(packed[i] << 8) >> 24), s[2]);
+                    s[3] = fma(sd, int_to_double_exact(packed[i] >> 24), s[3]);
+                } else {
+                    s[0] += (double)__fmul_rn(sc, (float)(int8_t)(packed[i] & 0xff));
+                    s[1] += (double)__fmul_rn(sc, (float)(int8_t)((packed[i] >> 8) & 0xff));
+                    s[2] += (double)__fmul_rn(sc, (float)(int8_t)((packed[i] >> 16) & 0xff));
+                    s[3] += (double)__fmul_rn(sc, (float)(int8_t)((packed[i] >> 24) & 0xff));
+                }
             }
         }
 #pragma unroll
@@ -78,7 +101,7 @@ using namespace lutb;
 
 extern "C" int lutb_infer_int8_accumulate(const lutb_layer_cfg *cfg, int64_t batch, const int8_t *q_tables,
                                           const float *scales, const float *x, const int32_t *anchors,
-                                          int32_t *acc, int32_t *idx, void *stream) {
+                                          int32_t *acc, int32_t *idx, int dequant, void *stream) {
     int rc = validate_cfg(cfg);
     if (rc) return rc;
     LUTB_REQUIRE(cfg->seq_len == 1, LUTB_ERR_MODE, "int8 inference is defined for non-sequence layers");
@@ -87,6 +110,8 @@ extern "C" int lutb_infer_int8_accumulate(const lutb_layer_cfg *cfg, int64_t bat
     LUTB_REQUIRE(cfg->n_outputs % 4 == 0, LUTB_ERR_SHAPE, "int8 inference needs n_outputs to be a multiple of 4");
     LUTB_REQUIRE((reinterpret_cast<uintptr_t>(q_tables) & 3) == 0, LUTB_ERR_ALIGN, "q_tables must be 4-byte aligned");
     LUTB_REQUIRE(cfg->int_rescaler > 0.0, LUTB_ERR_MODE, "int_rescaler must be positive");
+    LUTB_REQUIRE(dequant == LUTB_INT8_DEQUANT_F32 || dequant == LUTB_INT8_DEQUANT_EXACT, LUTB_ERR_MODE,
+                 "unknown de-quantisation rule %d", dequant);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     rc = launch_check_detectors(x, batch, cfg->n_inputs, anchors, cfg->n_detectors, cfg->n_anchors, cfg->cmp_eps, idx,
                                 nullptr, nullptr, st);
@@ -97,10 +122,25 @@ extern "C" int lutb_infer_int8_accumulate(const lutb_layer_cfg *cfg, int64_t bat
     const int n_chunks = (cfg->n_outputs + lanes * 4 - 1) / (lanes * 4);
     const int64_t blocks = (batch + 7) / 8;
     LUTB_REQUIRE(blocks <= 0x7FFFFFFF && n_chunks <= 65535, LUTB_ERR_SHAPE, "grid too large");
-    KernelScope scope(K_INT8_GATHER, st);
     const dim3 grid((unsigned)blocks, (unsigned)n_chunks);
-#define LUTB_INT8(LGV) int8_gather_kernel<LGV><<<grid, 256, 0, st>>>(q_tables, scales, idx, acc, batch, cfg->n_outputs, \
-        cfg->n_detectors, 1 << cfg->n_anchors, cfg->backward_group, cfg->int_rescaler)
+    // detector ranges of at most 40 MB of tables (whole blocks): the rows of a range are fetched from DRAM once and
+    // then served by L2 while the batch streams through
+    const size_t table_bytes = ((size_t)1 << cfg->n_anchors) * cfg->n_outputs;
+    int64_t per_range = (int64_t)((size_t)(40u << 20) / table_bytes);
+    per_range = per_range / cfg->backward_group * cfg->backward_group;
+    if (per_range < cfg->backward_group) per_range = cfg->backward_group;
+    for (int64_t t0 = 0; t0 < cfg->n_detectors; t0 += per_range) {
+    const int det_begin = (int)t0, det_end = (int)(t0 + per_range < cfg->n_detectors ? t0 + per_range : cfg->n_detectors);
+    KernelScope scope(K_INT8_GATHER, st);
+#define LUTB_INT8(LGV)                                                                                                  \
+    do {                                                                                                               \
+        if (dequant == LUTB_INT8_DEQUANT_EXACT)                                                                        \
+            int8_gather_kernel<LGV, true><<<grid, 256, 0, st>>>(q_tables, scales, idx, acc, batch, cfg->n_outputs,     \
+                cfg->n_detectors, 1 << cfg->n_anchors, cfg->backward_group, cfg->int_rescaler, det_begin, det_end);    \
+        else                                                                                                           \
+            int8_gather_kernel<LGV, false><<<grid, 256, 0, st>>>(q_tables, scales, idx, acc, batch, cfg->n_outputs,    \
+                cfg->n_detectors, 1 << cfg->n_anchors, cfg->backward_group, cfg->int_rescaler, det_begin, det_end);    \
+    } while (0)
     switch (lanes) {
         case 32: LUTB_INT8(32); break;
         case 16: LUTB_INT8(16); break;
@@ -109,8 +149,9 @@ extern "C" int lutb_infer_int8_accumulate(const lutb_layer_cfg *cfg, int64_t bat
         case 2: LUTB_INT8(2); break;
         default: LUTB_INT8(1); break;
     }
-#undef LUTB_INT8
     LUTB_LAUNCH_CHECK();
+    }
+#undef LUTB_INT8
     return LUTB_OK;
 }
 

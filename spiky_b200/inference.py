@@ -3,8 +3,10 @@
 Neither exists in the reference (it has no quantised tables and is single-device).  Definitions:
 
 * int8 tables: ``q int8 [Nt, T, O]`` with one fp32 scale per table.  Outputs are the reference's int32
-  fixed-point forward (``LUTDataManagerI``) evaluated on the de-quantised table ``f32(scale[t] * q)``, so the
-  existing fixed-point oracle pins the arithmetic bit for bit.
+  fixed-point forward (``LUTDataManagerI``) evaluated on the de-quantised table: ``dequant='f32'`` takes the
+  entries as the fp32 numbers ``f32(scale[t] * q)`` (exactly what the reference would be handed, so the
+  fixed-point oracle pins the arithmetic bit for bit), ``dequant='exact'`` (default, about four times faster) as
+  the exact reals ``scale[t] * q``; the two differ by one fp32 rounding per entry before the block truncation.
 * detector sharding: rank r owns detectors ``[r * Nt / G, (r + 1) * Nt / G)`` with their anchors and tables,
   the input batch is replicated, every rank produces partial sums for all outputs and one all-reduce
   combines them (int32 accumulators for int8 tables: exact, order independent; fp32 for fp32 tables).
@@ -38,8 +40,9 @@ class LUTInference:
     """
 
     def __init__(self, n_inputs, n_outputs, n_detectors, n_anchors, anchors, tables, scales=None, cmp_eps=0.0,
-                 backward_group_size=32, int_rescaler=0.001, group=None, device="cuda:0"):
+                 backward_group_size=32, int_rescaler=0.001, group=None, device="cuda:0", dequant="exact"):
         self.device = torch.device(device)
+        self.dequant = {"f32": _native.INT8_DEQUANT_F32, "exact": _native.INT8_DEQUANT_EXACT}[dequant]
         self.I, self.O, self.Nt, self.Nc = n_inputs, n_outputs, n_detectors, n_anchors
         self.anchors = anchors.to(self.device, torch.int32).reshape(-1).contiguous()
         self.int8 = tables.dtype == torch.int8
@@ -81,7 +84,8 @@ class LUTInference:
             if self.int8:
                 acc = torch.zeros(B * self.O, dtype=torch.int32, device=self.device)
                 rc = L.lutb_infer_int8_accumulate(ctypes.byref(self.cfg), B, _ptr(self.tables), _ptr(self.scales),
-                                                  _ptr(x.view(-1)), _ptr(self.anchors), _ptr(acc), _ptr(idx), stream)
+                                                  _ptr(x.view(-1)), _ptr(self.anchors), _ptr(acc), _ptr(idx), self.dequant,
+                                                  stream)
             else:
                 acc = torch.zeros(B * self.O, dtype=torch.float32, device=self.device)
                 rc = L.lutb_nonseq_fc_forward(ctypes.byref(self.cfg), B, _ptr(self.tables), _ptr(x.view(-1)),

@@ -68,3 +68,54 @@ def test_failed_rank_is_reported_on_the_host(tmp_path):
     with pytest.raises(Exception):
         mp.spawn(_worker, args=(2, _free_port(), str(tmp_path), 1), nprocs=2, join=True)
     assert not (tmp_path / "ok").exists()
+
+
+def _overlap_worker(rank, world, port, result_dir):
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests", "golden"))
+    import datetime
+    import synth
+    from oracle import lut_oracle as orc
+    from spiky_b200.data_parallel import OverlappedGradientSync
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=20))
+    try:
+        # (1) hook-driven exchange: every parameter's gradient is averaged over the ranks as soon as autograd has
+        # produced it; wait_each yields the parameters in production order
+        a = torch.nn.Parameter(torch.arange(6, dtype=torch.float32))
+        b = torch.nn.Parameter(torch.ones(4))
+        sync = OverlappedGradientSync([a, b], average=True)
+        loss = ((rank + 1) * a).sum() + ((rank + 1) ** 2 * b * b).sum()
+        loss.backward()
+        order = [id(p) for p in sync.wait_each()]
+        mean1 = sum(r + 1 for r in range(world)) / world
+        mean2 = sum(2 * (r + 1) ** 2 for r in range(world)) / world
+        ok = set(order) == {id(a), id(b)} and torch.allclose(a.grad, torch.full((6,), mean1)) and \
+            torch.allclose(b.grad, torch.full((4,), mean2)) and sync.handles == []
+        sync.remove()
+        # (2) detector sharding: integer partial accumulators of the shards add up to the unsharded result exactly
+        B, I, Nt, Nc, O = 10, 64, 128, 5, 8
+        x = synth.normal(11, (B, I))
+        anchors = synth.anchor_pairs(12, Nt, Nc, I)
+        q = synth.integers(13, (Nt * (1 << Nc) * O,), -127, 128).astype(np.int8)
+        s = (0.02 / 127 * synth.uniform(14, (Nt,), 0.5, 1.5)).astype(np.float32)
+        per = Nt // world
+        T = 1 << Nc
+        part, _ = orc.infer_int8(q.reshape(Nt, -1)[rank * per:(rank + 1) * per].reshape(-1), s[rank * per:(rank + 1) * per],
+                                 x, anchors.reshape(Nt, -1)[rank * per:(rank + 1) * per].reshape(per, Nc, 2), per, Nc, O,
+                                 int_rescaler=0.05)
+        acc = torch.from_numpy(part.copy())
+        dist.all_reduce(acc, op=dist.ReduceOp.SUM)
+        full, _ = orc.infer_int8(q, s, x, anchors, Nt, Nc, O, int_rescaler=0.05)
+        ok = ok and np.array_equal(acc.numpy(), full)
+        if rank == 0:
+            open(os.path.join(result_dir, "ok2"), "w").write(str(bool(ok)))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_overlapped_gradient_sync_and_sharded_accumulators(tmp_path):
+    mp.spawn(_overlap_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
+    assert open(tmp_path / "ok2").read() == "True"

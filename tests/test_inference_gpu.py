@@ -33,12 +33,34 @@ def test_int8_inference_is_bit_exact_with_fixed_point_reference_on_dequantized_t
     B, I, Nt, Nc, O = shape
     x, anchors, q, s = make_problem(900, B, I, Nt, Nc, O)
     layer = LUTInference(I, O, Nt, Nc, torch.from_numpy(anchors), torch.from_numpy(q), torch.from_numpy(s),
-                         int_rescaler=0.05)
+                         int_rescaler=0.05, dequant="f32")
     y = layer(torch.from_numpy(x).cuda()).cpu().numpy()
     ref, ridx, _, _ = orc.nonseq_fc_forward(dequantize(q, s, Nt), x, anchors, Nt, Nc, O, train=False, int_mode=True,
                                             int_rescaler=0.05)
     assert np.array_equal(layer.last_indices.cpu().numpy(), ridx)
     assert np.array_equal(y, ref)
+    # the dedicated int8 oracle function agrees with the pinned fixed-point forward on the de-quantised table
+    acc, _ = orc.infer_int8(q, s, x, anchors, Nt, Nc, O, int_rescaler=0.05, exact=False)
+    assert np.array_equal(orc.int_to_float(acc, 0.05), ref)
+
+
+@pytest.mark.parametrize("shape", [(33, 256, 64, 8, 64), (16, 4096, 512, 8, 64), (9, 40, 96, 5, 12), (5, 64, 70, 6, 128)])
+def test_int8_inference_exact_product_rule_is_bit_exact(shape):
+    """Entries taken as the exact reals scale * q (the default, fast rule): bit-exact against the oracle's
+    restatement, and within one fp32 rounding per entry of the f32 rule."""
+    from spiky_b200.inference import LUTInference
+
+    B, I, Nt, Nc, O = shape
+    x, anchors, q, s = make_problem(905, B, I, Nt, Nc, O)
+    layer = LUTInference(I, O, Nt, Nc, torch.from_numpy(anchors), torch.from_numpy(q), torch.from_numpy(s),
+                         int_rescaler=0.05)
+    xt = torch.from_numpy(x).cuda()
+    acc = layer.partial(xt).cpu().numpy()
+    want, ridx = orc.infer_int8(q, s, x, anchors, Nt, Nc, O, int_rescaler=0.05, exact=True)
+    assert np.array_equal(layer.last_indices.cpu().numpy(), ridx)
+    assert np.array_equal(acc, want)
+    other, _ = orc.infer_int8(q, s, x, anchors, Nt, Nc, O, int_rescaler=0.05, exact=False)
+    assert np.abs(acc.astype(np.int64) - other).max() <= (Nt + 31) // 32   # at most one unit per detector block
 
 
 @pytest.mark.parametrize("world", [2, 4])
