@@ -13,6 +13,8 @@ namespace lutb {
 constexpr double kDenom = 1048575.0;                  // DENOMINATOR32 = 0xFFFFF
 constexpr double kDenomRecip = 9.536752259018191e-07;  // DENOMINATOR32_RECIPROC
 constexpr double kEps = 0.00000000000000001;           // EPS: contributions with |v| <= EPS are dropped
+// largest float not above EPS: for a float g, fabsf(g) > kEpsF is the same predicate as fabs((double)g) > kEps
+constexpr float kEpsF = 1e-17f;
 constexpr int32_t kNoAnchor = -1;                      // 0xFFFFFFFF marks an unused anchor pair
 
 constexpr int kMaxSmemPerBlock = 227 * 1024;  // opt-in dynamic shared memory limit on sm_100

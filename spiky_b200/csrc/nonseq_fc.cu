@@ -465,9 +465,13 @@ int launch_fc_gather_forward(const float *W, const int32_t *idx, float *y, int64
 
 // --------------------------------------------------------------------------------------------
 // Kernel 3: surrogate input gradient (reference: propagate_through_detectors_non_seq_fc_logic,
-// proto:1421-1499).  Per (sample, detector): g = sum_o dY[o] * (W[t, j, o] - W[t, j ^ 2^k, o]) in
-// double, du = up(min_delta) * g, then +du / -du on the two inputs of the flipped anchor pair.
-// Same warp layout as the forward gather; both rows are read with coalesced vector loads.
+// proto:1421-1499).  Per (sample, detector): g = sum_o dY[o] * (W[t, j, o] - W[t, j ^ 2^k, o]),
+// du = up(min_delta) * g, then +du / -du on the two inputs of the flipped anchor pair.
+// Same warp layout as the forward gather; both rows are read with coalesced vector loads.  The products of one
+// vector are summed in fp32 and added to a double per lane (converting every operand to double kept the
+// conversion unit busy: three conversions per element), the lane groups are reduced in double, and the dot
+// products of 32 detectors are parked in shared memory so that the surrogate derivative (a double division) and
+// the two reductions into dX run once per detector on 32 lanes instead of once per lane group on one lane in LG.
 // --------------------------------------------------------------------------------------------
 template <int VEC>
 __global__ void __launch_bounds__(256) fc_input_grad_kernel(const float *__restrict__ W, const float *__restrict__ dY,
@@ -477,9 +481,11 @@ __global__ void __launch_bounds__(256) fc_input_grad_kernel(const float *__restr
                                                            const int32_t *__restrict__ min_k, float *__restrict__ dX,
                                                            int64_t batch, int n_inputs, int n_outputs, int n_detectors,
                                                            int n_anchors, int table_rows, int lanes_per_row) {
+    __shared__ double dots[8][32];
     const int lane = threadIdx.x & 31;
     const int64_t b = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (b >= batch) return;
+    double *my_dots = dots[(threadIdx.x >> 5) & 7];
     const int LG = lanes_per_row;
     const int NG = 32 / LG;
     const int g = lane / LG;
@@ -491,20 +497,19 @@ __global__ void __launch_bounds__(256) fc_input_grad_kernel(const float *__restr
 
     for (int tb = 0; tb < n_detectors; tb += 32) {
         const int nvalid = min(32, n_detectors - tb);
-        int32_t my_idx = 0, my_k = 0;
+        int32_t my_idx = 0, my_k = -1;
         float my_m = 0.f;
         if (lane < nvalid) {
             my_idx = __ldg(idx + base + tb + lane);
             my_k = __ldg(min_k + base + tb + lane);
             my_m = __ldg(min_delta + base + tb + lane);
         }
-        for (int sb = 0; sb < nvalid; sb += NG) {
+        for (int sb = 0; sb < nvalid; sb += NG) {   // uniform trip count: every lane runs every shuffle
             const int s = sb + g;
             const int32_t li = __shfl_sync(0xffffffffu, my_idx, s & 31);
             const int32_t k = __shfl_sync(0xffffffffu, my_k, s & 31);
-            const float m = __shfl_sync(0xffffffffu, my_m, s & 31);
             double acc = 0.0;
-            const bool valid = s < nvalid;
+            const bool valid = s < nvalid && k >= 0;
             if (valid) {
                 const int t = tb + s;
                 const float *row = W + ((size_t)t * table_rows + li) * n_outputs;
@@ -514,20 +519,25 @@ __global__ void __launch_bounds__(256) fc_input_grad_kernel(const float *__restr
                     Vec<VEC>::load(row + col, a);
                     Vec<VEC>::load(alt + col, c);
                     Vec<VEC>::load(dy + col, d);
+                    float part = 0.f;
 #pragma unroll
-                    for (int e = 0; e < VEC; e++) acc += (double)d[e] * ((double)a[e] - (double)c[e]);
+                    for (int e = 0; e < VEC; e++) part = fmaf(d[e], a[e] - c[e], part);
+                    acc += (double)part;
                 }
             }
             for (int off = 1; off < LG; off <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
-            if (valid && j == 0) {
-                const double du = surrogate_up(m) * acc;
-                if (fabs(du) > kEps) {
-                    const int2 p = __ldg(anchors + (size_t)(tb + s) * n_anchors + k);
-                    atomicAdd(dx + p.x, (float)du);
-                    atomicAdd(dx + p.y, -(float)du);
-                }
+            if (s < nvalid && j == 0) my_dots[s] = acc;
+        }
+        __syncwarp();
+        if (lane < nvalid && my_k >= 0) {
+            const double du = surrogate_up(my_m) * my_dots[lane];
+            if (fabs(du) > kEps) {
+                const int2 p = __ldg(anchors + (size_t)(tb + lane) * n_anchors + my_k);
+                atomicAdd(dx + p.x, (float)du);
+                atomicAdd(dx + p.y, -(float)du);
             }
         }
+        __syncwarp();
     }
 }
 

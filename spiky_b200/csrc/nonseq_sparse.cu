@@ -197,10 +197,10 @@ __device__ __forceinline__ void chunk_backward(const SparseView &sp, const Chunk
         float val = 0.f;
         int32_t ival = 0;
         bool active = false;
-        if (DO_DW && valid && fabs((double)gp) > kEps) {
+        if (DO_DW && valid && fabsf(gp) > kEpsF) {
             active = true;
             if (INT_DW) ival = to_fixed((double)gp * lr, fixed_scale);
-            else val = (float)((double)gp * lr);
+            else val = lr == 1.0 ? gp : (float)((double)gp * lr);   // the product with 1.0 is gp itself
         }
         float v[LG];
 #pragma unroll
