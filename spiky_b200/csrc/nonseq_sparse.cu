@@ -52,6 +52,24 @@ __device__ __forceinline__ ChunkStatic load_chunk(const SparseView &sp, int64_t 
     return cs;
 }
 
+// With 512 samples over 256-row tables every row is touched about twice per step, so half of the row gathers are
+// compulsory DRAM misses at random addresses.  Each warp therefore asks L2 for its share of the tables of the
+// chunk that will be processed kPrefetchAhead chunks later (about the chunks in flight on the whole GPU), turning
+// those misses into a sequential stream that is resident when the gathers arrive.  Measured: forward -4 %, fused
+// backward -0.5 % (prefetching the gradient rows as well made the backward slower, so they are not prefetched).
+constexpr int kPrefetchAhead = 40;
+
+__device__ __forceinline__ void prefetch_chunk(const SparseView &sp, const float *base, int64_t c, int64_t r, int64_t runs,
+                                               int lane) {
+    if (c >= sp.n_chunks) return;
+    const ChunkStatic cs = load_chunk(sp, c);
+    const int64_t lines = ((int64_t)cs.ndet * cs.table * 4 + 127) >> 7;
+    const int64_t per = (lines + runs - 1) / runs;
+    const int64_t end = min(lines, (r + 1) * per);
+    const char *p = reinterpret_cast<const char *>(base + cs.wbase0);
+    for (int64_t l = r * per + lane; l < end; l += 32) asm volatile("prefetch.global.L2 [%0];" ::"l"(p + (l << 7)));
+}
+
 // --------------------------------------------------------------------------------------------
 // Forward: y[b, target(p)] += sum over the chunk's detectors of W[row(t, idx[b, t]) + p]
 // (reference: fill_outputs_non_seq_sparse_logic + fire_single_synapse_group, proto:1160-1212, 215-313).
@@ -113,6 +131,7 @@ __global__ void __launch_bounds__(256, 4) sparse_forward_kernel(SparseView sp, c
     const int64_t c = work / runs;
     const int64_t b0 = (work - c * runs) * kSampleRun;
     const int64_t b1 = min(batch, b0 + kSampleRun);
+    prefetch_chunk(sp, W, c + kPrefetchAhead, work - c * runs, runs, lane);
     const ChunkStatic cs = load_chunk(sp, c);
     if (cs.P <= 8) chunk_forward<8, INT_MODE>(sp, cs, W, idx, y, b0, b1, n_outputs, n_detectors, lane, fixed_scale);
     else if (cs.P <= 16) chunk_forward<16, INT_MODE>(sp, cs, W, idx, y, b0, b1, n_outputs, n_detectors, lane, fixed_scale);
@@ -262,6 +281,7 @@ __global__ void __launch_bounds__(256, 4) sparse_backward_kernel(SparseView sp, 
     const int64_t c = work / runs;
     const int64_t b0 = (work - c * runs) * kSampleRun;
     const int64_t b1 = min(batch, b0 + kSampleRun);
+    if (DO_DX) prefetch_chunk(sp, W, c + kPrefetchAhead, work - c * runs, runs, lane);
     const ChunkStatic cs = load_chunk(sp, c);
     if (cs.P <= 8)
         chunk_backward<8, DO_DX, DO_DW, INT_DW>(sp, cs, W, dY, anchors, idx, min_delta, min_k, dX, target_arr, b0, b1, n_inputs, n_outputs, n_detectors, n_anchors, lane, lr, fixed_scale);
