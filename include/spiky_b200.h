@@ -270,6 +270,23 @@ int lutb_infer_int8_accumulate(const lutb_layer_cfg *cfg, int64_t batch, const i
                                void *stream);
 int lutb_fixed_to_float(float *buffer, int64_t n, double int_rescaler, void *stream);
 
+/*
+ * Compaction of a dense 32-bit array (fp32 or int32 bit patterns) into sorted (index, value) lists: what the Sparse
+ * gradient policy runs on the dense table gradient.  Replaces DenseToSparseConverterNative::count_nonzero and
+ * ::dense_to_sparse_32 (spiky_cuda/torch_utils/torch_utils.cu:212-322 and :29-210; kernels densify_logic,
+ * count_nonzero_logic, densify_new_logic in spiky_cuda/torch_utils/torch_utils_kernels_logic.proto:1-324).  Differences: positions come from a prefix sum, so the lists are in index
+ * order and deterministic (the reference's order depends on scheduling); the scratch is a caller workspace of
+ * lutb_dense_to_sparse_workspace(n) bytes instead of a counter tensor.
+ *   source 32-bit words [n] (device); count_out int64 (device): number of non-zero words
+ *   indices int64 [capacity], values 32-bit [capacity]: the first min(count, capacity) entries are written
+ *   erase_input != 0: the source is zeroed (the shared gradient buffer is handed to the next layer clean)
+ */
+size_t lutb_dense_to_sparse_workspace(int64_t n);
+int lutb_count_nonzero_32(const void *source, int64_t n, int64_t *count_out, void *workspace, size_t workspace_bytes,
+                          void *stream);
+int lutb_dense_to_sparse_32(void *source, int64_t n, int64_t *indices, void *values, int64_t capacity,
+                            int64_t *count_out, int erase_input, void *workspace, size_t workspace_bytes, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -87,6 +87,9 @@ SIGNATURES = {
     "lutb_nonseq_fc_backward_noalloc": (_int, [_cfgp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _dbl, _vp]),
     "lutb_infer_int8_accumulate": (_int, [_cfgp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _int, _vp]),
     "lutb_fixed_to_float": (_int, [_vp, _i64, _dbl, _vp]),
+    "lutb_dense_to_sparse_workspace": (_size, [_i64]),
+    "lutb_count_nonzero_32": (_int, [_vp, _i64, _vp, _vp, _size, _vp]),
+    "lutb_dense_to_sparse_32": (_int, [_vp, _i64, _vp, _vp, _i64, _vp, _int, _vp, _size, _vp]),
     "lutb_nonseq_sparse_forward": (_int, [_cfgp, _spp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "lutb_nonseq_sparse_backward": (_int, [_cfgp, _spp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _dbl, _vp]),
 }

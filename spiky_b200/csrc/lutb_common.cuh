@@ -88,6 +88,7 @@ enum KernelId {
     K_PRODUCT_ROW_DOTS,
     K_PRODUCT_ROUTE,
     K_PRODUCT_HIST_WEIGHT_GRAD,
+    K_DENSE_TO_SPARSE,
     K_COUNT
 };
 

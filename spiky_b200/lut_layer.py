@@ -91,6 +91,14 @@ class LUTSharedContext(object):
             assert torch.count_nonzero(buf) == 0
         return buf[:numel]
 
+    def get_dense_to_sparse_converter(self, multi_id=0):
+        """One reusable converter per multi_id (reference: LUTLayer.py:88-94)."""
+        from .torch_utils import DenseToSparseConverter
+        convs = self.__dict__.setdefault("_dense_to_sparse_converters", {})
+        if multi_id not in convs:
+            convs[multi_id] = DenseToSparseConverter()
+        return convs[multi_id]
+
     def get_cuda_streams(self, device, multi_id=0):
         return None
 
@@ -430,13 +438,11 @@ class LUTLayerBasic(nn.Module):
         if w_grad is None:
             return None
         if policy.type == GradientType.Sparse:
-            n = self._weights.numel()
-            dense = w_grad[:n]
-            nz = torch.nonzero(dense, as_tuple=False).view(-1)
-            if nz.numel() == 0:
+            # compaction kernel (sorted, deterministic); erases the shared buffer so the next layer gets it clean
+            nz, values = self._shared_context.get_dense_to_sparse_converter(self._multi_id).dense_to_sparse_32(
+                w_grad, erase_input=True)
+            if nz is None:
                 return None
-            values = dense[nz].clone()
-            dense.zero_()  # the shared buffer must be clean for the next layer
             if policy.normalized:
                 values /= values.abs().max().clip(1e-16)
             return torch.sparse_coo_tensor(nz.unsqueeze(0), values, size=self._weights.shape, device=self.device,
