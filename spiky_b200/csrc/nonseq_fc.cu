@@ -16,6 +16,15 @@ namespace lutb {
 // emits the packed table index and, for training, the first anchor pair of minimal |delta| with its
 // signed delta (reference: check_detectors[_eval]_logic, lut_runtime_kernels_logic.proto:1050-1158).
 // --------------------------------------------------------------------------------------------
+// 16-byte slots of the transposed staging area are XOR-swizzled with the 8-slot row they lie in: neighbouring
+// lanes stage inputs 4 apart (slots 4 * R / 4 apart), which without the swizzle all fall into the same banks.
+__device__ __forceinline__ int swizzle_slot(int slot) { return slot ^ ((slot >> 3) & 7); }
+// floats of one row group's staging area (whole 8-slot rows, so a swizzled slot never leaves the area)
+template <int R>
+__host__ __device__ constexpr size_t staged_floats(int n_inputs) {
+    return R % 4 == 0 ? ((((size_t)n_inputs * (R / 4)) + 7) & ~(size_t)7) * 4 : (size_t)R * n_inputs;
+}
+
 template <int R, bool TRAIN>
 __global__ void __launch_bounds__(256) check_detectors_kernel(const float *__restrict__ x, int64_t rows, int n_inputs,
                                                              const int2 *__restrict__ anchors, int n_detectors,
@@ -27,7 +36,7 @@ __global__ void __launch_bounds__(256) check_detectors_kernel(const float *__res
     const int groups = blockDim.x / threads_per_group;
     const int g = threadIdx.x / threads_per_group;
     const int lt = threadIdx.x - g * threads_per_group;
-    float *xs = xs_all + (size_t)g * R * n_inputs;
+    float *xs = xs_all + (size_t)g * staged_floats<R>(n_inputs);
     const int64_t row0 = ((int64_t)blockIdx.x * groups + g) * R;
     const int nrows = (int)min((int64_t)R, max((int64_t)0, rows - row0));
 
@@ -49,7 +58,7 @@ __global__ void __launch_bounds__(256) check_detectors_kernel(const float *__res
                 if constexpr (R % 4 == 0) {
 #pragma unroll
                     for (int r4 = 0; r4 < R / 4; r4++)
-                        reinterpret_cast<float4 *>(dst)[r4] =
+                        reinterpret_cast<float4 *>(xs)[swizzle_slot((4 * i4 + j) * (R / 4) + r4)] =
                             make_float4(v[4 * r4][j], v[4 * r4 + 1][j], v[4 * r4 + 2][j], v[4 * r4 + 3][j]);
                 } else {
 #pragma unroll
@@ -77,6 +86,7 @@ __global__ void __launch_bounds__(256) check_detectors_kernel(const float *__res
 #pragma unroll
         for (int r = 0; r < R; r++) { li[r] = 0; md[r] = 0.f; mk[r] = -1; }
         const int2 *ap = anchors + (size_t)t * n_anchors;
+#pragma unroll 4
         for (int k = 0; k < n_anchors; k++) {
             const int2 p = __ldg(ap + k);
             if (p.x == kNoAnchor || p.y == kNoAnchor) continue;
@@ -84,8 +94,8 @@ __global__ void __launch_bounds__(256) check_detectors_kernel(const float *__res
             if constexpr (R % 4 == 0) {
 #pragma unroll
                 for (int r4 = 0; r4 < R / 4; r4++) {
-                    const float4 qa = reinterpret_cast<const float4 *>(xs + (size_t)p.x * R)[r4];
-                    const float4 qb = reinterpret_cast<const float4 *>(xs + (size_t)p.y * R)[r4];
+                    const float4 qa = reinterpret_cast<const float4 *>(xs)[swizzle_slot(p.x * (R / 4) + r4)];
+                    const float4 qb = reinterpret_cast<const float4 *>(xs)[swizzle_slot(p.y * (R / 4) + r4)];
                     a[4 * r4] = qa.x; a[4 * r4 + 1] = qa.y; a[4 * r4 + 2] = qa.z; a[4 * r4 + 3] = qa.w;
                     b[4 * r4] = qb.x; b[4 * r4 + 1] = qb.y; b[4 * r4 + 2] = qb.z; b[4 * r4 + 3] = qb.w;
                 }
@@ -144,7 +154,7 @@ template <int R>
 static int launch_check_detectors_r(const float *x, int64_t rows, int n_inputs, const int32_t *anchors,
                                     int n_detectors, int n_anchors, float cmp_eps, int32_t *idx, float *min_delta,
                                     int32_t *min_k, int tpg, int groups, int det_slices, cudaStream_t stream) {
-    const size_t smem = (size_t)groups * R * n_inputs * sizeof(float);
+    const size_t smem = (size_t)groups * staged_floats<R>(n_inputs) * sizeof(float);
     const int64_t rows_per_block = (int64_t)groups * R;
     const int64_t blocks = (rows + rows_per_block - 1) / rows_per_block;
     LUTB_REQUIRE(blocks <= 0x7FFFFFFF, LUTB_ERR_SHAPE, "batch too large for one launch");
