@@ -69,7 +69,11 @@ __global__ void __launch_bounds__(256) check_detectors_kernel(const float *__res
     } else {
         for (int i = lt; i < n_inputs; i += threads_per_group) {
 #pragma unroll
-            for (int r = 0; r < R; r++) xs[(size_t)i * R + r] = (r < nrows) ? __ldcs(x + (row0 + r) * n_inputs + i) : 0.f;
+            for (int r = 0; r < R; r++) {
+                const float v = (r < nrows) ? __ldcs(x + (row0 + r) * n_inputs + i) : 0.f;
+                if constexpr (R % 4 == 0) xs[swizzle_slot(i * (R / 4) + (r >> 2)) * 4 + (r & 3)] = v;
+                else xs[(size_t)i * R + r] = v;
+            }
         }
     }
     __syncthreads();
