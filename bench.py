@@ -197,8 +197,8 @@ class LutLayerWorkload:
     dominant_kernel = "fc_weight_grad"
     # DRAM bytes per step by kernel family at batch 65536, from the ncu capture summarised in profiles/fc_layer_b65536.md
     # (other batch sizes: not captured)
-    ncu_dram_bytes_b65536 = {"fc_weight_grad": 25.7e6, "fc_input_grad": 352.3e6, "fc_gather_forward": 25.7e6,
-                             "check_detectors": 215.1e6}
+    ncu_dram_bytes_b65536 = {"fc_weight_grad": 25.7e6, "fc_input_grad": 349.9e6, "fc_gather_forward": 25.7e6,
+                             "check_detectors": 213.3e6}
 
     @property
     def ncu_dram_bytes_per_step(self):
@@ -342,7 +342,7 @@ class SparseConvNetWorkload:
     dominant_kernel = None  # picked by measured time
     # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) per step of each kernel family, summed over its three
     # launches, from the ncu capture summarised in profiles/sparse_convnet_step_b512.md
-    ncu_dram_bytes_per_step = {"sparse_backward_fused": 928.2e6, "sparse_forward": 354.6e6}
+    ncu_dram_bytes_per_step = {"sparse_backward_fused": 928.2e6, "sparse_forward": 432.1e6, "check_detectors": 7.7e6}
 
     def algorithmic_bytes(self):
         """Per sample and kernel family, summed over the layers that launch it."""
@@ -563,6 +563,93 @@ class CharTransformerWorkload:
         return time.perf_counter() - t0
 
 
+class AttentionLayerWorkload:
+    """One product-mode attention LUT layer of the character transformer, forward + backward: context 128, 256 inputs
+    and outputs, 64 detectors x 8 anchor pairs (256-row tables), 4 positional dims; x uniform [0,1), tables N(0, 0.02),
+    upstream gradient N(0,1).  Small enough for full ncu captures of the product-mode kernels."""
+
+    metric = "LUT attention layer fwd+bwd tokens/sec"
+    unit = "tokens/s"
+    dtype = "f32"
+    dominant_kernel = None
+
+    def __init__(self, batch=8, context=128, d_model=256, n_detectors=64, nc=8, npe=4):
+        self.B, self.S, self.E, self.Nt, self.Nc, self.Npe = batch, context, d_model, n_detectors, nc, npe
+        self.units_per_step = batch * context
+        self.name = (f"product-mode attention LUT layer fwd+bwd (context {context}, batch {batch}, E=O={d_model}, "
+                     f"Nt={n_detectors}, Nc={nc}, Npe={npe})")
+
+    def setup(self, device, rank):
+        import torch
+        from spiky_b200.lut_layer import LUTLayer, SynapseMeta
+        self.layer = LUTLayer(self.E, self.Nc, self.Nt, self.E, sequence_length=self.S,
+                              synapse_meta=SynapseMeta(min_weight=-1.0, max_weight=1.0), concatenation_product=False,
+                              positional_dim=self.Npe, random_seed=3, device=device)
+        with torch.no_grad():
+            self.layer._weights.copy_(torch.empty(self.layer._weights.shape).normal_(0.0, 0.02,
+                                                                                     generator=torch.Generator().manual_seed(1)))
+        self.layer.train()
+        g = torch.Generator().manual_seed(1000 + rank)
+        self.hx = torch.rand(self.B, self.S, self.E, generator=g).pin_memory()
+        self.hdy = torch.randn(self.B, self.S, self.E, generator=g).pin_memory()
+        self.dx, self.ddy = self.hx.to(device), self.hdy.to(device)
+        self.device = device
+        self.h2d_bytes = (self.hx.numel() + self.hdy.numel()) * 4
+        self.d2h_bytes = 4
+        self.l2_note = "flushed"
+
+    allreduce = None
+
+    def trainable_parameters(self):
+        return [p for p in self.layer.parameters() if p.requires_grad]
+
+    def _run(self, x, dy):
+        for p in self.layer.parameters():
+            p.grad = None
+        x = x.detach().requires_grad_(True)
+        y = self.layer(x)
+        y.backward(dy)
+        if self.allreduce is not None:
+            self.allreduce(self.trainable_parameters())
+        return y
+
+    def step_device(self):
+        return self._run(self.dx, self.ddy)
+
+    def step_e2e(self):
+        return self._run(self.hx.to(self.device, non_blocking=True), self.hdy.to(self.device, non_blocking=True)).sum()
+
+    def algorithmic_bytes(self):
+        E, Na = self.E, self.Nt
+        pairs = (self.S - 1) / 2.0
+        return {
+            "product_forward": pairs * Na * 4 * E + 8 * E,
+            "product_backward": pairs * Na * 16 * E + 12 * E,
+            "product_hist": 4 * E,
+            "product_row_dots": pairs * Na * 8 * E,
+            "product_route": 12 * E,
+            "product_hist_weight_grad": pairs * Na * 8 * E,
+            "product_hist_forward": pairs * Na * 4 * E + 4 * E,
+        }
+
+    def cpu_step(self, batch, threads):
+        import numpy as np
+        from oracle import lut_oracle as orc
+        orc.set_threads(threads)
+        rng = np.random.default_rng(5)
+        S, E, Na, Nc, Npe = self.S, self.E, self.Nt, self.Nc, self.Npe
+        x = rng.random((batch, S, E), dtype=np.float32)
+        dy = rng.standard_normal((batch, S, E)).astype(np.float32)
+        a1 = rng.integers(0, 2 * E + Npe, (Na, Nc))
+        anchors = np.stack([a1, (a1 + 1 + rng.integers(0, 2 * E + Npe - 1, (Na, Nc))) % (2 * E + Npe)], -1).astype(np.int32)
+        W = (0.02 * rng.standard_normal((Na, 1 << Nc, E))).astype(np.float32)
+        pe = rng.uniform(-1, 1, (S - 1, Na, Npe)).astype(np.float32)
+        t0 = time.perf_counter()
+        orc.product_forward(W, x, pe, anchors, Na, Nc, E, Npe)
+        orc.product_backward(W, x, pe, anchors, dy, Na, Nc, Npe)
+        return time.perf_counter() - t0
+
+
 class LargeTransformerWorkload(CharTransformerWorkload):
     """Large LUTTransformer training step: vocab 32768 (Zipf s=1.05), context 1024, 32 sequences per GPU, d_model 1024,
     12 layers, 16 heads, 10 anchor pairs (1024-row tables), product attention with 16 detectors per head and 4
@@ -618,7 +705,7 @@ class LutInferWorkload:
     scaling = "strong"
     dominant_kernel = None
     # DRAM bytes per step on one GPU at batch 16384 (profiles/lut_infer_b16384.md; fp32: 6 launches of 146 MB)
-    ncu_dram_bytes_b16384 = {"int8_gather": 923.1e6, "fc_gather_forward": 6 * 146.0e6, "check_detectors": 478.7e6}
+    ncu_dram_bytes_b16384 = {"int8_gather": 238.1e6 + 135.8e6, "fc_gather_forward": 6 * 146.0e6, "check_detectors": 478.2e6}
 
     @property
     def ncu_dram_bytes_per_step(self):
@@ -725,6 +812,7 @@ WORKLOADS = {
     "lut_infer_int8": lambda: LutInferWorkload("int8"),
     "lut_infer_fp32": lambda: LutInferWorkload("fp32"),
     "char_transformer": lambda: CharTransformerWorkload(),
+    "attention_layer": lambda: AttentionLayerWorkload(),
     "large_transformer": lambda: LargeTransformerWorkload(),
     "large_transformer_b4": lambda: LargeTransformerWorkload(batch=4),
     "sparse_convnet": lambda: SparseConvNetWorkload(),

@@ -12,7 +12,7 @@ namespace lutb {
 // rows its j keys select in a per-warp shared-memory histogram and writes it out as T uint16 counters.
 // H layout: [detector][row of the chunk = local sequence * S + j][T].
 // --------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(256) product_hist_kernel(const float *__restrict__ x1, const float *__restrict__ x2,
+__global__ void __launch_bounds__(512) product_hist_kernel(const float *__restrict__ x1, const float *__restrict__ x2,
                                                           const float *__restrict__ pe,
                                                           const int32_t *__restrict__ anchors, uint16_t *__restrict__ H,
                                                           int64_t b0, int64_t chunk_rows, int S, int e1, int e2, int npe,
@@ -62,7 +62,7 @@ __global__ void __launch_bounds__(256) product_hist_kernel(const float *__restri
 // per warp.
 // --------------------------------------------------------------------------------------------
 template <bool SMEM_ACC>
-__global__ void __launch_bounds__(256) product_route_kernel(const float *__restrict__ x1, const float *__restrict__ x2,
+__global__ void __launch_bounds__(512) product_route_kernel(const float *__restrict__ x1, const float *__restrict__ x2,
                                                            const float *__restrict__ pe,
                                                            const int32_t *__restrict__ anchors,
                                                            const float *__restrict__ Q, float *__restrict__ dX1,
@@ -177,7 +177,8 @@ __device__ __forceinline__ void fetch_tile(Frag &f, const void *base, int64_t ld
         }
     } else if (KIND == KC_U16) {
         const uint16_t *p = static_cast<const uint16_t *>(base);
-        const int m = m0 + (tid >> 1), k = k0 + (tid & 1) * 8;
+        // a warp takes 32 consecutive rows of one k-half: its transposed stores then fall into 32 different banks
+        const int m = m0 + (tid & 127), k = k0 + (tid >> 7) * 8;
         if (m < M && k < K) f.r[0] = __ldg(reinterpret_cast<const uint4 *>(p + (int64_t)m * ld + k));
     } else if (KIND == RK_F32) {
         const float *p = static_cast<const float *>(base);
@@ -211,7 +212,7 @@ __device__ __forceinline__ void stash_tile(const Frag &f, float (*tile)[GLD]) {
             tile[k + 3][m] = __uint_as_float(f.r[h].w);
         }
     } else if (KIND == KC_U16) {
-        const int m = tid >> 1, k = (tid & 1) * 8;
+        const int m = tid & 127, k = (tid >> 7) * 8;
         tile[k + 0][m] = lo16(f.r[0].x); tile[k + 1][m] = hi16(f.r[0].x);
         tile[k + 2][m] = lo16(f.r[0].y); tile[k + 3][m] = hi16(f.r[0].y);
         tile[k + 4][m] = lo16(f.r[0].z); tile[k + 5][m] = hi16(f.r[0].z);
@@ -338,8 +339,14 @@ static int launch_contract(KernelId id, GemmArgs g, int batches, cudaStream_t st
 
 static size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
 
-static size_t stage_bytes(const ProductCall &c, size_t per_warp_floats) {
-    return (pair_stage_floats(c.S, c.cfg->n_anchors, c.cfg->pos_dim) + 8 * per_warp_floats) * 4;
+static size_t stage_bytes(const ProductCall &c, size_t per_warp_floats, int warps = 8) {
+    return (pair_stage_floats(c.S, c.cfg->n_anchors, c.cfg->pos_dim) + (size_t)warps * per_warp_floats) * 4;
+}
+
+// Long sequences leave room for only one block per SM (the staged tokens alone are 130 KB at 1024 tokens): give that
+// block 16 warps when its per-warp scratch still fits.
+static int pair_block_warps(const ProductCall &c, size_t per_warp_floats) {
+    return (c.S >= 512 && stage_bytes(c, per_warp_floats, 16) <= (size_t)kMaxSmemPerBlock - 1024) ? 16 : 8;
 }
 
 bool product_hist_supported(const ProductCall &c, const void *weights, const void *io_rows, const void *dW) {
@@ -386,11 +393,12 @@ static int plan(const ProductCall &c, bool backward, void *workspace, size_t byt
 static int launch_hist(const ProductCall &c, const HistPlan &p, int64_t b0, int64_t n, cudaStream_t stream) {
     const lutb_layer_cfg *cfg = c.cfg;
     const size_t T = (size_t)1 << cfg->n_anchors;
-    const size_t smem = stage_bytes(c, T);
+    const int warps = pair_block_warps(c, T);
+    const size_t smem = stage_bytes(c, T, warps);
     if (smem > 48 * 1024) LUTB_CUDA(cudaFuncSetAttribute(product_hist_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     dim3 grid((unsigned)cfg->n_detectors, (unsigned)n);
     KernelScope scope(K_PRODUCT_HIST, stream);
-    product_hist_kernel<<<grid, 256, smem, stream>>>(c.x1, c.x2, c.pe, c.anchors, p.H, b0, n * c.S, c.S, c.e1, c.e2,
+    product_hist_kernel<<<grid, warps * 32, smem, stream>>>(c.x1, c.x2, c.pe, c.anchors, p.H, b0, n * c.S, c.S, c.e1, c.e2,
                                                      cfg->pos_dim, cfg->n_detectors, cfg->n_anchors, cfg->sliced_product,
                                                      cfg->cmp_eps);
     LUTB_LAUNCH_CHECK();
@@ -429,7 +437,8 @@ int launch_product_hist_backward(const ProductCall &c, const float *weights, con
     if (rc) return rc;
     const lutb_layer_cfg *cfg = c.cfg;
     const int T = 1 << cfg->n_anchors, O = cfg->n_outputs, Nt = cfg->n_detectors;
-    size_t route_smem = stage_bytes(c, (size_t)T + 64 * cfg->n_anchors);
+    const int route_warps = pair_block_warps(c, (size_t)T + 64 * cfg->n_anchors);
+    size_t route_smem = stage_bytes(c, (size_t)T + 64 * cfg->n_anchors, route_warps);
     const size_t acc_bytes = ((size_t)c.S * 2 * cfg->n_anchors + (size_t)(c.S - 1) * cfg->pos_dim) * 4;
     // block-level accumulators only while two blocks still fit an SM
     const bool smem_acc = route_smem + acc_bytes <= 100 * 1024;
@@ -476,11 +485,11 @@ int launch_product_hist_backward(const ProductCall &c, const float *weights, con
             dim3 grid((unsigned)Nt, (unsigned)n);
             KernelScope scope(K_PRODUCT_ROUTE, stream);
             if (smem_acc)
-                product_route_kernel<true><<<grid, 256, route_smem, stream>>>(c.x1, c.x2, c.pe, c.anchors, p.Q, dX1, dX2, dPE, b0,
+                product_route_kernel<true><<<grid, route_warps * 32, route_smem, stream>>>(c.x1, c.x2, c.pe, c.anchors, p.Q, dX1, dX2, dPE, b0,
                                                                               rows, c.S, c.e1, c.e2, cfg->pos_dim, Nt,
                                                                               cfg->n_anchors, cfg->sliced_product, cfg->cmp_eps);
             else
-                product_route_kernel<false><<<grid, 256, route_smem, stream>>>(c.x1, c.x2, c.pe, c.anchors, p.Q, dX1, dX2, dPE, b0,
+                product_route_kernel<false><<<grid, route_warps * 32, route_smem, stream>>>(c.x1, c.x2, c.pe, c.anchors, p.Q, dX1, dX2, dPE, b0,
                                                                                rows, c.S, c.e1, c.e2, cfg->pos_dim, Nt,
                                                                                cfg->n_anchors, cfg->sliced_product, cfg->cmp_eps);
             LUTB_LAUNCH_CHECK();

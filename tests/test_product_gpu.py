@@ -61,7 +61,7 @@ def compare(cfg, got, ref):
         if cfg.get("int_mode"):
             assert np.array_equal(got[k], ref[k]), f"{k}: fixed-point results must be bit-exact"
         else:
-            golden_util.assert_close(got[k], ref[k], REL, k)
+            golden_util.assert_close(got[k], ref[k], cfg.get("rel", REL), k)
 
 
 def inputs_for(cfg):
@@ -95,6 +95,10 @@ def hist_capable(cfg):
     return not cfg.get("int_mode") and 4 <= cfg["Nc"] <= 12 and cfg["O"] % 4 == 0 and cfg["S"] >= 2
 
 
+# more than 512 tokens: the histogram and routing kernels switch to 16-warp blocks.  A table cell here sums up to ~1e5
+# fp32 terms in the oracle and on the GPU alike, in different orders: the order-dependent rounding of such a sum is a
+# few 1e-5 of its size, so this case is checked at 1e-4
+ORACLE_CASES["long_sequence"] = dict(seed=707, B=1, S=520, E=8, Nt=3, Nc=6, Npe=2, O=8, n_virtual=18, rel=1e-4)
 ORACLE_CASES["internal_sgd"] = dict(seed=706, B=3, S=24, E=16, Nt=5, Nc=5, Npe=3, O=12, policy="internal", ext_lr=0.25,
                                     lr_meta=0.5, n_virtual=35)
 VARIANT_CASES = [(n, v) for n in sorted(ORACLE_CASES) for v in (1, 2) if v == 1 or hist_capable(ORACLE_CASES[n])]
