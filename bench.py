@@ -808,17 +808,22 @@ class LutInferWorkload:
         return time.perf_counter() - t0
 
 
+def _b(batch):
+    """Keyword for the --batch override (None keeps the workload's configured batch)."""
+    return {} if batch is None else {"batch": int(batch)}
+
+
 WORKLOADS = {
-    "lut_infer_int8": lambda: LutInferWorkload("int8"),
-    "lut_infer_fp32": lambda: LutInferWorkload("fp32"),
-    "char_transformer": lambda: CharTransformerWorkload(),
-    "attention_layer": lambda: AttentionLayerWorkload(),
-    "large_transformer": lambda: LargeTransformerWorkload(),
-    "large_transformer_b4": lambda: LargeTransformerWorkload(batch=4),
-    "sparse_convnet": lambda: SparseConvNetWorkload(),
-    "lut_layer": lambda: LutLayerWorkload(),
-    "lut_layer_b256": lambda: LutLayerWorkload(batch=256),
-    "lut_layer_b256_graph": lambda: LutLayerWorkload(batch=256, graph=True),
+    "lut_infer_int8": lambda batch=None: LutInferWorkload("int8", **_b(batch)),
+    "lut_infer_fp32": lambda batch=None: LutInferWorkload("fp32", **_b(batch)),
+    "char_transformer": lambda batch=None: CharTransformerWorkload(**_b(batch)),
+    "attention_layer": lambda batch=None: AttentionLayerWorkload(**_b(batch)),
+    "large_transformer": lambda batch=None: LargeTransformerWorkload(**_b(batch)),
+    "large_transformer_b4": lambda batch=None: LargeTransformerWorkload(batch=batch or 4),
+    "sparse_convnet": lambda batch=None: SparseConvNetWorkload(**_b(batch)),
+    "lut_layer": lambda batch=None: LutLayerWorkload(**_b(batch)),
+    "lut_layer_b256": lambda batch=None: LutLayerWorkload(batch=batch or 256),
+    "lut_layer_b256_graph": lambda batch=None: LutLayerWorkload(batch=batch or 256, graph=True),
 }
 DEFAULT_WORKLOAD = "sparse_convnet"
 
@@ -847,7 +852,7 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    wl = WORKLOADS[args.workload]()
+    wl = WORKLOADS[args.workload](args.batch)
     threads = os.cpu_count() or 1
     per_item = getattr(wl, "S", 1) if wl.unit == "tokens/s" else 1   # units per batch item
     full = wl.units_per_step // per_item
@@ -889,7 +894,7 @@ def run_ours(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
 
-    wl = WORKLOADS[args.workload]()
+    wl = WORKLOADS[args.workload](args.batch)
     wl.setup(device, rank)
     if world > 1:
         # gradients are exchanged per parameter as soon as its backward has run, overlapping the rest of
@@ -1013,7 +1018,7 @@ def run_ours(args):
             "gpu_launches": int(launches),
             "clocks": clocks,
         }
-        if world == 1:
+        if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(wl)
         print(json.dumps(line))
     if world > 1:
@@ -1027,6 +1032,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
+    ap.add_argument("--batch", type=int, default=None,
+                    help="override the workload's per-GPU batch (batch sweeps; the default is the configuration's batch)")
+    ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU oracle timing (batch sweeps)")
     ap.add_argument("--profile-only", action="store_true",
                     help="run only warm-up + steps of the device-resident step and exit (for ncu captures)")
     args = ap.parse_args()
