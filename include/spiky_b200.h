@@ -31,9 +31,10 @@ extern "C" {
 #define LUTB_ERR_ALIGN (-5)     /* a pointer is not aligned as documented */
 
 /* weight-gradient kernel selection for the backward entry points */
-#define LUTB_DW_AUTO 0      /* pick by the expected number of hits per table row */
-#define LUTB_DW_ATOMIC 1    /* row-coalesced global reductions (red.global.add) */
-#define LUTB_DW_SMEM 2      /* shared-memory privatised table slices, flushed once per block */
+#define LUTB_DW_AUTO 0      /* the library's choice: currently ATOMIC */
+#define LUTB_DW_ATOMIC 1    /* row-coalesced global reductions (red.global.add.v4.f32 into L2) */
+#define LUTB_DW_SMEM 2      /* reserved for shared-memory privatised table slices; runs the ATOMIC kernel: on B200 shared
+                               fp32 atomics sustained 0.8 T adds/s against 1.5 T adds/s for L2 reductions */
 #define LUTB_DW_SORTED 3    /* counting sort of the batch by row + segmented reduce; deterministic order; needs workspace */
 
 /*
