@@ -115,6 +115,11 @@ PRODUCT_CASES = {
                           lr_meta=0.5),
     "prod_wide_f32": dict(seed=306, B=2, S=9, E=12, Nt=5, Nc=4, Npe=4, O=40, unified_pe=True),
     "prod_wide_i32": dict(seed=307, B=2, S=9, E=12, Nt=5, Nc=4, Npe=4, O=40, int_mode=True, int_rescaler=0.5),
+    # sequences longer than the table (2^4 rows): the CUDA path takes the histogram / contraction kernels in both passes
+    "prod_long_f32": dict(seed=308, B=2, S=24, E=6, Nt=3, Nc=4, Npe=2, O=8),
+    "prod_long_internal": dict(seed=309, B=3, S=20, E=6, Nt=4, Nc=4, Npe=3, O=12, policy="internal", ext_lr=0.25,
+                               lr_meta=0.5, quantized_input=True, cmp_eps=1e-4),
+    "prod_two_tokens": dict(seed=310, B=3, S=2, E=5, Nt=2, Nc=3, Npe=1, O=4),
 }
 for _c in PRODUCT_CASES.values():
     _c["n_virtual"] = 3 * _c["E"] if _c.get("sliced") else 2 * _c["E"] + _c["Npe"]
