@@ -143,15 +143,21 @@ __global__ void __launch_bounds__(256, 4) sparse_forward_kernel(SparseView sp, c
         for (int64_t b = b0; b < b1; b++) {
             const int32_t li = lane < cs.ndet ? __ldg(idx + b * n_detectors + cs.det0 + lane) : 0;
             const int32_t row_off = lane * cs.table + li * cs.stride;
-            for (int p = lane; p < cs.P; p += 32) {
+            // uniform trip count: every lane takes part in the offset broadcasts, lanes beyond the row only skip the loads
+            for (int p0 = 0; p0 < cs.P; p0 += 32) {
+                const int p = p0 + lane;
+                const bool in_row = p < cs.P;
                 const int q = p + hole_offset(p, sp);
                 float acc = 0.f;
                 int32_t iacc = 0;
                 for (int d = 0; d < cs.ndet; d++) {
-                    const float w = __ldg(Wb + (int64_t)__shfl_sync(0xffffffffu, row_off, d) + q);
+                    const int32_t ro = __shfl_sync(0xffffffffu, row_off, d);
+                    if (!in_row) continue;
+                    const float w = __ldg(Wb + (int64_t)ro + q);
                     if (INT_MODE) iacc += to_fixed((double)w, fixed_scale);
                     else acc += w;
                 }
+                if (!in_row) continue;
                 const int target = __ldg(sp.syn_target + cs.toff + p);
                 if (INT_MODE) atomicAdd(reinterpret_cast<int32_t *>(y) + b * n_outputs + target, iacc);
                 else atomicAdd(y + b * n_outputs + target, acc);

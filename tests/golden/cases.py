@@ -82,6 +82,14 @@ PROJECTION_CASES = {
                                 receptive=(7, 7), projection=(4, 4), G=8),
     "proj_multigroup_i32": dict(seed=205, B=4, in_shape=(14, 14), out_shape=(14, 14), Nc=3, groups=5, per_group=2,
                                 receptive=(7, 7), projection=(4, 4), G=8, int_mode=True, int_rescaler=0.25),
+    # rows longer than a warp (7x7 projections: up to 49 targets, two synapse groups of 32 per row)
+    "proj_longrows_f32": dict(seed=207, B=5, in_shape=(14, 14), out_shape=(14, 14), Nc=3, groups=4, per_group=3,
+                              receptive=(5, 5), projection=(7, 7)),
+    "proj_longrows_i32": dict(seed=208, B=5, in_shape=(14, 14), out_shape=(14, 14), Nc=3, groups=4, per_group=3,
+                              receptive=(5, 5), projection=(7, 7), int_mode=True, int_rescaler=0.5),
+    # a slice of the first layer of the sparse conv-net configuration: 256-row tables, more samples than one sample run
+    "proj_c2_slice_f32": dict(seed=209, B=21, in_shape=(28, 28), out_shape=(24, 24), Nc=8, groups=6, per_group=8,
+                              receptive=(5, 5), projection=(4, 4), sparse_input=True),
     "proj_internal": dict(seed=206, B=7, in_shape=(12, 12), out_shape=(8, 8), Nc=3, groups=6, per_group=3,
                           receptive=(5, 5), projection=(3, 3), policy="internal", ext_lr=0.5, lr_meta=0.25),
 }
