@@ -192,11 +192,15 @@ __global__ void __launch_bounds__(256) concat_backward_kernel(const float *__res
                                     part += g.x * (a.x - c.x) + g.y * (a.y - c.y) + g.z * (a.z - c.z) + g.w * (a.w - c.w);
                                 }
                                 if (DO_DW && pass == 0) {
-                                    float4 u;
-                                    u.x = fabs((double)g.x) > kEps ? (float)((double)g.x * lr) : 0.f;
-                                    u.y = fabs((double)g.y) > kEps ? (float)((double)g.y * lr) : 0.f;
-                                    u.z = fabs((double)g.z) > kEps ? (float)((double)g.z * lr) : 0.f;
-                                    u.w = fabs((double)g.w) > kEps ? (float)((double)g.w * lr) : 0.f;
+                                    float4 u = g;   // lr == 1: the product is dY itself
+                                    if (lr != 1.0) {
+                                        u.x = (float)((double)g.x * lr); u.y = (float)((double)g.y * lr);
+                                        u.z = (float)((double)g.z * lr); u.w = (float)((double)g.w * lr);
+                                    }
+                                    u.x = fabsf(g.x) > kEpsF ? u.x : 0.f;
+                                    u.y = fabsf(g.y) > kEpsF ? u.y : 0.f;
+                                    u.z = fabsf(g.z) > kEpsF ? u.z : 0.f;
+                                    u.w = fabsf(g.w) > kEpsF ? u.w : 0.f;
                                     asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(Tt + r0 * n_outputs + col),
                                                  "f"(u.x), "f"(u.y), "f"(u.z), "f"(u.w) : "memory");
                                 }
