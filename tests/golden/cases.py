@@ -21,6 +21,8 @@ def nonseq_fc_inputs(cfg):
     anchors = synth.anchor_pairs(s + 12, Nt, Nc, I)
     if cfg.get("unused_pair"):
         anchors[0, Nc - 1, :] = -1  # a disabled pair (0xFFFFFFFF), spiky_cuda/lut/lut_runtime_kernels_logic.proto:1077
+    if cfg.get("unused_leading_pairs"):
+        anchors[1, :Nc - 1, :] = -1  # only the last pair of detector 1 is live: indices are 0 or 2^(Nc-1)
     W = synth.normal(s + 13, (Nt * T * O,), 0.0, cfg.get("w_std", 0.02))
     dY = synth.normal(s + 14, (B, O))
     if cfg.get("zero_dy"):
@@ -48,6 +50,12 @@ NONSEQ_FC_CASES = {
     # wider outputs than one forward group, more detectors than one backward group
     "fc_wide_f32": dict(seed=111, B=4, I=40, Nt=35, Nc=3, O=35, G=32, Gb=32),
     "fc_wide_i32": dict(seed=112, B=4, I=40, Nt=35, Nc=3, O=35, G=32, Gb=32, int_mode=True, int_rescaler=3.0),
+    # rows far longer than one warp pass, odd length; more detectors than one block of 32
+    "fc_long_rows_f32": dict(seed=113, B=3, I=24, Nt=37, Nc=2, O=515),
+    "fc_long_rows_i32": dict(seed=114, B=3, I=24, Nt=37, Nc=2, O=515, int_mode=True, int_rescaler=0.25),
+    # 1024-row tables; a detector with a single live pair
+    "fc_big_table_f32": dict(seed=115, B=10, I=50, Nt=3, Nc=10, O=8, unused_leading_pairs=True),
+    "fc_rows_vec4_f32": dict(seed=116, B=9, I=33, Nt=40, Nc=4, O=64, cmp_eps=0.01),
 }
 
 
@@ -90,6 +98,9 @@ PROJECTION_CASES = {
     # a slice of the first layer of the sparse conv-net configuration: 256-row tables, more samples than one sample run
     "proj_c2_slice_f32": dict(seed=209, B=21, in_shape=(28, 28), out_shape=(24, 24), Nc=8, groups=6, per_group=8,
                               receptive=(5, 5), projection=(4, 4), sparse_input=True),
+    # short rows (2x2 projections: 4 to 9 targets) take the 8-lane row groups
+    "proj_shortrows_f32": dict(seed=210, B=9, in_shape=(12, 12), out_shape=(12, 12), Nc=4, groups=8, per_group=5,
+                               receptive=(5, 5), projection=(2, 2)),
     "proj_internal": dict(seed=206, B=7, in_shape=(12, 12), out_shape=(8, 8), Nc=3, groups=6, per_group=3,
                           receptive=(5, 5), projection=(3, 3), policy="internal", ext_lr=0.5, lr_meta=0.25),
 }
@@ -143,4 +154,6 @@ CONCAT_CASES = {
     # more than one 32x32 pair tile, outputs wider than one forward group
     "concat_long_f32": dict(seed=405, B=1, S=40, E=10, Nt=2, Nc=2, Npe=1, O=35),
     "concat_long_i32": dict(seed=406, B=1, S=40, E=10, Nt=2, Nc=2, Npe=1, O=35, int_mode=True, int_rescaler=0.5),
+    # one key more than a 32-wide pair tile, dead band, vector-width rows
+    "concat_tile_edge_f32": dict(seed=407, B=2, S=34, E=12, Nt=3, Nc=2, Npe=2, O=16, cmp_eps=0.02, quantized_input=True),
 }
