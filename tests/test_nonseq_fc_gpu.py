@@ -101,6 +101,15 @@ ORACLE_CASES = {
     # outputs not a multiple of 4 (scalar path), many detectors
     "ragged": dict(seed=505, B=19, I=333, Nt=150, Nc=5, O=10),
     "ragged_i32": dict(seed=506, B=19, I=333, Nt=150, Nc=5, O=10, int_mode=True, G=3, Gb=7),
+    # every lane-group width of the vectorised forward gather: 1, 2, 4, 8 (c1), 16 (c5), 32 float4 per row, two chunks
+    "rows_of_4": dict(seed=510, B=37, I=64, Nt=45, Nc=5, O=4),
+    "rows_of_8": dict(seed=511, B=37, I=64, Nt=45, Nc=5, O=8),
+    "rows_of_16": dict(seed=512, B=37, I=64, Nt=45, Nc=5, O=16),
+    "rows_of_128": dict(seed=513, B=21, I=64, Nt=33, Nc=5, O=128),
+    "rows_of_260": dict(seed=514, B=21, I=64, Nt=33, Nc=5, O=260),
+    # one sample; more detectors than threads of a row group; inputs not a multiple of 4
+    "one_sample": dict(seed=515, B=1, I=50, Nt=300, Nc=7, O=12),
+    "odd_inputs": dict(seed=516, B=13, I=4099, Nt=64, Nc=8, O=32, normal_input=True),
     # a slice of the large inference layer (4096 inputs, 8 pairs, 64 outputs)
     "c5_slice": dict(seed=507, B=40, I=4096, Nt=512, Nc=8, O=64, normal_input=True),
     "nan_inputs": dict(seed=508, B=8, I=32, Nt=8, Nc=4, O=8, nan_input=True),

@@ -99,6 +99,11 @@ def hist_capable(cfg):
 # fp32 terms in the oracle and on the GPU alike, in different orders: the order-dependent rounding of such a sum is a
 # few 1e-5 of its size, so this case is checked at 1e-4
 ORACLE_CASES["long_sequence"] = dict(seed=707, B=1, S=520, E=8, Nt=3, Nc=6, Npe=2, O=8, n_virtual=18, rel=1e-4)
+ORACLE_CASES["hist_no_positional"] = dict(seed=720, B=2, S=70, E=9, Nt=4, Nc=5, Npe=0, O=8, n_virtual=18)
+ORACLE_CASES["hist_sliced"] = dict(seed=721, B=2, S=50, E=10, Nt=5, Nc=4, Npe=10, O=12, sliced=True, unified_pe=True,
+                                   cmp_eps=1e-4, quantized_input=True, n_virtual=30)
+ORACLE_CASES["hist_big_table"] = dict(seed=722, B=1, S=260, E=16, Nt=2, Nc=10, Npe=3, O=8, n_virtual=35)
+ORACLE_CASES["hist_odd_shapes"] = dict(seed=723, B=3, S=67, E=7, Nt=37, Nc=4, Npe=1, O=20, n_virtual=15)
 ORACLE_CASES["internal_sgd"] = dict(seed=706, B=3, S=24, E=16, Nt=5, Nc=5, Npe=3, O=12, policy="internal", ext_lr=0.25,
                                     lr_meta=0.5, n_virtual=35)
 VARIANT_CASES = [(n, v) for n in sorted(ORACLE_CASES) for v in (1, 2) if v == 1 or hist_capable(ORACLE_CASES[n])]
