@@ -111,3 +111,25 @@ def test_projection_autograd_and_sgd_step():
     before = layer._weights.detach().clone()
     opt.step()
     assert not torch.equal(before, layer._weights.detach())
+
+
+@pytest.mark.parametrize("per_group,projection,batch", [(40, (3, 3), 9), (1, (4, 4), 130), (33, (2, 2), 7), (5, (6, 6), 6)])
+def test_chunk_shapes_match_oracle(per_group, projection, batch):
+    """Detector groups that do not fill a 32-detector chunk, spill into a second chunk, or hold a single detector;
+    batches that are not a multiple of the per-warp sample run; rows of 4 to 36 synapses."""
+    from spiky_b200.lut_layer import ProjectionLUTLayer, SynapseMeta
+
+    layer = ProjectionLUTLayer(
+        (14, 14), (12, 12), 5, 6, per_group, (5, 5), projection,
+        synapse_meta=SynapseMeta(min_weight=-1.0, max_weight=1.0, initial_noise_level=0.1, initial_weight=0.02),
+        random_seed=7, device="cuda:0")
+    x = synth.sparse_images(15, (batch, 14 * 14))
+    dY = synth.normal(16, (batch, 12 * 12))
+    got = run_layer(layer, x, dY, None)
+    index = layer._lut_dm._sparse
+    sp = dict(index.numpy(), group_size=index.group_size)
+    W = layer._weights.detach().cpu().numpy()
+    anchors = layer._detector_anchors.cpu().numpy()
+    y, idx, md, mk = orc.nonseq_sparse_forward(W, x, anchors, sp, 5, 12 * 12)
+    dX, dW = orc.nonseq_sparse_backward(W, dY, anchors, idx, md, mk, sp, 14 * 14, 5)
+    compare(got, dict(y=y, y_eval=y, idx=idx, min_delta=md, min_k=mk, dX=dX, dW=dW), False)
