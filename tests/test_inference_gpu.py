@@ -44,6 +44,21 @@ def test_int8_inference_is_bit_exact_with_fixed_point_reference_on_dequantized_t
     assert np.array_equal(orc.int_to_float(acc, 0.05), ref)
 
 
+def test_int8_inference_detector_ranges_and_odd_blocks():
+    """Tables larger than one L2 range (two launches over detector ranges), detector blocks of 7 with a ragged last
+    block, 4-wide rows."""
+    from spiky_b200.inference import LUTInference
+
+    for (B, I, Nt, Nc, O, blk) in [(5, 64, 700, 8, 256, 32), (11, 30, 45, 3, 4, 7)]:
+        x, anchors, q, s = make_problem(930, B, I, Nt, Nc, O)
+        for rule, exact in (("exact", True), ("f32", False)):
+            layer = LUTInference(I, O, Nt, Nc, torch.from_numpy(anchors), torch.from_numpy(q), torch.from_numpy(s),
+                                 int_rescaler=0.05, backward_group_size=blk, dequant=rule)
+            acc = layer.partial(torch.from_numpy(x).cuda()).cpu().numpy()
+            want, _ = orc.infer_int8(q, s, x, anchors, Nt, Nc, O, backward_group_size=blk, int_rescaler=0.05, exact=exact)
+            assert np.array_equal(acc, want), (B, I, Nt, Nc, O, blk, rule)
+
+
 @pytest.mark.parametrize("shape", [(33, 256, 64, 8, 64), (16, 4096, 512, 8, 64), (9, 40, 96, 5, 12), (5, 64, 70, 6, 128)])
 def test_int8_inference_exact_product_rule_is_bit_exact(shape):
     """Entries taken as the exact reals scale * q (the default, fast rule): bit-exact against the oracle's
