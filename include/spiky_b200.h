@@ -250,6 +250,26 @@ int lutb_concat_backward(const lutb_layer_cfg *cfg, int64_t batch, float *weight
                          float *dPE, float *dW, double external_lr, void *stream);
 
 /*
+ * Concatenation-mode sequence layer with sparse lookup -> output connectivity (the reference builds it with
+ * Conv2DLUTLayer(sequence_length > 1, lut_receptive_field_shape = ...)).  Replace the sparse branches of
+ * LUTDataManager::forward_step_concat / backward_backprop_concat: fill_outputs_sparse_seq_logic
+ * (lut_runtime_kernels_logic.proto:1906-2013), propagate_through_detectors_seq_sparse_logic (:3371-3627) and
+ * gather_w_gradients_seq_sparse_logic (:3837-3942).  Arguments as lutb_concat_forward / lutb_concat_backward plus
+ * the connectivity; the index holds 2^(2*Nc + pos_dim) rows per detector and weights is fp32 [sparse->n_weights].
+ * (Product-mode layers with sparse connectivity are not provided: the reference implements them for its CUDA build
+ * only, so nothing pins their results here.)
+ */
+int lutb_concat_sparse_forward(const lutb_layer_cfg *cfg, const lutb_sparse_index *sparse, int64_t batch,
+                               const float *weights, const float *x, const int32_t *anchors, const float *pos_embeddings,
+                               float *y, int32_t *idx, float *min_delta, int32_t *min_k, int32_t *pos_idx,
+                               float *pos_min_delta, int32_t *pos_min_k, void *stream);
+int lutb_concat_sparse_backward(const lutb_layer_cfg *cfg, const lutb_sparse_index *sparse, int64_t batch, float *weights,
+                                const float *dY, const int32_t *anchors, const int32_t *idx, const float *min_delta,
+                                const int32_t *min_k, const int32_t *pos_idx, const float *pos_min_delta,
+                                const int32_t *pos_min_k, float *dX, float *dPE, float *dW, double external_lr,
+                                void *stream);
+
+/*
  * Forward-only inference with int8 tables (non-sequence, fully connected).  No counterpart in the reference,
  * which has no quantised tables: the result is DEFINED as the reference's int32 fixed-point forward
  * (LUTDataManagerI::forward_step, spiky_cuda/lut/lut.cu:629-716 with INTEGERS_INSTEAD_OF_FLOATS) run on the

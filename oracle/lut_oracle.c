@@ -667,3 +667,149 @@ void orc_concat_backward(float *W, const float *dY, const int32_t *anchors, cons
         if (Npe > 0) orc_int_to_float(dPE, (int64_t)(S - 1) * Nt * Npe, rescaler);
     }
 }
+
+/* ------------------------------------------------------------------------------------------
+ * Concatenation-mode sequence layers with sparse lookup -> output connectivity: the pair (i < j) selects
+ * lookup neuron t * T + row(i, j) as in the fully connected case, and that neuron's synapse groups are walked
+ * like in the non-sequence sparse layer (same arrays: det_wbase / det_stride / det_count / det_toff / targets).
+ * Host loop nest of the reference: (sample, synapse group) outermost, 32x32 pair tiles row-major, detectors,
+ * inside a tile key index outer / query index inner (i = thread / TILE, j = thread % TILE).
+ * ------------------------------------------------------------------------------------------ */
+
+/* fill_outputs_sparse_seq_logic (proto:1906-2013) + fire_single_synapse_group (:215-313) */
+void orc_concat_sparse_forward(const float *W, const int32_t *idx, const int32_t *pidx, float *y, int64_t B, int S, int O,
+                               int Nt, int Nc, int Npe, const int64_t *det_wbase, const int32_t *det_stride,
+                               const int32_t *det_count, const int32_t *det_toff, const int32_t *targets, int G,
+                               int int_mode, double rescaler) {
+    int max_groups = 0;
+    for (int t = 0; t < Nt; t++) {
+        int g = (det_count[t] + G - 1) / G;
+        if (g > max_groups) max_groups = g;
+    }
+    int tiles = (S + 31) / 32;
+    for (int64_t b = 0; b < B; b++)
+        for (int ob = 0; ob < max_groups; ob++)
+            for (int ti = 0; ti < tiles; ti++)
+                for (int tj = 0; tj < tiles; tj++) {
+                    if (ti > tj) continue;
+                    for (int t = 0; t < Nt; t++) {
+                        int P = det_count[t];
+                        int p0 = ob * G, p1 = p0 + G < P ? p0 + G : P;
+                        if (p0 >= P) continue;
+                        const int32_t *tg = targets + det_toff[t];
+                        for (int il = 0; il < 32; il++)
+                            for (int jl = 0; jl < 32; jl++) {
+                                int i = ti * 32 + il, j = tj * 32 + jl;
+                                if (i >= j || i >= S || j >= S) continue;
+                                int32_t K = idx[(b * S + i) * Nt + t], Q = idx[(b * S + j) * Nt + t];
+                                int32_t PE = Npe > 0 ? pidx[(int64_t)(j - i - 1) * Nt + t] : 0;
+                                int64_t row = det_wbase[t] + orc_concat_row(Q, K, PE, Nc, Npe) * det_stride[t];
+                                float *yb = y + (b * S + j) * O;
+                                for (int p = p0; p < p1; p++) {
+                                    double w = (double)W[orc_syn_slot(row, p, G)];
+                                    if (int_mode) *(int32_t *)(yb + tg[p]) += (int32_t)(w * ORC_DENOM * rescaler);
+                                    else yb[tg[p]] += (float)w;
+                                }
+                            }
+                    }
+                }
+    if (int_mode) orc_int_to_float(y, B * S * O, rescaler);
+}
+
+/* propagate_through_detectors_seq_sparse_logic (proto:3371-3627, helper accumulate_grad_sum_sparse :315-395) and
+ * gather_w_gradients_seq_sparse_logic (proto:3837-3942, helper gather_weight_gradients_sparse :584-714). */
+void orc_concat_sparse_backward(float *W, const float *dY, const int32_t *anchors, const int32_t *idx,
+                                const float *min_delta, const int32_t *min_k, const int32_t *pidx, const float *pmin,
+                                const int32_t *pmin_k, float *dX, float *dPE, float *dW, int64_t B, int S, int I, int O,
+                                int Nt, int Nc, int Npe, const int64_t *det_wbase, const int32_t *det_stride,
+                                const int32_t *det_count, const int32_t *det_toff, const int32_t *targets, int G,
+                                int64_t n_weights, double lr_meta, double ext_lr, int int_mode, double rescaler) {
+    int max_groups = 0;
+    for (int t = 0; t < Nt; t++) {
+        int g = (det_count[t] + G - 1) / G;
+        if (g > max_groups) max_groups = g;
+    }
+    int tiles = (S + 31) / 32;
+    double lr = lr_meta;
+    if (ext_lr >= 0) lr *= -ext_lr;
+    float *target = ext_lr >= 0 ? W : dW;
+    for (int pass = 0; pass < 2; pass++)  /* 0: input + positional gradients, 1: table gradients */
+        for (int64_t b = 0; b < B; b++)
+            for (int ob = 0; ob < max_groups; ob++)
+                for (int ti = 0; ti < tiles; ti++)
+                    for (int tj = 0; tj < tiles; tj++) {
+                        if (ti > tj) continue;
+                        for (int t = 0; t < Nt; t++) {
+                            int P = det_count[t];
+                            int p0 = ob * G, p1 = p0 + G < P ? p0 + G : P;
+                            if (p0 >= P) continue;
+                            const int32_t *tg = targets + det_toff[t];
+                            for (int il = 0; il < 32; il++)
+                                for (int jl = 0; jl < 32; jl++) {
+                                    int i = ti * 32 + il, j = tj * 32 + jl;
+                                    if (i >= j || i >= S || j >= S) continue;
+                                    const float *dy = dY + (b * S + j) * O;
+                                    int64_t ko = (b * S + i) * Nt + t, qo = (b * S + j) * Nt + t;
+                                    int32_t K = idx[ko], Q = idx[qo];
+                                    int32_t PE = 0, pk = -1;
+                                    float pm = 0.0f;
+                                    int64_t po = (int64_t)(j - i - 1) * Nt + t;
+                                    if (Npe > 0) { PE = pidx[po]; pk = pmin_k[po]; pm = pmin[po]; }
+                                    int64_t row = det_wbase[t] + orc_concat_row(Q, K, PE, Nc, Npe) * det_stride[t];
+                                    if (pass == 1) {
+                                        for (int p = p0; p < p1; p++) {
+                                            double g = (double)dy[tg[p]];
+                                            if (fabs(g) > ORC_EPS) {
+                                                int64_t slot = orc_syn_slot(row, p, G);
+                                                if (int_mode) *(int32_t *)(target + slot) += (int32_t)(g * lr * ORC_DENOM * rescaler);
+                                                else target[slot] += (float)(g * lr);
+                                            }
+                                        }
+                                        continue;
+                                    }
+                                    float qm = min_delta[qo], km = min_delta[ko];
+                                    int64_t alt;
+                                    double du;
+                                    int flip, pos;
+                                    if (fabsf(qm) < fabsf(km)) {
+                                        alt = det_wbase[t] + orc_concat_row(Q ^ (1 << min_k[qo]), K, PE, Nc, Npe) * det_stride[t];
+                                        du = orc_up(qm); flip = min_k[qo]; pos = j;
+                                    } else {
+                                        alt = det_wbase[t] + orc_concat_row(Q, K ^ (1 << min_k[ko]), PE, Nc, Npe) * det_stride[t];
+                                        du = orc_up(km); flip = min_k[ko]; pos = i;
+                                    }
+                                    double ms = 0.0, as = 0.0;
+                                    for (int p = p0; p < p1; p++) ms += (double)W[orc_syn_slot(row, p, G)] * (double)dy[tg[p]];
+                                    for (int p = p0; p < p1; p++) as += (double)W[orc_syn_slot(alt, p, G)] * (double)dy[tg[p]];
+                                    du *= ms - as;
+                                    if (fabs(du) > ORC_EPS) {
+                                        int32_t a1 = anchors[((int64_t)t * Nc + flip) * 2], a2 = anchors[((int64_t)t * Nc + flip) * 2 + 1];
+                                        float *dx = dX + (b * S + pos) * (int64_t)I;
+                                        if (int_mode) {
+                                            int32_t d = (int32_t)(du * ORC_DENOM * rescaler);
+                                            *(int32_t *)(dx + a1) += d;
+                                            *(int32_t *)(dx + a2) -= d;
+                                        } else {
+                                            dx[a1] += du;
+                                            dx[a2] -= du;
+                                        }
+                                    }
+                                    if (Npe > 0 && fabsf(pm) < fabsf(qm) && fabsf(pm) < fabsf(km)) {
+                                        int64_t palt = det_wbase[t] + orc_concat_row(Q, K, PE ^ (1 << pk), Nc, Npe) * det_stride[t];
+                                        double dp = orc_up(pm);
+                                        double ps = 0.0;
+                                        for (int p = p0; p < p1; p++) ps += (double)W[orc_syn_slot(palt, p, G)] * (double)dy[tg[p]];
+                                        dp *= ms - ps;
+                                        float *cell = dPE + po * Npe + pk;
+                                        if (int_mode) *(int32_t *)cell += (int32_t)(dp * ORC_DENOM * rescaler);
+                                        else *cell += dp;
+                                    }
+                                }
+                        }
+                    }
+    if (int_mode) {
+        orc_int_to_float(dX, B * S * (int64_t)I, rescaler);
+        if (dW) orc_int_to_float(dW, n_weights, rescaler);
+        if (Npe > 0) orc_int_to_float(dPE, (int64_t)(S - 1) * Nt * Npe, rescaler);
+    }
+}

@@ -280,3 +280,51 @@ def concat_backward(W, dY, anchors, state, n_inputs, n_anchors, pos_dim, lr_meta
                               _i(forward_group_size), _d(float(np.float32(lr_meta))),
                               _d(float(np.float32(external_lr))), _i(int(int_mode)), _d(int_rescaler))
     return dX, dW, dPE
+
+
+def _sp_args(sp):
+    return (_ptr(_i64(sp["det_wbase"])), _ptr(_i32(sp["det_stride"])), _ptr(_i32(sp["det_count"])),
+            _ptr(_i32(sp["det_sstart"])), _ptr(_i32(sp["syn_target"])), _i(int(sp["group_size"])))
+
+
+def concat_sparse_forward(W, x, pe, anchors, sp, n_anchors, n_outputs, pos_dim, cmp_eps=0.0, train=True,
+                          int_mode=False, int_rescaler=0.001):
+    """``forward_step_concat`` of a layer with sparse lookup -> output connectivity (``sp`` as in
+    nonseq_sparse_forward, with 2^(2*Nc+Npe) rows per detector).  Returns (y [B,S,O], state)."""
+    x = _f32(x)
+    B, S, I = x.shape
+    Nt = len(sp["det_count"])
+    res = check_detectors(x.reshape(B * S, I), anchors, Nt, n_anchors, cmp_eps, train)
+    idx, md, mk = res if train else (res, None, None)
+    pidx = pm = pk = None
+    if pos_dim > 0:
+        pres = check_positional(pe, S, Nt, pos_dim, cmp_eps, train)
+        pidx, pm, pk = pres if train else (pres, None, None)
+    y = np.zeros((B, S, n_outputs), np.float32)
+    W = _f32(W).reshape(-1)
+    lib().orc_concat_sparse_forward(_ptr(W), _ptr(idx), _ptr(pidx), _ptr(y), _l(B), _i(S), _i(n_outputs), _i(Nt),
+                                    _i(n_anchors), _i(pos_dim), *_sp_args(sp), _i(int(int_mode)), _d(int_rescaler))
+    return y, dict(idx=idx, min_delta=md, min_k=mk, pidx=pidx, pmin=pm, pmin_k=pk)
+
+
+def concat_sparse_backward(W, dY, anchors, state, sp, n_inputs, n_anchors, pos_dim, lr_meta=1.0, external_lr=-1.0,
+                           int_mode=False, int_rescaler=0.001):
+    """``backward_backprop_concat`` of a sparse sequence layer; returns (dX [B,S,I], dW or None, dPE or None)."""
+    dY = _f32(dY)
+    B, S, O = dY.shape
+    Nt = len(sp["det_count"])
+    if external_lr >= 0:
+        assert W.dtype == np.float32 and W.flags["C_CONTIGUOUS"] and W.flags["WRITEABLE"]
+        Wf, dW = W.reshape(-1), None
+    else:
+        Wf = _f32(W).reshape(-1)
+        dW = np.zeros(Wf.size, np.float32)
+    dX = np.zeros((B, S, n_inputs), np.float32)
+    dPE = np.zeros((S - 1) * Nt * pos_dim, np.float32) if pos_dim > 0 else None
+    lib().orc_concat_sparse_backward(_ptr(Wf), _ptr(dY), _ptr(_i32(anchors).reshape(-1)), _ptr(state["idx"]),
+                                     _ptr(state["min_delta"]), _ptr(state["min_k"]), _ptr(state["pidx"]),
+                                     _ptr(state["pmin"]), _ptr(state["pmin_k"]), _ptr(dX), _ptr(dPE), _ptr(dW), _l(B),
+                                     _i(S), _i(n_inputs), _i(O), _i(Nt), _i(n_anchors), _i(pos_dim), *_sp_args(sp),
+                                     _l(Wf.size), _d(float(np.float32(lr_meta))), _d(float(np.float32(external_lr))),
+                                     _i(int(int_mode)), _d(int_rescaler))
+    return dX, dW, dPE

@@ -79,6 +79,8 @@ SIGNATURES = {
     "lutb_nonseq_fc_backward": (_int, [_cfgp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _dbl, _int, _vp, _size, _vp]),
     "lutb_concat_forward": (_int, [_cfgp, _i64] + [_vp] * 12),
     "lutb_concat_backward": (_int, [_cfgp, _i64] + [_vp] * 12 + [_dbl, _vp]),
+    "lutb_concat_sparse_forward": (_int, [_cfgp, _spp, _i64] + [_vp] * 12),
+    "lutb_concat_sparse_backward": (_int, [_cfgp, _spp, _i64] + [_vp] * 12 + [_dbl, _vp]),
     "lutb_product_workspace": (_size, [_cfgp, _i64, ctypes.c_int32, _int]),
     "lutb_product_forward": (_int, [_cfgp, _i64, ctypes.c_int32, _vp, _vp, _vp, ctypes.c_int32, ctypes.c_int32, _vp, _vp, _vp,
                                     _int, _vp, _size, _vp]),

@@ -316,6 +316,144 @@ __global__ void concat_backward_fixed_kernel(const float *__restrict__ W, const 
     }
 }
 
+// --------------------------------------------------------------------------------------------
+// Concatenation-mode layers with sparse lookup -> output connectivity (reference: fill_outputs_sparse_seq_logic,
+// proto:1906-2013; propagate_through_detectors_seq_sparse_logic, :3371-3627; gather_w_gradients_seq_sparse_logic,
+// :3837-3942).  A causal pair selects lookup neuron (t, row(i, j)) as in the fully connected case; that neuron's
+// synapses (slot p + 2 * (p / G) behind the row base, targets shared by all rows of the detector) are walked as in
+// the non-sequence sparse layer.  One thread per (sample, query, detector, key): sums in double per synapse group
+// (every group issues its own contribution, as the reference does with one block per group), fp32 or int32
+// fixed-point atomics.  No layer of the benchmark configurations takes this path; it is written for exactness.
+// --------------------------------------------------------------------------------------------
+struct SparseRows {
+    const int64_t *wbase;
+    const int32_t *stride, *count, *sstart, *target;
+    int group;
+};
+
+__device__ __forceinline__ int64_t sparse_slot(int64_t row_base, int p, int G) { return row_base + p + 2 * (p / G); }
+
+template <bool INT_MODE>
+__global__ void concat_sparse_forward_kernel(const float *__restrict__ W, const int32_t *__restrict__ idx,
+                                             const int32_t *__restrict__ pidx, float *__restrict__ y, SparseRows sp,
+                                             int64_t batch, int S, int n_outputs, int n_detectors, int nc, int npe,
+                                             double fixed_scale) {
+    const int64_t total = batch * S * (int64_t)n_detectors * S;
+    for (int64_t w = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; w < total; w += (int64_t)gridDim.x * blockDim.x) {
+        const int i = (int)(w % S);
+        int64_t r = w / S;
+        const int t = (int)(r % n_detectors);
+        r /= n_detectors;
+        const int j = (int)(r % S);
+        const int64_t b = r / S;
+        if (i >= j) continue;
+        const int32_t K = idx[(b * S + i) * n_detectors + t], Q = idx[(b * S + j) * n_detectors + t];
+        const int32_t PE = npe > 0 ? pidx[(int64_t)(j - i - 1) * n_detectors + t] : 0;
+        const int64_t row = sp.wbase[t] + (int64_t)concat_row(Q, K, PE, nc, npe) * sp.stride[t];
+        const int32_t *tg = sp.target + sp.sstart[t];
+        float *yb = y + (b * S + j) * n_outputs;
+        const int P = sp.count[t];
+        for (int p = 0; p < P; p++) {
+            const float wv = __ldg(W + sparse_slot(row, p, sp.group));
+            if (INT_MODE) atomicAdd(reinterpret_cast<int32_t *>(yb) + tg[p], to_fixed((double)wv, fixed_scale));
+            else atomicAdd(yb + tg[p], wv);
+        }
+    }
+}
+
+template <bool INT_MODE>
+__global__ void concat_sparse_backward_kernel(const float *__restrict__ W, const float *__restrict__ dY,
+                                              const int2 *__restrict__ anchors, const int32_t *__restrict__ idx,
+                                              const float *__restrict__ min_delta, const int32_t *__restrict__ min_k,
+                                              const int32_t *__restrict__ pidx, const float *__restrict__ pmin,
+                                              const int32_t *__restrict__ pmin_k, float *__restrict__ dX,
+                                              float *__restrict__ dPE, float *__restrict__ target, SparseRows sp,
+                                              int64_t batch, int S, int n_inputs, int n_outputs, int n_detectors, int nc,
+                                              int npe, int do_dx, double lr, double fixed_scale) {
+    const int64_t total = batch * S * (int64_t)n_detectors * S;
+    for (int64_t w = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; w < total; w += (int64_t)gridDim.x * blockDim.x) {
+        const int i = (int)(w % S);
+        int64_t r = w / S;
+        const int t = (int)(r % n_detectors);
+        r /= n_detectors;
+        const int j = (int)(r % S);
+        const int64_t b = r / S;
+        if (i >= j) continue;
+        const int64_t ko = (b * S + i) * n_detectors + t, qo = (b * S + j) * n_detectors + t;
+        const int32_t K = idx[ko], Q = idx[qo];
+        const int64_t po = (int64_t)(j - i - 1) * n_detectors + t;
+        int32_t PE = 0, pk = -1;
+        float pm = 0.f;
+        if (npe > 0) { PE = pidx[po]; pk = pmin_k[po]; pm = pmin[po]; }
+        const int64_t base = sp.wbase[t];
+        const int64_t stride = sp.stride[t];
+        const int64_t row = base + (int64_t)concat_row(Q, K, PE, nc, npe) * stride;
+        const int32_t *tg = sp.target + sp.sstart[t];
+        const float *dy = dY + (b * S + j) * n_outputs;
+        const int P = sp.count[t], G = sp.group;
+        if (do_dx) {
+            const float qm = min_delta[qo], km = min_delta[ko];
+            int64_t alt;
+            double up;
+            int flip, pos;
+            if (fabsf(qm) < fabsf(km)) {
+                alt = base + (int64_t)concat_row(Q ^ (1 << min_k[qo]), K, PE, nc, npe) * stride;
+                up = surrogate_up(qm); flip = min_k[qo]; pos = j;
+            } else {
+                alt = base + (int64_t)concat_row(Q, K ^ (1 << min_k[ko]), PE, nc, npe) * stride;
+                up = surrogate_up(km); flip = min_k[ko]; pos = i;
+            }
+            const bool pe_flip = npe > 0 && fabsf(pm) < fabsf(qm) && fabsf(pm) < fabsf(km);
+            const int64_t palt = pe_flip ? base + (int64_t)concat_row(Q, K, PE ^ (1 << pk), nc, npe) * stride : 0;
+            const int2 a = __ldg(anchors + (size_t)t * nc + flip);
+            float *dx = dX + (b * S + pos) * (int64_t)n_inputs;
+            for (int p0 = 0; p0 < P; p0 += G) {
+                const int p1 = min(P, p0 + G);
+                double ms = 0.0, as = 0.0, ps = 0.0;
+                for (int p = p0; p < p1; p++) ms += (double)__ldg(W + sparse_slot(row, p, G)) * (double)__ldg(dy + tg[p]);
+                for (int p = p0; p < p1; p++) as += (double)__ldg(W + sparse_slot(alt, p, G)) * (double)__ldg(dy + tg[p]);
+                const double du = up * (ms - as);
+                if (fabs(du) > kEps) {
+                    if (INT_MODE) {
+                        const int32_t d = to_fixed(du, fixed_scale);
+                        atomicAdd(reinterpret_cast<int32_t *>(dx) + a.x, d);
+                        atomicAdd(reinterpret_cast<int32_t *>(dx) + a.y, -d);
+                    } else {
+                        atomicAdd(dx + a.x, (float)du);
+                        atomicAdd(dx + a.y, -(float)du);
+                    }
+                }
+                if (pe_flip) {
+                    for (int p = p0; p < p1; p++) ps += (double)__ldg(W + sparse_slot(palt, p, G)) * (double)__ldg(dy + tg[p]);
+                    const double dp = surrogate_up(pm) * (ms - ps);
+                    if (INT_MODE) atomicAdd(reinterpret_cast<int32_t *>(dPE) + po * npe + pk, to_fixed(dp, fixed_scale));
+                    else atomicAdd(dPE + po * npe + pk, (float)dp);
+                }
+            }
+        }
+        if (target) {
+            for (int p = 0; p < P; p++) {
+                const double g = (double)__ldg(dy + tg[p]);
+                if (fabs(g) > kEps) {
+                    const int64_t slot = sparse_slot(row, p, G);
+                    if (INT_MODE) atomicAdd(reinterpret_cast<int32_t *>(target) + slot, to_fixed(g * lr, fixed_scale));
+                    else atomicAdd(target + slot, (float)(g * lr));
+                }
+            }
+        }
+    }
+}
+
+static int validate_sparse_rows(const lutb_sparse_index *sp, SparseRows *out) {
+    LUTB_REQUIRE(sp != nullptr, LUTB_ERR_NULL, "sparse index is NULL");
+    LUTB_REQUIRE(sp->det_wbase && sp->det_stride && sp->det_count && sp->det_sstart && sp->syn_target, LUTB_ERR_NULL,
+                 "a sparse index array is NULL");
+    LUTB_REQUIRE(sp->group_size > 0 && sp->n_weights > 0, LUTB_ERR_SHAPE, "empty sparse index");
+    out->wbase = sp->det_wbase; out->stride = sp->det_stride; out->count = sp->det_count;
+    out->sstart = sp->det_sstart; out->target = sp->syn_target; out->group = sp->group_size;
+    return LUTB_OK;
+}
+
 static int validate_concat(const lutb_layer_cfg *cfg, int64_t batch) {
     int rc = validate_cfg(cfg);
     if (rc) return rc;
@@ -428,6 +566,106 @@ extern "C" int lutb_concat_backward(const lutb_layer_cfg *cfg, int64_t batch, fl
         if (rc) return rc;
         if (dW) {
             rc = launch_fixed_to_float(dW, (int64_t)Nt * ((int64_t)1 << (2 * Nc + npe)) * O, cfg->int_rescaler, st);
+            if (rc) return rc;
+        }
+        if (npe > 0) rc = launch_fixed_to_float(dPE, (int64_t)(S - 1) * Nt * npe, cfg->int_rescaler, st);
+    }
+    return rc;
+}
+
+extern "C" int lutb_concat_sparse_forward(const lutb_layer_cfg *cfg, const lutb_sparse_index *sparse, int64_t batch,
+                                          const float *weights, const float *x, const int32_t *anchors,
+                                          const float *pos_embeddings, float *y, int32_t *idx, float *min_delta,
+                                          int32_t *min_k, int32_t *pos_idx, float *pos_min_delta, int32_t *pos_min_k,
+                                          void *stream) {
+    int rc = validate_concat(cfg, batch);
+    if (rc) return rc;
+    SparseRows rows;
+    rc = validate_sparse_rows(sparse, &rows);
+    if (rc) return rc;
+    LUTB_REQUIRE(weights && x && anchors && y && idx, LUTB_ERR_NULL, "a required tensor pointer is NULL");
+    LUTB_REQUIRE((min_delta == nullptr) == (min_k == nullptr), LUTB_ERR_MODE,
+                 "min_anchor_deltas and min_anchor_delta_indices must be given together");
+    const int S = cfg->seq_len, npe = cfg->pos_dim, Nt = cfg->n_detectors;
+    const bool train = min_delta != nullptr;
+    if (npe > 0) {
+        LUTB_REQUIRE(pos_embeddings && pos_idx, LUTB_ERR_NULL, "positional embeddings / indices are NULL");
+        LUTB_REQUIRE(!train || (pos_min_delta && pos_min_k), LUTB_ERR_NULL, "positional min-delta outputs are NULL");
+    }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    rc = launch_check_detectors(x, batch * S, cfg->n_inputs, anchors, Nt, cfg->n_anchors, cfg->cmp_eps, idx, min_delta,
+                                min_k, st);
+    if (rc) return rc;
+    if (npe > 0) {
+        const int64_t n = (int64_t)(S - 1) * Nt;
+        KernelScope scope(K_CHECK_POSITIONAL, st);
+        if (train) check_positional_kernel<true><<<(unsigned)((n + 127) / 128), 128, 0, st>>>(pos_embeddings, n, npe, cfg->cmp_eps, pos_idx, pos_min_delta, pos_min_k);
+        else check_positional_kernel<false><<<(unsigned)((n + 127) / 128), 128, 0, st>>>(pos_embeddings, n, npe, cfg->cmp_eps, pos_idx, nullptr, nullptr);
+        LUTB_LAUNCH_CHECK();
+    }
+    {
+        const int64_t total = batch * S * (int64_t)Nt * S;
+        const int64_t blocks = min((total + 127) / 128, (int64_t)device_info().sm_count * 64);
+        KernelScope scope(K_CONCAT_FORWARD, st);
+        if (cfg->int_mode)
+            concat_sparse_forward_kernel<true><<<(unsigned)blocks, 128, 0, st>>>(weights, idx, pos_idx, y, rows, batch, S, cfg->n_outputs, Nt, cfg->n_anchors, npe, cfg->int_rescaler);
+        else
+            concat_sparse_forward_kernel<false><<<(unsigned)blocks, 128, 0, st>>>(weights, idx, pos_idx, y, rows, batch, S, cfg->n_outputs, Nt, cfg->n_anchors, npe, cfg->int_rescaler);
+        LUTB_LAUNCH_CHECK();
+    }
+    if (cfg->int_mode) return launch_fixed_to_float(y, batch * S * (int64_t)cfg->n_outputs, cfg->int_rescaler, st);
+    return LUTB_OK;
+}
+
+extern "C" int lutb_concat_sparse_backward(const lutb_layer_cfg *cfg, const lutb_sparse_index *sparse, int64_t batch,
+                                           float *weights, const float *dY, const int32_t *anchors, const int32_t *idx,
+                                           const float *min_delta, const int32_t *min_k, const int32_t *pos_idx,
+                                           const float *pos_min_delta, const int32_t *pos_min_k, float *dX, float *dPE,
+                                           float *dW, double external_lr, void *stream) {
+    int rc = validate_concat(cfg, batch);
+    if (rc) return rc;
+    SparseRows rows;
+    rc = validate_sparse_rows(sparse, &rows);
+    if (rc) return rc;
+    LUTB_REQUIRE(weights && dY && anchors && idx && min_delta && min_k && dX, LUTB_ERR_NULL, "a required tensor pointer is NULL");
+    const int S = cfg->seq_len, npe = cfg->pos_dim, Nt = cfg->n_detectors, O = cfg->n_outputs, Nc = cfg->n_anchors;
+    LUTB_REQUIRE(npe == 0 || (pos_idx && pos_min_delta && pos_min_k && dPE), LUTB_ERR_NULL, "positional tensors are NULL");
+    LUTB_REQUIRE(!(external_lr >= 0.0 && dW != nullptr), LUTB_ERR_MODE,
+                 "in internal weight gradients mode w_weights_gradients should be nullptr");
+    LUTB_REQUIRE(!(external_lr < 0.0 && dW == nullptr), LUTB_ERR_NULL, "w_weights_gradients is NULL");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    double lr = cfg->lr_meta;
+    if (external_lr >= 0.0) lr *= -(double)(float)external_lr;
+    const int2 *an = reinterpret_cast<const int2 *>(anchors);
+    const int64_t total = batch * S * (int64_t)Nt * S;
+    const int64_t blocks = min((total + 127) / 128, (int64_t)device_info().sm_count * 64);
+#define LUTB_CS_BWD(DO_DX, TARGET)                                                                                          \
+    do {                                                                                                                    \
+        if (cfg->int_mode)                                                                                                  \
+            concat_sparse_backward_kernel<true><<<(unsigned)blocks, 128, 0, st>>>(weights, dY, an, idx, min_delta, min_k, pos_idx, pos_min_delta, pos_min_k, dX, dPE, TARGET, rows, batch, S, cfg->n_inputs, O, Nt, Nc, npe, DO_DX, lr, cfg->int_rescaler); \
+        else                                                                                                                \
+            concat_sparse_backward_kernel<false><<<(unsigned)blocks, 128, 0, st>>>(weights, dY, an, idx, min_delta, min_k, pos_idx, pos_min_delta, pos_min_k, dX, dPE, TARGET, rows, batch, S, cfg->n_inputs, O, Nt, Nc, npe, DO_DX, lr, cfg->int_rescaler); \
+    } while (0)
+    if (external_lr >= 0.0) {
+        // in-place SGD: every input gradient is computed from the unmodified tables first
+        {
+            KernelScope scope(K_CONCAT_BACKWARD, st);
+            LUTB_CS_BWD(1, nullptr);
+        }
+        LUTB_LAUNCH_CHECK();
+        KernelScope scope(K_CONCAT_WEIGHT_UPDATE, st);
+        LUTB_CS_BWD(0, weights);
+    } else {
+        KernelScope scope(K_CONCAT_BACKWARD, st);
+        LUTB_CS_BWD(1, dW);
+    }
+#undef LUTB_CS_BWD
+    LUTB_LAUNCH_CHECK();
+    if (cfg->int_mode) {
+        rc = launch_fixed_to_float(dX, batch * S * (int64_t)cfg->n_inputs, cfg->int_rescaler, st);
+        if (rc) return rc;
+        if (dW) {
+            rc = launch_fixed_to_float(dW, sparse->n_weights, cfg->int_rescaler, st);
             if (rc) return rc;
         }
         if (npe > 0) rc = launch_fixed_to_float(dPE, (int64_t)(S - 1) * Nt * npe, cfg->int_rescaler, st);

@@ -431,8 +431,6 @@ class _LUTDataManager:
             raise ValueError("batch_size == 0")
         if self._seq_len <= 1:
             raise ValueError("forward_step_concat should only be called when sequence_length > 1")
-        if not self._fully_connected:
-            raise ValueError("sequence layers are only available with fully connected outputs in this backend")
         B, S = int(batch_size), self._seq_len
         self._expect(r_input, B * S * self._n_inputs, "r_input")
         self._expect(w_output, B * S * self._n_outputs, "w_output")
@@ -442,8 +440,14 @@ class _LUTDataManager:
             raise ValueError("positional embeddings and their index buffer are required when positional_dim > 0")
         cfg = self._cfg(cmp_eps)
         with torch.cuda.device(dev):
-            rc = _native.lib().lutb_concat_forward(
-                ctypes.byref(cfg), B, _ptr(r_weights), _ptr(r_input), _ptr(r_detector_anchors),
+            fn, head = _native.lib().lutb_concat_forward, (ctypes.byref(cfg),)
+            if not self._fully_connected:
+                if self._sparse is None:
+                    raise ValueError("sparse connectivity is not attached")
+                sp = self._sparse.c_struct()
+                fn, head = _native.lib().lutb_concat_sparse_forward, (ctypes.byref(cfg), ctypes.byref(sp))
+            rc = fn(
+                *head, B, _ptr(r_weights), _ptr(r_input), _ptr(r_detector_anchors),
                 _ptr(r_positional_embeddings), _ptr(w_output), _ptr(w_lookup_indices), _ptr(w_min_anchor_deltas),
                 _ptr(w_min_anchor_delta_indices), _ptr(w_positional_lookup_indices), _ptr(w_positional_min_deltas),
                 _ptr(w_positional_min_delta_indices), self._stream())
@@ -483,8 +487,14 @@ class _LUTDataManager:
         self._expect(w_input_gradients, B * S * self._n_inputs, "w_input_gradients")
         cfg = self._cfg()
         with torch.cuda.device(dev):
-            rc = _native.lib().lutb_concat_backward(
-                ctypes.byref(cfg), B, _ptr(r_weights), _ptr(r_output_gradients), _ptr(r_detector_anchors),
+            fn, head = _native.lib().lutb_concat_backward, (ctypes.byref(cfg),)
+            if not self._fully_connected:
+                if self._sparse is None:
+                    raise ValueError("sparse connectivity is not attached")
+                sp = self._sparse.c_struct()
+                fn, head = _native.lib().lutb_concat_sparse_backward, (ctypes.byref(cfg), ctypes.byref(sp))
+            rc = fn(
+                *head, B, _ptr(r_weights), _ptr(r_output_gradients), _ptr(r_detector_anchors),
                 _ptr(r_lookup_indices), _ptr(r_min_anchor_deltas), _ptr(r_min_anchor_delta_indices),
                 _ptr(r_positional_lookup_indices), _ptr(r_positional_min_deltas),
                 _ptr(r_positional_min_delta_indices), _ptr(w_input_gradients),

@@ -589,6 +589,19 @@ class LUTLayerBasic(nn.Module):
             return w_grad, pe_grad
         return x_grad.view(x.shape), w_grad, pe_grad
 
+    def load_structure(self, anchors, source_ids, weight_slots, target_ids, n_weights):
+        """Adopt the structure of a reference-built layer: its anchor pairs and its synapse export (per
+        synapse: lookup neuron id, slot in the flat weight array, output index).  Weights of that layer
+        can then be copied into ``_weights`` verbatim."""
+        self._set_anchors(torch.as_tensor(anchors))
+        index = _structure.SparseIndex.from_export(
+            source_ids, weight_slots, target_ids, self._n_detectors, self._n_lookup_neurons // self._n_detectors,
+            self._forward_group_size, self._n_outputs, n_weights)
+        self._lut_dm.set_sparse_index(index)
+        self._weights = nn.Parameter(torch.zeros(n_weights, dtype=torch.float32, device=self.device))
+        self._lut_dm.to_device(self.device.index if self.device.type == "cuda" else -1)
+        return self
+
     def forward(self, x):
         if self._sequence_length == 1:
             return _LUTFunction.apply(x, self._weights, None, self)
@@ -796,19 +809,6 @@ class ProjectionLUTLayer(LUTLayerBasic):
         self._weights = nn.Parameter(index.initial_weights(synapse_meta, random_seed))
         if device is not None:
             self.to(device=device)
-
-    def load_structure(self, anchors, source_ids, weight_slots, target_ids, n_weights):
-        """Adopt the structure of a reference-built layer: its anchor pairs and its synapse export (per
-        synapse: lookup neuron id, slot in the flat weight array, output index).  Weights of that layer
-        can then be copied into ``_weights`` verbatim."""
-        self._set_anchors(torch.as_tensor(anchors))
-        index = _structure.SparseIndex.from_export(
-            source_ids, weight_slots, target_ids, self._n_detectors, 1 << self._n_anchors_per_detector,
-            self._forward_group_size, self._n_outputs, n_weights)
-        self._lut_dm.set_sparse_index(index)
-        self._weights = nn.Parameter(torch.zeros(n_weights, dtype=torch.float32, device=self.device))
-        self._lut_dm.to_device(self.device.index if self.device.type == "cuda" else -1)
-        return self
 
     def input_shape(self):
         return self._input_shape

@@ -157,3 +157,38 @@ CONCAT_CASES = {
     # one key more than a 32-wide pair tile, dead band, vector-width rows
     "concat_tile_edge_f32": dict(seed=407, B=2, S=34, E=12, Nt=3, Nc=2, Npe=2, O=16, cmp_eps=0.02, quantized_input=True),
 }
+
+
+# Concatenation-mode sequence layers whose lookup -> output connectivity is sparse (Conv2DLUTLayer with a second
+# sliding window over the detector grid): geometry arguments of the layer plus batch / sequence sizes.
+CONCAT_SPARSE_CASES = {
+    # (the reference can only build these layers without positional embeddings: its output window counts
+    # 2^(2*Nc) lookup channels per detector, LUTLayer.py:199-203 against :1370)
+    "sparse_concat_f32": dict(seed=500, B=2, S=6, in_shape=(4, 4), Nc=2, Npe=0, det_shape=(2, 2), out_kernel=(2, 2),
+                              rf=(2, 2), rf_stride=(2, 2), lut_rf=(2, 2), lut_rf_stride=(2, 2)),
+    "sparse_concat_i32": dict(seed=501, B=2, S=6, in_shape=(4, 4), Nc=2, Npe=0, det_shape=(2, 2), out_kernel=(2, 2),
+                              rf=(2, 2), rf_stride=(2, 2), lut_rf=(2, 2), lut_rf_stride=(2, 2), int_mode=True,
+                              int_rescaler=2.0),
+    # more than one 32x32 pair tile; rows longer than one synapse group (group size 4 < 9 targets)
+    "sparse_concat_long_f32": dict(seed=502, B=1, S=35, in_shape=(4, 6), Nc=2, Npe=0, det_shape=(1, 2), out_kernel=(1, 1),
+                                   rf=(2, 2), rf_stride=(2, 2), lut_rf=(2, 3), lut_rf_stride=(1, 1), G=4,
+                                   quantized_input=True),
+    "sparse_concat_internal": dict(seed=503, B=2, S=5, in_shape=(4, 4), Nc=2, Npe=0, det_shape=(2, 1), out_kernel=(1, 2),
+                                   rf=(2, 2), rf_stride=(2, 2), lut_rf=(2, 1), lut_rf_stride=(1, 1), policy="internal",
+                                   ext_lr=0.25, lr_meta=0.5),
+}
+
+
+def concat_sparse_inputs(cfg, n_weights, n_outputs, n_detectors):
+    """x [B,S,E], tables (flat, reference layout), positional embeddings (flat, as stored) and dY [B,S,O]."""
+    s = cfg["seed"]
+    B, S = cfg["B"], cfg["S"]
+    E = cfg["in_shape"][0] * cfg["in_shape"][1]
+    x = synth.uniform(s + 41, (B, S, E), -1.0, 1.0)
+    if cfg.get("quantized_input"):
+        x = (x * 4).round().astype("float32") / 4
+    W = synth.normal(s + 42, (n_weights,), 0.0, 0.1)
+    n_pe = (S - 1) * (1 if cfg.get("unified_pe") else n_detectors) * cfg["Npe"]
+    pe = synth.uniform(s + 43, (n_pe,), -1.0, 1.0) if n_pe > 0 else None
+    dY = synth.normal(s + 44, (B, S, n_outputs))
+    return x, W, pe, dY

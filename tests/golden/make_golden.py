@@ -20,7 +20,7 @@ import torch
 
 sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 import synth  # noqa: E402,F401
-from cases import (CONCAT_CASES, NONSEQ_FC_CASES, PROJECTION_CASES, PRODUCT_CASES, nonseq_fc_inputs, projection_inputs,  # noqa: E402
+from cases import (CONCAT_CASES, CONCAT_SPARSE_CASES, concat_sparse_inputs, NONSEQ_FC_CASES, PROJECTION_CASES, PRODUCT_CASES, nonseq_fc_inputs, projection_inputs,  # noqa: E402
                    sequence_inputs)
 
 from spiky.lut.LUTLayer import (  # noqa: E402  (the reference)
@@ -240,6 +240,60 @@ def run_concat(name, cfg):
     save(name, dict(cfg, kind="concat"), in_x=x, in_anchors=anchors, **out)
 
 
+# ----------------------------------------------------------------------------- sparse concatenation-mode layers
+def run_concat_sparse(name, cfg):
+    from spiky.lut.LUTLayer import Conv2DLUTLayer
+    int_mode = cfg.get("int_mode", False)
+    policy = {"dense": GradientType.Dense, "internal": GradientType.Internal}[cfg.get("policy", "dense")]
+    B, S, Nc, Npe = cfg["B"], cfg["S"], cfg["Nc"], cfg["Npe"]
+    layer = Conv2DLUTLayer(
+        input_shape=cfg["in_shape"], n_anchors_per_detector=Nc, detectors_shape=cfg["det_shape"],
+        output_kernel_shape=cfg["out_kernel"], sequence_length=S, receptive_field_shape=cfg["rf"],
+        receptive_field_stride_shape=cfg["rf_stride"], lut_receptive_field_shape=cfg["lut_rf"],
+        lut_receptive_field_stride_shape=cfg["lut_rf_stride"],
+        synapse_meta=SynapseMeta(learning_rate=cfg.get("lr_meta", 1.0), min_weight=-1.0, max_weight=1.0),
+        concatenation_product=True, positional_dim=Npe, unified_pe=cfg.get("unified_pe", False),
+        weights_gradient_policy=GradientPolicy(policy), summation_dtype=torch.int32 if int_mode else torch.float32,
+        _int_rescaler=cfg.get("int_rescaler", 0.001), _forward_group_size=cfg.get("G", 32), random_seed=cfg["seed"],
+    )
+    src, slot, tgt = export_structure(layer)
+    n_weights = layer._weights.numel()
+    Nt, O = layer.n_detectors(), layer.n_outputs()
+    E = cfg["in_shape"][0] * cfg["in_shape"][1]
+    x, W, pe, dY = concat_sparse_inputs(cfg, n_weights, O, Nt)
+    with torch.no_grad():
+        layer._weights.copy_(torch.from_numpy(W))
+        if pe is not None:
+            layer._positional_embeddings.copy_(torch.from_numpy(pe))
+    xt = torch.from_numpy(x).view((B, S) + tuple(cfg["in_shape"]))
+    pos = layer._prepare_positional_embeddings() if Npe > 0 else None
+    if pos is not None:
+        pos = pos.detach()
+    layer.eval()
+    out = {"y_eval": t2n(layer.forward_step_concat(xt, pos)).reshape(B, S, O)}
+    layer.train()
+    y, idx, md, mk, pidx, pmd, pmk = layer.forward_step_concat(xt, pos)
+    out.update(y=t2n(y).reshape(B, S, O), idx=t2n(idx).reshape(B * S, Nt), min_delta=t2n(md).reshape(B * S, Nt),
+               min_k=t2n(mk).reshape(B * S, Nt))
+    if Npe > 0:
+        out.update(pidx=t2n(pidx).reshape(-1), pmin=t2n(pmd).reshape(-1), pmin_k=t2n(pmk).reshape(-1))
+    if policy == GradientType.Internal:
+        layer.set_external_learning_rate_hook(lambda w: cfg["ext_lr"])
+    dyt = torch.from_numpy(dY).view((B, S) + tuple(layer.output_shape()))
+    dx, dw, dpe = layer.backward_step_concat(xt, dyt, idx, md, mk, pidx, pmd, pmk)
+    out["dX"] = t2n(dx).reshape(B, S, E)
+    if dpe is not None:
+        out["dPE"] = t2n(dpe)
+    if policy == GradientType.Internal:
+        out["W_after"] = t2n(layer._weights)
+    else:
+        out["dW"] = t2n(dw)
+    save(name, dict(cfg, kind="concat_sparse", Nt=Nt, O=O, E=E, n_weights=n_weights,
+                    n_lookup_neurons=layer.n_lookup_neurons(), out_shape=tuple(layer.output_shape())),
+         anchors=t2n(layer._detector_anchors), syn_source=src.astype(np.int32), syn_slot=slot.astype(np.int32),
+         syn_target=tgt.astype(np.int32), **out)
+
+
 def main():
     prefixes = sys.argv[1:]
     for name, cfg in NONSEQ_FC_CASES.items():
@@ -254,6 +308,9 @@ def main():
     for name, cfg in PROJECTION_CASES.items():
         if not prefixes or any(name.startswith(p) for p in prefixes):
             run_projection(name, cfg)
+    for name, cfg in CONCAT_SPARSE_CASES.items():
+        if not prefixes or any(name.startswith(p) for p in prefixes):
+            run_concat_sparse(name, cfg)
 
 
 if __name__ == "__main__":

@@ -174,3 +174,31 @@ def test_concat_oracle_matches_reference(name):
         assert np.array_equal(Wb, ref["W_after"])
     else:
         assert np.array_equal(dW, ref["dW"])
+
+
+@pytest.mark.parametrize("name", golden_util.names("sparse_concat_"))
+def test_concat_sparse_oracle_matches_reference(name):
+    """Concatenation-mode layers with sparse lookup -> output connectivity (reference: Conv2DLUTLayer with a second
+    sliding window, sequence_length > 1)."""
+    from cases import concat_sparse_inputs
+
+    cfg, ref = golden_util.load(name)
+    index = sparse_index_from_golden(cfg, ref)
+    sp = dict(index.numpy(), group_size=index.group_size)
+    x, W, pe, dY = concat_sparse_inputs(cfg, cfg["n_weights"], cfg["O"], cfg["Nt"])
+    kw = dict(int_mode=cfg.get("int_mode", False), int_rescaler=cfg.get("int_rescaler", 0.001))
+    anchors = ref["anchors"]
+    y_eval, _ = orc.concat_sparse_forward(W, x, None, anchors, sp, cfg["Nc"], cfg["O"], cfg["Npe"], train=False, **kw)
+    y, st = orc.concat_sparse_forward(W, x, None, anchors, sp, cfg["Nc"], cfg["O"], cfg["Npe"], train=True, **kw)
+    assert np.array_equal(st["idx"], ref["idx"]) and np.array_equal(st["min_k"], ref["min_k"])
+    assert np.array_equal(y, ref["y"]) and np.array_equal(y_eval, ref["y_eval"])
+    internal = cfg.get("policy") == "internal"
+    Wb = W.copy()
+    dX, dW, _ = orc.concat_sparse_backward(Wb, dY, anchors, st, sp, cfg["E"], cfg["Nc"], cfg["Npe"],
+                                           lr_meta=cfg.get("lr_meta", 1.0),
+                                           external_lr=cfg["ext_lr"] if internal else -1.0, **kw)
+    assert np.array_equal(dX, ref["dX"])
+    if internal:
+        assert np.array_equal(Wb, ref["W_after"])
+    else:
+        assert np.array_equal(dW, ref["dW"])
