@@ -256,8 +256,8 @@ int lutb_concat_backward(const lutb_layer_cfg *cfg, int64_t batch, float *weight
  * (lut_runtime_kernels_logic.proto:1906-2013), propagate_through_detectors_seq_sparse_logic (:3371-3627) and
  * gather_w_gradients_seq_sparse_logic (:3837-3942).  Arguments as lutb_concat_forward / lutb_concat_backward plus
  * the connectivity; the index holds 2^(2*Nc + pos_dim) rows per detector and weights is fp32 [sparse->n_weights].
- * (Product-mode layers with sparse connectivity are not provided: the reference implements them for its CUDA build
- * only, so nothing pins their results here.)
+ * (Product-mode layers with sparse connectivity are not provided: the reference's layer classes cannot construct
+ * one, so no caller reaches that branch and nothing pins its results.)
  */
 int lutb_concat_sparse_forward(const lutb_layer_cfg *cfg, const lutb_sparse_index *sparse, int64_t batch,
                                const float *weights, const float *x, const int32_t *anchors, const float *pos_embeddings,

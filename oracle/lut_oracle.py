@@ -328,3 +328,4 @@ def concat_sparse_backward(W, dY, anchors, state, sp, n_inputs, n_anchors, pos_d
                                      _l(Wf.size), _d(float(np.float32(lr_meta))), _d(float(np.float32(external_lr))),
                                      _i(int(int_mode)), _d(int_rescaler))
     return dX, dW, dPE
+

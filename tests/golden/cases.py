@@ -192,3 +192,4 @@ def concat_sparse_inputs(cfg, n_weights, n_outputs, n_detectors):
     pe = synth.uniform(s + 43, (n_pe,), -1.0, 1.0) if n_pe > 0 else None
     dY = synth.normal(s + 44, (B, S, n_outputs))
     return x, W, pe, dY
+

@@ -294,6 +294,7 @@ def run_concat_sparse(name, cfg):
          syn_target=tgt.astype(np.int32), **out)
 
 
+
 def main():
     prefixes = sys.argv[1:]
     for name, cfg in NONSEQ_FC_CASES.items():
