@@ -110,6 +110,10 @@ ORACLE_CASES = {
     # one sample; more detectors than threads of a row group; inputs not a multiple of 4
     "one_sample": dict(seed=515, B=1, I=50, Nt=300, Nc=7, O=12),
     "odd_inputs": dict(seed=516, B=13, I=4099, Nt=64, Nc=8, O=32, normal_input=True),
+    # input rows so long that fewer rows are staged together (2, then 1), and rows that do not fit shared memory at all
+    "inputs_10k": dict(seed=517, B=5, I=10001, Nt=20, Nc=5, O=8, normal_input=True),
+    "inputs_20k": dict(seed=518, B=3, I=20002, Nt=20, Nc=5, O=8, normal_input=True),
+    "inputs_60k": dict(seed=519, B=3, I=60001, Nt=20, Nc=5, O=8, normal_input=True),
     # a slice of the large inference layer (4096 inputs, 8 pairs, 64 outputs)
     "c5_slice": dict(seed=507, B=40, I=4096, Nt=512, Nc=8, O=64, normal_input=True),
     "nan_inputs": dict(seed=508, B=8, I=32, Nt=8, Nc=4, O=8, nan_input=True),
