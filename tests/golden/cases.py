@@ -193,3 +193,26 @@ def concat_sparse_inputs(cfg, n_weights, n_outputs, n_detectors):
     dY = synth.normal(s + 44, (B, S, n_outputs))
     return x, W, pe, dY
 
+
+
+# Non-sequence Conv2DLUTLayer: detectors on sliding receptive fields, outputs through a second sliding window over the
+# detector grid (sparse) or fully connected (lut_rf None).  The fixtures also pin the geometry: which inputs a
+# detector may compare and which outputs it feeds.
+CONV2D_CASES = {
+    "conv2d_sparse_f32": dict(seed=700, B=5, in_shape=(8, 10), Nc=3, det_shape=(2, 3), out_kernel=(2, 2), rf=(4, 4),
+                              rf_stride=(2, 3), lut_rf=(3, 3), lut_rf_stride=(1, 2)),
+    "conv2d_sparse_i32": dict(seed=701, B=5, in_shape=(8, 10), Nc=3, det_shape=(2, 3), out_kernel=(2, 2), rf=(4, 4),
+                              rf_stride=(2, 3), lut_rf=(3, 3), lut_rf_stride=(1, 2), int_mode=True, int_rescaler=0.5),
+    "conv2d_fc_f32": dict(seed=702, B=4, in_shape=(6, 6), Nc=4, det_shape=(1, 2), out_kernel=(3, 2), rf=(3, 3),
+                          rf_stride=(3, 3), lut_rf=None, lut_rf_stride=None),
+}
+
+
+def conv2d_inputs(cfg, n_weights, n_outputs):
+    s = cfg["seed"]
+    B = cfg["B"]
+    I = cfg["in_shape"][0] * cfg["in_shape"][1]
+    x = synth.uniform(s + 51, (B, I), -1.0, 1.0)
+    W = synth.normal(s + 52, (n_weights,), 0.0, 0.1)
+    dY = synth.normal(s + 53, (B, n_outputs))
+    return x, W, dY

@@ -20,7 +20,7 @@ import torch
 
 sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 import synth  # noqa: E402,F401
-from cases import (CONCAT_CASES, CONCAT_SPARSE_CASES, concat_sparse_inputs, NONSEQ_FC_CASES, PROJECTION_CASES, PRODUCT_CASES, nonseq_fc_inputs, projection_inputs,  # noqa: E402
+from cases import (CONCAT_CASES, CONCAT_SPARSE_CASES, CONV2D_CASES, concat_sparse_inputs, conv2d_inputs, NONSEQ_FC_CASES, PROJECTION_CASES, PRODUCT_CASES, nonseq_fc_inputs, projection_inputs,  # noqa: E402
                    sequence_inputs)
 
 from spiky.lut.LUTLayer import (  # noqa: E402  (the reference)
@@ -295,6 +295,43 @@ def run_concat_sparse(name, cfg):
 
 
 
+# ----------------------------------------------------------------------------- non-sequence Conv2DLUTLayer
+def run_conv2d(name, cfg):
+    from spiky.lut.LUTLayer import Conv2DLUTLayer
+    int_mode = cfg.get("int_mode", False)
+    layer = Conv2DLUTLayer(
+        input_shape=cfg["in_shape"], n_anchors_per_detector=cfg["Nc"], detectors_shape=cfg["det_shape"],
+        output_kernel_shape=cfg["out_kernel"], receptive_field_shape=cfg["rf"],
+        receptive_field_stride_shape=cfg["rf_stride"], lut_receptive_field_shape=cfg["lut_rf"],
+        lut_receptive_field_stride_shape=cfg["lut_rf_stride"],
+        synapse_meta=SynapseMeta(min_weight=-1.0, max_weight=1.0),
+        summation_dtype=torch.int32 if int_mode else torch.float32, _int_rescaler=cfg.get("int_rescaler", 0.001),
+        random_seed=cfg["seed"],
+    )
+    sparse = cfg["lut_rf"] is not None
+    extra = {}
+    if sparse:
+        src, slot, tgt = export_structure(layer)
+        extra = dict(syn_source=src.astype(np.int32), syn_slot=slot.astype(np.int32), syn_target=tgt.astype(np.int32))
+    n_weights = layer._weights.numel()
+    Nt, O = layer.n_detectors(), layer.n_outputs()
+    I = cfg["in_shape"][0] * cfg["in_shape"][1]
+    B = cfg["B"]
+    x, W, dY = conv2d_inputs(cfg, n_weights, O)
+    with torch.no_grad():
+        layer._weights.copy_(torch.from_numpy(W))
+    xt = torch.from_numpy(x).view((B, 1) + tuple(cfg["in_shape"]))
+    layer.train()
+    y, idx, md, mk = layer.forward_step(xt)
+    out = dict(y=t2n(y).reshape(B, O), idx=t2n(idx).reshape(B, Nt), min_delta=t2n(md).reshape(B, Nt),
+               min_k=t2n(mk).reshape(B, Nt))
+    dx, dw = layer.backward_step(xt, torch.from_numpy(dY).view((B, 1) + tuple(layer.output_shape())), idx, md, mk)
+    out.update(dX=t2n(dx).reshape(B, I), dW=t2n(dw))
+    save(name, dict(cfg, kind="conv2d", Nt=Nt, O=O, n_weights=n_weights, n_lookup_neurons=layer.n_lookup_neurons(),
+                    out_shape=tuple(layer.output_shape()), lut_shape=tuple(layer.lut_shape())),
+         anchors=t2n(layer._detector_anchors), **extra, **out)
+
+
 def main():
     prefixes = sys.argv[1:]
     for name, cfg in NONSEQ_FC_CASES.items():
@@ -309,6 +346,9 @@ def main():
     for name, cfg in PROJECTION_CASES.items():
         if not prefixes or any(name.startswith(p) for p in prefixes):
             run_projection(name, cfg)
+    for name, cfg in CONV2D_CASES.items():
+        if not prefixes or any(name.startswith(p) for p in prefixes):
+            run_conv2d(name, cfg)
     for name, cfg in CONCAT_SPARSE_CASES.items():
         if not prefixes or any(name.startswith(p) for p in prefixes):
             run_concat_sparse(name, cfg)
