@@ -4,13 +4,13 @@
 # reference is copied into this repository: the copy, the generated sources and the built
 # module all live under $SCRATCH (default /tmp/spiky_ref).
 #
-#   usage: tests/golden/build_reference_cpu.sh [reference_root] [scratch_dir]
+#   usage: tests/golden/build_reference_cpu.sh <reference_checkout> [scratch_dir]
 #
 # Notes: the reference generates its kernel sources from .proto files by hand (its setup.py
 # only does so when run as __main__, after setup()), and the image's default /opt/gcc links
 # libstdc++ statically, which breaks the module's iostream use - hence /usr/bin/g++.
 set -euo pipefail
-REF=${1:-/root/reference}
+REF=${1:?usage: build_reference_cpu.sh <reference_checkout> [scratch_dir]}
 SCRATCH=${2:-/tmp/spiky_ref}
 mkdir -p "$SCRATCH"
 cp -r "$REF/spiky_cuda" "$REF/src" "$SCRATCH/"

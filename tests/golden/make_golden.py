@@ -2,7 +2,7 @@
 
 Run in a container that has the reference checkout:
 
-    tests/golden/build_reference_cpu.sh                      # once, builds into /tmp/spiky_ref
+    tests/golden/build_reference_cpu.sh <reference checkout>  # once, builds into /tmp/spiky_ref
     PYTHONPATH=/tmp/spiky_ref/spiky_cuda:/tmp/spiky_ref/src \
         python tests/golden/make_golden.py [case-name-prefix ...]
 
