@@ -132,3 +132,94 @@ class OverlappedGradientSync:
         for h in self._hooks:
             h.remove()
         self._hooks = []
+
+
+def exchange_sparse_gradients(params, group=None, average=False):
+    """Exchange of ``GradientType.Sparse`` table gradients: every rank contributes the (cell, value) lists of the
+    cells its shard of the batch touched and receives everybody's, so the payload is the touched cells instead of
+    the whole table (a concatenation-mode table has 2^(2Nc+Npe) rows of which a step touches a few).
+
+    One all-gather of the list lengths for all parameters, then per parameter one all-gather of the cell numbers and
+    one of the values, padded to the longest list.  The received lists are concatenated into an uncoalesced sparse
+    gradient: cells touched by several ranks appear once per rank and are summed when the optimiser coalesces (or
+    densifies) the gradient, which is the same sum a dense all-reduce would have produced.  Parameters whose
+    gradient is dense or missing on every rank are left alone.
+    """
+    if not dist.is_available() or not dist.is_initialized() or dist.get_world_size(group) == 1:
+        return
+    world = dist.get_world_size(group)
+    params = list(params)
+    if not params:
+        return
+    device = params[0].device
+    # Every rank must issue the same collectives.  A rank whose shard touched nothing has no gradient at all for a
+    # table, so the list lengths are exchanged for every parameter first: -1 = no gradient here, -2 = dense gradient
+    # here; a parameter takes part when any rank holds a sparse gradient for it, ranks without one send an empty list.
+    grads, lengths = [], []
+    for p in params:
+        g = p.grad
+        if g is None:
+            lengths.append(-1)
+        elif not g.is_sparse:
+            lengths.append(-2)
+        else:
+            g = g if g.is_coalesced() else g.coalesce()
+            lengths.append(g._nnz())
+        grads.append(g)
+    counts = torch.tensor(lengths, dtype=torch.int64, device=device)
+    all_counts = [torch.empty_like(counts) for _ in range(world)]
+    dist.all_gather(all_counts, counts, group=group)
+    all_counts = torch.stack(all_counts).cpu()  # [world][n_params]
+    for n, (p, g) in enumerate(zip(params, grads)):
+        column = all_counts[:, n]
+        if int(column.max()) < 0:
+            continue  # nobody holds a sparse gradient for this parameter
+        if int((column == -2).sum()) > 0:
+            raise ValueError(f"parameter {n}: dense gradient on one rank, sparse on another")
+        longest = int(column.max())
+        if longest == 0:
+            continue
+        mine = 0 if g is None else g._nnz()
+        dtype = p.dtype if g is None else g.dtype
+        cells = torch.zeros(longest, dtype=torch.int64, device=device)
+        values = torch.zeros(longest, dtype=dtype, device=device)
+        if mine:
+            cells[:mine] = g.indices()[0]
+            values[:mine] = g.values()
+        got_cells = [torch.empty_like(cells) for _ in range(world)]
+        got_values = [torch.empty_like(values) for _ in range(world)]
+        dist.all_gather(got_cells, cells, group=group)
+        dist.all_gather(got_values, values, group=group)
+        keep = [max(int(column[r]), 0) for r in range(world)]
+        cells = torch.cat([c[:k] for c, k in zip(got_cells, keep)])
+        values = torch.cat([v[:k] for v, k in zip(got_values, keep)])
+        if average:
+            values = values / world
+        p.grad = torch.sparse_coo_tensor(cells.unsqueeze(0), values, size=p.shape, device=device,
+                                         check_invariants=False, is_coalesced=False)
+
+
+def average_internal_policy_weights(module, group=None):
+    """Data parallelism for tables trained with ``GradientType.Internal``: the backward kernel has already applied
+    ``W_r = W - lr * dW_r`` on every rank with that rank's shard gradient, so averaging the tables over the ranks
+    gives ``W - lr * mean_r(dW_r)``, the update a reduce-then-apply with the averaged gradient would have made
+    (equal up to fp32 rounding of the per-rank updates).  Call once per step, after backward; positional embeddings
+    of such layers are ordinary parameters with ordinary gradients and are not touched here.
+    """
+    if not dist.is_available() or not dist.is_initialized() or dist.get_world_size(group) == 1:
+        return 0
+    from .lut_layer import GradientType, LUTLayerBasic
+
+    world = dist.get_world_size(group)
+    nccl = dist.get_backend(group) == "nccl"
+    done = 0
+    for layer in module.modules():
+        if isinstance(layer, LUTLayerBasic) and layer._weights_gradient_policy.type == GradientType.Internal:
+            w = layer._weights.data
+            if nccl:
+                dist.all_reduce(w, op=dist.ReduceOp.AVG, group=group)
+            else:
+                dist.all_reduce(w, op=dist.ReduceOp.SUM, group=group)
+                w.div_(world)
+            done += 1
+    return done

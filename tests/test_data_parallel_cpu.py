@@ -119,3 +119,75 @@ def _overlap_worker(rank, world, port, result_dir):
 def test_overlapped_gradient_sync_and_sharded_accumulators(tmp_path):
     mp.spawn(_overlap_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
     assert open(tmp_path / "ok2").read() == "True"
+
+
+def _sparse_worker(rank, world, port, result_dir):
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests", "golden"))
+    import datetime
+    import synth
+    from oracle import lut_oracle as orc
+    from spiky_b200.data_parallel import average_internal_policy_weights, exchange_sparse_gradients, shard_batch
+    from spiky_b200.lut_layer import GradientPolicy, GradientType, LUTLayer, SynapseMeta
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=20))
+    try:
+        # (1) sparse exchange: each rank holds the touched cells of its shard's table gradient; after the exchange
+        # the (summed) sparse gradient equals the full-batch dense gradient
+        B, I, Nt, Nc, O = 12, 40, 6, 5, 8
+        x = synth.uniform(1, (B, I))
+        anchors = synth.anchor_pairs(2, Nt, Nc, I)
+        W = synth.normal(3, (Nt * (1 << Nc) * O,), 0.0, 0.02)
+        dY = synth.normal(4, (B, O))
+        b0, b1 = shard_batch(B, rank, world)
+        _, idx, md, mk = orc.nonseq_fc_forward(W, x[b0:b1], anchors, Nt, Nc, O)
+        _, dW = orc.nonseq_fc_backward(W, dY[b0:b1], anchors, idx, md, mk, I, Nc)
+        p = torch.nn.Parameter(torch.from_numpy(W.copy()))
+        cells = torch.from_numpy(np.flatnonzero(dW))
+        p.grad = torch.sparse_coo_tensor(cells.unsqueeze(0), torch.from_numpy(dW)[cells], size=p.shape)
+        untouched = torch.nn.Parameter(torch.zeros(7))          # no gradient on any rank
+        lonely = torch.nn.Parameter(torch.zeros(9))             # gradient on rank 1 only
+        if rank == 1:
+            lonely.grad = torch.sparse_coo_tensor(torch.tensor([[2, 5]]), torch.tensor([1.5, -2.0]), size=(9,))
+        dense = torch.nn.Parameter(torch.zeros(3))              # dense everywhere: left alone
+        dense.grad = torch.full((3,), float(rank))
+        exchange_sparse_gradients([p, untouched, lonely, dense])
+        _, idx, md, mk = orc.nonseq_fc_forward(W, x, anchors, Nt, Nc, O)
+        _, full = orc.nonseq_fc_backward(W, dY, anchors, idx, md, mk, I, Nc)
+        got = p.grad.to_dense().numpy()
+        ok = p.grad.is_sparse and float(np.abs(got - full).max()) <= 1e-6 * float(np.abs(full).max())
+        ok = ok and p.grad._nnz() < p.numel() and untouched.grad is None
+        expect = torch.zeros(9)
+        expect[2], expect[5] = 1.5, -2.0
+        ok = ok and torch.equal(lonely.grad.to_dense(), expect)
+        ok = ok and torch.equal(dense.grad, torch.full((3,), float(rank)))
+        # (2) Internal policy: tables that took their rank's in-place update are averaged over the ranks
+        layer = LUTLayer(n_inputs=16, n_anchors_per_detector=3, n_detectors=4, n_outputs=5,
+                         synapse_meta=SynapseMeta(min_weight=-1.0, max_weight=1.0),
+                         weights_gradient_policy=GradientPolicy(GradientType.Internal), random_seed=5, device=None)
+        other = LUTLayer(n_inputs=16, n_anchors_per_detector=3, n_detectors=4, n_outputs=5,
+                         synapse_meta=SynapseMeta(min_weight=-1.0, max_weight=1.0), random_seed=5, device=None)
+        model = torch.nn.ModuleList([layer, other])
+        start = layer._weights.detach().clone()
+        step = torch.arange(start.numel(), dtype=torch.float32) * 1e-3
+        with torch.no_grad():
+            layer._weights -= (rank + 1) * step      # stands for -lr * dW_r
+            other._weights += rank                   # not an Internal-policy layer: must stay as it is
+        kept = other._weights.detach().clone()
+        n = average_internal_policy_weights(model)
+        mean = sum(r + 1 for r in range(world)) / world
+        ok = ok and n == 1 and torch.allclose(layer._weights.detach(), start - mean * step, atol=1e-6)
+        ok = ok and torch.equal(other._weights.detach(), kept)
+        flags = [torch.zeros(1) for _ in range(world)]
+        dist.all_gather(flags, torch.tensor([1.0 if ok else 0.0]))
+        if rank == 0:
+            open(os.path.join(result_dir, "ok3"), "w").write(str(all(float(f) == 1.0 for f in flags)))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_sparse_gradient_exchange_and_internal_policy_average(tmp_path):
+    mp.spawn(_sparse_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
+    assert open(tmp_path / "ok3").read() == "True"
