@@ -113,6 +113,38 @@ class _LUTDataManager:
             return self._n_lookup_neurons * self._n_outputs
         return 0 if self._sparse is None else int(self._sparse.n_synapses)
 
+    def count_synapses(self, neuron_indices_to_process):
+        """Number of lookup -> output synapses of the given lookup neurons (reference: lut.cu:1182-1193)."""
+        if self._fully_connected:
+            raise ValueError("count_synapses: there is nothing to count in fully connected mode")
+        if self._sparse is None:
+            raise ValueError("sparse connectivity has not been attached yet")
+        return int(self._sparse.synapses_of(neuron_indices_to_process)[0].numel())
+
+    def export_synapses(self, weights, neuron_indices_to_process, target_internal_source_indices, target_weights,
+                        target_internal_target_indices, target_synapse_meta_indices=None):
+        """Fills the caller's tensors with one entry per synapse of the given lookup neurons: lookup neuron id,
+        weight, and the output's neuron id (outputs are numbered after the lookup neurons), in neuron order and
+        synapse order inside a neuron (reference: lut.cu:1195-1221).  Not a hot path: plain tensor indexing."""
+        if self._fully_connected:
+            raise ValueError("export_synapses: there is nothing to export in fully connected mode")
+        if self._sparse is None:
+            raise ValueError("sparse connectivity has not been attached yet")
+        src, slot, tgt = self._sparse.synapses_of(neuron_indices_to_process)
+        n = src.numel()
+        for t, name in ((target_internal_source_indices, "target_internal_source_indices"),
+                        (target_weights, "target_weights"),
+                        (target_internal_target_indices, "target_internal_target_indices")):
+            if t.numel() < n:
+                raise ValueError(f"{name} holds {t.numel()} entries, {n} synapses to export")
+        dev = target_weights.device
+        target_internal_source_indices.view(-1)[:n] = src.to(dev).to(target_internal_source_indices.dtype)
+        target_weights.view(-1)[:n] = weights.detach().view(-1)[slot.to(weights.device)].to(dev)
+        target_internal_target_indices.view(-1)[:n] = (tgt + self._n_lookup_neurons).to(dev).to(
+            target_internal_target_indices.dtype)
+        if target_synapse_meta_indices is not None:
+            target_synapse_meta_indices.view(-1)[:n] = 0
+
     def get_weights_dimension(self):
         if self._fully_connected:
             return self._n_lookup_neurons * self._n_outputs

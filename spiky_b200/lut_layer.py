@@ -351,6 +351,33 @@ class LUTLayerBasic(nn.Module):
             raise RuntimeError("Detectors are not initialized, call initialize_detectors() first")
         return self._detector_anchors.view(self._n_detectors, self._n_anchors_per_detector, 2)
 
+    def _count_synapses(self, neuron_ids):
+        if self._is_fully_connected:
+            return self._n_lookup_neurons * self._n_outputs
+        return self._lut_dm.count_synapses(neuron_ids)
+
+    def _export_synapses(self, neuron_ids, source_ids, weights, target_ids, synapse_metas=None):
+        """One entry per synapse of the given lookup neurons into the caller's tensors: lookup neuron id, weight,
+        output neuron id (outputs are numbered after the lookup neurons) (reference: LUTLayer.py:1206-1230)."""
+        if self._is_fully_connected:
+            source_ids[:] = neuron_ids.view(neuron_ids.numel(), -1).repeat(1, self._n_outputs).flatten()
+            weights[:] = self._weights.detach().view(self._n_lookup_neurons, self._n_outputs)[neuron_ids.long()].flatten()
+            target_ids[:] = torch.arange(self._n_outputs, device=self.device, dtype=torch.int32).repeat(
+                neuron_ids.numel())
+            target_ids += self._n_lookup_neurons
+            if synapse_metas is not None:
+                synapse_metas[:] = 0.0
+        else:
+            self._lut_dm.export_synapses(self._weights, neuron_ids, source_ids, weights, target_ids, synapse_metas)
+
+    def _export_all_synapses(self):
+        n = self.n_synapses()
+        source_ids = torch.zeros([n], dtype=torch.int32, device=self.device)
+        target_ids = torch.zeros([n], dtype=torch.int32, device=self.device)
+        weights = torch.zeros([n], dtype=torch.float32, device=self.device)
+        self._export_synapses(self.get_lookup_neuron_ids(), source_ids, weights, target_ids)
+        return weights, source_ids, target_ids
+
     # ------------------------------------------------------------------ structure
     def _set_anchors(self, anchors):
         anchors = anchors.to(dtype=torch.int32, device=self.device).reshape(-1).contiguous()
@@ -704,6 +731,18 @@ class Conv2DLUTLayer(LUTLayerBasic):
     def lut_receptive_field_shape(self):
         return self._lut_receptive_field_shape
 
+    def export_weights(self, inverse_order=True):
+        """Weights ordered by (output, lookup neuron) and shaped output_shape + lut_receptive_field_shape, or the
+        other way round (reference: LUTLayer.py:1417-1437)."""
+        weights, source_ids, target_ids = self._export_all_synapses()
+        if inverse_order:
+            order = torch.argsort(source_ids, stable=True)
+            order = order[torch.argsort(target_ids[order], stable=True)]
+            return weights[order].view(tuple(self.output_shape()) + tuple(self.lut_receptive_field_shape()))
+        order = torch.argsort(target_ids, stable=True)
+        order = order[torch.argsort(source_ids[order], stable=True)]
+        return weights[order].view(tuple(self.lut_receptive_field_shape()) + tuple(self.output_shape()))
+
     def __repr__(self):
         return (f"Conv2DLUTLayer(input_shape={self.input_shape()}, output_shape={self.output_shape()}, "
                 f"detectors_shape={self.detectors_shape()}, n_anchors_per_detector={self.n_anchors_per_detector()})")
@@ -818,6 +857,14 @@ class ProjectionLUTLayer(LUTLayerBasic):
 
     def detectors_shape(self):
         return (self._n_detector_groups, self._n_detectors_in_group)
+
+    def export_weights(self):
+        """(weights, lookup neuron ids, output neuron ids) ordered by output, then lookup neuron
+        (reference: LUTLayer.py:1629-1645)."""
+        weights, source_ids, target_ids = self._export_all_synapses()
+        order = torch.argsort(source_ids, stable=True)
+        order = order[torch.argsort(target_ids[order], stable=True)]
+        return weights[order], source_ids[order], target_ids[order]
 
     def __repr__(self):
         return (f"ProjectionLUTLayer(input_shape={self.input_shape()}, output_shape={self.output_shape()}, "

@@ -320,6 +320,25 @@ class SparseIndex:
         mask = torch.arange(det_targets.shape[1]).view(1, -1) < counts.view(-1, 1)
         return cls(wbase, stride, counts, det_targets[mask], group_size, n_weights, n_outputs, rows_per_detector)
 
+    def synapses_of(self, neuron_ids):
+        """Per synapse of the given lookup neurons (table rows; id = detector * rows_per_detector + row), in the
+        order given and in synapse order inside a row: (lookup neuron, slot in the flat weight array, output index),
+        all int64 on the index's device.  Inverse of ``from_export``."""
+        dev = self.det_wbase.device
+        ids = torch.as_tensor(neuron_ids, device=dev).to(torch.int64).reshape(-1)
+        n_neurons = self.det_count.numel() * self.rows_per_detector
+        if ids.numel() and (int(ids.min()) < 0 or int(ids.max()) >= n_neurons):
+            raise ValueError("lookup neuron id out of range")
+        det = ids // self.rows_per_detector
+        row = ids - det * self.rows_per_detector
+        counts = self.det_count.to(torch.int64)[det]
+        which = torch.repeat_interleave(torch.arange(ids.numel(), device=dev), counts)
+        p = torch.arange(which.numel(), device=dev) - (torch.cumsum(counts, 0) - counts)[which]
+        d = det[which]
+        slot = self.det_wbase[d] + row[which] * self.det_stride.to(torch.int64)[d] + p + 2 * (p // self.group_size)
+        target = self.syn_target.to(torch.int64)[self.det_sstart.to(torch.int64)[d] + p]
+        return ids[which], slot, target
+
     def initial_weights(self, synapse_meta, seed=None):
         """fp32 [n_weights]: noise * U[0,1) + initial weight, clipped to the meta's range; holes are zero."""
         gen = None
