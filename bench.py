@@ -249,34 +249,42 @@ class SparseConvNetWorkload:
     READOUT = (256, 10, 64, 8)  # inputs, outputs, tables, anchor pairs
     LR = 0.01
 
-    def __init__(self, batch=512):
+    def __init__(self, batch=512, internal=False):
         self.B = batch
         self.units_per_step = batch
+        # internal: the reference's GradientType.Internal, the backward kernel applies W -= lr * dW in place (no dense
+        # gradient, no optimiser pass); default: dense gradients + torch.optim.SGD
+        self.internal = internal
         self.name = ("sparse LUT conv-net training step (3 ProjectionLUTLayers 32/64/128 tables per position, "
-                     f"Nc=8, 5x5 receptive, stride 2, 4x4 projection + LUT readout to 10), batch {batch}")
+                     f"Nc=8, 5x5 receptive, stride 2, 4x4 projection + LUT readout to 10), batch {batch}"
+                     + (", SGD update inside the backward kernel (Internal gradient policy)" if internal else ""))
 
     # ---- model
     def build(self, device):
         import torch
         import synth
-        from spiky_b200.lut_layer import (LUTLayer, ProjectionLUTLayer, SynapseMeta, PointSamplingPolicy,
-                                          PointSamplingType)
+        from spiky_b200.lut_layer import (GradientPolicy, GradientType, LUTLayer, ProjectionLUTLayer, SynapseMeta,
+                                          PointSamplingPolicy, PointSamplingType)
         meta = SynapseMeta(min_weight=-1.0, max_weight=1.0)
+        policy = GradientPolicy(GradientType.Internal if self.internal else GradientType.Dense)
         layers = []
         for li, (h, o, g, per) in enumerate(self.LAYERS):
             layer = ProjectionLUTLayer(
                 (h, h), (o, o), self.NC, g * g, per, (5, 5), (4, 4), synapse_meta=meta,
                 detectors_sampling_policy=PointSamplingPolicy(PointSamplingType.Grid, grid_h=g, grid_w=g, stride_h=2,
                                                               stride_w=2, pad_h=2, pad_w=2),
-                random_seed=100 + li)
+                weights_gradient_policy=policy, random_seed=100 + li)
             with torch.no_grad():
                 layer._weights.normal_(0.0, 0.02, generator=torch.Generator().manual_seed(200 + li))
             layers.append(layer)
         I, O, Nt, Nc = self.READOUT
-        readout = LUTLayer(I, Nc, Nt, O, synapse_meta=meta, random_seed=104)
+        readout = LUTLayer(I, Nc, Nt, O, synapse_meta=meta, weights_gradient_policy=policy, random_seed=104)
         with torch.no_grad():
             readout._weights.normal_(0.0, 0.02, generator=torch.Generator().manual_seed(204))
         layers.append(readout)
+        if self.internal:
+            for l in layers:
+                l.set_external_learning_rate_hook(lambda w: self.LR)
         if device is not None:
             for l in layers:
                 l.to(device=device)
@@ -294,7 +302,7 @@ class SparseConvNetWorkload:
         for l in self.layers:
             l.train()
         params = [l._weights for l in self.layers]
-        self.opt = torch.optim.SGD(params, lr=self.LR)
+        self.opt = None if self.internal else torch.optim.SGD(params, lr=self.LR)
         x, labels = self.host_inputs(1000 + rank, self.B)
         self.hx = torch.from_numpy(x).view(self.B, 1, 28, 28).pin_memory()
         self.hl = torch.from_numpy(labels).pin_memory()
@@ -309,14 +317,18 @@ class SparseConvNetWorkload:
     def _run(self, x, labels):
         import torch
         import torch.nn.functional as F
-        self.opt.zero_grad(set_to_none=True)
+        if self.opt is not None:
+            self.opt.zero_grad(set_to_none=True)
         z = x
         for l in self.layers[:-1]:
             z = l(z)
         logits = self.layers[-1](z.reshape(z.shape[0], 1, -1)).reshape(z.shape[0], -1)
         loss = F.cross_entropy(logits, labels)
         loss.backward()
-        if self.grad_sync is not None:
+        if self.internal:
+            if self.average_tables is not None:
+                self.average_tables()
+        elif self.grad_sync is not None:
             # plain SGD, applied per table as soon as its gradient exchange has finished
             with torch.no_grad():
                 for p in self.grad_sync.wait_each():
@@ -327,9 +339,10 @@ class SparseConvNetWorkload:
 
     allreduce = None
     grad_sync = None
+    average_tables = None  # data parallel + Internal policy: tables are averaged over the ranks after the step
 
     def trainable_parameters(self):
-        return self.grad_params
+        return [] if self.internal else self.grad_params
 
     def step_device(self):
         return self._run(self.dx, self.dl)
@@ -342,12 +355,12 @@ class SparseConvNetWorkload:
     dominant_kernel = None  # picked by measured time
     # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) per step of each kernel family, summed over its three
     # launches, from the ncu capture summarised in profiles/sparse_convnet_step_b512.md
-    ncu_dram_bytes_per_step = {"sparse_backward_fused": 928.2e6, "sparse_forward": 432.1e6, "check_detectors": 7.7e6}
+    ncu_dram_bytes_per_step = {"sparse_forward": 432.1e6, "check_detectors": 7.7e6}
 
     def algorithmic_bytes(self):
         """Per sample and kernel family, summed over the layers that launch it."""
         out = {k: 0 for k in ("check_detectors", "sparse_forward", "sparse_input_grad", "sparse_weight_grad",
-                              "sparse_backward_fused", "fc_gather_forward", "fc_input_grad", "fc_weight_grad")}
+                              "fc_gather_forward", "fc_input_grad", "fc_weight_grad")}
         for (h, o, g, per) in self.LAYERS:
             I, O, Nt = h * h, o * o, g * g * per
             sp = self._syn_per_sample.get((h, o), None)
@@ -355,8 +368,6 @@ class SparseConvNetWorkload:
             out["sparse_forward"] += 4 * Nt + 4 * sp[0] + 4 * sp[1] + 4 * O
             out["sparse_input_grad"] += 4 * O + 12 * Nt + 2 * 4 * sp[0] + 16 * Nt
             out["sparse_weight_grad"] += 4 * O + 4 * Nt + 2 * 4 * sp[0]
-            # fused input + table gradient: dY, idx / margins, rows S and S-bar, dX updates, dW row RMW
-            out["sparse_backward_fused"] += 4 * O + 12 * Nt + 2 * 4 * sp[0] + 16 * Nt + 2 * 4 * sp[0]
         I, O, Nt, Nc = self.READOUT
         out["check_detectors"] += 4 * I + 12 * Nt
         out["fc_gather_forward"] += 4 * Nt + 4 * Nt * O + 4 * O
@@ -821,6 +832,7 @@ WORKLOADS = {
     "large_transformer": lambda batch=None: LargeTransformerWorkload(**_b(batch)),
     "large_transformer_b4": lambda batch=None: LargeTransformerWorkload(batch=batch or 4),
     "sparse_convnet": lambda batch=None: SparseConvNetWorkload(**_b(batch)),
+    "sparse_convnet_internal": lambda batch=None: SparseConvNetWorkload(internal=True, **_b(batch)),
     "lut_layer": lambda batch=None: LutLayerWorkload(**_b(batch)),
     "lut_layer_b256": lambda batch=None: LutLayerWorkload(batch=batch or 256),
     "lut_layer_b256_graph": lambda batch=None: LutLayerWorkload(batch=batch or 256, graph=True),
@@ -903,6 +915,10 @@ def run_ours(args):
         sync = OverlappedGradientSync(wl.trainable_parameters(), average=True)
         wl.allreduce = lambda params: sync.wait()
         wl.grad_sync = sync
+        if getattr(wl, "internal", False):
+            from spiky_b200.data_parallel import average_internal_policy_weights
+            holder = torch.nn.ModuleList(wl.layers)
+            wl.average_tables = lambda: average_internal_policy_weights(holder)
     flush = None
     if wl.l2_note == "flushed":
         flush = torch.empty(2 * L2_BYTES, dtype=torch.uint8, device=device)

@@ -96,7 +96,8 @@ size_t lutb_nonseq_fc_backward_workspace(const lutb_layer_cfg *cfg, int64_t batc
 /*
  * Non-sequence, fully connected backward.  Replaces LUTDataManager::backward_backprop
  * (spiky_cuda/lut/lut.cu:1030-1088 -> LUTRuntimeContext::backward_backprop, lut_runtime.cu:213-397).
- *   dX  fp32 [batch * I] accumulated into.
+ *   dX  fp32 [batch * I] accumulated into; NULL (not possible in the reference, which always computes it) skips
+ *       the input-gradient kernels: for a first layer whose input needs no gradient.
  *   external_lr < 0: dW fp32 [Nt * 2^Nc * O] receives lr_meta * dY rows (accumulated into).
  *   external_lr >= 0: dW must be NULL and weights are updated in place by -external_lr * lr_meta * dY.
  */
@@ -172,7 +173,8 @@ int lutb_nonseq_sparse_forward(const lutb_layer_cfg *cfg, const lutb_sparse_inde
 /*
  * Non-sequence, sparse backward.  Replaces LUTDataManager::backward_backprop for sparse layers
  * (lut.cu:1030-1088 -> propagate_through_detectors_non_seq_sparse_logic, proto:1303-1419, and
- * gather_w_gradients_non_seq_sparse_logic, proto:1501-1545).  Arguments as lutb_nonseq_fc_backward.
+ * gather_w_gradients_non_seq_sparse_logic, proto:1501-1545).  Arguments as lutb_nonseq_fc_backward (dX may be
+ * NULL).  Runs as two passes over the (sample, detector chunk) pairs: input gradient, then table gradient.
  */
 int lutb_nonseq_sparse_backward(const lutb_layer_cfg *cfg, const lutb_sparse_index *sp, int64_t batch,
                                 float *weights, const float *dY, const int32_t *anchors, const int32_t *idx,

@@ -685,8 +685,8 @@ int launch_fc_backward(const lutb_layer_cfg *cfg, int64_t batch, float *W, const
     LUTB_REQUIRE(blocks <= 0x7FFFFFFF, LUTB_ERR_SHAPE, "batch too large for one launch");
     const int sm = device_info().sm_count;
 
-    // input gradient
-    {
+    // input gradient (dX == nullptr: the caller does not want it)
+    if (dX != nullptr) {
     KernelScope scope(K_FC_INPUT_GRAD, stream);
     if (int_mode) {
         const int64_t total = batch * Nt;
@@ -776,7 +776,7 @@ extern "C" int lutb_nonseq_fc_backward(const lutb_layer_cfg *cfg, int64_t batch,
         LUTB_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, LUTB_ERR_ALIGN, "workspace must be 256-byte aligned");
     }
     LUTB_REQUIRE(batch > 0, LUTB_ERR_SHAPE, "batch_size == 0");
-    LUTB_REQUIRE(weights && dY && anchors && idx && min_delta && min_k && dX, LUTB_ERR_NULL,
+    LUTB_REQUIRE(weights && dY && anchors && idx && min_delta && min_k, LUTB_ERR_NULL,
                  "a required tensor pointer is NULL");
     LUTB_REQUIRE(!(external_lr >= 0.0 && dW != nullptr), LUTB_ERR_MODE,
                  "in internal weight gradients mode w_weights_gradients should be nullptr");
@@ -794,7 +794,7 @@ extern "C" int lutb_nonseq_fc_backward(const lutb_layer_cfg *cfg, int64_t batch,
         if (rc) return rc;
     }
     if (cfg->int_mode) {
-        rc = launch_fixed_to_float(dX, batch * (int64_t)cfg->n_inputs, cfg->int_rescaler, st);
+        if (dX) rc = launch_fixed_to_float(dX, batch * (int64_t)cfg->n_inputs, cfg->int_rescaler, st);
         if (rc) return rc;
         if (dW) rc = launch_fixed_to_float(dW, (int64_t)cfg->n_detectors * (1 << cfg->n_anchors) * cfg->n_outputs, cfg->int_rescaler, st);
     }

@@ -298,7 +298,10 @@ class _LUTDataManager:
         self._require_cuda()
         dev = self._device
         _check_tensor(r_weights, "r_weights", True, dev)
-        _check_tensor(w_input_gradients, "w_input_gradients", True, dev)
+        # w_input_gradients=None (an extension of the reference's signature): the input gradient is not wanted, its
+        # kernels are skipped
+        if w_input_gradients is not None:
+            _check_tensor(w_input_gradients, "w_input_gradients", True, dev)
         _check_tensor(r_output_gradients, "r_output_gradients", True, dev)
         _check_tensor(r_detector_anchors, "r_detector_anchors", False, dev)
         _check_tensor(r_lookup_indices, "r_lookup_indices", False, dev)
@@ -312,7 +315,8 @@ class _LUTDataManager:
             raise ValueError("in internal weight gradients mode w_weights_gradients should be nullptr")
         B = int(batch_size)
         self._expect(r_output_gradients, B * self._n_outputs, "r_output_gradients")
-        self._expect(w_input_gradients, B * self._n_inputs, "w_input_gradients")
+        if w_input_gradients is not None:
+            self._expect(w_input_gradients, B * self._n_inputs, "w_input_gradients")
         self._expect(r_lookup_indices, B * self._n_detectors, "r_lookup_indices")
         if w_weights_gradients is not None and w_weights_gradients.numel() < self.get_weights_dimension():
             raise ValueError("w_weights_gradients is smaller than the weights")

@@ -148,7 +148,7 @@ class _LUTFunction(torch.autograd.Function):
         layer = ctx.layer
         if ctx.mode == "nonseq":
             x, idx, md, mk = ctx.saved_tensors
-            dx, dw = layer.backward_step(x, grad_output, idx, md, mk)
+            dx, dw = layer.backward_step(x, grad_output, idx, md, mk, need_input_grad=ctx.needs_input_grad[0])
             return dx, dw, None, None
         if ctx.mode == "concat":
             saved = list(ctx.saved_tensors)
@@ -478,7 +478,11 @@ class LUTLayerBasic(nn.Module):
             w_grad /= w_grad.abs().max().clip(1e-16)
         return w_grad
 
-    def backward_step(self, x, grad_output, lookup_indices, min_anchor_deltas, min_anchor_delta_indices, x_grad=None):
+    def backward_step(self, x, grad_output, lookup_indices, min_anchor_deltas, min_anchor_delta_indices, x_grad=None,
+                      need_input_grad=True):
+        """need_input_grad=False (not in the reference, which always computes it): the input-gradient kernels are
+        skipped and None is returned in its place; autograd asks for this when the layer's input needs no gradient
+        (the first layer of a network fed with data)."""
         assert self._sequence_length == 1
         x = self._check_input(x, 1)
         B = x.shape[0]
@@ -487,16 +491,16 @@ class LUTLayerBasic(nn.Module):
         assert min_anchor_delta_indices.shape == shape
         assert grad_output.shape == (B, 1) + tuple(self.output_shape())
         external = x_grad is not None
-        if not external:
+        if not external and need_input_grad:
             x_grad = torch.zeros(x.numel(), dtype=torch.float32, device=self.device)
         w_grad = self._weight_grad_target()
         self._lut_dm.backward_backprop(
             self._weights.detach(), B, grad_output.contiguous().view(-1), self._detector_anchors,
             lookup_indices.reshape(-1), min_anchor_deltas.reshape(-1), min_anchor_delta_indices.reshape(-1),
-            x_grad.view(-1), self._external_lr(), w_grad, None, dw_variant=self._dw_variant)
+            None if x_grad is None else x_grad.view(-1), self._external_lr(), w_grad, None, dw_variant=self._dw_variant)
         if not external:
             w_grad = self._process_gradients(w_grad, B)
-            return x_grad.view(x.shape), w_grad
+            return (None if x_grad is None else x_grad.view(x.shape)), w_grad
         return (w_grad,)
 
     # ------------------------------------------------------------------ runtime: sequence layers

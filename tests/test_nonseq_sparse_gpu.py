@@ -133,3 +133,40 @@ def test_chunk_shapes_match_oracle(per_group, projection, batch):
     y, idx, md, mk = orc.nonseq_sparse_forward(W, x, anchors, sp, 5, 12 * 12)
     dX, dW = orc.nonseq_sparse_backward(W, dY, anchors, idx, md, mk, sp, 14 * 14, 5)
     compare(got, dict(y=y, y_eval=y, idx=idx, min_delta=md, min_k=mk, dX=dX, dW=dW), False)
+
+
+@pytest.mark.parametrize("kind", ["sparse", "fc", "sparse_int"])
+def test_input_gradient_is_skipped_when_not_needed(kind):
+    """A layer whose input needs no gradient (first layer of a network) skips the input-gradient kernels: the table
+    gradient is unchanged, autograd returns no gradient for the input."""
+    from spiky_b200.lut_layer import LUTLayer, ProjectionLUTLayer, SynapseMeta
+
+    meta = SynapseMeta(min_weight=-1.0, max_weight=1.0, initial_noise_level=0.2, initial_weight=-0.1)
+    if kind == "fc":
+        layer = LUTLayer(64, 5, 12, 16, synapse_meta=meta, random_seed=2, device="cuda:0")
+        x = torch.rand(9, 1, 64, device="cuda:0")
+    else:
+        layer = ProjectionLUTLayer((16, 16), (12, 12), 4, 10, 4, (5, 5), (3, 3), synapse_meta=meta, random_seed=2,
+                                   summation_dtype=torch.int32 if kind == "sparse_int" else torch.float32,
+                                   _int_rescaler=0.01, device="cuda:0")
+        x = torch.rand(9, 1, 16, 16, device="cuda:0")
+    layer.train()
+    y, idx, md, mk = layer.forward_step(x)
+    dY = torch.randn_like(y)
+    dx, dw = layer.backward_step(x, dY, idx, md, mk)
+    none, dw2 = layer.backward_step(x, dY, idx, md, mk, need_input_grad=False)
+    assert none is None and dx is not None and dx.abs().sum() > 0
+    if kind == "sparse_int":
+        assert torch.equal(dw, dw2)
+    else:
+        golden_util.assert_close(dw2.cpu().numpy(), dw.cpu().numpy(), 1e-6, "dW")
+    # through autograd: input without requires_grad
+    layer.zero_grad()
+    out = layer(x)
+    (out * dY).sum().backward()
+    assert x.grad is None
+    golden_util.assert_close(layer._weights.grad.cpu().numpy(), dw.cpu().numpy(), 1e-6, "dW via autograd")
+    xg = x.clone().requires_grad_(True)
+    layer.zero_grad()
+    (layer(xg) * dY).sum().backward()
+    golden_util.assert_close(xg.grad.cpu().numpy(), dx.cpu().numpy(), 1e-6, "dX via autograd")
