@@ -355,18 +355,20 @@ class SparseConvNetWorkload:
     dominant_kernel = None  # picked by measured time
     # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) per step of each kernel family, summed over its three
     # launches, from the ncu capture summarised in profiles/sparse_convnet_step_b512.md
-    ncu_dram_bytes_per_step = {"sparse_forward": 432.1e6, "check_detectors": 7.7e6}
+    ncu_dram_bytes_per_step = {"sparse_forward": 430.7e6, "sparse_input_grad": 412.9e6, "sparse_weight_grad": 429.0e6,
+                               "check_detectors": 7.7e6}
 
     def algorithmic_bytes(self):
         """Per sample and kernel family, summed over the layers that launch it."""
         out = {k: 0 for k in ("check_detectors", "sparse_forward", "sparse_input_grad", "sparse_weight_grad",
                               "fc_gather_forward", "fc_input_grad", "fc_weight_grad")}
-        for (h, o, g, per) in self.LAYERS:
+        for li, (h, o, g, per) in enumerate(self.LAYERS):
             I, O, Nt = h * h, o * o, g * g * per
             sp = self._syn_per_sample.get((h, o), None)
             out["check_detectors"] += 4 * I + 12 * Nt
             out["sparse_forward"] += 4 * Nt + 4 * sp[0] + 4 * sp[1] + 4 * O
-            out["sparse_input_grad"] += 4 * O + 12 * Nt + 2 * 4 * sp[0] + 16 * Nt
+            if li > 0:  # the first layer's input is data: autograd asks for no input gradient, the pass is skipped
+                out["sparse_input_grad"] += 4 * O + 12 * Nt + 2 * 4 * sp[0] + 16 * Nt
             out["sparse_weight_grad"] += 4 * O + 4 * Nt + 2 * 4 * sp[0]
         I, O, Nt, Nc = self.READOUT
         out["check_detectors"] += 4 * I + 12 * Nt
