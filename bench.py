@@ -249,15 +249,21 @@ class SparseConvNetWorkload:
     READOUT = (256, 10, 64, 8)  # inputs, outputs, tables, anchor pairs
     LR = 0.01
 
-    def __init__(self, batch=512, internal=False):
+    def __init__(self, batch=512, internal=False, sharded=False):
         self.B = batch
         self.units_per_step = batch
+        # sharded: data parallelism without dense gradient exchange for the three sparse layers: ranks all-gather
+        # (table index, output gradient) pairs, update their share of the detectors in place for the whole batch
+        # and all-gather the updated tables (spiky_b200.data_parallel.ShardedTableUpdate); the readout layer keeps
+        # all-reduce + SGD
+        self.sharded = sharded
         # internal: the reference's GradientType.Internal, the backward kernel applies W -= lr * dW in place (no dense
         # gradient, no optimiser pass); default: dense gradients + torch.optim.SGD
         self.internal = internal
         self.name = ("sparse LUT conv-net training step (3 ProjectionLUTLayers 32/64/128 tables per position, "
                      f"Nc=8, 5x5 receptive, stride 2, 4x4 projection + LUT readout to 10), batch {batch}"
-                     + (", SGD update inside the backward kernel (Internal gradient policy)" if internal else ""))
+                     + (", SGD update inside the backward kernel (Internal gradient policy)" if internal else "")
+                     + (", sharded in-place table update" if sharded else ""))
 
     # ---- model
     def build(self, device):
@@ -302,6 +308,10 @@ class SparseConvNetWorkload:
         for l in self.layers:
             l.train()
         params = [l._weights for l in self.layers]
+        if self.sharded:
+            from spiky_b200.data_parallel import ShardedTableUpdate
+            self.sharded_sync = ShardedTableUpdate(self.layers[:-1], self.LR)
+            params = params[-1:]
         self.opt = None if self.internal else torch.optim.SGD(params, lr=self.LR)
         x, labels = self.host_inputs(1000 + rank, self.B)
         self.hx = torch.from_numpy(x).view(self.B, 1, 28, 28).pin_memory()
@@ -319,6 +329,8 @@ class SparseConvNetWorkload:
         import torch.nn.functional as F
         if self.opt is not None:
             self.opt.zero_grad(set_to_none=True)
+        if self.sharded:
+            self.sharded_sync.wait()  # the tables updated by the previous step have arrived
         z = x
         for l in self.layers[:-1]:
             z = l(z)
@@ -835,6 +847,7 @@ WORKLOADS = {
     "large_transformer_b4": lambda batch=None: LargeTransformerWorkload(batch=batch or 4),
     "sparse_convnet": lambda batch=None: SparseConvNetWorkload(**_b(batch)),
     "sparse_convnet_internal": lambda batch=None: SparseConvNetWorkload(internal=True, **_b(batch)),
+    "sparse_convnet_sharded": lambda batch=None: SparseConvNetWorkload(sharded=True, **_b(batch)),
     "lut_layer": lambda batch=None: LutLayerWorkload(**_b(batch)),
     "lut_layer_b256": lambda batch=None: LutLayerWorkload(batch=batch or 256),
     "lut_layer_b256_graph": lambda batch=None: LutLayerWorkload(batch=batch or 256, graph=True),

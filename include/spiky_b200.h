@@ -175,11 +175,30 @@ int lutb_nonseq_sparse_forward(const lutb_layer_cfg *cfg, const lutb_sparse_inde
  * (lut.cu:1030-1088 -> propagate_through_detectors_non_seq_sparse_logic, proto:1303-1419, and
  * gather_w_gradients_non_seq_sparse_logic, proto:1501-1545).  Arguments as lutb_nonseq_fc_backward (dX may be
  * NULL).  Runs as two passes over the (sample, detector chunk) pairs: input gradient, then table gradient.
+ * external_lr == LUTB_SKIP_TABLE_GRADIENT (dW must be NULL): only the input gradient; the caller makes the table
+ * update itself with lutb_nonseq_sparse_table_grad.
  */
+#define LUTB_SKIP_TABLE_GRADIENT (-2.0)
 int lutb_nonseq_sparse_backward(const lutb_layer_cfg *cfg, const lutb_sparse_index *sp, int64_t batch,
                                 float *weights, const float *dY, const int32_t *anchors, const int32_t *idx,
                                 const float *min_delta, const int32_t *min_k, float *dX, float *dW,
                                 double external_lr, void *stream);
+
+/*
+ * Table-gradient pass of a sparse non-sequence layer alone, over the detector chunks [chunk_begin, chunk_end) of
+ * the index (lutb_sparse_index::chunk_info rows; a chunk is a run of up to 32 detectors with one target list):
+ *   target[row(t, idx[b, t]) + p] += scale * cfg->lr_meta * dY[b, target(p)]   for |dY| > 1e-17,
+ * the arithmetic of gather_w_gradients_non_seq_sparse_logic (lut_runtime_kernels_logic.proto:1501-1545).  target is
+ * a dense gradient (scale 1) or the weights themselves (scale = -learning rate: in-place SGD).  No counterpart in
+ * the single-process reference: it serves data-parallel ranks that each own a share of the detectors, gather
+ * (idx, dY) of the whole batch - idx_bytes = 1 or 2 lets the indices travel as uint8 / uint16 when the tables have
+ * at most 256 / 65536 rows - and update their share for all samples, instead of all-reducing dense gradients.
+ *   idx  [batch * Nt] of idx_bytes-wide unsigned (4: int32) table indices; dY fp32 [batch * O].
+ * fp32 accumulators only; rows of at most 32 synapses.
+ */
+int lutb_nonseq_sparse_table_grad(const lutb_layer_cfg *cfg, const lutb_sparse_index *sp, int64_t batch,
+                                  const float *dY, const void *idx, int idx_bytes, float *target, double scale,
+                                  int64_t chunk_begin, int64_t chunk_end, void *stream);
 
 /*
  * Product-mode sequence layer, forward.  Replaces LUTDataManager::forward_step_product

@@ -11,6 +11,7 @@ LIB_PATH = os.path.join(_HERE, "lib", "libspiky_b200.so")
 
 # dW kernel variants (include/spiky_b200.h)
 DW_AUTO, DW_ATOMIC, DW_SMEM, DW_SORTED = 0, 1, 2, 3
+SKIP_TABLE_GRADIENT = -2.0  # external_lr value: input gradient only (lutb_nonseq_sparse_backward)
 # product-mode kernel variants (include/spiky_b200.h)
 PRODUCT_AUTO, PRODUCT_DIRECT, PRODUCT_HIST = 0, 1, 2
 # de-quantisation rules of the int8 inference path (include/spiky_b200.h)
@@ -94,6 +95,7 @@ SIGNATURES = {
     "lutb_dense_to_sparse_32": (_int, [_vp, _i64, _vp, _vp, _i64, _vp, _int, _vp, _size, _vp]),
     "lutb_nonseq_sparse_forward": (_int, [_cfgp, _spp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "lutb_nonseq_sparse_backward": (_int, [_cfgp, _spp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _dbl, _vp]),
+    "lutb_nonseq_sparse_table_grad": (_int, [_cfgp, _spp, _i64, _vp, _vp, _int, _vp, _dbl, _i64, _i64, _vp]),
 }
 
 _lib = None

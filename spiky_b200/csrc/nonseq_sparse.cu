@@ -297,6 +297,66 @@ __global__ void __launch_bounds__(256, 4) sparse_backward_kernel(SparseView sp, 
         chunk_backward<32, DO_DX, DO_DW, INT_DW>(sp, cs, W, dY, anchors, idx, min_delta, min_k, dX, target_arr, b0, b1, n_inputs, n_outputs, n_detectors, n_anchors, lane, lr, fixed_scale);
 }
 
+// --------------------------------------------------------------------------------------------
+// Table gradient alone over a range of chunks, table indices of 1, 2 or 4 bytes.  For data-parallel ranks
+// that own a share of the detectors: every rank gathers the (index, output gradient) pairs of the whole
+// batch - one byte per (sample, detector) for 256-row tables, against a dense gradient as large as the
+// tables - and applies the update of all samples to its own share.  Same reductions as the DO_DW pass of
+// chunk_backward.
+// --------------------------------------------------------------------------------------------
+template <int LG, typename IdxT>
+__device__ __forceinline__ void chunk_table_grad(const SparseView &sp, const ChunkStatic &cs,
+                                                 const float *__restrict__ dY, const IdxT *__restrict__ idx,
+                                                 float *__restrict__ target_arr, int64_t b0, int64_t b1,
+                                                 int n_outputs, int n_detectors, int lane, double lr) {
+    constexpr int NG = 32 / LG;
+    const int g = lane / LG, j = lane - g * LG;
+    const bool valid = j < cs.P;
+    const bool has_det = lane < cs.ndet;
+    const int my_target = valid ? __ldg(sp.syn_target + cs.toff + j) : 0;
+    float *Tb = target_arr + cs.wbase0 + j + hole_offset(j, sp);
+    const int64_t det_l = cs.det0 + lane;
+    int32_t li_n = has_det ? (int32_t)__ldg(idx + b0 * n_detectors + det_l) : 0;
+    float gp_n = valid ? __ldg(dY + b0 * n_outputs + my_target) : 0.f;
+    for (int64_t b = b0; b < b1; b++) {
+        const int32_t li = li_n;
+        const float gp = gp_n;
+        if (b + 1 < b1) {
+            if (has_det) li_n = (int32_t)__ldg(idx + (b + 1) * n_detectors + det_l);
+            if (valid) gp_n = __ldg(dY + (b + 1) * n_outputs + my_target);
+        }
+        const int32_t row_off = has_det ? lane * cs.table + li * cs.stride : 0;
+        const bool active = valid && fabsf(gp) > kEpsF;
+        const float val = lr == 1.0 ? gp : (float)((double)gp * lr);
+        // every lane takes part in the offset broadcasts; only the reductions are predicated
+#pragma unroll
+        for (int i = 0; i < LG; i++) {
+            const int d = i * NG + g;
+            const int32_t ro = __shfl_sync(0xffffffffu, row_off, d);
+            if (active && d < cs.ndet) atomicAdd(Tb + ro, val);
+        }
+    }
+}
+
+template <typename IdxT>
+__global__ void __launch_bounds__(256, 4) sparse_table_grad_range_kernel(SparseView sp, const float *__restrict__ dY,
+                                                                     const IdxT *__restrict__ idx,
+                                                                     float *__restrict__ target_arr, int64_t batch,
+                                                                     int n_outputs, int n_detectors, double lr,
+                                                                     int64_t chunk_begin, int64_t n_range) {
+    const int lane = threadIdx.x & 31;
+    const int64_t runs = (batch + kSampleRun - 1) / kSampleRun;
+    const int64_t work = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (work >= runs * n_range) return;
+    const int64_t c = work / runs;
+    const int64_t b0 = (work - c * runs) * kSampleRun;
+    const int64_t b1 = min(batch, b0 + kSampleRun);
+    const ChunkStatic cs = load_chunk(sp, chunk_begin + c);
+    if (cs.P <= 8) chunk_table_grad<8, IdxT>(sp, cs, dY, idx, target_arr, b0, b1, n_outputs, n_detectors, lane, lr);
+    else if (cs.P <= 16) chunk_table_grad<16, IdxT>(sp, cs, dY, idx, target_arr, b0, b1, n_outputs, n_detectors, lane, lr);
+    else chunk_table_grad<32, IdxT>(sp, cs, dY, idx, target_arr, b0, b1, n_outputs, n_detectors, lane, lr);
+}
+
 // Generic fp32 backward for rows longer than 32 synapses: one warp per (sample, detector).
 template <bool DO_DX, bool DO_DW, bool INT_DW>
 __global__ void __launch_bounds__(256) sparse_backward_long_kernel(SparseView sp, const float *__restrict__ W,
@@ -464,7 +524,9 @@ extern "C" int lutb_nonseq_sparse_backward(const lutb_layer_cfg *cfg, const lutb
                  "a required tensor pointer is NULL");
     LUTB_REQUIRE(!(external_lr >= 0.0 && dW != nullptr), LUTB_ERR_MODE,
                  "in internal weight gradients mode w_weights_gradients should be nullptr");
-    LUTB_REQUIRE(!(external_lr < 0.0 && dW == nullptr), LUTB_ERR_NULL, "w_weights_gradients is NULL");
+    const bool skip_table = external_lr == LUTB_SKIP_TABLE_GRADIENT;
+    LUTB_REQUIRE(!(skip_table && dW != nullptr), LUTB_ERR_MODE, "no table gradient asked for, w_weights_gradients should be nullptr");
+    LUTB_REQUIRE(!(external_lr < 0.0 && dW == nullptr && !skip_table), LUTB_ERR_NULL, "w_weights_gradients is NULL");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int sm = device_info().sm_count;
     SparseView v = make_view(sp);
@@ -501,7 +563,7 @@ extern "C" int lutb_nonseq_sparse_backward(const lutb_layer_cfg *cfg, const lutb
         }
         LUTB_LAUNCH_CHECK();
     }
-    {
+    if (!skip_table) {
         KernelScope scope(K_SPARSE_WEIGHT_GRAD, st);
         if (cfg->int_mode) LUTB_SPARSE_BWD(false, true, true);
         else LUTB_SPARSE_BWD(false, true, false);
@@ -514,4 +576,42 @@ extern "C" int lutb_nonseq_sparse_backward(const lutb_layer_cfg *cfg, const lutb
         if (dW) rc = launch_fixed_to_float(dW, sp->n_weights, cfg->int_rescaler, st);
     }
     return rc;
+}
+
+extern "C" int lutb_nonseq_sparse_table_grad(const lutb_layer_cfg *cfg, const lutb_sparse_index *sp, int64_t batch,
+                                             const float *dY, const void *idx, int idx_bytes, float *target,
+                                             double scale, int64_t chunk_begin, int64_t chunk_end, void *stream) {
+    int rc = validate_cfg(cfg);
+    if (rc) return rc;
+    rc = validate_sparse(sp);
+    if (rc) return rc;
+    LUTB_REQUIRE(cfg->seq_len == 1, LUTB_ERR_MODE, "the table-gradient pass is for sequence_length == 1");
+    LUTB_REQUIRE(cfg->int_mode == 0, LUTB_ERR_MODE, "the ranged table-gradient pass needs fp32 accumulators");
+    LUTB_REQUIRE(sp->max_count <= 32, LUTB_ERR_MODE, "the ranged table-gradient pass supports rows of at most 32 synapses");
+    LUTB_REQUIRE(batch > 0 && batch <= 0x7FFFFFFF, LUTB_ERR_SHAPE, "batch_size == 0 or too large");
+    LUTB_REQUIRE(dY && idx && target, LUTB_ERR_NULL, "a required tensor pointer is NULL");
+    LUTB_REQUIRE(idx_bytes == 1 || idx_bytes == 2 || idx_bytes == 4, LUTB_ERR_MODE, "idx_bytes must be 1, 2 or 4");
+    LUTB_REQUIRE(idx_bytes == 4 || cfg->n_anchors <= 8 * idx_bytes, LUTB_ERR_MODE,
+                 "table indices of 2^%d rows do not fit %d byte(s)", cfg->n_anchors, idx_bytes);
+    LUTB_REQUIRE(chunk_begin >= 0 && chunk_begin <= chunk_end && chunk_end <= sp->n_chunks, LUTB_ERR_SHAPE,
+                 "chunk range [%lld, %lld) outside [0, %lld)", (long long)chunk_begin, (long long)chunk_end,
+                 (long long)sp->n_chunks);
+    if (chunk_begin == chunk_end) return LUTB_OK;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    SparseView v = make_view(sp);
+    const int64_t n_range = chunk_end - chunk_begin;
+    unsigned blocks;
+    rc = chunk_grid(((batch + kSampleRun - 1) / kSampleRun) * n_range, &blocks);
+    if (rc) return rc;
+    const double lr = cfg->lr_meta * scale;
+    const int O = cfg->n_outputs, Nt = cfg->n_detectors;
+    KernelScope scope(K_SPARSE_WEIGHT_GRAD, st);
+    if (idx_bytes == 1)
+        sparse_table_grad_range_kernel<uint8_t><<<blocks, 256, 0, st>>>(v, dY, static_cast<const uint8_t *>(idx), target, batch, O, Nt, lr, chunk_begin, n_range);
+    else if (idx_bytes == 2)
+        sparse_table_grad_range_kernel<uint16_t><<<blocks, 256, 0, st>>>(v, dY, static_cast<const uint16_t *>(idx), target, batch, O, Nt, lr, chunk_begin, n_range);
+    else
+        sparse_table_grad_range_kernel<int32_t><<<blocks, 256, 0, st>>>(v, dY, static_cast<const int32_t *>(idx), target, batch, O, Nt, lr, chunk_begin, n_range);
+    LUTB_LAUNCH_CHECK();
+    return LUTB_OK;
 }

@@ -313,6 +313,8 @@ class _LUTDataManager:
             raise ValueError("backward_backprop should only be called when sequence_length == 1")
         if external_lr >= 0.0 and w_weights_gradients is not None:
             raise ValueError("in internal weight gradients mode w_weights_gradients should be nullptr")
+        if external_lr == _native.SKIP_TABLE_GRADIENT and self._fully_connected:
+            raise ValueError("skipping the table gradient is only available for sparse lookup connectivity")
         B = int(batch_size)
         self._expect(r_output_gradients, B * self._n_outputs, "r_output_gradients")
         if w_input_gradients is not None:
@@ -338,6 +340,37 @@ class _LUTDataManager:
                 rc = self._sparse_backward(L, cfg, B, r_weights, r_output_gradients, r_detector_anchors,
                                            r_lookup_indices, r_min_anchor_deltas, r_min_anchor_delta_indices,
                                            w_input_gradients, external_lr, w_weights_gradients)
+        _native.check(rc)
+
+    def table_gradient(self, batch_size, r_output_gradients, r_lookup_indices, w_target, scale, chunk_begin=0,
+                       chunk_end=None):
+        """Table-gradient pass alone (sparse layers, fp32) over the detector chunks [chunk_begin, chunk_end):
+        ``w_target[row(t, idx[b, t]) + p] += scale * lr_meta * dY[b, target(p)]``.  ``w_target`` is a dense gradient
+        or the weights themselves (``scale = -learning_rate``); ``r_lookup_indices`` may be uint8 / int16 / int32.
+        Not part of the reference's class: used by the data-parallel sharded table update."""
+        self._require_cuda()
+        dev = self._device
+        if self._fully_connected or self._sparse is None:
+            raise ValueError("table_gradient needs a layer with sparse lookup connectivity")
+        _check_tensor(r_output_gradients, "r_output_gradients", True, dev)
+        _check_tensor(w_target, "w_target", True, dev)
+        idx = r_lookup_indices
+        if not (isinstance(idx, torch.Tensor) and idx.is_contiguous() and idx.dim() == 1 and idx.device.type == "cuda"
+                and idx.device.index == dev and idx.dtype in (torch.uint8, torch.int16, torch.int32)):
+            raise RuntimeError("r_lookup_indices must be a flat contiguous uint8 / int16 / int32 tensor on the layer's device")
+        B = int(batch_size)
+        self._expect(r_output_gradients, B * self._n_outputs, "r_output_gradients")
+        self._expect(idx, B * self._n_detectors, "r_lookup_indices")
+        if w_target.numel() < self.get_weights_dimension():
+            raise ValueError("w_target is smaller than the weights")
+        if chunk_end is None:
+            chunk_end = self._sparse.n_chunks
+        cfg = self._cfg()
+        sp = self._sparse.c_struct()
+        with torch.cuda.device(dev):
+            rc = _native.lib().lutb_nonseq_sparse_table_grad(
+                ctypes.byref(cfg), ctypes.byref(sp), B, _ptr(r_output_gradients), _ptr(idx), idx.element_size(),
+                _ptr(w_target), float(scale), int(chunk_begin), int(chunk_end), self._stream())
         _native.check(rc)
 
     # ------------------------------------------------------------------ product-mode sequence runtime

@@ -493,6 +493,19 @@ class LUTLayerBasic(nn.Module):
         external = x_grad is not None
         if not external and need_input_grad:
             x_grad = torch.zeros(x.numel(), dtype=torch.float32, device=self.device)
+        hook = getattr(self, "_table_update_hook", None)
+        if hook is not None and not external:
+            # data-parallel sharded table update: only the input gradient is computed here; the hook gathers the
+            # (index, output gradient) pairs of all ranks and updates this rank's share of the tables in place
+            from ._native import SKIP_TABLE_GRADIENT
+            grad_flat = grad_output.contiguous().view(-1)
+            if x_grad is not None:
+                self._lut_dm.backward_backprop(
+                    self._weights.detach(), B, grad_flat, self._detector_anchors, lookup_indices.reshape(-1),
+                    min_anchor_deltas.reshape(-1), min_anchor_delta_indices.reshape(-1), x_grad.view(-1),
+                    SKIP_TABLE_GRADIENT, None, None)
+            hook(self, lookup_indices.reshape(-1), grad_flat, B)
+            return (None if x_grad is None else x_grad.view(x.shape)), None
         w_grad = self._weight_grad_target()
         self._lut_dm.backward_backprop(
             self._weights.detach(), B, grad_output.contiguous().view(-1), self._detector_anchors,

@@ -339,6 +339,27 @@ class SparseIndex:
         target = self.syn_target.to(torch.int64)[self.det_sstart.to(torch.int64)[d] + p]
         return ids[which], slot, target
 
+    def chunk_weight_bounds(self):
+        """int64 [n_chunks + 1]: chunk c's tables occupy the weight slots [bounds[c], bounds[c + 1]); the ranges are
+        contiguous, disjoint and cover every synapse slot (the last one ends at n_weights)."""
+        info = self.chunk_info.cpu().to(torch.int64)
+        low = torch.where(info[:, 6] < 0, info[:, 6] + (1 << 32), info[:, 6])
+        start = (info[:, 7] << 32) | low
+        return torch.cat([start, torch.tensor([self.n_weights], dtype=torch.int64)])
+
+    def shard_chunks(self, world):
+        """Splits the chunks into ``world`` consecutive ranges of about equal table size; returns the world + 1
+        chunk boundaries (a range may be empty when there are fewer chunks than ranks)."""
+        bounds = self.chunk_weight_bounds()
+        total = int(bounds[-1] - bounds[0])
+        cuts = [0]
+        for r in range(1, world):
+            want = int(bounds[0]) + (total * r) // world
+            c = int(torch.searchsorted(bounds, torch.tensor(want), right=False))
+            cuts.append(min(max(c, cuts[-1]), self.n_chunks))
+        cuts.append(self.n_chunks)
+        return cuts
+
     def initial_weights(self, synapse_meta, seed=None):
         """fp32 [n_weights]: noise * U[0,1) + initial weight, clipped to the meta's range; holes are zero."""
         gen = None

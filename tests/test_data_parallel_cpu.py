@@ -191,3 +191,72 @@ def _sparse_worker(rank, world, port, result_dir):
 def test_sparse_gradient_exchange_and_internal_policy_average(tmp_path):
     mp.spawn(_sparse_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
     assert open(tmp_path / "ok3").read() == "True"
+
+
+def _sharded_worker(rank, world, port, result_dir, weight_gather):
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests", "golden"))
+    import datetime
+    import synth
+    from oracle import lut_oracle as orc
+    from spiky_b200.data_parallel import ShardedTableUpdate, shard_batch
+    from spiky_b200.lut_layer import ProjectionLUTLayer, SynapseMeta
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=30))
+    try:
+        meta = SynapseMeta(min_weight=-1.0, max_weight=1.0, initial_noise_level=0.2, initial_weight=-0.1)
+        layer = ProjectionLUTLayer((16, 16), (12, 12), 4, 10, 4, (5, 5), (3, 3), synapse_meta=meta, random_seed=2,
+                                   device=None)
+        index = layer._lut_dm._sparse
+        sp = dict(index.numpy(), group_size=index.group_size)
+        anchors = layer._detector_anchors.numpy()
+        W0 = layer._weights.detach().numpy().copy()
+        B, I, O, Nc, lr = 10, 256, 144, 4, 0.05
+        x = synth.sparse_images(41, (B, I))
+        dY = synth.normal(42, (B, O))
+        _, idx, md, mk = orc.nonseq_sparse_forward(W0, x, anchors, sp, Nc, O)
+        _, dW_global = orc.nonseq_sparse_backward(W0, dY, anchors, idx, md, mk, sp, I, Nc)
+
+        sync = ShardedTableUpdate([layer], lr, weight_gather=weight_gather)
+        plan = sync._plans[id(layer)]
+        calls = []
+
+        def apply_with_oracle(layer_, batch, dY_all, idx_all, scale, c0, c1):
+            # the kernel's arithmetic on the gathered batch, restricted to this rank's share of the weight slots
+            assert idx_all.dtype == torch.uint8 and batch == B
+            idx_np = idx_all.numpy().astype(np.int32).reshape(batch, -1)
+            dY_np = dY_all.numpy().reshape(batch, O)
+            w = layer_._weights.detach().numpy()
+            zeros = np.zeros_like(idx_np)
+            _, dW = orc.nonseq_sparse_backward(w, dY_np, anchors, idx_np, zeros.astype(np.float32) + 1.0, zeros, sp, I, Nc)
+            lo, hi = plan["wcuts"][plan["cuts"].index(c0)], plan["wcuts"][plan["cuts"].index(c0) + 1]
+            calls.append((c0, c1, lo, hi))
+            with torch.no_grad():
+                layer_._weights[lo:hi] += scale * torch.from_numpy(dW[lo:hi])
+
+        sync._apply = apply_with_oracle
+        b0, b1 = shard_batch(B, rank, world)
+        sync._on_backward(layer, torch.from_numpy(idx[b0:b1].reshape(-1).copy()),
+                          torch.from_numpy(dY[b0:b1].reshape(-1).copy()), b1 - b0)
+        sync.wait()
+        got = layer._weights.detach().numpy()
+        want = W0 - (lr / world) * dW_global
+        err = float(np.abs(got - want).max())
+        ok = err <= 1e-6 * max(float(np.abs(want).max()), 1e-30) and len(calls) == 1
+        ok = ok and calls[0][:2] == (plan["cuts"][rank], plan["cuts"][rank + 1]) and plan["cuts"][0] == 0
+        ok = ok and plan["wcuts"][-1] == index.n_weights and float(np.abs(got - W0).max()) > 0
+        flags = [torch.zeros(1) for _ in range(world)]
+        dist.all_gather(flags, torch.tensor([1.0 if ok else 0.0]))
+        if rank == 0:
+            open(os.path.join(result_dir, "ok4"), "w").write(f"{all(float(f) == 1.0 for f in flags)} {err}")
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("weight_gather", ["padded", "uneven"])
+def test_sharded_table_update_equals_global_batch_sgd(tmp_path, weight_gather):
+    mp.spawn(_sharded_worker, args=(2, _free_port(), str(tmp_path), weight_gather), nprocs=2, join=True)
+    ok, err = open(tmp_path / "ok4").read().split()
+    assert ok == "True", f"max abs error {err}"

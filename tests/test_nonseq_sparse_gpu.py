@@ -170,3 +170,71 @@ def test_input_gradient_is_skipped_when_not_needed(kind):
     layer.zero_grad()
     (layer(xg) * dY).sum().backward()
     golden_util.assert_close(xg.grad.cpu().numpy(), dx.cpu().numpy(), 1e-6, "dX via autograd")
+
+
+@pytest.mark.parametrize("idx_dtype", [torch.uint8, torch.int16, torch.int32])
+def test_ranged_table_gradient_matches_backward(idx_dtype):
+    """The table-gradient pass alone, run over two chunk ranges and fed with narrow table indices, reproduces the dense
+    table gradient of the full backward; the input-gradient-only call leaves the tables' gradient out."""
+    from spiky_b200 import _native
+    from spiky_b200.lut_layer import ProjectionLUTLayer, SynapseMeta
+
+    meta = SynapseMeta(learning_rate=0.5, min_weight=-1.0, max_weight=1.0, initial_noise_level=0.2, initial_weight=-0.1)
+    layer = ProjectionLUTLayer((16, 16), (12, 12), 5, 10, 40, (5, 5), (3, 3), synapse_meta=meta, random_seed=2,
+                               device="cuda:0")
+    layer.train()
+    B = 37
+    x = torch.rand(B, 1, 16, 16, device="cuda:0")
+    y, idx, md, mk = layer.forward_step(x)
+    dY = torch.randn_like(y)
+    dx, dw = layer.backward_step(x, dY, idx, md, mk)
+    dm, index = layer._lut_dm, layer._lut_dm._sparse
+    assert index.n_chunks >= 4
+    cut = index.n_chunks // 3
+    target = torch.zeros_like(dw)
+    narrow = idx.reshape(-1).to(idx_dtype)
+    flat = dY.contiguous().view(-1)
+    dm.table_gradient(B, flat, narrow, target, 1.0, 0, cut)
+    bounds = index.chunk_weight_bounds()
+    assert not target[int(bounds[cut]):].any() and target[:int(bounds[cut])].any()
+    dm.table_gradient(B, flat, narrow, target, 1.0, cut, index.n_chunks)
+    dm.table_gradient(B, flat, narrow, target, 1.0, cut, cut)  # empty range: nothing happens
+    golden_util.assert_close(target.cpu().numpy(), dw.cpu().numpy(), 1e-6, "dW from two ranges")
+    # input gradient only
+    dx2 = torch.zeros(x.numel(), device="cuda:0")
+    dm.backward_backprop(layer._weights.detach(), B, flat, layer._detector_anchors, idx.reshape(-1), md.reshape(-1),
+                         mk.reshape(-1), dx2, _native.SKIP_TABLE_GRADIENT, None, None)
+    golden_util.assert_close(dx2.cpu().numpy(), dx.reshape(-1).cpu().numpy(), 1e-6, "dX alone")
+    with pytest.raises(ValueError):
+        dm.table_gradient(B, flat, narrow, target, 1.0, 0, index.n_chunks + 1)
+
+
+def test_sharded_table_update_on_one_rank_equals_in_place_sgd():
+    """Without a process group the sharded update degenerates to in-place SGD on all chunks: same tables afterwards
+    as the Internal gradient policy, and no gradient on the parameter."""
+    from spiky_b200.data_parallel import ShardedTableUpdate
+    from spiky_b200.lut_layer import GradientPolicy, GradientType, ProjectionLUTLayer, SynapseMeta
+
+    meta = SynapseMeta(min_weight=-1.0, max_weight=1.0, initial_noise_level=0.2, initial_weight=-0.1)
+    kw = dict(synapse_meta=meta, random_seed=2, device="cuda:0")
+    a = ProjectionLUTLayer((16, 16), (12, 12), 4, 10, 4, (5, 5), (3, 3), **kw)
+    b = ProjectionLUTLayer((16, 16), (12, 12), 4, 10, 4, (5, 5), (3, 3),
+                           weights_gradient_policy=GradientPolicy(GradientType.Internal), **kw)
+    assert torch.equal(a._weights, b._weights) and torch.equal(a._detector_anchors, b._detector_anchors)
+    b.set_external_learning_rate_hook(lambda w: 0.05)
+    sync = ShardedTableUpdate([a], 0.05)
+    x = torch.rand(12, 1, 16, 16, device="cuda:0", requires_grad=True)
+    g = torch.randn(12, 1, 12, 12, device="cuda:0")
+    grads = []
+    for layer in (a, b):
+        layer.train()
+        xin = x.detach().clone().requires_grad_(True)
+        (layer(xin) * g).sum().backward()
+        grads.append(xin.grad)
+    sync.wait()
+    torch.cuda.synchronize()
+    assert a._weights.grad is None
+    golden_util.assert_close(grads[0].cpu().numpy(), grads[1].cpu().numpy(), 1e-6, "dX")
+    golden_util.assert_close(a._weights.detach().cpu().numpy(), b._weights.detach().cpu().numpy(), 1e-6, "tables")
+    sync.remove()
+    assert not hasattr(a, "_table_update_hook")
