@@ -216,3 +216,24 @@ def conv2d_inputs(cfg, n_weights, n_outputs):
     W = synth.normal(s + 52, (n_weights,), 0.0, 0.1)
     dY = synth.normal(s + 53, (B, n_outputs))
     return x, W, dY
+
+
+# Whole LUTTransformer models (reference: src/spiky/lut/LUTTransformer.py): the fixture carries every parameter and
+# anchor of the reference-built model, the tokens, the logits and the gradients of all parameters for a seeded
+# upstream gradient, so that the block wiring (attention -> residual, feed-forward -> residual, unembedder) is pinned.
+TRANSFORMER_CASES = {
+    "transformer_product_f32": dict(seed=31, B=3, V=23, E=16, S=8, Npe=4, layers=2, heads=2, Nt=3, Nc=4, concat=False),
+    "transformer_concat_f32": dict(seed=32, B=2, V=19, E=12, S=6, Npe=2, layers=2, heads=2, Nt=2, Nc=3, concat=True),
+    "transformer_concat_i32": dict(seed=33, B=2, V=19, E=12, S=6, Npe=2, layers=1, heads=2, Nt=2, Nc=3, concat=True,
+                                   int_mode=True, int_rescaler=10.0),
+    "transformer_product_unified_noffn_f32": dict(seed=34, B=2, V=17, E=16, S=7, Npe=4, layers=2, heads=1, Nt=4, Nc=4,
+                                                  concat=False, unified_pe=True, no_ffn=True, Nc_att=5),
+}
+
+
+def transformer_inputs(cfg):
+    """tokens int64 [B, S] and the upstream gradient of the logits fp32 [B, S, V]."""
+    s = cfg["seed"]
+    tokens = synth.integers(s + 51, (cfg["B"], cfg["S"]), 0, cfg["V"]).astype("int64")
+    dlogits = synth.normal(s + 52, (cfg["B"], cfg["S"], cfg["V"]))
+    return tokens, dlogits

@@ -20,7 +20,7 @@ import torch
 
 sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 import synth  # noqa: E402,F401
-from cases import (CONCAT_CASES, CONCAT_SPARSE_CASES, CONV2D_CASES, concat_sparse_inputs, conv2d_inputs, NONSEQ_FC_CASES, PROJECTION_CASES, PRODUCT_CASES, nonseq_fc_inputs, projection_inputs,  # noqa: E402
+from cases import (CONCAT_CASES, CONCAT_SPARSE_CASES, CONV2D_CASES, TRANSFORMER_CASES, transformer_inputs, concat_sparse_inputs, conv2d_inputs, NONSEQ_FC_CASES, PROJECTION_CASES, PRODUCT_CASES, nonseq_fc_inputs, projection_inputs,  # noqa: E402
                    sequence_inputs)
 
 from spiky.lut.LUTLayer import (  # noqa: E402  (the reference)
@@ -332,6 +332,42 @@ def run_conv2d(name, cfg):
          anchors=t2n(layer._detector_anchors), **extra, **out)
 
 
+# ----------------------------------------------------------------------------- whole LUTTransformer models
+def run_transformer(name, cfg):
+    from spiky.lut.LUTTransformer import LUTTransformer
+
+    int_mode = cfg.get("int_mode", False)
+    model = LUTTransformer(
+        vocab_size=cfg["V"], embedding_dim=cfg["E"], context_size=cfg["S"], positional_dim=cfg["Npe"],
+        num_layers=cfg["layers"], num_heads=cfg["heads"], n_detectors=cfg["Nt"], n_anchors_per_detector=cfg["Nc"],
+        n_anchors_per_detector_attention=cfg.get("Nc_att"), no_ffn=cfg.get("no_ffn", False),
+        concatenation_product=cfg["concat"], unified_pe=cfg.get("unified_pe", False),
+        weights_gradient_policy=GradientPolicy(GradientType.Dense), device=torch.device("cpu"),
+        synapse_meta=SynapseMeta(min_weight=-1.0, max_weight=1.0, initial_noise_level=0.4, initial_weight=-0.2),
+        seed=cfg["seed"], summation_dtype=torch.int32 if int_mode else torch.float32,
+        _int_rescaler=cfg.get("int_rescaler", 0.001))
+    model.train()
+    tokens, dlogits = transformer_inputs(cfg)
+    logits = model(torch.from_numpy(tokens))
+    logits.backward(torch.from_numpy(dlogits))
+    arrays = dict(embedding=t2n(model.token_embedder.weight), logits=t2n(logits))
+
+    def put(prefix, layer):
+        arrays[prefix + "_anchors"] = t2n(layer._detector_anchors)
+        arrays[prefix + "_W"] = t2n(layer._weights)
+        arrays[prefix + "_dW"] = t2n(layer._weights.grad)
+        if getattr(layer, "_positional_embeddings", None) is not None:
+            arrays[prefix + "_pe"] = t2n(layer._positional_embeddings)
+            arrays[prefix + "_dpe"] = t2n(layer._positional_embeddings.grad)
+
+    for li, block in enumerate(model.layers):
+        put(f"att{li}", block["attention_lut"])
+        if not cfg.get("no_ffn", False):
+            put(f"ffn{li}", block["ffn"])
+    put("unembedder", model.unembedder)
+    save(name, dict(cfg, kind="transformer"), **arrays)
+
+
 def main():
     prefixes = sys.argv[1:]
     for name, cfg in NONSEQ_FC_CASES.items():
@@ -346,6 +382,9 @@ def main():
     for name, cfg in PROJECTION_CASES.items():
         if not prefixes or any(name.startswith(p) for p in prefixes):
             run_projection(name, cfg)
+    for name, cfg in TRANSFORMER_CASES.items():
+        if not prefixes or any(name.startswith(p) for p in prefixes):
+            run_transformer(name, cfg)
     for name, cfg in CONV2D_CASES.items():
         if not prefixes or any(name.startswith(p) for p in prefixes):
             run_conv2d(name, cfg)

@@ -12,7 +12,7 @@ pytestmark = pytest.mark.gpu
 REL = 1e-5
 
 
-def build_layer(cfg, anchors, W, pe):
+def build_layer(cfg, anchors, W, pe, device="cuda:0"):
     from spiky_b200.lut_layer import LUTLayer, SynapseMeta, GradientPolicy, GradientType
 
     internal = cfg.get("policy") == "internal"
@@ -23,7 +23,7 @@ def build_layer(cfg, anchors, W, pe):
         weights_gradient_policy=GradientPolicy(GradientType.Internal if internal else GradientType.Dense),
         summation_dtype=torch.int32 if cfg.get("int_mode") else torch.float32,
         _explicit_anchors=torch.from_numpy(anchors.reshape(-1).copy()), _int_rescaler=cfg.get("int_rescaler", 0.001),
-        _forward_group_size=cfg.get("G", 32), random_seed=1, device="cuda:0")
+        _forward_group_size=cfg.get("G", 32), random_seed=1, device=device)
     with torch.no_grad():
         layer._weights.copy_(torch.from_numpy(W))
         if pe is not None:
@@ -33,17 +33,21 @@ def build_layer(cfg, anchors, W, pe):
     return layer
 
 
-def run_gpu(cfg, x, anchors, W, pe, dY):
-    layer = build_layer(cfg, anchors, W, pe)
-    xt = torch.from_numpy(x).cuda()
+def run_gpu(cfg, x, anchors, W, pe, dY, device="cuda:0", prepare=None):
+    layer = build_layer(cfg, anchors, W, pe, device)
+    if prepare is not None:
+        prepare(layer)  # the CPU tests swap the runtime for the oracle here
+    dev = torch.device("cpu" if device is None else device)
+    xt = torch.from_numpy(x).to(dev)
     pos = layer._prepare_positional_embeddings()
     pos = None if pos is None else pos.detach()
     layer.eval()
     y_eval = layer.forward_step_concat(xt, pos)
     layer.train()
     y, idx, md, mk, pidx, pmd, pmk = layer.forward_step_concat(xt, pos)
-    dx, dw, dpe = layer.backward_step_concat(xt, torch.from_numpy(dY).cuda(), idx, md, mk, pidx, pmd, pmk)
-    torch.cuda.synchronize()
+    dx, dw, dpe = layer.backward_step_concat(xt, torch.from_numpy(dY).to(dev), idx, md, mk, pidx, pmd, pmk)
+    if dev.type == "cuda":
+        torch.cuda.synchronize()
     n = cfg["B"] * cfg["S"]
     out = dict(y=y.cpu().numpy(), y_eval=y_eval.cpu().numpy(), dX=dx.cpu().numpy(),
                idx=idx.cpu().numpy().reshape(n, -1), min_k=mk.cpu().numpy().reshape(n, -1),

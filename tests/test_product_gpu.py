@@ -12,11 +12,11 @@ pytestmark = pytest.mark.gpu
 REL = 1e-5
 
 
-def build_layer(cfg, anchors, W, pe):
+def build_layer(cfg, anchors, W, pe, device="cuda:0"):
     from spiky_b200.lut_layer import LUTLayer, SynapseMeta, GradientPolicy, GradientType, LUTSharedContext
 
     internal = cfg.get("policy") == "internal"
-    ctx = LUTSharedContext(_cmp_eps=cfg.get("cmp_eps", 0.0)).to_device("cuda:0")
+    ctx = LUTSharedContext(_cmp_eps=cfg.get("cmp_eps", 0.0)).to_device("cpu" if device is None else device)
     layer = LUTLayer(
         cfg["E"], cfg["Nc"], cfg["Nt"], cfg["O"], sequence_length=cfg["S"],
         synapse_meta=SynapseMeta(learning_rate=cfg.get("lr_meta", 1.0), min_weight=-1.0, max_weight=1.0),
@@ -25,7 +25,7 @@ def build_layer(cfg, anchors, W, pe):
         weights_gradient_policy=GradientPolicy(GradientType.Internal if internal else GradientType.Dense),
         shared_context=ctx, summation_dtype=torch.int32 if cfg.get("int_mode") else torch.float32,
         _explicit_anchors=torch.from_numpy(anchors.reshape(-1).copy()), _int_rescaler=cfg.get("int_rescaler", 0.001),
-        random_seed=1, device="cuda:0")
+        random_seed=1, device=device)
     with torch.no_grad():
         layer._weights.copy_(torch.from_numpy(W))
         if pe is not None:
@@ -35,16 +35,20 @@ def build_layer(cfg, anchors, W, pe):
     return layer
 
 
-def run_gpu(cfg, x, anchors, W, pe, dY, variant=0):
-    layer = build_layer(cfg, anchors, W, pe)
+def run_gpu(cfg, x, anchors, W, pe, dY, variant=0, device="cuda:0", prepare=None):
+    layer = build_layer(cfg, anchors, W, pe, device)
+    if prepare is not None:
+        prepare(layer)  # the CPU tests swap the runtime for the oracle here
+    dev = torch.device("cpu" if device is None else device)
     layer._product_variant = variant  # 0 auto, 1 direct gathers, 2 histogram + tiled contraction
     layer.train()
-    xt = torch.from_numpy(x).cuda()
+    xt = torch.from_numpy(x).to(dev)
     pos = layer._prepare_positional_embeddings()
     pos = None if pos is None else pos.detach()
     y = layer.forward_step_product(xt, pos)
-    dx, dw, dpe = layer.backward_step_product(xt, pos, torch.from_numpy(dY).cuda())
-    torch.cuda.synchronize()
+    dx, dw, dpe = layer.backward_step_product(xt, pos, torch.from_numpy(dY).to(dev))
+    if dev.type == "cuda":
+        torch.cuda.synchronize()
     out = dict(y=y.cpu().numpy(), dX=dx.cpu().numpy())
     if dpe is not None:
         out["dPE"] = dpe.cpu().numpy()
