@@ -41,7 +41,7 @@ def build(cfg, ref, device):
     return model, layers
 
 
-def check(cfg, ref, model, layers, device):
+def check(cfg, ref, model, layers, device, rel=1e-5):
     tokens, dlogits = transformer_inputs(cfg)
     logits = model(torch.from_numpy(tokens).to(device))
     logits.backward(torch.from_numpy(dlogits).to(device))
@@ -53,7 +53,7 @@ def check(cfg, ref, model, layers, device):
         if int_mode:
             assert np.array_equal(got, want), f"{what}: fixed-point results must be bit-exact"
         else:
-            golden_util.assert_close(got, want, 1e-5, what)
+            golden_util.assert_close(got, want, rel, what)
 
     same(logits, ref["logits"], "logits")
     for prefix, layer in layers.items():
@@ -77,4 +77,5 @@ def test_transformer_wiring_matches_reference_on_cpu(name):
 def test_transformer_matches_reference_golden(name):
     cfg, ref = golden_util.load(name)
     model, layers = build(cfg, ref, "cuda:0")
-    check(cfg, ref, model, layers, torch.device("cuda:0"))
+    # gradients pass through up to five layers whose fp32 sums run in another order than the reference's
+    check(cfg, ref, model, layers, torch.device("cuda:0"), rel=2e-5)
