@@ -98,7 +98,9 @@ def _cpu_layer(cfg):
         receptive_field_stride_shape=tuple(cfg["rf_stride"]),
         lut_receptive_field_shape=None if cfg["lut_rf"] is None else tuple(cfg["lut_rf"]),
         lut_receptive_field_stride_shape=None if cfg["lut_rf_stride"] is None else tuple(cfg["lut_rf_stride"]),
-        synapse_meta=SynapseMeta(min_weight=-1.0, max_weight=1.0), random_seed=cfg["seed"], device=None)
+        synapse_meta=SynapseMeta(min_weight=-1.0, max_weight=1.0),
+        summation_dtype=torch.int32 if cfg.get("int_mode") else torch.float32,
+        _int_rescaler=cfg.get("int_rescaler", 0.001), random_seed=cfg["seed"], device=None)
 
 
 @pytest.mark.parametrize("name", golden_util.names("conv2d_"))

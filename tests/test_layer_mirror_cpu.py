@@ -89,3 +89,78 @@ def test_gradient_policies_through_autograd_on_cpu(policy_name):
     assert torch.equal(grad.to_dense(), want)
     assert not ctx.get_weight_gradients_buffer(want.numel(), torch.device("cpu"), layer._multi_id).any()
     assert torch_utils.DenseToSparseConverter is not None
+
+
+def _run_nonseq_layer(layer, x, dY, internal_lr=None):
+    """forward_step (eval + train) and backward_step of a non-sequence layer on CPU tensors; numpy results."""
+    B = x.shape[0]
+    I, O, Nt = layer.n_inputs(), layer.n_outputs(), layer.n_detectors()
+    xt = torch.from_numpy(x).view((B, 1) + tuple(layer.input_shape()))
+    out = {}
+    layer.eval()
+    out["y_eval"] = layer.forward_step(xt).numpy().reshape(B, O)
+    layer.train()
+    y, idx, md, mk = layer.forward_step(xt)
+    if internal_lr is not None:
+        layer.set_external_learning_rate_hook(lambda w: internal_lr)
+    dx, dw = layer.backward_step(xt, torch.from_numpy(dY).view((B, 1) + tuple(layer.output_shape())), idx, md, mk)
+    out.update(y=y.numpy().reshape(B, O), idx=idx.numpy().reshape(B, Nt), min_delta=md.numpy().reshape(B, Nt),
+               min_k=mk.numpy().reshape(B, Nt), dX=dx.numpy().reshape(B, I))
+    if internal_lr is not None:
+        out["W_after"] = layer._weights.detach().numpy()
+    else:
+        out["dW"] = dw.numpy()
+    return out
+
+
+def _compare_nonseq(got, ref, int_mode):
+    assert np.array_equal(got["idx"], ref["idx"]) and np.array_equal(got["min_k"], ref["min_k"])
+    assert np.array_equal(got["min_delta"].view(np.int32), ref["min_delta"].view(np.int32))
+    for k in ["y", "y_eval", "dX"] + (["W_after"] if "W_after" in ref else ["dW"]):
+        if k not in ref:
+            continue
+        if int_mode:
+            assert np.array_equal(got[k], ref[k]), f"{k}: fixed-point results must be bit-exact"
+        else:
+            golden_util.assert_close(got[k], ref[k], 1e-5, k)
+
+
+@pytest.mark.parametrize("name", golden_util.names("proj_"))
+def test_projection_layer_on_cpu_matches_reference(name):
+    from cases import projection_inputs
+    from spiky_b200.lut_layer import GradientPolicy, GradientType, ProjectionLUTLayer, SynapseMeta
+
+    cfg, ref = golden_util.load(name)
+    internal = cfg.get("policy") == "internal"
+    layer = ProjectionLUTLayer(
+        cfg["in_shape"], cfg["out_shape"], cfg["Nc"], cfg["groups"], cfg["per_group"], cfg["receptive"],
+        cfg["projection"], synapse_meta=SynapseMeta(learning_rate=cfg.get("lr_meta", 1.0), min_weight=-1.0, max_weight=1.0),
+        weights_gradient_policy=GradientPolicy(GradientType.Internal if internal else GradientType.Dense),
+        summation_dtype=torch.int32 if cfg.get("int_mode") else torch.float32,
+        _int_rescaler=cfg.get("int_rescaler", 0.001), _forward_group_size=cfg.get("G", 32), random_seed=1, device=None)
+    layer.load_structure(ref["anchors"], ref["syn_source"], ref["syn_slot"], ref["syn_target"], cfg["n_weights"])
+    use_oracle_backend(layer)
+    x, W, dY = projection_inputs(cfg, cfg["n_weights"])
+    with torch.no_grad():
+        layer._weights.copy_(torch.from_numpy(W))
+    got = _run_nonseq_layer(layer, x, dY, cfg["ext_lr"] if internal else None)
+    _compare_nonseq(got, ref, cfg.get("int_mode", False))
+
+
+@pytest.mark.parametrize("name", golden_util.names("conv2d_"))
+def test_conv2d_layer_on_cpu_matches_reference(name):
+    from cases import conv2d_inputs
+    from test_conv2d_structure import _cpu_layer
+
+    cfg, ref = golden_util.load(name)
+    layer = _cpu_layer(cfg)
+    if cfg["lut_rf"] is not None:
+        layer.load_structure(ref["anchors"], ref["syn_source"], ref["syn_slot"], ref["syn_target"], cfg["n_weights"])
+    else:
+        layer._set_anchors(torch.from_numpy(ref["anchors"]))
+    use_oracle_backend(layer)
+    x, W, dY = conv2d_inputs(cfg, cfg["n_weights"], cfg["O"])
+    with torch.no_grad():
+        layer._weights.copy_(torch.from_numpy(W))
+    got = _run_nonseq_layer(layer, x, dY)
+    _compare_nonseq(got, ref, cfg.get("int_mode", False))
