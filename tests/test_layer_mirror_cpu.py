@@ -66,22 +66,12 @@ def test_gradient_policies_through_autograd_on_cpu(policy_name):
         assert torch.allclose(layer._weights.detach(), before - 0.5 * want, atol=1e-6)
         assert torch.allclose(xi.grad, xd.grad, atol=1e-6)
         return
-    # Sparse: the compaction runs in the CUDA library; stand in for it with the same contract (sorted cells, erased
-    # buffer) so that the layer's handling of the converter's result is what is tested
-    class HostConverter:
-        def dense_to_sparse_32(self, buf, erase_input=True):
-            cells = torch.nonzero(buf.view(torch.int32) != 0).flatten()
-            if cells.numel() == 0:
-                return None, None
-            values = buf[cells].clone()
-            if erase_input:
-                buf.zero_()
-            return cells, values
-
+    # Sparse: the compaction runs in the CUDA library; _HostConverter stands in for it, so that the layer's handling of
+    # the converter's result is what is tested
     layer = make(GradientType.Sparse)
     with torch.no_grad():
         layer._weights.copy_(dense._weights)
-    ctx.__dict__.setdefault("_dense_to_sparse_converters", {})[layer._multi_id] = HostConverter()
+    ctx.__dict__.setdefault("_dense_to_sparse_converters", {})[layer._multi_id] = _HostConverter()
     xs = x.clone().requires_grad_(True)
     (layer(xs) * g).sum().backward()
     grad = layer._weights.grad
@@ -164,3 +154,71 @@ def test_conv2d_layer_on_cpu_matches_reference(name):
         layer._weights.copy_(torch.from_numpy(W))
     got = _run_nonseq_layer(layer, x, dY)
     _compare_nonseq(got, ref, cfg.get("int_mode", False))
+
+
+class _HostConverter:
+    """Stand-in for the CUDA compaction of the Sparse policy with the same contract: sorted non-zero cells, their
+    values, the source buffer erased."""
+
+    def dense_to_sparse_32(self, buf, erase_input=True):
+        cells = torch.nonzero(buf.view(torch.int32) != 0).flatten()
+        if cells.numel() == 0:
+            return None, None
+        values = buf[cells].clone()
+        if erase_input:
+            buf.zero_()
+        return cells, values
+
+
+@pytest.mark.parametrize("concat", [True, False])
+def test_training_steps_agree_across_gradient_policies(concat):
+    """A small LUTTransformer trained for a few SGD steps ends with the same tables and embeddings whether the table
+    gradients leave the layers dense, as sparse COO tensors, or are applied inside the backward call (the matrix the
+    reference's test_lut_transformer_small.py runs against its pure-Python model)."""
+    from spiky_b200.lut_layer import GradientPolicy, GradientType, LUTSharedContext, SynapseMeta
+    from spiky_b200.lut_transformer import LUTTransformer
+
+    lr, steps, V, S = 0.05, 4, 17, 6
+    meta = SynapseMeta(min_weight=-1.0, max_weight=1.0, initial_noise_level=0.4, initial_weight=-0.2)
+    gen = torch.Generator().manual_seed(5)
+    tokens = torch.randint(0, V, (steps, 3, S + 1), generator=gen)
+
+    def train(policy):
+        ctx = LUTSharedContext().to_device("cpu")
+        ctx.__dict__["_dense_to_sparse_converters"] = {0: _HostConverter()}
+        model = LUTTransformer(V, 12, S, positional_dim=2, num_layers=2, num_heads=2, n_detectors=2,
+                               n_anchors_per_detector=3, concatenation_product=concat, seed=11, device=None,
+                               weights_gradient_policy=GradientPolicy(policy), synapse_meta=meta,
+                               lut_shared_context=ctx)
+        use_oracle_backend(model)
+        model.train()
+        return model
+
+    models = {p: train(p) for p in (GradientType.Dense, GradientType.Sparse, GradientType.Internal)}
+    first = models[GradientType.Dense]
+    for m in models.values():  # initial noise comes from the global generator: start from identical parameters
+        m.load_state_dict(first.state_dict())
+    start = {k: v.clone() for k, v in first.state_dict().items()}
+    models[GradientType.Internal].set_external_learning_rate_hook(lambda w: lr)
+    for policy, model in models.items():
+        params = [p for p in model.parameters() if p.requires_grad]
+        opt = torch.optim.SGD(params, lr=lr)
+        for step in range(steps):
+            opt.zero_grad(set_to_none=True)
+            logits = model(tokens[step, :, :-1])
+            loss = torch.nn.functional.cross_entropy(logits.reshape(-1, V), tokens[step, :, 1:].reshape(-1))
+            loss.backward()
+            if policy == GradientType.Sparse:
+                assert any(p.grad is not None and p.grad.is_sparse for p in params)
+            if policy == GradientType.Internal:
+                assert all(layer._weights.grad is None for layer in model._lut_layers())
+            opt.step()
+    want = first.state_dict()
+    assert any("_weights" in k and not torch.equal(v, start[k]) for k, v in want.items()), "training moved nothing"
+    for policy in (GradientType.Sparse, GradientType.Internal):
+        got = models[policy].state_dict()
+        for key, value in want.items():
+            if value.dtype.is_floating_point:
+                assert torch.allclose(got[key], value, rtol=1e-4, atol=1e-6), f"{policy}: {key}"
+            else:
+                assert torch.equal(got[key], value), f"{policy}: {key}"
