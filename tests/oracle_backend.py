@@ -77,7 +77,9 @@ class OracleDataManager:
         md = _np(r_min_anchor_deltas).reshape(B, r._n_detectors)
         mk = _np(r_min_anchor_delta_indices).reshape(B, r._n_detectors)
         W = r_weights.numpy() if external_lr >= 0 else _np(r_weights)  # in-place SGD writes through
-        common = dict(lr_meta=r._lr_meta(), external_lr=external_lr, **self._kw())
+        skip_table = external_lr == -2.0  # input gradient only (spiky_b200._native.SKIP_TABLE_GRADIENT)
+        assert not (skip_table and w_weights_gradients is not None)
+        common = dict(lr_meta=r._lr_meta(), external_lr=-1.0 if skip_table else external_lr, **self._kw())
         if r._fully_connected:
             dX, dW = orc.nonseq_fc_backward(W, dY, _np(r_detector_anchors), idx, md, mk, r._n_inputs, r._n_anchors,
                                             forward_group_size=r._fwd_group, **common)
@@ -86,6 +88,29 @@ class OracleDataManager:
                                                 r._n_anchors, **common)
         _acc(w_input_gradients, dX)
         _acc(w_weights_gradients, dW)
+
+    def table_gradient(self, batch_size, r_output_gradients, r_lookup_indices, w_target, scale, chunk_begin=0,
+                       chunk_end=None):
+        """w_target[row(t, idx) + p] += scale * lr_meta * dY[b, target(p)] for the detectors of the chunk range."""
+        r = self._real
+        index = r._sparse
+        chunk_end = index.n_chunks if chunk_end is None else chunk_end
+        if not 0 <= chunk_begin <= chunk_end <= index.n_chunks:
+            raise ValueError("chunk range outside the index")
+        B = batch_size
+        dY = _np(r_output_gradients).reshape(B, r._n_outputs)
+        idx = _np(r_lookup_indices).reshape(B, r._n_detectors)
+        if idx.dtype == np.int16:
+            idx = idx.view(np.uint16)
+        idx = idx.astype(np.int32)
+        ones = np.ones(idx.shape, np.float32)
+        anchors = np.zeros((r._n_detectors, r._n_anchors, 2), np.int32)  # only the (discarded) input gradient reads them
+        _, dW = orc.nonseq_sparse_backward(_np(w_target), dY, anchors, idx, ones,
+                                           np.zeros_like(idx), self._sp(), r._n_inputs, r._n_anchors,
+                                           lr_meta=r._lr_meta(), **self._kw())
+        bounds = index.chunk_weight_bounds()
+        lo, hi = int(bounds[chunk_begin]), int(bounds[chunk_end])
+        w_target.view(-1)[lo:hi] += float(scale) * torch.from_numpy(dW[lo:hi])
 
     # ---- product-mode sequence layers
     def _pe3(self, pe, S):

@@ -260,3 +260,81 @@ def test_sharded_table_update_equals_global_batch_sgd(tmp_path, weight_gather):
     mp.spawn(_sharded_worker, args=(2, _free_port(), str(tmp_path), weight_gather), nprocs=2, join=True)
     ok, err = open(tmp_path / "ok4").read().split()
     assert ok == "True", f"max abs error {err}"
+
+
+def _sharded_model_worker(rank, world, port, result_dir):
+    """Two sparse layers and a fully connected readout trained for two steps: ranks with half the batch each and the
+    sharded table update must end with the tables a single process gets from SGD on the whole batch."""
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    sys.path.insert(0, os.path.join(ROOT, "tests", "golden"))
+    import datetime
+    import synth
+    from oracle_backend import use_oracle_backend
+    from spiky_b200.data_parallel import ShardedTableUpdate, allreduce_gradients, shard_batch
+    from spiky_b200.lut_layer import LUTLayer, ProjectionLUTLayer, SynapseMeta
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=60))
+    try:
+        meta = SynapseMeta(min_weight=-1.0, max_weight=1.0, initial_noise_level=0.3, initial_weight=-0.15)
+
+        def build():
+            torch.manual_seed(123)  # the initial noise comes from the global generator
+            layers = torch.nn.ModuleList([
+                ProjectionLUTLayer((12, 12), (10, 10), 4, 6, 5, (5, 5), (3, 3), synapse_meta=meta, random_seed=2, device=None),
+                ProjectionLUTLayer((10, 10), (8, 8), 4, 5, 6, (5, 5), (3, 3), synapse_meta=meta, random_seed=3, device=None),
+                LUTLayer(64, 4, 6, 5, synapse_meta=meta, random_seed=4, device=None)])
+            use_oracle_backend(layers)
+            layers.train()
+            return layers
+
+        def run(layers, x, labels):
+            z = x
+            for layer in layers[:-1]:
+                z = layer(z)
+            logits = layers[-1](z.reshape(z.shape[0], 1, -1)).reshape(z.shape[0], -1)
+            return torch.nn.functional.cross_entropy(logits, labels)
+
+        B, lr, steps = 8, 0.1, 2
+        xs = [torch.from_numpy(synth.sparse_images(60 + s, (B, 144))).view(B, 1, 12, 12) for s in range(steps)]
+        ys = [torch.from_numpy(synth.integers(70 + s, (B,), 0, 5).astype(np.int64)) for s in range(steps)]
+        # (a) single process, whole batch, dense gradients + SGD
+        full = build()
+        opt = torch.optim.SGD([l._weights for l in full], lr=lr)
+        for s in range(steps):
+            opt.zero_grad()
+            run(full, xs[s], ys[s]).backward()
+            opt.step()
+        # (b) this rank's half of the batch, sharded in-place update of the sparse layers, all-reduce for the readout
+        mine = build()
+        sync = ShardedTableUpdate(list(mine[:-1]), lr)
+        opt = torch.optim.SGD([mine[-1]._weights], lr=lr)
+        b0, b1 = shard_batch(B, rank, world)
+        for s in range(steps):
+            sync.wait()
+            opt.zero_grad()
+            run(mine, xs[s][b0:b1], ys[s][b0:b1]).backward()
+            assert mine[0]._weights.grad is None and mine[1]._weights.grad is None
+            allreduce_gradients([mine[-1]._weights], average=True)
+            opt.step()
+        sync.wait()
+        ok = True
+        worst = 0.0
+        for a, b in zip(full, mine):
+            err = float((a._weights - b._weights).abs().max())
+            worst = max(worst, err)
+            ok = ok and err <= 2e-6
+        flags = [torch.zeros(1) for _ in range(world)]
+        dist.all_gather(flags, torch.tensor([1.0 if ok else 0.0]))
+        if rank == 0:
+            open(os.path.join(result_dir, "ok5"), "w").write(f"{all(float(f) == 1.0 for f in flags)} {worst}")
+    finally:
+        dist.destroy_process_group()
+
+
+def test_sharded_table_update_trains_like_one_process(tmp_path):
+    mp.spawn(_sharded_model_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
+    ok, err = open(tmp_path / "ok5").read().split()
+    assert ok == "True", f"max abs difference of the tables {err}"
