@@ -78,3 +78,26 @@ def test_constructor_argument_errors():
     layer = LUTLayer(16, 3, 4, 5, synapse_meta=_meta(), device=None)
     with pytest.raises(ValueError):
         layer.set_external_learning_rate_hook(lambda w: 0.1)  # only for the Internal policy
+
+
+def test_quantize_tables_is_symmetric_per_table():
+    from spiky_b200.inference import LUTInference, quantize_tables
+
+    gen = torch.Generator().manual_seed(9)
+    Nt, T, O = 5, 8, 4
+    w = torch.randn(Nt * T * O, generator=gen) * torch.tensor([0.01, 0.1, 1.0, 3.0, 0.0]).repeat_interleave(T * O)
+    q, scale = quantize_tables(w, Nt, T, O)
+    assert q.dtype == torch.int8 and q.shape == w.shape and scale.shape == (Nt,)
+    per = w.view(Nt, -1)
+    assert torch.allclose(scale[:4], per[:4].abs().amax(dim=1) / 127.0)
+    assert scale[4] > 0 and not q.view(Nt, -1)[4].any()          # an all-zero table keeps a usable scale
+    assert int(q.abs().max()) == 127 and int(q.min()) >= -127    # symmetric range, -128 unused
+    back = q.view(Nt, -1).float() * scale[:, None]
+    assert bool(((back - per).abs() <= scale[:, None] / 2 + 1e-12).all())
+    # shard boundaries must keep whole detector blocks
+    anchors = torch.zeros(64 * 3 * 2, dtype=torch.int32)
+    tables = torch.zeros(64 * 8 * 4)
+    with pytest.raises(AssertionError):
+        LUTInference.shard_of(0, 3, 16, 4, 64, 3, anchors, tables)          # 64 detectors over 3 ranks
+    with pytest.raises(AssertionError):
+        LUTInference.shard_of(0, 4, 16, 4, 64, 3, anchors, tables)          # 16 per rank, blocks of 32
