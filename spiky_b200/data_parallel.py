@@ -315,15 +315,12 @@ class ShardedTableUpdate:
         ctx = torch.cuda.stream(self._side) if on_gpu else _NullContext()
         with ctx:
             small = idx.to(plan["idx_dtype"])
-            if W > 1:
-                idx_all = torch.empty(W * small.numel(), dtype=small.dtype, device=small.device)
-                dY_all = torch.empty(W * dY.numel(), dtype=dY.dtype, device=dY.device)
-                w1 = dist.all_gather_into_tensor(idx_all, small, group=G, async_op=True)
-                w2 = dist.all_gather_into_tensor(dY_all, dY.contiguous(), group=G, async_op=True)
-                w1.wait()
-                w2.wait()
-            else:
-                idx_all, dY_all = small, dY
+            idx_all = torch.empty(W * small.numel(), dtype=small.dtype, device=small.device)
+            dY_all = torch.empty(W * dY.numel(), dtype=dY.dtype, device=dY.device)
+            w1 = dist.all_gather_into_tensor(idx_all, small, group=G, async_op=True)
+            w2 = dist.all_gather_into_tensor(dY_all, dY.contiguous(), group=G, async_op=True)
+            w1.wait()  # orders the update below (same stream) after the collectives; the host does not block
+            w2.wait()
             if on_gpu:
                 # tensors made on the main stream, used on the side stream
                 idx.record_stream(self._side)
