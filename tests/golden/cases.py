@@ -226,6 +226,11 @@ TRANSFORMER_CASES = {
     "transformer_concat_f32": dict(seed=32, B=2, V=19, E=12, S=6, Npe=2, layers=2, heads=2, Nt=2, Nc=3, concat=True),
     "transformer_concat_i32": dict(seed=33, B=2, V=19, E=12, S=6, Npe=2, layers=1, heads=2, Nt=2, Nc=3, concat=True,
                                    int_mode=True, int_rescaler=10.0),
+    # 2-D embeddings: the attention layer is a Conv2DLUTLayer whose single receptive field covers the whole input
+    "transformer_concat_2d_f32": dict(seed=35, B=2, V=15, E=(3, 4), S=5, Npe=2, layers=2, heads=2, Nt=2, Nc=3, concat=True),
+    # BatchNorm1d on every branch before the residual addition (training mode: batch statistics)
+    "transformer_product_bn_f32": dict(seed=36, B=3, V=21, E=16, S=6, Npe=3, layers=2, heads=2, Nt=3, Nc=4, concat=False,
+                                       batch_norm=True),
     "transformer_product_unified_noffn_f32": dict(seed=34, B=2, V=17, E=16, S=7, Npe=4, layers=2, heads=1, Nt=4, Nc=4,
                                                   concat=False, unified_pe=True, no_ffn=True, Nc_att=5),
 }

@@ -338,10 +338,12 @@ def run_transformer(name, cfg):
 
     int_mode = cfg.get("int_mode", False)
     model = LUTTransformer(
-        vocab_size=cfg["V"], embedding_dim=cfg["E"], context_size=cfg["S"], positional_dim=cfg["Npe"],
+        vocab_size=cfg["V"], embedding_dim=cfg["E"] if isinstance(cfg["E"], int) else tuple(cfg["E"]),
+        context_size=cfg["S"], positional_dim=cfg["Npe"],
         num_layers=cfg["layers"], num_heads=cfg["heads"], n_detectors=cfg["Nt"], n_anchors_per_detector=cfg["Nc"],
         n_anchors_per_detector_attention=cfg.get("Nc_att"), no_ffn=cfg.get("no_ffn", False),
         concatenation_product=cfg["concat"], unified_pe=cfg.get("unified_pe", False),
+        use_batch_norm=cfg.get("batch_norm", False),
         weights_gradient_policy=GradientPolicy(GradientType.Dense), device=torch.device("cpu"),
         synapse_meta=SynapseMeta(min_weight=-1.0, max_weight=1.0, initial_noise_level=0.4, initial_weight=-0.2),
         seed=cfg["seed"], summation_dtype=torch.int32 if int_mode else torch.float32,
@@ -364,6 +366,11 @@ def run_transformer(name, cfg):
         put(f"att{li}", block["attention_lut"])
         if not cfg.get("no_ffn", False):
             put(f"ffn{li}", block["ffn"])
+        if cfg.get("batch_norm", False):
+            for branch in ("attention", "ffn"):
+                bn = block[branch + "_bn"]
+                arrays[f"{branch}{li}_bn_dweight"] = t2n(bn.weight.grad)
+                arrays[f"{branch}{li}_bn_dbias"] = t2n(bn.bias.grad)
     put("unembedder", model.unembedder)
     save(name, dict(cfg, kind="transformer"), **arrays)
 

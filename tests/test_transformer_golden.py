@@ -16,7 +16,8 @@ def build(cfg, ref, device):
 
     int_mode = cfg.get("int_mode", False)
     model = LUTTransformer(
-        vocab_size=cfg["V"], embedding_dim=cfg["E"], context_size=cfg["S"], positional_dim=cfg["Npe"],
+        vocab_size=cfg["V"], embedding_dim=cfg["E"] if isinstance(cfg["E"], int) else tuple(cfg["E"]),
+        context_size=cfg["S"], positional_dim=cfg["Npe"], use_batch_norm=cfg.get("batch_norm", False),
         num_layers=cfg["layers"], num_heads=cfg["heads"], n_detectors=cfg["Nt"], n_anchors_per_detector=cfg["Nc"],
         n_anchors_per_detector_attention=cfg.get("Nc_att"), no_ffn=cfg.get("no_ffn", False),
         concatenation_product=cfg["concat"], unified_pe=cfg.get("unified_pe", False),
@@ -56,6 +57,11 @@ def check(cfg, ref, model, layers, device, rel=1e-5):
             golden_util.assert_close(got, want, rel, what)
 
     same(logits, ref["logits"], "logits")
+    if cfg.get("batch_norm", False):
+        for li, block in enumerate(model.layers):
+            for branch in ("attention", "ffn"):
+                same(block[branch + "_bn"].weight.grad, ref[f"{branch}{li}_bn_dweight"], f"{branch}{li} bn dweight")
+                same(block[branch + "_bn"].bias.grad, ref[f"{branch}{li}_bn_dbias"], f"{branch}{li} bn dbias")
     for prefix, layer in layers.items():
         same(layer._weights.grad, ref[prefix + "_dW"], prefix + " dW")
         if prefix + "_dpe" in ref:
