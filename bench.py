@@ -33,24 +33,26 @@ def measured_peaks():
 
 # ------------------------------------------------------------------------------------ clocks
 class ClockSampler:
-    """Samples SM clocks and throttle reasons through NVML from a thread while the timed region runs."""
+    """Samples SM clocks and throttle reasons through NVML from a thread.  NVML is initialised in start() (before
+    the warm-up), samples carry a host timestamp, and summary(t0, t1) reports those taken inside a timed region."""
 
     REASONS = {  # nvmlClocksEventReason* bit masks
         0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap",
     }
 
-    def __init__(self, gpu_index, period_s=0.01):
+    def __init__(self, gpu_index, period_s=0.005):
         import threading
         self.gpu_index = gpu_index
         self.period_s = period_s
-        self.samples = []
-        self.reasons = set()
+        self.samples = []   # (time.perf_counter(), SM MHz, reason mask)
         self.max_mhz = None
         self._stop = threading.Event()
         self._thread = None
         self._error = None
+        self._handle = None
 
-    def _run(self):
+    def start(self):
+        import threading
         try:
             import pynvml
             pynvml.nvmlInit()
@@ -61,29 +63,42 @@ class ClockSampler:
                 ids = [v.strip() for v in vis.split(",")]
                 if index < len(ids) and ids[index].isdigit():
                     index = int(ids[index])
-            h = pynvml.nvmlDeviceGetHandleByIndex(index)
-            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM))
-            while not self._stop.is_set():
-                self.samples.append(float(pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM)))
-                mask = pynvml.nvmlDeviceGetCurrentClocksEventReasons(h)
-                for bit, name in self.REASONS.items():
-                    if mask & bit:
-                        self.reasons.add(name)
-                time.sleep(self.period_s)
+            self._handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self._handle, pynvml.NVML_CLOCK_SM))
+            self._nvml = pynvml
         except Exception as e:  # NVML missing or restricted: report it instead of failing the run
             self._error = repr(e)
-
-    def start(self):
-        import threading
+            return
         self._thread = threading.Thread(target=self._run, daemon=True)
         self._thread.start()
+
+    def _run(self):
+        try:
+            while not self._stop.is_set():
+                mhz = float(self._nvml.nvmlDeviceGetClockInfo(self._handle, self._nvml.NVML_CLOCK_SM))
+                mask = self._nvml.nvmlDeviceGetCurrentClocksEventReasons(self._handle)
+                self.samples.append((time.perf_counter(), mhz, mask))
+                time.sleep(self.period_s)
+        except Exception as e:
+            self._error = repr(e)
 
     def stop(self):
         self._stop.set()
         if self._thread is not None:
             self._thread.join(timeout=5)
-        out = {"sm_mhz": statistics.median(self.samples) if self.samples else None, "sm_max_mhz": self.max_mhz,
-               "samples": len(self.samples), "reasons": sorted(self.reasons)}
+
+    def summary(self, t0, t1, ms_per_step=None):
+        inside = [(m, r) for (t, m, r) in self.samples if t0 <= t <= t1]
+        reasons = set()
+        for _, mask in inside:
+            for bit, name in self.REASONS.items():
+                if mask & bit:
+                    reasons.add(name)
+        med = statistics.median(m for m, _ in inside) if inside else None
+        out = {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "samples": len(inside), "reasons": sorted(reasons),
+               "window_s": t1 - t0}
+        if med and ms_per_step:
+            out["ms_per_step_x_mhz"] = ms_per_step * med   # clock-normalised step time (lower clock, longer step)
         if self._error:
             out["error"] = self._error
         return out
@@ -103,10 +118,15 @@ class LutLayerWorkload:
     unit = "samples/s"
     dtype = "f32"
 
+    def l2_policy(self):
+        """How cold caches are ensured between timed steps: the step's inputs exceed L2, or L2 is flushed."""
+        return "inputs>L2" if getattr(self, "static_input_bytes", 0) > L2_BYTES else "flushed"
+
     def __init__(self, batch=65536, n_inputs=784, n_detectors=64, n_anchors=6, n_outputs=32, graph=False):
         self.B, self.I, self.Nt, self.Nc, self.O = batch, n_inputs, n_detectors, n_anchors, n_outputs
         self.name = f"single LUT layer fwd+bwd fp32 (I={n_inputs}, Nt={n_detectors}, Nc={n_anchors}, O={n_outputs}), batch {batch}"
         self.units_per_step = batch
+        self.static_input_bytes = batch * (n_inputs + n_outputs) * 4
         # graph: the device-resident step (autograd forward + backward, 4 kernels of this library plus torch's
         # fills) is captured once into a CUDA graph and replayed; small batches are launch-latency bound otherwise
         self.graph = graph
@@ -144,7 +164,6 @@ class LutLayerWorkload:
         self.h2d_bytes = self.hx.numel() * 4 + self.hdy.numel() * 4
         self.d2h_bytes = 4
         self.input_bytes = self.h2d_bytes
-        self.l2_note = "inputs>L2" if self.input_bytes > L2_BYTES else "flushed"
         self.cuda_graph = None
         if self.graph:
             from spiky_b200 import _native
@@ -195,14 +214,10 @@ class LutLayerWorkload:
 
     # dominant kernel: the table-gradient scatter (2 x 4 x Nt x O bytes of row read-modify-write per sample)
     dominant_kernel = "fc_weight_grad"
-    # DRAM bytes per step by kernel family at batch 65536, from the ncu capture summarised in profiles/fc_layer_b65536.md
-    # (other batch sizes: not captured)
-    ncu_dram_bytes_b65536 = {"fc_weight_grad": 25.7e6, "fc_input_grad": 349.9e6, "fc_gather_forward": 25.7e6,
-                             "check_detectors": 213.3e6}
 
-    @property
-    def ncu_dram_bytes_per_step(self):
-        return self.ncu_dram_bytes_b65536 if self.B == 65536 and self.cuda_graph is None else {}
+    def traffic_key(self):
+        # DRAM traffic was captured at batch 65536 only
+        return "lut_layer_b65536" if self.B == 65536 and self.cuda_graph is None else None
 
     def algorithmic_bytes(self):
         """Per sample, by kernel family (every gathered / scattered row at full size, RMW counted twice)."""
@@ -248,6 +263,10 @@ class SparseConvNetWorkload:
     NC = 8
     READOUT = (256, 10, 64, 8)  # inputs, outputs, tables, anchor pairs
     LR = 0.01
+
+    def l2_policy(self):
+        """How cold caches are ensured between timed steps: the step's inputs exceed L2, or L2 is flushed."""
+        return "inputs>L2" if getattr(self, "static_input_bytes", 0) > L2_BYTES else "flushed"
 
     def __init__(self, batch=512, internal=False, sharded=False):
         self.B = batch
@@ -321,7 +340,6 @@ class SparseConvNetWorkload:
         self.device = device
         self.h2d_bytes = self.hx.numel() * 4 + self.hl.numel() * 8
         self.d2h_bytes = 4
-        self.l2_note = "flushed"
         self.grad_params = params
 
     def _run(self, x, labels):
@@ -365,10 +383,9 @@ class SparseConvNetWorkload:
         return self._run(x, labels)
 
     dominant_kernel = None  # picked by measured time
-    # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) per step of each kernel family, summed over its three
-    # launches, from the ncu capture summarised in profiles/sparse_convnet_step_b512.md
-    ncu_dram_bytes_per_step = {"sparse_forward": 430.7e6, "sparse_input_grad": 412.9e6, "sparse_weight_grad": 429.0e6,
-                               "check_detectors": 7.7e6}
+
+    def traffic_key(self):
+        return "sparse_convnet_b512" if self.B == 512 else None
 
     def algorithmic_bytes(self):
         """Per sample and kernel family, summed over the layers that launch it."""
@@ -399,8 +416,10 @@ class SparseConvNetWorkload:
         return res
 
     # ---- CPU baseline: the same network and step on the CPU oracle
-    def cpu_setup(self):
-        if getattr(self, "_cpu", None) is None:
+    def cpu_setup(self, fresh=False):
+        """The network as numpy arrays for the oracle; cached (cpu_step trains it), fresh=True builds a new copy
+        with the initial tables."""
+        if fresh or getattr(self, "_cpu", None) is None:
             layers = self.build(None)
             cpu = []
             for l in layers[:-1]:
@@ -409,8 +428,43 @@ class SparseConvNetWorkload:
                                 anchors=l._detector_anchors.numpy().copy(), I=l.n_inputs(), O=l.n_outputs()))
             r = layers[-1]
             cpu.append(dict(W=r._weights.detach().numpy().copy(), anchors=r._detector_anchors.numpy().copy()))
+            if fresh:
+                return cpu
             self._cpu = cpu
         return self._cpu
+
+    def cpu_loss(self, x, labels):
+        """Cross-entropy of the freshly built network on (x, labels), computed by the oracle."""
+        import numpy as np
+        from oracle import lut_oracle as orc
+        cpu = self.cpu_setup(fresh=True)
+        I, O, Nt, Nc = self.READOUT
+        a = x
+        for c in cpu[:-1]:
+            a = orc.nonseq_sparse_forward(c["W"], a, c["anchors"], c["sp"], self.NC, c["O"])[0]
+        logits = orc.nonseq_fc_forward(cpu[-1]["W"], a, cpu[-1]["anchors"], Nt, Nc, O)[0].astype(np.float64)
+        z = logits - logits.max(axis=1, keepdims=True)
+        logp = z - np.log(np.exp(z).sum(axis=1, keepdims=True))
+        return float(-logp[np.arange(x.shape[0]), labels].mean())
+
+    def parity_check(self, device):
+        """The first step's loss on the GPU (freshly built network, the library's kernels, layers chained on the
+        device) against the oracle's loss on the same batch."""
+        import torch
+        import torch.nn.functional as F
+        layers = self.build(device)
+        x, labels = self.host_inputs(77, self.B)
+        with torch.no_grad():
+            z = torch.from_numpy(x).view(self.B, 1, 28, 28).to(device)
+            for l in layers[:-1]:
+                l.train()
+                z = l(z)
+            layers[-1].train()
+            logits = layers[-1](z.reshape(self.B, 1, -1)).reshape(self.B, -1)
+            loss_gpu = float(F.cross_entropy(logits.double(), torch.from_numpy(labels).to(device)))
+        loss_cpu = self.cpu_loss(x, labels)
+        return {"loss_gpu": loss_gpu, "loss_oracle": loss_cpu, "rel": abs(loss_gpu - loss_cpu) / abs(loss_cpu),
+                "what": f"cross-entropy of the first step's forward pass, batch {self.B}, same seeded batch and tables"}
 
     def cpu_step(self, batch, threads):
         import numpy as np
@@ -456,13 +510,13 @@ class CharTransformerWorkload:
     dtype = "f32"
     dominant_kernel = None
     zipf_s = 1.1
-    # DRAM bytes per step (4 layers) of the two contractions at batch 64: captured on one layer and 8 sequences
-    # (profiles/product_attention_layer.md) and scaled: the uint16 histograms / Q grow with the batch, the tables do not
-    ncu_dram_bytes_c3 = {"product_hist_weight_grad": 4 * (8 * 33.5e6 + 17.9e6), "product_row_dots": 4 * (8 * 10.1e6 + 17.9e6)}
 
-    @property
-    def ncu_dram_bytes_per_step(self):
-        return self.ncu_dram_bytes_c3 if (self.B, self.S, self.E, self.L) == (64, 128, 256, 4) else {}
+    def traffic_key(self):
+        return "char_transformer_b64" if (self.B, self.S, self.E, self.L) == (64, 128, 256, 4) else None
+
+    def l2_policy(self):
+        """How cold caches are ensured between timed steps: the step's inputs exceed L2, or L2 is flushed."""
+        return "inputs>L2" if getattr(self, "static_input_bytes", 0) > L2_BYTES else "flushed"
 
     def __init__(self, batch=64, context=128, vocab=65, d_model=256, layers=4, heads=4, n_detectors=16, nc=8, npe=4):
         self.B, self.S, self.V, self.E, self.L, self.H = batch, context, vocab, d_model, layers, heads
@@ -499,7 +553,6 @@ class CharTransformerWorkload:
         self.device = device
         self.h2d_bytes = self.htok.numel() * 8
         self.d2h_bytes = 4
-        self.l2_note = "flushed"
 
     allreduce = None
 
@@ -598,6 +651,10 @@ class AttentionLayerWorkload:
     dtype = "f32"
     dominant_kernel = None
 
+    def l2_policy(self):
+        """How cold caches are ensured between timed steps: the step's inputs exceed L2, or L2 is flushed."""
+        return "inputs>L2" if getattr(self, "static_input_bytes", 0) > L2_BYTES else "flushed"
+
     def __init__(self, batch=8, context=128, d_model=256, n_detectors=64, nc=8, npe=4):
         self.B, self.S, self.E, self.Nt, self.Nc, self.Npe = batch, context, d_model, n_detectors, nc, npe
         self.units_per_step = batch * context
@@ -621,7 +678,6 @@ class AttentionLayerWorkload:
         self.device = device
         self.h2d_bytes = (self.hx.numel() + self.hdy.numel()) * 4
         self.d2h_bytes = 4
-        self.l2_note = "flushed"
 
     allreduce = None
 
@@ -729,18 +785,20 @@ class LutInferWorkload:
     unit = "samples/s"
     scaling = "strong"
     dominant_kernel = None
-    # DRAM bytes per step on one GPU at batch 16384 (profiles/lut_infer_b16384.md; fp32: 6 launches of 146 MB)
-    ncu_dram_bytes_b16384 = {"int8_gather": 238.1e6 + 135.8e6, "fc_gather_forward": 6 * 146.0e6, "check_detectors": 478.2e6}
 
-    @property
-    def ncu_dram_bytes_per_step(self):
-        return self.ncu_dram_bytes_b16384 if self.B == 16384 and self.world == 1 else {}
+    def traffic_key(self):
+        return "lut_infer_b16384" if self.B == 16384 and getattr(self, "world", 1) == 1 else None
+
+    def l2_policy(self):
+        """How cold caches are ensured between timed steps: the step's inputs exceed L2, or L2 is flushed."""
+        return "inputs>L2" if getattr(self, "static_input_bytes", 0) > L2_BYTES else "flushed"
 
     def __init__(self, table_dtype="int8", batch=16384, n_inputs=4096, n_detectors=4096, n_anchors=8, n_outputs=64):
         self.kind = table_dtype
         self.dtype = "i8" if table_dtype == "int8" else "f32"
         self.B, self.I, self.Nt, self.Nc, self.O = batch, n_inputs, n_detectors, n_anchors, n_outputs
         self.units_per_step = batch
+        self.static_input_bytes = batch * n_inputs * 4
         self.name = (f"single LUT layer inference, {table_dtype} tables (I={n_inputs}, Nt={n_detectors}, Nc={n_anchors}, "
                      f"O={n_outputs}), batch {batch}")
 
@@ -775,7 +833,6 @@ class LutInferWorkload:
         self.device = device
         self.h2d_bytes = self.hx.numel() * 4
         self.d2h_bytes = 4
-        self.l2_note = "inputs>L2" if self.h2d_bytes > L2_BYTES else "flushed"
         self.world = world
 
     allreduce = None
@@ -855,34 +912,53 @@ WORKLOADS = {
 DEFAULT_WORKLOAD = "sparse_convnet"
 
 
-def cpu_baseline(wl, budget_s=12.0):
-    """Times the CPU oracle on a bounded sample of the workload (rank 0, N=1 only)."""
-    threads = os.cpu_count() or 1
+def workload_config(wl):
+    """The `config` object of the JSON line; both arms print exactly this for the same workload."""
+    return {"workload": wl.name, "l2": wl.l2_policy(), "per_gpu_units": wl.units_per_step}
+
+
+def _sample_sizes(wl):
     per_item = getattr(wl, "S", 1) if wl.unit == "tokens/s" else 1   # units per batch item
-    full = wl.units_per_step // per_item
+    return per_item, wl.units_per_step // per_item
+
+
+def cpu_baseline(wl, budget_s=12.0):
+    """Times the CPU oracle on a bounded sample of the workload (rank 0, N=1 only): all host threads (the figure
+    reported), and one thread on a smaller sample (the reference's own CPU path is single-threaded)."""
+    threads = os.cpu_count() or 1
+    per_item, full = _sample_sizes(wl)
     batch = min(full, 256 if per_item == 1 else 1)
     dt = wl.cpu_step(batch, threads)  # warm-up and calibration
     per_unit = max(dt / batch, 1e-9)
     batch = int(max(batch, min(full, budget_s / 3 / per_unit)))
     times = [wl.cpu_step(batch, threads) for _ in range(3 if per_item == 1 else 1)]
     best = min(times)
+    value = batch * per_item / best
+    # one thread: a sample sized for ~3 s
+    b1 = int(max(1, min(batch, 3.0 / (per_unit * threads))))
+    t1 = wl.cpu_step(b1, 1)
+    single = b1 * per_item / t1
+    what = wl.unit.split("/")[0]
     if getattr(wl, "cpu_note", None):
-        return {"value": batch * per_item / best, "unit": wl.unit, "cores": threads, "kind": "port",
-                "sample": wl.cpu_note + f", OpenMP ({threads} threads)"}
-    return {"value": batch * per_item / best, "unit": wl.unit, "cores": threads, "kind": "port",
-            "sample": f"{batch} batch items ({batch * per_item} {wl.unit.split('/')[0]}) of the same workload, best of "
-                      f"{len(times)}, OpenMP ({threads} threads; the reference's own CPU path is single-threaded)"}
+        sample = wl.cpu_note + f", OpenMP ({threads} threads); one thread: {single:.4g} {wl.unit}"
+    else:
+        sample = (f"{batch} batch items ({batch * per_item} {what}) of the same workload, best of {len(times)}, OpenMP "
+                  f"({threads} threads); one thread (the reference's own CPU path is single-threaded): {single:.4g} "
+                  f"{wl.unit} on {b1} batch items")
+    return {"value": value, "unit": wl.unit, "cores": threads, "kind": "port", "sample": sample,
+            "single_thread_value": single}
 
 
 # ------------------------------------------------------------------------------------ arms
 def run_reference(args):
+    """The reference's CPU implementation of the path as the arm: the C oracle (a port pinned bit for bit to fixtures
+    recorded from the reference's own CPU build) on all host threads, each step a bounded sample of the workload."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     wl = WORKLOADS[args.workload](args.batch)
     threads = os.cpu_count() or 1
-    per_item = getattr(wl, "S", 1) if wl.unit == "tokens/s" else 1   # units per batch item
-    full = wl.units_per_step // per_item
+    per_item, full = _sample_sizes(wl)
     batch = min(full, 256 if per_item == 1 else 1)
     per_unit = max(wl.cpu_step(batch, threads) / batch, 1e-9)
     # each step is a bounded sample so that warmup + steps stay within ~2 minutes in total
@@ -899,12 +975,45 @@ def run_reference(args):
         sample = f"{wl.cpu_note}; CPU oracle (port of the reference CPU path), {threads} threads"
     print(json.dumps({
         "impl": "reference", "metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+        "scaling": getattr(wl, "scaling", "weak"),
         "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic",
-        "config": {"workload": wl.name, "sample": sample},
+        "config": workload_config(wl),
         "cpu_baseline": {"value": value, "unit": wl.unit, "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": wl.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
+
+
+def _attach_data_parallel(wl, world):
+    """Gradient exchange of a data-parallel run: per-parameter all-reduce hooks (or the table average of the
+    Internal policy); returns the sync object (None when there is nothing to exchange)."""
+    import torch
+    if world <= 1:
+        return None
+    # gradients are exchanged per parameter as soon as its backward has run, overlapping the rest of
+    # the backward pass; the workload only waits for the outstanding collectives before it updates
+    from spiky_b200.data_parallel import OverlappedGradientSync
+    sync = OverlappedGradientSync(wl.trainable_parameters(), average=True)
+    wl.allreduce = lambda params: sync.wait()
+    wl.grad_sync = sync
+    if getattr(wl, "internal", False):
+        from spiky_b200.data_parallel import average_internal_policy_weights
+        holder = torch.nn.ModuleList(wl.layers)
+        wl.average_tables = lambda: average_internal_policy_weights(holder)
+    return sync
+
+
+def _replica_check(params, world):
+    """max over parameters of the spread of a checksum over the ranks (0.0: the replicas hold identical tables)."""
+    import torch
+    import torch.distributed as dist
+    if world <= 1 or not params:
+        return None
+    sums = torch.stack([torch.stack([p.detach().double().sum(), p.detach().abs().max().double()]) for p in params])
+    lo, hi = sums.clone(), sums.clone()
+    dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+    dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+    return float((hi - lo).abs().max())
 
 
 def run_ours(args):
@@ -921,46 +1030,46 @@ def run_ours(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
 
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()   # NVML is up and sampling before the warm-up
     wl = WORKLOADS[args.workload](args.batch)
     wl.setup(device, rank)
-    if world > 1:
-        # gradients are exchanged per parameter as soon as its backward has run, overlapping the rest of
-        # the backward pass; the workload only waits for the outstanding collectives before it updates
-        from spiky_b200.data_parallel import OverlappedGradientSync
-        sync = OverlappedGradientSync(wl.trainable_parameters(), average=True)
-        wl.allreduce = lambda params: sync.wait()
-        wl.grad_sync = sync
-        if getattr(wl, "internal", False):
-            from spiky_b200.data_parallel import average_internal_policy_weights
-            holder = torch.nn.ModuleList(wl.layers)
-            wl.average_tables = lambda: average_internal_policy_weights(holder)
-    flush = None
-    if wl.l2_note == "flushed":
-        flush = torch.empty(2 * L2_BYTES, dtype=torch.uint8, device=device)
+    sync = _attach_data_parallel(wl, world)
+    flush = torch.empty(2 * L2_BYTES, dtype=torch.uint8, device=device)
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    def timed_region(step_fn, steps, profile):
-        """Returns (ms per step measured with CUDA events on the current stream, launches)."""
+    def finish_step(w):
+        # exchanges a workload leaves running on a side stream belong to the step that started them
+        if getattr(w, "sharded", False):
+            w.sharded_sync.wait()
+
+    def timed_region(w, steps, profile):
+        """Returns (ms per step measured with CUDA events on the current stream, profiler records, host window)."""
         _native.profiler_reset()
         _native.profiler_enable(profile)
         starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
         stops = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+        do_flush = w.l2_policy() == "flushed"
         barrier()
+        t0 = time.perf_counter()
         for i in range(steps):
-            if flush is not None:
+            if do_flush:
                 flush.zero_()
             starts[i].record()
-            step_fn()
+            w.step_device()
+            finish_step(w)
             stops[i].record()
         barrier()
+        t1 = time.perf_counter()
         ms = sum(a.elapsed_time(b) for a, b in zip(starts, stops)) / steps
         prof = _native.profiler_read()
         _native.profiler_enable(False)
-        return ms, prof
+        return ms, prof, (t0, t1)
 
     if args.profile_only:
         # bare loop for profilers: warm-up + steps of the device-resident step, nothing else
@@ -968,13 +1077,12 @@ def run_ours(args):
             wl.step_device()
         torch.cuda.synchronize()
         return
-    for _ in range(max(args.warmup, 3)):
+    warmup = max(args.warmup, 3)
+    for _ in range(warmup):
         wl.step_device()
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
-    ms_dev, prof = timed_region(wl.step_device, args.steps, profile=True)
-    clocks = sampler.stop() if rank == 0 else None
+        finish_step(wl)
+    ms_dev, prof, window = timed_region(wl, args.steps, profile=True)
+
     def e2e_region(steps):
         """End to end: every step copies its inputs from pinned host memory, runs, and its result is read back on the
         host; the read of step k is taken while step k+1 runs (two result slots), so the device never waits for the
@@ -983,12 +1091,14 @@ def run_ours(args):
         done = [torch.cuda.Event() for _ in range(2)]
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         seen = []
+        do_flush = wl.l2_policy() == "flushed"
         barrier()
         start.record()
         for i in range(steps):
-            if flush is not None:
+            if do_flush:
                 flush.zero_()
             r = wl.step_e2e()
+            finish_step(wl)
             slots[i % 2].copy_(r.detach().reshape(1).float(), non_blocking=True)
             done[i % 2].record()
             if i >= 1:
@@ -1004,11 +1114,55 @@ def run_ours(args):
     e2e_region(2)
     ms_e2e = e2e_region(args.steps)
 
-    t = torch.tensor([ms_dev, ms_e2e], dtype=torch.float64, device=device)
+    # ---- data-parallel evidence: what the exchange costs, how fast the same payload moves alone, replicas identical
+    comm = None
+    if world > 1 and sync is not None and wl.trainable_parameters():
+        params = wl.trainable_parameters()
+        payload = sum(p.numel() * p.element_size() for p in params)
+        sync.paused = True    # same step, gradients stay local: the difference is the exposed part of the exchange
+        for _ in range(2):
+            wl.step_device()
+        ms_local, _, _ = timed_region(wl, max(3, args.steps // 4), profile=False)
+        sync.paused = False
+        bufs = [torch.zeros_like(p) for p in params]
+        iso = []
+        for rep in range(4):
+            barrier()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for t in bufs:
+                dist.all_reduce(t, op=dist.ReduceOp.AVG)
+            b.record()
+            torch.cuda.synchronize()
+            iso.append(a.elapsed_time(b))
+        del bufs
+        comm = {"ms_local": ms_local, "ms_isolated": min(iso[1:]), "payload": payload}
+    replica = _replica_check([p for l in getattr(wl, "layers", []) for p in [l._weights]] or wl.trainable_parameters(), world)
+
+    secondary = None
+    if args.workload == DEFAULT_WORKLOAD and not args.no_secondary:
+        # the LUTTransformer half of the metric, measured in the same process on the same GPUs
+        if sync is not None:
+            sync.remove()
+        del wl.layers
+        torch.cuda.empty_cache()
+        w2 = WORKLOADS["char_transformer"](None)
+        w2.setup(device, rank)
+        sync2 = _attach_data_parallel(w2, world)
+        for _ in range(3):
+            w2.step_device()
+        ms2, _, _ = timed_region(w2, 10, profile=False)
+        secondary = {"ms": ms2, "replica_check": _replica_check(w2.trainable_parameters(), world), "wl": w2}
+
+    t = torch.tensor([ms_dev, ms_e2e, comm["ms_local"] if comm else 0.0, comm["ms_isolated"] if comm else 0.0,
+                      secondary["ms"] if secondary else 0.0], dtype=torch.float64, device=device)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_dev, ms_e2e = t.tolist()
+    ms_dev, ms_e2e, ms_local, ms_isolated, ms_secondary = t.tolist()
+    wait_errors = _native.device_wait_errors()
     if rank == 0:
+        sampler.stop()
+        clocks = sampler.summary(window[0], window[1], ms_dev)
         peak, peak_kind = measured_peaks()
         units = wl.units_per_step * (1 if getattr(wl, "scaling", "weak") == "strong" else world)
         value = units / (ms_dev / 1e3)
@@ -1032,28 +1186,74 @@ def run_ours(args):
         dom_ms = d["ms"] / max(d["timed"], 1)
         dom_ms_per_step = d["ms"] / args.steps
         achieved = alg[dom] * wl.units_per_step / 1e9 / (dom_ms_per_step / 1e3)
+        traffic, traffic_note = ncu_traffic(wl, dom)
         line = {
             "metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": ms_dev, "higher_is_better": True,
+            "warmup": warmup, "ms_per_step": ms_dev, "higher_is_better": True,
             "scaling": getattr(wl, "scaling", "weak"),
             "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic",
-            "config": {"workload": wl.name, "l2": wl.l2_note, "per_gpu_units": wl.units_per_step},
+            "config": workload_config(wl),
             "roofline": {"bound": "hbm", "kernel": dom, "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "peak_kind": peak_kind,
-                         "traffic": (getattr(wl, "ncu_dram_bytes_per_step", {}).get(dom, 0) / max(d["timed"] / args.steps, 1)) or None,
+                         "traffic": (traffic / max(d["timed"] / args.steps, 1)) if traffic else None,
+                         "traffic_source": traffic_note,
                          "algorithmic_bytes_per_launch": alg[dom] * wl.units_per_step / max(d["timed"] / args.steps, 1),
                          "ms_per_launch": dom_ms, "launches_per_step": d["timed"] / args.steps},
             "kernels": per_kernel,
             "e2e": {"value": units / (ms_e2e / 1e3), "unit": wl.unit, "h2d_bytes_per_step": wl.h2d_bytes,
                     "d2h_bytes_per_step": wl.d2h_bytes, "ms_per_step": ms_e2e},
             "gpu_launches": int(launches),
+            "device_wait_errors": int(wait_errors),
             "clocks": clocks,
         }
+        if comm:
+            ring = 2.0 * (world - 1) / world * comm["payload"] / 1e9
+            exposed = max(ms_dev - ms_local, 1e-6)
+            line["comm"] = {
+                "exchange": "all-reduce (NCCL, averaged) of every table gradient, overlapped with the backward pass",
+                "payload_bytes_per_step": comm["payload"], "ms_step_without_exchange": ms_local,
+                "exposed_ms": ms_dev - ms_local, "busbw_gbs": ring / (exposed / 1e3),
+                "isolated_ms": ms_isolated, "isolated_busbw_gbs": ring / (ms_isolated / 1e3),
+                "frac_of_nvlink": ring / (ms_isolated / 1e3) / 900.0,
+                "hidden_frac": 1.0 - (ms_dev - ms_local) / ms_isolated,
+            }
+        if replica is not None:
+            line["replica_check"] = replica
+        if secondary:
+            w2 = secondary["wl"]
+            line["secondary"] = {"metric": w2.metric, "unit": w2.unit, "workload": w2.name, "steps": 10, "warmup": 3,
+                                 "ms_per_step": ms_secondary, "value": w2.units_per_step * world / (ms_secondary / 1e3),
+                                 "scaling": "weak"}
+            if secondary["replica_check"] is not None:
+                line["secondary"]["replica_check"] = secondary["replica_check"]
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(wl)
+            if hasattr(wl, "parity_check"):
+                line["parity_check"] = wl.parity_check(device)
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
+
+
+def ncu_traffic(wl, kernel):
+    """DRAM bytes per step of a kernel family from the ncu capture summarised under profiles/ (dram_traffic.txt, JSON),
+    valid only while the kernel's source file is the one that was profiled (sha256 recorded with the figure)."""
+    import hashlib
+    path = os.path.join(ROOT, "profiles", "dram_traffic.txt")
+    key = getattr(wl, "traffic_key", None)
+    if key is None or not os.path.exists(path):
+        return None, None
+    with open(path) as f:
+        table = json.load(f)
+    rec = table.get(key() if callable(key) else key, {}).get(kernel)
+    if not rec:
+        return None, None
+    src = os.path.join(ROOT, "spiky_b200", "csrc", rec["source"])
+    with open(src, "rb") as f:
+        sha = hashlib.sha256(f.read()).hexdigest()
+    if sha != rec["sha256"]:
+        return None, f"stale: {rec['source']} changed since the capture in {rec['summary']}"
+    return rec["dram_bytes_per_step"], rec["summary"]
 
 
 def main():
@@ -1066,6 +1266,8 @@ def main():
     ap.add_argument("--batch", type=int, default=None,
                     help="override the workload's per-GPU batch (batch sweeps; the default is the configuration's batch)")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU oracle timing (batch sweeps)")
+    ap.add_argument("--no-secondary", action="store_true",
+                    help="skip the character-transformer measurement that the default workload appends")
     ap.add_argument("--profile-only", action="store_true",
                     help="run only warm-up + steps of the device-resident step and exit (for ncu captures)")
     args = ap.parse_args()

@@ -122,7 +122,9 @@ int lutb_nonseq_fc_backward(const lutb_layer_cfg *cfg, int64_t batch, float *wei
  *   - limit: lutb_nonseq_fc_backward_workspace(cfg, batch, LUTB_DW_SORTED) must not exceed
  *     LUTB_STATIC_SCRATCH_BYTES; larger problems are refused with LUTB_ERR_WORKSPACE and a message;
  *   - the first call on a device looks the array's device address up (cudaGetSymbolAddress with that device
- *     current); make that first call before any stream capture begins;
+ *     current); make that first call before any stream capture begins.  Like any first launch it may also make the CUDA runtime
+ *     load the library's module and kernels (lazy loading), which allocates inside the driver: call it once at
+ *     start-up, before the phase that must not allocate;
  *   - every call on a device shares the one array and overwrites what the previous call left there (the part
  *     that must start at zero is cleared on the stream first): two calls that overlap on the GPU, e.g. on
  *     different streams, race; serialise them;
@@ -159,7 +161,30 @@ typedef struct lutb_sparse_index {
     int64_t n_weights;          /* length of the flat weight array */
     int32_t group_size;         /* forward_group_size G */
     int32_t max_count;          /* max of det_count */
+    int32_t max_table_slots;    /* largest "slots per detector table" of chunk_info; 0 = unknown (gather kernels only) */
+    int32_t tables_aligned16;   /* 1 when every detector table starts at a multiple of 4 slots and spans a multiple of
+                                   4 slots, so that it can be bulk-copied with 16-byte granularity; 0 otherwise */
 } lutb_sparse_index;
+
+/*
+ * Kernel family of the forward and input-gradient passes of sparse non-sequence layers (no reference counterpart:
+ * the reference has one kernel per pass).  Process-wide; the environment variable LUTB_SPARSE_KERNELS=auto|gather|staged
+ * sets the initial value.
+ *   GATHER  one warp per (detector chunk, few samples); the selected rows are fetched through L2.  Any layer.
+ *   STAGED  a block owns a range of detectors for 512 samples at a time; whole tables are streamed through a
+ *           shared-memory ring (cp.async.bulk + mbarrier) and the samples' rows are read from there.  fp32 accumulators,
+ *           rows of at most 32 synapses, tables_aligned16, three tables must fit 227 KB; LUTB_ERR_MODE when forced and
+ *           not possible.
+ *   AUTO    STAGED when possible, 2 * batch >= rows per table and the layer has at least 4 detectors per SM, else GATHER.
+ * lutb_device_wait_errors: every device-side wait of the staged kernels is bounded (1 s); a wait that runs out makes
+ * its block leave early (results are then incomplete) and is counted here.  Reads the counter of the current device
+ * and synchronises it; 0 in a healthy run.
+ */
+#define LUTB_SPARSE_AUTO 0
+#define LUTB_SPARSE_GATHER 1
+#define LUTB_SPARSE_STAGED 2
+int lutb_sparse_kernel_select(int kernels);
+int lutb_device_wait_errors(int *count_out);
 
 /*
  * Non-sequence, sparse forward.  Replaces LUTDataManager::forward_step for layers built with lookup

@@ -16,6 +16,8 @@ SKIP_TABLE_GRADIENT = -2.0  # external_lr value: input gradient only (lutb_nonse
 PRODUCT_AUTO, PRODUCT_DIRECT, PRODUCT_HIST = 0, 1, 2
 # de-quantisation rules of the int8 inference path (include/spiky_b200.h)
 INT8_DEQUANT_F32, INT8_DEQUANT_EXACT = 0, 1
+# kernel family of the sparse forward / input-gradient passes (include/spiky_b200.h)
+SPARSE_AUTO, SPARSE_GATHER, SPARSE_STAGED = 0, 1, 2
 
 
 class LayerCfg(ctypes.Structure):
@@ -55,6 +57,8 @@ class SparseIndexC(ctypes.Structure):
         ("n_weights", ctypes.c_int64),
         ("group_size", ctypes.c_int32),
         ("max_count", ctypes.c_int32),
+        ("max_table_slots", ctypes.c_int32),
+        ("tables_aligned16", ctypes.c_int32),
     ]
 
 
@@ -93,6 +97,8 @@ SIGNATURES = {
     "lutb_dense_to_sparse_workspace": (_size, [_i64]),
     "lutb_count_nonzero_32": (_int, [_vp, _i64, _vp, _vp, _size, _vp]),
     "lutb_dense_to_sparse_32": (_int, [_vp, _i64, _vp, _vp, _i64, _vp, _int, _vp, _size, _vp]),
+    "lutb_sparse_kernel_select": (_int, [_int]),
+    "lutb_device_wait_errors": (_int, [ctypes.POINTER(_int)]),
     "lutb_nonseq_sparse_forward": (_int, [_cfgp, _spp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "lutb_nonseq_sparse_backward": (_int, [_cfgp, _spp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _dbl, _vp]),
     "lutb_nonseq_sparse_table_grad": (_int, [_cfgp, _spp, _i64, _vp, _vp, _int, _vp, _dbl, _i64, _i64, _vp]),
@@ -151,3 +157,15 @@ def profiler_read():
         check(L.lutb_profiler_read(k, ctypes.byref(ms), ctypes.byref(timed), ctypes.byref(launches)))
         out[L.lutb_profiler_kernel_name(k).decode()] = {"ms": ms.value, "timed": timed.value, "launches": launches.value}
     return out
+
+
+def sparse_kernel_select(kernels):
+    """Force the gather or the staged kernels for sparse layers (SPARSE_AUTO restores the library's choice)."""
+    check(lib().lutb_sparse_kernel_select(int(kernels)))
+
+
+def device_wait_errors():
+    """Bounded device-side waits that ran out on the current device (0 in a healthy run); synchronises the device."""
+    n = _int(0)
+    check(lib().lutb_device_wait_errors(ctypes.byref(n)))
+    return n.value

@@ -2,27 +2,16 @@
 // Each table row holds one weight per target of its detector; all rows of a detector share the target
 // list, so the layer is a set of small fully connected tables whose outputs are scattered to shared
 // output cells.
+#include <atomic>
+#include <cstdlib>
+#include <cstring>
+
 #include "lutb_common.cuh"
 #include "nonseq_fc.cuh"
+#include "sparse_staged.cuh"
+#include "sparse_view.cuh"
 
 namespace lutb {
-
-struct SparseView {
-    const int64_t *det_wbase;
-    const int32_t *det_stride;
-    const int32_t *det_count;
-    const int32_t *det_sstart;
-    const int32_t *syn_target;
-    const int4 *chunks;   // two int4 per chunk, see lutb_sparse_index::chunk_info
-    int64_t n_chunks;
-    int32_t group;
-    int32_t group_shift;  // log2(group) when group is a power of two, else -1
-};
-
-__device__ __forceinline__ int hole_offset(int p, const SparseView &sp) {
-    // two unused slots in front of every group of `group` synapses (the first pair lies before the row base)
-    return 2 * (sp.group_shift >= 0 ? (p >> sp.group_shift) : (p / sp.group));
-}
 
 // The training kernels give one warp to a (chunk, run of kSampleRun samples) pair.  A chunk is a run of
 // up to 32 consecutive detectors that share one target list (the detectors of one group) and whose
@@ -36,21 +25,6 @@ __device__ __forceinline__ int hole_offset(int p, const SparseView &sp) {
 // sample are in flight together.  Rows of up to LG synapses use LG-lane groups (NG = 32 / LG groups
 // take detectors round-robin).
 constexpr int kSampleRun = 4;
-
-struct ChunkStatic {
-    int det0, ndet, toff, P, stride, table;
-    int64_t wbase0;
-};
-
-__device__ __forceinline__ ChunkStatic load_chunk(const SparseView &sp, int64_t c) {
-    const int4 a = __ldg(sp.chunks + 2 * c);
-    const int4 w = __ldg(sp.chunks + 2 * c + 1);
-    ChunkStatic cs;
-    cs.det0 = a.x; cs.ndet = a.y; cs.toff = a.z; cs.P = a.w;
-    cs.stride = w.x; cs.table = w.y;
-    cs.wbase0 = (int64_t)(((uint64_t)(uint32_t)w.w << 32) | (uint32_t)w.z);
-    return cs;
-}
 
 // With 512 samples over 256-row tables every row is touched about twice per step, so half of the row gathers are
 // compulsory DRAM misses at random addresses.  Each warp therefore asks L2 for its share of the tables of the
@@ -444,14 +418,34 @@ __global__ void sparse_input_grad_fixed_kernel(SparseView sp, const float *__res
     }
 }
 
-static SparseView make_view(const lutb_sparse_index *sp) {
-    SparseView v;
-    v.det_wbase = sp->det_wbase; v.det_stride = sp->det_stride; v.det_count = sp->det_count;
-    v.det_sstart = sp->det_sstart; v.syn_target = sp->syn_target;
-    v.chunks = reinterpret_cast<const int4 *>(sp->chunk_info); v.n_chunks = sp->n_chunks; v.group = sp->group_size;
-    v.group_shift = -1;
-    for (int s = 0; s < 31; s++) if ((1 << s) == sp->group_size) v.group_shift = s;
+// Kernel family of the forward and input-gradient passes: the library's choice, or forced by
+// lutb_sparse_kernel_select / the LUTB_SPARSE_KERNELS environment variable (auto, gather, staged).
+static std::atomic<int> g_sparse_kernels{-1};
+
+static int sparse_kernels() {
+    int v = g_sparse_kernels.load(std::memory_order_relaxed);
+    if (v >= 0) return v;
+    v = LUTB_SPARSE_AUTO;
+    if (const char *e = getenv("LUTB_SPARSE_KERNELS")) {
+        if (!strcmp(e, "gather")) v = LUTB_SPARSE_GATHER;
+        else if (!strcmp(e, "staged")) v = LUTB_SPARSE_STAGED;
+    }
+    g_sparse_kernels.store(v, std::memory_order_relaxed);
     return v;
+}
+
+// 1: run the staged kernels, 0: the gather kernels, < 0: staged was forced but cannot run this layer.
+static int use_staged(const lutb_layer_cfg *cfg, const lutb_sparse_index *sp, int64_t batch, const float *weights) {
+    const int v = sparse_kernels();
+    if (v == LUTB_SPARSE_GATHER) return 0;
+    const bool possible = sparse_staged_possible(cfg, sp, weights);
+    if (v == LUTB_SPARSE_STAGED) {
+        LUTB_REQUIRE(possible, LUTB_ERR_MODE,
+                     "the staged sparse kernels need fp32 accumulators, rows of at most 32 synapses and 16-byte aligned "
+                     "detector tables of which three fit shared memory");
+        return 1;
+    }
+    return possible && sparse_staged_preferred(cfg, sp, batch) ? 1 : 0;
 }
 
 static int validate_sparse(const lutb_sparse_index *sp) {
@@ -478,6 +472,13 @@ static int chunk_grid(int64_t items, unsigned *blocks) {
 
 using namespace lutb;
 
+extern "C" int lutb_sparse_kernel_select(int kernels) {
+    LUTB_REQUIRE(kernels == LUTB_SPARSE_AUTO || kernels == LUTB_SPARSE_GATHER || kernels == LUTB_SPARSE_STAGED, LUTB_ERR_MODE,
+                 "kernels must be LUTB_SPARSE_AUTO, LUTB_SPARSE_GATHER or LUTB_SPARSE_STAGED");
+    g_sparse_kernels.store(kernels);
+    return LUTB_OK;
+}
+
 extern "C" int lutb_nonseq_sparse_forward(const lutb_layer_cfg *cfg, const lutb_sparse_index *sp, int64_t batch,
                                           const float *weights, const float *x, const int32_t *anchors, float *y,
                                           int32_t *idx, float *min_delta, int32_t *min_k, void *stream) {
@@ -494,6 +495,9 @@ extern "C" int lutb_nonseq_sparse_forward(const lutb_layer_cfg *cfg, const lutb_
     rc = launch_check_detectors(x, batch, cfg->n_inputs, anchors, cfg->n_detectors, cfg->n_anchors, cfg->cmp_eps, idx,
                                 min_delta, min_k, st);
     if (rc) return rc;
+    const int staged = use_staged(cfg, sp, batch, weights);
+    if (staged < 0) return staged;
+    if (staged) return launch_sparse_forward_staged(cfg, sp, batch, weights, idx, y, st);
     SparseView v = make_view(sp);
     unsigned blocks;
     rc = chunk_grid(((batch + kSampleRun - 1) / kSampleRun) * sp->n_chunks, &blocks);
@@ -551,7 +555,12 @@ extern "C" int lutb_nonseq_sparse_backward(const lutb_layer_cfg *cfg, const lutb
     // three layers of the conv-net step): the reductions of the fused kernel queue in front of its own row gathers.  With
     // in-place SGD the order is also required: every sample must read the weights before any of them is modified.
     // dX == nullptr: the caller does not want the input gradient (first layer of a network).
-    if (dX != nullptr) {
+    const int staged = dX != nullptr ? use_staged(cfg, sp, batch, weights) : 0;
+    if (staged < 0) return staged;
+    if (staged) {
+        rc = launch_sparse_input_grad_staged(cfg, sp, batch, weights, dY, anchors, idx, min_delta, min_k, dX, st);
+        if (rc) return rc;
+    } else if (dX != nullptr) {
         KernelScope scope(K_SPARSE_INPUT_GRAD, st);
         if (cfg->int_mode) {
             const int64_t total = batch * Nt;

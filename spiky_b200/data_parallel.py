@@ -86,6 +86,7 @@ class OverlappedGradientSync:
     def __init__(self, params, group=None, average=True):
         self.average = average
         self.handles = []
+        self.paused = False   # True: gradients stay local (used to time a step without its exchange)
         self.enabled = dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1
         self.world = dist.get_world_size(group) if self.enabled else 1
         self._hooks = []
@@ -107,6 +108,9 @@ class OverlappedGradientSync:
             return
         if g.is_sparse:
             p.grad = g = g.to_dense()
+        if self.paused:
+            self.handles.append((p, None))
+            return
         op = dist.ReduceOp.SUM
         if self.average:
             if self._nccl:
@@ -117,7 +121,8 @@ class OverlappedGradientSync:
 
     def wait(self):
         for _, h in self.handles:
-            h.wait()
+            if h is not None:
+                h.wait()
         self.handles = []
 
     def wait_each(self):
@@ -125,7 +130,8 @@ class OverlappedGradientSync:
         an update applied per parameter overlaps the exchanges that are still in flight."""
         handles, self.handles = self.handles, []
         for p, h in handles:
-            h.wait()
+            if h is not None:
+                h.wait()
             yield p
 
     def remove(self):

@@ -115,8 +115,11 @@ class LUTTransformer(nn.Module):
     def to(self, *args, **kwargs):
         device = kwargs.get("device", None)
         if device is None and args and not isinstance(args[0], torch.dtype):
+            device = args[0]
+        # strings and ordinals name a device in both the positional and the keyword form
+        if isinstance(device, (str, int)) and not isinstance(device, bool):
             try:
-                device = torch.device(args[0]) if isinstance(args[0], str) else args[0]
+                device = torch.device(device)
             except (RuntimeError, ValueError):
                 device = None
         super().to(*args, **kwargs)

@@ -219,6 +219,15 @@ class SparseIndex:
             assert int(self.syn_target.min()) >= 0 and int(self.syn_target.max()) < n_outputs
         self.chunk_info = self._build_chunks()
         self.n_chunks = self.chunk_info.shape[0]
+        # what the staged kernels need to know on the host: the largest detector table, and whether every table can
+        # be bulk-copied with 16-byte granularity (start and size multiples of 4 slots)
+        if self.n_chunks:
+            ci = self.chunk_info.to(torch.int64)
+            wbase0 = (ci[:, 6] & 0xFFFFFFFF) | (ci[:, 7] << 32)
+            self.max_table_slots = int(ci[:, 5].max().item())
+            self.tables_aligned16 = int(bool(((wbase0 % 4 == 0) & (ci[:, 5] % 4 == 0)).all().item()))
+        else:
+            self.max_table_slots, self.tables_aligned16 = 0, 0
 
     CHUNK = 32  # detectors per chunk = lanes of a warp
 
@@ -400,7 +409,7 @@ class SparseIndex:
             det_count=self.det_count.data_ptr(), det_sstart=self.det_sstart.data_ptr(),
             syn_det=self.syn_det.data_ptr(), syn_target=self.syn_target.data_ptr(),
             chunk_info=self.chunk_info.data_ptr(), n_chunks=self.n_chunks, n_syn_per_sample=self.n_syn_per_sample, n_weights=self.n_weights, group_size=self.group_size,
-            max_count=self.max_count)
+            max_count=self.max_count, max_table_slots=self.max_table_slots, tables_aligned16=self.tables_aligned16)
 
     def nbytes(self):
         return sum(getattr(self, n).numel() * getattr(self, n).element_size() for n in self._TENSORS)
