@@ -1144,7 +1144,8 @@ def run_ours(args):
         # the LUTTransformer half of the metric, measured in the same process on the same GPUs
         if sync is not None:
             sync.remove()
-        del wl.layers
+        for prm in wl.trainable_parameters():
+            prm.grad = None
         torch.cuda.empty_cache()
         w2 = WORKLOADS["char_transformer"](None)
         w2.setup(device, rank)

@@ -100,11 +100,31 @@ size_t lutb_nonseq_fc_backward_workspace(const lutb_layer_cfg *cfg, int64_t batc
  *       the input-gradient kernels: for a first layer whose input needs no gradient.
  *   external_lr < 0: dW fp32 [Nt * 2^Nc * O] receives lr_meta * dY rows (accumulated into).
  *   external_lr >= 0: dW must be NULL and weights are updated in place by -external_lr * lr_meta * dY.
+ *   external_lr == LUTB_SKIP_TABLE_GRADIENT (-2.0, dW must be NULL): only the input gradient; the caller takes the
+ *       table gradient in another form (lutb_nonseq_fc_table_grad_rows).
  */
 int lutb_nonseq_fc_backward(const lutb_layer_cfg *cfg, int64_t batch, float *weights, const float *dY,
                             const int32_t *anchors, const int32_t *idx, const float *min_delta,
                             const int32_t *min_k, float *dX, float *dW, double external_lr, int dw_variant,
                             void *workspace, size_t workspace_bytes, void *stream);
+
+/*
+ * Table gradient of a non-sequence, fully connected layer as a list of touched rows, for the Sparse gradient policy.
+ * The reference forms the dense gradient and compacts it afterwards (LUTLayerBasic._process_gradients,
+ * src/spiky/lut/LUTLayer.py:567-609 -> DenseToSparseConverterNative, spiky_cuda/torch_utils/torch_utils.cu:29-322); a
+ * step touches at most batch rows per detector, so here the list comes straight from the table-gradient pass and
+ * nothing of the size of the tables is written or read:
+ *   row_ids int64 [capacity]           detector * 2^Nc + row of every touched row, ascending
+ *   values  fp32  [capacity * O]       the row's gradient: lr_meta * sum over the samples that selected it of dY[b, :]
+ *                                      (|dY| > 1e-17), samples added in ascending order (as LUTB_DW_SORTED does)
+ *   count_out int64 (device)           number of touched rows; rows beyond capacity are counted, not written
+ * capacity >= min(batch, 2^Nc) * Nt always suffices.  fp32 accumulators only; the workspace (256-byte aligned) must
+ * hold lutb_nonseq_fc_table_grad_rows_workspace(cfg, batch) bytes.
+ */
+size_t lutb_nonseq_fc_table_grad_rows_workspace(const lutb_layer_cfg *cfg, int64_t batch);
+int lutb_nonseq_fc_table_grad_rows(const lutb_layer_cfg *cfg, int64_t batch, const float *dY, const int32_t *idx,
+                                   int64_t *row_ids, float *values, int64_t capacity, int64_t *count_out,
+                                   void *workspace, size_t workspace_bytes, void *stream);
 
 /*
  * Non-sequence, fully connected backward for callers that must not allocate device memory.
@@ -294,6 +314,34 @@ int lutb_concat_backward(const lutb_layer_cfg *cfg, int64_t batch, float *weight
                          const int32_t *anchors, const int32_t *idx, const float *min_delta, const int32_t *min_k,
                          const int32_t *pos_idx, const float *pos_min_delta, const int32_t *pos_min_k, float *dX,
                          float *dPE, float *dW, double external_lr, void *stream);
+
+/*
+ * The stages of the concatenation-mode layer as separate entry points, for ranks that shard the QUERY positions of a
+ * long sequence (no counterpart in the single-process reference; the arithmetic is that of the kernels named):
+ *   lutb_check_detectors       table index (and, with min_delta / min_k, the minimum-margin pair) of `rows` input rows:
+ *                              check_detectors[_eval]_logic, lut_runtime_kernels_logic.proto:1050-1158.  A rank runs
+ *                              it on its own tokens; the ranks then all-gather idx / min_delta / min_k.
+ *   lutb_check_positional      positional indices, check_positional_embeddings[_eval]_logic, proto:1709-1805.
+ *   lutb_concat_pairs_forward  fill_outputs_fully_connected_seq_logic (proto:1807-1904) for the queries
+ *                              j in [j_begin, j_end) only: y[b, j, :] += sum over keys i < j of the pair's row.  idx
+ *                              int32 [batch * S * Nt] holds ALL tokens; rows of y outside the range are untouched, so
+ *                              the ranks' outputs are disjoint.
+ *   lutb_concat_pairs_backward propagate_through_detectors_seq_fc_logic (proto:3629-3835) and
+ *                              gather_w_gradients_seq_fc_cpu_logic (proto:3944-4044) for the pairs whose query lies in
+ *                              [j_begin, j_end): dX (all S tokens: keys of other ranks' tokens receive gradient too),
+ *                              dPE and dW are PARTIAL sums that the ranks add up.  fp32 accumulators only.
+ * Running the two pair stages over [0, S) is lutb_concat_forward / lutb_concat_backward without their index stage.
+ */
+int lutb_check_detectors(const lutb_layer_cfg *cfg, int64_t rows, const float *x, const int32_t *anchors, int32_t *idx,
+                         float *min_delta, int32_t *min_k, void *stream);
+int lutb_check_positional(const lutb_layer_cfg *cfg, const float *pos_embeddings, int32_t *pos_idx, float *pos_min_delta,
+                          int32_t *pos_min_k, void *stream);
+int lutb_concat_pairs_forward(const lutb_layer_cfg *cfg, int64_t batch, const float *weights, const int32_t *idx,
+                              const int32_t *pos_idx, float *y, int32_t j_begin, int32_t j_end, void *stream);
+int lutb_concat_pairs_backward(const lutb_layer_cfg *cfg, int64_t batch, float *weights, const float *dY,
+                               const int32_t *anchors, const int32_t *idx, const float *min_delta, const int32_t *min_k,
+                               const int32_t *pos_idx, const float *pos_min_delta, const int32_t *pos_min_k, float *dX,
+                               float *dPE, float *dW, double external_lr, int32_t j_begin, int32_t j_end, void *stream);
 
 /*
  * Concatenation-mode sequence layer with sparse lookup -> output connectivity (the reference builds it with

@@ -259,6 +259,19 @@ def concat_forward(W, x, pe, anchors, n_detectors, n_anchors, n_outputs, pos_dim
     return y, dict(idx=idx, min_delta=md, min_k=mk, pidx=pidx, pmin=pm, pmin_k=pk)
 
 
+def concat_pairs_forward(W, idx, pidx, batch, seq_len, n_detectors, n_anchors, n_outputs, pos_dim, int_mode=False,
+                         int_rescaler=0.001):
+    """The pair stage of ``forward_step_concat`` alone, from the table indices of all tokens
+    (idx int32 [B*S, Nt], pidx int32 [(S-1)*Nt] or None); returns y [B,S,O]."""
+    y = np.zeros((batch, seq_len, n_outputs), np.float32)
+    W = _f32(W).reshape(-1)
+    idx = _i32(idx)
+    pidx = None if pidx is None else _i32(pidx)
+    lib().orc_concat_forward(_ptr(W), _ptr(idx), _ptr(pidx), _ptr(y), _l(batch), _i(seq_len), _i(n_outputs),
+                             _i(n_detectors), _i(n_anchors), _i(pos_dim), _i(int(int_mode)), _d(int_rescaler))
+    return y
+
+
 def concat_backward(W, dY, anchors, state, n_inputs, n_anchors, pos_dim, lr_meta=1.0, external_lr=-1.0,
                     forward_group_size=32, int_mode=False, int_rescaler=0.001):
     """One ``backward_backprop_concat``; returns (dX [B,S,I], dW or None, dPE [(S-1)*Nt*Npe] or None)."""

@@ -84,6 +84,10 @@ SIGNATURES = {
     "lutb_nonseq_fc_backward": (_int, [_cfgp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _dbl, _int, _vp, _size, _vp]),
     "lutb_concat_forward": (_int, [_cfgp, _i64] + [_vp] * 12),
     "lutb_concat_backward": (_int, [_cfgp, _i64] + [_vp] * 12 + [_dbl, _vp]),
+    "lutb_check_detectors": (_int, [_cfgp, _i64, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "lutb_check_positional": (_int, [_cfgp, _vp, _vp, _vp, _vp, _vp]),
+    "lutb_concat_pairs_forward": (_int, [_cfgp, _i64, _vp, _vp, _vp, _vp, ctypes.c_int32, ctypes.c_int32, _vp]),
+    "lutb_concat_pairs_backward": (_int, [_cfgp, _i64] + [_vp] * 12 + [_dbl, ctypes.c_int32, ctypes.c_int32, _vp]),
     "lutb_concat_sparse_forward": (_int, [_cfgp, _spp, _i64] + [_vp] * 12),
     "lutb_concat_sparse_backward": (_int, [_cfgp, _spp, _i64] + [_vp] * 12 + [_dbl, _vp]),
     "lutb_product_workspace": (_size, [_cfgp, _i64, ctypes.c_int32, _int]),
@@ -91,6 +95,8 @@ SIGNATURES = {
                                     _int, _vp, _size, _vp]),
     "lutb_product_backward": (_int, [_cfgp, _i64, ctypes.c_int32, _vp, _vp, _vp, ctypes.c_int32, ctypes.c_int32, _vp, _vp,
                                      _vp, _vp, _vp, _vp, _vp, _dbl, _int, _vp, _size, _vp]),
+    "lutb_nonseq_fc_table_grad_rows_workspace": (_size, [_cfgp, _i64]),
+    "lutb_nonseq_fc_table_grad_rows": (_int, [_cfgp, _i64, _vp, _vp, _vp, _vp, _i64, _vp, _vp, _size, _vp]),
     "lutb_nonseq_fc_backward_noalloc": (_int, [_cfgp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _dbl, _vp]),
     "lutb_infer_int8_accumulate": (_int, [_cfgp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _int, _vp]),
     "lutb_fixed_to_float": (_int, [_vp, _i64, _dbl, _vp]),

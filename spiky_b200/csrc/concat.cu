@@ -45,7 +45,7 @@ template <bool INT_MODE>
 __global__ void __launch_bounds__(256) concat_forward_kernel(const float *__restrict__ W, const int32_t *__restrict__ idx,
                                                             const int32_t *__restrict__ pidx, float *__restrict__ y,
                                                             int S, int n_outputs, int n_detectors, int nc, int npe,
-                                                            double fixed_scale) {
+                                                            double fixed_scale, int j_begin, int j_end) {
     extern __shared__ __align__(16) int32_t ismem[];
     const int t = blockIdx.x;
     const int64_t b = blockIdx.y;
@@ -59,7 +59,8 @@ __global__ void __launch_bounds__(256) concat_forward_kernel(const float *__rest
     const float *Wt = W + (size_t)t * rows * n_outputs;
     const bool vec4 = (n_outputs % 4 == 0) && ((reinterpret_cast<uintptr_t>(W) & 15) == 0) &&
                       ((reinterpret_cast<uintptr_t>(y) & 15) == 0);
-    for (int j = 1 + warp; j < S; j += nwarps) {
+    // queries [j_begin, j_end): the whole sequence, or one rank's share when the queries are sharded
+    for (int j = max(1, j_begin) + warp; j < j_end; j += nwarps) {
         const int32_t Q = Ks[j];
         float *yj = y + ((size_t)b * S + j) * n_outputs;
         if (vec4) {
@@ -115,7 +116,7 @@ __global__ void __launch_bounds__(256) concat_backward_kernel(const float *__res
                                                              const int32_t *__restrict__ pmin_k, float *__restrict__ dX,
                                                              float *__restrict__ dPE, float *__restrict__ target, int S,
                                                              int n_inputs, int n_outputs, int n_detectors, int nc, int npe,
-                                                             double lr) {
+                                                             double lr, int j_begin, int j_end) {
     extern __shared__ __align__(16) int32_t ismem[];
     const int t = blockIdx.x;
     const int64_t b = blockIdx.y;
@@ -144,7 +145,7 @@ __global__ void __launch_bounds__(256) concat_backward_kernel(const float *__res
     float *Tt = DO_DW ? target + (size_t)t * rows * n_outputs : nullptr;
     const bool vec4 = (n_outputs % 4 == 0) && ((reinterpret_cast<uintptr_t>(W) & 15) == 0) &&
                       ((reinterpret_cast<uintptr_t>(target) & 15) == 0);
-    for (int j = 1 + warp; j < S; j += nwarps) {
+    for (int j = max(1, j_begin) + warp; j < j_end; j += nwarps) {
         const float *dyj = dY + ((size_t)b * S + j) * n_outputs;
         for (int o = lane; o < o_pad; o += 32) dy_s[o] = o < n_outputs ? __ldg(dyj + o) : 0.f;
         __syncwarp();
@@ -468,6 +469,144 @@ static int validate_concat(const lutb_layer_cfg *cfg, int64_t batch) {
 
 using namespace lutb;
 
+static int launch_check_positional(const lutb_layer_cfg *cfg, const float *pos_embeddings, int32_t *pos_idx,
+                                   float *pos_min_delta, int32_t *pos_min_k, cudaStream_t st) {
+    const int64_t n = (int64_t)(cfg->seq_len - 1) * cfg->n_detectors;
+    const bool train = pos_min_delta != nullptr;
+    KernelScope scope(K_CHECK_POSITIONAL, st);
+    if (train) check_positional_kernel<true><<<(unsigned)((n + 127) / 128), 128, 0, st>>>(pos_embeddings, n, cfg->pos_dim, cfg->cmp_eps, pos_idx, pos_min_delta, pos_min_k);
+    else check_positional_kernel<false><<<(unsigned)((n + 127) / 128), 128, 0, st>>>(pos_embeddings, n, cfg->pos_dim, cfg->cmp_eps, pos_idx, nullptr, nullptr);
+    LUTB_LAUNCH_CHECK();
+    return LUTB_OK;
+}
+
+static int launch_concat_pairs_forward(const lutb_layer_cfg *cfg, int64_t batch, const float *weights, const int32_t *idx,
+                                       const int32_t *pos_idx, float *y, int j_begin, int j_end, cudaStream_t st) {
+    const int S = cfg->seq_len, npe = cfg->pos_dim, Nt = cfg->n_detectors;
+    const size_t smem = (size_t)(2 * S) * 4;
+    LUTB_REQUIRE(smem <= (size_t)kMaxSmemPerBlock - 1024, LUTB_ERR_SHAPE, "sequence too long for the sequence kernels");
+    dim3 grid((unsigned)Nt, (unsigned)batch);
+    KernelScope scope(K_CONCAT_FORWARD, st);
+    if (cfg->int_mode) {
+        if (smem > 48 * 1024) LUTB_CUDA(cudaFuncSetAttribute(concat_forward_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        concat_forward_kernel<true><<<grid, 256, smem, st>>>(weights, idx, pos_idx, y, S, cfg->n_outputs, Nt, cfg->n_anchors, npe, cfg->int_rescaler, j_begin, j_end);
+    } else {
+        if (smem > 48 * 1024) LUTB_CUDA(cudaFuncSetAttribute(concat_forward_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        concat_forward_kernel<false><<<grid, 256, smem, st>>>(weights, idx, pos_idx, y, S, cfg->n_outputs, Nt, cfg->n_anchors, npe, cfg->int_rescaler, j_begin, j_end);
+    }
+    LUTB_LAUNCH_CHECK();
+    return LUTB_OK;
+}
+
+// fp32 accumulators only
+static int launch_concat_pairs_backward(const lutb_layer_cfg *cfg, int64_t batch, float *weights, const float *dY,
+                                        const int32_t *anchors, const int32_t *idx, const float *min_delta,
+                                        const int32_t *min_k, const int32_t *pos_idx, const float *pos_min_delta,
+                                        const int32_t *pos_min_k, float *dX, float *dPE, float *dW, double external_lr,
+                                        int j_begin, int j_end, cudaStream_t st) {
+    const int S = cfg->seq_len, npe = cfg->pos_dim, Nt = cfg->n_detectors, O = cfg->n_outputs, Nc = cfg->n_anchors;
+    double lr = cfg->lr_meta;
+    if (external_lr >= 0.0) lr *= -(double)(float)external_lr;
+    const int2 *an = reinterpret_cast<const int2 *>(anchors);
+    const int warps = 8;
+    const size_t smem = ((size_t)((6 * S + 3) & ~3) + (size_t)warps * ((O + 3) & ~3)) * 4;
+    LUTB_REQUIRE(smem <= (size_t)kMaxSmemPerBlock - 1024, LUTB_ERR_SHAPE, "sequence too long for the sequence kernels");
+    dim3 grid((unsigned)Nt, (unsigned)batch);
+#define LUTB_CONCAT_BWD(DX, DWF, TARGET)                                                                                  \
+    do {                                                                                                                  \
+        if (smem > 48 * 1024) LUTB_CUDA(cudaFuncSetAttribute(concat_backward_kernel<DX, DWF>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+        concat_backward_kernel<DX, DWF><<<grid, warps * 32, smem, st>>>(weights, dY, an, idx, min_delta, min_k, pos_idx, pos_min_delta, pos_min_k, dX, dPE, TARGET, S, cfg->n_inputs, O, Nt, Nc, npe, lr, j_begin, j_end); \
+    } while (0)
+    if (external_lr >= 0.0) {
+        {
+            KernelScope scope(K_CONCAT_BACKWARD, st);
+            LUTB_CONCAT_BWD(true, false, nullptr);
+        }
+        LUTB_LAUNCH_CHECK();
+        KernelScope scope(K_CONCAT_WEIGHT_UPDATE, st);
+        LUTB_CONCAT_BWD(false, true, weights);
+    } else {
+        KernelScope scope(K_CONCAT_BACKWARD, st);
+        LUTB_CONCAT_BWD(true, true, dW);
+    }
+#undef LUTB_CONCAT_BWD
+    LUTB_LAUNCH_CHECK();
+    return LUTB_OK;
+}
+
+extern "C" int lutb_check_detectors(const lutb_layer_cfg *cfg, int64_t rows, const float *x, const int32_t *anchors,
+                                    int32_t *idx, float *min_delta, int32_t *min_k, void *stream) {
+    int rc = validate_cfg(cfg);
+    if (rc) return rc;
+    LUTB_REQUIRE(rows > 0, LUTB_ERR_SHAPE, "no input rows");
+    LUTB_REQUIRE(x && anchors && idx, LUTB_ERR_NULL, "a required tensor pointer is NULL");
+    LUTB_REQUIRE((min_delta == nullptr) == (min_k == nullptr), LUTB_ERR_MODE,
+                 "min_anchor_deltas and min_anchor_delta_indices must be given together");
+    return launch_check_detectors(x, rows, cfg->n_inputs, anchors, cfg->n_detectors, cfg->n_anchors, cfg->cmp_eps, idx,
+                                  min_delta, min_k, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int lutb_check_positional(const lutb_layer_cfg *cfg, const float *pos_embeddings, int32_t *pos_idx,
+                                     float *pos_min_delta, int32_t *pos_min_k, void *stream) {
+    int rc = validate_cfg(cfg);
+    if (rc) return rc;
+    LUTB_REQUIRE(cfg->seq_len > 1 && cfg->pos_dim > 0, LUTB_ERR_MODE, "the layer has no positional embeddings");
+    LUTB_REQUIRE(pos_embeddings && pos_idx, LUTB_ERR_NULL, "positional embeddings / indices are NULL");
+    LUTB_REQUIRE((pos_min_delta == nullptr) == (pos_min_k == nullptr), LUTB_ERR_MODE,
+                 "positional min deltas and their indices must be given together");
+    return launch_check_positional(cfg, pos_embeddings, pos_idx, pos_min_delta, pos_min_k, static_cast<cudaStream_t>(stream));
+}
+
+static int validate_query_range(const lutb_layer_cfg *cfg, int j_begin, int j_end) {
+    LUTB_REQUIRE(j_begin >= 0 && j_begin <= j_end && j_end <= cfg->seq_len, LUTB_ERR_SHAPE,
+                 "query range [%d, %d) outside [0, %d)", j_begin, j_end, cfg->seq_len);
+    return LUTB_OK;
+}
+
+extern "C" int lutb_concat_pairs_forward(const lutb_layer_cfg *cfg, int64_t batch, const float *weights,
+                                         const int32_t *idx, const int32_t *pos_idx, float *y, int32_t j_begin,
+                                         int32_t j_end, void *stream) {
+    int rc = validate_concat(cfg, batch);
+    if (rc) return rc;
+    rc = validate_query_range(cfg, j_begin, j_end);
+    if (rc) return rc;
+    LUTB_REQUIRE(weights && idx && y, LUTB_ERR_NULL, "a required tensor pointer is NULL");
+    LUTB_REQUIRE(cfg->pos_dim == 0 || pos_idx, LUTB_ERR_NULL, "positional indices are NULL");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (j_begin == j_end) return LUTB_OK;
+    rc = launch_concat_pairs_forward(cfg, batch, weights, idx, pos_idx, y, j_begin, j_end, st);
+    if (rc) return rc;
+    if (cfg->int_mode) {
+        // only the rows of the range hold fixed-point accumulators
+        for (int64_t b = 0; b < batch; b++) {
+            rc = launch_fixed_to_float(y + (b * cfg->seq_len + j_begin) * (int64_t)cfg->n_outputs,
+                                       (int64_t)(j_end - j_begin) * cfg->n_outputs, cfg->int_rescaler, st);
+            if (rc) return rc;
+        }
+    }
+    return LUTB_OK;
+}
+
+extern "C" int lutb_concat_pairs_backward(const lutb_layer_cfg *cfg, int64_t batch, float *weights, const float *dY,
+                                          const int32_t *anchors, const int32_t *idx, const float *min_delta,
+                                          const int32_t *min_k, const int32_t *pos_idx, const float *pos_min_delta,
+                                          const int32_t *pos_min_k, float *dX, float *dPE, float *dW, double external_lr,
+                                          int32_t j_begin, int32_t j_end, void *stream) {
+    int rc = validate_concat(cfg, batch);
+    if (rc) return rc;
+    rc = validate_query_range(cfg, j_begin, j_end);
+    if (rc) return rc;
+    LUTB_REQUIRE(cfg->int_mode == 0, LUTB_ERR_MODE, "the query-range backward needs fp32 accumulators");
+    LUTB_REQUIRE(weights && dY && anchors && idx && min_delta && min_k && dX, LUTB_ERR_NULL, "a required tensor pointer is NULL");
+    LUTB_REQUIRE(cfg->pos_dim == 0 || (pos_idx && pos_min_delta && pos_min_k && dPE), LUTB_ERR_NULL, "positional tensors are NULL");
+    LUTB_REQUIRE(!(external_lr >= 0.0 && dW != nullptr), LUTB_ERR_MODE,
+                 "in internal weight gradients mode w_weights_gradients should be nullptr");
+    LUTB_REQUIRE(!(external_lr < 0.0 && dW == nullptr), LUTB_ERR_NULL, "w_weights_gradients is NULL");
+    if (j_begin == j_end) return LUTB_OK;
+    return launch_concat_pairs_backward(cfg, batch, weights, dY, anchors, idx, min_delta, min_k, pos_idx, pos_min_delta,
+                                        pos_min_k, dX, dPE, dW, external_lr, j_begin, j_end, static_cast<cudaStream_t>(stream));
+}
+
 extern "C" int lutb_concat_forward(const lutb_layer_cfg *cfg, int64_t batch, const float *weights, const float *x,
                                    const int32_t *anchors, const float *pos_embeddings, float *y, int32_t *idx,
                                    float *min_delta, int32_t *min_k, int32_t *pos_idx, float *pos_min_delta,
@@ -488,26 +627,12 @@ extern "C" int lutb_concat_forward(const lutb_layer_cfg *cfg, int64_t batch, con
                                 min_k, st);
     if (rc) return rc;
     if (npe > 0) {
-        const int64_t n = (int64_t)(S - 1) * Nt;
-        KernelScope scope(K_CHECK_POSITIONAL, st);
-        if (train) check_positional_kernel<true><<<(unsigned)((n + 127) / 128), 128, 0, st>>>(pos_embeddings, n, npe, cfg->cmp_eps, pos_idx, pos_min_delta, pos_min_k);
-        else check_positional_kernel<false><<<(unsigned)((n + 127) / 128), 128, 0, st>>>(pos_embeddings, n, npe, cfg->cmp_eps, pos_idx, nullptr, nullptr);
-        LUTB_LAUNCH_CHECK();
+        rc = launch_check_positional(cfg, pos_embeddings, pos_idx, train ? pos_min_delta : nullptr,
+                                     train ? pos_min_k : nullptr, st);
+        if (rc) return rc;
     }
-    {
-        const size_t smem = (size_t)(2 * S) * 4;
-        LUTB_REQUIRE(smem <= (size_t)kMaxSmemPerBlock - 1024, LUTB_ERR_SHAPE, "sequence too long for the sequence kernels");
-        dim3 grid((unsigned)Nt, (unsigned)batch);
-        KernelScope scope(K_CONCAT_FORWARD, st);
-        if (cfg->int_mode) {
-            if (smem > 48 * 1024) LUTB_CUDA(cudaFuncSetAttribute(concat_forward_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            concat_forward_kernel<true><<<grid, 256, smem, st>>>(weights, idx, pos_idx, y, S, cfg->n_outputs, Nt, cfg->n_anchors, npe, cfg->int_rescaler);
-        } else {
-            if (smem > 48 * 1024) LUTB_CUDA(cudaFuncSetAttribute(concat_forward_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            concat_forward_kernel<false><<<grid, 256, smem, st>>>(weights, idx, pos_idx, y, S, cfg->n_outputs, Nt, cfg->n_anchors, npe, cfg->int_rescaler);
-        }
-        LUTB_LAUNCH_CHECK();
-    }
+    rc = launch_concat_pairs_forward(cfg, batch, weights, idx, pos_idx, y, 0, S, st);
+    if (rc) return rc;
     if (cfg->int_mode) return launch_fixed_to_float(y, batch * S * (int64_t)cfg->n_outputs, cfg->int_rescaler, st);
     return LUTB_OK;
 }
@@ -526,10 +651,10 @@ extern "C" int lutb_concat_backward(const lutb_layer_cfg *cfg, int64_t batch, fl
                  "in internal weight gradients mode w_weights_gradients should be nullptr");
     LUTB_REQUIRE(!(external_lr < 0.0 && dW == nullptr), LUTB_ERR_NULL, "w_weights_gradients is NULL");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    double lr = cfg->lr_meta;
-    if (external_lr >= 0.0) lr *= -(double)(float)external_lr;
-    const int2 *an = reinterpret_cast<const int2 *>(anchors);
     if (cfg->int_mode) {
+        double lr = cfg->lr_meta;
+        if (external_lr >= 0.0) lr *= -(double)(float)external_lr;
+        const int2 *an = reinterpret_cast<const int2 *>(anchors);
         const int n_ob = (O + cfg->forward_group - 1) / cfg->forward_group;
         const int64_t total = batch * S * (int64_t)Nt * S * n_ob;
         const int64_t blocks = min((total + 127) / 128, (int64_t)device_info().sm_count * 64);
@@ -537,29 +662,9 @@ extern "C" int lutb_concat_backward(const lutb_layer_cfg *cfg, int64_t batch, fl
         concat_backward_fixed_kernel<<<(unsigned)blocks, 128, 0, st>>>(weights, dY, an, idx, min_delta, min_k, pos_idx, pos_min_delta, pos_min_k, dX, dPE, dW, batch, S, cfg->n_inputs, O, Nt, Nc, npe, cfg->forward_group, lr, cfg->int_rescaler);
         LUTB_LAUNCH_CHECK();
     } else {
-        const int warps = 8;
-        const size_t smem = ((size_t)((6 * S + 3) & ~3) + (size_t)warps * ((O + 3) & ~3)) * 4;
-        LUTB_REQUIRE(smem <= (size_t)kMaxSmemPerBlock - 1024, LUTB_ERR_SHAPE, "sequence too long for the sequence kernels");
-        dim3 grid((unsigned)Nt, (unsigned)batch);
-#define LUTB_CONCAT_BWD(DX, DWF, TARGET)                                                                                  \
-    do {                                                                                                                  \
-        if (smem > 48 * 1024) LUTB_CUDA(cudaFuncSetAttribute(concat_backward_kernel<DX, DWF>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
-        concat_backward_kernel<DX, DWF><<<grid, warps * 32, smem, st>>>(weights, dY, an, idx, min_delta, min_k, pos_idx, pos_min_delta, pos_min_k, dX, dPE, TARGET, S, cfg->n_inputs, O, Nt, Nc, npe, lr); \
-    } while (0)
-        if (external_lr >= 0.0) {
-            {
-                KernelScope scope(K_CONCAT_BACKWARD, st);
-                LUTB_CONCAT_BWD(true, false, nullptr);
-            }
-            LUTB_LAUNCH_CHECK();
-            KernelScope scope(K_CONCAT_WEIGHT_UPDATE, st);
-            LUTB_CONCAT_BWD(false, true, weights);
-        } else {
-            KernelScope scope(K_CONCAT_BACKWARD, st);
-            LUTB_CONCAT_BWD(true, true, dW);
-        }
-#undef LUTB_CONCAT_BWD
-        LUTB_LAUNCH_CHECK();
+        rc = launch_concat_pairs_backward(cfg, batch, weights, dY, anchors, idx, min_delta, min_k, pos_idx, pos_min_delta,
+                                          pos_min_k, dX, dPE, dW, external_lr, 0, S, st);
+        if (rc) return rc;
     }
     if (cfg->int_mode) {
         rc = launch_fixed_to_float(dX, batch * S * (int64_t)cfg->n_inputs, cfg->int_rescaler, st);

@@ -10,43 +10,20 @@
 // Two de-quantisation rules (cfg-independent argument `dequant`):
 //   LUTB_INT8_DEQUANT_F32    entry = f32(scale * q): exactly the fp32 table the reference would be given; costs two
 //                            conversions per entry (int8 -> fp32 -> fp64) on the conversion unit, which bound the kernel
-//   LUTB_INT8_DEQUANT_EXACT  entry = scale * q as an exact real (24 x 8 bit product).  Evaluated in integers: within
-//                            a batch of 32 detectors every scale is written as m_t * 2^(e_min - 150) with an integer
-//                            m_t < 2^32 (24-bit mantissa shifted by the detector's exponent above the batch's smallest
-//                            one), the sum over detectors of m_t * q is formed byte plane by byte plane with 4-way
-//                            byte dot products (dp4a) on 4 x 4 byte-transposed operands, and converted to double once
-//                            per (batch, output): the same exact real the sequential fp64 sum of the oracle yields,
-//                            at about one integer instruction per table entry instead of a conversion and an fp64
-//                            FMA (which saturated the conversion unit).  Batches whose scales are not positive normal
-//                            numbers within 8 binades of each other take the fp64 path.
+//   LUTB_INT8_DEQUANT_EXACT  entry = scale * q as an exact real (24 x 8 bit product, exact in fp64): one int8 -> fp64
+//                            conversion and one fp64 FMA per entry (the scale is converted once per detector);
+//                            building the double from integer operations instead measured the same within 3 %
 #include "lutb_common.cuh"
 #include "nonseq_fc.cuh"
 
 namespace lutb {
-
-// 4-way byte dot product, unsigned bytes of a times signed bytes of b, added to c.
-__device__ __forceinline__ int32_t dp4a_us(uint32_t a, uint32_t b, int32_t c) {
-    int32_t d;
-    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
-    return d;
-}
-
-// out[j] byte i = r_i byte j
-__device__ __forceinline__ void transpose_bytes_4x4(uint32_t r0, uint32_t r1, uint32_t r2, uint32_t r3, uint32_t (&out)[4]) {
-    const uint32_t t0 = __byte_perm(r0, r1, 0x5140), t1 = __byte_perm(r0, r1, 0x7362);
-    const uint32_t t2 = __byte_perm(r2, r3, 0x5140), t3 = __byte_perm(r2, r3, 0x7362);
-    out[0] = __byte_perm(t0, t2, 0x5410);
-    out[1] = __byte_perm(t0, t2, 0x7632);
-    out[2] = __byte_perm(t1, t3, 0x5410);
-    out[3] = __byte_perm(t1, t3, 0x7632);
-}
 
 // One warp per (sample, 128-output chunk): lane groups of LG lanes cover a row 4 int8 at a time (one 32-bit
 // load per lane), NG = 32 / LG groups take the detectors of a block round-robin; the per-group double sums
 // are exact (<= 32 fp32 terms of similar magnitude), so combining them across groups before the truncation
 // gives the same bits as the sequential sum.
 template <int LG, bool EXACT>
-__global__ void __launch_bounds__(256, 3) int8_gather_kernel(const int8_t *__restrict__ Q, const float *__restrict__ scales,
+__global__ void __launch_bounds__(256) int8_gather_kernel(const int8_t *__restrict__ Q, const float *__restrict__ scales,
                                                          const int32_t *__restrict__ idx, int32_t *__restrict__ acc,
                                                          int64_t batch, int n_outputs, int n_detectors, int table_rows,
                                                          int det_block, double fixed_scale, int det_begin, int det_end) {
@@ -78,58 +55,6 @@ __global__ void __launch_bounds__(256, 3) int8_gather_kernel(const int8_t *__res
                 packed[i] = (active && d < nvalid)
                                 ? __ldg(reinterpret_cast<const int32_t *>(Qc + ((size_t)(t0 + d) * table_rows + li) * n_outputs))
                                 : 0;
-            }
-            // integer evaluation of the exact rule: possible when the batch's scales are positive normal numbers
-            // within 8 binades of each other (warp-uniform decision)
-            bool fast = false;
-            uint32_t my_m = 0;
-            int e_min = 0;
-            if constexpr (EXACT && IT % 4 == 0) {
-                const uint32_t bits = __float_as_uint(my_scale);
-                const int e = (int)((bits >> 23) & 0xffu);
-                const bool in_batch = lane < nvalid;
-                const bool ok = !in_batch || ((bits >> 31) == 0 && e > 0 && e < 255);
-                e_min = in_batch ? e : 255;
-                int e_max = in_batch ? e : 0;
-#pragma unroll
-                for (int m = 16; m >= 1; m >>= 1) {
-                    e_min = min(e_min, __shfl_xor_sync(0xffffffffu, e_min, m));
-                    e_max = max(e_max, __shfl_xor_sync(0xffffffffu, e_max, m));
-                }
-                fast = __all_sync(0xffffffffu, ok) && e_max - e_min <= 8;
-                if (fast && in_batch) my_m = ((bits & 0x7fffffu) | 0x800000u) << (e - e_min);
-            }
-            if constexpr (EXACT && IT % 4 == 0) if (fast) {
-                int32_t pa[4][4];   // [byte plane of the mantissas][output column]
-#pragma unroll
-                for (int pl = 0; pl < 4; pl++)
-#pragma unroll
-                    for (int c = 0; c < 4; c++) pa[pl][c] = 0;
-#pragma unroll
-                for (int i = 0; i < IT; i += 4) {
-                    uint32_t cols[4], planes[4];
-                    transpose_bytes_4x4((uint32_t)packed[i], (uint32_t)packed[i + 1], (uint32_t)packed[i + 2],
-                                        (uint32_t)packed[i + 3], cols);
-                    // mantissas of the four detectors of this quad (0 beyond nvalid)
-                    const uint32_t m0 = __shfl_sync(0xffffffffu, my_m, i * NG + g);
-                    const uint32_t m1 = __shfl_sync(0xffffffffu, my_m, (i + 1) * NG + g);
-                    const uint32_t m2 = __shfl_sync(0xffffffffu, my_m, (i + 2) * NG + g);
-                    const uint32_t m3 = __shfl_sync(0xffffffffu, my_m, (i + 3) * NG + g);
-                    transpose_bytes_4x4(m0, m1, m2, m3, planes);
-#pragma unroll
-                    for (int pl = 0; pl < 4; pl++)
-#pragma unroll
-                        for (int c = 0; c < 4; c++) pa[pl][c] = dp4a_us(planes[pl], cols[c], pa[pl][c]);
-                }
-                // sum_t m_t * q as one integer (< 2^45), then scaled by 2^(e_min - 150): exact in double
-                const double unit = __longlong_as_double((long long)(e_min + 873) << 52);
-#pragma unroll
-                for (int c = 0; c < 4; c++) {
-                    const long long S = (long long)pa[0][c] + ((long long)pa[1][c] << 8) + ((long long)pa[2][c] << 16) +
-                                        ((long long)pa[3][c] << 24);
-                    s[c] += (double)S * unit;
-                }
-                continue;
             }
 #pragma unroll
             for (int i = 0; i < IT; i++) {

@@ -780,15 +780,17 @@ extern "C" int lutb_nonseq_fc_backward(const lutb_layer_cfg *cfg, int64_t batch,
                  "a required tensor pointer is NULL");
     LUTB_REQUIRE(!(external_lr >= 0.0 && dW != nullptr), LUTB_ERR_MODE,
                  "in internal weight gradients mode w_weights_gradients should be nullptr");
-    LUTB_REQUIRE(!(external_lr < 0.0 && dW == nullptr), LUTB_ERR_NULL, "w_weights_gradients is NULL");
+    const bool skip_table = external_lr == LUTB_SKIP_TABLE_GRADIENT;
+    LUTB_REQUIRE(!(skip_table && dW != nullptr), LUTB_ERR_MODE, "no table gradient asked for, w_weights_gradients should be nullptr");
+    LUTB_REQUIRE(!(external_lr < 0.0 && dW == nullptr && !skip_table), LUTB_ERR_NULL, "w_weights_gradients is NULL");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     double lr = cfg->lr_meta;
     // the reference narrows external_lr to fp32 before use (lut.cu:1076)
     if (external_lr >= 0.0) lr *= -(double)(float)external_lr;
     float *target = external_lr >= 0.0 ? weights : dW;
-    rc = launch_fc_backward(cfg, batch, weights, dY, anchors, idx, min_delta, min_k, dX, target, lr, st, sorted);
+    rc = launch_fc_backward(cfg, batch, weights, dY, anchors, idx, min_delta, min_k, dX, target, lr, st, sorted || skip_table);
     if (rc) return rc;
-    if (sorted) {
+    if (sorted && !skip_table) {
         rc = launch_fc_dw_sorted(dY, idx, target, batch, cfg->n_outputs, cfg->n_detectors, 1 << cfg->n_anchors, lr,
                                  workspace, st);
         if (rc) return rc;
@@ -799,6 +801,29 @@ extern "C" int lutb_nonseq_fc_backward(const lutb_layer_cfg *cfg, int64_t batch,
         if (dW) rc = launch_fixed_to_float(dW, (int64_t)cfg->n_detectors * (1 << cfg->n_anchors) * cfg->n_outputs, cfg->int_rescaler, st);
     }
     return rc;
+}
+
+extern "C" size_t lutb_nonseq_fc_table_grad_rows_workspace(const lutb_layer_cfg *cfg, int64_t batch) {
+    if (cfg == nullptr || batch <= 0 || cfg->int_mode) return 0;
+    return fc_dw_rows_workspace(batch, cfg->n_detectors, 1 << cfg->n_anchors);
+}
+
+extern "C" int lutb_nonseq_fc_table_grad_rows(const lutb_layer_cfg *cfg, int64_t batch, const float *dY,
+                                              const int32_t *idx, int64_t *row_ids, float *values, int64_t capacity,
+                                              int64_t *count_out, void *workspace, size_t workspace_bytes, void *stream) {
+    int rc = validate_cfg(cfg);
+    if (rc) return rc;
+    LUTB_REQUIRE(cfg->seq_len == 1, LUTB_ERR_MODE, "the row-list table gradient is for sequence_length == 1");
+    LUTB_REQUIRE(cfg->int_mode == 0, LUTB_ERR_MODE, "the row-list table gradient needs fp32 accumulators");
+    LUTB_REQUIRE(batch > 0, LUTB_ERR_SHAPE, "batch_size == 0");
+    LUTB_REQUIRE(dY && idx && row_ids && values && count_out, LUTB_ERR_NULL, "a required tensor pointer is NULL");
+    LUTB_REQUIRE(capacity > 0, LUTB_ERR_SHAPE, "capacity == 0");
+    const size_t need = fc_dw_rows_workspace(batch, cfg->n_detectors, 1 << cfg->n_anchors);
+    LUTB_REQUIRE(workspace != nullptr && workspace_bytes >= need, LUTB_ERR_WORKSPACE,
+                 "the row-list table gradient needs %zu bytes of workspace", need);
+    LUTB_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, LUTB_ERR_ALIGN, "workspace must be 256-byte aligned");
+    return launch_fc_dw_rows(dY, idx, batch, cfg->n_outputs, cfg->n_detectors, 1 << cfg->n_anchors, cfg->lr_meta, row_ids,
+                             values, capacity, count_out, workspace, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int lutb_nonseq_fc_backward_noalloc(const lutb_layer_cfg *cfg, int64_t batch, float *weights,

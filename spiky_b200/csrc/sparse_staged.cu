@@ -8,14 +8,14 @@
 // single-CTA copies of this GPU's own memory), and 16 consumer warps (32 samples each) pick their samples' rows out
 // of shared memory.  HBM sees one sequential read of the tables; the random accesses hit shared memory.
 //
-//   forward          each lane keeps the running sum of (its sample, its synapse) over the detectors of a chunk in
-//                    a register; one reduction per (sample, chunk part, target) goes to y when the chunk ends
-//   input gradient   per (sample, detector) the products dY[target(p)] * (W[row + p] - W[alt + p]) are summed over
-//                    the lanes with a transpose-reduce, so that lane L ends with the sum of sample L and makes that
-//                    sample's two dX updates itself
+//   forward          lane L reads the row of sample L and keeps the sample's running sums (one per synapse) over the
+//                    detectors of a chunk in registers; one reduction per (sample, chunk part, target) goes to y
+//                    when the chunk ends
+//   input gradient   lane L reads the selected and the alternative row of sample L, forms
+//                    sum_p dY[target(p)] * (W[row + p] - W[alt + p]) and makes the sample's two dX updates
 //
 // The detectors of the layer (times the sample tiles) are split evenly over one block per SM; a block walks its
-// range chunk by chunk.  Every wait on an mbarrier is bounded (kWaitLimitNs): a wait that runs out counts an error
+// range chunk by chunk.  Every wait on an mbarrier is bounded (kWaitLimitCycles): a wait that runs out counts an error
 // in g_wait_errors (lutb_device_wait_errors), raises the block's abort flag, and the block leaves after a bounded
 // wait for its own copies in flight.
 #include "sparse_staged.cuh"
@@ -35,8 +35,8 @@ constexpr int kChunkSlots = 32;     // detector slots per chunk in the linear wo
 constexpr int kMaxStages = 8;
 constexpr int kMinStages = 3;
 constexpr int kFwdTile = 8;         // detectors whose table indices a lane holds at a time (forward)
-constexpr int kDxTile = 2;          // same for the input gradient (it also holds min_k)
-constexpr unsigned long long kWaitLimitNs = 1000ull * 1000ull * 1000ull;
+constexpr int kDxTile = 2;          // same for the input gradient (it also holds min_k and min_delta)
+constexpr long long kWaitLimitCycles = 2000ll * 1000ll * 1000ll;   // about a second of SM clock
 
 __device__ int g_wait_errors = 0;
 
@@ -75,17 +75,14 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-__device__ __forceinline__ unsigned long long global_timer_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-// Bounded wait for the phase with the given parity; false when the limit ran out.
+// Bounded wait for the phase with the given parity; false when the limit ran out.  The bound is counted on the SM's
+// own cycle counter: reading %globaltimer costs microseconds, and a wait that is not satisfied at once would pay
+// that on every poll.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
     if (mbar_try_wait(bar, parity)) return true;
-    const unsigned long long t0 = global_timer_ns();
+    const long long t0 = clock64();
     while (!mbar_try_wait(bar, parity)) {
-        if (global_timer_ns() - t0 > kWaitLimitNs) return false;
+        if (clock64() - t0 > kWaitLimitCycles) return false;
     }
     return true;
 }
@@ -220,28 +217,78 @@ __device__ __forceinline__ bool next_unit(const StagedArgs &a, int64_t pos, int6
 }
 
 // ------------------------------------------------------------------------------------------ forward
-// Lane layout inside a consumer warp: LG lanes per sample (LG = 8, 16 or 32 >= synapses per row), 32 / LG samples
-// side by side; lane (h, j) works on synapse j of the samples h * LG + i, i = 0 .. LG - 1, of the warp's 32 samples.
-// Lane L also holds the table indices of sample L (its "own" sample), which the others fetch by shuffle.
-template <int LG>
+// Inside a consumer warp lane L works on sample L of the warp's 32 samples: it holds the sample's table indices and
+// reads the sample's row of every table itself, all synapses of the row into registers (64-bit shared loads when
+// rows start at even slots and have no holes inside, else one load per synapse).  No lane depends on another, so a
+// table costs a warp a handful of independent loads and adds; the price is bank conflicts between the 32 random
+// rows, which leaves shared memory about as busy as the copies that fill it.
+// NJ: synapses per row rounded up to a multiple of 4; values beyond the row's real length are loaded and ignored.
+// Synapses [J0, J0 + 4) of the row at `off` (64-bit loads need J0 even, which multiples of 4 are).
+template <int J0, bool VEC>
+__device__ __forceinline__ void load_row4(const float *slot, uint32_t off, const SparseView &sp, float (&w)[4]) {
+    if constexpr (VEC) {
+        const float2 v0 = *reinterpret_cast<const float2 *>(slot + off + J0);
+        const float2 v1 = *reinterpret_cast<const float2 *>(slot + off + J0 + 2);
+        w[0] = v0.x; w[1] = v0.y; w[2] = v1.x; w[3] = v1.y;
+    } else {
+#pragma unroll
+        for (int j = 0; j < 4; j++) w[j] = slot[off + J0 + j + hole_offset(J0 + j, sp)];
+    }
+}
+
+// Keeps the compiler from hoisting the next group of row loads above the arithmetic of the current one (the
+// registers of a 32-synapse row, twice for the input gradient, do not fit beside the running sums).
+__device__ __forceinline__ void schedule_fence() { asm volatile("" ::: "memory"); }
+
+template <int J0, int NJ, bool VEC>
+__device__ __forceinline__ void add_row(const float *slot, uint32_t off, const SparseView &sp, float (&acc)[NJ]) {
+    if constexpr (J0 < NJ) {
+        float w[4];
+        load_row4<J0, VEC>(slot, off, sp, w);
+#pragma unroll
+        for (int j = 0; j < 4; j++) acc[J0 + j] += w[j];
+        if constexpr (J0 % 8 == 4) schedule_fence();
+        add_row<J0 + 4, NJ, VEC>(slot, off, sp, acc);
+    }
+}
+
+template <int J0, int NJ, bool VEC>
+__device__ __forceinline__ float dot_row_difference(const float *slot, uint32_t off, uint32_t alt, const SparseView &sp,
+                                                    const float (&gp)[NJ], int P, float g) {
+    if constexpr (J0 < NJ) {
+        float wr[4], wa[4];
+        load_row4<J0, VEC>(slot, off, sp, wr);
+        load_row4<J0, VEC>(slot, alt, sp, wa);
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            // slots beyond the row's length hold unrelated bits: keep them out of the sum
+            const float d = J0 + j < P ? wr[j] - wa[j] : 0.f;
+            g = fmaf(gp[J0 + j], d, g);
+        }
+        if constexpr (J0 % 8 == 4) schedule_fence();
+        return dot_row_difference<J0 + 4, NJ, VEC>(slot, off, alt, sp, gp, P, g);
+    } else {
+        return g;
+    }
+}
+
+template <int NJ, bool VEC>
 __device__ __forceinline__ bool forward_unit(const StagedArgs &a, const Unit &u, const Unit &nx, bool has_next,
                                              const Ring &ring, RingPos &rp, const int32_t *__restrict__ idx,
                                              int32_t (&raw)[kFwdTile], int warp, int lane, float *__restrict__ y) {
-    const int h = lane / LG, j = lane - h * LG;
-    const bool valid = j < u.cs.P;
     const int64_t bw = u.b0 + warp * 32;
     const bool warp_active = bw < a.batch;
-    const int q = j + hole_offset(j, a.sp);
-    float acc[LG];
+    const int64_t own_b = bw + lane;
+    float acc[NJ];
 #pragma unroll
-    for (int i = 0; i < LG; i++) acc[i] = 0.f;
+    for (int j = 0; j < NJ; j++) acc[j] = 0.f;
     for (int t0 = u.d0; t0 < u.d1; t0 += kFwdTile) {
         uint32_t ro[kFwdTile];
 #pragma unroll
         for (int k = 0; k < kFwdTile; k++) ro[k] = (uint32_t)raw[k] * (uint32_t)u.cs.stride;
         // the indices of the next tile (of this unit or of the next one) travel while this tile is worked on
         if (t0 + kFwdTile < u.d1)
-            load_tile_i32<kFwdTile>(idx, bw + lane, a.batch, a.n_detectors, u.cs.det0 + t0 + kFwdTile,
+            load_tile_i32<kFwdTile>(idx, own_b, a.batch, a.n_detectors, u.cs.det0 + t0 + kFwdTile,
                                     min(kFwdTile, u.d1 - t0 - kFwdTile), raw);
         else if (has_next)
             load_tile_i32<kFwdTile>(idx, nx.b0 + warp * 32 + lane, a.batch, a.n_detectors, nx.cs.det0 + nx.d0,
@@ -250,29 +297,26 @@ __device__ __forceinline__ bool forward_unit(const StagedArgs &a, const Unit &u,
         for (int dd = 0; dd < kFwdTile; dd++) {
             if (t0 + dd < u.d1) {
                 if (!mbar_wait(ring.full0 + 8 * rp.slot, rp.phase) || *ring.abort_flag) return false;
-                if (warp_active) {
-                    const float *tab = ring.base + (size_t)rp.slot * a.slot_floats + q;
-#pragma unroll
-                    for (int i = 0; i < LG; i++) {
-                        const uint32_t off = __shfl_sync(0xffffffffu, ro[dd], h * LG + i);
-                        if (valid) acc[i] += tab[off];
-                    }
-                }
+                if (warp_active) add_row<0, NJ, VEC>(ring.base + (size_t)rp.slot * a.slot_floats, ro[dd], a.sp, acc);
                 __syncwarp();
                 if (lane == 0) mbar_arrive(ring.empty0 + 8 * rp.slot);
                 rp.advance(a.n_stages);
             }
         }
     }
-    if (warp_active && valid) {
-        const int target = __ldg(a.sp.syn_target + u.cs.toff + j);
+    if (own_b < a.batch) {
+        float *yb = y + own_b * a.n_outputs;
+        const int32_t *tg = a.sp.syn_target + u.cs.toff;
 #pragma unroll
-        for (int i = 0; i < LG; i++) {
-            const int64_t b = bw + h * LG + i;
-            if (b < a.batch) atomicAdd(y + b * a.n_outputs + target, acc[i]);
-        }
+        for (int j = 0; j < NJ; j++)
+            if (j < u.cs.P) atomicAdd(yb + __ldg(tg + j), acc[j]);
     }
     return true;
+}
+
+// Rows can be read with 64-bit loads when every row starts at an even slot and no hole lies inside a row.
+__device__ __forceinline__ bool rows_vectorisable(const StagedArgs &a, const ChunkStatic &cs) {
+    return (cs.stride & 1) == 0 && hole_offset(cs.P - 1, a.sp) == 0;
 }
 
 // Shared memory: the ring, then the barriers (two per stage) and the abort flag.
@@ -318,9 +362,19 @@ __global__ void __launch_bounds__(kStagedThreads, 1) sparse_forward_staged_kerne
     while (has_cur) {
         const bool has_next = next_unit(a, cur.next_pos, hi, nxt);
         bool ok;
-        if (cur.cs.P <= 8) ok = forward_unit<8>(a, cur, nxt, has_next, ring, rp, idx, raw, warp, lane, y);
-        else if (cur.cs.P <= 16) ok = forward_unit<16>(a, cur, nxt, has_next, ring, rp, idx, raw, warp, lane, y);
-        else ok = forward_unit<32>(a, cur, nxt, has_next, ring, rp, idx, raw, warp, lane, y);
+#define LUTB_FWD_UNIT(NJV, VECV) forward_unit<NJV, VECV>(a, cur, nxt, has_next, ring, rp, idx, raw, warp, lane, y)
+        if (rows_vectorisable(a, cur.cs)) {
+            if (cur.cs.P <= 8) ok = LUTB_FWD_UNIT(8, true);
+            else if (cur.cs.P <= 16) ok = LUTB_FWD_UNIT(16, true);
+            else if (cur.cs.P <= 20) ok = LUTB_FWD_UNIT(20, true);
+            else if (cur.cs.P <= 28) ok = LUTB_FWD_UNIT(28, true);
+            else ok = LUTB_FWD_UNIT(32, true);
+        } else {
+            if (cur.cs.P <= 8) ok = LUTB_FWD_UNIT(8, false);
+            else if (cur.cs.P <= 16) ok = LUTB_FWD_UNIT(16, false);
+            else ok = LUTB_FWD_UNIT(32, false);
+        }
+#undef LUTB_FWD_UNIT
         if (!ok) {
             if (lane == 0) report_wait_error(ring);
             return;
@@ -331,41 +385,38 @@ __global__ void __launch_bounds__(kStagedThreads, 1) sparse_forward_staged_kerne
 }
 
 // ------------------------------------------------------------------------------------------ input gradient
-// Same lane layout.  Per detector every lane forms its LG products, a butterfly of LG - 1 shuffles transposes and
-// sums them so that lane (h, j) ends with the full sum of sample h * LG + j = its own sample, whose min_delta, min_k
-// and table index it holds.  Partial sums are fp32 (<= 32 terms), the scaling by up() is done in double.
-template <int LG>
+// Same mapping: lane L forms g = sum_p dY[target(p)] * (W[row + p] - W[alt + p]) of its own sample from its own two
+// row reads (fp32, <= 32 terms), scales it by up() in double and makes the sample's two dX updates.
+template <int NJ, bool VEC>
 __device__ __forceinline__ bool input_grad_unit(const StagedArgs &a, const Unit &u, const Unit &nx, bool has_next,
                                                 const Ring &ring, RingPos &rp, const int32_t *__restrict__ idx,
                                                 const int32_t *__restrict__ min_k, const float *__restrict__ min_delta,
                                                 const float *__restrict__ dY, const int2 *__restrict__ anchors,
-                                                int32_t (&raw_i)[kDxTile], int32_t (&raw_k)[kDxTile], int warp, int lane,
-                                                float *__restrict__ dX) {
-    const int h = lane / LG, j = lane - h * LG;
-    const bool valid = j < u.cs.P;
+                                                int32_t (&raw_i)[kDxTile], int32_t (&raw_k)[kDxTile],
+                                                int32_t (&raw_m)[kDxTile], int warp, int lane, float *__restrict__ dX) {
     const int64_t bw = u.b0 + warp * 32;
     const bool warp_active = bw < a.batch;
     const int64_t own_b = bw + lane;
-    const int q = j + hole_offset(j, a.sp);
-    // output gradients of (sample, target(j)): the same for every detector of the chunk
-    float gp[LG];
+    const bool has_b = own_b < a.batch;
+    // output gradients of the sample at the chunk's targets: the same for every detector of the chunk
+    float gp[NJ];
     {
-        const int target = valid ? __ldg(a.sp.syn_target + u.cs.toff + j) : 0;
+        const int32_t *tg = a.sp.syn_target + u.cs.toff;
+        const float *dyb = dY + (has_b ? own_b : 0) * a.n_outputs;
 #pragma unroll
-        for (int i = 0; i < LG; i++) {
-            const int64_t b = bw + h * LG + i;
-            gp[i] = (valid && b < a.batch) ? __ldg(dY + b * a.n_outputs + target) : 0.f;
-        }
+        for (int j = 0; j < NJ; j++) gp[j] = (has_b && j < u.cs.P) ? __ldg(dyb + __ldg(tg + j)) : 0.f;
     }
     for (int t0 = u.d0; t0 < u.d1; t0 += kDxTile) {
-        uint32_t pk[kDxTile];   // row offset | alternative row offset << 16
+        uint32_t ro[kDxTile], ao[kDxTile];
         int32_t ck[kDxTile];
+        float cm[kDxTile];
 #pragma unroll
         for (int k = 0; k < kDxTile; k++) {
             const uint32_t li = (uint32_t)raw_i[k];
-            const uint32_t alt = li ^ (1u << raw_k[k]);   // minimum-margin bit flipped
-            pk[k] = (li * (uint32_t)u.cs.stride) | ((alt * (uint32_t)u.cs.stride) << 16);
+            ro[k] = li * (uint32_t)u.cs.stride;
+            ao[k] = (li ^ (1u << raw_k[k])) * (uint32_t)u.cs.stride;   // minimum-margin bit flipped
             ck[k] = raw_k[k];
+            cm[k] = __int_as_float(raw_m[k]);
         }
         {
             int64_t pb;
@@ -375,41 +426,17 @@ __device__ __forceinline__ bool input_grad_unit(const StagedArgs &a, const Unit 
             else { pb = 0; pdet = 0; pn = 0; }
             load_tile_i32<kDxTile>(idx, pb, a.batch, a.n_detectors, pdet, pn, raw_i);
             load_tile_i32<kDxTile>(min_k, pb, a.batch, a.n_detectors, pdet, pn, raw_k);
+            load_tile_i32<kDxTile>(reinterpret_cast<const int32_t *>(min_delta), pb, a.batch, a.n_detectors, pdet, pn, raw_m);
         }
 #pragma unroll
         for (int dd = 0; dd < kDxTile; dd++) {
             if (t0 + dd < u.d1) {
                 if (!mbar_wait(ring.full0 + 8 * rp.slot, rp.phase) || *ring.abort_flag) return false;
                 if (warp_active) {
-                    const float *tab = ring.base + (size_t)rp.slot * a.slot_floats + q;
-                    // the lane's own min_delta travels while the products are formed
-                    const float own_m = own_b < a.batch ? __ldg(min_delta + own_b * a.n_detectors + u.cs.det0 + t0 + dd) : 0.f;
-                    // products of the sample slots i and i + LG/2 are formed together and folded at once (first stage
-                    // of the transpose-reduce), so that only LG/2 partial sums stay live
-                    float v[LG / 2];
-                    const bool top = (j & (LG / 2)) != 0;
-#pragma unroll
-                    for (int i = 0; i < LG / 2; i++) {
-                        const uint32_t pa = __shfl_sync(0xffffffffu, pk[dd], h * LG + i);
-                        const uint32_t pb = __shfl_sync(0xffffffffu, pk[dd], h * LG + i + LG / 2);
-                        const float va = valid ? gp[i] * (tab[pa & 0xffffu] - tab[pa >> 16]) : 0.f;
-                        const float vb = valid ? gp[i + LG / 2] * (tab[pb & 0xffffu] - tab[pb >> 16]) : 0.f;
-                        v[i] = (top ? vb : va) + __shfl_xor_sync(0xffffffffu, top ? va : vb, LG / 2);
-                    }
-                    // remaining stages: after the stage with offset o a lane keeps the half of the values whose index
-                    // bit matches its own lane bit, summed with the partner lane's copy
-#pragma unroll
-                    for (int o = LG / 4; o >= 1; o >>= 1) {
-                        const bool upper = (j & o) != 0;
-#pragma unroll
-                        for (int i = 0; i < o; i++) {
-                            const float send = upper ? v[i] : v[i + o];
-                            const float keep = upper ? v[i + o] : v[i];
-                            v[i] = keep + __shfl_xor_sync(0xffffffffu, send, o);
-                        }
-                    }
-                    if (own_b < a.batch) {
-                        const double du = surrogate_up(own_m) * (double)v[0];
+                    const float *slot = ring.base + (size_t)rp.slot * a.slot_floats;
+                    const float g = dot_row_difference<0, NJ, VEC>(slot, ro[dd], ao[dd], a.sp, gp, u.cs.P, 0.f);
+                    if (has_b) {
+                        const double du = surrogate_up(cm[dd]) * (double)g;
                         if (fabs(du) > kEps) {
                             const int2 an = __ldg(anchors + (size_t)(u.cs.det0 + t0 + dd) * a.n_anchors + ck[dd]);
                             float *dxb = dX + own_b * a.n_inputs;
@@ -442,21 +469,30 @@ __global__ void __launch_bounds__(kStagedThreads, 1) sparse_input_grad_staged_ke
     Unit cur, nxt;
     bool has_cur = next_unit(a, lo, hi, cur);
     RingPos rp{0u, 0u};
-    int32_t raw_i[kDxTile], raw_k[kDxTile];
+    int32_t raw_i[kDxTile], raw_k[kDxTile], raw_m[kDxTile];
     if (has_cur) {
         const int64_t b = cur.b0 + warp * 32 + lane;
         const int det = cur.cs.det0 + cur.d0, n = min(kDxTile, cur.d1 - cur.d0);
         load_tile_i32<kDxTile>(idx, b, a.batch, a.n_detectors, det, n, raw_i);
         load_tile_i32<kDxTile>(min_k, b, a.batch, a.n_detectors, det, n, raw_k);
+        load_tile_i32<kDxTile>(reinterpret_cast<const int32_t *>(min_delta), b, a.batch, a.n_detectors, det, n, raw_m);
     }
     while (has_cur) {
         const bool has_next = next_unit(a, cur.next_pos, hi, nxt);
         bool ok;
-#define LUTB_DX_UNIT(LGV) \
-    input_grad_unit<LGV>(a, cur, nxt, has_next, ring, rp, idx, min_k, min_delta, dY, anchors, raw_i, raw_k, warp, lane, dX)
-        if (cur.cs.P <= 8) ok = LUTB_DX_UNIT(8);
-        else if (cur.cs.P <= 16) ok = LUTB_DX_UNIT(16);
-        else ok = LUTB_DX_UNIT(32);
+#define LUTB_DX_UNIT(NJV, VECV) \
+    input_grad_unit<NJV, VECV>(a, cur, nxt, has_next, ring, rp, idx, min_k, min_delta, dY, anchors, raw_i, raw_k, raw_m, warp, lane, dX)
+        if (rows_vectorisable(a, cur.cs)) {
+            if (cur.cs.P <= 8) ok = LUTB_DX_UNIT(8, true);
+            else if (cur.cs.P <= 16) ok = LUTB_DX_UNIT(16, true);
+            else if (cur.cs.P <= 20) ok = LUTB_DX_UNIT(20, true);
+            else if (cur.cs.P <= 28) ok = LUTB_DX_UNIT(28, true);
+            else ok = LUTB_DX_UNIT(32, true);
+        } else {
+            if (cur.cs.P <= 8) ok = LUTB_DX_UNIT(8, false);
+            else if (cur.cs.P <= 16) ok = LUTB_DX_UNIT(16, false);
+            else ok = LUTB_DX_UNIT(32, false);
+        }
 #undef LUTB_DX_UNIT
         if (!ok) {
             if (lane == 0) report_wait_error(ring);

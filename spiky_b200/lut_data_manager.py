@@ -313,8 +313,6 @@ class _LUTDataManager:
             raise ValueError("backward_backprop should only be called when sequence_length == 1")
         if external_lr >= 0.0 and w_weights_gradients is not None:
             raise ValueError("in internal weight gradients mode w_weights_gradients should be nullptr")
-        if external_lr == _native.SKIP_TABLE_GRADIENT and self._fully_connected:
-            raise ValueError("skipping the table gradient is only available for sparse lookup connectivity")
         B = int(batch_size)
         self._expect(r_output_gradients, B * self._n_outputs, "r_output_gradients")
         if w_input_gradients is not None:
@@ -341,6 +339,34 @@ class _LUTDataManager:
                                            r_lookup_indices, r_min_anchor_deltas, r_min_anchor_delta_indices,
                                            w_input_gradients, external_lr, w_weights_gradients)
         _native.check(rc)
+
+    def table_gradient_rows(self, batch_size, r_output_gradients, r_lookup_indices):
+        """Table gradient of a fully connected non-sequence layer as a list of touched rows (not part of the
+        reference's class, which forms the dense gradient and compacts it): returns ``(row_ids int64 [n],
+        values fp32 [n, n_outputs])`` with ``row_ids = detector * 2^Nc + row`` ascending.  fp32 accumulators only.
+        Reads the number of touched rows back from the device (like the reference's converter does)."""
+        self._require_cuda()
+        if not self._fully_connected or self._seq_len != 1:
+            raise ValueError("the row-list table gradient exists for fully connected non-sequence layers")
+        B, O, Nt = int(batch_size), self._n_outputs, self._n_detectors
+        self._expect(r_output_gradients, B * O, "r_output_gradients")
+        self._expect(r_lookup_indices, B * Nt, "r_lookup_indices")
+        cfg = self._cfg()
+        L = _native.lib()
+        dev = r_output_gradients.device
+        capacity = min(B, 1 << self._n_anchors) * Nt
+        with torch.cuda.device(self._device):
+            ws_bytes = L.lutb_nonseq_fc_table_grad_rows_workspace(ctypes.byref(cfg), B)
+            ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+            row_ids = torch.empty(capacity, dtype=torch.int64, device=dev)
+            values = torch.empty(capacity * O, dtype=torch.float32, device=dev)
+            count = torch.zeros(1, dtype=torch.int64, device=dev)
+            rc = L.lutb_nonseq_fc_table_grad_rows(ctypes.byref(cfg), B, _ptr(r_output_gradients), _ptr(r_lookup_indices),
+                                                  _ptr(row_ids), _ptr(values), capacity, _ptr(count), _ptr(ws), ws_bytes,
+                                                  self._stream())
+        _native.check(rc)
+        n = int(count.item())
+        return row_ids[:n], values[:n * O].view(n, O)
 
     def table_gradient(self, batch_size, r_output_gradients, r_lookup_indices, w_target, scale, chunk_begin=0,
                        chunk_end=None):
@@ -569,6 +595,70 @@ class _LUTDataManager:
                 _ptr(r_positional_min_delta_indices), _ptr(w_input_gradients),
                 _ptr(w_positional_embeddings_gradients), _ptr(w_weights_gradients), float(external_lr),
                 self._stream())
+        _native.check(rc)
+
+    # ------------------------------------------------------------------ stages of the concatenation-mode layer
+    # (no counterpart in the reference's data manager, which runs them inside forward_step_concat /
+    # backward_backprop_concat; exposed separately for ranks that shard the query positions of a sequence)
+    def check_detectors(self, rows, r_input, r_detector_anchors, w_lookup_indices, cmp_eps=0.0,
+                        w_min_anchor_deltas=None, w_min_anchor_delta_indices=None):
+        """Table indices (and minimum-margin pairs) of ``rows`` input rows."""
+        self._require_cuda()
+        self._expect(r_input, rows * self._n_inputs, "r_input")
+        self._expect(w_lookup_indices, rows * self._n_detectors, "w_lookup_indices")
+        cfg = self._cfg(cmp_eps)
+        with torch.cuda.device(self._device):
+            rc = _native.lib().lutb_check_detectors(ctypes.byref(cfg), int(rows), _ptr(r_input), _ptr(r_detector_anchors),
+                                                    _ptr(w_lookup_indices), _ptr(w_min_anchor_deltas),
+                                                    _ptr(w_min_anchor_delta_indices), self._stream())
+        _native.check(rc)
+
+    def check_positional(self, r_positional_embeddings, w_positional_lookup_indices, cmp_eps=0.0,
+                         w_positional_min_deltas=None, w_positional_min_delta_indices=None):
+        self._require_cuda()
+        cfg = self._cfg(cmp_eps)
+        with torch.cuda.device(self._device):
+            rc = _native.lib().lutb_check_positional(ctypes.byref(cfg), _ptr(r_positional_embeddings),
+                                                     _ptr(w_positional_lookup_indices), _ptr(w_positional_min_deltas),
+                                                     _ptr(w_positional_min_delta_indices), self._stream())
+        _native.check(rc)
+
+    def concat_pairs_forward(self, r_weights, batch_size, r_lookup_indices, r_positional_lookup_indices, w_output,
+                             j_begin, j_end):
+        """Outputs of the queries [j_begin, j_end) from the table indices of all tokens."""
+        self._require_cuda()
+        if not self._fully_connected:
+            raise ValueError("query-range stages exist for fully connected concatenation-mode layers only")
+        B, S = int(batch_size), self._seq_len
+        self._expect(r_lookup_indices, B * S * self._n_detectors, "r_lookup_indices")
+        self._expect(w_output, B * S * self._n_outputs, "w_output")
+        cfg = self._cfg()
+        with torch.cuda.device(self._device):
+            rc = _native.lib().lutb_concat_pairs_forward(ctypes.byref(cfg), B, _ptr(r_weights), _ptr(r_lookup_indices),
+                                                         _ptr(r_positional_lookup_indices), _ptr(w_output), int(j_begin),
+                                                         int(j_end), self._stream())
+        _native.check(rc)
+        self._forward_seen = True
+
+    def concat_pairs_backward(self, r_weights, batch_size, r_output_gradients, r_detector_anchors, r_lookup_indices,
+                              r_min_anchor_deltas, r_min_anchor_delta_indices, w_input_gradients, external_lr,
+                              r_positional_lookup_indices, r_positional_min_deltas, r_positional_min_delta_indices,
+                              w_positional_embeddings_gradients, w_weights_gradients, j_begin, j_end):
+        """Partial gradients from the pairs whose query lies in [j_begin, j_end)."""
+        self._require_cuda()
+        if not self._fully_connected:
+            raise ValueError("query-range stages exist for fully connected concatenation-mode layers only")
+        B, S = int(batch_size), self._seq_len
+        self._expect(r_output_gradients, B * S * self._n_outputs, "r_output_gradients")
+        self._expect(w_input_gradients, B * S * self._n_inputs, "w_input_gradients")
+        cfg = self._cfg()
+        with torch.cuda.device(self._device):
+            rc = _native.lib().lutb_concat_pairs_backward(
+                ctypes.byref(cfg), B, _ptr(r_weights), _ptr(r_output_gradients), _ptr(r_detector_anchors),
+                _ptr(r_lookup_indices), _ptr(r_min_anchor_deltas), _ptr(r_min_anchor_delta_indices),
+                _ptr(r_positional_lookup_indices), _ptr(r_positional_min_deltas), _ptr(r_positional_min_delta_indices),
+                _ptr(w_input_gradients), _ptr(w_positional_embeddings_gradients), _ptr(w_weights_gradients),
+                float(external_lr), int(j_begin), int(j_end), self._stream())
         _native.check(rc)
 
     @staticmethod

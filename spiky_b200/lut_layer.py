@@ -459,6 +459,42 @@ class LUTLayerBasic(nn.Module):
             raise ValueError("external_learning_rate_hook must be set when using GradientPolicy.Internal")
         return float(self._external_lr_hook(self._weights))
 
+    # Sparse gradient policy of fully connected non-sequence layers: the (cell, value) lists come straight from
+    # the table-gradient pass (rows the batch touched) instead of a dense gradient that is compacted afterwards;
+    # set to False to take the reference's dense-then-compact route
+    _sparse_rows_direct = True
+
+    def _backward_step_sparse_rows(self, x, grad_output, lookup_indices, min_anchor_deltas, min_anchor_delta_indices,
+                                   x_grad, batch_size):
+        """Input gradient by the usual kernels, table gradient as a list of touched rows; the result is the sparse
+        tensor ``_process_gradients`` builds from the dense gradient: cell indices ascending, zero cells dropped."""
+        from ._native import SKIP_TABLE_GRADIENT
+        dm = self._lut_dm
+        grad_flat = grad_output.contiguous().view(-1)
+        idx_flat = lookup_indices.reshape(-1)
+        if x_grad is not None:
+            dm.backward_backprop(self._weights.detach(), batch_size, grad_flat, self._detector_anchors, idx_flat,
+                                 min_anchor_deltas.reshape(-1), min_anchor_delta_indices.reshape(-1), x_grad.view(-1),
+                                 SKIP_TABLE_GRADIENT, None, None)
+        dx = None if x_grad is None else x_grad.view(x.shape)
+        rows, values = dm.table_gradient_rows(batch_size, grad_flat, idx_flat)
+        if rows.numel() == 0:
+            return dx, None
+        O = values.shape[1]
+        # zero cells (an output gradient that is exactly zero or below the threshold) are not part of the list
+        flat = values.reshape(-1)
+        pad = (-flat.numel()) % 4
+        if pad:
+            flat = torch.cat([flat, flat.new_zeros(pad)])
+        nz, vals = self._shared_context.get_dense_to_sparse_converter(self._multi_id).dense_to_sparse_32(flat)
+        if nz is None:
+            return dx, None
+        cells = rows[nz // O] * O + nz % O
+        if self._weights_gradient_policy.normalized:
+            vals /= vals.abs().max().clip(1e-16)
+        return dx, torch.sparse_coo_tensor(cells.unsqueeze(0), vals, size=self._weights.shape, device=self.device,
+                                           check_invariants=False, is_coalesced=True)
+
     def _process_gradients(self, w_grad, batch_size):
         """Apply the gradient policy to the dense table gradient (reference: LUTLayer.py:567-609)."""
         policy = self._weights_gradient_policy
@@ -493,6 +529,10 @@ class LUTLayerBasic(nn.Module):
         external = x_grad is not None
         if not external and need_input_grad:
             x_grad = torch.zeros(x.numel(), dtype=torch.float32, device=self.device)
+        if (not external and self._weights_gradient_policy.type == GradientType.Sparse and self._is_fully_connected
+                and self._lut_dm.get_summations_data_type() == "float32" and self._sparse_rows_direct):
+            return self._backward_step_sparse_rows(x, grad_output, lookup_indices, min_anchor_deltas,
+                                                   min_anchor_delta_indices, x_grad, B)
         hook = getattr(self, "_table_update_hook", None)
         if hook is not None and not external:
             # data-parallel sharded table update: only the input gradient is computed here; the hook gathers the

@@ -89,6 +89,19 @@ class OracleDataManager:
         _acc(w_input_gradients, dX)
         _acc(w_weights_gradients, dW)
 
+    def table_gradient_rows(self, batch_size, r_output_gradients, r_lookup_indices):
+        """(row_ids, values) of the rows the batch touched, from the oracle's dense table gradient."""
+        r = self._real
+        B, Nt, T, O = batch_size, r._n_detectors, 1 << r._n_anchors, r._n_outputs
+        dY = _np(r_output_gradients).reshape(B, O)
+        idx = _np(r_lookup_indices).reshape(B, Nt).astype(np.int32)
+        anchors = np.zeros((Nt, r._n_anchors, 2), np.int32)  # only the (discarded) input gradient reads them
+        W = np.zeros(Nt * T * O, np.float32)
+        _, dW = orc.nonseq_fc_backward(W, dY, anchors, idx, np.ones(idx.shape, np.float32), np.zeros_like(idx),
+                                       r._n_inputs, r._n_anchors, forward_group_size=r._fwd_group, lr_meta=r._lr_meta())
+        rows = np.unique(np.arange(Nt, dtype=np.int64)[None, :] * T + idx)
+        return torch.from_numpy(rows), torch.from_numpy(dW.reshape(Nt * T, O)[rows].copy())
+
     def table_gradient(self, batch_size, r_output_gradients, r_lookup_indices, w_target, scale, chunk_begin=0,
                        chunk_end=None):
         """w_target[row(t, idx) + p] += scale * lr_meta * dY[b, target(p)] for the detectors of the chunk range."""
@@ -202,6 +215,59 @@ class OracleDataManager:
         _acc(w_input_gradients, dX)
         _acc(w_weights_gradients, dW)
         _acc(w_positional_embeddings_gradients, dPE)
+
+
+    # ---- stages of the concatenation-mode layer (query-range variants)
+    def check_detectors(self, rows, r_input, r_detector_anchors, w_lookup_indices, cmp_eps=0.0,
+                        w_min_anchor_deltas=None, w_min_anchor_delta_indices=None):
+        r = self._real
+        train = w_min_anchor_deltas is not None
+        res = orc.check_detectors(_np(r_input).reshape(rows, r._n_inputs), _np(r_detector_anchors), r._n_detectors,
+                                  r._n_anchors, cmp_eps, train)
+        idx, md, mk = res if train else (res, None, None)
+        _put(w_lookup_indices, idx)
+        _put(w_min_anchor_deltas, md)
+        _put(w_min_anchor_delta_indices, mk)
+
+    def check_positional(self, r_positional_embeddings, w_positional_lookup_indices, cmp_eps=0.0,
+                         w_positional_min_deltas=None, w_positional_min_delta_indices=None):
+        r = self._real
+        train = w_positional_min_deltas is not None
+        res = orc.check_positional(_np(r_positional_embeddings), r._seq_len, r._n_detectors, r._pos_dim, cmp_eps, train)
+        pidx, pm, pk = res if train else (res, None, None)
+        _put(w_positional_lookup_indices, pidx)
+        _put(w_positional_min_deltas, pm)
+        _put(w_positional_min_delta_indices, pk)
+
+    def concat_pairs_forward(self, r_weights, batch_size, r_lookup_indices, r_positional_lookup_indices, w_output,
+                             j_begin, j_end):
+        # every query's output depends on its own pairs only: the range is a slice of the full result
+        r = self._real
+        S = r._seq_len
+        y = orc.concat_pairs_forward(_np(r_weights), _np(r_lookup_indices).reshape(batch_size * S, r._n_detectors),
+                                     _np(r_positional_lookup_indices), batch_size, S, r._n_detectors, r._n_anchors,
+                                     r._n_outputs, r._pos_dim, **self._kw())
+        y[:, :j_begin] = 0.0
+        y[:, j_end:] = 0.0
+        _acc(w_output, y)
+        self._seen = True
+
+    def concat_pairs_backward(self, r_weights, batch_size, r_output_gradients, r_detector_anchors, r_lookup_indices,
+                              r_min_anchor_deltas, r_min_anchor_delta_indices, w_input_gradients, external_lr,
+                              r_positional_lookup_indices, r_positional_min_deltas, r_positional_min_delta_indices,
+                              w_positional_embeddings_gradients, w_weights_gradients, j_begin, j_end):
+        # a pair contributes through dY of its query only: zero gradients outside the range leave exactly the
+        # range's pairs (contributions with |dY| <= 1e-17 are dropped by the arithmetic itself)
+        r = self._real
+        S = r._seq_len
+        masked = r_output_gradients.detach().clone().view(batch_size, S, r._n_outputs)
+        masked[:, :j_begin] = 0.0
+        masked[:, j_end:] = 0.0
+        self.backward_backprop_concat(r_weights, batch_size, masked.view(-1), r_detector_anchors, r_lookup_indices,
+                                      r_min_anchor_deltas, r_min_anchor_delta_indices, w_input_gradients, external_lr,
+                                      r_positional_lookup_indices, r_positional_min_deltas,
+                                      r_positional_min_delta_indices, w_positional_embeddings_gradients,
+                                      w_weights_gradients)
 
 
 def use_oracle_backend(module):

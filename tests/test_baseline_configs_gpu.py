@@ -200,9 +200,15 @@ def test_char_transformer_config_layer_by_layer():
             y = l.forward_step_product(xt, pos)
             dx, dw, dpe = l.backward_step_product(xt, pos, torch.from_numpy(rec["dY"]).cuda())
         torch.cuda.synchronize()
-        golden_util.assert_close(y.cpu().numpy().reshape(rec["y"].shape), rec["y"], REL, what + " y")
+        y64 = dw64 = None
+        if rec["kind"] == "att":
+            # an output of the attention layer sums up to 127 x 64 table rows, a table cell hundreds of gradient rows:
+            # two fp32 summation orders need not agree to 1e-5; both are then held against the fp64 sums
+            cfg = dict(B=B, S=S, E=E, Nt=l._n_detectors, Nc=l._n_anchors_per_detector, Npe=l._positional_dim, O=E)
+            y64, dw64 = fp64_product_sums(cfg, rec["x"], rec["A"], rec["W"], rec["pe"], rec["dY"])
+        close_or_as_close_as_oracle(y.cpu().numpy().reshape(rec["y"].shape), rec["y"], y64, what + " y")
         golden_util.assert_close(dx.cpu().numpy().reshape(rec["dX"].shape), rec["dX"], REL, what + " dX")
-        golden_util.assert_close(dw.cpu().numpy().reshape(-1), rec["dW"].reshape(-1), REL, what + " dW")
+        close_or_as_close_as_oracle(dw.cpu().numpy().reshape(-1), rec["dW"].reshape(-1), dw64, what + " dW")
         if dpe is not None:
             golden_util.assert_close(dpe.cpu().numpy().reshape(-1), rec["dPE"].reshape(-1), REL, what + " dPE")
 
@@ -215,6 +221,8 @@ def fp64_product_sums(cfg, x, anchors, W, pe3, dY):
     dW_t = H[:, t]^T . dY in double."""
     B, S, E, Nt, Nc, Npe, O = (cfg[k] for k in ("B", "S", "E", "Nt", "Nc", "Npe", "O"))
     T = 1 << Nc
+    anchors = np.asarray(anchors).reshape(Nt, Nc, 2)
+    pe3 = None if pe3 is None else np.asarray(pe3).reshape(S - 1, Nt, Npe)
     W64 = W.reshape(Nt, T, O).astype(np.float64)
     y = np.zeros((B, S, O))
     dW = np.zeros((Nt, T, O))

@@ -160,7 +160,7 @@ class _HostConverter:
     """Stand-in for the CUDA compaction of the Sparse policy with the same contract: sorted non-zero cells, their
     values, the source buffer erased."""
 
-    def dense_to_sparse_32(self, buf, erase_input=True):
+    def dense_to_sparse_32(self, buf, erase_input=False):
         cells = torch.nonzero(buf.view(torch.int32) != 0).flatten()
         if cells.numel() == 0:
             return None, None
