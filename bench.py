@@ -281,8 +281,7 @@ class SparseConvNetWorkload:
         self.internal = internal
         self.name = ("sparse LUT conv-net training step (3 ProjectionLUTLayers 32/64/128 tables per position, "
                      f"Nc=8, 5x5 receptive, stride 2, 4x4 projection + LUT readout to 10), batch {batch}"
-                     + (", SGD update inside the backward kernel (Internal gradient policy)" if internal else "")
-                     + (", sharded in-place table update" if sharded else ""))
+                     + (", SGD update inside the backward kernel (Internal gradient policy)" if internal else ""))
 
     # ---- model
     def build(self, device):
@@ -1037,6 +1036,9 @@ def run_ours(args):
     wl.setup(device, rank)
     sync = _attach_data_parallel(wl, world)
     flush = torch.empty(2 * L2_BYTES, dtype=torch.uint8, device=device)
+    dp_strategy = None
+    if world > 1:
+        dp_strategy = "sharded table update" if getattr(wl, "sharded", False) else "gradient all-reduce"
 
     def barrier():
         if world > 1:
@@ -1081,6 +1083,34 @@ def run_ours(args):
     for _ in range(warmup):
         wl.step_device()
         finish_step(wl)
+    dp_trial = None
+    if world > 1 and args.workload == DEFAULT_WORKLOAD and args.dp == "auto":
+        # Two ways to keep the replicas' tables equal (same SGD step, spiky_b200/data_parallel.py): all-reduce the dense
+        # table gradients, or gather (index, output gradient) pairs and update a share of the tables in place.  Which one
+        # is faster depends on the number of ranks and on the interconnect: both are timed for a few steps and the
+        # faster one runs the measurement.
+        alt = WORKLOADS["sparse_convnet_sharded"](args.batch)
+        alt.setup(device, rank)
+        alt_sync = _attach_data_parallel(alt, world)
+        for _ in range(3):
+            alt.step_device()
+            finish_step(alt)
+        t_alt, _, _ = timed_region(alt, 8, profile=False)
+        t_cur, _, _ = timed_region(wl, 8, profile=False)
+        t = torch.tensor([t_cur, t_alt], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        t_cur, t_alt = t.tolist()
+        dp_trial = {"gradient all-reduce": t_cur, "sharded table update": t_alt}
+        if t_alt < t_cur:
+            if sync is not None:
+                sync.remove()
+            wl, sync, dp_strategy = alt, alt_sync, "sharded table update"
+        else:
+            alt.sharded_sync.remove()
+            if alt_sync is not None:
+                alt_sync.remove()
+            del alt
+        torch.cuda.empty_cache()
     ms_dev, prof, window = timed_region(wl, args.steps, profile=True)
 
     def e2e_region(steps):
@@ -1116,7 +1146,27 @@ def run_ours(args):
 
     # ---- data-parallel evidence: what the exchange costs, how fast the same payload moves alone, replicas identical
     comm = None
-    if world > 1 and sync is not None and wl.trainable_parameters():
+    if world > 1 and getattr(wl, "sharded", False):
+        # payload of the sharded update: every rank receives the other ranks' (index, output gradient) pairs and
+        # table shares; the weight all-gather of the same sizes is timed alone for comparison
+        tables = [l._weights for l in wl.layers[:-1]]
+        pairs = sum(l.n_detectors() + 4 * l.n_outputs() for l in wl.layers[:-1]) * wl.B
+        payload = (world - 1) * pairs + sum(p.numel() * p.element_size() for p in tables) * (world - 1) // world
+        iso = []
+        shares = [torch.zeros((p.numel() + world - 1) // world, device=device) for p in tables]
+        outs = [torch.empty(world * s_.numel(), device=device) for s_ in shares]
+        for rep in range(4):
+            barrier()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for s_, o_ in zip(shares, outs):
+                dist.all_gather_into_tensor(o_, s_)
+            b.record()
+            torch.cuda.synchronize()
+            iso.append(a.elapsed_time(b))
+        del shares, outs
+        comm = {"ms_local": 0.0, "ms_isolated": min(iso[1:]), "payload": payload, "sharded": True}
+    elif world > 1 and sync is not None and wl.trainable_parameters():
         params = wl.trainable_parameters()
         payload = sum(p.numel() * p.element_size() for p in params)
         sync.paused = True    # same step, gradients stay local: the difference is the exposed part of the exchange
@@ -1139,6 +1189,19 @@ def run_ours(args):
         comm = {"ms_local": ms_local, "ms_isolated": min(iso[1:]), "payload": payload}
     replica = _replica_check([p for l in getattr(wl, "layers", []) for p in [l._weights]] or wl.trainable_parameters(), world)
 
+    variants = None
+    if world == 1 and args.workload == DEFAULT_WORKLOAD and not args.no_secondary:
+        # the same training step with the SGD update made inside the backward kernel (the reference's
+        # GradientType.Internal): no dense gradient, no optimiser pass
+        w1 = WORKLOADS["sparse_convnet_internal"](args.batch)
+        w1.setup(device, rank)
+        for _ in range(3):
+            w1.step_device()
+        ms1, _, _ = timed_region(w1, 20, profile=False)
+        variants = {"internal_gradient_policy": {"ms_per_step": ms1, "value": w1.units_per_step / (ms1 / 1e3),
+                                                 "unit": w1.unit, "steps": 20}}
+        del w1
+        torch.cuda.empty_cache()
     secondary = None
     if args.workload == DEFAULT_WORKLOAD and not args.no_secondary:
         # the LUTTransformer half of the metric, measured in the same process on the same GPUs
@@ -1207,7 +1270,16 @@ def run_ours(args):
             "device_wait_errors": int(wait_errors),
             "clocks": clocks,
         }
-        if comm:
+        if comm and comm.get("sharded"):
+            gb = comm["payload"] / 1e9
+            line["comm"] = {
+                "exchange": "all-gather of (table index, output gradient) pairs, in-place update of a share of the tables, "
+                            "all-gather of the updated shares (NCCL), overlapped with the backward pass",
+                "payload_bytes_per_step": comm["payload"], "isolated_ms": ms_isolated,
+                "isolated_busbw_gbs": gb / (ms_isolated / 1e3), "frac_of_nvlink": gb / (ms_isolated / 1e3) / 900.0,
+                "isolated_what": "all-gather of the table shares alone (received bytes per rank / time)",
+            }
+        elif comm:
             ring = 2.0 * (world - 1) / world * comm["payload"] / 1e9
             exposed = max(ms_dev - ms_local, 1e-6)
             line["comm"] = {
@@ -1218,6 +1290,10 @@ def run_ours(args):
                 "frac_of_nvlink": ring / (ms_isolated / 1e3) / 900.0,
                 "hidden_frac": 1.0 - (ms_dev - ms_local) / ms_isolated,
             }
+        if dp_strategy:
+            line["dp_strategy"] = dp_strategy
+            if dp_trial:
+                line["dp_trial_ms_per_step"] = dp_trial
         if replica is not None:
             line["replica_check"] = replica
         if secondary:
@@ -1227,6 +1303,8 @@ def run_ours(args):
                                  "scaling": "weak"}
             if secondary["replica_check"] is not None:
                 line["secondary"]["replica_check"] = secondary["replica_check"]
+        if variants:
+            line["variants"] = variants
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(wl)
             if hasattr(wl, "parity_check"):
@@ -1267,6 +1345,9 @@ def main():
     ap.add_argument("--batch", type=int, default=None,
                     help="override the workload's per-GPU batch (batch sweeps; the default is the configuration's batch)")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU oracle timing (batch sweeps)")
+    ap.add_argument("--dp", default="auto", choices=["auto", "keep"],
+                    help="data-parallel runs of the default workload: auto = time both exchange strategies for a few "
+                         "steps and measure the faster one; keep = the workload as named")
     ap.add_argument("--no-secondary", action="store_true",
                     help="skip the character-transformer measurement that the default workload appends")
     ap.add_argument("--profile-only", action="store_true",

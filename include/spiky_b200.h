@@ -31,10 +31,9 @@ extern "C" {
 #define LUTB_ERR_ALIGN (-5)     /* a pointer is not aligned as documented */
 
 /* weight-gradient kernel selection for the backward entry points */
-#define LUTB_DW_AUTO 0      /* the library's choice: currently ATOMIC */
+#define LUTB_DW_AUTO 0      /* the library's choice between the two below, from the measured contention sweep (batch
+                               against rows per table) recorded with the kernels in nonseq_fc.cu */
 #define LUTB_DW_ATOMIC 1    /* row-coalesced global reductions (red.global.add.v4.f32 into L2) */
-#define LUTB_DW_SMEM 2      /* reserved for shared-memory privatised table slices; runs the ATOMIC kernel: on B200 shared
-                               fp32 atomics sustained 0.8 T adds/s against 1.5 T adds/s for L2 reductions */
 #define LUTB_DW_SORTED 3    /* counting sort of the batch by row + segmented reduce; deterministic order; needs workspace */
 
 /*
@@ -187,23 +186,24 @@ typedef struct lutb_sparse_index {
 } lutb_sparse_index;
 
 /*
- * Kernel family of the forward and input-gradient passes of sparse non-sequence layers (no reference counterpart:
- * the reference has one kernel per pass).  Process-wide; the environment variable LUTB_SPARSE_KERNELS=auto|gather|staged
- * sets the initial value.
+ * Kernel family of the forward pass and of the input-gradient pass of sparse non-sequence layers, chosen independently
+ * (no reference counterpart: the reference has one kernel per pass).  Process-wide; the environment variable
+ * LUTB_SPARSE_KERNELS="<forward>,<input gradient>" (or one word for both: auto, gather, staged) sets the initial value.
  *   GATHER  one warp per (detector chunk, few samples); the selected rows are fetched through L2.  Any layer.
  *   STAGED  a block owns a range of detectors for 512 samples at a time; whole tables are streamed through a
  *           shared-memory ring (cp.async.bulk + mbarrier) and the samples' rows are read from there.  fp32 accumulators,
  *           rows of at most 32 synapses, tables_aligned16, three tables must fit 227 KB; LUTB_ERR_MODE when forced and
  *           not possible.
- *   AUTO    STAGED when possible, 2 * batch >= rows per table and the layer has at least 4 detectors per SM, else GATHER.
- * lutb_device_wait_errors: every device-side wait of the staged kernels is bounded (1 s); a wait that runs out makes
- * its block leave early (results are then incomplete) and is counted here.  Reads the counter of the current device
- * and synchronises it; 0 in a healthy run.
+ *   AUTO    forward: STAGED when possible, 2 * batch >= rows per table and the layer has at least 4 detectors per SM,
+ *           else GATHER; input gradient: GATHER (the staged variant measured slower on B200).
+ * lutb_device_wait_errors: every device-side wait of the staged kernels is bounded (about a second); a wait that runs
+ * out makes its block leave early (results are then incomplete) and is counted here.  Reads the counter of the current
+ * device and synchronises it; 0 in a healthy run.
  */
 #define LUTB_SPARSE_AUTO 0
 #define LUTB_SPARSE_GATHER 1
 #define LUTB_SPARSE_STAGED 2
-int lutb_sparse_kernel_select(int kernels);
+int lutb_sparse_kernel_select(int forward_kernels, int input_grad_kernels);
 int lutb_device_wait_errors(int *count_out);
 
 /*
@@ -266,18 +266,22 @@ int lutb_product_forward(const lutb_layer_cfg *cfg, int64_t batch, int32_t seq_l
  * Kernel variants of the product-mode layer (no reference counterpart: the reference has one kernel per pass).
  *   DIRECT  one table row per (pair, detector) is gathered (forward) or gathered twice and scatter-added
  *           (backward) through L2; needs no workspace.
- *   HIST    per (query, detector) the selected rows are counted into a histogram first and the pass becomes
- *           a register-tiled fp32 contraction with the tables (see spiky_b200/csrc/product_hist.cuh); fp32
- *           accumulators only, 4 <= Nc <= 12, O % 4 == 0, 16-byte aligned tensors, and a caller workspace of at
- *           least lutb_product_workspace(cfg, 1, S, backward) bytes (the batch is processed in chunks of as
- *           many sequences as fit); LUTB_ERR_WORKSPACE / LUTB_ERR_MODE when asked for and not possible.
+ *   HIST    per (query, detector) the selected rows are counted into a histogram first and the pass becomes dense
+ *           contractions with the tables (see spiky_b200/csrc/product_hist.cuh): on the tensor cores when the library
+ *           was built with them (lutb_fp32_gemm_available) and the workspace holds one sequence in their operand
+ *           layout, else as register-tiled fp32 FMA contractions; fp32 accumulators only, 4 <= Nc <= 12, O % 4 == 0,
+ *           16-byte aligned tensors, and a caller workspace of at least lutb_product_workspace(cfg, 1, S, backward)
+ *           bytes (the batch is processed in chunks of as many sequences as fit); LUTB_ERR_WORKSPACE / LUTB_ERR_MODE
+ *           when asked for and not possible.
+ *   HIST_FMA  HIST with the fp32 FMA contractions forced.
  *   AUTO    HIST when it is possible, a workspace is supplied and the sequence is long enough against the
- *           table (forward: S >= 2^Nc; backward: 4 * S >= 2^Nc), else DIRECT.
+ *           table (4 * S >= 2^Nc; forward without tensor cores: S >= 2^Nc), else DIRECT.
  * lutb_product_workspace returns the bytes that let `batch` sequences go through in one chunk.
  */
 #define LUTB_PRODUCT_AUTO 0
 #define LUTB_PRODUCT_DIRECT 1
 #define LUTB_PRODUCT_HIST 2
+#define LUTB_PRODUCT_HIST_FMA 3
 size_t lutb_product_workspace(const lutb_layer_cfg *cfg, int64_t batch, int32_t seq_len, int backward);
 
 /*
@@ -401,6 +405,32 @@ int lutb_count_nonzero_32(const void *source, int64_t n, int64_t *count_out, voi
                           void *stream);
 int lutb_dense_to_sparse_32(void *source, int64_t n, int64_t *indices, void *values, int64_t capacity,
                             int64_t *count_out, int erase_input, void *workspace, size_t workspace_bytes, void *stream);
+
+/*
+ * fp32 GEMM on the sm_100a tensor cores with fp32-class accuracy (no reference counterpart; the reference has no
+ * dense contraction): C [m x n] row-major = alpha * op(A) . op(B) + beta * C.  Default route: every operand is written
+ * once as hi (low 13 mantissa bits cleared: exact in TF32) and lo = x - hi, and hi.hi + hi.lo + lo.hi is accumulated by
+ * three TF32 GEMMs (tcgen05.mma, fp32 accumulators in tensor memory, operands staged by TMA); with
+ * LUTB_GEMM_FAST_FP32 or'ed into `kind` a single GEMM splits the operands into BF16 terms inside its mainloop
+ * instead (no scratch copies, about half the speed).  Either way results agree with an fp32 FMA contraction to about
+ * 1e-6 relative.  The long-sequence (histogram) path of the product-mode layer runs its three contractions through the
+ * default route.
+ *   kind  LUTB_GEMM_A_ROWS_B_ROWS_OF_N: A [m x k] row-major, B stored as [n x k] row-major (C = A . B^T)
+ *         LUTB_GEMM_A_ROWS_B_ROWS_OF_K: A [m x k] row-major, B stored as [k x n] row-major (C = A . B)
+ *         LUTB_GEMM_A_COLS_B_ROWS_OF_K: A stored as [k x m] row-major, B as [k x n] row-major (C = A^T . B)
+ * Pointers 16-byte aligned, leading dimensions and row lengths multiples of 4; workspace of
+ * lutb_fp32_gemm_workspace(m, n, k) bytes (it holds the hi / lo copies).
+ * lutb_fp32_gemm_available() is 0 when the library was built without a CUTLASS header tree (the call then fails with
+ * LUTB_ERR_MODE and the histogram path keeps its fp32 FMA contractions).
+ */
+#define LUTB_GEMM_A_ROWS_B_ROWS_OF_N 0
+#define LUTB_GEMM_A_ROWS_B_ROWS_OF_K 1
+#define LUTB_GEMM_A_COLS_B_ROWS_OF_K 2
+#define LUTB_GEMM_FAST_FP32 16
+int lutb_fp32_gemm_available(void);
+size_t lutb_fp32_gemm_workspace(int32_t m, int32_t n, int32_t k);
+int lutb_fp32_gemm(int kind, int32_t m, int32_t n, int32_t k, const float *a, int64_t lda, const float *b, int64_t ldb,
+                   float *c, int64_t ldc, float alpha, float beta, void *workspace, size_t workspace_bytes, void *stream);
 
 #ifdef __cplusplus
 }

@@ -10,10 +10,10 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "lib", "libspiky_b200.so")
 
 # dW kernel variants (include/spiky_b200.h)
-DW_AUTO, DW_ATOMIC, DW_SMEM, DW_SORTED = 0, 1, 2, 3
+DW_AUTO, DW_ATOMIC, DW_SORTED = 0, 1, 3
 SKIP_TABLE_GRADIENT = -2.0  # external_lr value: input gradient only (lutb_nonseq_sparse_backward)
 # product-mode kernel variants (include/spiky_b200.h)
-PRODUCT_AUTO, PRODUCT_DIRECT, PRODUCT_HIST = 0, 1, 2
+PRODUCT_AUTO, PRODUCT_DIRECT, PRODUCT_HIST, PRODUCT_HIST_FMA = 0, 1, 2, 3
 # de-quantisation rules of the int8 inference path (include/spiky_b200.h)
 INT8_DEQUANT_F32, INT8_DEQUANT_EXACT = 0, 1
 # kernel family of the sparse forward / input-gradient passes (include/spiky_b200.h)
@@ -103,8 +103,12 @@ SIGNATURES = {
     "lutb_dense_to_sparse_workspace": (_size, [_i64]),
     "lutb_count_nonzero_32": (_int, [_vp, _i64, _vp, _vp, _size, _vp]),
     "lutb_dense_to_sparse_32": (_int, [_vp, _i64, _vp, _vp, _i64, _vp, _int, _vp, _size, _vp]),
-    "lutb_sparse_kernel_select": (_int, [_int]),
+    "lutb_sparse_kernel_select": (_int, [_int, _int]),
     "lutb_device_wait_errors": (_int, [ctypes.POINTER(_int)]),
+    "lutb_fp32_gemm_available": (_int, []),
+    "lutb_fp32_gemm_workspace": (_size, [ctypes.c_int32, ctypes.c_int32, ctypes.c_int32]),
+    "lutb_fp32_gemm": (_int, [_int, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, _vp, _i64, _vp, _i64, _vp, _i64,
+                              ctypes.c_float, ctypes.c_float, _vp, _size, _vp]),
     "lutb_nonseq_sparse_forward": (_int, [_cfgp, _spp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "lutb_nonseq_sparse_backward": (_int, [_cfgp, _spp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _dbl, _vp]),
     "lutb_nonseq_sparse_table_grad": (_int, [_cfgp, _spp, _i64, _vp, _vp, _int, _vp, _dbl, _i64, _i64, _vp]),
@@ -165,9 +169,10 @@ def profiler_read():
     return out
 
 
-def sparse_kernel_select(kernels):
-    """Force the gather or the staged kernels for sparse layers (SPARSE_AUTO restores the library's choice)."""
-    check(lib().lutb_sparse_kernel_select(int(kernels)))
+def sparse_kernel_select(forward, input_grad=None):
+    """Force the gather or the staged kernels for the forward and the input-gradient pass of sparse layers
+    (SPARSE_AUTO restores the library's choice; one argument sets both passes)."""
+    check(lib().lutb_sparse_kernel_select(int(forward), int(forward if input_grad is None else input_grad)))
 
 
 def device_wait_errors():

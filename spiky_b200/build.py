@@ -34,6 +34,36 @@ def _host_compiler():
     return ["-ccbin", "/usr/bin/g++"] if os.path.exists("/usr/bin/g++") else []
 
 
+def _cutlass_includes():
+    """Include directories of the CUTLASS / CuTe header tree shipped inside the flashinfer package (headers only;
+    used by fp32_gemm_sm100.cu).  Empty when no tree is found: that file then builds its stubs."""
+    import importlib.util
+    for pkg, sub in (("flashinfer", ("data", "cutlass")), ("tilelang", ("3rdparty", "cutlass"))):
+        try:
+            spec = importlib.util.find_spec(pkg)
+        except (ImportError, ValueError):
+            spec = None
+        if spec is None or not spec.submodule_search_locations:
+            continue
+        root = os.path.join(list(spec.submodule_search_locations)[0], *sub)
+        inc, util = os.path.join(root, "include"), os.path.join(root, "tools", "util", "include")
+        if os.path.exists(os.path.join(inc, "cutlass", "gemm", "collective", "builders", "sm100_9xBF16_umma_builder.inl")):
+            return [inc] + ([util] if os.path.isdir(util) else [])
+    return []
+
+
+def _extra_flags(src):
+    if os.path.basename(src) != "fp32_gemm_sm100.cu":
+        return []
+    inc = _cutlass_includes()
+    if not inc:
+        return ["-DLUTB_NO_CUTLASS"]
+    flags = ["--expt-relaxed-constexpr"]
+    for d in inc:
+        flags += ["-I", d]
+    return flags
+
+
 def _newest(paths):
     return max(os.path.getmtime(p) for p in paths)
 
@@ -54,7 +84,7 @@ def build(force=False, verbose=False):
         obj = os.path.join(objdir, os.path.basename(src)[:-3] + ".o")
         if not force and os.path.exists(obj) and os.path.getmtime(obj) >= max(os.path.getmtime(src), hdr_time):
             return obj, ""
-        cmd = [nvcc] + ARCH + FLAGS + _host_compiler() + ["-c", src, "-o", obj]
+        cmd = [nvcc] + ARCH + FLAGS + _extra_flags(src) + _host_compiler() + ["-c", src, "-o", obj]
         p = subprocess.run(cmd, capture_output=True, text=True)
         if p.returncode != 0:
             raise RuntimeError("nvcc failed for %s:\n%s\n%s" % (src, p.stdout, p.stderr))

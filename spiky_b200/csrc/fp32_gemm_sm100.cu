@@ -1,0 +1,289 @@
+// fp32 GEMMs on the sm_100a tensor cores for the contractions of the product-mode histogram path.
+//
+// The contractions (product_hist.cuh) multiply exact small integers (row counts) or fp32 tables / gradients and must
+// keep fp32 accuracy (parity bar 1e-5), so plain TF32 or BF16 inputs are not an option.  Two routes, both CUTLASS 3
+// collectives instantiated for sm_100a (operands arrive in shared memory by TMA - cluster 1x1x1: plain copies of this
+// GPU's own memory -, tcgen05.mma accumulates in fp32 in tensor memory, the epilogue reads the accumulators back with
+// tcgen05.ld and applies alpha / beta):
+//
+//   split TF32 (default)  every fp32 operand x is written once as hi = x with the low 13 mantissa bits cleared and
+//                         lo = x - hi (exact), and the product is formed as hi.hi + hi.lo + lo.hi by up to three TF32
+//                         GEMMs that accumulate into C; an operand that holds integers below 2048 (row counts) is
+//                         exact in TF32 and needs no split, which leaves two GEMMs.  The dropped lo.lo term and the
+//                         truncation of lo to TF32 are below 2^-21 relative.
+//   fast fp32             one GEMM whose mainloop splits the operands into three BF16 terms on the fly (CUTLASS'
+//                         "FastF32" schedule); simpler, no scratch, but bound by the conversion work: 80-90 TFLOP/s on
+//                         the contraction shapes against 2-3 times that for the split TF32 route.
+//
+// Results agree with an fp32 FMA contraction to about 1e-6 relative; the summation order differs.
+// All matrices are fp32 with 16-byte aligned base pointers and leading dimensions that are multiples of 4.
+#include "fp32_gemm_sm100.cuh"
+
+#ifdef LUTB_NO_CUTLASS
+// built without a CUTLASS header tree: the callers keep their fp32 FMA contractions
+namespace lutb {
+bool tc_gemm_available() { return false; }
+size_t tc_gemm_workspace(int, int, int, bool) { return 0; }
+size_t tc_gemm_fast_workspace(int, int, int) { return 0; }
+int tc_gemm(TcGemmKind, int, int, int, const float *, int64_t, const float *, int64_t, float *, int64_t, float, float, bool,
+            void *, size_t, cudaStream_t) {
+    set_error("the library was built without the tensor-core contractions (no CUTLASS headers at build time)");
+    return LUTB_ERR_MODE;
+}
+int tc_gemm_fast(TcGemmKind, int, int, int, const float *, int64_t, const float *, int64_t, float *, int64_t, float, float,
+                 void *, size_t, cudaStream_t) {
+    set_error("the library was built without the tensor-core contractions (no CUTLASS headers at build time)");
+    return LUTB_ERR_MODE;
+}
+}  // namespace lutb
+#else
+
+#include "cutlass/cutlass.h"
+#include "cutlass/epilogue/collective/collective_builder.hpp"
+#include "cutlass/gemm/collective/collective_builder.hpp"
+#include "cutlass/gemm/device/gemm_universal_adapter.h"
+#include "cutlass/gemm/kernel/gemm_universal.hpp"
+#include "cutlass/util/packed_stride.hpp"
+
+namespace lutb {
+
+using namespace cute;
+
+template <class LayoutA, class LayoutB>
+struct FastF32Gemm {
+    using Element = float;
+    using LayoutC = cutlass::layout::RowMajor;
+    static constexpr int kAlign = 4;   // 16 bytes
+    using MmaTile = Shape<_128, _128, _16>;
+    using Cluster = Shape<_1, _1, _1>;
+    using Epilogue = typename cutlass::epilogue::collective::CollectiveBuilder<
+        cutlass::arch::Sm100, cutlass::arch::OpClassTensorOp, MmaTile, Cluster,
+        cutlass::epilogue::collective::EpilogueTileAuto, float, float, Element, LayoutC, kAlign, Element, LayoutC, kAlign,
+        cutlass::epilogue::collective::EpilogueScheduleAuto>::CollectiveOp;
+    using Mainloop = typename cutlass::gemm::collective::CollectiveBuilder<
+        cutlass::arch::Sm100, cutlass::arch::OpClassTensorOp, Element, LayoutA, kAlign, Element, LayoutB, kAlign, float, MmaTile,
+        Cluster, cutlass::gemm::collective::StageCountAutoCarveout<static_cast<int>(sizeof(typename Epilogue::SharedStorage))>,
+        cutlass::gemm::KernelTmaWarpSpecialized1SmFastFP32Sm100>::CollectiveOp;
+    using Kernel = cutlass::gemm::kernel::GemmUniversal<Shape<int, int, int, int>, Mainloop, Epilogue>;
+    using Gemm = cutlass::gemm::device::GemmUniversalAdapter<Kernel>;
+    using StrideA = typename Kernel::StrideA;
+    using StrideB = typename Kernel::StrideB;
+    using StrideC = typename Kernel::StrideC;
+    using StrideD = typename Kernel::StrideD;
+};
+
+template <class LayoutA, class LayoutB>
+struct Tf32Gemm {
+    using Element = cutlass::tfloat32_t;   // fp32 storage; the MMA reads sign, exponent and the top 10 mantissa bits
+    using LayoutC = cutlass::layout::RowMajor;
+    static constexpr int kAlign = 4;
+    using MmaTile = Shape<_128, _128, _32>;
+    using Cluster = Shape<_1, _1, _1>;
+    using Epilogue = typename cutlass::epilogue::collective::CollectiveBuilder<
+        cutlass::arch::Sm100, cutlass::arch::OpClassTensorOp, MmaTile, Cluster,
+        cutlass::epilogue::collective::EpilogueTileAuto, float, float, float, LayoutC, kAlign, float, LayoutC, kAlign,
+        cutlass::epilogue::collective::EpilogueScheduleAuto>::CollectiveOp;
+    using Mainloop = typename cutlass::gemm::collective::CollectiveBuilder<
+        cutlass::arch::Sm100, cutlass::arch::OpClassTensorOp, Element, LayoutA, kAlign, Element, LayoutB, kAlign, float, MmaTile,
+        Cluster, cutlass::gemm::collective::StageCountAutoCarveout<static_cast<int>(sizeof(typename Epilogue::SharedStorage))>,
+        cutlass::gemm::collective::KernelScheduleAuto>::CollectiveOp;
+    using Kernel = cutlass::gemm::kernel::GemmUniversal<Shape<int, int, int, int>, Mainloop, Epilogue>;
+    using Gemm = cutlass::gemm::device::GemmUniversalAdapter<Kernel>;
+    using StrideA = typename Kernel::StrideA;
+    using StrideB = typename Kernel::StrideB;
+    using StrideC = typename Kernel::StrideC;
+    using StrideD = typename Kernel::StrideD;
+};
+
+template <class Cfg>
+static size_t workspace_of(int M, int N, int K) {
+    typename Cfg::Gemm::Arguments args{cutlass::gemm::GemmUniversalMode::kGemm, {M, N, K, 1}};
+    return Cfg::Gemm::get_workspace_size(args);
+}
+
+template <class Cfg>
+static int run(int M, int N, int K, const float *A, int64_t lda, const float *B, int64_t ldb, float *C, int64_t ldc,
+               float alpha, float beta, void *workspace, size_t workspace_bytes, cudaStream_t stream) {
+    typename Cfg::StrideA sa;
+    typename Cfg::StrideB sb;
+    typename Cfg::StrideC sc;
+    // the dynamic (non unit) mode of every stride is the leading dimension; one batch
+    if constexpr (cute::is_same_v<decltype(get<1>(sa)), cute::Int<1>>) sa = make_stride(lda, Int<1>{}, int64_t(0));
+    else sa = make_stride(Int<1>{}, lda, int64_t(0));
+    if constexpr (cute::is_same_v<decltype(get<1>(sb)), cute::Int<1>>) sb = make_stride(ldb, Int<1>{}, int64_t(0));
+    else sb = make_stride(Int<1>{}, ldb, int64_t(0));
+    sc = make_stride(ldc, Int<1>{}, int64_t(0));
+    using ElementAB = typename Cfg::Element;
+    typename Cfg::Gemm::Arguments args{cutlass::gemm::GemmUniversalMode::kGemm,
+                                       {M, N, K, 1},
+                                       {reinterpret_cast<const ElementAB *>(A), sa, reinterpret_cast<const ElementAB *>(B), sb},
+                                       {{alpha, beta}, C, sc, C, sc}};
+    typename Cfg::Gemm gemm;
+    LUTB_REQUIRE(gemm.can_implement(args) == cutlass::Status::kSuccess, LUTB_ERR_SHAPE,
+                 "tensor-core contraction: shapes or alignments not supported (M=%d N=%d K=%d)", M, N, K);
+    const size_t need = Cfg::Gemm::get_workspace_size(args);
+    LUTB_REQUIRE(need <= workspace_bytes, LUTB_ERR_WORKSPACE, "tensor-core contraction needs %zu bytes of workspace", need);
+    cutlass::Status st = gemm.initialize(args, workspace, stream);
+    LUTB_REQUIRE(st == cutlass::Status::kSuccess, LUTB_ERR_MODE, "tensor-core contraction: initialisation failed (%d)", (int)st);
+    st = gemm.run(stream);
+    LUTB_REQUIRE(st == cutlass::Status::kSuccess, LUTB_ERR_MODE, "tensor-core contraction: launch failed (%d)", (int)st);
+    return LUTB_OK;
+}
+
+// operand layouts: TN = A [M x K] row-major, B stored as [N x K] row-major; NN = A [M x K], B [K x N] row-major;
+// TT = A stored as [K x M] row-major, B [K x N] row-major
+using FastTN = FastF32Gemm<cutlass::layout::RowMajor, cutlass::layout::ColumnMajor>;
+using FastNN = FastF32Gemm<cutlass::layout::RowMajor, cutlass::layout::RowMajor>;
+using FastTT = FastF32Gemm<cutlass::layout::ColumnMajor, cutlass::layout::RowMajor>;
+using Tf32TN = Tf32Gemm<cutlass::layout::RowMajor, cutlass::layout::ColumnMajor>;
+using Tf32NN = Tf32Gemm<cutlass::layout::RowMajor, cutlass::layout::RowMajor>;
+using Tf32TT = Tf32Gemm<cutlass::layout::ColumnMajor, cutlass::layout::RowMajor>;
+
+bool tc_gemm_available() { return true; }
+
+// hi = x with the low 13 mantissa bits cleared (exactly representable in TF32), lo = x - hi (exact in fp32)
+__global__ void split_tf32_kernel(const float *__restrict__ x, int64_t rows, int64_t cols, int64_t ld, float *__restrict__ hi,
+                                  float *__restrict__ lo) {
+    const int64_t n4 = rows * (cols / 4);
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i / (cols / 4), c = (i - r * (cols / 4)) * 4;
+        const float4 v = *reinterpret_cast<const float4 *>(x + r * ld + c);
+        float4 h, l;
+        h.x = __uint_as_float(__float_as_uint(v.x) & 0xFFFFE000u); l.x = v.x - h.x;
+        h.y = __uint_as_float(__float_as_uint(v.y) & 0xFFFFE000u); l.y = v.y - h.y;
+        h.z = __uint_as_float(__float_as_uint(v.z) & 0xFFFFE000u); l.z = v.z - h.z;
+        h.w = __uint_as_float(__float_as_uint(v.w) & 0xFFFFE000u); l.w = v.w - h.w;
+        *reinterpret_cast<float4 *>(hi + r * cols + c) = h;
+        *reinterpret_cast<float4 *>(lo + r * cols + c) = l;
+    }
+}
+
+static int split(const float *x, int64_t rows, int64_t cols, int64_t ld, float *hi, float *lo, cudaStream_t stream) {
+    const int64_t n4 = rows * (cols / 4);
+    int64_t blocks = (n4 + 255) / 256;
+    const int64_t cap = (int64_t)device_info().sm_count * 16;
+    if (blocks > cap) blocks = cap;
+    split_tf32_kernel<<<(unsigned)blocks, 256, 0, stream>>>(x, rows, cols, ld, hi, lo);
+    LUTB_LAUNCH_CHECK();
+    return LUTB_OK;
+}
+
+// stored extents of the operands of a kind: A is [ar x ac], B is [br x bc] (row-major, contiguous in the second)
+static void stored_extents(TcGemmKind kind, int M, int N, int K, int64_t *ar, int64_t *ac, int64_t *br, int64_t *bc) {
+    *ar = kind == TC_A_COLS_B_ROWS_OF_K ? K : M;
+    *ac = kind == TC_A_COLS_B_ROWS_OF_K ? M : K;
+    *br = kind == TC_A_ROWS_B_ROWS_OF_N ? N : K;
+    *bc = kind == TC_A_ROWS_B_ROWS_OF_N ? K : N;
+}
+
+static size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
+
+size_t tc_gemm_workspace(int M, int N, int K, bool a_exact) {
+    size_t w = workspace_of<Tf32TN>(M, N, K);
+    const size_t w2 = workspace_of<Tf32NN>(M, N, K), w3 = workspace_of<Tf32TT>(M, N, K);
+    w = w > w2 ? w : w2;
+    w = w > w3 ? w : w3;
+    // split copies: B always, A unless exact
+    const size_t a = a_exact ? 0 : 2 * align256((size_t)M * K * 4), b = 2 * align256((size_t)N * K * 4);
+    return align256(w) + a + b + 256;
+}
+
+template <class Cfg>
+static int run3(int M, int N, int K, const float *Ah, const float *Al, int64_t lda, const float *Bh, const float *Bl, int64_t ldb,
+                float *C, int64_t ldc, float alpha, float beta, void *ws, size_t ws_bytes, cudaStream_t stream) {
+    // small terms first, so that they are added to each other before they meet the large one
+    int rc = run<Cfg>(M, N, K, Ah, lda, Bl, ldb, C, ldc, alpha, beta, ws, ws_bytes, stream);
+    if (rc) return rc;
+    if (Al != nullptr) {
+        rc = run<Cfg>(M, N, K, Al, lda, Bh, ldb, C, ldc, alpha, 1.f, ws, ws_bytes, stream);
+        if (rc) return rc;
+    }
+    return run<Cfg>(M, N, K, Ah, lda, Bh, ldb, C, ldc, alpha, 1.f, ws, ws_bytes, stream);
+}
+
+int tc_gemm(TcGemmKind kind, int M, int N, int K, const float *A, int64_t lda, const float *B, int64_t ldb, float *C,
+            int64_t ldc, float alpha, float beta, bool a_exact, void *workspace, size_t workspace_bytes, cudaStream_t stream) {
+    LUTB_REQUIRE(workspace_bytes >= tc_gemm_workspace(M, N, K, a_exact), LUTB_ERR_WORKSPACE,
+                 "tensor-core contraction needs %zu bytes of workspace", tc_gemm_workspace(M, N, K, a_exact));
+    int64_t ar, ac, br, bc;
+    stored_extents(kind, M, N, K, &ar, &ac, &br, &bc);
+    LUTB_REQUIRE(ac % 4 == 0 && bc % 4 == 0, LUTB_ERR_ALIGN, "tensor-core contraction: row lengths must be multiples of 4");
+    unsigned char *p = static_cast<unsigned char *>(workspace);
+    p = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(p) + 255) & ~(uintptr_t)255);
+    size_t gemm_ws = workspace_of<Tf32TN>(M, N, K);
+    {
+        const size_t w2 = workspace_of<Tf32NN>(M, N, K), w3 = workspace_of<Tf32TT>(M, N, K);
+        gemm_ws = gemm_ws > w2 ? gemm_ws : w2;
+        gemm_ws = align256(gemm_ws > w3 ? gemm_ws : w3);
+    }
+    void *gw = p;
+    p += gemm_ws;
+    const size_t bsz = align256((size_t)N * K * 4), asz = align256((size_t)M * K * 4);
+    float *Bh = reinterpret_cast<float *>(p), *Bl = reinterpret_cast<float *>(p + bsz);
+    p += 2 * bsz;
+    int rc = split(B, br, bc, ldb, Bh, Bl, stream);
+    if (rc) return rc;
+    const float *Ah = A, *Al = nullptr;
+    int64_t lda_s = lda;
+    if (!a_exact) {
+        float *h = reinterpret_cast<float *>(p), *l = reinterpret_cast<float *>(p + asz);
+        rc = split(A, ar, ac, lda, h, l, stream);
+        if (rc) return rc;
+        Ah = h; Al = l; lda_s = ac;
+    }
+    switch (kind) {
+        case TC_A_ROWS_B_ROWS_OF_N: return run3<Tf32TN>(M, N, K, Ah, Al, lda_s, Bh, Bl, bc, C, ldc, alpha, beta, gw, gemm_ws, stream);
+        case TC_A_ROWS_B_ROWS_OF_K: return run3<Tf32NN>(M, N, K, Ah, Al, lda_s, Bh, Bl, bc, C, ldc, alpha, beta, gw, gemm_ws, stream);
+        default: return run3<Tf32TT>(M, N, K, Ah, Al, lda_s, Bh, Bl, bc, C, ldc, alpha, beta, gw, gemm_ws, stream);
+    }
+}
+
+size_t tc_gemm_fast_workspace(int M, int N, int K) {
+    size_t w = workspace_of<FastTN>(M, N, K);
+    const size_t w2 = workspace_of<FastNN>(M, N, K), w3 = workspace_of<FastTT>(M, N, K);
+    w = w > w2 ? w : w2;
+    return (w > w3 ? w : w3) + 256;
+}
+
+int tc_gemm_fast(TcGemmKind kind, int M, int N, int K, const float *A, int64_t lda, const float *B, int64_t ldb, float *C,
+                 int64_t ldc, float alpha, float beta, void *workspace, size_t workspace_bytes, cudaStream_t stream) {
+    switch (kind) {
+        case TC_A_ROWS_B_ROWS_OF_N: return run<FastTN>(M, N, K, A, lda, B, ldb, C, ldc, alpha, beta, workspace, workspace_bytes, stream);
+        case TC_A_ROWS_B_ROWS_OF_K: return run<FastNN>(M, N, K, A, lda, B, ldb, C, ldc, alpha, beta, workspace, workspace_bytes, stream);
+        default: return run<FastTT>(M, N, K, A, lda, B, ldb, C, ldc, alpha, beta, workspace, workspace_bytes, stream);
+    }
+}
+
+}  // namespace lutb
+#endif  // LUTB_NO_CUTLASS
+
+// C-ABI face of the contraction (used by the tests and by callers that want the same fp32-accurate tensor-core GEMM
+// the histogram path uses).
+extern "C" int lutb_fp32_gemm_available(void) { return lutb::tc_gemm_available() ? 1 : 0; }
+
+extern "C" size_t lutb_fp32_gemm_workspace(int32_t m, int32_t n, int32_t k) {
+    if (!(m > 0 && n > 0 && k > 0)) return 0;
+    const size_t a = lutb::tc_gemm_workspace(m, n, k, false), b = lutb::tc_gemm_fast_workspace(m, n, k);
+    return a > b ? a : b;
+}
+
+extern "C" int lutb_fp32_gemm(int kind, int32_t m, int32_t n, int32_t k, const float *a, int64_t lda, const float *b,
+                              int64_t ldb, float *c, int64_t ldc, float alpha, float beta, void *workspace,
+                              size_t workspace_bytes, void *stream) {
+    using namespace lutb;
+    const bool fast = (kind & LUTB_GEMM_FAST_FP32) != 0;
+    kind &= ~LUTB_GEMM_FAST_FP32;
+    LUTB_REQUIRE(kind >= LUTB_GEMM_A_ROWS_B_ROWS_OF_N && kind <= LUTB_GEMM_A_COLS_B_ROWS_OF_K, LUTB_ERR_MODE, "unknown GEMM kind %d", kind);
+    LUTB_REQUIRE(m > 0 && n > 0 && k > 0, LUTB_ERR_SHAPE, "empty GEMM");
+    LUTB_REQUIRE(a && b && c, LUTB_ERR_NULL, "a matrix pointer is NULL");
+    LUTB_REQUIRE(((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(c)) & 15) == 0,
+                 LUTB_ERR_ALIGN, "matrices must be 16-byte aligned");
+    LUTB_REQUIRE(((lda | ldb | ldc) & 3) == 0, LUTB_ERR_ALIGN, "leading dimensions must be multiples of 4");
+    KernelScope scope(K_FP32_GEMM, static_cast<cudaStream_t>(stream));
+    if (fast)
+        return tc_gemm_fast(static_cast<TcGemmKind>(kind), m, n, k, a, lda, b, ldb, c, ldc, alpha, beta, workspace,
+                            workspace_bytes, static_cast<cudaStream_t>(stream));
+    return tc_gemm(static_cast<TcGemmKind>(kind), m, n, k, a, lda, b, ldb, c, ldc, alpha, beta, false, workspace, workspace_bytes,
+                   static_cast<cudaStream_t>(stream));
+}
+

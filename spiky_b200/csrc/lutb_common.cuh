@@ -89,6 +89,7 @@ enum KernelId {
     K_PRODUCT_ROUTE,
     K_PRODUCT_HIST_WEIGHT_GRAD,
     K_DENSE_TO_SPARSE,
+    K_FP32_GEMM,
     K_COUNT
 };
 

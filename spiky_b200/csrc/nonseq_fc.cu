@@ -766,7 +766,8 @@ extern "C" int lutb_nonseq_fc_backward(const lutb_layer_cfg *cfg, int64_t batch,
     int rc = validate_cfg(cfg);
     if (rc) return rc;
     LUTB_REQUIRE(cfg->seq_len == 1, LUTB_ERR_MODE, "backward_backprop should only be called when sequence_length == 1");
-    LUTB_REQUIRE(dw_variant >= LUTB_DW_AUTO && dw_variant <= LUTB_DW_SORTED, LUTB_ERR_MODE, "unknown dw_variant");
+    LUTB_REQUIRE(dw_variant == LUTB_DW_AUTO || dw_variant == LUTB_DW_ATOMIC || dw_variant == LUTB_DW_SORTED, LUTB_ERR_MODE,
+                 "unknown dw_variant %d", dw_variant);
     // fixed-point sums are order independent already: the sorted variant only applies to fp32 accumulators
     const bool sorted = dw_variant == LUTB_DW_SORTED && !cfg->int_mode;
     if (sorted) {

@@ -418,25 +418,37 @@ __global__ void sparse_input_grad_fixed_kernel(SparseView sp, const float *__res
     }
 }
 
-// Kernel family of the forward and input-gradient passes: the library's choice, or forced by
-// lutb_sparse_kernel_select / the LUTB_SPARSE_KERNELS environment variable (auto, gather, staged).
-static std::atomic<int> g_sparse_kernels{-1};
+// Kernel family of the forward pass and of the input-gradient pass, chosen independently: the library's choice, or
+// forced by lutb_sparse_kernel_select / the LUTB_SPARSE_KERNELS environment variable
+// ("<forward>,<input gradient>" or one word for both; auto, gather, staged).
+static std::atomic<int> g_sparse_kernels[2] = {{-1}, {-1}};
 
-static int sparse_kernels() {
-    int v = g_sparse_kernels.load(std::memory_order_relaxed);
-    if (v >= 0) return v;
-    v = LUTB_SPARSE_AUTO;
-    if (const char *e = getenv("LUTB_SPARSE_KERNELS")) {
-        if (!strcmp(e, "gather")) v = LUTB_SPARSE_GATHER;
-        else if (!strcmp(e, "staged")) v = LUTB_SPARSE_STAGED;
-    }
-    g_sparse_kernels.store(v, std::memory_order_relaxed);
-    return v;
+static int parse_kernels(const char *word, size_t len) {
+    if (len == 6 && !strncmp(word, "gather", 6)) return LUTB_SPARSE_GATHER;
+    if (len == 6 && !strncmp(word, "staged", 6)) return LUTB_SPARSE_STAGED;
+    return LUTB_SPARSE_AUTO;
 }
 
-// 1: run the staged kernels, 0: the gather kernels, < 0: staged was forced but cannot run this layer.
-static int use_staged(const lutb_layer_cfg *cfg, const lutb_sparse_index *sp, int64_t batch, const float *weights) {
-    const int v = sparse_kernels();
+static int sparse_kernels(int pass) {
+    int v = g_sparse_kernels[pass].load(std::memory_order_relaxed);
+    if (v >= 0) return v;
+    int both[2] = {LUTB_SPARSE_AUTO, LUTB_SPARSE_AUTO};
+    if (const char *e = getenv("LUTB_SPARSE_KERNELS")) {
+        const char *comma = strchr(e, ',');
+        both[0] = parse_kernels(e, comma ? (size_t)(comma - e) : strlen(e));
+        both[1] = comma ? parse_kernels(comma + 1, strlen(comma + 1)) : both[0];
+    }
+    for (int i = 0; i < 2; i++) {
+        int expected = -1;
+        g_sparse_kernels[i].compare_exchange_strong(expected, both[i]);
+    }
+    return g_sparse_kernels[pass].load(std::memory_order_relaxed);
+}
+
+// 1: run the staged kernel, 0: the gather kernel, < 0: staged was forced but cannot run this layer.
+// pass 0 = forward, 1 = input gradient.
+static int use_staged(int pass, const lutb_layer_cfg *cfg, const lutb_sparse_index *sp, int64_t batch, const float *weights) {
+    const int v = sparse_kernels(pass);
     if (v == LUTB_SPARSE_GATHER) return 0;
     const bool possible = sparse_staged_possible(cfg, sp, weights);
     if (v == LUTB_SPARSE_STAGED) {
@@ -445,7 +457,7 @@ static int use_staged(const lutb_layer_cfg *cfg, const lutb_sparse_index *sp, in
                      "detector tables of which three fit shared memory");
         return 1;
     }
-    return possible && sparse_staged_preferred(cfg, sp, batch) ? 1 : 0;
+    return possible && sparse_staged_preferred(pass, cfg, sp, batch) ? 1 : 0;
 }
 
 static int validate_sparse(const lutb_sparse_index *sp) {
@@ -472,10 +484,12 @@ static int chunk_grid(int64_t items, unsigned *blocks) {
 
 using namespace lutb;
 
-extern "C" int lutb_sparse_kernel_select(int kernels) {
-    LUTB_REQUIRE(kernels == LUTB_SPARSE_AUTO || kernels == LUTB_SPARSE_GATHER || kernels == LUTB_SPARSE_STAGED, LUTB_ERR_MODE,
-                 "kernels must be LUTB_SPARSE_AUTO, LUTB_SPARSE_GATHER or LUTB_SPARSE_STAGED");
-    g_sparse_kernels.store(kernels);
+extern "C" int lutb_sparse_kernel_select(int forward_kernels, int input_grad_kernels) {
+    for (int k : {forward_kernels, input_grad_kernels})
+        LUTB_REQUIRE(k == LUTB_SPARSE_AUTO || k == LUTB_SPARSE_GATHER || k == LUTB_SPARSE_STAGED, LUTB_ERR_MODE,
+                     "kernels must be LUTB_SPARSE_AUTO, LUTB_SPARSE_GATHER or LUTB_SPARSE_STAGED");
+    g_sparse_kernels[0].store(forward_kernels);
+    g_sparse_kernels[1].store(input_grad_kernels);
     return LUTB_OK;
 }
 
@@ -495,7 +509,7 @@ extern "C" int lutb_nonseq_sparse_forward(const lutb_layer_cfg *cfg, const lutb_
     rc = launch_check_detectors(x, batch, cfg->n_inputs, anchors, cfg->n_detectors, cfg->n_anchors, cfg->cmp_eps, idx,
                                 min_delta, min_k, st);
     if (rc) return rc;
-    const int staged = use_staged(cfg, sp, batch, weights);
+    const int staged = use_staged(0, cfg, sp, batch, weights);
     if (staged < 0) return staged;
     if (staged) return launch_sparse_forward_staged(cfg, sp, batch, weights, idx, y, st);
     SparseView v = make_view(sp);
@@ -555,7 +569,7 @@ extern "C" int lutb_nonseq_sparse_backward(const lutb_layer_cfg *cfg, const lutb
     // three layers of the conv-net step): the reductions of the fused kernel queue in front of its own row gathers.  With
     // in-place SGD the order is also required: every sample must read the weights before any of them is modified.
     // dX == nullptr: the caller does not want the input gradient (first layer of a network).
-    const int staged = dX != nullptr ? use_staged(cfg, sp, batch, weights) : 0;
+    const int staged = dX != nullptr ? use_staged(1, cfg, sp, batch, weights) : 0;
     if (staged < 0) return staged;
     if (staged) {
         rc = launch_sparse_input_grad_staged(cfg, sp, batch, weights, dY, anchors, idx, min_delta, min_k, dX, st);

@@ -7,6 +7,7 @@
 // Reference: calculate_product_lookup_index[_backprop] (lut_runtime_kernels_logic.proto:32-198),
 // fill_outputs_product_cpu_logic (:2148-2264), propagate_backward_product_cpu_logic (:2396-2628),
 // gather_w_gradients_internal_product_cpu_logic (:2630-2744).
+#include "fp32_gemm_sm100.cuh"
 #include "product_hist.cuh"
 #include "product_pairs.cuh"
 
@@ -294,24 +295,30 @@ static int validate_product(const lutb_layer_cfg *cfg, int64_t batch, int S, int
     return LUTB_OK;
 }
 
-// Resolves LUTB_PRODUCT_* into "use the histogram path".
+// Resolves LUTB_PRODUCT_* into "use the histogram path" and "its contractions may run on the tensor cores".
 static int choose_variant(const ProductCall &c, int variant, bool backward, const void *weights, const void *io_rows,
-                          const void *dW, const void *workspace, size_t workspace_bytes, bool &hist) {
+                          const void *dW, const void *workspace, size_t workspace_bytes, bool &hist, bool &allow_tc) {
     hist = false;
-    LUTB_REQUIRE(variant == LUTB_PRODUCT_AUTO || variant == LUTB_PRODUCT_DIRECT || variant == LUTB_PRODUCT_HIST,
+    allow_tc = variant != LUTB_PRODUCT_HIST_FMA;
+    LUTB_REQUIRE(variant == LUTB_PRODUCT_AUTO || variant == LUTB_PRODUCT_DIRECT || variant == LUTB_PRODUCT_HIST ||
+                     variant == LUTB_PRODUCT_HIST_FMA,
                  LUTB_ERR_MODE, "unknown product kernel variant %d", variant);
     if (variant == LUTB_PRODUCT_DIRECT) return LUTB_OK;
     const bool possible = product_hist_supported(c, weights, io_rows, dW);
-    if (variant == LUTB_PRODUCT_HIST) {
+    if (variant == LUTB_PRODUCT_HIST || variant == LUTB_PRODUCT_HIST_FMA) {
         LUTB_REQUIRE(possible, LUTB_ERR_MODE,
                      "the histogram variant needs fp32 accumulators, 4 <= Nc <= 12, O %% 4 == 0, S >= 2 and 16-byte aligned tensors");
         hist = true;
         return LUTB_OK;
     }
+    // The contractions cost rows-per-table multiply-adds per (query, detector, output), the direct kernels one table
+    // row through L2 per key: with the FMA contraction the histogram path pays once a query has about a quarter
+    // (backward) or all (forward) of the table's rows as keys; on the tensor cores the contraction is several times
+    // cheaper and the forward threshold drops to a quarter as well.
     const int64_t rows = (int64_t)1 << c.cfg->n_anchors;
-    const bool long_enough = backward ? 4 * (int64_t)c.S >= rows : (int64_t)c.S >= rows;
+    const bool long_enough = (backward || tc_gemm_available()) ? 4 * (int64_t)c.S >= rows : (int64_t)c.S >= rows;
     hist = possible && long_enough && workspace != nullptr &&
-           workspace_bytes >= product_hist_bytes_per_sequence(c.cfg, c.S, backward) + 256;
+           workspace_bytes >= product_hist_workspace_bytes(c.cfg, 1, c.S, backward);
     return LUTB_OK;
 }
 
@@ -321,7 +328,7 @@ using namespace lutb;
 
 extern "C" size_t lutb_product_workspace(const lutb_layer_cfg *cfg, int64_t batch, int32_t seq_len, int backward) {
     if (!cfg || batch <= 0 || seq_len <= 0 || cfg->n_anchors < 1 || cfg->n_anchors > 16) return 0;
-    return (size_t)batch * product_hist_bytes_per_sequence(cfg, seq_len, backward != 0) + 256;
+    return product_hist_workspace_bytes(cfg, batch, seq_len, backward != 0);
 }
 
 extern "C" int lutb_product_forward(const lutb_layer_cfg *cfg, int64_t batch, int32_t seq_len, const float *weights,
@@ -334,10 +341,10 @@ extern "C" int lutb_product_forward(const lutb_layer_cfg *cfg, int64_t batch, in
     LUTB_REQUIRE(cfg->pos_dim == 0 || pos_embeddings, LUTB_ERR_NULL, "positional embeddings are NULL");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const ProductCall call{cfg, batch, seq_len, n_inputs_1, n_inputs_2, x1, x2, pos_embeddings, anchors};
-    bool hist = false;
-    rc = choose_variant(call, variant, false, weights, y, nullptr, workspace, workspace_bytes, hist);
+    bool hist = false, allow_tc = true;
+    rc = choose_variant(call, variant, false, weights, y, nullptr, workspace, workspace_bytes, hist, allow_tc);
     if (rc) return rc;
-    if (hist) return launch_product_hist_forward(call, weights, y, workspace, workspace_bytes, st);
+    if (hist) return launch_product_hist_forward(call, weights, y, allow_tc, workspace, workspace_bytes, st);
     if (seq_len > 1) {
         const int warps = 8;
         const size_t smem = (pair_stage_floats(seq_len, cfg->n_anchors, cfg->pos_dim) + (size_t)warps * seq_len) * 4;
@@ -374,12 +381,12 @@ extern "C" int lutb_product_backward(const lutb_layer_cfg *cfg, int64_t batch, i
     double lr = cfg->lr_meta;
     if (external_lr >= 0.0) lr *= -(double)(float)external_lr;
     const ProductCall call{cfg, batch, seq_len, n_inputs_1, n_inputs_2, x1, x2, pos_embeddings, anchors};
-    bool hist = false;
-    rc = choose_variant(call, variant, true, weights, dY, dW, workspace, workspace_bytes, hist);
+    bool hist = false, allow_tc = true;
+    rc = choose_variant(call, variant, true, weights, dY, dW, workspace, workspace_bytes, hist, allow_tc);
     if (rc) return rc;
     if (hist)
         return launch_product_hist_backward(call, weights, dY, dX1, dX2, dPE, external_lr >= 0.0 ? weights : dW, lr,
-                                            external_lr >= 0.0, workspace, workspace_bytes, st);
+                                            external_lr >= 0.0, allow_tc, workspace, workspace_bytes, st);
     if (seq_len > 1) {
         if (cfg->int_mode) {
             const int64_t total = batch * seq_len * (int64_t)Nt * seq_len;

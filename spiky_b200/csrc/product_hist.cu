@@ -3,6 +3,7 @@
 // Reference semantics: fill_outputs_product_cpu_logic (lut_runtime_kernels_logic.proto:2148-2264),
 // propagate_backward_product_cpu_logic (:2396-2628), gather_w_gradients_internal_product_cpu_logic (:2630-2744).
 #include "product_hist.cuh"
+#include "fp32_gemm_sm100.cuh"
 #include "product_pairs.cuh"
 
 namespace lutb {
@@ -12,9 +13,12 @@ namespace lutb {
 // rows its j keys select in a per-warp shared-memory histogram and writes it out as T uint16 counters.
 // H layout: [detector][row of the chunk = local sequence * S + j][T].
 // --------------------------------------------------------------------------------------------
+// F32_ROWS: the counters are written as fp32 in the layout [row of the chunk][detector][T], the operand layout of the
+// tensor-core contractions (one plain GEMM over all detectors per pass).
+template <bool F32_ROWS>
 __global__ void __launch_bounds__(512) product_hist_kernel(const float *__restrict__ x1, const float *__restrict__ x2,
                                                           const float *__restrict__ pe,
-                                                          const int32_t *__restrict__ anchors, uint16_t *__restrict__ H,
+                                                          const int32_t *__restrict__ anchors, void *__restrict__ Hout,
                                                           int64_t b0, int64_t chunk_rows, int S, int e1, int e2, int npe,
                                                           int n_detectors, int n_anchors, int sliced, float cmp_eps) {
     extern __shared__ __align__(16) float smem[];
@@ -35,7 +39,17 @@ __global__ void __launch_bounds__(512) product_hist_kernel(const float *__restri
             if (i < j) atomicAdd(hist + eval_pair<false>(st, n_anchors, i, j, cmp_eps, km, dm), 1u);
         }
         __syncwarp();
-        uint16_t *out = H + ((size_t)t * chunk_rows + bl * S + j) * T;
+        if (F32_ROWS) {
+            float *out = static_cast<float *>(Hout) + ((size_t)(bl * S + j) * n_detectors + t) * T;
+            for (int r = lane * 4; r < T; r += 128) {
+                const uint4 c = *reinterpret_cast<const uint4 *>(hist + r);
+                *reinterpret_cast<float4 *>(out + r) = make_float4((float)c.x, (float)c.y, (float)c.z, (float)c.w);
+                *reinterpret_cast<uint4 *>(hist + r) = make_uint4(0u, 0u, 0u, 0u);
+            }
+            __syncwarp();
+            continue;
+        }
+        uint16_t *out = static_cast<uint16_t *>(Hout) + ((size_t)t * chunk_rows + bl * S + j) * T;
         for (int r = lane * 8; r < T; r += 256) {
             const uint4 lo = *reinterpret_cast<const uint4 *>(hist + r);
             const uint4 hi = *reinterpret_cast<const uint4 *>(hist + r + 4);
@@ -67,8 +81,9 @@ __global__ void __launch_bounds__(512) product_route_kernel(const float *__restr
                                                            const int32_t *__restrict__ anchors,
                                                            const float *__restrict__ Q, float *__restrict__ dX1,
                                                            float *__restrict__ dX2, float *__restrict__ dPE, int64_t b0,
-                                                           int64_t chunk_rows, int S, int e1, int e2, int npe,
-                                                           int n_detectors, int n_anchors, int sliced, float cmp_eps) {
+                                                           int64_t q_row_stride, int64_t q_det_stride, int S, int e1,
+                                                           int e2, int npe, int n_detectors, int n_anchors, int sliced,
+                                                           float cmp_eps) {
     extern __shared__ __align__(16) float smem[];
     const int t = blockIdx.x;
     const int64_t bl = blockIdx.y, b = b0 + bl;
@@ -90,7 +105,7 @@ __global__ void __launch_bounds__(512) product_route_kernel(const float *__restr
         __syncthreads();
     }
     for (int j = 1 + warp; j < S; j += nwarps) {
-        const float *qrow = Q + ((size_t)t * chunk_rows + bl * S + j) * T;
+        const float *qrow = Q + (size_t)t * q_det_stride + (size_t)(bl * S + j) * q_row_stride;
         for (int r = lane * 4; r < T; r += 128)
             *reinterpret_cast<float4 *>(q_s + r) = __ldcs(reinterpret_cast<const float4 *>(qrow + r));
         for (int q = 0; q < ends; q++) jacc[q * 32 + lane] = 0.f;
@@ -365,33 +380,68 @@ bool product_hist_supported(const ProductCall &c, const void *weights, const voi
     return stage_bytes(c, T + 64 * cfg->n_anchors) <= (size_t)kMaxSmemPerBlock - 1024;
 }
 
-size_t product_hist_bytes_per_sequence(const lutb_layer_cfg *cfg, int S, bool backward) {
+static size_t bytes_per_sequence(const lutb_layer_cfg *cfg, int S, bool backward, bool tc) {
     const size_t cells = (size_t)cfg->n_detectors * S * ((size_t)1 << cfg->n_anchors);
-    return align256(cells * 2) + (backward ? align256(cells * 4) : 0) + 512;
+    return align256(cells * (tc ? 4 : 2)) + (backward ? align256(cells * 4) : 0) + 512;
+}
+
+// Scratch of the tensor-core GEMMs of one pass over `rows` query rows: their own workspace plus the hi / lo copies of
+// the operands (the tables, and the output gradients in the backward pass); the largest of the calls the pass makes.
+static size_t tc_scratch_bytes(const lutb_layer_cfg *cfg, int64_t rows, bool backward) {
+    const int KT = cfg->n_detectors << cfg->n_anchors, O = cfg->n_outputs;
+    if (!backward) return align256(tc_gemm_workspace((int)rows, O, KT, true));
+    const size_t dw = tc_gemm_workspace(KT, O, (int)rows, true), q = tc_gemm_workspace((int)rows, KT, O, false);
+    return align256(dw > q ? dw : q);
+}
+
+size_t product_hist_workspace_bytes(const lutb_layer_cfg *cfg, int64_t batch, int S, bool backward) {
+    // what lets `batch` sequences through in one pass with either contraction: fp32 counters and operand copies for the
+    // tensor cores, uint16 counters for the FMA kernel
+    const bool tc = tc_gemm_available();
+    return (tc ? tc_scratch_bytes(cfg, batch * S, backward) : 0) + (size_t)batch * bytes_per_sequence(cfg, S, backward, tc) + 256;
 }
 
 struct HistPlan {
     int64_t chunk;  // sequences per pass
-    uint16_t *H;
+    bool tc;        // tensor-core contractions: H is fp32 [row][detector][T], Q fp32 [row][detector][T]
+    void *H;
     float *Q;
+    void *gemm_ws;
+    size_t gemm_ws_bytes;
 };
 
-static int plan(const ProductCall &c, bool backward, void *workspace, size_t bytes, HistPlan &p) {
+static int plan(const ProductCall &c, bool backward, bool allow_tc, void *workspace, size_t bytes, HistPlan &p) {
     LUTB_REQUIRE(workspace != nullptr, LUTB_ERR_WORKSPACE, "product histogram path needs a workspace");
-    const uintptr_t base = (reinterpret_cast<uintptr_t>(workspace) + 255) & ~(uintptr_t)255;
-    const size_t slack = base - reinterpret_cast<uintptr_t>(workspace);
-    const size_t per_seq = product_hist_bytes_per_sequence(c.cfg, c.S, backward);
+    const uintptr_t base0 = (reinterpret_cast<uintptr_t>(workspace) + 255) & ~(uintptr_t)255;
+    const size_t slack = base0 - reinterpret_cast<uintptr_t>(workspace);
+    const size_t T = (size_t)1 << c.cfg->n_anchors;
+    // tensor cores when the library has them, the workspace holds at least one sequence in their layout, the GEMM
+    // extents fit 32-bit sizes and the row counts (at most S - 1) are exact in TF32
+    p.tc = allow_tc && tc_gemm_available() && c.S <= 2048 && (size_t)c.cfg->n_detectors * T < ((size_t)1 << 30) &&
+           bytes >= slack + tc_scratch_bytes(c.cfg, c.S, backward) + bytes_per_sequence(c.cfg, c.S, backward, true);
+    const size_t per_seq = bytes_per_sequence(c.cfg, c.S, backward, p.tc);
     LUTB_REQUIRE(bytes >= slack + per_seq, LUTB_ERR_WORKSPACE,
                  "product histogram path: workspace of %zu bytes is smaller than the %zu bytes one sequence needs", bytes,
                  per_seq + 256);
     p.chunk = (int64_t)((bytes - slack) / per_seq);
     if (p.chunk > c.batch) p.chunk = c.batch;
-    // grid.y of the contraction covers chunk * S / 128 row tiles
-    const int64_t max_rows = (int64_t)65535 * GM;
+    // grid.y of the FMA contraction covers chunk * S / 128 row tiles; the GEMM extents are 32-bit
+    const int64_t max_rows = p.tc ? (int64_t)1 << 30 : (int64_t)65535 * GM;
     if (p.chunk * c.S > max_rows) p.chunk = max_rows / c.S;
-    const size_t cells = (size_t)c.cfg->n_detectors * (size_t)p.chunk * c.S * ((size_t)1 << c.cfg->n_anchors);
-    p.H = reinterpret_cast<uint16_t *>(base);
-    p.Q = backward ? reinterpret_cast<float *>(base + align256(cells * 2)) : nullptr;
+    size_t head = 0;
+    if (p.tc) {
+        // the GEMM scratch grows with the rows of a pass: shrink the pass until both fit
+        while (p.chunk > 1 && slack + tc_scratch_bytes(c.cfg, p.chunk * c.S, backward) + (size_t)p.chunk * per_seq > bytes) p.chunk--;
+        head = tc_scratch_bytes(c.cfg, p.chunk * c.S, backward);
+    }
+    LUTB_REQUIRE(p.chunk >= 1, LUTB_ERR_SHAPE, "product histogram path: sequence too long");
+    const size_t cells = (size_t)c.cfg->n_detectors * (size_t)p.chunk * c.S * T;
+    uintptr_t base = base0;
+    p.gemm_ws = p.tc ? reinterpret_cast<void *>(base) : nullptr;
+    p.gemm_ws_bytes = head;
+    base += head;
+    p.H = reinterpret_cast<void *>(base);
+    p.Q = backward ? reinterpret_cast<float *>(base + align256(cells * (p.tc ? 4 : 2))) : nullptr;
     return LUTB_OK;
 }
 
@@ -400,20 +450,28 @@ static int launch_hist(const ProductCall &c, const HistPlan &p, int64_t b0, int6
     const size_t T = (size_t)1 << cfg->n_anchors;
     const int warps = pair_block_warps(c, T);
     const size_t smem = stage_bytes(c, T, warps);
-    if (smem > 48 * 1024) LUTB_CUDA(cudaFuncSetAttribute(product_hist_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    if (smem > 48 * 1024) {
+        LUTB_CUDA(cudaFuncSetAttribute(product_hist_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        LUTB_CUDA(cudaFuncSetAttribute(product_hist_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    }
     dim3 grid((unsigned)cfg->n_detectors, (unsigned)n);
     KernelScope scope(K_PRODUCT_HIST, stream);
-    product_hist_kernel<<<grid, warps * 32, smem, stream>>>(c.x1, c.x2, c.pe, c.anchors, p.H, b0, n * c.S, c.S, c.e1, c.e2,
-                                                     cfg->pos_dim, cfg->n_detectors, cfg->n_anchors, cfg->sliced_product,
-                                                     cfg->cmp_eps);
+    if (p.tc)
+        product_hist_kernel<true><<<grid, warps * 32, smem, stream>>>(c.x1, c.x2, c.pe, c.anchors, p.H, b0, n * c.S, c.S, c.e1, c.e2,
+                                                               cfg->pos_dim, cfg->n_detectors, cfg->n_anchors,
+                                                               cfg->sliced_product, cfg->cmp_eps);
+    else
+        product_hist_kernel<false><<<grid, warps * 32, smem, stream>>>(c.x1, c.x2, c.pe, c.anchors, p.H, b0, n * c.S, c.S, c.e1, c.e2,
+                                                                cfg->pos_dim, cfg->n_detectors, cfg->n_anchors,
+                                                                cfg->sliced_product, cfg->cmp_eps);
     LUTB_LAUNCH_CHECK();
     return LUTB_OK;
 }
 
-int launch_product_hist_forward(const ProductCall &c, const float *weights, float *y, void *workspace,
+int launch_product_hist_forward(const ProductCall &c, const float *weights, float *y, bool allow_tc, void *workspace,
                                 size_t workspace_bytes, cudaStream_t stream) {
     HistPlan p;
-    int rc = plan(c, false, workspace, workspace_bytes, p);
+    int rc = plan(c, false, allow_tc, workspace, workspace_bytes, p);
     if (rc) return rc;
     const lutb_layer_cfg *cfg = c.cfg;
     const int T = 1 << cfg->n_anchors, O = cfg->n_outputs, Nt = cfg->n_detectors;
@@ -422,6 +480,14 @@ int launch_product_hist_forward(const ProductCall &c, const float *weights, floa
         const int64_t rows = n * c.S;
         rc = launch_hist(c, p, b0, n, stream);
         if (rc) return rc;
+        if (p.tc) {
+            // y[rows, O] += H[rows, Nt*T] . W[Nt*T, O]
+            KernelScope scope(K_PRODUCT_HIST_FORWARD, stream);
+            rc = tc_gemm(TC_A_ROWS_B_ROWS_OF_K, (int)rows, O, Nt * T, static_cast<const float *>(p.H), (int64_t)Nt * T, weights, O,
+                         y + b0 * c.S * O, O, 1.f, 1.f, /*a_exact=*/true, p.gemm_ws, p.gemm_ws_bytes, stream);
+            if (rc) return rc;
+            continue;
+        }
         GemmArgs g{};
         g.A = p.H; g.B = weights; g.C = y + b0 * c.S * O;
         g.M = (int)rows; g.N = O; g.K = Nt * T;
@@ -435,10 +501,10 @@ int launch_product_hist_forward(const ProductCall &c, const float *weights, floa
 }
 
 int launch_product_hist_backward(const ProductCall &c, const float *weights, const float *dY, float *dX1, float *dX2,
-                                 float *dPE, float *target, double lr, bool in_place, void *workspace,
+                                 float *dPE, float *target, double lr, bool in_place, bool allow_tc, void *workspace,
                                  size_t workspace_bytes, cudaStream_t stream) {
     HistPlan p;
-    int rc = plan(c, true, workspace, workspace_bytes, p);
+    int rc = plan(c, true, allow_tc, workspace, workspace_bytes, p);
     if (rc) return rc;
     const lutb_layer_cfg *cfg = c.cfg;
     const int T = 1 << cfg->n_anchors, O = cfg->n_outputs, Nt = cfg->n_detectors;
@@ -456,6 +522,12 @@ int launch_product_hist_backward(const ProductCall &c, const float *weights, con
     // runs as a second sweep over the chunks.
     const bool second_sweep = in_place && p.chunk < c.batch;
     auto table_gradient = [&](int64_t b0, int64_t rows) -> int {
+        if (p.tc) {
+            // target[Nt*T, O] += lr * H^T . dY  (H stored [rows, Nt*T])
+            KernelScope scope(K_PRODUCT_HIST_WEIGHT_GRAD, stream);
+            return tc_gemm(TC_A_COLS_B_ROWS_OF_K, Nt * T, O, (int)rows, static_cast<const float *>(p.H), (int64_t)Nt * T,
+                           dY + b0 * c.S * O, O, target, O, (float)lr, 1.f, /*a_exact=*/true, p.gemm_ws, p.gemm_ws_bytes, stream);
+        }
         GemmArgs g{};
         g.A = p.H; g.B = dY + b0 * c.S * O; g.C = target;
         g.M = T; g.N = O; g.K = (int)rows;
@@ -475,7 +547,13 @@ int launch_product_hist_backward(const ProductCall &c, const float *weights, con
         const int64_t rows = n * c.S;
         rc = launch_hist(c, p, b0, n, stream);
         if (rc) return rc;
-        {
+        if (p.tc) {
+            // Q[rows, Nt*T] = dY[rows, O] . W^T  (W stored [Nt*T, O])
+            KernelScope scope(K_PRODUCT_ROW_DOTS, stream);
+            rc = tc_gemm(TC_A_ROWS_B_ROWS_OF_N, (int)rows, Nt * T, O, dY + b0 * c.S * O, O, weights, O, p.Q, (int64_t)Nt * T, 1.f,
+                         0.f, /*a_exact=*/false, p.gemm_ws, p.gemm_ws_bytes, stream);
+            if (rc) return rc;
+        } else {
             GemmArgs g{};
             g.A = dY + b0 * c.S * O; g.B = weights; g.C = p.Q;
             g.M = (int)rows; g.N = T; g.K = O;
@@ -487,15 +565,16 @@ int launch_product_hist_backward(const ProductCall &c, const float *weights, con
             if (rc) return rc;
         }
         {
+            const int64_t q_row_stride = p.tc ? (int64_t)Nt * T : T, q_det_stride = p.tc ? T : rows * T;
             dim3 grid((unsigned)Nt, (unsigned)n);
             KernelScope scope(K_PRODUCT_ROUTE, stream);
             if (smem_acc)
                 product_route_kernel<true><<<grid, route_warps * 32, route_smem, stream>>>(c.x1, c.x2, c.pe, c.anchors, p.Q, dX1, dX2, dPE, b0,
-                                                                              rows, c.S, c.e1, c.e2, cfg->pos_dim, Nt,
+                                                                              q_row_stride, q_det_stride, c.S, c.e1, c.e2, cfg->pos_dim, Nt,
                                                                               cfg->n_anchors, cfg->sliced_product, cfg->cmp_eps);
             else
                 product_route_kernel<false><<<grid, route_warps * 32, route_smem, stream>>>(c.x1, c.x2, c.pe, c.anchors, p.Q, dX1, dX2, dPE, b0,
-                                                                               rows, c.S, c.e1, c.e2, cfg->pos_dim, Nt,
+                                                                               q_row_stride, q_det_stride, c.S, c.e1, c.e2, cfg->pos_dim, Nt,
                                                                                cfg->n_anchors, cfg->sliced_product, cfg->cmp_eps);
             LUTB_LAUNCH_CHECK();
         }

@@ -8,9 +8,9 @@
 // single-CTA copies of this GPU's own memory), and 16 consumer warps (32 samples each) pick their samples' rows out
 // of shared memory.  HBM sees one sequential read of the tables; the random accesses hit shared memory.
 //
-//   forward          lane L reads the row of sample L and keeps the sample's running sums (one per synapse) over the
-//                    detectors of a chunk in registers; one reduction per (sample, chunk part, target) goes to y
-//                    when the chunk ends
+//   forward          the lanes of a group read one sample's row side by side and keep the running sums of (sample,
+//                    synapse) over the detectors of a chunk in registers; one reduction per (sample, chunk part,
+//                    target) goes to y when the chunk ends
 //   input gradient   lane L reads the selected and the alternative row of sample L, forms
 //                    sum_p dY[target(p)] * (W[row + p] - W[alt + p]) and makes the sample's two dX updates
 //
@@ -34,7 +34,7 @@ constexpr int kTileSamples = kConsumerWarps * 32;
 constexpr int kChunkSlots = 32;     // detector slots per chunk in the linear work order
 constexpr int kMaxStages = 8;
 constexpr int kMinStages = 3;
-constexpr int kFwdTile = 8;         // detectors whose table indices a lane holds at a time (forward)
+constexpr int kFwdTile = 4;         // detectors whose table indices a lane holds at a time (forward)
 constexpr int kDxTile = 2;          // same for the input gradient (it also holds min_k and min_delta)
 constexpr long long kWaitLimitCycles = 2000ll * 1000ll * 1000ll;   // about a second of SM clock
 
@@ -50,6 +50,7 @@ struct StagedArgs {
     int n_outputs, n_detectors, n_inputs, n_anchors;
     int slot_floats;
     int n_stages;
+    int forward;   // 1: forward kernel, 0: input gradient (the two weigh tables differently when splitting the work)
 };
 
 // ------------------------------------------------------------------------------------------ PTX wrappers
@@ -119,10 +120,76 @@ __device__ __forceinline__ Unit decode_unit(const StagedArgs &a, int64_t pos, in
     return u;
 }
 
-__device__ __forceinline__ void block_range(const StagedArgs &a, int64_t *lo, int64_t *hi) {
-    const int64_t per = (a.total_slots + gridDim.x - 1) / gridDim.x;
-    *lo = min(a.total_slots, (int64_t)blockIdx.x * per);
-    *hi = min(a.total_slots, *lo + per);
+// Rows can be read with 64-bit loads when every row starts at an even slot and no hole lies inside a row.
+__device__ __forceinline__ bool rows_vectorisable(const StagedArgs &a, const ChunkStatic &cs) {
+    return (cs.stride & 1) == 0 && hole_offset(cs.P - 1, a.sp) == 0;
+}
+
+// Relative cost of one table of a chunk for the consumers (measured on B200: a fixed part for the hand-over of the
+// slot, then the row reads).  Forward: one row read per sample-group of the warp (32 / 16 / 8 per table).  Input
+// gradient: every lane reads its own two rows; rows that need one 32-bit load per synapse cost about three times the
+// 64-bit ones.
+__device__ __forceinline__ int table_cost(const StagedArgs &a, const ChunkStatic &cs) {
+    if (a.forward) return 8 + (cs.P <= 8 ? 8 : cs.P <= 16 ? 16 : 32);
+    const int nj = cs.P <= 8 ? 8 : cs.P <= 16 ? 16 : cs.P <= 20 ? 20 : cs.P <= 28 ? 28 : 32;
+    return rows_vectorisable(a, cs) ? 8 + nj : 8 + 3 * (cs.P <= 8 ? 8 : cs.P <= 16 ? 16 : 32);
+}
+
+constexpr int kMaxBalanced = 2 * kStagedThreads;   // chunk instances the cost-balanced split can look at
+
+// [lo, hi) of the block in the linear work order.  The tables are split by COST, not by count: the block with the
+// slow tables would otherwise set the kernel's time.  Every block looks at all chunks (a few hundred 32-byte
+// records), sums their cost and finds the two positions where the running cost crosses its share's borders;
+// neighbouring blocks evaluate the same border the same way, so the ranges tile the work exactly.  Layers with more
+// chunk instances than kMaxBalanced fall back to an even split by count.
+__device__ void block_range(const StagedArgs &a, int64_t *lo, int64_t *hi) {
+    __shared__ int32_t s_cost[kMaxBalanced];
+    __shared__ long long s_border[2];
+    const int64_t n_items = a.total_slots / kChunkSlots;   // chunk instances (chunks x sample tiles)
+    if (n_items > kMaxBalanced) {
+        const int64_t per = (a.total_slots + gridDim.x - 1) / gridDim.x;
+        *lo = min(a.total_slots, (int64_t)blockIdx.x * per);
+        *hi = min(a.total_slots, *lo + per);
+        return;
+    }
+    for (int64_t i = threadIdx.x; i < n_items; i += blockDim.x) {
+        const ChunkStatic cs = load_chunk(a.sp, i % a.sp.n_chunks);
+        s_cost[i] = cs.ndet * table_cost(a, cs);
+    }
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        const int lane = threadIdx.x;
+        long long total = 0;
+        for (int64_t i = lane; i < n_items; i += 32) total += s_cost[i];
+#pragma unroll
+        for (int m = 16; m >= 1; m >>= 1) total += __shfl_xor_sync(0xffffffffu, total, m);
+        const long long t_lo = total * blockIdx.x / gridDim.x, t_hi = total * (blockIdx.x + 1) / gridDim.x;
+        if (lane == 0) { s_border[0] = a.total_slots; s_border[1] = a.total_slots; }
+        __syncwarp();
+        long long run = 0;   // cost of all items before this round
+        for (int64_t base = 0; base < n_items; base += 32) {
+            const int64_t i = base + lane;
+            const long long c = i < n_items ? s_cost[i] : 0;
+            long long incl = c;
+#pragma unroll
+            for (int m = 1; m < 32; m <<= 1) {
+                const long long up = __shfl_up_sync(0xffffffffu, incl, m);
+                if (lane >= m) incl += up;
+            }
+            const long long excl = run + incl - c;
+            if (c > 0) {
+                const ChunkStatic cs = load_chunk(a.sp, i % a.sp.n_chunks);
+                const int w = (int)(c / cs.ndet);
+                // the border lies inside this item: so many whole tables of it belong to the earlier block
+                if (t_lo >= excl && t_lo < excl + c) s_border[0] = i * kChunkSlots + (t_lo - excl) / w;
+                if (t_hi >= excl && t_hi < excl + c) s_border[1] = i * kChunkSlots + (t_hi - excl) / w;
+            }
+            run += __shfl_sync(0xffffffffu, incl, 31);
+        }
+    }
+    __syncthreads();
+    *lo = s_border[0];
+    *hi = s_border[1];
 }
 
 struct RingPos {
@@ -144,9 +211,7 @@ __device__ __forceinline__ void report_wait_error(const Ring &ring) {
 }
 
 // Producer warp: streams the tables of the block's range into the ring.
-__device__ void producer_loop(const StagedArgs &a, const Ring &ring, int lane) {
-    int64_t lo, hi;
-    block_range(a, &lo, &hi);
+__device__ void producer_loop(const StagedArgs &a, const Ring &ring, int64_t lo, int64_t hi, int lane) {
     RingPos rp{0u, 0u};
     uint32_t issued = 0;
     bool ok = true;
@@ -272,23 +337,30 @@ __device__ __forceinline__ float dot_row_difference(const float *slot, uint32_t 
     }
 }
 
-template <int NJ, bool VEC>
+// Forward, lane layout inside a consumer warp: LG lanes per sample (LG = 8, 16 or 32 >= synapses per row), 32 / LG
+// samples side by side; lane (h, j) works on synapse j of the samples h * LG + i, i = 0 .. LG - 1, of the warp's 32
+// samples, so a row is read by neighbouring lanes as one contiguous piece of shared memory (no bank conflicts inside
+// a row) and the sums of a sample leave the warp as one reduction over neighbouring output cells.  Lane L also holds
+// the table indices of sample L (its "own" sample), which the others fetch by shuffle.
+template <int LG>
 __device__ __forceinline__ bool forward_unit(const StagedArgs &a, const Unit &u, const Unit &nx, bool has_next,
                                              const Ring &ring, RingPos &rp, const int32_t *__restrict__ idx,
                                              int32_t (&raw)[kFwdTile], int warp, int lane, float *__restrict__ y) {
+    const int h = lane / LG, j = lane - h * LG;
+    const bool valid = j < u.cs.P;
     const int64_t bw = u.b0 + warp * 32;
     const bool warp_active = bw < a.batch;
-    const int64_t own_b = bw + lane;
-    float acc[NJ];
+    const int q = j + hole_offset(j, a.sp);
+    float acc[LG];
 #pragma unroll
-    for (int j = 0; j < NJ; j++) acc[j] = 0.f;
+    for (int i = 0; i < LG; i++) acc[i] = 0.f;
     for (int t0 = u.d0; t0 < u.d1; t0 += kFwdTile) {
         uint32_t ro[kFwdTile];
 #pragma unroll
         for (int k = 0; k < kFwdTile; k++) ro[k] = (uint32_t)raw[k] * (uint32_t)u.cs.stride;
         // the indices of the next tile (of this unit or of the next one) travel while this tile is worked on
         if (t0 + kFwdTile < u.d1)
-            load_tile_i32<kFwdTile>(idx, own_b, a.batch, a.n_detectors, u.cs.det0 + t0 + kFwdTile,
+            load_tile_i32<kFwdTile>(idx, bw + lane, a.batch, a.n_detectors, u.cs.det0 + t0 + kFwdTile,
                                     min(kFwdTile, u.d1 - t0 - kFwdTile), raw);
         else if (has_next)
             load_tile_i32<kFwdTile>(idx, nx.b0 + warp * 32 + lane, a.batch, a.n_detectors, nx.cs.det0 + nx.d0,
@@ -297,26 +369,39 @@ __device__ __forceinline__ bool forward_unit(const StagedArgs &a, const Unit &u,
         for (int dd = 0; dd < kFwdTile; dd++) {
             if (t0 + dd < u.d1) {
                 if (!mbar_wait(ring.full0 + 8 * rp.slot, rp.phase) || *ring.abort_flag) return false;
-                if (warp_active) add_row<0, NJ, VEC>(ring.base + (size_t)rp.slot * a.slot_floats, ro[dd], a.sp, acc);
+                if (warp_active) {
+                    const float *tab = ring.base + (size_t)rp.slot * a.slot_floats + q;
+                    // in batches of 8 rows: all row offsets first, then all row reads, then the additions, so that
+                    // the shuffles and the shared-memory reads of a batch are in flight together instead of forming
+                    // one dependent chain per row
+                    constexpr int BATCH = 8;
+#pragma unroll
+                    for (int i0 = 0; i0 < LG; i0 += BATCH) {
+                        uint32_t off[BATCH];
+                        float val[BATCH];
+#pragma unroll
+                        for (int i = 0; i < BATCH; i++) off[i] = __shfl_sync(0xffffffffu, ro[dd], h * LG + i0 + i);
+#pragma unroll
+                        for (int i = 0; i < BATCH; i++) val[i] = valid ? tab[off[i]] : 0.f;
+#pragma unroll
+                        for (int i = 0; i < BATCH; i++) acc[i0 + i] += val[i];
+                    }
+                }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(ring.empty0 + 8 * rp.slot);
                 rp.advance(a.n_stages);
             }
         }
     }
-    if (own_b < a.batch) {
-        float *yb = y + own_b * a.n_outputs;
-        const int32_t *tg = a.sp.syn_target + u.cs.toff;
+    if (warp_active && valid) {
+        const int target = __ldg(a.sp.syn_target + u.cs.toff + j);
 #pragma unroll
-        for (int j = 0; j < NJ; j++)
-            if (j < u.cs.P) atomicAdd(yb + __ldg(tg + j), acc[j]);
+        for (int i = 0; i < LG; i++) {
+            const int64_t b = bw + h * LG + i;
+            if (b < a.batch) atomicAdd(y + b * a.n_outputs + target, acc[i]);
+        }
     }
     return true;
-}
-
-// Rows can be read with 64-bit loads when every row starts at an even slot and no hole lies inside a row.
-__device__ __forceinline__ bool rows_vectorisable(const StagedArgs &a, const ChunkStatic &cs) {
-    return (cs.stride & 1) == 0 && hole_offset(cs.P - 1, a.sp) == 0;
 }
 
 // Shared memory: the ring, then the barriers (two per stage) and the abort flag.
@@ -346,12 +431,12 @@ __global__ void __launch_bounds__(kStagedThreads, 1) sparse_forward_staged_kerne
     extern __shared__ __align__(128) unsigned char smem[];
     const Ring ring = setup_ring(a, smem);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    int64_t lo, hi;
+    block_range(a, &lo, &hi);   // all threads: it synchronises the block
     if (warp == kConsumerWarps) {
-        producer_loop(a, ring, lane);
+        producer_loop(a, ring, lo, hi, lane);
         return;
     }
-    int64_t lo, hi;
-    block_range(a, &lo, &hi);
     Unit cur, nxt;
     bool has_cur = next_unit(a, lo, hi, cur);
     RingPos rp{0u, 0u};
@@ -362,18 +447,10 @@ __global__ void __launch_bounds__(kStagedThreads, 1) sparse_forward_staged_kerne
     while (has_cur) {
         const bool has_next = next_unit(a, cur.next_pos, hi, nxt);
         bool ok;
-#define LUTB_FWD_UNIT(NJV, VECV) forward_unit<NJV, VECV>(a, cur, nxt, has_next, ring, rp, idx, raw, warp, lane, y)
-        if (rows_vectorisable(a, cur.cs)) {
-            if (cur.cs.P <= 8) ok = LUTB_FWD_UNIT(8, true);
-            else if (cur.cs.P <= 16) ok = LUTB_FWD_UNIT(16, true);
-            else if (cur.cs.P <= 20) ok = LUTB_FWD_UNIT(20, true);
-            else if (cur.cs.P <= 28) ok = LUTB_FWD_UNIT(28, true);
-            else ok = LUTB_FWD_UNIT(32, true);
-        } else {
-            if (cur.cs.P <= 8) ok = LUTB_FWD_UNIT(8, false);
-            else if (cur.cs.P <= 16) ok = LUTB_FWD_UNIT(16, false);
-            else ok = LUTB_FWD_UNIT(32, false);
-        }
+#define LUTB_FWD_UNIT(LGV) forward_unit<LGV>(a, cur, nxt, has_next, ring, rp, idx, raw, warp, lane, y)
+        if (cur.cs.P <= 8) ok = LUTB_FWD_UNIT(8);
+        else if (cur.cs.P <= 16) ok = LUTB_FWD_UNIT(16);
+        else ok = LUTB_FWD_UNIT(32);
 #undef LUTB_FWD_UNIT
         if (!ok) {
             if (lane == 0) report_wait_error(ring);
@@ -460,12 +537,12 @@ __global__ void __launch_bounds__(kStagedThreads, 1) sparse_input_grad_staged_ke
     extern __shared__ __align__(128) unsigned char smem[];
     const Ring ring = setup_ring(a, smem);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    int64_t lo, hi;
+    block_range(a, &lo, &hi);   // all threads: it synchronises the block
     if (warp == kConsumerWarps) {
-        producer_loop(a, ring, lane);
+        producer_loop(a, ring, lo, hi, lane);
         return;
     }
-    int64_t lo, hi;
-    block_range(a, &lo, &hi);
     Unit cur, nxt;
     bool has_cur = next_unit(a, lo, hi, cur);
     RingPos rp{0u, 0u};
@@ -507,7 +584,8 @@ __global__ void __launch_bounds__(kStagedThreads, 1) sparse_input_grad_staged_ke
 static size_t slot_bytes_of(const lutb_sparse_index *sp) { return (((size_t)sp->max_table_slots * 4) + 127) & ~(size_t)127; }
 
 static int stages_of(const lutb_sparse_index *sp) {
-    const size_t tail = 16 * kMaxStages + 128;
+    // barriers + abort flag behind the ring, and the kernels' static shared memory (cost table of block_range)
+    const size_t tail = 16 * kMaxStages + 128 + (kMaxBalanced * sizeof(int32_t) + 256);
     const size_t slot = slot_bytes_of(sp);
     if (slot == 0 || slot + tail > (size_t)kMaxSmemPerBlock) return 0;
     const size_t n = ((size_t)kMaxSmemPerBlock - tail) / slot;
@@ -521,15 +599,21 @@ bool sparse_staged_possible(const lutb_layer_cfg *cfg, const lutb_sparse_index *
     return stages_of(sp) >= kMinStages;
 }
 
-bool sparse_staged_preferred(const lutb_layer_cfg *cfg, const lutb_sparse_index *sp, int64_t batch) {
+bool sparse_staged_preferred(int pass, const lutb_layer_cfg *cfg, const lutb_sparse_index *sp, int64_t batch) {
     // whole tables are streamed whatever the batch: worth it once the batch selects most rows of a table anyway,
-    // and when the layer has enough detectors to give every SM a range
+    // and when the layer has enough detectors to give every SM a range.  Input gradient: the staged kernel measured
+    // slower than the gather kernel on B200 (both end up bound by the load/store unit: the two scattered dX
+    // reductions per (sample, detector) cost the same in either, and 32 lanes reading 32 different rows of a table
+    // in shared memory collide on its banks about as often as they would miss in L1), so it is never the
+    // library's choice.
+    if (pass != 0) return false;
     const int64_t rows = (int64_t)1 << cfg->n_anchors;
     return 2 * batch >= rows && cfg->n_detectors >= 4 * device_info().sm_count;
 }
 
 static int fill_args(const lutb_layer_cfg *cfg, const lutb_sparse_index *sp, int64_t batch, const float *weights,
-                     StagedArgs *a, unsigned *grid, size_t *smem) {
+                     bool forward, StagedArgs *a, unsigned *grid, size_t *smem) {
+    a->forward = forward ? 1 : 0;
     a->sp = make_view(sp);
     a->W = weights;
     a->n_weights = sp->n_weights;
@@ -562,7 +646,7 @@ int launch_sparse_forward_staged(const lutb_layer_cfg *cfg, const lutb_sparse_in
     StagedArgs a;
     unsigned grid;
     size_t smem;
-    int rc = fill_args(cfg, sp, batch, weights, &a, &grid, &smem);
+    int rc = fill_args(cfg, sp, batch, weights, true, &a, &grid, &smem);
     if (rc) return rc;
     rc = allow_smem(sparse_forward_staged_kernel, smem);
     if (rc) return rc;
@@ -578,7 +662,7 @@ int launch_sparse_input_grad_staged(const lutb_layer_cfg *cfg, const lutb_sparse
     StagedArgs a;
     unsigned grid;
     size_t smem;
-    int rc = fill_args(cfg, sp, batch, weights, &a, &grid, &smem);
+    int rc = fill_args(cfg, sp, batch, weights, false, &a, &grid, &smem);
     if (rc) return rc;
     rc = allow_smem(sparse_input_grad_staged_kernel, smem);
     if (rc) return rc;

@@ -12,8 +12,8 @@ bool sparse_staged_possible(const lutb_layer_cfg *cfg, const lutb_sparse_index *
 
 // The library's choice between the gather kernels (one warp per (chunk, few samples), rows fetched through L2) and
 // the staged kernels (whole tables streamed through shared memory once per 512 samples): staged pays when most rows
-// of a table are selected by some sample of the batch anyway.
-bool sparse_staged_preferred(const lutb_layer_cfg *cfg, const lutb_sparse_index *sp, int64_t batch);
+// of a table are selected by some sample of the batch anyway.  pass 0 = forward, 1 = input gradient.
+bool sparse_staged_preferred(int pass, const lutb_layer_cfg *cfg, const lutb_sparse_index *sp, int64_t batch);
 
 // y[b, target(p)] += sum over detectors of W[row(t, idx[b, t]) + p]      (fill_outputs_non_seq_sparse)
 int launch_sparse_forward_staged(const lutb_layer_cfg *cfg, const lutb_sparse_index *sp, int64_t batch,

@@ -280,6 +280,7 @@ class ShardedTableUpdate:
         self._pending = []
         self._side = None
         self._plans = {}
+        self._bufs = {}
         for layer in self.layers:
             if not isinstance(layer, LUTLayerBasic) or layer._is_fully_connected or layer._sequence_length != 1:
                 raise ValueError("ShardedTableUpdate handles non-sequence layers with sparse lookup connectivity")
@@ -320,9 +321,9 @@ class ShardedTableUpdate:
             self._side.wait_stream(main)  # input gradient of this layer (it reads the tables) and dY are ordered before
         ctx = torch.cuda.stream(self._side) if on_gpu else _NullContext()
         with ctx:
-            small = idx.to(plan["idx_dtype"])
-            idx_all = torch.empty(W * small.numel(), dtype=small.dtype, device=small.device)
-            dY_all = torch.empty(W * dY.numel(), dtype=dY.dtype, device=dY.device)
+            buf = self._buffers(layer, plan, idx, dY)
+            small, idx_all, dY_all = buf["small"], buf["idx_all"], buf["dY_all"]
+            small.copy_(idx)   # narrowing copy: the indices travel as uint8 / int16 when the table allows it
             w1 = dist.all_gather_into_tensor(idx_all, small, group=G, async_op=True)
             w2 = dist.all_gather_into_tensor(dY_all, dY.contiguous(), group=G, async_op=True)
             w1.wait()  # orders the update below (same stream) after the collectives; the host does not block
@@ -339,14 +340,37 @@ class ShardedTableUpdate:
                 self._pending.extend(_all_gather_uneven(views, self.rank, G))
             else:
                 longest = max(v.numel() for v in views)
-                send = torch.empty(longest, dtype=w.dtype, device=w.device)
-                send[:views[self.rank].numel()] = views[self.rank]
-                recv = torch.empty(W * longest, dtype=w.dtype, device=w.device)
+                lo = plan["wcuts"][self.rank]
+                if lo + longest <= w.numel():
+                    # the share is sent in place, padded with whatever follows it in the table (the receivers keep
+                    # only the share's own length)
+                    send = w[lo:lo + longest]
+                else:
+                    send = buf["send"]
+                    send[:views[self.rank].numel()] = views[self.rank]
+                recv = buf["recv"]
                 work = dist.all_gather_into_tensor(recv, send, group=G, async_op=True)
                 work.wait()  # orders the copies below (same stream) after the collective; the host does not block
                 for r, v in enumerate(views):
                     if r != self.rank and v.numel():
                         v.copy_(recv[r * longest:r * longest + v.numel()])
+
+    def _buffers(self, layer, plan, idx, dY):
+        """Exchange buffers of a layer, allocated once per batch size (on the stream that uses them)."""
+        key = (id(layer), idx.numel(), dY.numel())
+        buf = self._bufs.get(key)
+        if buf is None:
+            W = self.world
+            w = layer._weights
+            longest = max(plan["wcuts"][r + 1] - plan["wcuts"][r] for r in range(W))
+            buf = dict(small=torch.empty(idx.numel(), dtype=plan["idx_dtype"], device=idx.device),
+                       idx_all=torch.empty(W * idx.numel(), dtype=plan["idx_dtype"], device=idx.device),
+                       dY_all=torch.empty(W * dY.numel(), dtype=dY.dtype, device=dY.device))
+            if self.weight_gather != "uneven":
+                buf["send"] = torch.empty(longest, dtype=w.dtype, device=w.device)
+                buf["recv"] = torch.empty(W * longest, dtype=w.dtype, device=w.device)
+            self._bufs[key] = buf
+        return buf
 
     def wait(self):
         """Makes the current stream (and, for CPU process groups, the host) wait for every outstanding exchange."""

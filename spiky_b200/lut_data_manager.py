@@ -481,16 +481,18 @@ class _LUTDataManager:
     # scratch of the histogram variant of the product kernels: one buffer per device, shared by all layers
     # (a call only uses it between its own launches on the current stream)
     _product_scratch = {}
-    product_scratch_limit = 4 << 30
+    product_scratch_limit = 16 << 30
 
     def _product_workspace(self, cfg, B, S, backward, variant, device):
         """(tensor or None, bytes) handed to the product entry points; None lets AUTO fall back to DIRECT."""
         if variant == _native.PRODUCT_DIRECT or self._INT_MODE or S < 2:
             return None, 0
         rows = 1 << self._n_anchors
-        if variant == _native.PRODUCT_AUTO and not ((4 * S >= rows) if backward else (S >= rows)):
-            return None, 0
         L = _native.lib()
+        # the library's own rule for AUTO (include/spiky_b200.h): no workspace is needed when it will pick DIRECT
+        quarter = backward or bool(L.lutb_fp32_gemm_available())
+        if variant == _native.PRODUCT_AUTO and not ((4 * S >= rows) if quarter else (S >= rows)):
+            return None, 0
         one = L.lutb_product_workspace(ctypes.byref(cfg), 1, S, int(backward))
         want = min(L.lutb_product_workspace(ctypes.byref(cfg), B, S, int(backward)),
                    max(one, _LUTDataManager.product_scratch_limit))

@@ -245,7 +245,7 @@ def fp64_product_sums(cfg, x, anchors, W, pe3, dY):
     return y, dW.reshape(-1)
 
 
-@pytest.mark.parametrize("variant", [1, 2], ids=["direct", "histogram"])
+@pytest.mark.parametrize("variant", [1, 2, 3], ids=["direct", "histogram", "histogram_fma"])
 def test_large_transformer_attention_head_shape(variant):
     """Context 1024, 1024-row tables, 1024 outputs, the 16 detectors of one head, one sequence."""
     from cases import sequence_inputs

@@ -61,7 +61,7 @@ def test_sparse_layer_with_full_connectivity_equals_fully_connected():
     golden_util.assert_close(dws[slot.reshape(-1)], dwd[fc_cell.reshape(-1)], REL, "dW")
 
 
-@pytest.mark.parametrize("variant", [1, 2])
+@pytest.mark.parametrize("variant", [1, 2, 3])
 def test_product_layer_equals_plain_layer_on_materialised_pairs(variant):
     from spiky_b200.lut_layer import LUTLayer, SynapseMeta
 

@@ -110,7 +110,8 @@ ORACLE_CASES["hist_big_table"] = dict(seed=722, B=1, S=260, E=16, Nt=2, Nc=10, N
 ORACLE_CASES["hist_odd_shapes"] = dict(seed=723, B=3, S=67, E=7, Nt=37, Nc=4, Npe=1, O=20, n_virtual=15)
 ORACLE_CASES["internal_sgd"] = dict(seed=706, B=3, S=24, E=16, Nt=5, Nc=5, Npe=3, O=12, policy="internal", ext_lr=0.25,
                                     lr_meta=0.5, n_virtual=35)
-VARIANT_CASES = [(n, v) for n in sorted(ORACLE_CASES) for v in (1, 2) if v == 1 or hist_capable(ORACLE_CASES[n])]
+# 1 direct gathers, 2 histogram + contraction (tensor cores when the library has them), 3 histogram + fp32 FMA contraction
+VARIANT_CASES = [(n, v) for n in sorted(ORACLE_CASES) for v in (1, 2, 3) if v == 1 or hist_capable(ORACLE_CASES[n])]
 
 
 @pytest.mark.parametrize("name,variant", VARIANT_CASES)

@@ -90,9 +90,10 @@ def test_staged_and_gather_kernels_match_oracle(shape):
     layer, x, dY, nc = build(shape)
     ref = oracle_layer(layer, x, dY, nc)
     assert layer._lut_dm._sparse.tables_aligned16 == 1
-    for kernels, name in ((_native.SPARSE_STAGED, "staged"), (_native.SPARSE_GATHER, "gather")):
-        _native.sparse_kernel_select(kernels)
-        check(run_layer(layer, x, dY), ref, f"{shape}/{name}")
+    for fwd, dx in ((_native.SPARSE_STAGED, _native.SPARSE_STAGED), (_native.SPARSE_GATHER, _native.SPARSE_GATHER),
+                    (_native.SPARSE_STAGED, _native.SPARSE_GATHER)):
+        _native.sparse_kernel_select(fwd, dx)
+        check(run_layer(layer, x, dY), ref, f"{shape}/forward {fwd}, input gradient {dx}")
     assert _native.device_wait_errors() == 0
 
 
@@ -135,3 +136,5 @@ def test_kernel_select_rejects_unknown_values():
 
     with pytest.raises(ValueError):
         _native.sparse_kernel_select(7)
+    with pytest.raises(ValueError):
+        _native.sparse_kernel_select(_native.SPARSE_AUTO, -1)
