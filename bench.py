@@ -1144,7 +1144,9 @@ def run_ours(args):
     e2e_region(2)
     ms_e2e = e2e_region(args.steps)
 
-    # ---- data-parallel evidence: what the exchange costs, how fast the same payload moves alone, replicas identical
+    # ---- data-parallel evidence: replicas identical (checked BEFORE the run without exchange below, which lets
+    # them drift on purpose), what the exchange costs, how fast the same payload moves alone
+    replica = _replica_check([p for l in getattr(wl, "layers", []) for p in [l._weights]] or wl.trainable_parameters(), world)
     comm = None
     if world > 1 and getattr(wl, "sharded", False):
         # payload of the sharded update: every rank receives the other ranks' (index, output gradient) pairs and
@@ -1187,7 +1189,6 @@ def run_ours(args):
             iso.append(a.elapsed_time(b))
         del bufs
         comm = {"ms_local": ms_local, "ms_isolated": min(iso[1:]), "payload": payload}
-    replica = _replica_check([p for l in getattr(wl, "layers", []) for p in [l._weights]] or wl.trainable_parameters(), world)
 
     variants = None
     if world == 1 and args.workload == DEFAULT_WORKLOAD and not args.no_secondary:

@@ -6,11 +6,11 @@
 // GPU's own memory -, tcgen05.mma accumulates in fp32 in tensor memory, the epilogue reads the accumulators back with
 // tcgen05.ld and applies alpha / beta):
 //
-//   split TF32 (default)  every fp32 operand x is written once as hi = x with the low 13 mantissa bits cleared and
-//                         lo = x - hi (exact), and the product is formed as hi.hi + hi.lo + lo.hi by up to three TF32
-//                         GEMMs that accumulate into C; an operand that holds integers below 2048 (row counts) is
-//                         exact in TF32 and needs no split, which leaves two GEMMs.  The dropped lo.lo term and the
-//                         truncation of lo to TF32 are below 2^-21 relative.
+//   split TF32 (default)  every fp32 operand x is written once as hi = x rounded to TF32 and lo = x - hi (exact)
+//                         rounded to TF32, and the product is formed as hi.hi + hi.lo + lo.hi; concatenated copies
+//                         make that ONE TF32 GEMM wherever the layouts allow.  An operand that holds integers below
+//                         2048 (row counts) is exact in TF32 and needs no split.  The dropped lo.lo term and the
+//                         rounding of lo are each below 2^-22 relative.
 //   fast fp32             one GEMM whose mainloop splits the operands into three BF16 terms on the fly (CUTLASS'
 //                         "FastF32" schedule); simpler, no scratch, but bound by the conversion work: 80-90 TFLOP/s on
 //                         the contraction shapes against 2-3 times that for the split TF32 route.
@@ -23,7 +23,7 @@
 // built without a CUTLASS header tree: the callers keep their fp32 FMA contractions
 namespace lutb {
 bool tc_gemm_available() { return false; }
-size_t tc_gemm_workspace(int, int, int, bool) { return 0; }
+size_t tc_gemm_workspace(TcGemmKind, int, int, int, bool) { return 0; }
 size_t tc_gemm_fast_workspace(int, int, int) { return 0; }
 int tc_gemm(TcGemmKind, int, int, int, const float *, int64_t, const float *, int64_t, float *, int64_t, float, float, bool,
             void *, size_t, cudaStream_t) {
@@ -141,51 +141,104 @@ using Tf32TT = Tf32Gemm<cutlass::layout::ColumnMajor, cutlass::layout::RowMajor>
 
 bool tc_gemm_available() { return true; }
 
-// hi = x with the low 13 mantissa bits cleared (exactly representable in TF32), lo = x - hi (exact in fp32)
-__global__ void split_tf32_kernel(const float *__restrict__ x, int64_t rows, int64_t cols, int64_t ld, float *__restrict__ hi,
-                                  float *__restrict__ lo) {
+// Nearest value with a 10-bit mantissa (what a TF32 operand keeps; the MMA itself would truncate).
+__device__ __forceinline__ float round_tf32(float x) {
+    return __uint_as_float((__float_as_uint(x) + 0x00001000u) & 0xFFFFE000u);
+}
+
+// hi = x rounded to TF32 (|x - hi| <= 2^-11 |x|), lo = x - hi (exact in fp32) rounded to TF32 (error <= 2^-22 |x|).
+// The two parts of a [rows x cols] matrix are written into a [rows x parts * cols] matrix, part p at columns
+// [p * cols, (p + 1) * cols); `pattern` says which part goes where (bit p set: lo, clear: hi).  Concatenating along
+// the contraction index turns hi.hi + hi.lo + lo.hi into ONE GEMM with three times the depth (A parts hi|hi|lo, B
+// parts hi|lo|hi); concatenating B along its free index turns A.hi + A.lo into one GEMM with twice the width.
+__global__ void split_tf32_kernel(const float *__restrict__ x, int64_t rows, int64_t cols, int64_t ld, float *__restrict__ out,
+                                  int parts, unsigned pattern) {
     const int64_t n4 = rows * (cols / 4);
+    const int64_t ldo = (int64_t)parts * cols;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (int64_t)gridDim.x * blockDim.x) {
         const int64_t r = i / (cols / 4), c = (i - r * (cols / 4)) * 4;
         const float4 v = *reinterpret_cast<const float4 *>(x + r * ld + c);
         float4 h, l;
-        h.x = __uint_as_float(__float_as_uint(v.x) & 0xFFFFE000u); l.x = v.x - h.x;
-        h.y = __uint_as_float(__float_as_uint(v.y) & 0xFFFFE000u); l.y = v.y - h.y;
-        h.z = __uint_as_float(__float_as_uint(v.z) & 0xFFFFE000u); l.z = v.z - h.z;
-        h.w = __uint_as_float(__float_as_uint(v.w) & 0xFFFFE000u); l.w = v.w - h.w;
-        *reinterpret_cast<float4 *>(hi + r * cols + c) = h;
-        *reinterpret_cast<float4 *>(lo + r * cols + c) = l;
+        h.x = round_tf32(v.x); l.x = round_tf32(v.x - h.x);
+        h.y = round_tf32(v.y); l.y = round_tf32(v.y - h.y);
+        h.z = round_tf32(v.z); l.z = round_tf32(v.z - h.z);
+        h.w = round_tf32(v.w); l.w = round_tf32(v.w - h.w);
+        for (int p = 0; p < parts; p++)
+            *reinterpret_cast<float4 *>(out + r * ldo + p * cols + c) = ((pattern >> p) & 1u) ? l : h;
     }
 }
 
-static int split(const float *x, int64_t rows, int64_t cols, int64_t ld, float *hi, float *lo, cudaStream_t stream) {
+static int split(const float *x, int64_t rows, int64_t cols, int64_t ld, float *out, int parts, unsigned pattern,
+                 cudaStream_t stream) {
     const int64_t n4 = rows * (cols / 4);
     int64_t blocks = (n4 + 255) / 256;
     const int64_t cap = (int64_t)device_info().sm_count * 16;
     if (blocks > cap) blocks = cap;
-    split_tf32_kernel<<<(unsigned)blocks, 256, 0, stream>>>(x, rows, cols, ld, hi, lo);
+    split_tf32_kernel<<<(unsigned)blocks, 256, 0, stream>>>(x, rows, cols, ld, out, parts, pattern);
     LUTB_LAUNCH_CHECK();
     return LUTB_OK;
 }
 
-// stored extents of the operands of a kind: A is [ar x ac], B is [br x bc] (row-major, contiguous in the second)
-static void stored_extents(TcGemmKind kind, int M, int N, int K, int64_t *ar, int64_t *ac, int64_t *br, int64_t *bc) {
-    *ar = kind == TC_A_COLS_B_ROWS_OF_K ? K : M;
-    *ac = kind == TC_A_COLS_B_ROWS_OF_K ? M : K;
-    *br = kind == TC_A_ROWS_B_ROWS_OF_N ? N : K;
-    *bc = kind == TC_A_ROWS_B_ROWS_OF_N ? K : N;
+// C = alpha * (P[:, 0:N] + P[:, N:2N]) + beta * C  (lo part first into the sum, as the smaller one)
+__global__ void combine_halves_kernel(const float *__restrict__ P, float *__restrict__ C, int64_t M, int64_t N, int64_t ldc,
+                                      float alpha, float beta) {
+    const int64_t n4 = M * (N / 4);
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i / (N / 4), c = (i - r * (N / 4)) * 4;
+        const float4 hi = *reinterpret_cast<const float4 *>(P + r * 2 * N + c);
+        const float4 lo = *reinterpret_cast<const float4 *>(P + r * 2 * N + N + c);
+        float4 *dst = reinterpret_cast<float4 *>(C + r * ldc + c);
+        float4 v = make_float4(alpha * (lo.x + hi.x), alpha * (lo.y + hi.y), alpha * (lo.z + hi.z), alpha * (lo.w + hi.w));
+        if (beta != 0.f) {
+            const float4 o = *dst;
+            v.x += beta * o.x; v.y += beta * o.y; v.z += beta * o.z; v.w += beta * o.w;
+        }
+        *dst = v;
+    }
 }
 
 static size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
 
-size_t tc_gemm_workspace(int M, int N, int K, bool a_exact) {
-    size_t w = workspace_of<Tf32TN>(M, N, K);
-    const size_t w2 = workspace_of<Tf32NN>(M, N, K), w3 = workspace_of<Tf32TT>(M, N, K);
-    w = w > w2 ? w : w2;
-    w = w > w3 ? w : w3;
-    // split copies: B always, A unless exact
-    const size_t a = a_exact ? 0 : 2 * align256((size_t)M * K * 4), b = 2 * align256((size_t)N * K * 4);
-    return align256(w) + a + b + 256;
+template <class T3>
+static size_t gemm_ws3(int M, int N, int K) {
+    return workspace_of<T3>(M, N, K);
+}
+
+// Plan of one call.  TN (both operands contraction-major): one GEMM of depth 3K on concatenated copies.  NN / TT with an
+// exact A: one GEMM of width 2N on B = [hi | lo], halves added in the epilogue pass.  Anything else: the generic
+// sequence of two or three GEMMs on separate hi / lo copies.
+struct SplitPlan {
+    int mode;            // 0: deep TN, 1: wide (exact A), 2: generic
+    size_t gemm_ws, a_bytes, b_bytes, p_bytes;
+};
+
+static SplitPlan split_plan(TcGemmKind kind, int M, int N, int K, bool a_exact) {
+    SplitPlan p{};
+    if (kind == TC_A_ROWS_B_ROWS_OF_N && !a_exact) {
+        p.mode = 0;
+        p.gemm_ws = align256(workspace_of<Tf32TN>(M, N, 3 * K));
+        p.a_bytes = align256((size_t)M * 3 * K * 4);
+        p.b_bytes = align256((size_t)N * 3 * K * 4);
+    } else if (kind != TC_A_ROWS_B_ROWS_OF_N && a_exact && N % 4 == 0) {
+        p.mode = 1;
+        p.gemm_ws = align256(kind == TC_A_ROWS_B_ROWS_OF_K ? workspace_of<Tf32NN>(M, 2 * N, K) : workspace_of<Tf32TT>(M, 2 * N, K));
+        p.b_bytes = align256((size_t)K * 2 * N * 4);
+        p.p_bytes = align256((size_t)M * 2 * N * 4);
+    } else {
+        p.mode = 2;
+        size_t w = workspace_of<Tf32TN>(M, N, K);
+        const size_t w2 = workspace_of<Tf32NN>(M, N, K), w3 = workspace_of<Tf32TT>(M, N, K);
+        w = w > w2 ? w : w2;
+        p.gemm_ws = align256(w > w3 ? w : w3);
+        p.a_bytes = a_exact ? 0 : align256((size_t)M * K * 4 * 2);
+        p.b_bytes = align256((size_t)N * K * 4 * 2);
+    }
+    return p;
+}
+
+size_t tc_gemm_workspace(TcGemmKind kind, int M, int N, int K, bool a_exact) {
+    const SplitPlan p = split_plan(kind, M, N, K, a_exact);
+    return p.gemm_ws + p.a_bytes + p.b_bytes + p.p_bytes + 512;
 }
 
 template <class Cfg>
@@ -203,38 +256,61 @@ static int run3(int M, int N, int K, const float *Ah, const float *Al, int64_t l
 
 int tc_gemm(TcGemmKind kind, int M, int N, int K, const float *A, int64_t lda, const float *B, int64_t ldb, float *C,
             int64_t ldc, float alpha, float beta, bool a_exact, void *workspace, size_t workspace_bytes, cudaStream_t stream) {
-    LUTB_REQUIRE(workspace_bytes >= tc_gemm_workspace(M, N, K, a_exact), LUTB_ERR_WORKSPACE,
-                 "tensor-core contraction needs %zu bytes of workspace", tc_gemm_workspace(M, N, K, a_exact));
-    int64_t ar, ac, br, bc;
-    stored_extents(kind, M, N, K, &ar, &ac, &br, &bc);
+    const size_t need = tc_gemm_workspace(kind, M, N, K, a_exact);
+    LUTB_REQUIRE(workspace_bytes >= need, LUTB_ERR_WORKSPACE, "tensor-core contraction needs %zu bytes of workspace", need);
+    // stored extents of the operands: A is [ar x ac], B is [br x bc] (row-major, contiguous in the second)
+    const int64_t ar = kind == TC_A_COLS_B_ROWS_OF_K ? K : M, ac = kind == TC_A_COLS_B_ROWS_OF_K ? M : K;
+    const int64_t br = kind == TC_A_ROWS_B_ROWS_OF_N ? N : K, bc = kind == TC_A_ROWS_B_ROWS_OF_N ? K : N;
     LUTB_REQUIRE(ac % 4 == 0 && bc % 4 == 0, LUTB_ERR_ALIGN, "tensor-core contraction: row lengths must be multiples of 4");
-    unsigned char *p = static_cast<unsigned char *>(workspace);
-    p = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(p) + 255) & ~(uintptr_t)255);
-    size_t gemm_ws = workspace_of<Tf32TN>(M, N, K);
-    {
-        const size_t w2 = workspace_of<Tf32NN>(M, N, K), w3 = workspace_of<Tf32TT>(M, N, K);
-        gemm_ws = gemm_ws > w2 ? gemm_ws : w2;
-        gemm_ws = align256(gemm_ws > w3 ? gemm_ws : w3);
-    }
+    const SplitPlan plan = split_plan(kind, M, N, K, a_exact);
+    unsigned char *p = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(workspace) + 255) & ~(uintptr_t)255);
     void *gw = p;
-    p += gemm_ws;
-    const size_t bsz = align256((size_t)N * K * 4), asz = align256((size_t)M * K * 4);
-    float *Bh = reinterpret_cast<float *>(p), *Bl = reinterpret_cast<float *>(p + bsz);
-    p += 2 * bsz;
-    int rc = split(B, br, bc, ldb, Bh, Bl, stream);
+    p += plan.gemm_ws;
+    float *Bs = reinterpret_cast<float *>(p);
+    p += plan.b_bytes;
+    float *As = reinterpret_cast<float *>(p);
+    p += plan.a_bytes;
+    float *P = reinterpret_cast<float *>(p);
+    int rc;
+    if (plan.mode == 0) {
+        // A' = [hi | hi | lo], B' = [hi | lo | hi] along the contraction index: one GEMM of depth 3K
+        rc = split(A, M, K, lda, As, 3, 0b100u, stream);
+        if (rc) return rc;
+        rc = split(B, N, K, ldb, Bs, 3, 0b010u, stream);
+        if (rc) return rc;
+        return run<Tf32TN>(M, N, 3 * K, As, 3 * (int64_t)K, Bs, 3 * (int64_t)K, C, ldc, alpha, beta, gw, plan.gemm_ws, stream);
+    }
+    if (plan.mode == 1) {
+        // B' = [hi | lo] along the free index: one GEMM of width 2N into P, then C = alpha * (P_hi + P_lo) + beta * C
+        rc = split(B, K, N, ldb, Bs, 2, 0b10u, stream);
+        if (rc) return rc;
+        if (kind == TC_A_ROWS_B_ROWS_OF_K) rc = run<Tf32NN>(M, 2 * N, K, A, lda, Bs, 2 * (int64_t)N, P, 2 * (int64_t)N, 1.f, 0.f, gw, plan.gemm_ws, stream);
+        else rc = run<Tf32TT>(M, 2 * N, K, A, lda, Bs, 2 * (int64_t)N, P, 2 * (int64_t)N, 1.f, 0.f, gw, plan.gemm_ws, stream);
+        if (rc) return rc;
+        const int64_t n4 = (int64_t)M * (N / 4);
+        int64_t blocks = (n4 + 255) / 256;
+        const int64_t cap = (int64_t)device_info().sm_count * 16;
+        if (blocks > cap) blocks = cap;
+        combine_halves_kernel<<<(unsigned)blocks, 256, 0, stream>>>(P, C, M, N, ldc, alpha, beta);
+        LUTB_LAUNCH_CHECK();
+        return LUTB_OK;
+    }
+    // generic: separate hi / lo copies (one matrix with two parts each), two or three GEMMs
+    rc = split(B, br, bc, ldb, Bs, 2, 0b10u, stream);
     if (rc) return rc;
     const float *Ah = A, *Al = nullptr;
     int64_t lda_s = lda;
     if (!a_exact) {
-        float *h = reinterpret_cast<float *>(p), *l = reinterpret_cast<float *>(p + asz);
-        rc = split(A, ar, ac, lda, h, l, stream);
+        rc = split(A, ar, ac, lda, As, 2, 0b10u, stream);
         if (rc) return rc;
-        Ah = h; Al = l; lda_s = ac;
+        Ah = As; Al = As + ac; lda_s = 2 * ac;
     }
+    const float *Bh = Bs, *Bl = Bs + bc;
+    const int64_t ldb_s = 2 * bc;
     switch (kind) {
-        case TC_A_ROWS_B_ROWS_OF_N: return run3<Tf32TN>(M, N, K, Ah, Al, lda_s, Bh, Bl, bc, C, ldc, alpha, beta, gw, gemm_ws, stream);
-        case TC_A_ROWS_B_ROWS_OF_K: return run3<Tf32NN>(M, N, K, Ah, Al, lda_s, Bh, Bl, bc, C, ldc, alpha, beta, gw, gemm_ws, stream);
-        default: return run3<Tf32TT>(M, N, K, Ah, Al, lda_s, Bh, Bl, bc, C, ldc, alpha, beta, gw, gemm_ws, stream);
+        case TC_A_ROWS_B_ROWS_OF_N: return run3<Tf32TN>(M, N, K, Ah, Al, lda_s, Bh, Bl, ldb_s, C, ldc, alpha, beta, gw, plan.gemm_ws, stream);
+        case TC_A_ROWS_B_ROWS_OF_K: return run3<Tf32NN>(M, N, K, Ah, Al, lda_s, Bh, Bl, ldb_s, C, ldc, alpha, beta, gw, plan.gemm_ws, stream);
+        default: return run3<Tf32TT>(M, N, K, Ah, Al, lda_s, Bh, Bl, ldb_s, C, ldc, alpha, beta, gw, plan.gemm_ws, stream);
     }
 }
 
@@ -263,7 +339,12 @@ extern "C" int lutb_fp32_gemm_available(void) { return lutb::tc_gemm_available()
 
 extern "C" size_t lutb_fp32_gemm_workspace(int32_t m, int32_t n, int32_t k) {
     if (!(m > 0 && n > 0 && k > 0)) return 0;
-    const size_t a = lutb::tc_gemm_workspace(m, n, k, false), b = lutb::tc_gemm_fast_workspace(m, n, k);
+    size_t a = 0;
+    for (int kind = 0; kind < 3; kind++) {
+        const size_t w = lutb::tc_gemm_workspace(static_cast<lutb::TcGemmKind>(kind), m, n, k, false);
+        a = w > a ? w : a;
+    }
+    const size_t b = lutb::tc_gemm_fast_workspace(m, n, k);
     return a > b ? a : b;
 }
 

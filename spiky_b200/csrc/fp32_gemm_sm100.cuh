@@ -14,9 +14,10 @@ enum TcGemmKind {
 // false when the library was built without a CUTLASS header tree (tc_gemm then fails with LUTB_ERR_MODE)
 bool tc_gemm_available();
 // C [M x N] row-major = alpha * op(A) . op(B) + beta * C; all pointers 16-byte aligned, lda / ldb / ldc multiples of 4.
-// Split-TF32 route (up to three TF32 GEMMs on hi / lo copies of the operands kept in the workspace).
+// Split-TF32 route: hi / lo copies of the operands in the workspace, concatenated so that one TF32 GEMM forms all the
+// cross products wherever the layouts allow (else two or three GEMMs accumulate into C).
 // a_exact: A holds integers below 2048 (row counts), which TF32 represents exactly: A is used as it is, two GEMMs.
-size_t tc_gemm_workspace(int M, int N, int K, bool a_exact);
+size_t tc_gemm_workspace(TcGemmKind kind, int M, int N, int K, bool a_exact);
 int tc_gemm(TcGemmKind kind, int M, int N, int K, const float *A, int64_t lda, const float *B, int64_t ldb, float *C,
             int64_t ldc, float alpha, float beta, bool a_exact, void *workspace, size_t workspace_bytes, cudaStream_t stream);
 // Single-GEMM route: the mainloop splits the fp32 operands into BF16 terms on the fly.

@@ -245,7 +245,7 @@ __device__ __forceinline__ void chunk_backward(const SparseView &sp, const Chunk
 }
 
 template <bool DO_DX, bool DO_DW, bool INT_DW>
-__global__ void __launch_bounds__(256, 4) sparse_backward_kernel(SparseView sp, const float *__restrict__ W,
+__global__ void __launch_bounds__(256, DO_DX ? 3 : 4) sparse_backward_kernel(SparseView sp, const float *__restrict__ W,
                                                              const float *__restrict__ dY,
                                                              const int2 *__restrict__ anchors,
                                                              const int32_t *__restrict__ idx,

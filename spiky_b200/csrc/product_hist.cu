@@ -389,8 +389,9 @@ static size_t bytes_per_sequence(const lutb_layer_cfg *cfg, int S, bool backward
 // the operands (the tables, and the output gradients in the backward pass); the largest of the calls the pass makes.
 static size_t tc_scratch_bytes(const lutb_layer_cfg *cfg, int64_t rows, bool backward) {
     const int KT = cfg->n_detectors << cfg->n_anchors, O = cfg->n_outputs;
-    if (!backward) return align256(tc_gemm_workspace((int)rows, O, KT, true));
-    const size_t dw = tc_gemm_workspace(KT, O, (int)rows, true), q = tc_gemm_workspace((int)rows, KT, O, false);
+    if (!backward) return align256(tc_gemm_workspace(TC_A_ROWS_B_ROWS_OF_K, (int)rows, O, KT, true));
+    const size_t dw = tc_gemm_workspace(TC_A_COLS_B_ROWS_OF_K, KT, O, (int)rows, true),
+                 q = tc_gemm_workspace(TC_A_ROWS_B_ROWS_OF_N, (int)rows, KT, O, false);
     return align256(dw > q ? dw : q);
 }
 
