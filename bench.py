@@ -268,7 +268,7 @@ class SparseConvNetWorkload:
         """How cold caches are ensured between timed steps: the step's inputs exceed L2, or L2 is flushed."""
         return "inputs>L2" if getattr(self, "static_input_bytes", 0) > L2_BYTES else "flushed"
 
-    def __init__(self, batch=512, internal=False, sharded=False):
+    def __init__(self, batch=512, internal=False, sharded=False, peer=False):
         self.B = batch
         self.units_per_step = batch
         # sharded: data parallelism without dense gradient exchange for the three sparse layers: ranks all-gather
@@ -276,6 +276,9 @@ class SparseConvNetWorkload:
         # and all-gather the updated tables (spiky_b200.data_parallel.ShardedTableUpdate); the readout layer keeps
         # all-reduce + SGD
         self.sharded = sharded
+        # peer: data parallelism with the gradient reduction, the SGD update and the distribution of the updated tables
+        # in one kernel over peer memory (spiky_b200.data_parallel.PeerTableUpdate), for all four layers
+        self.peer = peer
         # internal: the reference's GradientType.Internal, the backward kernel applies W -= lr * dW in place (no dense
         # gradient, no optimiser pass); default: dense gradients + torch.optim.SGD
         self.internal = internal
@@ -328,9 +331,13 @@ class SparseConvNetWorkload:
         params = [l._weights for l in self.layers]
         if self.sharded:
             from spiky_b200.data_parallel import ShardedTableUpdate
-            self.sharded_sync = ShardedTableUpdate(self.layers[:-1], self.LR)
+            self.table_sync = ShardedTableUpdate(self.layers[:-1], self.LR)
             params = params[-1:]
-        self.opt = None if self.internal else torch.optim.SGD(params, lr=self.LR)
+        if self.peer:
+            from spiky_b200.data_parallel import PeerTableUpdate
+            self.table_sync = PeerTableUpdate(self.layers, self.LR)
+            params = []
+        self.opt = None if (self.internal or not params) else torch.optim.SGD(params, lr=self.LR)
         x, labels = self.host_inputs(1000 + rank, self.B)
         self.hx = torch.from_numpy(x).view(self.B, 1, 28, 28).pin_memory()
         self.hl = torch.from_numpy(labels).pin_memory()
@@ -346,8 +353,8 @@ class SparseConvNetWorkload:
         import torch.nn.functional as F
         if self.opt is not None:
             self.opt.zero_grad(set_to_none=True)
-        if self.sharded:
-            self.sharded_sync.wait()  # the tables updated by the previous step have arrived
+        if self.table_sync is not None:
+            self.table_sync.wait()  # the tables updated by the previous step have arrived
         z = x
         for l in self.layers[:-1]:
             z = l(z)
@@ -362,12 +369,13 @@ class SparseConvNetWorkload:
             with torch.no_grad():
                 for p in self.grad_sync.wait_each():
                     p.add_(p.grad, alpha=-self.LR)
-        else:
+        elif self.opt is not None:
             self.opt.step()
         return loss
 
     allreduce = None
     grad_sync = None
+    table_sync = None     # sharded / peer table update: the exchange it leaves running belongs to the step
     average_tables = None  # data parallel + Internal policy: tables are averaged over the ranks after the step
 
     def trainable_parameters(self):
@@ -904,6 +912,7 @@ WORKLOADS = {
     "sparse_convnet": lambda batch=None: SparseConvNetWorkload(**_b(batch)),
     "sparse_convnet_internal": lambda batch=None: SparseConvNetWorkload(internal=True, **_b(batch)),
     "sparse_convnet_sharded": lambda batch=None: SparseConvNetWorkload(sharded=True, **_b(batch)),
+    "sparse_convnet_peer": lambda batch=None: SparseConvNetWorkload(peer=True, **_b(batch)),
     "lut_layer": lambda batch=None: LutLayerWorkload(**_b(batch)),
     "lut_layer_b256": lambda batch=None: LutLayerWorkload(batch=batch or 256),
     "lut_layer_b256_graph": lambda batch=None: LutLayerWorkload(batch=batch or 256, graph=True),
@@ -987,7 +996,7 @@ def _attach_data_parallel(wl, world):
     """Gradient exchange of a data-parallel run: per-parameter all-reduce hooks (or the table average of the
     Internal policy); returns the sync object (None when there is nothing to exchange)."""
     import torch
-    if world <= 1:
+    if world <= 1 or (not wl.trainable_parameters() and not getattr(wl, "internal", False)):
         return None
     # gradients are exchanged per parameter as soon as its backward has run, overlapping the rest of
     # the backward pass; the workload only waits for the outstanding collectives before it updates
@@ -1000,6 +1009,12 @@ def _attach_data_parallel(wl, world):
         holder = torch.nn.ModuleList(wl.layers)
         wl.average_tables = lambda: average_internal_policy_weights(holder)
     return sync
+
+
+def _dp_strategy(wl):
+    if getattr(wl, "peer", False):
+        return "fused update over peer memory"
+    return "sharded table update" if getattr(wl, "sharded", False) else "gradient all-reduce"
 
 
 def _replica_check(params, world):
@@ -1038,7 +1053,7 @@ def run_ours(args):
     flush = torch.empty(2 * L2_BYTES, dtype=torch.uint8, device=device)
     dp_strategy = None
     if world > 1:
-        dp_strategy = "sharded table update" if getattr(wl, "sharded", False) else "gradient all-reduce"
+        dp_strategy = _dp_strategy(wl)
 
     def barrier():
         if world > 1:
@@ -1047,8 +1062,8 @@ def run_ours(args):
 
     def finish_step(w):
         # exchanges a workload leaves running on a side stream belong to the step that started them
-        if getattr(w, "sharded", False):
-            w.sharded_sync.wait()
+        if getattr(w, "table_sync", None) is not None:
+            w.table_sync.wait()
 
     def timed_region(w, steps, profile):
         """Returns (ms per step measured with CUDA events on the current stream, profiler records, host window)."""
@@ -1085,32 +1100,47 @@ def run_ours(args):
         finish_step(wl)
     dp_trial = None
     if world > 1 and args.workload == DEFAULT_WORKLOAD and args.dp == "auto":
-        # Two ways to keep the replicas' tables equal (same SGD step, spiky_b200/data_parallel.py): all-reduce the dense
-        # table gradients, or gather (index, output gradient) pairs and update a share of the tables in place.  Which one
-        # is faster depends on the number of ranks and on the interconnect: both are timed for a few steps and the
-        # faster one runs the measurement.
-        alt = WORKLOADS["sparse_convnet_sharded"](args.batch)
-        alt.setup(device, rank)
-        alt_sync = _attach_data_parallel(alt, world)
-        for _ in range(3):
-            alt.step_device()
-            finish_step(alt)
-        t_alt, _, _ = timed_region(alt, 8, profile=False)
-        t_cur, _, _ = timed_region(wl, 8, profile=False)
-        t = torch.tensor([t_cur, t_alt], dtype=torch.float64, device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        t_cur, t_alt = t.tolist()
-        dp_trial = {"gradient all-reduce": t_cur, "sharded table update": t_alt}
-        if t_alt < t_cur:
-            if sync is not None:
-                sync.remove()
-            wl, sync, dp_strategy = alt, alt_sync, "sharded table update"
-        else:
-            alt.sharded_sync.remove()
-            if alt_sync is not None:
-                alt_sync.remove()
+        # Three ways to keep the replicas' tables equal (same SGD step, spiky_b200/data_parallel.py): all-reduce the
+        # dense table gradients and run the optimiser; gather (index, output gradient) pairs and update a share of the
+        # tables in place; or reduce, update and distribute in one kernel over peer memory.  Which one is fastest
+        # depends on the number of ranks and on the interconnect: each is timed for a few steps and the fastest one
+        # runs the measurement.
+        def agreed(ms):
+            t = torch.tensor([ms], dtype=torch.float64, device=device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return float(t)
+
+        def release(w, s_):
+            if s_ is not None:
+                s_.remove()
+            if getattr(w, "table_sync", None) is not None:
+                w.table_sync.remove()
+
+        best = (agreed(timed_region(wl, 8, profile=False)[0]), wl, sync)
+        dp_trial = {_dp_strategy(wl): best[0]}
+        for name in ("sparse_convnet_sharded", "sparse_convnet_peer"):
+            alt = WORKLOADS[name](args.batch)
+            try:
+                alt.setup(device, rank)
+            except RuntimeError as e:
+                # the constructors agree over the ranks before they raise, so every rank lands here together
+                dp_trial[_dp_strategy(alt)] = "unavailable: " + str(e)[:200]
+                continue
+            alt_sync = _attach_data_parallel(alt, world)
+            for _ in range(3):
+                alt.step_device()
+                finish_step(alt)
+            t_alt = agreed(timed_region(alt, 8, profile=False)[0])
+            dp_trial[_dp_strategy(alt)] = t_alt
+            if t_alt < best[0]:
+                release(best[1], best[2])
+                best = (t_alt, alt, alt_sync)
+            else:
+                release(alt, alt_sync)
             del alt
-        torch.cuda.empty_cache()
+            torch.cuda.empty_cache()
+        _, wl, sync = best
+        dp_strategy = _dp_strategy(wl)
     ms_dev, prof, window = timed_region(wl, args.steps, profile=True)
 
     def e2e_region(steps):
@@ -1168,6 +1198,32 @@ def run_ours(args):
             iso.append(a.elapsed_time(b))
         del shares, outs
         comm = {"ms_local": 0.0, "ms_isolated": min(iso[1:]), "payload": payload, "sharded": True}
+    elif world > 1 and getattr(wl, "peer", False):
+        # the fused update: per rank (G-1)/G of the tables come in over the links and the same amount goes out; timed
+        # as the step without exchange (every rank updates its own copy from its own gradient) and alone (learning
+        # rate 0: the same loads and stores, tables unchanged)
+        ts = wl.table_sync
+        payload = sum(l._weights.numel() * 4 for l in wl.layers) * (world - 1) // world
+        ts.paused = True
+        for _ in range(2):
+            wl.step_device()
+            finish_step(wl)
+        ms_local, _, _ = timed_region(wl, max(3, args.steps // 4), profile=False)
+        ts.paused = False
+        lr0, ts.lr = ts.lr, 0.0
+        iso = []
+        for rep in range(4):
+            barrier()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for l in reversed(wl.layers):
+                ts.gradient_ready(l)
+            ts.wait()
+            b.record()
+            torch.cuda.synchronize()
+            iso.append(a.elapsed_time(b))
+        ts.lr = lr0
+        comm = {"ms_local": ms_local, "ms_isolated": min(iso[1:]), "payload": payload, "peer": True}
     elif world > 1 and sync is not None and wl.trainable_parameters():
         params = wl.trainable_parameters()
         payload = sum(p.numel() * p.element_size() for p in params)
@@ -1279,6 +1335,19 @@ def run_ours(args):
                 "payload_bytes_per_step": comm["payload"], "isolated_ms": ms_isolated,
                 "isolated_busbw_gbs": gb / (ms_isolated / 1e3), "frac_of_nvlink": gb / (ms_isolated / 1e3) / 900.0,
                 "isolated_what": "all-gather of the table shares alone (received bytes per rank / time)",
+            }
+        elif comm and comm.get("peer"):
+            gb = comm["payload"] / 1e9
+            line["comm"] = {
+                "exchange": "one kernel per layer over peer memory (CUDA IPC, NVLink): each rank reads its slice of every "
+                            "rank's table gradient, applies the SGD step and stores the new slice into every rank's "
+                            "tables; overlapped with the backward pass of the layers below",
+                "payload_bytes_per_step_per_direction": comm["payload"], "ms_step_without_exchange": ms_local,
+                "exposed_ms": ms_dev - ms_local, "isolated_ms": ms_isolated,
+                "isolated_gbs_per_direction": gb / (ms_isolated / 1e3),
+                "frac_of_nvlink": gb / (ms_isolated / 1e3) / 900.0,
+                "frac_of_measured_peer_copy": gb / (ms_isolated / 1e3) / 770.0,
+                "hidden_frac": 1.0 - (ms_dev - ms_local) / ms_isolated,
             }
         elif comm:
             ring = 2.0 * (world - 1) / world * comm["payload"] / 1e9

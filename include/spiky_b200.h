@@ -196,8 +196,8 @@ typedef struct lutb_sparse_index {
  *           not possible.
  *   AUTO    forward: STAGED when possible, 2 * batch >= rows per table and the layer has at least 4 detectors per SM,
  *           else GATHER; input gradient: GATHER (the staged variant measured slower on B200).
- * lutb_device_wait_errors: every device-side wait of the staged kernels is bounded (about a second); a wait that runs
- * out makes its block leave early (results are then incomplete) and is counted here.  Reads the counter of the current
+ * lutb_device_wait_errors: every device-side wait (the staged kernels' and lutb_peer_barrier's) is bounded (about a
+ * second); a wait that runs out makes its block leave early (results are then incomplete) and is counted here.  Reads the counter of the current
  * device and synchronises it; 0 in a healthy run.
  */
 #define LUTB_SPARSE_AUTO 0
@@ -431,6 +431,35 @@ int lutb_fp32_gemm_available(void);
 size_t lutb_fp32_gemm_workspace(int32_t m, int32_t n, int32_t k);
 int lutb_fp32_gemm(int kind, int32_t m, int32_t n, int32_t k, const float *a, int64_t lda, const float *b, int64_t ldb,
                    float *c, int64_t ldc, float alpha, float beta, void *workspace, size_t workspace_bytes, void *stream);
+
+/*
+ * Data-parallel SGD over peer memory (no reference counterpart: the reference trains on one device).
+ * lutb_peer_alloc allocates device memory other processes of the node can map and writes its 64-byte handle;
+ * lutb_peer_open maps a buffer another process allocated (the handle travels by any host channel) and enables peer
+ * access to its device; lutb_peer_close / lutb_peer_free undo them.  A handle cannot be opened in the process that
+ * made it: that process uses the pointer it got from lutb_peer_alloc.
+ * lutb_peer_sgd_update: rank `rank` of `n_ranks` owns floats [begin, end) of a table set.  grads[r] / weights[r] are
+ * rank r's dense gradient and tables (own pointers or mapped ones, 16-byte aligned, same layout on every rank).  One
+ * kernel computes, for every owned element e,  w = weights[rank][e] - scale * (grads[0][e] + ... + grads[n-1][e])
+ * (fp32, summed in rank order, multiply and subtract rounded separately) and stores w into weights[r][e] of every
+ * rank.  The kernel waits on nothing: the caller makes sure every rank's gradient is complete before any rank
+ * launches it and that nobody reads the tables or rewrites the gradients before every rank's kernel has finished.
+ * lutb_peer_barrier: a barrier over the ranks on the stream, without the host: flags[r] is rank r's array of n_ranks
+ * 64-bit flags in shareable memory (zero before the first use); every rank calls it with the same epoch, 1, 2, 3, ...
+ * A kernel of one warp stores the epoch into this rank's slot of every rank's array (release at system scope, so what
+ * earlier kernels of the stream wrote is visible to the ranks that see the flag) and waits until every slot of its own
+ * array holds it.  The wait is bounded (about two seconds); one that runs out is counted by lutb_device_wait_errors and
+ * the kernel returns.  Every rank must be running on its own GPU.
+ */
+#define LUTB_PEER_HANDLE_BYTES 64
+#define LUTB_MAX_PEER_RANKS 16
+int lutb_peer_alloc(size_t bytes, void **ptr_out, unsigned char *handle_out);
+int lutb_peer_free(void *ptr);
+int lutb_peer_open(const unsigned char *handle, void **ptr_out);
+int lutb_peer_close(void *ptr);
+int lutb_peer_barrier(int32_t n_ranks, int32_t rank, void *const *flags, uint64_t epoch, void *stream);
+int lutb_peer_sgd_update(int32_t n_ranks, int32_t rank, const float *const *grads, float *const *weights,
+                         int64_t begin, int64_t end, float scale, void *stream);
 
 #ifdef __cplusplus
 }

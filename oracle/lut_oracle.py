@@ -342,3 +342,13 @@ def concat_sparse_backward(W, dY, anchors, state, sp, n_inputs, n_anchors, pos_d
                                      _i(int(int_mode)), _d(int_rescaler))
     return dX, dW, dPE
 
+
+
+def peer_sgd_update(weights, grads, scale):
+    """Data-parallel SGD step of one table set (no reference counterpart: the reference trains on one device; this
+    states what ``lutb_peer_sgd_update`` computes so that the kernel can be checked bit for bit): the ranks' fp32
+    gradients are added in rank order, ``w - scale * sum`` with the product and the difference rounded separately."""
+    acc = _f32(grads[0]).copy()
+    for g in grads[1:]:
+        acc += _f32(g)
+    return _f32(weights) - np.float32(scale) * acc

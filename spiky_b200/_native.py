@@ -109,6 +109,13 @@ SIGNATURES = {
     "lutb_fp32_gemm_workspace": (_size, [ctypes.c_int32, ctypes.c_int32, ctypes.c_int32]),
     "lutb_fp32_gemm": (_int, [_int, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, _vp, _i64, _vp, _i64, _vp, _i64,
                               ctypes.c_float, ctypes.c_float, _vp, _size, _vp]),
+    "lutb_peer_alloc": (_int, [_size, ctypes.POINTER(_vp), ctypes.c_char_p]),
+    "lutb_peer_free": (_int, [_vp]),
+    "lutb_peer_open": (_int, [ctypes.c_char_p, ctypes.POINTER(_vp)]),
+    "lutb_peer_close": (_int, [_vp]),
+    "lutb_peer_barrier": (_int, [ctypes.c_int32, ctypes.c_int32, ctypes.POINTER(_vp), ctypes.c_uint64, _vp]),
+    "lutb_peer_sgd_update": (_int, [ctypes.c_int32, ctypes.c_int32, ctypes.POINTER(_vp), ctypes.POINTER(_vp), _i64, _i64,
+                                    ctypes.c_float, _vp]),
     "lutb_nonseq_sparse_forward": (_int, [_cfgp, _spp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "lutb_nonseq_sparse_backward": (_int, [_cfgp, _spp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _dbl, _vp]),
     "lutb_nonseq_sparse_table_grad": (_int, [_cfgp, _spp, _i64, _vp, _vp, _int, _vp, _dbl, _i64, _i64, _vp]),
@@ -173,6 +180,50 @@ def sparse_kernel_select(forward, input_grad=None):
     """Force the gather or the staged kernels for the forward and the input-gradient pass of sparse layers
     (SPARSE_AUTO restores the library's choice; one argument sets both passes)."""
     check(lib().lutb_sparse_kernel_select(int(forward), int(forward if input_grad is None else input_grad)))
+
+
+PEER_HANDLE_BYTES = 64
+MAX_PEER_RANKS = 16
+
+
+def peer_alloc(nbytes):
+    """Device memory other processes of the node can map: (device pointer, 64-byte handle)."""
+    ptr = _vp()
+    handle = ctypes.create_string_buffer(PEER_HANDLE_BYTES)
+    check(lib().lutb_peer_alloc(int(nbytes), ctypes.byref(ptr), handle))
+    return ptr.value, handle.raw
+
+
+def peer_free(ptr):
+    check(lib().lutb_peer_free(_vp(ptr)))
+
+
+def peer_open(handle):
+    """Maps a buffer another process of the node allocated with peer_alloc; returns the device pointer."""
+    assert len(handle) == PEER_HANDLE_BYTES
+    ptr = _vp()
+    check(lib().lutb_peer_open(bytes(handle), ctypes.byref(ptr)))
+    return ptr.value
+
+
+def peer_close(ptr):
+    check(lib().lutb_peer_close(_vp(ptr)))
+
+
+def peer_barrier(rank, flag_ptrs, epoch, stream):
+    """Stream-ordered barrier over the ranks through flags in peer memory (flag_ptrs[r]: rank r's flag array)."""
+    n = len(flag_ptrs)
+    check(lib().lutb_peer_barrier(n, int(rank), (_vp * n)(*flag_ptrs), int(epoch), _vp(stream)))
+
+
+def peer_sgd_update(rank, grad_ptrs, weight_ptrs, begin, end, scale, stream):
+    """weights[r][begin:end] = weights[rank][begin:end] - scale * sum_r grads[r][begin:end] on every rank r; the
+    pointers are device addresses (own or mapped), one per rank."""
+    n = len(grad_ptrs)
+    assert len(weight_ptrs) == n
+    arr = _vp * n
+    check(lib().lutb_peer_sgd_update(n, int(rank), arr(*grad_ptrs), arr(*weight_ptrs), int(begin), int(end),
+                                     float(scale), _vp(stream)))
 
 
 def device_wait_errors():

@@ -101,21 +101,29 @@ static size_t workspace_of(int M, int N, int K) {
     return Cfg::Gemm::get_workspace_size(args);
 }
 
+// `batches` independent GEMMs of the same shape in one launch; operand b of batch l starts batch_b * l elements
+// after the first (and so on); one batch by default.
+struct Batches {
+    int count = 1;
+    int64_t a = 0, b = 0, c = 0;
+};
+
 template <class Cfg>
 static int run(int M, int N, int K, const float *A, int64_t lda, const float *B, int64_t ldb, float *C, int64_t ldc,
-               float alpha, float beta, void *workspace, size_t workspace_bytes, cudaStream_t stream) {
+               float alpha, float beta, void *workspace, size_t workspace_bytes, cudaStream_t stream,
+               Batches batches = Batches{}) {
     typename Cfg::StrideA sa;
     typename Cfg::StrideB sb;
     typename Cfg::StrideC sc;
-    // the dynamic (non unit) mode of every stride is the leading dimension; one batch
-    if constexpr (cute::is_same_v<decltype(get<1>(sa)), cute::Int<1>>) sa = make_stride(lda, Int<1>{}, int64_t(0));
-    else sa = make_stride(Int<1>{}, lda, int64_t(0));
-    if constexpr (cute::is_same_v<decltype(get<1>(sb)), cute::Int<1>>) sb = make_stride(ldb, Int<1>{}, int64_t(0));
-    else sb = make_stride(Int<1>{}, ldb, int64_t(0));
-    sc = make_stride(ldc, Int<1>{}, int64_t(0));
+    // the dynamic (non unit) mode of every stride is the leading dimension
+    if constexpr (cute::is_same_v<decltype(get<1>(sa)), cute::Int<1>>) sa = make_stride(lda, Int<1>{}, batches.a);
+    else sa = make_stride(Int<1>{}, lda, batches.a);
+    if constexpr (cute::is_same_v<decltype(get<1>(sb)), cute::Int<1>>) sb = make_stride(ldb, Int<1>{}, batches.b);
+    else sb = make_stride(Int<1>{}, ldb, batches.b);
+    sc = make_stride(ldc, Int<1>{}, batches.c);
     using ElementAB = typename Cfg::Element;
     typename Cfg::Gemm::Arguments args{cutlass::gemm::GemmUniversalMode::kGemm,
-                                       {M, N, K, 1},
+                                       {M, N, K, batches.count},
                                        {reinterpret_cast<const ElementAB *>(A), sa, reinterpret_cast<const ElementAB *>(B), sb},
                                        {{alpha, beta}, C, sc, C, sc}};
     typename Cfg::Gemm gemm;
@@ -179,14 +187,24 @@ static int split(const float *x, int64_t rows, int64_t cols, int64_t ld, float *
     return LUTB_OK;
 }
 
-// C = alpha * (P[:, 0:N] + P[:, N:2N]) + beta * C  (lo part first into the sum, as the smaller one)
+// C = alpha * sum over the slices s of (P_s[:, 0:N] + P_s[:, N:2N]) + beta * C, P_s = P + s * M * 2N; the lo halves are
+// summed first (the smaller terms), then the hi halves, in rounded fp32.
 __global__ void combine_halves_kernel(const float *__restrict__ P, float *__restrict__ C, int64_t M, int64_t N, int64_t ldc,
-                                      float alpha, float beta) {
+                                      float alpha, float beta, int slices) {
     const int64_t n4 = M * (N / 4);
+    const int64_t slice = M * 2 * N;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (int64_t)gridDim.x * blockDim.x) {
         const int64_t r = i / (N / 4), c = (i - r * (N / 4)) * 4;
-        const float4 hi = *reinterpret_cast<const float4 *>(P + r * 2 * N + c);
-        const float4 lo = *reinterpret_cast<const float4 *>(P + r * 2 * N + N + c);
+        float4 lo = *reinterpret_cast<const float4 *>(P + r * 2 * N + N + c);
+        for (int s_ = 1; s_ < slices; s_++) {
+            const float4 t = *reinterpret_cast<const float4 *>(P + s_ * slice + r * 2 * N + N + c);
+            lo.x += t.x; lo.y += t.y; lo.z += t.z; lo.w += t.w;
+        }
+        float4 hi = *reinterpret_cast<const float4 *>(P + r * 2 * N + c);
+        for (int s_ = 1; s_ < slices; s_++) {
+            const float4 t = *reinterpret_cast<const float4 *>(P + s_ * slice + r * 2 * N + c);
+            hi.x += t.x; hi.y += t.y; hi.z += t.z; hi.w += t.w;
+        }
         float4 *dst = reinterpret_cast<float4 *>(C + r * ldc + c);
         float4 v = make_float4(alpha * (lo.x + hi.x), alpha * (lo.y + hi.y), alpha * (lo.z + hi.z), alpha * (lo.w + hi.w));
         if (beta != 0.f) {
@@ -209,8 +227,35 @@ static size_t gemm_ws3(int M, int N, int K) {
 // sequence of two or three GEMMs on separate hi / lo copies.
 struct SplitPlan {
     int mode;            // 0: deep TN, 1: wide (exact A), 2: generic
+    int slices, kc;      // mode 1: the contraction index is cut into `slices` pieces of kc (see mode1_slices)
     size_t gemm_ws, a_bytes, b_bytes, p_bytes;
 };
+
+// How the wide plan cuts its contraction index.  Inside a slice the tensor core accumulates, truncating its fp32
+// accumulator after every step (a bias that grows with the length of the chain); the slices' results are added in
+// rounded fp32.  A . B with A [M x K] row-major (few output tiles, deep contraction: the forward pass of the histogram
+// path): the slices are the batches of ONE launch, each into its own partial result, which also gives the launch
+// K / kc times as many blocks.  A^T . B: the slices run one after the other and accumulate through the epilogue.  kc is
+// at least 8 N, which keeps the traffic of the partial results below half of the slice's operand traffic.
+static void mode1_slices(TcGemmKind kind, int N, int K, int *slices, int *kc) {
+    int want = ((8 * N + 255) / 256) * 256;
+    const int floor_ = kind == TC_A_ROWS_B_ROWS_OF_K ? 2048 : 8192;
+    if (want < floor_) want = floor_;
+    *slices = 1;
+    *kc = K;
+    if (kind == TC_A_ROWS_B_ROWS_OF_K) {
+        // equal slices (one batched launch): the largest count of pieces of at least `want` that divides K evenly
+        for (int l = K / want; l > 1; l--)
+            if (K % l == 0 && (K / l) % 4 == 0) {
+                *slices = l;
+                *kc = K / l;
+                break;
+            }
+    } else if (K > want) {
+        *kc = want;
+        *slices = (K + want - 1) / want;
+    }
+}
 
 static SplitPlan split_plan(TcGemmKind kind, int M, int N, int K, bool a_exact) {
     SplitPlan p{};
@@ -221,9 +266,10 @@ static SplitPlan split_plan(TcGemmKind kind, int M, int N, int K, bool a_exact) 
         p.b_bytes = align256((size_t)N * 3 * K * 4);
     } else if (kind != TC_A_ROWS_B_ROWS_OF_N && a_exact && N % 4 == 0) {
         p.mode = 1;
+        mode1_slices(kind, N, K, &p.slices, &p.kc);
         p.gemm_ws = align256(kind == TC_A_ROWS_B_ROWS_OF_K ? workspace_of<Tf32NN>(M, 2 * N, K) : workspace_of<Tf32TT>(M, 2 * N, K));
         p.b_bytes = align256((size_t)K * 2 * N * 4);
-        p.p_bytes = align256((size_t)M * 2 * N * 4);
+        p.p_bytes = align256((size_t)M * 2 * N * 4 * (kind == TC_A_ROWS_B_ROWS_OF_K ? p.slices : 1));
     } else {
         p.mode = 2;
         size_t w = workspace_of<Tf32TN>(M, N, K);
@@ -273,10 +319,12 @@ int tc_gemm(TcGemmKind kind, int M, int N, int K, const float *A, int64_t lda, c
     float *P = reinterpret_cast<float *>(p);
     int rc;
     if (plan.mode == 0) {
-        // A' = [hi | hi | lo], B' = [hi | lo | hi] along the contraction index: one GEMM of depth 3K
-        rc = split(A, M, K, lda, As, 3, 0b100u, stream);
+        // A' = [hi | lo | hi], B' = [lo | hi | hi] along the contraction index: one GEMM of depth 3K.  The mainloop
+        // walks the contraction index upwards and the tensor core truncates its fp32 accumulator after every step, an
+        // error proportional to the accumulator's size: the two small products go first, while it is small.
+        rc = split(A, M, K, lda, As, 3, 0b010u, stream);
         if (rc) return rc;
-        rc = split(B, N, K, ldb, Bs, 3, 0b010u, stream);
+        rc = split(B, N, K, ldb, Bs, 3, 0b001u, stream);
         if (rc) return rc;
         return run<Tf32TN>(M, N, 3 * K, As, 3 * (int64_t)K, Bs, 3 * (int64_t)K, C, ldc, alpha, beta, gw, plan.gemm_ws, stream);
     }
@@ -284,14 +332,29 @@ int tc_gemm(TcGemmKind kind, int M, int N, int K, const float *A, int64_t lda, c
         // B' = [hi | lo] along the free index: one GEMM of width 2N into P, then C = alpha * (P_hi + P_lo) + beta * C
         rc = split(B, K, N, ldb, Bs, 2, 0b10u, stream);
         if (rc) return rc;
-        if (kind == TC_A_ROWS_B_ROWS_OF_K) rc = run<Tf32NN>(M, 2 * N, K, A, lda, Bs, 2 * (int64_t)N, P, 2 * (int64_t)N, 1.f, 0.f, gw, plan.gemm_ws, stream);
-        else rc = run<Tf32TT>(M, 2 * N, K, A, lda, Bs, 2 * (int64_t)N, P, 2 * (int64_t)N, 1.f, 0.f, gw, plan.gemm_ws, stream);
-        if (rc) return rc;
+        int p_slices = 1;
+        if (kind == TC_A_ROWS_B_ROWS_OF_K) {
+            // the slices of the contraction index as the batches of one launch, each into its own partial result
+            Batches bt;
+            bt.count = p_slices = plan.slices;
+            bt.a = plan.kc;
+            bt.b = (int64_t)plan.kc * 2 * N;
+            bt.c = (int64_t)M * 2 * N;
+            rc = run<Tf32NN>(M, 2 * N, plan.kc, A, lda, Bs, 2 * (int64_t)N, P, 2 * (int64_t)N, 1.f, 0.f, gw, plan.gemm_ws, stream, bt);
+            if (rc) return rc;
+        } else {
+            for (int k0 = 0; k0 < K; k0 += plan.kc) {
+                const int kn = K - k0 < plan.kc ? K - k0 : plan.kc;
+                rc = run<Tf32TT>(M, 2 * N, kn, A + (int64_t)k0 * lda, lda, Bs + (int64_t)k0 * 2 * N, 2 * (int64_t)N, P,
+                                 2 * (int64_t)N, 1.f, k0 == 0 ? 0.f : 1.f, gw, plan.gemm_ws, stream);
+                if (rc) return rc;
+            }
+        }
         const int64_t n4 = (int64_t)M * (N / 4);
         int64_t blocks = (n4 + 255) / 256;
         const int64_t cap = (int64_t)device_info().sm_count * 16;
         if (blocks > cap) blocks = cap;
-        combine_halves_kernel<<<(unsigned)blocks, 256, 0, stream>>>(P, C, M, N, ldc, alpha, beta);
+        combine_halves_kernel<<<(unsigned)blocks, 256, 0, stream>>>(P, C, M, N, ldc, alpha, beta, p_slices);
         LUTB_LAUNCH_CHECK();
         return LUTB_OK;
     }

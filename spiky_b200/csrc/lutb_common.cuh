@@ -90,6 +90,8 @@ enum KernelId {
     K_PRODUCT_HIST_WEIGHT_GRAD,
     K_DENSE_TO_SPARSE,
     K_FP32_GEMM,
+    K_PEER_SGD_UPDATE,
+    K_PEER_BARRIER,
     K_COUNT
 };
 
@@ -126,6 +128,9 @@ __device__ __forceinline__ double surrogate_up(float m) {
 __device__ __forceinline__ int32_t to_fixed(double v, double scale) {
     return (int32_t)(v * kDenom * scale);  // cvt.rzi: truncation toward zero like the C cast
 }
+
+// Bounded waits of the peer-memory barrier that ran out on the current device (peer_update.cu).
+int peer_wait_errors(int *count_out);
 
 // In-place conversion of int32 fixed-point accumulators to fp32
 // (reference: convert_integers_to_floats_logic, proto:200-213).

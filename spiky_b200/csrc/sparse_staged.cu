@@ -680,5 +680,9 @@ int launch_sparse_input_grad_staged(const lutb_layer_cfg *cfg, const lutb_sparse
 extern "C" int lutb_device_wait_errors(int *count_out) {
     LUTB_REQUIRE(count_out != nullptr, LUTB_ERR_NULL, "count_out is NULL");
     LUTB_CUDA(cudaMemcpyFromSymbol(count_out, lutb::g_wait_errors, sizeof(int)));
+    int peer = 0;
+    const int rc = lutb::peer_wait_errors(&peer);
+    if (rc) return rc;
+    *count_out += peer;
     return LUTB_OK;
 }

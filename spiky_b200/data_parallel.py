@@ -386,6 +386,225 @@ class ShardedTableUpdate:
                 del layer._table_update_hook
 
 
+class _DeviceSpan:
+    """A span of device memory as an object ``torch.as_tensor`` can wrap without copying."""
+
+    def __init__(self, ptr, numel):
+        self.__cuda_array_interface__ = {"shape": (int(numel),), "typestr": "<f4", "data": (int(ptr), False),
+                                         "strides": None, "version": 2}
+
+
+class PeerTableUpdate:
+    """Data-parallel SGD for non-sequence LUT layers on one node: gradient reduction, table update and the broadcast
+    of the updated tables in ONE kernel over peer memory (``lutb_peer_sgd_update``), instead of an all-reduce of the
+    dense gradients followed by an optimiser pass.
+
+    Every rank's tables and dense table gradients live in buffers the other ranks have mapped (CUDA IPC over NVLink).
+    The layer's backward writes its table gradient into the rank's buffer; then rank r reads slice r of every rank's
+    gradient, applies ``w -= lr / G * sum`` (``average=False``: ``lr * sum``) and stores the new slice into every
+    rank's tables.  Per rank ``(G-1)/G`` of the tables cross the links in each direction, at the same time; the
+    optimiser pass, the gradient ``.grad`` tensors and NCCL's staging disappear, and because each element is computed
+    by one rank the replicas stay bit-identical.  The kernel itself never waits on another rank: a one-element
+    all-reduce of the process group before it (every rank's gradient of this layer is complete) and one after the last
+    layer (every rank's stores have landed) order it, on a side stream, so the exchange of a layer overlaps the
+    backward pass of the layers below it.
+
+    Use: ``sync = PeerTableUpdate(layers, lr)`` once, after the layers are on their device (their ``_weights`` move
+    into the shared buffers; ``remove()`` moves them back); run forward / backward as usual (the layers' ``_weights``
+    get no ``.grad``); call ``sync.wait()`` before the next forward.  fp32 tables, dense gradient policy, one
+    process per GPU, all ranks on one node.
+    """
+
+    def __init__(self, layers, lr, group=None, average=True, barrier="flags"):
+        from . import _native
+        from .lut_layer import GradientType, LUTLayerBasic
+
+        # how the ranks meet before and after the update kernels: "flags" = a one-warp kernel over flags in peer memory
+        # (lutb_peer_barrier: a few microseconds; its wait is bounded, a rank that is seconds late is counted by
+        # lutb_device_wait_errors and not waited for), "collective" = a one-element all-reduce of the process group
+        assert barrier in ("flags", "collective")
+        self.barrier = barrier
+        self._epoch = 0
+        self._native = _native
+        self.group = group
+        self.lr = lr
+        self.enabled = dist.is_available() and dist.is_initialized()
+        self.world = dist.get_world_size(group) if self.enabled else 1
+        self.rank = dist.get_rank(group) if self.enabled else 0
+        if self.world > _native.MAX_PEER_RANKS:
+            raise ValueError(f"PeerTableUpdate supports up to {_native.MAX_PEER_RANKS} ranks")
+        self.scale_div = self.world if average else 1
+        self.layers = list(layers)
+        self._side = None
+        self._dirty = False
+        # True: every rank applies its own gradient to its own copy (the replicas drift apart); for measuring what
+        # the exchange costs
+        self.paused = False
+        self._state = {}
+        self._owned = []    # pointers from peer_alloc
+        self._mapped = []   # pointers from peer_open
+        for layer in self.layers:
+            if not isinstance(layer, LUTLayerBasic) or layer._sequence_length != 1:
+                raise ValueError("PeerTableUpdate handles non-sequence LUT layers")
+            if layer._weights_gradient_policy.type != GradientType.Dense:
+                raise ValueError("PeerTableUpdate needs the dense gradient policy")
+            if not layer._weights.is_cuda or layer._weights.dtype != torch.float32:
+                raise ValueError("PeerTableUpdate needs fp32 tables on a CUDA device")
+        device = self.layers[0]._weights.device
+        # allocate, exchange the handles, map the other ranks' buffers.  A rank that fails tells the others through
+        # the same collectives, so that all ranks raise together instead of one leaving the others waiting.
+        handles, spans, error = [], [], None
+        f_ptr = f_handle = None
+        try:
+            with torch.cuda.device(device):
+                if self.world > 1:
+                    # the barrier's flags: one 64-bit slot per rank, zero before the first epoch
+                    f_ptr, f_handle = _native.peer_alloc(8 * _native.MAX_PEER_RANKS)
+                    self._owned.append(f_ptr)
+                    torch.as_tensor(_DeviceSpan(f_ptr, 2 * _native.MAX_PEER_RANKS), device=device).zero_()
+                for layer in self.layers:
+                    n = layer._weights.numel()
+                    nbytes = 4 * ((n + 3) // 4 * 4)
+                    g_ptr, g_handle = _native.peer_alloc(nbytes)
+                    self._owned.append(g_ptr)
+                    w_ptr, w_handle = _native.peer_alloc(nbytes)
+                    self._owned.append(w_ptr)
+                    handles.append((g_handle, w_handle))
+                    spans.append((g_ptr, w_ptr, n))
+        except RuntimeError as e:
+            error = str(e)
+        everyone = self._agree((error, handles, f_handle), "allocating shareable device memory")
+        g_all = [[g for g, _, _ in spans]]
+        w_all = [[w for _, w, _ in spans]]
+        if self.world > 1:
+            g_all, w_all, error = [], [], None
+            self._flag_ptrs = []
+            try:
+                with torch.cuda.device(device):
+                    for r in range(self.world):
+                        if r == self.rank:
+                            g_all.append([g for g, _, _ in spans])
+                            w_all.append([w for _, w, _ in spans])
+                            self._flag_ptrs.append(f_ptr)
+                            continue
+                        self._flag_ptrs.append(_native.peer_open(everyone[r][2]))
+                        self._mapped.append(self._flag_ptrs[-1])
+                        gs, ws = [], []
+                        for g_handle, w_handle in everyone[r][1]:
+                            gs.append(_native.peer_open(g_handle))
+                            self._mapped.append(gs[-1])
+                            ws.append(_native.peer_open(w_handle))
+                            self._mapped.append(ws[-1])
+                        g_all.append(gs)
+                        w_all.append(ws)
+            except RuntimeError as e:
+                error = str(e)
+            self._agree((error, None), "mapping the other ranks' buffers")  # also: everyone has mapped everything
+            self._token = torch.zeros(1, dtype=torch.float32, device=device)
+            self._side = torch.cuda.Stream(device=device)
+        for li, (layer, (g_ptr, w_ptr, n)) in enumerate(zip(self.layers, spans)):
+            grad = torch.as_tensor(_DeviceSpan(g_ptr, n), device=device)
+            shared = torch.as_tensor(_DeviceSpan(w_ptr, n), device=device)
+            assert grad.data_ptr() == g_ptr and shared.data_ptr() == w_ptr
+            grad.zero_()
+            shared.copy_(layer._weights.detach())
+            layer._weights.data = shared
+            # slice r of the tables belongs to rank r; cuts on 16-byte boundaries
+            cuts = [(n * r // self.world) // 4 * 4 for r in range(self.world)] + [n]
+            self._state[id(layer)] = dict(grad=grad, cuts=cuts, g_ptrs=[g_all[r][li] for r in range(self.world)],
+                                          w_ptrs=[w_all[r][li] for r in range(self.world)])
+            layer._table_gradient_sink = self
+        torch.cuda.synchronize(device)
+        if self.world > 1:
+            dist.barrier(group=group)  # every rank's tables are in place before anyone's kernel may store into them
+
+    def _agree(self, mine, what):
+        """All-gathers (error or None, payload); raises on every rank when any rank reported an error."""
+        everyone = [mine]
+        if self.world > 1:
+            everyone = [None] * self.world
+            dist.all_gather_object(everyone, mine, group=self.group)
+        errors = [f"rank {r}: {e[0]}" for r, e in enumerate(everyone) if e[0]]
+        if errors:
+            self._release()
+            raise RuntimeError(f"PeerTableUpdate: {what} failed ({errors[0]})")
+        return everyone
+
+    def _release(self):
+        """Unmaps the other ranks' buffers, then frees this rank's (collective when there are several ranks)."""
+        for p in self._mapped:
+            self._native.peer_close(p)
+        if self.world > 1:
+            dist.barrier(group=self.group)  # all mappings closed before the owners free
+        for p in self._owned:
+            self._native.peer_free(p)
+        self._mapped, self._owned = [], []
+
+    def _learning_rate(self):
+        return float(self.lr() if callable(self.lr) else self.lr)
+
+    def _rendezvous(self):
+        """Barrier over the ranks on the current stream (the host does not block)."""
+        if self.barrier == "flags":
+            self._epoch += 1
+            self._native.peer_barrier(self.rank, self._flag_ptrs, self._epoch,
+                                      torch.cuda.current_stream(self._side.device).cuda_stream)
+        else:
+            dist.all_reduce(self._token, group=self.group, async_op=True).wait()
+
+    # called by the layer's backward
+    def gradient_buffer(self, layer):
+        """The zeroed buffer the layer's backward accumulates its dense table gradient into."""
+        grad = self._state[id(layer)]["grad"]
+        grad.zero_()
+        return grad
+
+    def gradient_ready(self, layer):
+        """The layer's table gradient has been launched on the current stream: reduce, update, distribute."""
+        st = self._state[id(layer)]
+        scale = self._learning_rate() / self.scale_div
+        lo, hi = st["cuts"][self.rank], st["cuts"][self.rank + 1]
+        device = layer._weights.device
+        if self.world == 1 or self.paused:
+            # no exchange: this rank's gradient alone updates this rank's copy of the whole table set
+            own_g, own_w = [st["g_ptrs"][self.rank]], [st["w_ptrs"][self.rank]]
+            self._native.peer_sgd_update(0, own_g, own_w, 0, st["cuts"][-1], scale,
+                                         torch.cuda.current_stream(device).cuda_stream)
+            return
+        self._side.wait_stream(torch.cuda.current_stream(device))
+        with torch.cuda.stream(self._side):
+            self._rendezvous()  # every rank's gradient of this layer is complete and no rank still reads these tables
+            self._native.peer_sgd_update(self.rank, st["g_ptrs"], st["w_ptrs"], lo, hi, scale, self._side.cuda_stream)
+        self._dirty = True
+
+    def wait(self):
+        """Makes the current stream wait until every rank's update of this step has landed in this rank's tables."""
+        if self._side is None or not self._dirty:
+            return
+        with torch.cuda.stream(self._side):
+            self._rendezvous()
+        torch.cuda.current_stream(self._side.device).wait_stream(self._side)
+        self._dirty = False
+
+    def remove(self):
+        """Moves the tables back into ordinary device memory and releases the shared buffers (collective)."""
+        if not self.layers:
+            return
+        self.wait()
+        device = self.layers[0]._weights.device
+        for layer in self.layers:
+            layer._weights.data = layer._weights.data.clone()
+            if getattr(layer, "_table_gradient_sink", None) is self:
+                del layer._table_gradient_sink
+        self._state = {}
+        torch.cuda.synchronize(device)
+        if self.world > 1:
+            dist.barrier(group=self.group)  # nobody still reads a buffer that is about to go
+        with torch.cuda.device(device):
+            self._release()
+        self.layers = []
+
+
 class _NullContext:
     def __enter__(self):
         return self

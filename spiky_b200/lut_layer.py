@@ -546,11 +546,17 @@ class LUTLayerBasic(nn.Module):
                     SKIP_TABLE_GRADIENT, None, None)
             hook(self, lookup_indices.reshape(-1), grad_flat, B)
             return (None if x_grad is None else x_grad.view(x.shape)), None
-        w_grad = self._weight_grad_target()
+        sink = None if external else getattr(self, "_table_gradient_sink", None)
+        # data-parallel update over peer memory: the dense table gradient goes into the sink's shared buffer and the
+        # sink reduces it over the ranks and updates the tables; the parameter gets no .grad
+        w_grad = self._weight_grad_target() if sink is None else sink.gradient_buffer(self)
         self._lut_dm.backward_backprop(
             self._weights.detach(), B, grad_output.contiguous().view(-1), self._detector_anchors,
             lookup_indices.reshape(-1), min_anchor_deltas.reshape(-1), min_anchor_delta_indices.reshape(-1),
             None if x_grad is None else x_grad.view(-1), self._external_lr(), w_grad, None, dw_variant=self._dw_variant)
+        if sink is not None:
+            sink.gradient_ready(self)
+            return (None if x_grad is None else x_grad.view(x.shape)), None
         if not external:
             w_grad = self._process_gradients(w_grad, B)
             return (None if x_grad is None else x_grad.view(x.shape)), w_grad

@@ -154,6 +154,53 @@ def check_dp_sharded_update(rank, world, dev):
     sync.remove()
 
 
+def check_dp_peer_update(rank, world, dev, barrier="flags"):
+    """Gradient reduction + SGD + distribution of the tables in one kernel over peer memory: one step against the
+    single-process update of the whole batch, replicas bit-identical after a second one."""
+    from spiky_b200.data_parallel import PeerTableUpdate
+    from spiky_b200.lut_layer import GradientPolicy, GradientType
+
+    lr = 0.05
+    B = 32 * world
+    x = torch.from_numpy(synth.sparse_images(8, (B, 1, 20, 20))).to(dev)
+
+    def run(layers, xb):
+        z = xb
+        for l in layers:
+            z = l(z)
+        (z ** 2).sum().backward()
+
+    layers = small_convnet(dev, GradientPolicy(GradientType.Dense))
+    try:
+        sync = PeerTableUpdate(layers, lr, average=False, barrier=barrier)
+    except RuntimeError as e:
+        # all ranks raise together; a node that does not allow the mapping cannot run this path
+        report("dp_peer_update", True, "unavailable here: " + str(e)[:160])
+        return
+    per = B // world
+    run(layers, x[rank * per:(rank + 1) * per].contiguous())
+    sync.wait()
+    torch.cuda.synchronize()
+    ref = small_convnet(dev, GradientPolicy(GradientType.Internal))
+    for l in ref:
+        l.set_external_learning_rate_hook(lambda w: lr)
+    run(ref, x)
+    worst = max(rel_err(a._weights.detach().cpu().numpy(), b._weights.detach().cpu().numpy()) for a, b in zip(layers, ref))
+    # a second step on the updated tables (gradient buffers reused, exchange of step one long finished)
+    run(layers, x[rank * per:(rank + 1) * per].contiguous())
+    sync.wait()
+    torch.cuda.synchronize()
+    sums = torch.stack([l._weights.detach().double().sum() for l in layers])
+    lo, hi = sums.clone(), sums.clone()
+    dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+    dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+    no_grads = all(l._weights.grad is None for l in layers)
+    report("dp_peer_update_" + barrier, worst <= 1e-5 and bool((hi == lo).all()) and no_grads,
+           f"rel {worst:.2e}, checksum spread {float((hi - lo).abs().max()):.1e}")
+    sync.remove()
+    report("dp_peer_update_removed", all(l._weights.is_cuda and not hasattr(l, "_table_gradient_sink") for l in layers))
+
+
 def check_dp_sparse_exchange(rank, world, dev):
     from spiky_b200.data_parallel import exchange_sparse_gradients
     from spiky_b200.lut_layer import LUTLayer, SynapseMeta, GradientPolicy, GradientType
@@ -273,6 +320,8 @@ def main():
         check_dp_fc(rank, world, dev, True)
         check_dp_overlapped(rank, world, dev)
         check_dp_sharded_update(rank, world, dev)
+        check_dp_peer_update(rank, world, dev, "flags")
+        check_dp_peer_update(rank, world, dev, "collective")
         check_dp_sparse_exchange(rank, world, dev)
         check_sharded_inference(rank, world, dev)
         check_seq_concat(rank, world, dev)
