@@ -331,11 +331,12 @@ class SparseConvNetWorkload:
         params = [l._weights for l in self.layers]
         if self.sharded:
             from spiky_b200.data_parallel import ShardedTableUpdate
-            self.table_sync = ShardedTableUpdate(self.layers[:-1], self.LR)
+            self.table_sync = ShardedTableUpdate(self.layers[:-1], self.LR, batch_size=self.B,
+                                                 transport="peer" if self.sharded == "peer" else "collectives")
             params = params[-1:]
         if self.peer:
             from spiky_b200.data_parallel import PeerTableUpdate
-            self.table_sync = PeerTableUpdate(self.layers, self.LR)
+            self.table_sync = PeerTableUpdate(self.layers, self.LR, barrier=os.environ.get("BENCH_PEER_BARRIER", "flags"))
             params = []
         self.opt = None if (self.internal or not params) else torch.optim.SGD(params, lr=self.LR)
         x, labels = self.host_inputs(1000 + rank, self.B)
@@ -912,6 +913,7 @@ WORKLOADS = {
     "sparse_convnet": lambda batch=None: SparseConvNetWorkload(**_b(batch)),
     "sparse_convnet_internal": lambda batch=None: SparseConvNetWorkload(internal=True, **_b(batch)),
     "sparse_convnet_sharded": lambda batch=None: SparseConvNetWorkload(sharded=True, **_b(batch)),
+    "sparse_convnet_sharded_peer": lambda batch=None: SparseConvNetWorkload(sharded="peer", **_b(batch)),
     "sparse_convnet_peer": lambda batch=None: SparseConvNetWorkload(peer=True, **_b(batch)),
     "lut_layer": lambda batch=None: LutLayerWorkload(**_b(batch)),
     "lut_layer_b256": lambda batch=None: LutLayerWorkload(batch=batch or 256),
@@ -1014,6 +1016,8 @@ def _attach_data_parallel(wl, world):
 def _dp_strategy(wl):
     if getattr(wl, "peer", False):
         return "fused update over peer memory"
+    if getattr(wl, "sharded", False) == "peer":
+        return "sharded table update over peer memory"
     return "sharded table update" if getattr(wl, "sharded", False) else "gradient all-reduce"
 
 
@@ -1100,9 +1104,10 @@ def run_ours(args):
         finish_step(wl)
     dp_trial = None
     if world > 1 and args.workload == DEFAULT_WORKLOAD and args.dp == "auto":
-        # Three ways to keep the replicas' tables equal (same SGD step, spiky_b200/data_parallel.py): all-reduce the
-        # dense table gradients and run the optimiser; gather (index, output gradient) pairs and update a share of the
-        # tables in place; or reduce, update and distribute in one kernel over peer memory.  Which one is fastest
+        # Ways to keep the replicas' tables equal (same SGD step, spiky_b200/data_parallel.py): all-reduce the dense
+        # table gradients and run the optimiser; gather (index, output gradient) pairs and update a share of the tables
+        # in place (through NCCL all-gathers, or with plain stores into peer memory); or reduce the dense gradients,
+        # update and distribute in one kernel over peer memory.  Which one is fastest
         # depends on the number of ranks and on the interconnect: each is timed for a few steps and the fastest one
         # runs the measurement.
         def agreed(ms):
@@ -1118,7 +1123,7 @@ def run_ours(args):
 
         best = (agreed(timed_region(wl, 8, profile=False)[0]), wl, sync)
         dp_trial = {_dp_strategy(wl): best[0]}
-        for name in ("sparse_convnet_sharded", "sparse_convnet_peer"):
+        for name in ("sparse_convnet_sharded", "sparse_convnet_peer", "sparse_convnet_sharded_peer"):
             alt = WORKLOADS[name](args.batch)
             try:
                 alt.setup(device, rank)
@@ -1185,25 +1190,43 @@ def run_ours(args):
         pairs = sum(l.n_detectors() + 4 * l.n_outputs() for l in wl.layers[:-1]) * wl.B
         payload = (world - 1) * pairs + sum(p.numel() * p.element_size() for p in tables) * (world - 1) // world
         iso = []
-        shares = [torch.zeros((p.numel() + world - 1) // world, device=device) for p in tables]
-        outs = [torch.empty(world * s_.numel(), device=device) for s_ in shares]
-        for rep in range(4):
-            barrier()
-            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a.record()
-            for s_, o_ in zip(shares, outs):
-                dist.all_gather_into_tensor(o_, s_)
-            b.record()
-            torch.cuda.synchronize()
-            iso.append(a.elapsed_time(b))
-        del shares, outs
-        comm = {"ms_local": 0.0, "ms_isolated": min(iso[1:]), "payload": payload, "sharded": True}
+        if wl.sharded == "peer":
+            # the same stores and barriers with the update itself skipped (tables unchanged)
+            ts = wl.table_sync
+            ts.exchange_only = True
+            for rep in range(4):
+                barrier()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                for l in reversed(wl.layers[:-1]):
+                    ts._on_backward(l, *ts._plans[id(l)]["last"], wl.B)
+                ts.wait()
+                b.record()
+                torch.cuda.synchronize()
+                iso.append(a.elapsed_time(b))
+            ts.exchange_only = False
+        else:
+            shares = [torch.zeros((p.numel() + world - 1) // world, device=device) for p in tables]
+            outs = [torch.empty(world * s_.numel(), device=device) for s_ in shares]
+            for rep in range(4):
+                barrier()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                for s_, o_ in zip(shares, outs):
+                    dist.all_gather_into_tensor(o_, s_)
+                b.record()
+                torch.cuda.synchronize()
+                iso.append(a.elapsed_time(b))
+            del shares, outs
+        comm = {"ms_local": 0.0, "ms_isolated": min(iso[1:]), "payload": payload, "sharded": wl.sharded}
     elif world > 1 and getattr(wl, "peer", False):
-        # the fused update: per rank (G-1)/G of the tables come in over the links and the same amount goes out; timed
-        # as the step without exchange (every rank updates its own copy from its own gradient) and alone (learning
-        # rate 0: the same loads and stores, tables unchanged)
+        # the fused update: a rank fetches its slice of the other ranks' gradients ((G-1)/G of the tables come in) and
+        # stores its updated slice into their tables (as much goes out), while the others do the same with it: per GPU
+        # and direction 2 (G-1)/G of the table bytes cross the links, what a ring all-reduce moves.  Timed as the
+        # step without exchange (every rank updates its own copy from its own gradient) and alone (learning rate 0:
+        # the same loads and stores, tables unchanged)
         ts = wl.table_sync
-        payload = sum(l._weights.numel() * 4 for l in wl.layers) * (world - 1) // world
+        payload = 2 * sum(l._weights.numel() * 4 for l in wl.layers) * (world - 1) // world
         ts.paused = True
         for _ in range(2):
             wl.step_device()
@@ -1327,7 +1350,20 @@ def run_ours(args):
             "device_wait_errors": int(wait_errors),
             "clocks": clocks,
         }
-        if comm and comm.get("sharded"):
+        if comm and comm.get("sharded") == "peer":
+            gb = comm["payload"] / 1e9
+            line["comm"] = {
+                "exchange": "every rank stores its (table index, output gradient) pairs into every rank's arrays, updates "
+                            "its share of the tables in place for the whole batch and stores the share into every rank's "
+                            "tables: plain stores into peer memory (CUDA IPC, NVLink), barriers through flags in peer "
+                            "memory, overlapped with the backward pass",
+                "payload_bytes_per_step_per_direction": comm["payload"], "isolated_ms": ms_isolated,
+                "isolated_gbs_per_direction": gb / (ms_isolated / 1e3),
+                "frac_of_nvlink": gb / (ms_isolated / 1e3) / 900.0,
+                "frac_of_measured_peer_copy": gb / (ms_isolated / 1e3) / 770.0,
+                "isolated_what": "the stores and barriers of one step alone, update skipped",
+            }
+        elif comm and comm.get("sharded"):
             gb = comm["payload"] / 1e9
             line["comm"] = {
                 "exchange": "all-gather of (table index, output gradient) pairs, in-place update of a share of the tables, "
@@ -1339,9 +1375,10 @@ def run_ours(args):
         elif comm and comm.get("peer"):
             gb = comm["payload"] / 1e9
             line["comm"] = {
-                "exchange": "one kernel per layer over peer memory (CUDA IPC, NVLink): each rank reads its slice of every "
-                            "rank's table gradient, applies the SGD step and stores the new slice into every rank's "
-                            "tables; overlapped with the backward pass of the layers below",
+                "exchange": "one kernel per layer over peer memory (CUDA IPC, NVLink): each rank fetches its slice of every "
+                            "rank's table gradient (bulk copies into a shared-memory ring), applies the SGD step and "
+                            "stores the new slice into every rank's tables; overlapped with the backward pass of the "
+                            "layers below; barriers through flags in peer memory",
                 "payload_bytes_per_step_per_direction": comm["payload"], "ms_step_without_exchange": ms_local,
                 "exposed_ms": ms_dev - ms_local, "isolated_ms": ms_isolated,
                 "isolated_gbs_per_direction": gb / (ms_isolated / 1e3),
@@ -1416,8 +1453,8 @@ def main():
                     help="override the workload's per-GPU batch (batch sweeps; the default is the configuration's batch)")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU oracle timing (batch sweeps)")
     ap.add_argument("--dp", default="auto", choices=["auto", "keep"],
-                    help="data-parallel runs of the default workload: auto = time both exchange strategies for a few "
-                         "steps and measure the faster one; keep = the workload as named")
+                    help="data-parallel runs of the default workload: auto = time the exchange strategies for a few "
+                         "steps and measure the fastest one; keep = the workload as named")
     ap.add_argument("--no-secondary", action="store_true",
                     help="skip the character-transformer measurement that the default workload appends")
     ap.add_argument("--profile-only", action="store_true",

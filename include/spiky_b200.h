@@ -444,6 +444,9 @@ int lutb_fp32_gemm(int kind, int32_t m, int32_t n, int32_t k, const float *a, in
  * (fp32, summed in rank order, multiply and subtract rounded separately) and stores w into weights[r][e] of every
  * rank.  The kernel waits on nothing: the caller makes sure every rank's gradient is complete before any rank
  * launches it and that nobody reads the tables or rewrites the gradients before every rank's kernel has finished.
+ * lutb_peer_broadcast: copies `bytes` from `src` (this rank's memory) to dst[r] + dst_offset of every listed buffer
+ * (own pointers or mapped ones) with plain stores; 16-byte aligned offsets copy fastest.  Same ordering contract as
+ * lutb_peer_sgd_update.
  * lutb_peer_barrier: a barrier over the ranks on the stream, without the host: flags[r] is rank r's array of n_ranks
  * 64-bit flags in shareable memory (zero before the first use); every rank calls it with the same epoch, 1, 2, 3, ...
  * A kernel of one warp stores the epoch into this rank's slot of every rank's array (release at system scope, so what
@@ -457,6 +460,8 @@ int lutb_peer_alloc(size_t bytes, void **ptr_out, unsigned char *handle_out);
 int lutb_peer_free(void *ptr);
 int lutb_peer_open(const unsigned char *handle, void **ptr_out);
 int lutb_peer_close(void *ptr);
+int lutb_peer_broadcast(int32_t n_ranks, void *const *dst, int64_t dst_offset, const void *src, int64_t bytes,
+                        void *stream);
 int lutb_peer_barrier(int32_t n_ranks, int32_t rank, void *const *flags, uint64_t epoch, void *stream);
 int lutb_peer_sgd_update(int32_t n_ranks, int32_t rank, const float *const *grads, float *const *weights,
                          int64_t begin, int64_t end, float scale, void *stream);

@@ -77,7 +77,7 @@ static const char *const kKernelNames[K_COUNT] = {
     "check_positional", "concat_forward", "concat_backward", "concat_weight_update",
     "int8_gather",
     "product_hist", "product_hist_forward", "product_row_dots", "product_route", "product_hist_weight_grad",
-    "dense_to_sparse", "fp32_gemm", "peer_sgd_update", "peer_barrier",
+    "dense_to_sparse", "fp32_gemm", "peer_sgd_update", "peer_barrier", "peer_broadcast",
 };
 
 struct EventPair {

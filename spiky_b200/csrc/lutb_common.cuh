@@ -92,6 +92,7 @@ enum KernelId {
     K_FP32_GEMM,
     K_PEER_SGD_UPDATE,
     K_PEER_BARRIER,
+    K_PEER_BROADCAST,
     K_COUNT
 };
 

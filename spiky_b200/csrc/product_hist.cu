@@ -75,7 +75,11 @@ __global__ void __launch_bounds__(512) product_hist_kernel(const float *__restri
 // or two per pair to at most S * 2 * Nc + (S-1) * Npe); without it only the query token's cells are pre-reduced
 // per warp.
 // --------------------------------------------------------------------------------------------
-template <bool SMEM_ACC>
+// MAXM > 0: the pair loop keeps the address plan of the detector's mixed anchors (at most MAXM) in registers
+// (product_pairs.cuh, MixedPlan); 0: plain eval_pair.  The plan costs about 5 registers per anchor: it pays where the
+// block's shared memory already limits an SM to one block (tables of 1024 rows and more: 257 against 286 ms per step on
+// the 2048-token configuration) and loses where it takes the second block away (256-row tables: 5.1 against 3.5 ms).
+template <bool SMEM_ACC, int MAXM>
 __global__ void __launch_bounds__(512) product_route_kernel(const float *__restrict__ x1, const float *__restrict__ x2,
                                                            const float *__restrict__ pe,
                                                            const int32_t *__restrict__ anchors,
@@ -104,7 +108,14 @@ __global__ void __launch_bounds__(512) product_route_kernel(const float *__restr
         for (int w = threadIdx.x; w < S * ends + (S - 1) * npe; w += blockDim.x) tacc[w] = 0.f;
         __syncthreads();
     }
+    MixedPlan<MAXM == 0 ? 1 : MAXM> mp;
+    if (MAXM > 0) mp.load(st);
     for (int j = 1 + warp; j < S; j += nwarps) {
+        QueryPart qp{0u, 0.f};
+        if (MAXM > 0) {
+            mp.set_query(st, j);
+            qp = query_part(st, j);
+        }
         const float *qrow = Q + (size_t)t * q_det_stride + (size_t)(bl * S + j) * q_row_stride;
         for (int r = lane * 4; r < T; r += 128)
             *reinterpret_cast<float4 *>(q_s + r) = __ldcs(reinterpret_cast<const float4 *>(qrow + r));
@@ -114,7 +125,8 @@ __global__ void __launch_bounds__(512) product_route_kernel(const float *__restr
             const int i = i0 + lane;
             if (i >= j) continue;
             int k; float d;
-            const int32_t li = eval_pair<true>(st, n_anchors, i, j, cmp_eps, k, d);
+            const int32_t li = MAXM > 0 ? eval_pair_planned<true, (MAXM == 0 ? 1 : MAXM)>(st, mp, qp, i, j, cmp_eps, k, d)
+                                        : eval_pair<true>(st, n_anchors, i, j, cmp_eps, k, d);
             if (k < 0) continue;
             const double du = surrogate_up(d) * (double)(q_s[li] - q_s[li ^ (1 << k)]);
             if (!(fabs(du) > kEps)) continue;
@@ -451,20 +463,16 @@ static int launch_hist(const ProductCall &c, const HistPlan &p, int64_t b0, int6
     const size_t T = (size_t)1 << cfg->n_anchors;
     const int warps = pair_block_warps(c, T);
     const size_t smem = stage_bytes(c, T, warps);
-    if (smem > 48 * 1024) {
-        LUTB_CUDA(cudaFuncSetAttribute(product_hist_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        LUTB_CUDA(cudaFuncSetAttribute(product_hist_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    }
     dim3 grid((unsigned)cfg->n_detectors, (unsigned)n);
     KernelScope scope(K_PRODUCT_HIST, stream);
-    if (p.tc)
-        product_hist_kernel<true><<<grid, warps * 32, smem, stream>>>(c.x1, c.x2, c.pe, c.anchors, p.H, b0, n * c.S, c.S, c.e1, c.e2,
-                                                               cfg->pos_dim, cfg->n_detectors, cfg->n_anchors,
-                                                               cfg->sliced_product, cfg->cmp_eps);
-    else
-        product_hist_kernel<false><<<grid, warps * 32, smem, stream>>>(c.x1, c.x2, c.pe, c.anchors, p.H, b0, n * c.S, c.S, c.e1, c.e2,
-                                                                cfg->pos_dim, cfg->n_detectors, cfg->n_anchors,
-                                                                cfg->sliced_product, cfg->cmp_eps);
+    auto launch = [&](auto kern) -> int {
+        if (smem > 48 * 1024) LUTB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        kern<<<grid, warps * 32, smem, stream>>>(c.x1, c.x2, c.pe, c.anchors, p.H, b0, n * c.S, c.S, c.e1, c.e2, cfg->pos_dim,
+                                                 cfg->n_detectors, cfg->n_anchors, cfg->sliced_product, cfg->cmp_eps);
+        return LUTB_OK;
+    };
+    const int rc = p.tc ? launch(product_hist_kernel<true>) : launch(product_hist_kernel<false>);
+    if (rc) return rc;
     LUTB_LAUNCH_CHECK();
     return LUTB_OK;
 }
@@ -515,10 +523,6 @@ int launch_product_hist_backward(const ProductCall &c, const float *weights, con
     // block-level accumulators only while two blocks still fit an SM
     const bool smem_acc = route_smem + acc_bytes <= 100 * 1024;
     if (smem_acc) route_smem += acc_bytes;
-    if (route_smem > 48 * 1024) {
-        if (smem_acc) LUTB_CUDA(cudaFuncSetAttribute(product_route_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)route_smem));
-        else LUTB_CUDA(cudaFuncSetAttribute(product_route_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)route_smem));
-    }
     // In-place SGD reads unmodified tables for every input gradient: with more than one chunk the table update
     // runs as a second sweep over the chunks.
     const bool second_sweep = in_place && p.chunk < c.batch;
@@ -569,14 +573,20 @@ int launch_product_hist_backward(const ProductCall &c, const float *weights, con
             const int64_t q_row_stride = p.tc ? (int64_t)Nt * T : T, q_det_stride = p.tc ? T : rows * T;
             dim3 grid((unsigned)Nt, (unsigned)n);
             KernelScope scope(K_PRODUCT_ROUTE, stream);
-            if (smem_acc)
-                product_route_kernel<true><<<grid, route_warps * 32, route_smem, stream>>>(c.x1, c.x2, c.pe, c.anchors, p.Q, dX1, dX2, dPE, b0,
-                                                                              q_row_stride, q_det_stride, c.S, c.e1, c.e2, cfg->pos_dim, Nt,
-                                                                              cfg->n_anchors, cfg->sliced_product, cfg->cmp_eps);
-            else
-                product_route_kernel<false><<<grid, route_warps * 32, route_smem, stream>>>(c.x1, c.x2, c.pe, c.anchors, p.Q, dX1, dX2, dPE, b0,
-                                                                               q_row_stride, q_det_stride, c.S, c.e1, c.e2, cfg->pos_dim, Nt,
-                                                                               cfg->n_anchors, cfg->sliced_product, cfg->cmp_eps);
+            auto launch = [&](auto kern) -> int {
+                if (route_smem > 48 * 1024)
+                    LUTB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)route_smem));
+                kern<<<grid, route_warps * 32, route_smem, stream>>>(c.x1, c.x2, c.pe, c.anchors, p.Q, dX1, dX2, dPE, b0, q_row_stride,
+                                                                     q_det_stride, c.S, c.e1, c.e2, cfg->pos_dim, Nt, cfg->n_anchors,
+                                                                     cfg->sliced_product, cfg->cmp_eps);
+                return LUTB_OK;
+            };
+            const int na = cfg->n_anchors;
+            if (smem_acc) rc = na <= 8 ? launch(product_route_kernel<true, 0>) : na <= 12 ? launch(product_route_kernel<true, 12>)
+                                                                                          : launch(product_route_kernel<true, 16>);
+            else rc = na <= 8 ? launch(product_route_kernel<false, 0>) : na <= 12 ? launch(product_route_kernel<false, 12>)
+                                                                                   : launch(product_route_kernel<false, 16>);
+            if (rc) return rc;
             LUTB_LAUNCH_CHECK();
         }
         if (!second_sweep) {

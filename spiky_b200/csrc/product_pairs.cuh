@@ -28,6 +28,10 @@ struct PairStage {
     // offsets from U (row offset of the source added per pair)
     int4 *mixed;     // [kMaxPairs]
     int n_mixed;
+    // the same anchors as address arithmetic (MixedPlan below): end e of mixed anchor m reads
+    // U[i * lin[m].x/.y + j * jmul + off] with {jmul, off} = jplan[2 * m + e]
+    int2 *lin;       // [kMaxPairs]  i-multipliers of the two ends
+    int2 *jplan;     // [2 * kMaxPairs]
     // pair-independent anchors, per token / distance: bits | (first-min anchor + 1) << 16, and that delta
     uint32_t *tokI, *tokJ, *posP;
     float *tokId, *tokJd, *posPd;
@@ -79,10 +83,78 @@ __device__ __forceinline__ int32_t eval_pair(const PairStage &st, int /*n_anchor
     return li;
 }
 
+// The mixed anchors of a detector held in registers for one query j: end e of anchor m reads U[i * imul + base],
+// base = j * jmul + off folded per query (a source row is i, j or j - i - 1, so the address is linear in i).  MAXM
+// bounds the unrolled loops; anchors beyond n are skipped by a block-uniform test.
+template <int MAXM>
+struct MixedPlan {
+    int n;
+    int k[MAXM];
+    int imul1[MAXM], imul2[MAXM];
+    int base1[MAXM], base2[MAXM];
+
+    __device__ __forceinline__ void load(const PairStage &st) {
+        n = st.n_mixed;
+#pragma unroll
+        for (int m = 0; m < MAXM; m++) {
+            k[m] = 0; imul1[m] = imul2[m] = 0; base1[m] = base2[m] = 0;
+            if (m < n) {
+                k[m] = st.mixed[m].x;
+                const int2 l = st.lin[m];
+                imul1[m] = l.x;
+                imul2[m] = l.y;
+            }
+        }
+    }
+    __device__ __forceinline__ void set_query(const PairStage &st, int j) {
+#pragma unroll
+        for (int m = 0; m < MAXM; m++)
+            if (m < n) {
+                const int2 p1 = st.jplan[2 * m], p2 = st.jplan[2 * m + 1];
+                base1[m] = j * p1.x + p1.y;
+                base2[m] = j * p2.x + p2.y;
+            }
+    }
+};
+
+// Per-query part of a pair: the query token's pair-independent anchors.
+struct QueryPart {
+    uint32_t word;
+    float delta;
+};
+__device__ __forceinline__ QueryPart query_part(const PairStage &st, int j) { return QueryPart{st.tokJ[j], st.tokJd[j]}; }
+
+// eval_pair with the mixed anchors taken from a MixedPlan and the query token's part loaded once per query: the same
+// comparisons on the same operands (the first-minimum rule of `consider` does not depend on the evaluation order).
+template <bool TRACK, int MAXM>
+__device__ __forceinline__ int32_t eval_pair_planned(const PairStage &st, const MixedPlan<MAXM> &mp, const QueryPart &qp,
+                                                     int i, int j, float cmp_eps, int &kmin, float &dmin) {
+    const int dist = j - i - 1;
+    const uint32_t pi = st.tokI[i], pp = st.posP[dist];
+    int32_t li = (int32_t)((pi | qp.word | pp) & 0xffffu);
+    float md = kFltMax;
+    int mk = -1;
+    if (TRACK) {
+        consider(md, mk, st.tokId[i], (int)(pi >> 16) - 1);
+        consider(md, mk, qp.delta, (int)(qp.word >> 16) - 1);
+        consider(md, mk, st.posPd[dist], (int)(pp >> 16) - 1);
+    }
+#pragma unroll
+    for (int m = 0; m < MAXM; m++) {
+        if (m < mp.n) {
+            const float d = __fsub_rn(st.U[i * mp.imul1[m] + mp.base1[m]], st.U[i * mp.imul2[m] + mp.base2[m]]);
+            if (greater_than_zero(d, cmp_eps)) li |= 1 << mp.k[m];
+            if (TRACK) consider(md, mk, d, mp.k[m]);
+        }
+    }
+    if (TRACK) { kmin = mk; dmin = md; }
+    return li;
+}
+
 // ints of shared memory stage_pairs lays out in front of the per-warp scratch area
 inline size_t pair_stage_floats(int S, int n_anchors, int npe) {
     // anchor metadata + U + PE + per-token / per-distance tables, plus slack for 16-byte alignment
-    return 8 * kMaxPairs + (size_t)S * ((2 * n_anchors) | 1) + (size_t)(S > 1 ? S - 1 : 0) * (npe | 1) + 6 * (size_t)S + 12;
+    return 14 * kMaxPairs + (size_t)S * ((2 * n_anchors) | 1) + (size_t)(S > 1 ? S - 1 : 0) * (npe | 1) + 6 * (size_t)S + 12;
 }
 
 __device__ __forceinline__ void stage_pairs(PairStage &st, float *smem, const float *__restrict__ x1b,
@@ -94,7 +166,9 @@ __device__ __forceinline__ void stage_pairs(PairStage &st, float *smem, const fl
     st.mixed = reinterpret_cast<int4 *>(smem);
     st.comp = reinterpret_cast<int *>(smem) + 4 * kMaxPairs;
     st.elem = st.comp + 2 * kMaxPairs;
-    st.U = smem + 8 * kMaxPairs;
+    st.lin = reinterpret_cast<int2 *>(smem + 8 * kMaxPairs);
+    st.jplan = reinterpret_cast<int2 *>(smem + 10 * kMaxPairs);
+    st.U = smem + 14 * kMaxPairs;
     st.PE = st.U + S * st.ustride;
     float *p = st.PE + (S - 1) * st.pstride;
     st.tokI = reinterpret_cast<uint32_t *>(p); p += S;
@@ -120,6 +194,16 @@ __device__ __forceinline__ void stage_pairs(PairStage &st, float *smem, const fl
             if (c1 == 3 || c2 == 3 || c1 == c2) continue;
             const int col1 = c1 == 2 ? pe_col + st.elem[2 * k] : 2 * k;
             const int col2 = c2 == 2 ? pe_col + st.elem[2 * k + 1] : 2 * k + 1;
+            // U[(row of the source) * stride + col] with row = i, j or j - i - 1: linear in i and j
+            const int cs[2] = {c1, c2}, cols[2] = {col1, col2};
+            int imul[2];
+            for (int e = 0; e < 2; e++) {
+                const int a = cs[e] == 0 ? st.ustride : 0, b = cs[e] == 1 ? st.ustride : 0;
+                const int c = cs[e] == 2 ? st.pstride : 0;
+                imul[e] = a - c;
+                st.jplan[2 * nm + e] = make_int2(b + c, cols[e] - c);
+            }
+            st.lin[nm] = make_int2(imul[0], imul[1]);
             st.mixed[nm++] = make_int4(k, c1 | (c2 << 2), col1, col2);
         }
         n_mixed_s = nm;

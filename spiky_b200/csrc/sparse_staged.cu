@@ -24,6 +24,7 @@
 #include <cstdlib>
 #include <cstring>
 
+#include "mbarrier.cuh"
 #include "sparse_view.cuh"
 
 namespace lutb {
@@ -36,7 +37,6 @@ constexpr int kMaxStages = 8;
 constexpr int kMinStages = 3;
 constexpr int kFwdTile = 4;         // detectors whose table indices a lane holds at a time (forward)
 constexpr int kDxTile = 2;          // same for the input gradient (it also holds min_k and min_delta)
-constexpr long long kWaitLimitCycles = 2000ll * 1000ll * 1000ll;   // about a second of SM clock
 
 __device__ int g_wait_errors = 0;
 
@@ -52,47 +52,6 @@ struct StagedArgs {
     int n_stages;
     int forward;   // 1: forward kernel, 0: input gradient (the two weigh tables differently when splitting the work)
 };
-
-// ------------------------------------------------------------------------------------------ PTX wrappers
-__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-// Bounded wait for the phase with the given parity; false when the limit ran out.  The bound is counted on the SM's
-// own cycle counter: reading %globaltimer costs microseconds, and a wait that is not satisfied at once would pay
-// that on every poll.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-    if (mbar_try_wait(bar, parity)) return true;
-    const long long t0 = clock64();
-    while (!mbar_try_wait(bar, parity)) {
-        if (clock64() - t0 > kWaitLimitCycles) return false;
-    }
-    return true;
-}
-// One contiguous global -> shared copy; both addresses 16-byte aligned, bytes a multiple of 16.
-__device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
-                 "l"(src), "r"(bytes), "r"(bar)
-                 : "memory");
-}
 
 // ------------------------------------------------------------------------------------------ work order
 // Linear order of the work: sample tile major, then chunk, then detector slot (kChunkSlots per chunk; slots beyond a
@@ -418,8 +377,7 @@ __device__ __forceinline__ Ring setup_ring(const StagedArgs &a, unsigned char *s
             mbar_init(ring.empty0 + 8 * s, kConsumerWarps);   // one arrive per consumer warp
         }
         *ring.abort_flag = 0;
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        fence_barrier_init();
     }
     __syncthreads();
     return ring;

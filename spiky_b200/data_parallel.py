@@ -263,13 +263,29 @@ class ShardedTableUpdate:
     The exchange and the update of a layer run on a side stream and overlap the backward pass of the layers below.
     """
 
-    def __init__(self, layers, lr, group=None, average=True, weight_gather="padded"):
+    def __init__(self, layers, lr, group=None, average=True, weight_gather="padded", transport="collectives",
+                 batch_size=None, barrier="flags"):
         from .lut_layer import GradientType, LUTLayerBasic
 
         # how the updated shares travel: "padded" = one equal-size all-gather through a staging buffer (shares are
         # padded to the largest), "uneven" = all-gather on views of the tables (grouped broadcasts under NCCL)
         assert weight_gather in ("padded", "uneven")
         self.weight_gather = weight_gather
+        # transport "collectives": all-gathers of the process group.  "peer" (one node, CUDA): the tables and the
+        # gathered (index, output gradient) arrays live in buffers every rank has mapped; a rank stores its pairs into
+        # every rank's arrays and, after its update, its share of the tables into every rank's tables
+        # (lutb_peer_broadcast: plain posted stores over NVLink, no staging, no collective kernels), with
+        # lutb_peer_barrier between the phases.  Needs the per-rank batch size up front (the arrays are allocated
+        # once, collectively).
+        assert transport in ("collectives", "peer") and barrier in ("flags", "collective")
+        self.transport = transport
+        self.barrier = barrier
+        self.batch_size = batch_size
+        self._space = None
+        self._dirty = False
+        # True: the pairs and the table shares still travel but the update itself is skipped (tables unchanged); for
+        # timing the exchange alone
+        self.exchange_only = False
         self.group = group
         self.lr = lr
         self.enabled = dist.is_available() and dist.is_initialized()
@@ -298,6 +314,67 @@ class ShardedTableUpdate:
                 cuts=cuts, wcuts=[int(bounds[c]) for c in cuts],
                 idx_dtype=torch.uint8 if rows <= 256 else (torch.int16 if rows <= 65536 else torch.int32))
             layer._table_update_hook = self._on_backward
+        if self.transport == "peer" and self.world > 1:
+            self._setup_peer()
+
+    def _setup_peer(self):
+        if not self.batch_size:
+            raise ValueError("transport='peer' needs batch_size (samples per rank and step)")
+        device = self.layers[0]._weights.device
+        if device.type != "cuda":
+            raise ValueError("transport='peer' needs the tables on a CUDA device")
+        W, B = self.world, int(self.batch_size)
+        sizes = {}
+        for li, layer in enumerate(self.layers):
+            plan = self._plans[id(layer)]
+            item = torch.empty(0, dtype=plan["idx_dtype"]).element_size()
+            sizes[f"w{li}"] = 4 * ((layer._weights.numel() + 3) // 4 * 4)
+            sizes[f"i{li}"] = W * B * layer.n_detectors() * item
+            sizes[f"d{li}"] = W * B * layer.n_outputs() * 4
+        self._space = _PeerSpace(sizes, device, self.group, "ShardedTableUpdate")
+        self._side = torch.cuda.Stream(device=device)
+        for li, layer in enumerate(self.layers):
+            plan = self._plans[id(layer)]
+            shared = self._space.tensor(f"w{li}", torch.float32, layer._weights.numel())
+            shared.copy_(layer._weights.detach())
+            layer._weights.data = shared
+            plan["li"] = li
+            plan["idx_all"] = self._space.tensor(f"i{li}", plan["idx_dtype"])
+            plan["dY_all"] = self._space.tensor(f"d{li}", torch.float32)
+        torch.cuda.synchronize(device)
+        dist.barrier(group=self.group)  # every rank's tables are in place before anyone stores into them
+
+    def _on_backward_peer(self, layer, idx, dY, batch):
+        from . import _native
+        plan, space = self._plans[id(layer)], self._space
+        W, li = self.world, plan["li"]
+        if batch != self.batch_size:
+            raise ValueError(f"transport='peer' was set up for {self.batch_size} samples per rank, got {batch}")
+        main = torch.cuda.current_stream(idx.device)
+        self._side.wait_stream(main)  # the input gradient of this layer (it reads the tables) and dY are ordered before
+        with torch.cuda.stream(self._side):
+            side = self._side.cuda_stream
+            idx_all, dY_all = plan["idx_all"], plan["dY_all"]
+            n_i, n_d = idx.numel(), dY.numel()
+            own = idx_all[self.rank * n_i:(self.rank + 1) * n_i]
+            own.copy_(idx)   # narrowing copy: the indices travel as uint8 / int16 when the table allows it
+            _native.peer_broadcast(space.others(f"i{li}"), self.rank * n_i * own.element_size(), own.data_ptr(),
+                                   n_i * own.element_size(), side)
+            dYc = dY.contiguous()
+            _native.peer_broadcast(space.ptrs[f"d{li}"], self.rank * n_d * 4, dYc.data_ptr(), n_d * 4, side)
+            idx.record_stream(self._side)
+            dYc.record_stream(self._side)
+            plan["last"] = (idx, dYc)   # kept for callers that time the exchange alone
+            # every rank's pairs have landed everywhere, and no rank still reads these tables
+            space.barrier(self._side, self.barrier)
+            c0, c1 = plan["cuts"][self.rank], plan["cuts"][self.rank + 1]
+            if not self.exchange_only:
+                self._apply(layer, W * batch, dY_all, idx_all, -self._learning_rate() / self.scale_div, c0, c1)
+            lo, hi = plan["wcuts"][self.rank], plan["wcuts"][self.rank + 1]
+            if hi > lo:
+                _native.peer_broadcast(space.others(f"w{li}"), lo * 4, space.ptrs[f"w{li}"][self.rank] + lo * 4,
+                                       (hi - lo) * 4, side)
+        self._dirty = True
 
     def _learning_rate(self):
         return float(self.lr() if callable(self.lr) else self.lr)
@@ -313,6 +390,8 @@ class ShardedTableUpdate:
             # nothing to exchange: in-place SGD on all chunks, on the current stream
             self._apply(layer, batch, dY, idx, -self._learning_rate() / self.scale_div, 0, plan["cuts"][1])
             return
+        if self._space is not None:
+            return self._on_backward_peer(layer, idx, dY, batch)
         on_gpu = idx.is_cuda
         if on_gpu and self._side is None:
             self._side = torch.cuda.Stream(device=idx.device)
@@ -377,13 +456,32 @@ class ShardedTableUpdate:
         for w in self._pending:
             w.wait()
         self._pending = []
+        if self._space is not None and self._dirty:
+            # every rank's share has landed in this rank's tables (and nobody still reads the gathered pairs)
+            self._space.barrier(self._side, self.barrier)
+            self._dirty = False
         if self._side is not None:
             torch.cuda.current_stream(self._side.device).wait_stream(self._side)
 
     def remove(self):
+        """Detaches from the layers; with the peer transport also moves the tables back into ordinary device memory
+        and releases the shared buffers (collective)."""
+        if self._space is not None:
+            self.wait()
         for layer in self.layers:
             if getattr(layer, "_table_update_hook", None) is not None:
                 del layer._table_update_hook
+        if self._space is not None:
+            device = self._space.device
+            for layer in self.layers:
+                layer._weights.data = layer._weights.data.clone()
+            for plan in self._plans.values():
+                plan.pop("idx_all", None)
+                plan.pop("dY_all", None)
+            torch.cuda.synchronize(device)
+            dist.barrier(group=self.group)  # nobody still reads a buffer that is about to go
+            self._space.release()
+            self._space = None
 
 
 class _DeviceSpan:
@@ -392,6 +490,114 @@ class _DeviceSpan:
     def __init__(self, ptr, numel):
         self.__cuda_array_interface__ = {"shape": (int(numel),), "typestr": "<f4", "data": (int(ptr), False),
                                          "strides": None, "version": 2}
+
+
+class _PeerSpace:
+    """Named device buffers of this rank that every other rank of the group (same node) has mapped, plus the flags of
+    the stream-ordered barrier between them.  ``sizes``: ``{name: bytes}``, the same on every rank.  Construction and
+    ``release`` are collective.  A rank that fails to allocate or to map tells the others through the same
+    collectives, so that all ranks raise ``RuntimeError`` together instead of one leaving the others waiting."""
+
+    def __init__(self, sizes, device, group=None, what="peer memory"):
+        from . import _native
+
+        self._native = _native
+        self.group = group
+        self.device = device
+        self.what = what
+        enabled = dist.is_available() and dist.is_initialized()
+        self.world = dist.get_world_size(group) if enabled else 1
+        self.rank = dist.get_rank(group) if enabled else 0
+        if self.world > _native.MAX_PEER_RANKS:
+            raise ValueError(f"{what} supports up to {_native.MAX_PEER_RANKS} ranks")
+        self.names = list(sizes)
+        self.sizes = dict(sizes)
+        self._owned, self._mapped = [], []
+        self._epoch = 0
+        self._token = None
+        own, handles, error = {}, {}, None
+        try:
+            with torch.cuda.device(device):
+                # the barrier's flags: one 64-bit slot per rank, zero before the first epoch
+                own["_flags"], handles["_flags"] = _native.peer_alloc(8 * _native.MAX_PEER_RANKS)
+                self._owned.append(own["_flags"])
+                torch.as_tensor(_DeviceSpan(own["_flags"], 2 * _native.MAX_PEER_RANKS), device=device).zero_()
+                for name in self.names:
+                    own[name], handles[name] = _native.peer_alloc(max(16, (int(sizes[name]) + 15) // 16 * 16))
+                    self._owned.append(own[name])
+        except RuntimeError as e:
+            error = str(e)
+        everyone = self._agree((error, handles), "allocating shareable device memory")
+        # ptrs[name][r]: rank r's buffer as this process addresses it
+        self.ptrs = {name: [None] * self.world for name in ["_flags"] + self.names}
+        error = None
+        try:
+            with torch.cuda.device(device):
+                for r in range(self.world):
+                    for name in self.ptrs:
+                        if r == self.rank:
+                            self.ptrs[name][r] = own[name]
+                        else:
+                            self.ptrs[name][r] = _native.peer_open(everyone[r][1][name])
+                            self._mapped.append(self.ptrs[name][r])
+        except RuntimeError as e:
+            error = str(e)
+        self._agree((error, None), "mapping the other ranks' buffers")   # also: every rank has mapped every buffer
+        torch.cuda.synchronize(device)
+
+    def _agree(self, mine, doing):
+        everyone = [mine]
+        if self.world > 1:
+            everyone = [None] * self.world
+            dist.all_gather_object(everyone, mine, group=self.group)
+        errors = [f"rank {r}: {e[0]}" for r, e in enumerate(everyone) if e[0]]
+        if errors:
+            self.release()
+            raise RuntimeError(f"{self.what}: {doing} failed ({errors[0]})")
+        return everyone
+
+    def tensor(self, name, dtype=torch.float32, numel=None):
+        """This rank's buffer ``name`` as a flat tensor (no copy)."""
+        item = torch.empty(0, dtype=dtype).element_size()
+        n = self.sizes[name] // item if numel is None else int(numel)
+        assert n * item <= max(16, (self.sizes[name] + 15) // 16 * 16)
+        if dtype == torch.float32:
+            t = torch.as_tensor(_DeviceSpan(self.ptrs[name][self.rank], n), device=self.device)
+        else:
+            t = torch.as_tensor(_DeviceSpan(self.ptrs[name][self.rank], (n * item + 3) // 4), device=self.device)
+            t = t.view(torch.uint8)[:n * item].view(dtype)
+        assert t.data_ptr() == self.ptrs[name][self.rank]
+        return t
+
+    def others(self, name):
+        """The other ranks' buffers ``name`` (mapped pointers)."""
+        return [p for r, p in enumerate(self.ptrs[name]) if r != self.rank]
+
+    def barrier(self, stream, kind="flags"):
+        """Barrier over the ranks on ``stream`` (the host does not block): "flags" = lutb_peer_barrier, a one-warp
+        kernel over flags in peer memory whose wait is bounded (a rank that is seconds late is counted by
+        lutb_device_wait_errors and not waited for); "collective" = a one-element all-reduce of the process group."""
+        if self.world == 1:
+            return
+        if kind == "flags":
+            self._epoch += 1
+            self._native.peer_barrier(self.rank, self.ptrs["_flags"], self._epoch, stream.cuda_stream)
+        else:
+            if self._token is None:
+                self._token = torch.zeros(1, dtype=torch.float32, device=self.device)
+            with torch.cuda.stream(stream):
+                dist.all_reduce(self._token, group=self.group, async_op=True).wait()
+
+    def release(self):
+        """Unmaps the other ranks' buffers, then frees this rank's (collective when there are several ranks)."""
+        with torch.cuda.device(self.device):
+            for p in self._mapped:
+                self._native.peer_close(p)
+            if self.world > 1:
+                dist.barrier(group=self.group)  # all mappings closed before the owners free
+            for p in self._owned:
+                self._native.peer_free(p)
+        self._mapped, self._owned = [], []
 
 
 class PeerTableUpdate:
@@ -424,7 +630,6 @@ class PeerTableUpdate:
         # lutb_device_wait_errors and not waited for), "collective" = a one-element all-reduce of the process group
         assert barrier in ("flags", "collective")
         self.barrier = barrier
-        self._epoch = 0
         self._native = _native
         self.group = group
         self.lr = lr
@@ -441,8 +646,6 @@ class PeerTableUpdate:
         # the exchange costs
         self.paused = False
         self._state = {}
-        self._owned = []    # pointers from peer_alloc
-        self._mapped = []   # pointers from peer_open
         for layer in self.layers:
             if not isinstance(layer, LUTLayerBasic) or layer._sequence_length != 1:
                 raise ValueError("PeerTableUpdate handles non-sequence LUT layers")
@@ -451,106 +654,36 @@ class PeerTableUpdate:
             if not layer._weights.is_cuda or layer._weights.dtype != torch.float32:
                 raise ValueError("PeerTableUpdate needs fp32 tables on a CUDA device")
         device = self.layers[0]._weights.device
-        # allocate, exchange the handles, map the other ranks' buffers.  A rank that fails tells the others through
-        # the same collectives, so that all ranks raise together instead of one leaving the others waiting.
-        handles, spans, error = [], [], None
-        f_ptr = f_handle = None
-        try:
-            with torch.cuda.device(device):
-                if self.world > 1:
-                    # the barrier's flags: one 64-bit slot per rank, zero before the first epoch
-                    f_ptr, f_handle = _native.peer_alloc(8 * _native.MAX_PEER_RANKS)
-                    self._owned.append(f_ptr)
-                    torch.as_tensor(_DeviceSpan(f_ptr, 2 * _native.MAX_PEER_RANKS), device=device).zero_()
-                for layer in self.layers:
-                    n = layer._weights.numel()
-                    nbytes = 4 * ((n + 3) // 4 * 4)
-                    g_ptr, g_handle = _native.peer_alloc(nbytes)
-                    self._owned.append(g_ptr)
-                    w_ptr, w_handle = _native.peer_alloc(nbytes)
-                    self._owned.append(w_ptr)
-                    handles.append((g_handle, w_handle))
-                    spans.append((g_ptr, w_ptr, n))
-        except RuntimeError as e:
-            error = str(e)
-        everyone = self._agree((error, handles, f_handle), "allocating shareable device memory")
-        g_all = [[g for g, _, _ in spans]]
-        w_all = [[w for _, w, _ in spans]]
+        sizes = {}
+        for li, layer in enumerate(self.layers):
+            nbytes = 4 * ((layer._weights.numel() + 3) // 4 * 4)
+            sizes[f"g{li}"] = nbytes
+            sizes[f"w{li}"] = nbytes
+        self._space = _PeerSpace(sizes, device, group, "PeerTableUpdate")
         if self.world > 1:
-            g_all, w_all, error = [], [], None
-            self._flag_ptrs = []
-            try:
-                with torch.cuda.device(device):
-                    for r in range(self.world):
-                        if r == self.rank:
-                            g_all.append([g for g, _, _ in spans])
-                            w_all.append([w for _, w, _ in spans])
-                            self._flag_ptrs.append(f_ptr)
-                            continue
-                        self._flag_ptrs.append(_native.peer_open(everyone[r][2]))
-                        self._mapped.append(self._flag_ptrs[-1])
-                        gs, ws = [], []
-                        for g_handle, w_handle in everyone[r][1]:
-                            gs.append(_native.peer_open(g_handle))
-                            self._mapped.append(gs[-1])
-                            ws.append(_native.peer_open(w_handle))
-                            self._mapped.append(ws[-1])
-                        g_all.append(gs)
-                        w_all.append(ws)
-            except RuntimeError as e:
-                error = str(e)
-            self._agree((error, None), "mapping the other ranks' buffers")  # also: everyone has mapped everything
-            self._token = torch.zeros(1, dtype=torch.float32, device=device)
             self._side = torch.cuda.Stream(device=device)
-        for li, (layer, (g_ptr, w_ptr, n)) in enumerate(zip(self.layers, spans)):
-            grad = torch.as_tensor(_DeviceSpan(g_ptr, n), device=device)
-            shared = torch.as_tensor(_DeviceSpan(w_ptr, n), device=device)
-            assert grad.data_ptr() == g_ptr and shared.data_ptr() == w_ptr
+        for li, layer in enumerate(self.layers):
+            n = layer._weights.numel()
+            grad = self._space.tensor(f"g{li}", torch.float32, n)
+            shared = self._space.tensor(f"w{li}", torch.float32, n)
             grad.zero_()
             shared.copy_(layer._weights.detach())
             layer._weights.data = shared
             # slice r of the tables belongs to rank r; cuts on 16-byte boundaries
             cuts = [(n * r // self.world) // 4 * 4 for r in range(self.world)] + [n]
-            self._state[id(layer)] = dict(grad=grad, cuts=cuts, g_ptrs=[g_all[r][li] for r in range(self.world)],
-                                          w_ptrs=[w_all[r][li] for r in range(self.world)])
+            self._state[id(layer)] = dict(grad=grad, cuts=cuts, g_ptrs=self._space.ptrs[f"g{li}"],
+                                          w_ptrs=self._space.ptrs[f"w{li}"])
             layer._table_gradient_sink = self
         torch.cuda.synchronize(device)
         if self.world > 1:
             dist.barrier(group=group)  # every rank's tables are in place before anyone's kernel may store into them
 
-    def _agree(self, mine, what):
-        """All-gathers (error or None, payload); raises on every rank when any rank reported an error."""
-        everyone = [mine]
-        if self.world > 1:
-            everyone = [None] * self.world
-            dist.all_gather_object(everyone, mine, group=self.group)
-        errors = [f"rank {r}: {e[0]}" for r, e in enumerate(everyone) if e[0]]
-        if errors:
-            self._release()
-            raise RuntimeError(f"PeerTableUpdate: {what} failed ({errors[0]})")
-        return everyone
-
-    def _release(self):
-        """Unmaps the other ranks' buffers, then frees this rank's (collective when there are several ranks)."""
-        for p in self._mapped:
-            self._native.peer_close(p)
-        if self.world > 1:
-            dist.barrier(group=self.group)  # all mappings closed before the owners free
-        for p in self._owned:
-            self._native.peer_free(p)
-        self._mapped, self._owned = [], []
-
     def _learning_rate(self):
         return float(self.lr() if callable(self.lr) else self.lr)
 
     def _rendezvous(self):
-        """Barrier over the ranks on the current stream (the host does not block)."""
-        if self.barrier == "flags":
-            self._epoch += 1
-            self._native.peer_barrier(self.rank, self._flag_ptrs, self._epoch,
-                                      torch.cuda.current_stream(self._side.device).cuda_stream)
-        else:
-            dist.all_reduce(self._token, group=self.group, async_op=True).wait()
+        """Barrier over the ranks on the side stream (the host does not block)."""
+        self._space.barrier(self._side, self.barrier)
 
     # called by the layer's backward
     def gradient_buffer(self, layer):
@@ -600,8 +733,7 @@ class PeerTableUpdate:
         torch.cuda.synchronize(device)
         if self.world > 1:
             dist.barrier(group=self.group)  # nobody still reads a buffer that is about to go
-        with torch.cuda.device(device):
-            self._release()
+        self._space.release()
         self.layers = []
 
 

@@ -124,7 +124,7 @@ def check_dp_overlapped(rank, world, dev):
     report("dp_overlapped", worst <= 1e-5, f"rel {worst:.2e}")
 
 
-def check_dp_sharded_update(rank, world, dev):
+def check_dp_sharded_update(rank, world, dev, transport="collectives"):
     from spiky_b200.data_parallel import ShardedTableUpdate
     from spiky_b200.lut_layer import GradientPolicy, GradientType
 
@@ -139,8 +139,13 @@ def check_dp_sharded_update(rank, world, dev):
         (z ** 2).sum().backward()
 
     layers = small_convnet(dev)
-    sync = ShardedTableUpdate(layers, lr, average=False)
     per = B // world
+    try:
+        sync = ShardedTableUpdate(layers, lr, average=False, transport=transport, batch_size=per)
+    except RuntimeError as e:
+        # all ranks raise together; a node that does not allow the mapping cannot run the peer transport
+        report("dp_sharded_update_" + transport, True, "unavailable here: " + str(e)[:160])
+        return
     run(layers, x[rank * per:(rank + 1) * per].contiguous())
     sync.wait()
     torch.cuda.synchronize()
@@ -150,7 +155,16 @@ def check_dp_sharded_update(rank, world, dev):
     run(ref, x)
     worst = max(rel_err(a._weights.detach().cpu().numpy(), b._weights.detach().cpu().numpy()) for a, b in zip(layers, ref))
     moved = all(not torch.equal(a._weights, small._weights) for a, small in zip(ref, small_convnet(dev)))
-    report("dp_sharded_update", worst <= 1e-5 and moved, f"rel {worst:.2e}")
+    # a second step reuses the gathered arrays; the replicas must stay bit-identical
+    run(layers, x[rank * per:(rank + 1) * per].contiguous())
+    sync.wait()
+    torch.cuda.synchronize()
+    sums = torch.stack([l._weights.detach().double().sum() for l in layers])
+    lo, hi = sums.clone(), sums.clone()
+    dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+    dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+    report("dp_sharded_update_" + transport, worst <= 1e-5 and moved and bool((hi == lo).all()),
+           f"rel {worst:.2e}, checksum spread {float((hi - lo).abs().max()):.1e}")
     sync.remove()
 
 
@@ -320,6 +334,7 @@ def main():
         check_dp_fc(rank, world, dev, True)
         check_dp_overlapped(rank, world, dev)
         check_dp_sharded_update(rank, world, dev)
+        check_dp_sharded_update(rank, world, dev, "peer")
         check_dp_peer_update(rank, world, dev, "flags")
         check_dp_peer_update(rank, world, dev, "collective")
         check_dp_sparse_exchange(rank, world, dev)

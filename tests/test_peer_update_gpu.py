@@ -12,7 +12,7 @@ from oracle import lut_oracle as orc
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("n_ranks,n", [(1, 1000), (2, 4099), (3, 37), (4, 65536 + 5), (8, 300001), (11, 2050)])
+@pytest.mark.parametrize("n_ranks,n", [(1, 1000), (2, 4099), (3, 37), (4, 65536 + 5), (8, 300001), (11, 2050), (16, 70001)])
 def test_kernel_matches_the_oracle_bit_for_bit(n_ranks, n):
     from spiky_b200 import _native
 
@@ -166,3 +166,24 @@ def test_barrier_wait_is_bounded():
     out = subprocess.run([sys.executable, "-c", code], cwd=root, capture_output=True, text=True, timeout=300)
     assert out.returncode == 0, out.stdout + out.stderr
     assert "bounded" in out.stdout
+
+
+@pytest.mark.parametrize("nbytes,src_shift,dst_offset", [(4096, 0, 0), (100003, 0, 32), (1 << 20, 16, 4096), (77, 5, 5),
+                                                         (3000, 3, 16), (9, 0, 0)])
+def test_broadcast_copies_bytes_into_every_buffer(nbytes, src_shift, dst_offset):
+    """Three emulated ranks on one device: the byte range lands at the offset in every buffer and nowhere else; source
+    and destinations aligned alike (fast path) or not (byte path)."""
+    from spiky_b200 import _native
+
+    rng = np.random.default_rng(nbytes)
+    payload = rng.integers(0, 256, nbytes, dtype=np.uint8)
+    src = torch.zeros(nbytes + 64, dtype=torch.uint8, device="cuda")
+    src[src_shift:src_shift + nbytes] = torch.from_numpy(payload).cuda()
+    dst = [torch.full((dst_offset + nbytes + 64,), 0xAB, dtype=torch.uint8, device="cuda") for _ in range(3)]
+    _native.peer_broadcast([d.data_ptr() for d in dst], dst_offset, src.data_ptr() + src_shift, nbytes,
+                           torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    for d in dst:
+        got = d.cpu().numpy()
+        assert np.array_equal(got[dst_offset:dst_offset + nbytes], payload)
+        assert (got[:dst_offset] == 0xAB).all() and (got[dst_offset + nbytes:] == 0xAB).all()
