@@ -241,6 +241,31 @@ class LutLayerWorkload:
         return time.perf_counter() - t0
 
 
+class _Syncs:
+    """Several table-update objects behind one wait() / remove()."""
+
+    def __init__(self, parts):
+        self.parts = list(parts)
+        self.world = self.parts[0].world
+
+    def wait(self):
+        for p in self.parts:
+            p.wait()
+
+    def remove(self):
+        for p in self.parts:
+            p.remove()
+
+    def __getattr__(self, name):   # the sharded update's own attributes (exchange_only, _plans, _on_backward)
+        return getattr(self.parts[0], name)
+
+    def __setattr__(self, name, value):
+        if name in ("parts", "world"):
+            object.__setattr__(self, name, value)
+        else:
+            setattr(self.parts[0], name, value)
+
+
 class SparseConvNetWorkload:
     """Sparse LUT conv-net training step on 28x28 single-channel images (forward + backward + SGD).
 
@@ -268,7 +293,7 @@ class SparseConvNetWorkload:
         """How cold caches are ensured between timed steps: the step's inputs exceed L2, or L2 is flushed."""
         return "inputs>L2" if getattr(self, "static_input_bytes", 0) > L2_BYTES else "flushed"
 
-    def __init__(self, batch=512, internal=False, sharded=False, peer=False):
+    def __init__(self, batch=512, internal=False, sharded=False, peer=False, graph=False):
         self.B = batch
         self.units_per_step = batch
         # sharded: data parallelism without dense gradient exchange for the three sparse layers: ranks all-gather
@@ -279,6 +304,11 @@ class SparseConvNetWorkload:
         # peer: data parallelism with the gradient reduction, the SGD update and the distribution of the updated tables
         # in one kernel over peer memory (spiky_b200.data_parallel.PeerTableUpdate), for all four layers
         self.peer = peer
+        # graph: after the warm-up the device-resident step (forward, loss, backward, update, exchange) is captured into
+        # one CUDA graph and replayed: no host work per step.  Offered where the step makes no NCCL call (one GPU, or
+        # the peer-memory strategies, whose barriers count their epochs on the device).
+        self.graph = graph
+        self.graph_ok_multi = bool(peer) or sharded == "peer"
         # internal: the reference's GradientType.Internal, the backward kernel applies W -= lr * dW in place (no dense
         # gradient, no optimiser pass); default: dense gradients + torch.optim.SGD
         self.internal = internal
@@ -329,11 +359,20 @@ class SparseConvNetWorkload:
         for l in self.layers:
             l.train()
         params = [l._weights for l in self.layers]
+        # every step reads all tables (382 MB): the step's inputs exceed L2, no flush between steps
+        self.static_input_bytes = sum(p.numel() * p.element_size() for p in params)
         if self.sharded:
             from spiky_b200.data_parallel import ShardedTableUpdate
             self.table_sync = ShardedTableUpdate(self.layers[:-1], self.LR, batch_size=self.B,
                                                  transport="peer" if self.sharded == "peer" else "collectives")
+            # a replayed graph joins all its streams at its end: no overlap into the next step then
+            self.overlaps_steps = self.sharded == "peer" and self.table_sync.world > 1 and not self.graph
             params = params[-1:]
+            if self.sharded == "peer":
+                # the small readout layer through the fused peer update: the step then has no NCCL call and no optimiser
+                from spiky_b200.data_parallel import PeerTableUpdate
+                self.table_sync = _Syncs([self.table_sync, PeerTableUpdate(self.layers[-1:], self.LR)])
+                params = []
         if self.peer:
             from spiky_b200.data_parallel import PeerTableUpdate
             self.table_sync = PeerTableUpdate(self.layers, self.LR, barrier=os.environ.get("BENCH_PEER_BARRIER", "flags"))
@@ -349,12 +388,29 @@ class SparseConvNetWorkload:
         self.d2h_bytes = 4
         self.grad_params = params
 
-    def _run(self, x, labels):
+    cuda_graph = None
+    graph_keeps_kernel_profile = True   # the per-kernel times of the line come from an eager pass of the same step
+
+    def capture_graph(self):
+        """Captures the device-resident step (inputs in self.dx / self.dl) into a CUDA graph."""
+        import torch
+        from spiky_b200 import _native
+        if self.table_sync is not None:
+            self.table_sync.wait()
+        torch.cuda.synchronize()
+        _native.profiler_reset()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            self.graph_out = self._run(self.dx, self.dl, join=True)
+        self.graph_launches = sum(v["launches"] for v in _native.profiler_read().values())
+        self.cuda_graph = g
+
+    def _run(self, x, labels, join=False):
         import torch
         import torch.nn.functional as F
         if self.opt is not None:
             self.opt.zero_grad(set_to_none=True)
-        if self.table_sync is not None:
+        if self.table_sync is not None and not self.overlaps_steps:
             self.table_sync.wait()  # the tables updated by the previous step have arrived
         z = x
         for l in self.layers[:-1]:
@@ -372,20 +428,35 @@ class SparseConvNetWorkload:
                     p.add_(p.grad, alpha=-self.LR)
         elif self.opt is not None:
             self.opt.step()
+        if join and self.table_sync is not None:
+            self.table_sync.wait()   # a captured step ends with every stream it used joined
         return loss
 
     allreduce = None
     grad_sync = None
     table_sync = None     # sharded / peer table update: the exchange it leaves running belongs to the step
+    # True: every layer's forward pass waits for that layer's own exchange (the sharded update over peer memory), so the
+    # exchange of the upper layers may run into the next step's forward pass of the lower ones; the timed region then
+    # has no untimed gap between its steps and ends after the last exchange
+    overlaps_steps = False
     average_tables = None  # data parallel + Internal policy: tables are averaged over the ranks after the step
 
     def trainable_parameters(self):
         return [] if self.internal else self.grad_params
 
     def step_device(self):
+        if self.cuda_graph is not None:
+            self.cuda_graph.replay()
+            return self.graph_out
         return self._run(self.dx, self.dl)
 
     def step_e2e(self):
+        if self.cuda_graph is not None:
+            # the graph reads its inputs from fixed device buffers: copy this step's host batch into them
+            self.dx.copy_(self.hx, non_blocking=True)
+            self.dl.copy_(self.hl, non_blocking=True)
+            self.cuda_graph.replay()
+            return self.graph_out
         x = self.hx.to(self.device, non_blocking=True)
         labels = self.hl.to(self.device, non_blocking=True)
         return self._run(x, labels)
@@ -910,11 +981,14 @@ WORKLOADS = {
     "attention_layer": lambda batch=None: AttentionLayerWorkload(**_b(batch)),
     "large_transformer": lambda batch=None: LargeTransformerWorkload(**_b(batch)),
     "large_transformer_b4": lambda batch=None: LargeTransformerWorkload(batch=batch or 4),
-    "sparse_convnet": lambda batch=None: SparseConvNetWorkload(**_b(batch)),
-    "sparse_convnet_internal": lambda batch=None: SparseConvNetWorkload(internal=True, **_b(batch)),
+    "sparse_convnet": lambda batch=None: SparseConvNetWorkload(graph=True, **_b(batch)),
+    "sparse_convnet_eager": lambda batch=None: SparseConvNetWorkload(**_b(batch)),
+    "sparse_convnet_internal": lambda batch=None: SparseConvNetWorkload(internal=True, graph=True, **_b(batch)),
     "sparse_convnet_sharded": lambda batch=None: SparseConvNetWorkload(sharded=True, **_b(batch)),
     "sparse_convnet_sharded_peer": lambda batch=None: SparseConvNetWorkload(sharded="peer", **_b(batch)),
     "sparse_convnet_peer": lambda batch=None: SparseConvNetWorkload(peer=True, **_b(batch)),
+    "sparse_convnet_peer_graph": lambda batch=None: SparseConvNetWorkload(peer=True, graph=True, **_b(batch)),
+    "sparse_convnet_sharded_peer_graph": lambda batch=None: SparseConvNetWorkload(sharded="peer", graph=True, **_b(batch)),
     "lut_layer": lambda batch=None: LutLayerWorkload(**_b(batch)),
     "lut_layer_b256": lambda batch=None: LutLayerWorkload(batch=batch or 256),
     "lut_layer_b256_graph": lambda batch=None: LutLayerWorkload(batch=batch or 256, graph=True),
@@ -1014,11 +1088,34 @@ def _attach_data_parallel(wl, world):
 
 
 def _dp_strategy(wl):
+    tail = ", step replayed from a CUDA graph" if getattr(wl, "cuda_graph", None) is not None else ""
     if getattr(wl, "peer", False):
-        return "fused update over peer memory"
+        return "fused update over peer memory" + tail
     if getattr(wl, "sharded", False) == "peer":
-        return "sharded table update over peer memory"
-    return "sharded table update" if getattr(wl, "sharded", False) else "gradient all-reduce"
+        return "sharded table update over peer memory" + tail
+    return ("sharded table update" if getattr(wl, "sharded", False) else "gradient all-reduce") + tail
+
+
+def _try_capture(wl, world, device):
+    """Captures the workload's step into a CUDA graph when it asks for one; all ranks keep the graph or none does."""
+    import torch
+    import torch.distributed as dist
+    if not getattr(wl, "graph", False) or getattr(wl, "cuda_graph", None) is not None:
+        return
+    if world > 1 and not getattr(wl, "graph_ok_multi", False):
+        return   # the step makes NCCL calls from autograd hooks: issued eagerly
+    ok = 1
+    try:
+        wl.capture_graph()
+    except Exception as e:   # noqa: BLE001 - any failure means: run the step eagerly
+        sys.stderr.write(f"graph capture failed, the step runs eagerly: {e}\n")
+        ok = 0
+    if world > 1:
+        t = torch.tensor([ok], dtype=torch.int32, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        ok = int(t)
+    if not ok:
+        wl.cuda_graph = None
 
 
 def _replica_check(params, world):
@@ -1078,12 +1175,14 @@ def run_ours(args):
         do_flush = w.l2_policy() == "flushed"
         barrier()
         t0 = time.perf_counter()
+        assert not (do_flush and getattr(w, "overlaps_steps", False)), "steps that overlap need back-to-back brackets"
         for i in range(steps):
             if do_flush:
                 flush.zero_()
             starts[i].record()
             w.step_device()
-            finish_step(w)
+            if i == steps - 1 or not getattr(w, "overlaps_steps", False):
+                finish_step(w)
             stops[i].record()
         barrier()
         t1 = time.perf_counter()
@@ -1102,6 +1201,7 @@ def run_ours(args):
     for _ in range(warmup):
         wl.step_device()
         finish_step(wl)
+    _try_capture(wl, world, device)
     dp_trial = None
     if world > 1 and args.workload == DEFAULT_WORKLOAD and args.dp == "auto":
         # Ways to keep the replicas' tables equal (same SGD step, spiky_b200/data_parallel.py): all-reduce the dense
@@ -1123,7 +1223,8 @@ def run_ours(args):
 
         best = (agreed(timed_region(wl, 8, profile=False)[0]), wl, sync)
         dp_trial = {_dp_strategy(wl): best[0]}
-        for name in ("sparse_convnet_sharded", "sparse_convnet_peer", "sparse_convnet_sharded_peer"):
+        for name in ("sparse_convnet_sharded", "sparse_convnet_peer", "sparse_convnet_sharded_peer",
+                     "sparse_convnet_peer_graph", "sparse_convnet_sharded_peer_graph"):
             alt = WORKLOADS[name](args.batch)
             try:
                 alt.setup(device, rank)
@@ -1132,9 +1233,16 @@ def run_ours(args):
                 dp_trial[_dp_strategy(alt)] = "unavailable: " + str(e)[:200]
                 continue
             alt_sync = _attach_data_parallel(alt, world)
-            for _ in range(3):
+            for _ in range(5):
                 alt.step_device()
                 finish_step(alt)
+            _try_capture(alt, world, device)
+            if getattr(alt, "graph", False) and alt.cuda_graph is None:
+                dp_trial[_dp_strategy(alt) + ", step replayed from a CUDA graph"] = "unavailable: capture failed"
+                release(alt, alt_sync)
+                del alt
+                torch.cuda.empty_cache()
+                continue
             t_alt = agreed(timed_region(alt, 8, profile=False)[0])
             dp_trial[_dp_strategy(alt)] = t_alt
             if t_alt < best[0]:
@@ -1146,7 +1254,22 @@ def run_ours(args):
             torch.cuda.empty_cache()
         _, wl, sync = best
         dp_strategy = _dp_strategy(wl)
-    ms_dev, prof, window = timed_region(wl, args.steps, profile=True)
+    # The figure: K steps with nothing but the step on the device.  The per-kernel times for the roofline come from a
+    # second pass of the same K steps with the library's profiler on (two CUDA events around every launch): kept apart
+    # because the extra event calls cost host time, which a step with many small launches on several streams feels.
+    ms_dev, _, window = timed_region(wl, args.steps, profile=False)
+    graph = getattr(wl, "cuda_graph", None)
+    if graph is not None and getattr(wl, "graph_keeps_kernel_profile", False):
+        # replayed launches do not pass through the library's entry points: the kernel times come from the same step
+        # issued eagerly
+        wl.cuda_graph = None
+        for _ in range(2):
+            wl.step_device()
+            finish_step(wl)
+        ms_profiled, prof, _ = timed_region(wl, args.steps, profile=True)
+        wl.cuda_graph = graph
+    else:
+        ms_profiled, prof, _ = timed_region(wl, args.steps, profile=True)
 
     def e2e_region(steps):
         """End to end: every step copies its inputs from pinned host memory, runs, and its result is read back on the
@@ -1163,7 +1286,8 @@ def run_ours(args):
             if do_flush:
                 flush.zero_()
             r = wl.step_e2e()
-            finish_step(wl)
+            if i == steps - 1 or not getattr(wl, "overlaps_steps", False):
+                finish_step(wl)
             slots[i % 2].copy_(r.detach().reshape(1).float(), non_blocking=True)
             done[i % 2].record()
             if i >= 1:
@@ -1178,6 +1302,16 @@ def run_ours(args):
 
     e2e_region(2)
     ms_e2e = e2e_region(args.steps)
+
+    # host time per step: a few steps issued without waiting for the device (the launch queue absorbs them); well below
+    # ms_per_step means the device sets the pace, close to it means the step is bound by the host's launch rate
+    torch.cuda.synchronize()
+    h0 = time.perf_counter()
+    for _ in range(8):
+        wl.step_device()
+    host_ms = (time.perf_counter() - h0) / 8 * 1e3
+    finish_step(wl)
+    torch.cuda.synchronize()
 
     # ---- data-parallel evidence: replicas identical (checked BEFORE the run without exchange below, which lets
     # them drift on purpose), what the exchange costs, how fast the same payload moves alone
@@ -1227,12 +1361,14 @@ def run_ours(args):
         # the same loads and stores, tables unchanged)
         ts = wl.table_sync
         payload = 2 * sum(l._weights.numel() * 4 for l in wl.layers) * (world - 1) // world
-        ts.paused = True
-        for _ in range(2):
-            wl.step_device()
-            finish_step(wl)
-        ms_local, _, _ = timed_region(wl, max(3, args.steps // 4), profile=False)
-        ts.paused = False
+        ms_local = None
+        if getattr(wl, "cuda_graph", None) is None:   # (a replayed graph has the exchange baked in)
+            ts.paused = True
+            for _ in range(2):
+                wl.step_device()
+                finish_step(wl)
+            ms_local, _, _ = timed_region(wl, max(3, args.steps // 4), profile=False)
+            ts.paused = False
         lr0, ts.lr = ts.lr, 0.0
         iso = []
         for rep in range(4):
@@ -1277,9 +1413,20 @@ def run_ours(args):
         w1.setup(device, rank)
         for _ in range(3):
             w1.step_device()
+        _try_capture(w1, world, device)
         ms1, _, _ = timed_region(w1, 20, profile=False)
         variants = {"internal_gradient_policy": {"ms_per_step": ms1, "value": w1.units_per_step / (ms1 / 1e3),
                                                  "unit": w1.unit, "steps": 20}}
+        del w1
+        torch.cuda.empty_cache()
+        # the default step with every launch issued by the host (the default replays the step from a CUDA graph)
+        w1 = WORKLOADS["sparse_convnet_eager"](args.batch)
+        w1.setup(device, rank)
+        for _ in range(3):
+            w1.step_device()
+        ms1, _, _ = timed_region(w1, 20, profile=False)
+        variants["launched_by_the_host"] = {"ms_per_step": ms1, "value": w1.units_per_step / (ms1 / 1e3), "unit": w1.unit,
+                                            "steps": 20}
         del w1
         torch.cuda.empty_cache()
     secondary = None
@@ -1298,7 +1445,7 @@ def run_ours(args):
         ms2, _, _ = timed_region(w2, 10, profile=False)
         secondary = {"ms": ms2, "replica_check": _replica_check(w2.trainable_parameters(), world), "wl": w2}
 
-    t = torch.tensor([ms_dev, ms_e2e, comm["ms_local"] if comm else 0.0, comm["ms_isolated"] if comm else 0.0,
+    t = torch.tensor([ms_dev, ms_e2e, (comm["ms_local"] or 0.0) if comm else 0.0, comm["ms_isolated"] if comm else 0.0,
                       secondary["ms"] if secondary else 0.0], dtype=torch.float64, device=device)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -1312,7 +1459,9 @@ def run_ours(args):
         value = units / (ms_dev / 1e3)
         launches = sum(v["launches"] for v in prof.values())
         alg = wl.algorithmic_bytes()
-        if getattr(wl, "cuda_graph", None) is not None:
+        if getattr(wl, "cuda_graph", None) is not None and getattr(wl, "graph_keeps_kernel_profile", False):
+            launches = wl.graph_launches * args.steps
+        elif getattr(wl, "cuda_graph", None) is not None:
             # replayed launches never pass through the library's entry points: count what the capture recorded and
             # take the whole replayed step as one launch of all kernels for the roofline
             launches = wl.graph_launches * args.steps
@@ -1347,6 +1496,10 @@ def run_ours(args):
             "e2e": {"value": units / (ms_e2e / 1e3), "unit": wl.unit, "h2d_bytes_per_step": wl.h2d_bytes,
                     "d2h_bytes_per_step": wl.d2h_bytes, "ms_per_step": ms_e2e},
             "gpu_launches": int(launches),
+            "host_ms_per_step": host_ms,
+            "step_launch": "one CUDA graph replay per step" if getattr(wl, "cuda_graph", None) is not None
+                           else "every kernel launched by the host",
+            "ms_per_step_with_kernel_events": ms_profiled,
             "device_wait_errors": int(wait_errors),
             "clocks": clocks,
         }
@@ -1379,12 +1532,13 @@ def run_ours(args):
                             "rank's table gradient (bulk copies into a shared-memory ring), applies the SGD step and "
                             "stores the new slice into every rank's tables; overlapped with the backward pass of the "
                             "layers below; barriers through flags in peer memory",
-                "payload_bytes_per_step_per_direction": comm["payload"], "ms_step_without_exchange": ms_local,
-                "exposed_ms": ms_dev - ms_local, "isolated_ms": ms_isolated,
+                "payload_bytes_per_step_per_direction": comm["payload"],
+                "ms_step_without_exchange": ms_local if comm["ms_local"] is not None else None,
+                "exposed_ms": ms_dev - ms_local if comm["ms_local"] is not None else None, "isolated_ms": ms_isolated,
                 "isolated_gbs_per_direction": gb / (ms_isolated / 1e3),
                 "frac_of_nvlink": gb / (ms_isolated / 1e3) / 900.0,
                 "frac_of_measured_peer_copy": gb / (ms_isolated / 1e3) / 770.0,
-                "hidden_frac": 1.0 - (ms_dev - ms_local) / ms_isolated,
+                "hidden_frac": 1.0 - (ms_dev - ms_local) / ms_isolated if comm["ms_local"] is not None else None,
             }
         elif comm:
             ring = 2.0 * (world - 1) / world * comm["payload"] / 1e9

@@ -447,8 +447,11 @@ int lutb_fp32_gemm(int kind, int32_t m, int32_t n, int32_t k, const float *a, in
  * lutb_peer_broadcast: copies `bytes` from `src` (this rank's memory) to dst[r] + dst_offset of every listed buffer
  * (own pointers or mapped ones) with plain stores; 16-byte aligned offsets copy fastest.  Same ordering contract as
  * lutb_peer_sgd_update.
- * lutb_peer_barrier: a barrier over the ranks on the stream, without the host: flags[r] is rank r's array of n_ranks
- * 64-bit flags in shareable memory (zero before the first use); every rank calls it with the same epoch, 1, 2, 3, ...
+ * lutb_peer_barrier: a barrier over the ranks on the stream, without the host: flags[r] is rank r's array of
+ * 2 * LUTB_MAX_PEER_RANKS 64-bit words in shareable memory (zero before the first use: one flag per rank, then the
+ * rank's own barrier count); every rank calls it with the same epoch, 1, 2, 3, ..., or with epoch 0: the kernel then
+ * counts the barriers itself in device memory, and the launch, having no changing argument, can be part of a CUDA
+ * graph that is replayed.
  * A kernel of one warp stores the epoch into this rank's slot of every rank's array (release at system scope, so what
  * earlier kernels of the stream wrote is visible to the ranks that see the flag) and waits until every slot of its own
  * array holds it.  The wait is bounded (about two seconds); one that runs out is counted by lutb_device_wait_errors and

@@ -218,15 +218,29 @@ struct BarrierArgs {
 
 __global__ void peer_barrier_kernel(const BarrierArgs a) {
     const int r = threadIdx.x;
+    // epoch 0: the epoch is this rank's own count of barriers on these flags, kept in device memory behind the rank
+    // slots of its array (the launch carries no changing argument, so it may be replayed from a CUDA graph)
+    __shared__ unsigned long long epoch_s;
+    if (r == 0) {
+        unsigned long long e = a.epoch;
+        if (e == 0) {
+            unsigned long long *counter = a.flags[a.rank] + kMaxPeerRanks;
+            e = *counter + 1;
+            *counter = e;
+        }
+        epoch_s = e;
+    }
+    __syncthreads();
+    const unsigned long long epoch = epoch_s;
     if (r >= a.n_ranks) return;
     unsigned long long *out = a.flags[r] + a.rank;
-    asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(out), "l"(a.epoch) : "memory");
+    asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(out), "l"(epoch) : "memory");
     const unsigned long long *in = a.flags[a.rank] + r;
     const long long t0 = clock64();
     for (;;) {
         unsigned long long seen;
         asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(seen) : "l"(in) : "memory");
-        if (seen >= a.epoch) break;
+        if (seen >= epoch) break;
         if (clock64() - t0 > kBarrierLimitCycles) {
             atomicAdd(&g_peer_wait_errors, 1);
             break;
@@ -314,7 +328,6 @@ int lutb_peer_barrier(int32_t n_ranks, int32_t rank, void *const *flags, uint64_
     LUTB_REQUIRE(n_ranks >= 1 && n_ranks <= kMaxPeerRanks, LUTB_ERR_SHAPE, "lutb_peer_barrier: 1 <= n_ranks <= %d",
                  kMaxPeerRanks);
     LUTB_REQUIRE(rank >= 0 && rank < n_ranks && flags, LUTB_ERR_SHAPE, "lutb_peer_barrier: bad rank or null");
-    LUTB_REQUIRE(epoch > 0, LUTB_ERR_SHAPE, "lutb_peer_barrier: epochs start at 1 (the flags start at 0)");
     BarrierArgs a{};
     for (int r = 0; r < n_ranks; ++r) {
         LUTB_REQUIRE(flags[r] && ((uintptr_t)flags[r] & 7) == 0, LUTB_ERR_ALIGN, "lutb_peer_barrier: flag array of rank %d", r);
@@ -361,8 +374,14 @@ int lutb_peer_sgd_update(int32_t n_ranks, int32_t rank, const float *const *grad
     if (n_stages > kPeerMaxStages) n_stages = kPeerMaxStages;
     LUTB_REQUIRE(n_stages >= 2, LUTB_ERR_SHAPE, "lutb_peer_sgd_update: too many ranks for the shared-memory ring");
     const size_t smem = (size_t)n_stages * stage_bytes + 16 * kPeerMaxStages + 16;
-    LUTB_CUDA(cudaFuncSetAttribute(peer_sgd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                   (int)(kPeerRingBytes + 16 * kPeerMaxStages + 16)));
+    // once per device, so that later launches (stream capture included) are launches only
+    static unsigned long long attr_done = 0;
+    const int dev = device_info().device;
+    if (dev >= 64 || !((attr_done >> dev) & 1ull)) {
+        LUTB_CUDA(cudaFuncSetAttribute(peer_sgd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int)(kPeerRingBytes + 16 * kPeerMaxStages + 16)));
+        if (dev < 64) attr_done |= 1ull << dev;
+    }
     const int64_t pieces = (vecs * 4 + kPieceFloats - 1) / kPieceFloats;
     const int blocks = (int)max((int64_t)1, min((int64_t)device_info().sm_count, pieces));
     peer_sgd_kernel<<<blocks, kPeerThreads, smem, s>>>(a, n_stages, kPieceFloats);

@@ -331,8 +331,7 @@ class ShardedTableUpdate:
             sizes[f"w{li}"] = 4 * ((layer._weights.numel() + 3) // 4 * 4)
             sizes[f"i{li}"] = W * B * layer.n_detectors() * item
             sizes[f"d{li}"] = W * B * layer.n_outputs() * 4
-        self._space = _PeerSpace(sizes, device, self.group, "ShardedTableUpdate")
-        self._side = torch.cuda.Stream(device=device)
+        self._space = _PeerSpace(sizes, device, self.group, "ShardedTableUpdate", channels=len(self.layers))
         for li, layer in enumerate(self.layers):
             plan = self._plans[id(layer)]
             shared = self._space.tensor(f"w{li}", torch.float32, layer._weights.numel())
@@ -341,6 +340,13 @@ class ShardedTableUpdate:
             plan["li"] = li
             plan["idx_all"] = self._space.tensor(f"i{li}", plan["idx_dtype"])
             plan["dY_all"] = self._space.tensor(f"d{li}", torch.float32)
+            # The exchange of a layer runs on the layer's own stream and ends with its own barrier and event: the
+            # next forward pass of THAT layer waits for the event (forward pre-hook), nothing else does.  The upper
+            # layers' exchanges, which start first and move most bytes, so overlap the rest of the backward pass and
+            # the next step's forward pass of the layers below them; only the bottom layer's exchange is exposed.
+            plan["stream"] = torch.cuda.Stream(device=device)
+            plan["done"] = None
+            plan["hook"] = layer.register_forward_pre_hook(lambda module, inputs: self.wait_layer(module))
         torch.cuda.synchronize(device)
         dist.barrier(group=self.group)  # every rank's tables are in place before anyone stores into them
 
@@ -351,9 +357,10 @@ class ShardedTableUpdate:
         if batch != self.batch_size:
             raise ValueError(f"transport='peer' was set up for {self.batch_size} samples per rank, got {batch}")
         main = torch.cuda.current_stream(idx.device)
-        self._side.wait_stream(main)  # the input gradient of this layer (it reads the tables) and dY are ordered before
-        with torch.cuda.stream(self._side):
-            side = self._side.cuda_stream
+        stream = plan["stream"]
+        stream.wait_stream(main)  # the input gradient of this layer (it reads the tables) and dY are ordered before
+        with torch.cuda.stream(stream):
+            side = stream.cuda_stream
             idx_all, dY_all = plan["idx_all"], plan["dY_all"]
             n_i, n_d = idx.numel(), dY.numel()
             own = idx_all[self.rank * n_i:(self.rank + 1) * n_i]
@@ -362,11 +369,11 @@ class ShardedTableUpdate:
                                    n_i * own.element_size(), side)
             dYc = dY.contiguous()
             _native.peer_broadcast(space.ptrs[f"d{li}"], self.rank * n_d * 4, dYc.data_ptr(), n_d * 4, side)
-            idx.record_stream(self._side)
-            dYc.record_stream(self._side)
-            plan["last"] = (idx, dYc)   # kept for callers that time the exchange alone
+            # the layer's stream reads these after the main stream has moved on: they stay referenced until the next
+            # backward pass of the layer (by then its forward pass has waited for this exchange)
+            plan["last"] = (idx, dYc)
             # every rank's pairs have landed everywhere, and no rank still reads these tables
-            space.barrier(self._side, self.barrier)
+            space.barrier(stream, self.barrier, li)
             c0, c1 = plan["cuts"][self.rank], plan["cuts"][self.rank + 1]
             if not self.exchange_only:
                 self._apply(layer, W * batch, dY_all, idx_all, -self._learning_rate() / self.scale_div, c0, c1)
@@ -374,7 +381,17 @@ class ShardedTableUpdate:
             if hi > lo:
                 _native.peer_broadcast(space.others(f"w{li}"), lo * 4, space.ptrs[f"w{li}"][self.rank] + lo * 4,
                                        (hi - lo) * 4, side)
-        self._dirty = True
+            # every rank's share of this layer has landed in this rank's tables, nobody still reads the gathered pairs
+            space.barrier(stream, self.barrier, li)
+            plan["done"] = torch.cuda.Event()
+            plan["done"].record(stream)
+
+    def wait_layer(self, layer):
+        """Makes the current stream wait for the outstanding exchange of one layer (peer transport)."""
+        plan = self._plans.get(id(layer))
+        if plan is not None and plan.get("done") is not None:
+            torch.cuda.current_stream(layer._weights.device).wait_event(plan["done"])
+            plan["done"] = None
 
     def _learning_rate(self):
         return float(self.lr() if callable(self.lr) else self.lr)
@@ -456,10 +473,9 @@ class ShardedTableUpdate:
         for w in self._pending:
             w.wait()
         self._pending = []
-        if self._space is not None and self._dirty:
-            # every rank's share has landed in this rank's tables (and nobody still reads the gathered pairs)
-            self._space.barrier(self._side, self.barrier)
-            self._dirty = False
+        if self._space is not None:
+            for layer in self.layers:
+                self.wait_layer(layer)
         if self._side is not None:
             torch.cuda.current_stream(self._side.device).wait_stream(self._side)
 
@@ -478,6 +494,8 @@ class ShardedTableUpdate:
             for plan in self._plans.values():
                 plan.pop("idx_all", None)
                 plan.pop("dY_all", None)
+                plan.pop("last", None)
+                plan.pop("hook").remove()
             torch.cuda.synchronize(device)
             dist.barrier(group=self.group)  # nobody still reads a buffer that is about to go
             self._space.release()
@@ -498,7 +516,7 @@ class _PeerSpace:
     ``release`` are collective.  A rank that fails to allocate or to map tells the others through the same
     collectives, so that all ranks raise ``RuntimeError`` together instead of one leaving the others waiting."""
 
-    def __init__(self, sizes, device, group=None, what="peer memory"):
+    def __init__(self, sizes, device, group=None, what="peer memory", channels=1):
         from . import _native
 
         self._native = _native
@@ -513,15 +531,19 @@ class _PeerSpace:
         self.names = list(sizes)
         self.sizes = dict(sizes)
         self._owned, self._mapped = [], []
-        self._epoch = 0
+        # barrier channels: barriers issued on different streams must not share flags (a rank may run them in another
+        # order than its peers); every channel has its own flag array and epoch counter
+        self.channels = int(channels)
         self._token = None
         own, handles, error = {}, {}, None
         try:
             with torch.cuda.device(device):
                 # the barrier's flags: one 64-bit slot per rank, zero before the first epoch
-                own["_flags"], handles["_flags"] = _native.peer_alloc(8 * _native.MAX_PEER_RANKS)
+                # per channel: one 64-bit flag per rank, then this rank's own barrier count
+                own["_flags"], handles["_flags"] = _native.peer_alloc(16 * _native.MAX_PEER_RANKS * self.channels)
                 self._owned.append(own["_flags"])
-                torch.as_tensor(_DeviceSpan(own["_flags"], 2 * _native.MAX_PEER_RANKS), device=device).zero_()
+                torch.as_tensor(_DeviceSpan(own["_flags"], 4 * _native.MAX_PEER_RANKS * self.channels),
+                                device=device).zero_()
                 for name in self.names:
                     own[name], handles[name] = _native.peer_alloc(max(16, (int(sizes[name]) + 15) // 16 * 16))
                     self._owned.append(own[name])
@@ -573,15 +595,17 @@ class _PeerSpace:
         """The other ranks' buffers ``name`` (mapped pointers)."""
         return [p for r, p in enumerate(self.ptrs[name]) if r != self.rank]
 
-    def barrier(self, stream, kind="flags"):
+    def barrier(self, stream, kind="flags", channel=0):
         """Barrier over the ranks on ``stream`` (the host does not block): "flags" = lutb_peer_barrier, a one-warp
         kernel over flags in peer memory whose wait is bounded (a rank that is seconds late is counted by
-        lutb_device_wait_errors and not waited for); "collective" = a one-element all-reduce of the process group."""
+        lutb_device_wait_errors and not waited for); "collective" = a one-element all-reduce of the process group.
+        Every rank issues the barriers of a channel in the same order; channels are independent of each other."""
         if self.world == 1:
             return
         if kind == "flags":
-            self._epoch += 1
-            self._native.peer_barrier(self.rank, self.ptrs["_flags"], self._epoch, stream.cuda_stream)
+            # epoch 0: the kernel counts the barriers of the channel itself (the launch can be replayed from a graph)
+            off = channel * 16 * self._native.MAX_PEER_RANKS
+            self._native.peer_barrier(self.rank, [p + off for p in self.ptrs["_flags"]], 0, stream.cuda_stream)
         else:
             if self._token is None:
                 self._token = torch.zeros(1, dtype=torch.float32, device=self.device)

@@ -187,3 +187,17 @@ def test_broadcast_copies_bytes_into_every_buffer(nbytes, src_shift, dst_offset)
         got = d.cpu().numpy()
         assert np.array_equal(got[dst_offset:dst_offset + nbytes], payload)
         assert (got[:dst_offset] == 0xAB).all() and (got[dst_offset + nbytes:] == 0xAB).all()
+
+
+def test_barrier_counts_its_own_epochs():
+    """Epoch 0: the kernel keeps the count in device memory behind the rank slots, so the identical launch can be
+    repeated (CUDA-graph replay); one rank, three barriers."""
+    from spiky_b200 import _native
+
+    flags = torch.zeros(2 * _native.MAX_PEER_RANKS, dtype=torch.int64, device="cuda")
+    before = _native.device_wait_errors()
+    for _ in range(3):
+        _native.peer_barrier(0, [flags.data_ptr()], 0, torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    assert _native.device_wait_errors() == before
+    assert int(flags[0]) == 3 and int(flags[_native.MAX_PEER_RANKS]) == 3
