@@ -25,23 +25,10 @@ __host__ __device__ constexpr size_t staged_floats(int n_inputs) {
     return R % 4 == 0 ? ((((size_t)n_inputs * (R / 4)) + 7) & ~(size_t)7) * 4 : (size_t)R * n_inputs;
 }
 
-template <int R, bool TRAIN>
-__global__ void __launch_bounds__(256) check_detectors_kernel(const float *__restrict__ x, int64_t rows, int n_inputs,
-                                                             const int2 *__restrict__ anchors, int n_detectors,
-                                                             int n_anchors, float cmp_eps, int threads_per_group,
-                                                             int32_t *__restrict__ idx,
-                                                             float *__restrict__ min_delta,
-                                                             int32_t *__restrict__ min_k) {
-    extern __shared__ __align__(16) float xs_all[];
-    const int groups = blockDim.x / threads_per_group;
-    const int g = threadIdx.x / threads_per_group;
-    const int lt = threadIdx.x - g * threads_per_group;
-    float *xs = xs_all + (size_t)g * staged_floats<R>(n_inputs);
-    const int64_t row0 = ((int64_t)blockIdx.x * groups + g) * R;
-    const int nrows = (int)min((int64_t)R, max((int64_t)0, rows - row0));
-
-    // ---- stage rows: coalesced global reads, transposed shared writes
-    const bool vec_ok = (n_inputs % 4 == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0);
+// Stages the R rows [row0, row0 + nrows) of one row group: coalesced global reads, transposed shared writes.
+template <int R>
+__device__ __forceinline__ void stage_rows(float *xs, const float *__restrict__ x, int64_t row0, int nrows, int n_inputs,
+                                           int lt, int threads_per_group, bool vec_ok) {
     if (vec_ok) {
         const int n4 = n_inputs >> 2;
         for (int i4 = lt; i4 < n4; i4 += threads_per_group) {
@@ -76,14 +63,44 @@ __global__ void __launch_bounds__(256) check_detectors_kernel(const float *__res
             }
         }
     }
-    __syncthreads();
-    if (nrows <= 0) return;
+}
 
-    // blockIdx.y selects a slice of the detectors so that small batches still fill the machine
-    const int det_per_slice = (n_detectors + gridDim.y - 1) / gridDim.y;
-    const int det_begin = blockIdx.y * det_per_slice;
-    const int det_end = min(n_detectors, det_begin + det_per_slice);
-    for (int t = det_begin + lt; t < det_end; t += threads_per_group) {
+// Work items: (row tile of GROUPS * R rows, chunk of threads_per_group detectors), row tile major.  Block b takes the
+// items [n * b / grid, n * (b + 1) / grid): with a grid of one block per row tile that is the tile's own chunks; small
+// batches launch a multiple of the SM count instead and a block's range may cross into the next tile, which it then
+// stages as well.  (Splitting the detectors into a fixed number of slices per tile left 320 blocks on 148 SMs: the SMs
+// with three blocks set the kernel's time, max / avg active cycles 1.3.)
+template <int R, bool TRAIN>
+__global__ void __launch_bounds__(256) check_detectors_kernel(const float *__restrict__ x, int64_t rows, int n_inputs,
+                                                             const int2 *__restrict__ anchors, int n_detectors,
+                                                             int n_anchors, float cmp_eps, int threads_per_group,
+                                                             int32_t *__restrict__ idx,
+                                                             float *__restrict__ min_delta,
+                                                             int32_t *__restrict__ min_k) {
+    extern __shared__ __align__(16) float xs_all[];
+    const int groups = blockDim.x / threads_per_group;
+    const int g = threadIdx.x / threads_per_group;
+    const int lt = threadIdx.x - g * threads_per_group;
+    float *xs = xs_all + (size_t)g * staged_floats<R>(n_inputs);
+    const bool vec_ok = (n_inputs % 4 == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0);
+    const int chunks = (n_detectors + threads_per_group - 1) / threads_per_group;
+    const int64_t rows_per_tile = (int64_t)groups * R;
+    const int64_t n_items = ((rows + rows_per_tile - 1) / rows_per_tile) * chunks;
+    const int64_t item0 = n_items * blockIdx.x / gridDim.x, item1 = n_items * (blockIdx.x + 1) / gridDim.x;
+    int64_t staged = -1;
+    for (int64_t item = item0; item < item1; ++item) {
+        const int64_t tile = item / chunks;
+        const int chunk = (int)(item - tile * chunks);
+        const int64_t row0 = (tile * groups + g) * R;
+        const int nrows = (int)min((int64_t)R, max((int64_t)0, rows - row0));
+        if (tile != staged) {
+            if (staged >= 0) __syncthreads();   // everyone is done reading the previous tile
+            stage_rows<R>(xs, x, row0, nrows, n_inputs, lt, threads_per_group, vec_ok);
+            __syncthreads();
+            staged = tile;
+        }
+        const int t = chunk * threads_per_group + lt;
+        if (nrows <= 0 || t >= n_detectors) continue;
         int32_t li[R];
         float md[R];
         int32_t mk[R];
@@ -157,16 +174,14 @@ __global__ void check_detectors_global_kernel(const float *__restrict__ x, int64
 template <int R>
 static int launch_check_detectors_r(const float *x, int64_t rows, int n_inputs, const int32_t *anchors,
                                     int n_detectors, int n_anchors, float cmp_eps, int32_t *idx, float *min_delta,
-                                    int32_t *min_k, int tpg, int groups, int det_slices, cudaStream_t stream) {
+                                    int32_t *min_k, int tpg, int groups, int64_t blocks, cudaStream_t stream) {
     const size_t smem = (size_t)groups * staged_floats<R>(n_inputs) * sizeof(float);
-    const int64_t rows_per_block = (int64_t)groups * R;
-    const int64_t blocks = (rows + rows_per_block - 1) / rows_per_block;
     LUTB_REQUIRE(blocks <= 0x7FFFFFFF, LUTB_ERR_SHAPE, "batch too large for one launch");
     const bool train = min_delta != nullptr;
     auto kern = train ? check_detectors_kernel<R, true> : check_detectors_kernel<R, false>;
     if (smem > 48 * 1024) LUTB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     KernelScope scope(K_CHECK_DETECTORS, stream);
-    kern<<<dim3((unsigned)blocks, (unsigned)det_slices), tpg * groups, smem, stream>>>(x, rows, n_inputs, reinterpret_cast<const int2 *>(anchors),
+    kern<<<(unsigned)blocks, tpg * groups, smem, stream>>>(x, rows, n_inputs, reinterpret_cast<const int2 *>(anchors),
                                                           n_detectors, n_anchors, cmp_eps, tpg, idx, min_delta, min_k);
     LUTB_LAUNCH_CHECK();
     return LUTB_OK;
@@ -201,15 +216,16 @@ int launch_check_detectors(const float *x, int64_t rows, int n_inputs, const int
     }
     int groups = 256 / tpg;
     while (groups > 1 && ((size_t)groups * R * row_bytes > budget || rows < (int64_t)groups * R * 2 * sm)) groups >>= 1;
-    // small batches: split the detectors over blockIdx.y until there are ~2 blocks per SM
+    // one block per row tile; small batches: two blocks per SM, each with an equal share of the (tile, detector chunk)
+    // work items
     const int64_t row_tiles = (rows + (int64_t)groups * R - 1) / ((int64_t)groups * R);
-    const int max_slices = (n_detectors + tpg - 1) / tpg;
-    const int det_slices = (int)max((int64_t)1, min((int64_t)max_slices, ((int64_t)2 * sm + row_tiles - 1) / row_tiles));
+    const int64_t items = row_tiles * ((n_detectors + tpg - 1) / tpg);
+    const int64_t blocks = row_tiles >= (int64_t)2 * sm ? row_tiles : min(items, (int64_t)2 * sm);
     switch (R) {
-        case 8: return launch_check_detectors_r<8>(x, rows, n_inputs, anchors, n_detectors, n_anchors, cmp_eps, idx, min_delta, min_k, tpg, groups, det_slices, stream);
-        case 4: return launch_check_detectors_r<4>(x, rows, n_inputs, anchors, n_detectors, n_anchors, cmp_eps, idx, min_delta, min_k, tpg, groups, det_slices, stream);
-        case 2: return launch_check_detectors_r<2>(x, rows, n_inputs, anchors, n_detectors, n_anchors, cmp_eps, idx, min_delta, min_k, tpg, groups, det_slices, stream);
-        default: return launch_check_detectors_r<1>(x, rows, n_inputs, anchors, n_detectors, n_anchors, cmp_eps, idx, min_delta, min_k, tpg, groups, det_slices, stream);
+        case 8: return launch_check_detectors_r<8>(x, rows, n_inputs, anchors, n_detectors, n_anchors, cmp_eps, idx, min_delta, min_k, tpg, groups, blocks, stream);
+        case 4: return launch_check_detectors_r<4>(x, rows, n_inputs, anchors, n_detectors, n_anchors, cmp_eps, idx, min_delta, min_k, tpg, groups, blocks, stream);
+        case 2: return launch_check_detectors_r<2>(x, rows, n_inputs, anchors, n_detectors, n_anchors, cmp_eps, idx, min_delta, min_k, tpg, groups, blocks, stream);
+        default: return launch_check_detectors_r<1>(x, rows, n_inputs, anchors, n_detectors, n_anchors, cmp_eps, idx, min_delta, min_k, tpg, groups, blocks, stream);
     }
 }
 
