@@ -282,6 +282,21 @@ int lutb_product_forward(const lutb_layer_cfg *cfg, int64_t batch, int32_t seq_l
 #define LUTB_PRODUCT_DIRECT 1
 #define LUTB_PRODUCT_HIST 2
 #define LUTB_PRODUCT_HIST_FMA 3
+/*
+ * Flags or'ed into `variant` (training: the backward pass needs the same row histogram the forward pass has just
+ * counted).  KEEP_HIST on lutb_product_forward: lay the workspace out as lutb_product_backward does and leave the
+ * histogram in it.  REUSE_HIST on lutb_product_backward: the caller vouches that `workspace` is the one such a forward
+ * call over the SAME x1, x2, positional embeddings and anchors used, untouched since: the pass skips its own counting.
+ * Both only take effect when the histogram path runs and the whole batch goes through in one pass;
+ * lutb_product_keeps_histogram(cfg, batch, S, n_inputs_1, n_inputs_2, variant, workspace, workspace_bytes) returns 1
+ * exactly then (same variant, workspace pointer and size as the two calls; a workspace of
+ * lutb_product_workspace(cfg, batch, S, 1) bytes qualifies whenever the histogram path is chosen).  Otherwise the
+ * flags are ignored.
+ */
+#define LUTB_PRODUCT_KEEP_HIST 0x100
+#define LUTB_PRODUCT_REUSE_HIST 0x200
+int lutb_product_keeps_histogram(const lutb_layer_cfg *cfg, int64_t batch, int32_t seq_len, int32_t n_inputs_1,
+                                 int32_t n_inputs_2, int variant, void *workspace, size_t workspace_bytes);
 size_t lutb_product_workspace(const lutb_layer_cfg *cfg, int64_t batch, int32_t seq_len, int backward);
 
 /*

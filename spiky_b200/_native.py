@@ -14,6 +14,7 @@ DW_AUTO, DW_ATOMIC, DW_SORTED = 0, 1, 3
 SKIP_TABLE_GRADIENT = -2.0  # external_lr value: input gradient only (lutb_nonseq_sparse_backward)
 # product-mode kernel variants (include/spiky_b200.h)
 PRODUCT_AUTO, PRODUCT_DIRECT, PRODUCT_HIST, PRODUCT_HIST_FMA = 0, 1, 2, 3
+PRODUCT_KEEP_HIST, PRODUCT_REUSE_HIST = 0x100, 0x200   # flags or'ed into the variant
 # de-quantisation rules of the int8 inference path (include/spiky_b200.h)
 INT8_DEQUANT_F32, INT8_DEQUANT_EXACT = 0, 1
 # kernel family of the sparse forward / input-gradient passes (include/spiky_b200.h)
@@ -95,6 +96,7 @@ SIGNATURES = {
                                     _int, _vp, _size, _vp]),
     "lutb_product_backward": (_int, [_cfgp, _i64, ctypes.c_int32, _vp, _vp, _vp, ctypes.c_int32, ctypes.c_int32, _vp, _vp,
                                      _vp, _vp, _vp, _vp, _vp, _dbl, _int, _vp, _size, _vp]),
+    "lutb_product_keeps_histogram": (_int, [_cfgp, _i64, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, _int, _vp, _size]),
     "lutb_nonseq_fc_table_grad_rows_workspace": (_size, [_cfgp, _i64]),
     "lutb_nonseq_fc_table_grad_rows": (_int, [_cfgp, _i64, _vp, _vp, _vp, _vp, _i64, _vp, _vp, _size, _vp]),
     "lutb_nonseq_fc_backward_noalloc": (_int, [_cfgp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _dbl, _vp]),

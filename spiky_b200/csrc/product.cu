@@ -331,6 +331,20 @@ extern "C" size_t lutb_product_workspace(const lutb_layer_cfg *cfg, int64_t batc
     return product_hist_workspace_bytes(cfg, batch, seq_len, backward != 0);
 }
 
+extern "C" int lutb_product_keeps_histogram(const lutb_layer_cfg *cfg, int64_t batch, int32_t seq_len, int32_t n_inputs_1,
+                                            int32_t n_inputs_2, int variant, void *workspace, size_t workspace_bytes) {
+    if (validate_product(cfg, batch, seq_len, n_inputs_1, n_inputs_2) != LUTB_OK) return 0;
+    variant &= ~(LUTB_PRODUCT_KEEP_HIST | LUTB_PRODUCT_REUSE_HIST);
+    const ProductCall call{cfg, batch, seq_len, n_inputs_1, n_inputs_2, nullptr, nullptr, nullptr, nullptr};
+    bool hist_f = false, hist_b = false, tc_f = true, tc_b = true;
+    // both passes must take the histogram path with this workspace (tensor alignment is the caller's to keep)
+    const void *aligned = reinterpret_cast<const void *>((uintptr_t)256);
+    if (choose_variant(call, variant, false, aligned, aligned, nullptr, workspace, workspace_bytes, hist_f, tc_f) != LUTB_OK) return 0;
+    if (choose_variant(call, variant, true, aligned, aligned, aligned, workspace, workspace_bytes, hist_b, tc_b) != LUTB_OK) return 0;
+    if (!hist_f || !hist_b) return 0;
+    return product_hist_keeps(call, tc_f, workspace, workspace_bytes) ? 1 : 0;
+}
+
 extern "C" int lutb_product_forward(const lutb_layer_cfg *cfg, int64_t batch, int32_t seq_len, const float *weights,
                                     const float *x1, const float *x2, int32_t n_inputs_1, int32_t n_inputs_2,
                                     const float *pos_embeddings, const int32_t *anchors, float *y, int variant,
@@ -342,9 +356,11 @@ extern "C" int lutb_product_forward(const lutb_layer_cfg *cfg, int64_t batch, in
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const ProductCall call{cfg, batch, seq_len, n_inputs_1, n_inputs_2, x1, x2, pos_embeddings, anchors};
     bool hist = false, allow_tc = true;
+    const bool keep = (variant & LUTB_PRODUCT_KEEP_HIST) != 0;
+    variant &= ~(LUTB_PRODUCT_KEEP_HIST | LUTB_PRODUCT_REUSE_HIST);
     rc = choose_variant(call, variant, false, weights, y, nullptr, workspace, workspace_bytes, hist, allow_tc);
     if (rc) return rc;
-    if (hist) return launch_product_hist_forward(call, weights, y, allow_tc, workspace, workspace_bytes, st);
+    if (hist) return launch_product_hist_forward(call, weights, y, allow_tc, workspace, workspace_bytes, st, keep);
     if (seq_len > 1) {
         const int warps = 8;
         const size_t smem = (pair_stage_floats(seq_len, cfg->n_anchors, cfg->pos_dim) + (size_t)warps * seq_len) * 4;
@@ -382,11 +398,13 @@ extern "C" int lutb_product_backward(const lutb_layer_cfg *cfg, int64_t batch, i
     if (external_lr >= 0.0) lr *= -(double)(float)external_lr;
     const ProductCall call{cfg, batch, seq_len, n_inputs_1, n_inputs_2, x1, x2, pos_embeddings, anchors};
     bool hist = false, allow_tc = true;
+    const bool reuse = (variant & LUTB_PRODUCT_REUSE_HIST) != 0;
+    variant &= ~(LUTB_PRODUCT_KEEP_HIST | LUTB_PRODUCT_REUSE_HIST);
     rc = choose_variant(call, variant, true, weights, dY, dW, workspace, workspace_bytes, hist, allow_tc);
     if (rc) return rc;
     if (hist)
         return launch_product_hist_backward(call, weights, dY, dX1, dX2, dPE, external_lr >= 0.0 ? weights : dW, lr,
-                                            external_lr >= 0.0, allow_tc, workspace, workspace_bytes, st);
+                                            external_lr >= 0.0, allow_tc, workspace, workspace_bytes, st, reuse);
     if (seq_len > 1) {
         if (cfg->int_mode) {
             const int64_t total = batch * seq_len * (int64_t)Nt * seq_len;

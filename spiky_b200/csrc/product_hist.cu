@@ -79,7 +79,11 @@ __global__ void __launch_bounds__(512) product_hist_kernel(const float *__restri
 // (product_pairs.cuh, MixedPlan); 0: plain eval_pair.  The plan costs about 5 registers per anchor: it pays where the
 // block's shared memory already limits an SM to one block (tables of 1024 rows and more: 257 against 286 ms per step on
 // the 2048-token configuration) and loses where it takes the second block away (256-row tables: 5.1 against 3.5 ms).
-template <bool SMEM_ACC, int MAXM>
+// HIST: the kernel evaluates every pair anyway, so it can count the selected rows on the way and write the histogram
+// the table-gradient contraction needs (1: uint16 [detector][row of the chunk][T], 2: fp32 [row of the chunk][detector][T],
+// the layouts of product_hist_kernel); the backward pass then launches no histogram kernel of its own.  Used where the
+// extra T counters per warp do not cost the block its occupancy.
+template <bool SMEM_ACC, int MAXM, int HIST>
 __global__ void __launch_bounds__(512) product_route_kernel(const float *__restrict__ x1, const float *__restrict__ x2,
                                                            const float *__restrict__ pe,
                                                            const int32_t *__restrict__ anchors,
@@ -87,7 +91,7 @@ __global__ void __launch_bounds__(512) product_route_kernel(const float *__restr
                                                            float *__restrict__ dX2, float *__restrict__ dPE, int64_t b0,
                                                            int64_t q_row_stride, int64_t q_det_stride, int S, int e1,
                                                            int e2, int npe, int n_detectors, int n_anchors, int sliced,
-                                                           float cmp_eps) {
+                                                           float cmp_eps, void *__restrict__ Hout, int64_t chunk_rows) {
     extern __shared__ __align__(16) float smem[];
     const int t = blockIdx.x;
     const int64_t bl = blockIdx.y, b = b0 + bl;
@@ -97,8 +101,13 @@ __global__ void __launch_bounds__(512) product_route_kernel(const float *__restr
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
     const int T = 1 << n_anchors;
     const int ends = 2 * n_anchors;
-    const int per_warp = T + 32 * ends;
+    const int per_warp = T + 32 * ends + (HIST ? T : 0);
     float *q_s = st.scratch + warp * per_warp;
+    uint32_t *hist = reinterpret_cast<uint32_t *>(q_s + T + 32 * ends);
+    if (HIST) {
+        for (int r = lane; r < T; r += 32) hist[r] = 0u;
+        __syncwarp();
+    }
     // contributions to the query token j: a private column per lane ([end][lane], plain read-modify-write; every
     // lane of a pair batch would otherwise hit the same few cells), summed over the lanes once per query
     float *jacc = q_s + T;
@@ -110,7 +119,7 @@ __global__ void __launch_bounds__(512) product_route_kernel(const float *__restr
     }
     MixedPlan<MAXM == 0 ? 1 : MAXM> mp;
     if (MAXM > 0) mp.load(st);
-    for (int j = 1 + warp; j < S; j += nwarps) {
+    for (int j = (HIST ? 0 : 1) + warp; j < S; j += nwarps) {   // (query 0 has no pair: only its empty histogram row)
         QueryPart qp{0u, 0.f};
         if (MAXM > 0) {
             mp.set_query(st, j);
@@ -127,13 +136,18 @@ __global__ void __launch_bounds__(512) product_route_kernel(const float *__restr
             int k; float d;
             const int32_t li = MAXM > 0 ? eval_pair_planned<true, (MAXM == 0 ? 1 : MAXM)>(st, mp, qp, i, j, cmp_eps, k, d)
                                         : eval_pair<true>(st, n_anchors, i, j, cmp_eps, k, d);
+            if (HIST) atomicAdd(hist + li, 1u);
             if (k < 0) continue;
-            const double du = surrogate_up(d) * (double)(q_s[li] - q_s[li ^ (1 << k)]);
-            if (!(fabs(du) > kEps)) continue;
+            // up(d) * (Q[row] - Q[flipped row]) in fp32: Q is an fp32 contraction already, and the double-precision
+            // reciprocal of the reference's formula was the most expensive part of a pair (the direct kernels and the
+            // fixed-point mode keep it)
+            const float rcp = __frcp_rn(1.0f + fabsf(d));
+            const float du = (d > 0.f ? 0.5f : -0.5f) * rcp * rcp * (q_s[li] - q_s[li ^ (1 << k)]);
+            if (!(fabsf(du) > kEpsF)) continue;
 #pragma unroll
             for (int e = 0; e < 2; e++) {
                 const int comp = st.comp[2 * k + e], elem = st.elem[2 * k + e];
-                const float val = e == 0 ? (float)du : (float)(-du);
+                const float val = e == 0 ? du : -du;
                 if (comp == 0) {
                     if (SMEM_ACC) atomicAdd(tacc + i * ends + 2 * k + e, val);
                     else atomicAdd(dX1 + ((size_t)b * S + i) * e1 + elem, val);
@@ -156,6 +170,30 @@ __global__ void __launch_bounds__(512) product_route_kernel(const float *__restr
             }
         }
         __syncwarp();
+        if (HIST == 2) {
+            float *out = static_cast<float *>(Hout) + ((size_t)(bl * S + j) * n_detectors + t) * T;
+            for (int r = lane * 4; r < T; r += 128) {
+                const uint4 c = *reinterpret_cast<const uint4 *>(hist + r);
+                *reinterpret_cast<float4 *>(out + r) = make_float4((float)c.x, (float)c.y, (float)c.z, (float)c.w);
+                *reinterpret_cast<uint4 *>(hist + r) = make_uint4(0u, 0u, 0u, 0u);
+            }
+            __syncwarp();
+        } else if (HIST == 1) {
+            uint16_t *out = static_cast<uint16_t *>(Hout) + ((size_t)t * chunk_rows + bl * S + j) * T;
+            for (int r = lane * 8; r < T; r += 256) {
+                const uint4 lo = *reinterpret_cast<const uint4 *>(hist + r);
+                const uint4 hi = *reinterpret_cast<const uint4 *>(hist + r + 4);
+                uint4 packed;
+                packed.x = lo.x | (lo.y << 16);
+                packed.y = lo.z | (lo.w << 16);
+                packed.z = hi.x | (hi.y << 16);
+                packed.w = hi.z | (hi.w << 16);
+                *reinterpret_cast<uint4 *>(out + r) = packed;
+                *reinterpret_cast<uint4 *>(hist + r) = make_uint4(0u, 0u, 0u, 0u);
+                *reinterpret_cast<uint4 *>(hist + r + 4) = make_uint4(0u, 0u, 0u, 0u);
+            }
+            __syncwarp();
+        }
     }
     if (SMEM_ACC) {
         __syncthreads();
@@ -401,10 +439,14 @@ static size_t bytes_per_sequence(const lutb_layer_cfg *cfg, int S, bool backward
 // the operands (the tables, and the output gradients in the backward pass); the largest of the calls the pass makes.
 static size_t tc_scratch_bytes(const lutb_layer_cfg *cfg, int64_t rows, bool backward) {
     const int KT = cfg->n_detectors << cfg->n_anchors, O = cfg->n_outputs;
-    if (!backward) return align256(tc_gemm_workspace(TC_A_ROWS_B_ROWS_OF_K, (int)rows, O, KT, true));
+    const size_t fwd = tc_gemm_workspace(TC_A_ROWS_B_ROWS_OF_K, (int)rows, O, KT, true);
+    if (!backward) return align256(fwd);
+    // (the forward contraction's scratch counts here too: a forward pass that leaves its histogram for the backward
+    // pass lays the workspace out as the backward pass does)
     const size_t dw = tc_gemm_workspace(TC_A_COLS_B_ROWS_OF_K, KT, O, (int)rows, true),
                  q = tc_gemm_workspace(TC_A_ROWS_B_ROWS_OF_N, (int)rows, KT, O, false);
-    return align256(dw > q ? dw : q);
+    const size_t m = dw > q ? dw : q;
+    return align256(m > fwd ? m : fwd);
 }
 
 size_t product_hist_workspace_bytes(const lutb_layer_cfg *cfg, int64_t batch, int S, bool backward) {
@@ -477,10 +519,20 @@ static int launch_hist(const ProductCall &c, const HistPlan &p, int64_t b0, int6
     return LUTB_OK;
 }
 
-int launch_product_hist_forward(const ProductCall &c, const float *weights, float *y, bool allow_tc, void *workspace,
-                                size_t workspace_bytes, cudaStream_t stream) {
+bool product_hist_keeps(const ProductCall &c, bool allow_tc, void *workspace, size_t workspace_bytes) {
     HistPlan p;
-    int rc = plan(c, false, allow_tc, workspace, workspace_bytes, p);
+    if (workspace == nullptr || workspace_bytes < product_hist_workspace_bytes(c.cfg, 1, c.S, true)) return false;
+    if (plan(c, true, allow_tc, workspace, workspace_bytes, p) != LUTB_OK) return false;
+    return p.chunk == c.batch;
+}
+
+int launch_product_hist_forward(const ProductCall &c, const float *weights, float *y, bool allow_tc, void *workspace,
+                                size_t workspace_bytes, cudaStream_t stream, bool keep) {
+    HistPlan p;
+    // keep: the workspace is laid out as the backward pass lays it out, so that the histogram stays where that pass
+    // looks for it (only when the whole batch goes through in one pass; otherwise the forward pass's own layout)
+    const bool as_backward = keep && product_hist_keeps(c, allow_tc, workspace, workspace_bytes);
+    int rc = plan(c, as_backward, allow_tc, workspace, workspace_bytes, p);
     if (rc) return rc;
     const lutb_layer_cfg *cfg = c.cfg;
     const int T = 1 << cfg->n_anchors, O = cfg->n_outputs, Nt = cfg->n_detectors;
@@ -511,10 +563,13 @@ int launch_product_hist_forward(const ProductCall &c, const float *weights, floa
 
 int launch_product_hist_backward(const ProductCall &c, const float *weights, const float *dY, float *dX1, float *dX2,
                                  float *dPE, float *target, double lr, bool in_place, bool allow_tc, void *workspace,
-                                 size_t workspace_bytes, cudaStream_t stream) {
+                                 size_t workspace_bytes, cudaStream_t stream, bool reuse) {
     HistPlan p;
     int rc = plan(c, true, allow_tc, workspace, workspace_bytes, p);
     if (rc) return rc;
+    // reuse: the caller vouches that the workspace still holds the histogram a forward pass over the same inputs left
+    // there; it is complete only when the whole batch is one pass
+    const bool have_hist = reuse && p.chunk == c.batch;
     const lutb_layer_cfg *cfg = c.cfg;
     const int T = 1 << cfg->n_anchors, O = cfg->n_outputs, Nt = cfg->n_detectors;
     const int route_warps = pair_block_warps(c, (size_t)T + 64 * cfg->n_anchors);
@@ -526,6 +581,10 @@ int launch_product_hist_backward(const ProductCall &c, const float *weights, con
     // In-place SGD reads unmodified tables for every input gradient: with more than one chunk the table update
     // runs as a second sweep over the chunks.
     const bool second_sweep = in_place && p.chunk < c.batch;
+    // the routing kernel counts the rows itself where T more counters per warp still leave room for two blocks per SM
+    const bool fuse_hist = !have_hist && !second_sweep && smem_acc && cfg->n_anchors <= 8 &&
+                           route_smem + (size_t)route_warps * T * 4 <= 100 * 1024;
+    if (fuse_hist) route_smem += (size_t)route_warps * T * 4;
     auto table_gradient = [&](int64_t b0, int64_t rows) -> int {
         if (p.tc) {
             // target[Nt*T, O] += lr * H^T . dY  (H stored [rows, Nt*T])
@@ -550,8 +609,10 @@ int launch_product_hist_backward(const ProductCall &c, const float *weights, con
     for (int64_t b0 = 0; b0 < c.batch; b0 += p.chunk) {
         const int64_t n = (c.batch - b0 < p.chunk) ? c.batch - b0 : p.chunk;
         const int64_t rows = n * c.S;
-        rc = launch_hist(c, p, b0, n, stream);
-        if (rc) return rc;
+        if (!fuse_hist && !have_hist) {
+            rc = launch_hist(c, p, b0, n, stream);
+            if (rc) return rc;
+        }
         if (p.tc) {
             // Q[rows, Nt*T] = dY[rows, O] . W^T  (W stored [Nt*T, O])
             KernelScope scope(K_PRODUCT_ROW_DOTS, stream);
@@ -578,14 +639,15 @@ int launch_product_hist_backward(const ProductCall &c, const float *weights, con
                     LUTB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)route_smem));
                 kern<<<grid, route_warps * 32, route_smem, stream>>>(c.x1, c.x2, c.pe, c.anchors, p.Q, dX1, dX2, dPE, b0, q_row_stride,
                                                                      q_det_stride, c.S, c.e1, c.e2, cfg->pos_dim, Nt, cfg->n_anchors,
-                                                                     cfg->sliced_product, cfg->cmp_eps);
+                                                                     cfg->sliced_product, cfg->cmp_eps, p.H, n * c.S);
                 return LUTB_OK;
             };
             const int na = cfg->n_anchors;
-            if (smem_acc) rc = na <= 8 ? launch(product_route_kernel<true, 0>) : na <= 12 ? launch(product_route_kernel<true, 12>)
-                                                                                          : launch(product_route_kernel<true, 16>);
-            else rc = na <= 8 ? launch(product_route_kernel<false, 0>) : na <= 12 ? launch(product_route_kernel<false, 12>)
-                                                                                   : launch(product_route_kernel<false, 16>);
+            if (fuse_hist) rc = p.tc ? launch(product_route_kernel<true, 0, 2>) : launch(product_route_kernel<true, 0, 1>);
+            else if (smem_acc) rc = na <= 8 ? launch(product_route_kernel<true, 0, 0>) : na <= 12 ? launch(product_route_kernel<true, 12, 0>)
+                                                                                                  : launch(product_route_kernel<true, 16, 0>);
+            else rc = na <= 8 ? launch(product_route_kernel<false, 0, 0>) : na <= 12 ? launch(product_route_kernel<false, 12, 0>)
+                                                                                      : launch(product_route_kernel<false, 16, 0>);
             if (rc) return rc;
             LUTB_LAUNCH_CHECK();
         }

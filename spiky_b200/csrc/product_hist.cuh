@@ -32,11 +32,14 @@ size_t product_hist_workspace_bytes(const lutb_layer_cfg *cfg, int64_t batch, in
 
 // allow_tc: run the contractions on the tensor cores (fp32_gemm_sm100.cuh) when the library has them and the workspace
 // holds at least one sequence in their operand layout; otherwise, and when false, the fp32 FMA contraction runs.
+// keep: leave the row histogram in the workspace where launch_product_hist_backward(..., reuse = true) finds it
+// (product_hist_keeps tells whether a workspace of that size allows it: the whole batch must be one pass).
+bool product_hist_keeps(const ProductCall &c, bool allow_tc, void *workspace, size_t workspace_bytes);
 int launch_product_hist_forward(const ProductCall &c, const float *weights, float *y, bool allow_tc, void *workspace,
-                                size_t workspace_bytes, cudaStream_t stream);
+                                size_t workspace_bytes, cudaStream_t stream, bool keep = false);
 // target: dW (external gradients) or the tables themselves (in-place SGD: all input gradients first).
 int launch_product_hist_backward(const ProductCall &c, const float *weights, const float *dY, float *dX1, float *dX2,
                                  float *dPE, float *target, double lr, bool in_place, bool allow_tc, void *workspace,
-                                 size_t workspace_bytes, cudaStream_t stream);
+                                 size_t workspace_bytes, cudaStream_t stream, bool reuse = false);
 
 }  // namespace lutb

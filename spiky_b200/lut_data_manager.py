@@ -402,7 +402,11 @@ class _LUTDataManager:
     # ------------------------------------------------------------------ product-mode sequence runtime
     def forward_step_product(self, r_weights, batch_size, sequence_length, r_input_1, r_input_2, r_detector_anchors,
                              w_output, n_inputs_1, n_inputs_2, sliced_mode, cmp_eps=0.0, r_positional_embeddings=None,
-                             r_stream_handles=None, variant=_native.PRODUCT_AUTO):
+                             r_stream_handles=None, variant=_native.PRODUCT_AUTO, keep_histogram=False):
+        """keep_histogram (not in the reference): the caller will run backward_backprop_product on the same inputs
+        next (a training step); the row histogram this pass counts is then left in a workspace of its own and the
+        backward pass does not count it again.  Only where the whole batch fits one pass within
+        ``product_keep_limit`` bytes; silently off otherwise."""
         self._require_cuda()
         dev = self._device
         _check_tensor(r_weights, "r_weights", True, dev)
@@ -431,14 +435,39 @@ class _LUTDataManager:
                 raise ValueError("r_positional_embeddings is required when positional_dim > 0")
             self._expect(r_positional_embeddings, (S - 1) * self._n_detectors * self._pos_dim, "r_positional_embeddings")
         cfg = self._cfg(cmp_eps, sliced=sliced_mode)
+        self._kept_histogram = None
         with torch.cuda.device(dev):
             ws, ws_bytes = self._product_workspace(cfg, B, S, False, variant, r_weights.device)
+            flags = 0
+            if keep_histogram and ws is not None:
+                L = _native.lib()
+                want = L.lutb_product_workspace(ctypes.byref(cfg), B, S, 1)
+                if 0 < want <= _LUTDataManager.product_keep_limit:
+                    own = torch.empty(want, dtype=torch.uint8, device=r_weights.device)
+                    if L.lutb_product_keeps_histogram(ctypes.byref(cfg), B, S, int(n_inputs_1), int(n_inputs_2),
+                                                      int(variant), _ptr(own), want):
+                        ws, ws_bytes, flags = own, want, _native.PRODUCT_KEEP_HIST
+                        self._kept_histogram = (own, self._histogram_key(
+                            B, S, r_input_1, r_input_2, r_detector_anchors, r_positional_embeddings, n_inputs_1,
+                            n_inputs_2, sliced_mode, cmp_eps, variant))
             rc = _native.lib().lutb_product_forward(
                 ctypes.byref(cfg), B, S, _ptr(r_weights), _ptr(r_input_1), _ptr(r_input_2), int(n_inputs_1),
                 int(n_inputs_2), _ptr(r_positional_embeddings), _ptr(r_detector_anchors), _ptr(w_output),
-                int(variant), _ptr(ws), ws_bytes, self._stream())
+                int(variant) | flags, _ptr(ws), ws_bytes, self._stream())
         _native.check(rc)
         self._forward_seen = True
+
+    _kept_histogram = None
+    # largest workspace a forward pass may hold on to until its backward pass (per layer)
+    product_keep_limit = 2 << 30
+
+    @staticmethod
+    def _histogram_key(B, S, x1, x2, anchors, pe, e1, e2, sliced, cmp_eps, variant):
+        """What the row histogram depends on: the inputs (storage and version), anchors, embeddings and geometry."""
+        def ident(t):
+            return None if t is None else (t.data_ptr(), t._version, t.numel())
+        return (B, S, ident(x1), ident(x2), ident(anchors), ident(pe), int(e1), int(e2), bool(sliced), float(cmp_eps),
+                int(variant))
 
     def backward_backprop_product(self, r_weights, batch_size, sequence_length, r_input_1, r_input_2,
                                   r_detector_anchors, r_output_gradients, w_input_gradients_1, w_input_gradients_2,
@@ -469,8 +498,14 @@ class _LUTDataManager:
         self._expect(w_input_gradients_1, B * S * n_inputs_1, "w_input_gradients_1")
         self._expect(w_input_gradients_2, B * S * n_inputs_2, "w_input_gradients_2")
         cfg = self._cfg(cmp_eps, sliced=sliced_mode)
+        kept, self._kept_histogram = self._kept_histogram, None
         with torch.cuda.device(dev):
             ws, ws_bytes = self._product_workspace(cfg, B, S, True, variant, r_weights.device)
+            if kept is not None and kept[1] == self._histogram_key(
+                    B, S, r_input_1, r_input_2, r_detector_anchors, r_positional_embeddings, n_inputs_1, n_inputs_2,
+                    sliced_mode, cmp_eps, variant):
+                # the forward pass over these very inputs left its histogram in this workspace
+                ws, ws_bytes, variant = kept[0], kept[0].numel(), int(variant) | _native.PRODUCT_REUSE_HIST
             rc = _native.lib().lutb_product_backward(
                 ctypes.byref(cfg), B, S, _ptr(r_weights), _ptr(r_input_1), _ptr(r_input_2), int(n_inputs_1),
                 int(n_inputs_2), _ptr(r_positional_embeddings), _ptr(r_detector_anchors), _ptr(r_output_gradients),

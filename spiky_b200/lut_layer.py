@@ -650,7 +650,8 @@ class LUTLayerBasic(nn.Module):
         self._lut_dm.forward_step_product(self._weights.detach(), B, S, xf, xf, self._detector_anchors, output,
                                           self._n_inputs, self._n_inputs, self._sliced_product_mode,
                                           self._shared_context._cmp_eps, pe, None,
-                                          variant=getattr(self, "_product_variant", 0))
+                                          variant=getattr(self, "_product_variant", 0),
+                                          keep_histogram=self.training)
         return None if external else output.view((B, S) + tuple(self.output_shape()))
 
     def backward_step_product(self, x, pos_embeddings, grad_output, x_grad=None):

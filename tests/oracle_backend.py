@@ -132,7 +132,7 @@ class OracleDataManager:
 
     def forward_step_product(self, r_weights, batch_size, sequence_length, r_input_1, r_input_2, r_detector_anchors,
                              w_output, n_inputs_1, n_inputs_2, sliced_mode, cmp_eps=0.0, r_positional_embeddings=None,
-                             r_stream_handles=None, variant=0):
+                             r_stream_handles=None, variant=0, keep_histogram=False):
         r = self._real
         assert r_input_1.data_ptr() == r_input_2.data_ptr() and n_inputs_1 == n_inputs_2
         x = _np(r_input_1).reshape(batch_size, sequence_length, n_inputs_1)

@@ -143,13 +143,14 @@ def test_product_histogram_chunks_match_single_pass():
         cfg = ORACLE_CASES[name]
         x, anchors, W, pe, dY = inputs_for(cfg)
         full = run_gpu(cfg, x, anchors, W, pe, dY, 2)
-        saved = _LUTDataManager.product_scratch_limit
+        saved = _LUTDataManager.product_scratch_limit, _LUTDataManager.product_keep_limit
         _LUTDataManager.product_scratch_limit = 0
+        _LUTDataManager.product_keep_limit = 0   # (a forward pass that keeps its histogram takes the whole batch at once)
         _LUTDataManager._product_scratch.clear()
         try:
             chunked = run_gpu(cfg, x, anchors, W, pe, dY, 2)
         finally:
-            _LUTDataManager.product_scratch_limit = saved
+            _LUTDataManager.product_scratch_limit, _LUTDataManager.product_keep_limit = saved
             _LUTDataManager._product_scratch.clear()
         for k in full:
             golden_util.assert_close(chunked[k], full[k], REL, f"{name}.{k}")
@@ -177,3 +178,53 @@ def test_product_autograd_unified_pe():
     golden_util.assert_close(layer._weights.grad.cpu().numpy(), dW, REL, "dW")
     want = dPE.reshape(cfg["S"] - 1, cfg["Nt"], cfg["Npe"]).sum(axis=1).reshape(-1)
     golden_util.assert_close(layer._positional_embeddings.grad.cpu().numpy(), want, REL, "dPE (summed over detectors)")
+
+
+@pytest.mark.parametrize("variant", [2, 3], ids=["tensor_cores", "fma"])
+def test_backward_reuses_the_histogram_of_the_forward_pass(variant):
+    """Training: the forward pass leaves its row histogram for the backward pass (KEEP / REUSE flags of the C ABI).  Same
+    results as when the backward pass counts the rows itself; the workspace is held exactly from forward to backward."""
+    import ctypes
+    from spiky_b200 import _native
+    from spiky_b200.lut_data_manager import _LUTDataManager
+
+    cfg = ORACLE_CASES["c3_attention"]
+    x, anchors, W, pe, dY = inputs_for(cfg)
+    seen = {}
+
+    def spy(layer):
+        dm = layer._lut_dm
+        fwd = dm.forward_step_product
+
+        def wrapped(*a, **k):
+            fwd(*a, **k)
+            seen["kept"] = dm._kept_histogram is not None
+        dm.forward_step_product = wrapped
+        seen["dm"] = dm
+
+    kept = run_gpu(cfg, x, anchors, W, pe, dY, variant, prepare=spy)
+    assert seen["kept"] and seen["dm"]._kept_histogram is None   # held after forward, released by backward
+    saved = _LUTDataManager.product_keep_limit
+    _LUTDataManager.product_keep_limit = 0
+    try:
+        plain = run_gpu(cfg, x, anchors, W, pe, dY, variant, prepare=spy)
+    finally:
+        _LUTDataManager.product_keep_limit = saved
+    assert not seen["kept"]
+    assert np.array_equal(kept["y"], plain["y"])
+    assert np.array_equal(kept["dW"], plain["dW"])   # same integer counts into the same contraction
+    golden_util.assert_close(kept["dX"], plain["dX"], 1e-6, "dX")   # (shared-memory atomics: order of the adds varies)
+    golden_util.assert_close(kept["dPE"], plain["dPE"], 1e-6, "dPE")
+    # the C ABI's own statement of when the flags take effect
+    dm = seen["dm"]
+    c = dm._cfg(0.0, sliced=False)
+    L = _native.lib()
+    full = L.lutb_product_workspace(ctypes.byref(c), cfg["B"], cfg["S"], 1)
+    one = L.lutb_product_workspace(ctypes.byref(c), 1, cfg["S"], 1)
+    buf = torch.empty(full, dtype=torch.uint8, device="cuda")
+    e = cfg["E"]
+    assert L.lutb_product_keeps_histogram(ctypes.byref(c), cfg["B"], cfg["S"], e, e, variant, buf.data_ptr(), full) == 1
+    # room for one sequence only (the FMA contraction's uint16 counters are half the size: two of them fit `one`)
+    small = one if variant == 2 else one // 3
+    assert L.lutb_product_keeps_histogram(ctypes.byref(c), cfg["B"], cfg["S"], e, e, variant, buf.data_ptr(), small) == 0
+    assert L.lutb_product_keeps_histogram(ctypes.byref(c), cfg["B"], cfg["S"], e, e, 1, buf.data_ptr(), full) == 0
