@@ -125,7 +125,7 @@ __device__ void block_range(const StagedArgs &a, int64_t *lo, int64_t *hi) {
         const long long t_lo = total * blockIdx.x / gridDim.x, t_hi = total * (blockIdx.x + 1) / gridDim.x;
         if (lane == 0) { s_border[0] = a.total_slots; s_border[1] = a.total_slots; }
         __syncwarp();
-        long long run = 0;   // cost of all items before this round
+        long long run = 0;   // cost of all items before this group of 32
         for (int64_t base = 0; base < n_items; base += 32) {
             const int64_t i = base + lane;
             const long long c = i < n_items ? s_cost[i] : 0;
