@@ -83,7 +83,9 @@ __global__ void __launch_bounds__(512) product_hist_kernel(const float *__restri
 // the table-gradient contraction needs (1: uint16 [detector][row of the chunk][T], 2: fp32 [row of the chunk][detector][T],
 // the layouts of product_hist_kernel); the backward pass then launches no histogram kernel of its own.  Used where the
 // extra T counters per warp do not cost the block its occupancy.
-template <bool SMEM_ACC, int MAXM, int HIST>
+// QG: the two entries of Q a pair needs are read from global memory (through L1) instead of from a staged copy of the
+// query's row: T floats less scratch per warp, on long sequences the difference between 8 and 16 warps per block.
+template <bool SMEM_ACC, int MAXM, int HIST, bool QG>
 __global__ void __launch_bounds__(512) product_route_kernel(const float *__restrict__ x1, const float *__restrict__ x2,
                                                            const float *__restrict__ pe,
                                                            const int32_t *__restrict__ anchors,
@@ -101,16 +103,17 @@ __global__ void __launch_bounds__(512) product_route_kernel(const float *__restr
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
     const int T = 1 << n_anchors;
     const int ends = 2 * n_anchors;
-    const int per_warp = T + 32 * ends + (HIST ? T : 0);
+    const int q_floats = QG ? 0 : T;
+    const int per_warp = q_floats + 32 * ends + (HIST ? T : 0);
     float *q_s = st.scratch + warp * per_warp;
-    uint32_t *hist = reinterpret_cast<uint32_t *>(q_s + T + 32 * ends);
+    uint32_t *hist = reinterpret_cast<uint32_t *>(q_s + q_floats + 32 * ends);
     if (HIST) {
         for (int r = lane; r < T; r += 32) hist[r] = 0u;
         __syncwarp();
     }
     // contributions to the query token j: a private column per lane ([end][lane], plain read-modify-write; every
     // lane of a pair batch would otherwise hit the same few cells), summed over the lanes once per query
-    float *jacc = q_s + T;
+    float *jacc = q_s + q_floats;
     float *tacc = st.scratch + nwarps * per_warp;  // [S][ends]
     float *pacc = tacc + S * ends;                            // [S-1][npe]
     if (SMEM_ACC) {
@@ -126,8 +129,9 @@ __global__ void __launch_bounds__(512) product_route_kernel(const float *__restr
             qp = query_part(st, j);
         }
         const float *qrow = Q + (size_t)t * q_det_stride + (size_t)(bl * S + j) * q_row_stride;
-        for (int r = lane * 4; r < T; r += 128)
-            *reinterpret_cast<float4 *>(q_s + r) = __ldcs(reinterpret_cast<const float4 *>(qrow + r));
+        if (!QG)
+            for (int r = lane * 4; r < T; r += 128)
+                *reinterpret_cast<float4 *>(q_s + r) = __ldcs(reinterpret_cast<const float4 *>(qrow + r));
         for (int q = 0; q < ends; q++) jacc[q * 32 + lane] = 0.f;
         __syncwarp();
         for (int i0 = 0; i0 < j; i0 += 32) {
@@ -142,7 +146,9 @@ __global__ void __launch_bounds__(512) product_route_kernel(const float *__restr
             // reciprocal of the reference's formula was the most expensive part of a pair (the direct kernels and the
             // fixed-point mode keep it)
             const float rcp = __frcp_rn(1.0f + fabsf(d));
-            const float du = (d > 0.f ? 0.5f : -0.5f) * rcp * rcp * (q_s[li] - q_s[li ^ (1 << k)]);
+            const float q_sel = QG ? __ldg(qrow + li) : q_s[li];
+            const float q_alt = QG ? __ldg(qrow + (li ^ (1 << k))) : q_s[li ^ (1 << k)];
+            const float du = (d > 0.f ? 0.5f : -0.5f) * rcp * rcp * (q_sel - q_alt);
             if (!(fabsf(du) > kEpsF)) continue;
 #pragma unroll
             for (int e = 0; e < 2; e++) {
@@ -572,17 +578,20 @@ int launch_product_hist_backward(const ProductCall &c, const float *weights, con
     const bool have_hist = reuse && p.chunk == c.batch;
     const lutb_layer_cfg *cfg = c.cfg;
     const int T = 1 << cfg->n_anchors, O = cfg->n_outputs, Nt = cfg->n_detectors;
-    const int route_warps = pair_block_warps(c, (size_t)T + 64 * cfg->n_anchors);
-    size_t route_smem = stage_bytes(c, (size_t)T + 64 * cfg->n_anchors, route_warps);
+    int route_warps = pair_block_warps(c, (size_t)T + 64 * cfg->n_anchors);
+    // long sequences: Q read from global memory when that is what gives the block 16 warps
+    const bool q_global = route_warps < 16 && pair_block_warps(c, (size_t)64 * cfg->n_anchors) == 16;
+    if (q_global) route_warps = 16;
+    size_t route_smem = stage_bytes(c, (q_global ? 0 : (size_t)T) + 64 * cfg->n_anchors, route_warps);
     const size_t acc_bytes = ((size_t)c.S * 2 * cfg->n_anchors + (size_t)(c.S - 1) * cfg->pos_dim) * 4;
     // block-level accumulators only while two blocks still fit an SM
-    const bool smem_acc = route_smem + acc_bytes <= 100 * 1024;
+    const bool smem_acc = !q_global && route_smem + acc_bytes <= 100 * 1024;
     if (smem_acc) route_smem += acc_bytes;
     // In-place SGD reads unmodified tables for every input gradient: with more than one chunk the table update
     // runs as a second sweep over the chunks.
     const bool second_sweep = in_place && p.chunk < c.batch;
     // the routing kernel counts the rows itself where T more counters per warp still leave room for two blocks per SM
-    const bool fuse_hist = !have_hist && !second_sweep && smem_acc && cfg->n_anchors <= 8 &&
+    const bool fuse_hist = !have_hist && !second_sweep && smem_acc && !q_global && cfg->n_anchors <= 8 &&
                            route_smem + (size_t)route_warps * T * 4 <= 100 * 1024;
     if (fuse_hist) route_smem += (size_t)route_warps * T * 4;
     auto table_gradient = [&](int64_t b0, int64_t rows) -> int {
@@ -643,11 +652,14 @@ int launch_product_hist_backward(const ProductCall &c, const float *weights, con
                 return LUTB_OK;
             };
             const int na = cfg->n_anchors;
-            if (fuse_hist) rc = p.tc ? launch(product_route_kernel<true, 0, 2>) : launch(product_route_kernel<true, 0, 1>);
-            else if (smem_acc) rc = na <= 8 ? launch(product_route_kernel<true, 0, 0>) : na <= 12 ? launch(product_route_kernel<true, 12, 0>)
-                                                                                                  : launch(product_route_kernel<true, 16, 0>);
-            else rc = na <= 8 ? launch(product_route_kernel<false, 0, 0>) : na <= 12 ? launch(product_route_kernel<false, 12, 0>)
-                                                                                      : launch(product_route_kernel<false, 16, 0>);
+            if (fuse_hist) rc = p.tc ? launch(product_route_kernel<true, 0, 2, false>) : launch(product_route_kernel<true, 0, 1, false>);
+            else if (q_global)
+                rc = na <= 8 ? launch(product_route_kernel<false, 0, 0, true>) : na <= 12 ? launch(product_route_kernel<false, 12, 0, true>)
+                                                                                          : launch(product_route_kernel<false, 16, 0, true>);
+            else if (smem_acc) rc = na <= 8 ? launch(product_route_kernel<true, 0, 0, false>) : na <= 12 ? launch(product_route_kernel<true, 12, 0, false>)
+                                                                                                         : launch(product_route_kernel<true, 16, 0, false>);
+            else rc = na <= 8 ? launch(product_route_kernel<false, 0, 0, false>) : na <= 12 ? launch(product_route_kernel<false, 12, 0, false>)
+                                                                                             : launch(product_route_kernel<false, 16, 0, false>);
             if (rc) return rc;
             LUTB_LAUNCH_CHECK();
         }
