@@ -78,7 +78,7 @@ __global__ void __launch_bounds__(512) product_hist_kernel(const float *__restri
 // MAXM > 0: the pair loop keeps the address plan of the detector's mixed anchors (at most MAXM) in registers
 // (product_pairs.cuh, MixedPlan); 0: plain eval_pair.  The plan costs about 5 registers per anchor: it pays where the
 // block's shared memory already limits an SM to one block (tables of 1024 rows and more: 257 against 286 ms per step on
-// the 2048-token configuration) and loses where it takes the second block away (256-row tables: 5.1 against 3.5 ms).
+// the 1024-token, 1024-row configuration) and loses where it takes the second block away (256-row tables: 5.1 against 3.5 ms).
 // HIST: the kernel evaluates every pair anyway, so it can count the selected rows on the way and write the histogram
 // the table-gradient contraction needs (1: uint16 [detector][row of the chunk][T], 2: fp32 [row of the chunk][detector][T],
 // the layouts of product_hist_kernel); the backward pass then launches no histogram kernel of its own.  Used where the
