@@ -309,6 +309,9 @@ class SparseConvNetWorkload:
         # the peer-memory strategies, whose barriers count their epochs on the device).
         self.graph = graph
         self.graph_ok_multi = bool(peer) or sharded == "peer"
+        # every step reads all tables: at least 16 synapses per row, 2^Nc rows per table (the exact figure, 382 MB, is
+        # set when the layers are built); far beyond L2, so steps run back to back without a flush
+        self.static_input_bytes = sum(g * g * per for _, _, g, per in self.LAYERS) * (1 << self.NC) * 16 * 4
         # internal: the reference's GradientType.Internal, the backward kernel applies W -= lr * dW in place (no dense
         # gradient, no optimiser pass); default: dense gradients + torch.optim.SGD
         self.internal = internal

@@ -30,7 +30,7 @@ def test_convnet_step_variants_agree_on_cpu():
             start = [l._weights.detach().clone() for l in wl.layers]
         params = [l._weights for l in wl.layers]
         if wl.sharded:
-            wl.sharded_sync = ShardedTableUpdate(wl.layers[:-1], wl.LR)
+            wl.table_sync = ShardedTableUpdate(wl.layers[:-1], wl.LR)
             params = params[-1:]
         wl.opt = None if wl.internal else torch.optim.SGD(params, lr=wl.LR)
         losses = []
@@ -47,3 +47,15 @@ def test_convnet_step_variants_agree_on_cpu():
         assert np.allclose(losses, dense_losses, rtol=1e-5), variant
         for li, (a, b) in enumerate(zip(w, dense_w)):
             assert torch.allclose(a, b, rtol=1e-5, atol=1e-7), f"{variant}: layer {li}"
+
+
+def test_both_arms_describe_the_workload_identically():
+    """`config` of the JSON line must not depend on whether the workload was set up on a device (our arm) or only
+    constructed (the reference arm)."""
+    import bench
+
+    for name in ("sparse_convnet", "sparse_convnet_eager", "sparse_convnet_sharded_peer_graph"):
+        cfg = bench.workload_config(bench.WORKLOADS[name](None))
+        assert cfg["l2"] == "inputs>L2" and cfg["per_gpu_units"] == 512
+    assert bench.workload_config(bench.WORKLOADS["sparse_convnet"](None)) == \
+        bench.workload_config(bench.WORKLOADS["sparse_convnet_eager"](None))
