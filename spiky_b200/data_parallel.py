@@ -347,8 +347,36 @@ class ShardedTableUpdate:
             plan["stream"] = torch.cuda.Stream(device=device)
             plan["done"] = None
             plan["hook"] = layer.register_forward_pre_hook(lambda module, inputs: self.wait_layer(module))
+            # the indices of a layer are known after its forward pass: they leave for the other ranks then (four fifths
+            # of the pair bytes), off the path between the layer's backward pass and its update
+            plan["idx_sent"] = False
+            layer._table_forward_hook = self._on_forward_peer
         torch.cuda.synchronize(device)
         dist.barrier(group=self.group)  # every rank's tables are in place before anyone stores into them
+
+    def _send_indices(self, layer, idx, stream):
+        """Narrows this rank's table indices into its slot of the gathered array and stores the slot into every other
+        rank's array (on `stream`, inside the caller's stream context)."""
+        from . import _native
+        plan, space = self._plans[id(layer)], self._space
+        li, n_i = plan["li"], idx.numel()
+        own = plan["idx_all"][self.rank * n_i:(self.rank + 1) * n_i]
+        own.copy_(idx)   # narrowing copy: the indices travel as uint8 / int16 when the table allows it
+        _native.peer_broadcast(space.others(f"i{li}"), self.rank * n_i * own.element_size(), own.data_ptr(),
+                               n_i * own.element_size(), stream.cuda_stream)
+
+    def _on_forward_peer(self, layer, idx, batch):
+        plan = self._plans[id(layer)]
+        if batch != self.batch_size:
+            raise ValueError(f"transport='peer' was set up for {self.batch_size} samples per rank, got {batch}")
+        # (the layer's forward pre-hook has waited for the previous step's exchange of this layer: every rank is done
+        # reading the gathered indices of that step)
+        stream = plan["stream"]
+        stream.wait_stream(torch.cuda.current_stream(idx.device))
+        with torch.cuda.stream(stream):
+            self._send_indices(layer, idx, stream)
+        plan["idx_sent"] = True
+        plan["idx_ref"] = idx   # referenced until the layer's stream has read it (its backward pass comes later)
 
     def _on_backward_peer(self, layer, idx, dY, batch):
         from . import _native
@@ -362,11 +390,10 @@ class ShardedTableUpdate:
         with torch.cuda.stream(stream):
             side = stream.cuda_stream
             idx_all, dY_all = plan["idx_all"], plan["dY_all"]
-            n_i, n_d = idx.numel(), dY.numel()
-            own = idx_all[self.rank * n_i:(self.rank + 1) * n_i]
-            own.copy_(idx)   # narrowing copy: the indices travel as uint8 / int16 when the table allows it
-            _native.peer_broadcast(space.others(f"i{li}"), self.rank * n_i * own.element_size(), own.data_ptr(),
-                                   n_i * own.element_size(), side)
+            n_d = dY.numel()
+            if not plan["idx_sent"]:   # (a backward pass whose forward pass ran without the hook, e.g. exchange timing)
+                self._send_indices(layer, idx, stream)
+            plan["idx_sent"] = False
             dYc = dY.contiguous()
             _native.peer_broadcast(space.ptrs[f"d{li}"], self.rank * n_d * 4, dYc.data_ptr(), n_d * 4, side)
             # the layer's stream reads these after the main stream has moved on: they stay referenced until the next
@@ -495,7 +522,11 @@ class ShardedTableUpdate:
                 plan.pop("idx_all", None)
                 plan.pop("dY_all", None)
                 plan.pop("last", None)
+                plan.pop("idx_ref", None)
                 plan.pop("hook").remove()
+            for layer in self.layers:
+                if getattr(layer, "_table_forward_hook", None) is not None:
+                    del layer._table_forward_hook
             torch.cuda.synchronize(device)
             dist.barrier(group=self.group)  # nobody still reads a buffer that is about to go
             self._space.release()

@@ -129,6 +129,11 @@ class _LUTFunction(torch.autograd.Function):
             out, idx, md, mk = layer.forward_step(x)
             ctx.save_for_backward(x, idx, md, mk)
             ctx.mode = "nonseq"
+            fwd_hook = getattr(layer, "_table_forward_hook", None)
+            if fwd_hook is not None:
+                # data-parallel sharded table update: the table indices can travel to the other ranks right away,
+                # while the rest of the forward pass and the backward pass above this layer still run
+                fwd_hook(layer, idx.reshape(-1), x.shape[0])
         elif layer._concatenation_product:
             out, *saved = layer.forward_step_concat(x, pos_embeddings)
             ctx.has_pe = saved[3] is not None
