@@ -462,6 +462,8 @@ int lutb_fp32_gemm(int kind, int32_t m, int32_t n, int32_t k, const float *a, in
  * lutb_peer_broadcast: copies `bytes` from `src` (this rank's memory) to dst[r] + dst_offset of every listed buffer
  * (own pointers or mapped ones) with plain stores; 16-byte aligned offsets copy fastest.  Same ordering contract as
  * lutb_peer_sgd_update.
+ * lutb_peer_copy: one asynchronous device-to-device copy on the stream (either side may be a mapped buffer of another
+ * rank: the copy then runs on a copy engine over NVLink, without SMs).
  * lutb_peer_barrier: a barrier over the ranks on the stream, without the host: flags[r] is rank r's array of
  * 2 * LUTB_MAX_PEER_RANKS 64-bit words in shareable memory (zero before the first use: one flag per rank, then the
  * rank's own barrier count); every rank calls it with the same epoch, 1, 2, 3, ..., or with epoch 0: the kernel then
@@ -480,6 +482,7 @@ int lutb_peer_open(const unsigned char *handle, void **ptr_out);
 int lutb_peer_close(void *ptr);
 int lutb_peer_broadcast(int32_t n_ranks, void *const *dst, int64_t dst_offset, const void *src, int64_t bytes,
                         void *stream);
+int lutb_peer_copy(void *dst, const void *src, size_t bytes, void *stream);
 int lutb_peer_barrier(int32_t n_ranks, int32_t rank, void *const *flags, uint64_t epoch, void *stream);
 int lutb_peer_sgd_update(int32_t n_ranks, int32_t rank, const float *const *grads, float *const *weights,
                          int64_t begin, int64_t end, float scale, void *stream);

@@ -116,6 +116,7 @@ SIGNATURES = {
     "lutb_peer_open": (_int, [ctypes.c_char_p, ctypes.POINTER(_vp)]),
     "lutb_peer_close": (_int, [_vp]),
     "lutb_peer_broadcast": (_int, [ctypes.c_int32, ctypes.POINTER(_vp), _i64, _vp, _i64, _vp]),
+    "lutb_peer_copy": (_int, [_vp, _vp, _size, _vp]),
     "lutb_peer_barrier": (_int, [ctypes.c_int32, ctypes.c_int32, ctypes.POINTER(_vp), ctypes.c_uint64, _vp]),
     "lutb_peer_sgd_update": (_int, [ctypes.c_int32, ctypes.c_int32, ctypes.POINTER(_vp), ctypes.POINTER(_vp), _i64, _i64,
                                     ctypes.c_float, _vp]),
@@ -217,6 +218,11 @@ def peer_broadcast(dst_ptrs, dst_offset, src_ptr, nbytes, stream):
     """Copies nbytes from src_ptr (local) to dst_ptrs[r] + dst_offset of every listed buffer (own or mapped)."""
     n = len(dst_ptrs)
     check(lib().lutb_peer_broadcast(n, (_vp * n)(*dst_ptrs), int(dst_offset), _vp(src_ptr), int(nbytes), _vp(stream)))
+
+
+def peer_copy(dst_ptr, src_ptr, nbytes, stream):
+    """One asynchronous device-to-device copy (a copy engine carries it when one side is another rank's buffer)."""
+    check(lib().lutb_peer_copy(_vp(dst_ptr), _vp(src_ptr), int(nbytes), _vp(stream)))
 
 
 def peer_barrier(rank, flag_ptrs, epoch, stream):

@@ -325,6 +325,15 @@ int lutb_peer_broadcast(int32_t n_ranks, void *const *dst, int64_t dst_offset, c
     return LUTB_OK;
 }
 
+int lutb_peer_copy(void *dst, const void *src, size_t bytes, void *stream) {
+    LUTB_REQUIRE((dst && src) || bytes == 0, LUTB_ERR_NULL, "lutb_peer_copy: null pointer");
+    if (bytes == 0) return LUTB_OK;
+    // a plain asynchronous copy: between this GPU's memory and a mapped buffer of another it runs on a copy engine
+    // over NVLink and occupies no SM
+    LUTB_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, (cudaStream_t)stream));
+    return LUTB_OK;
+}
+
 int lutb_peer_barrier(int32_t n_ranks, int32_t rank, void *const *flags, uint64_t epoch, void *stream) {
     LUTB_REQUIRE(n_ranks >= 1 && n_ranks <= kMaxPeerRanks, LUTB_ERR_SHAPE, "lutb_peer_barrier: 1 <= n_ranks <= %d",
                  kMaxPeerRanks);

@@ -8,6 +8,8 @@ tests).  Forward outputs and input gradients are per-sample and need no communic
 Replicas must be built from the same seeds: anchors are structure, not parameters, and are never
 synchronised afterwards; ``broadcast_structure`` copies rank 0's anchors and parameters once at start-up.
 """
+import os
+
 import torch
 import torch.distributed as dist
 
@@ -280,6 +282,9 @@ class ShardedTableUpdate:
         assert transport in ("collectives", "peer") and barrier in ("flags", "collective")
         self.transport = transport
         self.barrier = barrier
+        # peer transport, how the updated shares travel: "stores" = lutb_peer_broadcast (one kernel stores into all
+        # ranks), "engine" = one asynchronous copy per rank on the copy engines
+        self.share_copies = os.environ.get("LUTB_SHARE_COPIES", "stores")
         self.batch_size = batch_size
         self._space = None
         self._dirty = False
@@ -405,7 +410,13 @@ class ShardedTableUpdate:
             if not self.exchange_only:
                 self._apply(layer, W * batch, dY_all, idx_all, -self._learning_rate() / self.scale_div, c0, c1)
             lo, hi = plan["wcuts"][self.rank], plan["wcuts"][self.rank + 1]
-            if hi > lo:
+            if hi > lo and self.share_copies == "engine":
+                # one copy per peer on the copy engines: no SM is taken from the kernels beside it
+                for r in range(W):
+                    if r != self.rank:
+                        _native.peer_copy(space.ptrs[f"w{li}"][r] + lo * 4, space.ptrs[f"w{li}"][self.rank] + lo * 4,
+                                          (hi - lo) * 4, side)
+            elif hi > lo:
                 _native.peer_broadcast(space.others(f"w{li}"), lo * 4, space.ptrs[f"w{li}"][self.rank] + lo * 4,
                                        (hi - lo) * 4, side)
             # every rank's share of this layer has landed in this rank's tables, nobody still reads the gathered pairs
