@@ -367,7 +367,8 @@ class SparseConvNetWorkload:
         if self.sharded:
             from spiky_b200.data_parallel import ShardedTableUpdate
             self.table_sync = ShardedTableUpdate(self.layers[:-1], self.LR, batch_size=self.B,
-                                                 transport="peer" if self.sharded == "peer" else "collectives")
+                                                 transport="peer" if self.sharded == "peer" else "collectives",
+                                                 share_copies=os.environ.get("BENCH_SHARE_COPIES", "stores"))
             # a replayed graph joins all its streams at its end: no overlap into the next step then
             self.overlaps_steps = self.sharded == "peer" and self.table_sync.world > 1 and not self.graph
             params = params[-1:]
@@ -1205,6 +1206,8 @@ def run_ours(args):
         wl.step_device()
         finish_step(wl)
     _try_capture(wl, world, device)
+    if world > 1:
+        dp_strategy = _dp_strategy(wl)
     dp_trial = None
     if world > 1 and args.workload == DEFAULT_WORKLOAD and args.dp == "auto":
         # Ways to keep the replicas' tables equal (same SGD step, spiky_b200/data_parallel.py): all-reduce the dense

@@ -8,8 +8,6 @@ tests).  Forward outputs and input gradients are per-sample and need no communic
 Replicas must be built from the same seeds: anchors are structure, not parameters, and are never
 synchronised afterwards; ``broadcast_structure`` copies rank 0's anchors and parameters once at start-up.
 """
-import os
-
 import torch
 import torch.distributed as dist
 
@@ -266,7 +264,7 @@ class ShardedTableUpdate:
     """
 
     def __init__(self, layers, lr, group=None, average=True, weight_gather="padded", transport="collectives",
-                 batch_size=None, barrier="flags"):
+                 batch_size=None, barrier="flags", share_copies="stores"):
         from .lut_layer import GradientType, LUTLayerBasic
 
         # how the updated shares travel: "padded" = one equal-size all-gather through a staging buffer (shares are
@@ -283,8 +281,10 @@ class ShardedTableUpdate:
         self.transport = transport
         self.barrier = barrier
         # peer transport, how the updated shares travel: "stores" = lutb_peer_broadcast (one kernel stores into all
-        # ranks), "engine" = one asynchronous copy per rank on the copy engines
-        self.share_copies = os.environ.get("LUTB_SHARE_COPIES", "stores")
+        # ranks), "engine" = one asynchronous copy per rank on the copy engines (no SM used; measured no faster: 0.98
+        # against 0.96 ms per step at two GPUs)
+        assert share_copies in ("stores", "engine")
+        self.share_copies = share_copies
         self.batch_size = batch_size
         self._space = None
         self._dirty = False
