@@ -261,6 +261,14 @@ class ShardedTableUpdate:
     Use: ``sync = ShardedTableUpdate(layers, lr)`` once; run forward / backward as usual (each layer's backward calls
     back into this object; the layer's ``_weights`` gets no ``.grad``); call ``sync.wait()`` before the next forward.
     The exchange and the update of a layer run on a side stream and overlap the backward pass of the layers below.
+
+    ``transport="peer"`` (one node, CUDA, ``batch_size`` given): nothing goes through collectives.  The tables and the
+    gathered arrays live in buffers every rank has mapped; the indices of a layer leave for the other ranks right
+    after its forward pass, its output gradients after its backward pass (``lutb_peer_broadcast``: plain stores into
+    the other ranks' memory), the ranks meet through flags in peer memory (``lutb_peer_barrier``), each updates its
+    share and stores it into every rank's tables.  Every layer has its own stream and barrier channel; the next
+    forward pass of a layer waits for that layer's exchange only (``wait()`` is then optional).  The launches carry no
+    per-step arguments, so the whole step, exchange included, can be captured into a CUDA graph and replayed.
     """
 
     def __init__(self, layers, lr, group=None, average=True, weight_gather="padded", transport="collectives",
