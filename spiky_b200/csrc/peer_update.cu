@@ -5,9 +5,10 @@
 // (CUDA IPC; NVLink / NVSwitch carries the accesses).  Rank r owns the slice [begin, end) of the tables: its kernel
 // fetches that slice of every rank's gradient (its own from HBM, the others over the links), sums them in rank order,
 // applies  w <- w - scale * sum  to its own copy and stores the new values into every rank's tables (peer stores).
-// Bytes over the links per rank: (G-1)/G of the tables in, the same out, in both directions at once - what a ring
-// all-reduce moves in two phases, but single hop, with the optimiser pass folded in and no staging buffers.  Every
-// element is computed by exactly one rank, so the replicas stay bit-identical.
+// Bytes over the links: a rank fetches (G-1)/G of the gradient bytes and stores (G-1)/G of the table bytes, and serves
+// as much to the others: 2 (G-1)/G of the table bytes per GPU and direction, what a ring all-reduce moves in two
+// phases, but single hop, with the optimiser pass folded in and no staging buffers.  Every element is computed by
+// exactly one rank, so the replicas stay bit-identical.
 //
 // The update kernel waits on no other rank: the caller orders it after every rank's gradient is complete and orders
 // the next reader of the tables after every rank's kernel (lutb_peer_barrier below, or a collective of the process
@@ -31,8 +32,8 @@ struct PeerArgs {
     float scale;
 };
 
-// The body of the slice is cut into pieces of kPieceFloats (1024 floats; 512 beyond 8 ranks); piece c belongs to block c % gridDim.x (one block per SM).
-// A producer warp streams, per piece, the n gradient pieces (the other ranks' over NVLink, this rank's from HBM) and the
+// The body of the slice is cut into pieces of kPieceFloats (1024 floats; 512 beyond 8 ranks); piece c belongs to block
+// c % gridDim.x (one block per SM).  A producer warp streams, per piece, the n gradient pieces (the other ranks' over NVLink, this rank's from HBM) and the
 // piece of this rank's tables into one stage of a shared-memory ring with bulk copies (cp.async.bulk + mbarrier
 // transaction counts): a peer access takes microseconds, so the link is only kept busy by the bytes in flight, and the
 // copy engine holds a whole ring of them per SM without occupying registers or warps.  Eight consumer warps add the
